@@ -1,0 +1,361 @@
+"""The cache manager: paged keys and values with a block table per request, and state slots.
+
+Layers with the same needs (``kv_heads``, ``head_dim``, ``window``) form a *group*;
+each group has its own pool of pages, its own key/value storage and its own block
+tables, so a model whose layers differ (all keys here, a window of them there) gives
+every kind of layer pages of the right shape and gives a window's pages back as soon
+as the window has passed them.  The reference has one geometry for all layers
+(src/kv_cache/paged.cpp:100-104, src/model/cuda_llama.cpp:147-154); groups are this
+engine's own.
+
+A page id is valid in every layer of its group (as in the reference, where a block
+spans all layers).  Storage of one group:
+``[layer, key|value, page, kv_head, slot in page, head_dim]``.
+
+Pages are reserved before a step (:meth:`CacheManager.extend`) and a request's
+length is published after it (:meth:`CacheManager.commit`), which is the reference's
+transaction boundary (src/runtime/cpu_engine.cpp:191, 207, 235).  Next to the pages
+every request owns one *state slot*: a row in each per-layer state tensor that a
+mixer asked for (fixed size, zeroed at admission), and a row in the block tables.
+"""
+from __future__ import annotations
+
+import dataclasses
+from collections import deque
+from typing import Deque, Dict, Hashable, List, Mapping, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .pages import OutOfPages, PagePool
+
+
+@dataclasses.dataclass(frozen=True)
+class KvNeed:
+    """What an attention-like mixer needs of the cache."""
+    kv_heads: int
+    head_dim: int
+    window: Optional[int] = None     # None: every earlier key stays live
+
+
+@dataclasses.dataclass(frozen=True)
+class StateNeed:
+    """Per-request state of fixed size that a mixer keeps between steps."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class CacheGroup:
+    def __init__(self, index: int, need: KvNeed, entries: List[int], num_pages: int,
+                 page_size: int, max_requests: int, max_pages_per_request: int,
+                 dtype: torch.dtype, device: torch.device, poison: bool) -> None:
+        self.index = index
+        self.need = need
+        self.entries = entries                      # schedule entries that own a layer here
+        self.pool = PagePool(num_pages)
+        self.page_size = page_size
+        self.poison = poison
+        shape = (len(entries), 2, num_pages, need.kv_heads, page_size, need.head_dim)
+        if poison:
+            self.storage = torch.full(shape, float("nan"), dtype=dtype, device=device)
+        else:
+            self.storage = torch.zeros(shape, dtype=dtype, device=device)
+        self.host_tables = np.full((max_requests, max_pages_per_request), -1, dtype=np.int32)
+        self.device_tables = torch.full((max_requests, max_pages_per_request), -1,
+                                        dtype=torch.int32, device=device)
+        self.dirty = False
+
+    @property
+    def bytes_per_token(self) -> int:
+        return (len(self.entries) * 2 * self.need.kv_heads * self.need.head_dim
+                * self.storage.element_size())
+
+
+@dataclasses.dataclass
+class RequestCache:
+    slot: int
+    length: int = 0                                  # tokens whose keys/values are published
+    reserved: int = 0                                # tokens the tables have pages for
+    tables: List[List[int]] = dataclasses.field(default_factory=list)   # per group, -1 = gone
+    first_live: List[int] = dataclasses.field(default_factory=list)     # per group
+
+
+class CacheManager:
+    def __init__(self, kv_needs: Mapping[int, KvNeed], state_needs: Mapping[int, StateNeed],
+                 page_size: int, num_pages: int, max_requests: int, max_positions: int,
+                 dtype: torch.dtype, device: torch.device, poison: bool = False) -> None:
+        if page_size <= 0 or max_requests <= 0 or max_positions <= 0:
+            raise ValueError("page_size, max_requests and max_positions must be positive")
+        self.page_size = int(page_size)
+        self.max_requests = int(max_requests)
+        self.max_positions = int(max_positions)
+        self.max_pages_per_request = -(-self.max_positions // self.page_size)
+        self.dtype = dtype
+        self.device = device
+        self.groups: List[CacheGroup] = []
+        self._entry_place: Dict[int, Tuple[int, int]] = {}
+        by_need: Dict[KvNeed, List[int]] = {}
+        for entry in sorted(kv_needs):
+            by_need.setdefault(kv_needs[entry], []).append(entry)
+        for need, entries in by_need.items():
+            group = CacheGroup(len(self.groups), need, entries, num_pages, self.page_size,
+                               self.max_requests, self.max_pages_per_request, dtype, device, poison)
+            for layer, entry in enumerate(entries):
+                self._entry_place[entry] = (group.index, layer)
+            self.groups.append(group)
+        self.states: Dict[int, torch.Tensor] = {
+            entry: torch.zeros((self.max_requests, *need.shape), dtype=need.dtype, device=device)
+            for entry, need in state_needs.items()}
+        self._free_slots: Deque[int] = deque(range(self.max_requests))
+        self._requests: Dict[Hashable, RequestCache] = {}
+
+    # ------------------------------------------------------------------ lookups
+
+    def group_of(self, entry: int) -> CacheGroup:
+        return self.groups[self._entry_place[entry][0]]
+
+    def layer_storage(self, entry: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Key and value storage ``[page, kv_head, slot, head_dim]`` of one schedule entry."""
+        group_index, layer = self._entry_place[entry]
+        storage = self.groups[group_index].storage
+        return storage[layer, 0], storage[layer, 1]
+
+    def state(self, entry: int) -> torch.Tensor:
+        return self.states[entry]
+
+    def has(self, request: Hashable) -> bool:
+        return request in self._requests
+
+    def slot(self, request: Hashable) -> int:
+        return self._requests[request].slot
+
+    def length(self, request: Hashable) -> int:
+        return self._requests[request].length
+
+    def live_requests(self) -> List[Hashable]:
+        return list(self._requests)
+
+    @property
+    def free_slots(self) -> int:
+        return len(self._free_slots)
+
+    def free_pages(self) -> List[int]:
+        return [group.pool.free_pages for group in self.groups]
+
+    def bytes_per_token(self) -> int:
+        return sum(group.bytes_per_token for group in self.groups)
+
+    # --------------------------------------------------------------- page maths
+
+    def pages_for(self, tokens: int) -> int:
+        return -(-tokens // self.page_size)
+
+    def pages_to_extend(self, request: Hashable, new_length: int) -> List[int]:
+        """Pages each group must add so that positions ``[0, new_length)`` have a place."""
+        record = self._requests[request]
+        return [max(0, self.pages_for(new_length) - len(table)) for table in record.tables]
+
+    def max_extend(self, request: Hashable, desired: int,
+                   available: Optional[Sequence[int]] = None) -> int:
+        """The most tokens (``<= desired``) that can be appended with ``available`` free pages
+        per group (default: what the pools hold now)."""
+        record = self._requests[request]
+        if available is None:
+            available = self.free_pages()
+        base = record.reserved
+        room = min(self.max_positions - base, desired)
+        best = max(room, 0)
+        for table, free in zip(record.tables, available):
+            tokens_with_pages = (len(table) + free) * self.page_size
+            best = min(best, max(0, tokens_with_pages - base))
+        return best
+
+    def max_extend_new(self, desired: int, available: Optional[Sequence[int]] = None) -> int:
+        """Same for a request that is not admitted yet (no pages, length 0)."""
+        if available is None:
+            available = self.free_pages()
+        best = min(desired, self.max_positions)
+        for free in available:
+            best = min(best, free * self.page_size)
+        return max(best, 0)
+
+    # ------------------------------------------------------------- life of a request
+
+    def admit(self, request: Hashable) -> int:
+        """Give the request a state slot (zeroed) and empty block tables."""
+        if request in self._requests:
+            raise KeyError(f"request {request!r} is already admitted")
+        if not self._free_slots:
+            raise OutOfPages("no state slot is free")
+        slot = self._free_slots.popleft()
+        for tensor in self.states.values():
+            tensor[slot].zero_()
+        for group in self.groups:
+            group.host_tables[slot, :] = -1
+            group.dirty = True
+        self._requests[request] = RequestCache(
+            slot=slot, tables=[[] for _ in self.groups], first_live=[0 for _ in self.groups])
+        return slot
+
+    def extend(self, request: Hashable, new_length: int) -> List[int]:
+        """Reserve pages for positions up to ``new_length`` in every group, or raise
+        :class:`OutOfPages` and change nothing.  Returns the pages added per group."""
+        record = self._requests[request]
+        if new_length > self.max_positions:
+            raise ValueError(f"length {new_length} exceeds max_positions {self.max_positions}")
+        if new_length < record.length:
+            raise ValueError("a request's cache never shrinks")
+        needed = self.pages_to_extend(request, new_length)
+        for group, count in zip(self.groups, needed):
+            if count > group.pool.free_pages:
+                raise OutOfPages(f"group {group.index}: {count} pages needed, "
+                                 f"{group.pool.free_pages} free")
+        for group, table, count in zip(self.groups, record.tables, needed):
+            if count == 0:
+                continue
+            pages = group.pool.allocate(count)
+            start = len(table)
+            table.extend(pages)
+            group.host_tables[record.slot, start:start + count] = pages
+            group.dirty = True
+        record.reserved = max(record.reserved, new_length)
+        return needed
+
+    def commit(self, request: Hashable, new_length: int) -> None:
+        """Publish the length after a step that succeeded; give back pages a window passed."""
+        record = self._requests[request]
+        if new_length < record.length or new_length > record.reserved:
+            raise ValueError(f"cannot publish length {new_length}: published {record.length}, "
+                             f"reserved {record.reserved}")
+        record.length = new_length
+        for index, group in enumerate(self.groups):
+            window = group.need.window
+            if window is None:
+                continue
+            # the next query sits at position new_length and reads keys >= new_length-window+1
+            dead_pages = max(0, new_length - window + 1) // self.page_size
+            table = record.tables[index]
+            first = record.first_live[index]
+            if dead_pages > first:
+                gone = [table[i] for i in range(first, dead_pages)]
+                self._give_back(group, gone)
+                for i in range(first, dead_pages):
+                    table[i] = -1
+                group.host_tables[record.slot, first:dead_pages] = -1
+                group.dirty = True
+                record.first_live[index] = dead_pages
+
+    def rollback(self, request: Hashable) -> None:
+        """Give back pages reserved beyond the published length (a step that failed)."""
+        record = self._requests[request]
+        keep = self.pages_for(record.length)
+        for index, group in enumerate(self.groups):
+            table = record.tables[index]
+            if len(table) > keep:
+                extra = [page for page in table[keep:] if page >= 0]
+                self._give_back(group, extra)
+                group.host_tables[record.slot, keep:len(table)] = -1
+                del table[keep:]
+                group.dirty = True
+        record.reserved = record.length
+
+    def release(self, request: Hashable) -> int:
+        """The request is over: give back its pages (in table order) and its slot."""
+        record = self._requests.pop(request)
+        freed = 0
+        for index, group in enumerate(self.groups):
+            pages = [page for page in record.tables[index] if page >= 0]
+            freed += self._give_back(group, pages)
+            group.host_tables[record.slot, :] = -1
+            group.dirty = True
+        self._free_slots.append(record.slot)
+        return freed
+
+    def fork(self, source: Hashable, request: Hashable, tokens: int) -> int:
+        """Admit ``request`` sharing the first ``tokens`` positions of ``source``.
+
+        Only whole pages are shared, so nothing is ever copied on write
+        (src/kv_cache/paged.cpp:535-620).  Groups with a window cannot share."""
+        if tokens <= 0 or tokens % self.page_size != 0:
+            raise ValueError("a shared prefix must be a positive multiple of the page size")
+        parent = self._requests[source]
+        if tokens > parent.length:
+            raise ValueError("cannot share more than the source has published")
+        if any(group.need.window is not None for group in self.groups):
+            raise ValueError("groups with a window do not share prefixes")
+        if self.states:
+            raise ValueError("requests with per-request state do not share prefixes")
+        slot = self.admit(request)
+        record = self._requests[request]
+        count = tokens // self.page_size
+        for index, group in enumerate(self.groups):
+            pages = parent.tables[index][:count]
+            group.pool.share(pages)
+            record.tables[index] = list(pages)
+            group.host_tables[slot, :count] = pages
+            group.dirty = True
+        record.length = tokens
+        record.reserved = tokens
+        return slot
+
+    def _give_back(self, group: CacheGroup, pages: List[int]) -> int:
+        if not pages:
+            return 0
+        before = group.pool.free_pages
+        freed = group.pool.release(pages)
+        if group.poison and freed:
+            # pages that just became free are the tail of the ring
+            newly_free = list(group.pool._free)[before:]
+            index = torch.tensor(newly_free, dtype=torch.long, device=group.storage.device)
+            group.storage[:, :, index] = float("nan")
+        return freed
+
+    # ------------------------------------------------------------------- device
+
+    def sync_tables(self) -> None:
+        """Copy block tables that changed since the last step to the device."""
+        for group in self.groups:
+            if group.dirty:
+                group.device_tables.copy_(torch.from_numpy(group.host_tables), non_blocking=True)
+                group.dirty = False
+
+    # -------------------------------------------------------------------- audit
+
+    def check(self) -> None:
+        """No page lost, held twice by mistake, or freed twice; no slot lost."""
+        slots = [record.slot for record in self._requests.values()]
+        assert len(slots) == len(set(slots)), "a state slot is held twice"
+        assert sorted(slots + list(self._free_slots)) == list(range(self.max_requests)), \
+            "a state slot is lost"
+        for index, group in enumerate(self.groups):
+            group.pool.check()
+            holders = [0] * group.pool.num_pages
+            for record in self._requests.values():
+                table = record.tables[index]
+                live = [page for page in table if page >= 0]
+                assert len(live) == len(set(live)), "a request holds a page twice"
+                for page in live:
+                    holders[page] += 1
+                assert len(table) >= self.pages_for(record.length), "published tokens lack a page"
+                row = group.host_tables[record.slot]
+                assert list(row[:len(table)]) == table, "host block table out of date"
+                assert (row[len(table):] == -1).all(), "stale block table entries"
+            for page in range(group.pool.num_pages):
+                assert holders[page] == group.pool.refcount(page), \
+                    f"group {index} page {page}: {holders[page]} holders, " \
+                    f"refcount {group.pool.refcount(page)}"
+
+    def stats(self) -> Dict[str, object]:
+        return {
+            "requests": len(self._requests),
+            "free_slots": len(self._free_slots),
+            "groups": [{
+                "window": group.need.window,
+                "layers": len(group.entries),
+                "pages": group.pool.num_pages,
+                "free_pages": group.pool.free_pages,
+                "peak_pages_in_use": group.pool.peak_in_use,
+                "allocations": group.pool.allocation_count,
+                "reuses": group.pool.reuse_count,
+            } for group in self.groups],
+        }

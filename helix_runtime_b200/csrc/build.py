@@ -1,0 +1,131 @@
+"""Compile the kernel library for sm_100a with nvcc and return the path of the shared object.
+
+The sources are plain CUDA with a C interface (no framework headers), so each file
+compiles in seconds and the files compile in parallel.  The library is built in the
+source tree (``csrc/_build``) so that a checkout carries it to wherever it runs; if
+the tree is read-only the build goes to a per-user folder under the system's
+temporary directory.  A hash of the sources and flags names the library, so a stale
+build is never loaded.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from typing import List, Optional
+
+CSRC = os.path.dirname(os.path.abspath(__file__))
+SOURCES = (
+    "hx_elementwise.cu",
+    "hx_gemm_simt.cu",
+    "hx_gemm_tc.cu",
+    "hx_attention.cu",
+    "hx_sampling.cu",
+)
+HEADERS = ("hx_common.cuh",)
+NVCC_FLAGS = (
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fvisibility=hidden",
+    "--expt-relaxed-constexpr",
+)
+
+
+def find_nvcc() -> str:
+    candidates = [os.environ.get("HELIX_NVCC"), shutil.which("nvcc"),
+                  os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"),
+                  "/usr/local/cuda/bin/nvcc"]
+    for candidate in candidates:
+        if candidate and os.path.isfile(candidate) and os.access(candidate, os.X_OK):
+            return candidate
+    raise RuntimeError("nvcc was not found (set HELIX_NVCC or CUDA_HOME); the engine has no "
+                       "fallback without its CUDA kernels")
+
+
+def source_hash(extra: str = "") -> str:
+    digest = hashlib.sha256()
+    for name in (*SOURCES, *HEADERS):
+        with open(os.path.join(CSRC, name), "rb") as source:
+            digest.update(name.encode())
+            digest.update(source.read())
+    digest.update(" ".join(NVCC_FLAGS).encode())
+    digest.update(extra.encode())
+    return digest.hexdigest()[:16]
+
+
+def _writable_build_dir() -> str:
+    preferred = os.path.join(CSRC, "_build")
+    try:
+        os.makedirs(preferred, exist_ok=True)
+        probe = os.path.join(preferred, f".probe{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return preferred
+    except OSError:
+        fallback = os.path.join(tempfile.gettempdir(), f"helix_runtime_b200_{os.getuid()}")
+        os.makedirs(fallback, exist_ok=True)
+        return fallback
+
+
+def library_path(build_dir: Optional[str] = None) -> str:
+    return os.path.join(build_dir or _writable_build_dir(), f"libhelix_b200_{source_hash()}.so")
+
+
+def _run(command: List[str]) -> None:
+    result = subprocess.run(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if result.returncode != 0:
+        raise RuntimeError("command failed: " + " ".join(command) + "\n" + result.stdout)
+
+
+def build(verbose: bool = True, force: bool = False) -> str:
+    """Build if needed; print a line now and then while compiling."""
+    build_dir = _writable_build_dir()
+    target = library_path(build_dir)
+    if os.path.exists(target) and not force:
+        return target
+    nvcc = find_nvcc()
+    started = time.time()
+    stop = threading.Event()
+
+    def say(message: str) -> None:
+        if verbose:
+            print(f"[helix_runtime_b200] {message}", file=sys.stderr, flush=True)
+
+    def heartbeat() -> None:
+        while not stop.wait(10.0):
+            say(f"still compiling CUDA kernels for sm_100a ({time.time() - started:.0f} s)")
+
+    say(f"compiling {len(SOURCES)} CUDA files for sm_100a into {build_dir} (first use only)")
+    thread = threading.Thread(target=heartbeat, daemon=True)
+    thread.start()
+    tag = f"{os.getpid()}_{source_hash()}"
+    objects = [os.path.join(build_dir, f"{os.path.splitext(name)[0]}_{tag}.o") for name in SOURCES]
+    try:
+        with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+            jobs = [pool.submit(_run, [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c",
+                                       os.path.join(CSRC, name), "-o", obj])
+                    for name, obj in zip(SOURCES, objects)]
+            for job in jobs:
+                job.result()
+        partial = target + f".{os.getpid()}.tmp"
+        _run([nvcc, "-shared", "-o", partial, *objects, "-cudart", "static"])
+        os.replace(partial, target)
+    finally:
+        stop.set()
+        for obj in objects:
+            if os.path.exists(obj):
+                os.remove(obj)
+    say(f"kernel library ready after {time.time() - started:.0f} s: {target}")
+    return target
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv))

@@ -1,0 +1,348 @@
+// Paged causal attention over block tables, float32 arithmetic, any batch shape.
+//
+// Every query token of the flattened batch attends to the keys of its own request at
+// absolute positions [lo, position], lo = 0 or position - window + 1; this step's
+// own keys are already in the pages (the rotary/append kernel ran first), so prompt
+// portions and single decode tokens are the same case.  The reference computes the
+// same thing in three stages through a materialised score tensor
+// (src/attention/cuda_paged.cu:108-192: scores, softmax, values); here one warp
+// walks the keys of one (token, head, key split) with an online softmax and never
+// stores a score.
+//
+// Exactness: dot products, the running maximum, exp, the running sum and the
+// weighted value sum are float32.  The order of every sum is a function of the
+// token's own position only (32-key chunks and `split_keys`-wide splits anchored at
+// lo, merged in ascending order), so a token's result does not depend on how the
+// batch was cut, what else is in it, or which pages hold the keys.
+#include "hx_common.cuh"
+
+namespace {
+
+constexpr int WARPS_PER_BLOCK = 4;
+constexpr int MAX_HEAD_DIM = 256;
+
+template <typename T, int VEC> struct VecLoad;
+template <> struct VecLoad<float, 4> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  }
+};
+template <> struct VecLoad<float, 2> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[2]) {
+    const float2 r = *reinterpret_cast<const float2*>(p);
+    v[0] = r.x; v[1] = r.y;
+  }
+};
+template <> struct VecLoad<float, 8> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
+template <> struct VecLoad<__nv_bfloat16, 2> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[2]) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    v[0] = f.x; v[1] = f.y;
+  }
+};
+template <> struct VecLoad<__nv_bfloat16, 4> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+};
+template <> struct VecLoad<__nv_bfloat16, 8> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.z));
+    const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.w));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  }
+};
+
+struct AttentionArgs {
+  const void* q;
+  int ldq;
+  const void* k_cache;
+  const void* v_cache;
+  const int* positions;
+  const int* token_request;
+  const int* request_table_row;
+  const int* block_tables;
+  int table_stride;
+  void* out;
+  int ldo;
+  float* partial;   // [tokens * heads][max_splits][head_dim + 2], only when max_splits > 1
+  int tokens;
+  int heads;
+  int kv_heads;
+  int head_dim;
+  int page_size;
+  int num_pages;
+  int window;       // 0: every earlier key
+  float scale;
+  int split_keys;
+  int max_splits;
+  int* status;
+};
+
+__device__ __forceinline__ void key_range(const AttentionArgs& a, int token, int& lo, int& hi) {
+  const int position = a.positions[token];
+  hi = position + 1;
+  lo = a.window > 0 ? max(0, hi - a.window) : 0;
+}
+
+// DPL: value coordinates per lane in the value phase (32 * DPL >= head_dim);
+// VEC: elements per load in the key phase.
+template <typename T, int DPL, int VEC>
+__global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(AttentionArgs a) {
+  __shared__ float q_shared[WARPS_PER_BLOCK][MAX_HEAD_DIM];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * WARPS_PER_BLOCK + warp;
+  const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
+  if (item >= items) return;
+  const int split = static_cast<int>(item % a.max_splits);
+  const int token_head = static_cast<int>(item / a.max_splits);
+  const int head = token_head % a.heads;
+  const int token = token_head / a.heads;
+
+  int lo, hi;
+  key_range(a, token, lo, hi);
+  const int n_splits = (hi - lo + a.split_keys - 1) / a.split_keys;
+  if (split >= n_splits) return;
+  const int begin = lo + split * a.split_keys;
+  const int end = min(begin + a.split_keys, hi);
+
+  const int D = a.head_dim;
+  const int kv_head = head / (a.heads / a.kv_heads);
+  const T* q = static_cast<const T*>(a.q) + static_cast<size_t>(token) * a.ldq +
+               static_cast<size_t>(head) * D;
+  float* qs = q_shared[warp];
+  for (int d = lane; d < D; d += 32) qs[d] = hx_to_float<T>(q[d]);
+  __syncwarp();
+
+  const int table_row = a.request_table_row[a.token_request[token]];
+  const int* table = a.block_tables + static_cast<size_t>(table_row) * a.table_stride;
+  const T* k_cache = static_cast<const T*>(a.k_cache);
+  const T* v_cache = static_cast<const T*>(a.v_cache);
+
+  float acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
+  float running_max = -INFINITY;
+  float running_sum = 0.0f;
+  const int my_dim = lane * DPL;
+
+  for (int chunk = begin; chunk < end; chunk += 32) {
+    const int key = chunk + lane;
+    bool valid = key < end;
+    int row = 0;
+    if (valid) {
+      const int page = table[key / a.page_size];
+      if (page < 0 || page >= a.num_pages) {
+        if (a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
+        valid = false;
+      } else {
+        row = (page * a.kv_heads + kv_head) * a.page_size + key % a.page_size;
+      }
+    }
+    float score = -INFINITY;
+    if (valid) {
+      const T* k = k_cache + static_cast<size_t>(row) * D;
+      float dot = 0.0f;
+      for (int d = 0; d < D; d += VEC) {
+        float kv[VEC];
+        VecLoad<T, VEC>::load(k + d, kv);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) dot = fmaf(qs[d + i], kv[i], dot);
+      }
+      score = dot * a.scale;
+    }
+    float chunk_max = score;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+      chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, offset));
+    const float new_max = fmaxf(running_max, chunk_max);
+    // a chunk whose keys are all unreadable leaves the state as it is
+    if (new_max == -INFINITY) continue;
+    const float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
+    const float probability = valid ? expf(score - new_max) : 0.0f;
+    float chunk_sum = probability;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+      chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, offset);
+    running_sum = running_sum * correction + chunk_sum;
+    running_max = new_max;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] *= correction;
+
+    const int keys_here = min(32, end - chunk);
+    for (int j = 0; j < keys_here; ++j) {
+      const float p = __shfl_sync(0xffffffffu, probability, j);
+      const int v_row = __shfl_sync(0xffffffffu, row, j);
+      if (p != 0.0f && my_dim < D) {
+        float vv[DPL];
+        VecLoad<T, DPL>::load(v_cache + static_cast<size_t>(v_row) * D + my_dim, vv);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p, vv[i], acc[i]);
+      }
+    }
+  }
+
+  if (a.max_splits == 1 || n_splits == 1) {
+    if (my_dim < D) {
+      const float inverse = 1.0f / running_sum;
+      T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
+               static_cast<size_t>(head) * D + my_dim;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) out[i] = hx_from_float<T>(acc[i] * inverse);
+    }
+  } else {
+    float* part = a.partial +
+                  (static_cast<size_t>(token_head) * a.max_splits + split) * (D + 2);
+    if (my_dim < D) {
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) part[my_dim + i] = acc[i];
+    }
+    if (lane == 0) {
+      part[D] = running_max;
+      part[D + 1] = running_sum;
+    }
+  }
+}
+
+// Combine the splits of one (token, head) in ascending order.
+template <typename T>
+__global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void attention_merge_kernel(AttentionArgs a) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long token_head = static_cast<long long>(blockIdx.x) * WARPS_PER_BLOCK + warp;
+  if (token_head >= static_cast<long long>(a.tokens) * a.heads) return;
+  const int head = static_cast<int>(token_head % a.heads);
+  const int token = static_cast<int>(token_head / a.heads);
+  int lo, hi;
+  key_range(a, token, lo, hi);
+  const int n_splits = (hi - lo + a.split_keys - 1) / a.split_keys;
+  if (n_splits <= 1) return;
+  const int D = a.head_dim;
+  const float* part = a.partial + static_cast<size_t>(token_head) * a.max_splits * (D + 2);
+  float total_max = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) total_max = fmaxf(total_max, part[s * (D + 2) + D]);
+  float total_sum = 0.0f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float m = part[s * (D + 2) + D];
+    const float w = m == -INFINITY ? 0.0f : expf(m - total_max);
+    total_sum += part[s * (D + 2) + D + 1] * w;
+  }
+  const float inverse = 1.0f / total_sum;
+  T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
+           static_cast<size_t>(head) * D;
+  for (int d = lane; d < D; d += 32) {
+    float value = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float m = part[s * (D + 2) + D];
+      const float w = m == -INFINITY ? 0.0f : expf(m - total_max);
+      value = fmaf(part[s * (D + 2) + d], w, value);
+    }
+    out[d] = hx_from_float<T>(value * inverse);
+  }
+}
+
+template <typename T, int DPL, int VEC>
+void launch_main(const AttentionArgs& a, cudaStream_t stream) {
+  const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
+  const int blocks = static_cast<int>((items + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
+  paged_attention_kernel<T, DPL, VEC><<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>(a);
+}
+
+template <typename T, int DPL>
+int dispatch_vec(const AttentionArgs& a, cudaStream_t stream) {
+  constexpr int kMaxVec = sizeof(T) == 2 ? 8 : 4;
+  if (kMaxVec == 8 && a.head_dim % 8 == 0) {
+    launch_main<T, DPL, 8>(a, stream);
+  } else if (a.head_dim % 4 == 0) {
+    launch_main<T, DPL, 4>(a, stream);
+  } else {
+    launch_main<T, DPL, 2>(a, stream);
+  }
+  return HX_OK;
+}
+
+template <typename T>
+int dispatch(const AttentionArgs& a, cudaStream_t stream) {
+  int rc;
+  if (a.head_dim <= 64 && a.head_dim % 2 == 0) {
+    rc = dispatch_vec<T, 2>(a, stream);
+  } else if (a.head_dim <= 128 && a.head_dim % 4 == 0) {
+    rc = dispatch_vec<T, 4>(a, stream);
+  } else if (a.head_dim <= 256 && a.head_dim % 8 == 0) {
+    rc = dispatch_vec<T, 8>(a, stream);
+  } else {
+    hx_set_error("hx_paged_attention: head_dim %d is not supported (even up to 64, a multiple of "
+                 "4 up to 128, a multiple of 8 up to 256)", a.head_dim);
+    return HX_ERR_UNSUPPORTED;
+  }
+  if (rc != HX_OK) return rc;
+  if (a.max_splits > 1) {
+    const long long pairs = static_cast<long long>(a.tokens) * a.heads;
+    const int blocks = static_cast<int>((pairs + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
+    attention_merge_kernel<T><<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>(a);
+  }
+  return HX_OK;
+}
+
+}  // namespace
+
+// Floats of scratch the call needs in `partial` (0 when max_splits == 1).
+HX_API long long hx_paged_attention_scratch_floats(int tokens, int heads, int head_dim,
+                                                   int max_splits) {
+  if (max_splits <= 1) return 0;
+  return static_cast<long long>(tokens) * heads * max_splits * (head_dim + 2);
+}
+
+HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                              int dtype, const int* positions, const int* token_request,
+                              const int* request_table_row, const int* block_tables,
+                              int table_stride, void* out, int ldo, float* partial, int tokens,
+                              int heads, int kv_heads, int head_dim, int page_size, int num_pages,
+                              int window, float scale, int split_keys, int max_splits, int* status,
+                              cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+             "hx_paged_attention: heads %d must be a positive multiple of kv_heads %d", heads,
+             kv_heads);
+  HX_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0,
+             "hx_paged_attention: bad cache geometry");
+  HX_REQUIRE(split_keys > 0 && max_splits > 0, "hx_paged_attention: bad split sizes");
+  HX_REQUIRE(max_splits == 1 || partial != nullptr, "hx_paged_attention: scratch missing");
+  HX_REQUIRE(window >= 0, "hx_paged_attention: window must not be negative");
+  HX_REQUIRE(ldq >= heads * head_dim && ldo >= heads * head_dim,
+             "hx_paged_attention: row strides too small");
+  HX_REQUIRE(static_cast<long long>(num_pages) * kv_heads * page_size < (1ll << 31),
+             "hx_paged_attention: cache rows exceed 32-bit indexing");
+  if (tokens == 0) return HX_OK;
+  AttentionArgs a{q, ldq, k_cache, v_cache, positions, token_request, request_table_row,
+                  block_tables, table_stride, out, ldo, partial, tokens, heads, kv_heads, head_dim,
+                  page_size, num_pages, window, scale, split_keys, max_splits, status};
+  const long long items = static_cast<long long>(tokens) * heads * max_splits;
+  HX_REQUIRE(items / WARPS_PER_BLOCK < (1ll << 31) - 1, "hx_paged_attention: grid too large");
+  int rc;
+  if (dtype == HX_F32) {
+    rc = dispatch<float>(a, stream);
+  } else if (dtype == HX_BF16) {
+    rc = dispatch<__nv_bfloat16>(a, stream);
+  } else {
+    HX_REQUIRE(false, "hx_paged_attention: unknown dtype %d", dtype);
+  }
+  if (rc != HX_OK) return rc;
+  HX_CHECK_LAUNCH("hx_paged_attention");
+  return HX_OK;
+}

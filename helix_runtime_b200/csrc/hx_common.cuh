@@ -1,0 +1,116 @@
+// Shared declarations of the sm_100a kernel library.
+//
+// Every entry point is `extern "C"`, takes raw device pointers, sizes and the
+// stream to launch on, allocates nothing and never synchronises; it returns 0 or
+// a negative code and leaves a message for hx_last_error().  Sizes a kernel
+// cannot run are refused here, on the host, before any launch.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+
+#define HX_API extern "C" __attribute__((visibility("default")))
+
+enum HxStatus : int {
+  HX_OK = 0,
+  HX_ERR_ARGUMENT = -1,     // a size or pointer the kernel refuses
+  HX_ERR_LAUNCH = -2,       // cudaGetLastError after the launch
+  HX_ERR_UNSUPPORTED = -3,  // valid model size, but no kernel instance for it
+};
+
+enum HxDType : int { HX_F32 = 0, HX_BF16 = 1 };
+
+// device status word bits, written by kernels that can detect a bad input or a wait
+// that ran out; the host reads the word after the step
+enum HxDeviceFlag : int {
+  HX_FLAG_BAD_TOKEN = 1,      // token id outside the vocabulary
+  HX_FLAG_BAD_PAGE = 2,       // block table entry outside the pool
+  HX_FLAG_WAIT_TIMEOUT = 4,   // a bounded mbarrier wait gave up
+  HX_FLAG_NONFINITE = 8,      // sampling saw a non-finite logit
+};
+
+void hx_set_error(const char* format, ...);
+
+#define HX_REQUIRE(cond, ...)            \
+  do {                                   \
+    if (!(cond)) {                       \
+      hx_set_error(__VA_ARGS__);         \
+      return HX_ERR_ARGUMENT;            \
+    }                                    \
+  } while (0)
+
+#define HX_CHECK_LAUNCH(name)                                              \
+  do {                                                                     \
+    cudaError_t hx_err__ = cudaGetLastError();                             \
+    if (hx_err__ != cudaSuccess) {                                         \
+      hx_set_error("%s: launch failed: %s", name, cudaGetErrorString(hx_err__)); \
+      return HX_ERR_LAUNCH;                                                \
+    }                                                                      \
+  } while (0)
+
+template <typename T> struct HxTraits;
+template <> struct HxTraits<float> {
+  static __device__ __forceinline__ float load(const float* p) { return *p; }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct HxTraits<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+template <typename T> __device__ __forceinline__ float hx_to_float(T v);
+template <> __device__ __forceinline__ float hx_to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float hx_to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T hx_from_float(float v);
+template <> __device__ __forceinline__ float hx_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 hx_from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// Block-wide sum with a fixed reduction tree: the result for a row never depends on
+// what else the grid is doing.  `scratch` holds at least 32 floats.
+__device__ __forceinline__ float hx_block_sum(float value, float* scratch) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) value += __shfl_xor_sync(0xffffffffu, value, offset);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = value;
+  __syncthreads();
+  float total = 0.0f;
+  for (int w = 0; w < warps; ++w) total += scratch[w];
+  return total;
+}
+
+__device__ __forceinline__ float hx_block_max(float value, float* scratch) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1)
+    value = fmaxf(value, __shfl_xor_sync(0xffffffffu, value, offset));
+  __syncthreads();
+  if (lane == 0) scratch[warp] = value;
+  __syncthreads();
+  float total = scratch[0];
+  for (int w = 1; w < warps; ++w) total = fmaxf(total, scratch[w]);
+  return total;
+}
+
+// silu(x) = x * sigmoid(x) with the branch-stable sigmoid of the reference
+// (src/kernels/cuda/transformer.cu:68-83).
+__device__ __forceinline__ float hx_silu(float x) {
+  float sigmoid;
+  if (x >= 0.0f) {
+    sigmoid = 1.0f / (1.0f + expf(-x));
+  } else {
+    const float e = expf(x);
+    sigmoid = e / (1.0f + e);
+  }
+  return x * sigmoid;
+}

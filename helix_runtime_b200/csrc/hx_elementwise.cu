@@ -1,0 +1,290 @@
+// Embedding gather, RMSNorm, SwiGLU and the rotary-encoding + cache-append kernel.
+//
+// The residual stream is float32 in both precisions: the embedding widens into
+// it, RMSNorm reads it and writes the compute dtype for the next matrix product.
+#include "hx_common.cuh"
+
+#include <cstdarg>
+#include <cstring>
+
+// ------------------------------------------------------------------ error text
+
+static thread_local char g_hx_error[512] = "";
+
+void hx_set_error(const char* format, ...) {
+  va_list args;
+  va_start(args, format);
+  vsnprintf(g_hx_error, sizeof(g_hx_error), format, args);
+  va_end(args);
+}
+
+HX_API const char* hx_last_error() { return g_hx_error; }
+
+HX_API int hx_abi_version() { return 3; }
+
+// ------------------------------------------------------------------- embedding
+
+// out[t, :] = table[id[t], :] widened to float32.  An id outside the vocabulary
+// gives a NaN row and sets a status bit, never an out-of-bounds read
+// (the reference's rule, src/kernels/cuda/embedding.cu:21-39).
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int hidden, int vocab, int* status) {
+  const int token = blockIdx.x;
+  const int id = ids[token];
+  float* row_out = out + static_cast<size_t>(token) * hidden;
+  if (id < 0 || id >= vocab) {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_out[c] = __int_as_float(0x7fc00000);
+    if (threadIdx.x == 0 && status != nullptr) atomicOr(status, HX_FLAG_BAD_TOKEN);
+    return;
+  }
+  const T* row = table + static_cast<size_t>(id) * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_out[c] = hx_to_float<T>(row[c]);
+}
+
+HX_API int hx_embed(const void* table, int dtype, const int* ids, float* out, int tokens,
+                    int hidden, int vocab, int* status, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "hx_embed: bad sizes");
+  if (tokens == 0) return HX_OK;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == HX_F32) {
+    embed_kernel<float><<<tokens, threads, 0, stream>>>(static_cast<const float*>(table), ids, out,
+                                                        hidden, vocab, status);
+  } else if (dtype == HX_BF16) {
+    embed_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab, status);
+  } else {
+    HX_REQUIRE(false, "hx_embed: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_embed");
+  return HX_OK;
+}
+
+// --------------------------------------------------------------------- RMSNorm
+
+// y = x * rsqrt(mean(x^2) + eps) * w, all in float32 (eps inside the root, added to
+// the mean; src/kernels/cuda/transformer.cu:32-66).  One block per row; `rows`, when
+// given, gathers the rows to normalise (the final norm runs on the wanted rows only).
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                               TOut* __restrict__ y, const int* __restrict__ rows, int hidden,
+                               float eps) {
+  __shared__ float scratch[32];
+  const int out_row = blockIdx.x;
+  const int in_row = rows != nullptr ? rows[out_row] : out_row;
+  const float* xr = x + static_cast<size_t>(in_row) * hidden;
+  float sum = 0.0f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = xr[c];
+    sum = fmaf(v, v, sum);
+  }
+  const float total = hx_block_sum(sum, scratch);
+  const float inverse = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
+  TOut* yr = y + static_cast<size_t>(out_row) * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    yr[c] = hx_from_float<TOut>(xr[c] * inverse * weight[c]);
+}
+
+HX_API int hx_rmsnorm(const float* x, const float* weight, void* y, int out_dtype, const int* rows,
+                      int n_rows, int hidden, float eps, cudaStream_t stream) {
+  HX_REQUIRE(n_rows >= 0 && hidden > 0, "hx_rmsnorm: bad sizes");
+  HX_REQUIRE(eps > 0.0f, "hx_rmsnorm: eps must be positive");
+  if (n_rows == 0) return HX_OK;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (out_dtype == HX_F32) {
+    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, weight, static_cast<float*>(y), rows,
+                                                          hidden, eps);
+  } else if (out_dtype == HX_BF16) {
+    rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
+        x, weight, static_cast<__nv_bfloat16*>(y), rows, hidden, eps);
+  } else {
+    HX_REQUIRE(false, "hx_rmsnorm: unknown dtype %d", out_dtype);
+  }
+  HX_CHECK_LAUNCH("hx_rmsnorm");
+  return HX_OK;
+}
+
+// ---------------------------------------------------------------------- SwiGLU
+
+// act[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; sigmoid and both products in
+// float32 (src/kernels/cuda/transformer.cu:68-83).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ act, int tokens,
+                              int intermediate, int ld_in) {
+  const size_t total = static_cast<size_t>(tokens) * intermediate;
+  for (size_t index = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; index < total;
+       index += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = index / intermediate;
+    const int i = static_cast<int>(index - t * intermediate);
+    const T* row = gate_up + t * ld_in;
+    const float g = hx_to_float<T>(row[i]);
+    const float u = hx_to_float<T>(row[intermediate + i]);
+    act[index] = hx_from_float<T>(hx_silu(g) * u);
+  }
+}
+
+HX_API int hx_swiglu(const void* gate_up, void* act, int dtype, int tokens, int intermediate,
+                     int ld_in, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && intermediate > 0 && ld_in >= 2 * intermediate, "hx_swiglu: bad sizes");
+  if (tokens == 0) return HX_OK;
+  const size_t total = static_cast<size_t>(tokens) * intermediate;
+  const int threads = 256;
+  const int blocks = static_cast<int>(total / threads + 1 < 148 * 16 ? total / threads + 1 : 148 * 16);
+  if (dtype == HX_F32) {
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(gate_up),
+                                                         static_cast<float*>(act), tokens,
+                                                         intermediate, ld_in);
+  } else if (dtype == HX_BF16) {
+    swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(act), tokens,
+        intermediate, ld_in);
+  } else {
+    HX_REQUIRE(false, "hx_swiglu: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_swiglu");
+  return HX_OK;
+}
+
+// ---------------------------------------------- rotary encoding + cache append
+
+// For token t of the flattened batch: rotate the first `rotary_dim` coordinates of
+// every query and key head by the angles of its absolute position, leave values as
+// they are, write the query back in place and write key (after rotation) and value
+// into the token's slot of its request's page.  Rotation in float32 from a cos/sin
+// table built on the host in double (src/model/llama_common.cpp:37-46;
+// src/kernels/cuda/transformer.cu:100-119); the reference's separate cache append
+// (src/kv_cache/cuda_paged.cpp:561-577) is fused in.
+//
+// qkv row: [q heads | k heads | v heads], each head `head_dim` wide.
+// pairing 0: pairs (2p, 2p+1); pairing 1: pairs (p, p + rotary_dim/2).
+// cache layer: [page][kv_head][slot in page][head_dim].
+template <typename T>
+__global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positions,
+                                   const int* __restrict__ token_request,
+                                   const int* __restrict__ request_table_row,
+                                   const int* __restrict__ block_tables, int table_stride,
+                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int write_cache,
+                                   const float* __restrict__ cos_table,
+                                   const float* __restrict__ sin_table, int table_positions,
+                                   int heads, int kv_heads, int head_dim, int rotary_dim,
+                                   int pairing, int page_size, int num_pages, int* status) {
+  const int token = blockIdx.x;
+  const int position = positions[token];
+  T* row = qkv + static_cast<size_t>(token) * ld;
+  const int half = rotary_dim / 2;
+  const int table_position = position < table_positions ? position : table_positions - 1;
+  const float* cos_row = cos_table + static_cast<size_t>(table_position) * half;
+  const float* sin_row = sin_table + static_cast<size_t>(table_position) * half;
+
+  int page = -1;
+  int slot = 0;
+  if (write_cache) {
+    const int request = token_request[token];
+    const int table_row = request_table_row[request];
+    page = block_tables[static_cast<size_t>(table_row) * table_stride + position / page_size];
+    slot = position % page_size;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0 && status != nullptr) atomicOr(status, HX_FLAG_BAD_PAGE);
+      page = -1;
+    }
+  }
+
+  const int pairs_per_head = head_dim / 2;
+  // queries and keys: one thread per coordinate pair
+  const int qk_pairs = (heads + kv_heads) * pairs_per_head;
+  for (int index = threadIdx.x; index < qk_pairs; index += blockDim.x) {
+    const int head = index / pairs_per_head;
+    const int pair = index - head * pairs_per_head;
+    T* vec = row + static_cast<size_t>(head) * head_dim;
+    int i0, i1;
+    bool rotate;
+    if (pairing == 0) {
+      i0 = 2 * pair;
+      i1 = i0 + 1;
+      rotate = i1 < rotary_dim;
+    } else {
+      // half-split pairs inside the rotary part; the rest are passed through two by two
+      if (pair < half) {
+        i0 = pair;
+        i1 = pair + half;
+        rotate = true;
+      } else {
+        i0 = rotary_dim + 2 * (pair - half);
+        i1 = i0 + 1;
+        rotate = false;
+      }
+    }
+    float a = hx_to_float<T>(vec[i0]);
+    float b = hx_to_float<T>(vec[i1]);
+    if (rotate) {
+      const int f = pairing == 0 ? pair : pair;
+      const float c = cos_row[f];
+      const float s = sin_row[f];
+      const float ra = a * c - b * s;
+      const float rb = a * s + b * c;
+      a = ra;
+      b = rb;
+    }
+    const T ta = hx_from_float<T>(a);
+    const T tb = hx_from_float<T>(b);
+    if (head < heads) {
+      vec[i0] = ta;
+      vec[i1] = tb;
+    } else if (page >= 0) {
+      const int kv_head = head - heads;
+      T* dst = k_cache +
+               ((static_cast<size_t>(page) * kv_heads + kv_head) * page_size + slot) * head_dim;
+      dst[i0] = ta;
+      dst[i1] = tb;
+    }
+  }
+  // values: straight copy into the page
+  if (page >= 0) {
+    const int v_elems = kv_heads * head_dim;
+    const T* v_row = row + static_cast<size_t>(heads + kv_heads) * head_dim;
+    for (int index = threadIdx.x; index < v_elems; index += blockDim.x) {
+      const int kv_head = index / head_dim;
+      const int d = index - kv_head * head_dim;
+      v_cache[((static_cast<size_t>(page) * kv_heads + kv_head) * page_size + slot) * head_dim + d] =
+          v_row[index];
+    }
+  }
+}
+
+HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
+                          const int* token_request, const int* request_table_row,
+                          const int* block_tables, int table_stride, void* k_cache, void* v_cache,
+                          int write_cache, const float* cos_table, const float* sin_table,
+                          int table_positions, int tokens, int heads, int kv_heads, int head_dim,
+                          int rotary_dim, int pairing, int page_size, int num_pages, int* status,
+                          cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0, "hx_rope_append: bad sizes");
+  HX_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "hx_rope_append: head_dim %d must be even", head_dim);
+  HX_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
+             "hx_rope_append: rotary_dim %d must be even and at most head_dim %d", rotary_dim,
+             head_dim);
+  HX_REQUIRE(pairing == 0 || pairing == 1, "hx_rope_append: unknown pairing %d", pairing);
+  HX_REQUIRE(ld >= (heads + 2 * kv_heads) * head_dim, "hx_rope_append: row stride too small");
+  HX_REQUIRE(!write_cache || (page_size > 0 && num_pages > 0 && k_cache && v_cache),
+             "hx_rope_append: cache arguments missing");
+  HX_REQUIRE(rotary_dim == 0 || table_positions > 0, "hx_rope_append: empty rotary table");
+  if (tokens == 0) return HX_OK;
+  const int threads = 256;
+  if (dtype == HX_F32) {
+    rope_append_kernel<float><<<tokens, threads, 0, stream>>>(
+        static_cast<float*>(qkv), ld, positions, token_request, request_table_row, block_tables,
+        table_stride, static_cast<float*>(k_cache), static_cast<float*>(v_cache), write_cache,
+        cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing,
+        page_size, num_pages, status);
+  } else if (dtype == HX_BF16) {
+    rope_append_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(qkv), ld, positions, token_request, request_table_row,
+        block_tables, table_stride, static_cast<__nv_bfloat16*>(k_cache),
+        static_cast<__nv_bfloat16*>(v_cache), write_cache, cos_table, sin_table, table_positions,
+        heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status);
+  } else {
+    HX_REQUIRE(false, "hx_rope_append: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_rope_append");
+  return HX_OK;
+}

@@ -1,0 +1,520 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05, sm_100a).
+//
+//   out[t, f] (+)= sum_k x[t, k] * w[f, k]        x: [tokens, K]   w: [features, K]
+//
+// Both operands are K-major, which is how the checkpoint stores its matrices, so no
+// transposed copy is ever made (the reference keeps [in, out] and multiplies with a
+// 16x16 shared-memory kernel, src/kernels/cuda/matmul.cu:36-71).
+//
+// Mapping.  The WEIGHT tile is the MMA's M operand (128 features per CTA) and the
+// TOKEN tile its N operand (BN = 16 ... 256 tokens), so one kernel covers decoding
+// (a handful of tokens, pure weight streaming) and prompt portions (256-token
+// tiles).  The accumulator lives in tensor memory as [128 feature lanes x BN token
+// columns] float32.  Warp roles:
+//   warp 0      one lane issues the TMA loads of both operand tiles, STAGES deep;
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma and commits;
+//   warps 2..5  epilogue: tcgen05.ld their 32-lane quarter, apply the epilogue, store.
+// Shared-memory tiles are [rows x 64] bfloat16 with the 128-byte swizzle that both
+// TMA and the MMA descriptors understand.
+//
+// Epilogues: store bf16, store f32 (logits), add into f32 (the residual stream; with
+// split-K through float32 atomics), and SwiGLU, where the CTA multiplies the same
+// token tile with a gate tile and an up tile of the fused [2I, K] matrix into two
+// accumulators and writes silu(gate) * up.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets a status bit, the
+// CTA skips its remaining work, frees its tensor memory and returns.
+#include "hx_common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;        // features per CTA (MMA M)
+constexpr int BK = 64;         // k elements per stage: 128 bytes, one swizzle span
+constexpr int UMMA_K = 16;     // k elements per tcgen05.mma of kind::f16
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 40u * 1000u * 1000u;
+
+enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
+
+// ---------------------------------------------------------------- PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < WAIT_LIMIT; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
+                                            int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(holder)),
+               "r"(columns)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, both K-major bf16, float32 accumulate.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The mbarrier gets one arrival when every MMA issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+
+// 32 lanes x 16 consecutive columns of float32: thread i gets lane (base lane + i).
+__device__ __forceinline__ void tmem_load16(uint32_t address, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(address)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor for a K-major tile of [rows x 64] bf16 written by TMA with
+// the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading
+// byte offset is unused for swizzled K-major tiles, descriptor version 1 (sm_100), layout
+// type 2 (128-byte swizzle).  Addresses and offsets are in units of 16 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_address) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_address & 0x3ffffu) >> 4);
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+  desc |= static_cast<uint64_t>(1) << 46;
+  desc |= static_cast<uint64_t>(2) << 61;
+  return desc;
+}
+
+// Instruction descriptor of kind::f16: float32 accumulator, bf16 A and B, both K-major.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------- kernel
+
+template <int BN, bool DUAL>
+struct TileConfig {
+  static constexpr int kWeightBytes = BM * BK * 2 * (DUAL ? 2 : 1);
+  static constexpr int kTokenBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kWeightBytes + kTokenBytes;
+  static constexpr int kBudget = 200 * 1024;
+  static constexpr int kStagesRaw = kBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int kAccumulatorColumns = BN * (DUAL ? 2 : 1);
+  static constexpr int kTmemColumns =
+      kAccumulatorColumns <= 32 ? 32
+      : kAccumulatorColumns <= 64 ? 64
+      : kAccumulatorColumns <= 128 ? 128
+      : kAccumulatorColumns <= 256 ? 256 : 512;
+};
+
+struct GemmArgs {
+  void* out;
+  int ldo;
+  int tokens;
+  int features;     // rows of the output the epilogue may write
+  int depth;        // K
+  int up_row_offset;  // SwiGLU: row of the first up-projection feature in the weight matrix
+  int k_blocks_per_split;
+  int* status;
+};
+
+template <int BN, int EPI>
+__global__ __launch_bounds__(THREADS, 1) void gemm_tc_kernel(
+    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+    const GemmArgs args) {
+  constexpr bool DUAL = EPI == EPI_SWIGLU;
+  using Config = TileConfig<BN, DUAL>;
+  constexpr int STAGES = Config::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Config::kStageBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* accum_bar = empty_bar + STAGES;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_bar + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int feature0 = blockIdx.x * BM;
+  const int token0 = blockIdx.y * BN;
+  const int total_k_blocks = (args.depth + BK - 1) / BK;
+  const int kb_begin = blockIdx.z * args.k_blocks_per_split;
+  const int kb_end = min(kb_begin + args.k_blocks_per_split, total_k_blocks);
+  const int n_k_blocks = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_holder, Config::kTmemColumns);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (n_k_blocks > 0) {
+    if (warp == 0) {
+      // ------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        for (int i = 0; i < n_k_blocks; ++i) {
+          const int s = i % STAGES;
+          const uint32_t round = static_cast<uint32_t>(i / STAGES);
+          if (!mbar_wait(&empty_bar[s], (round & 1u) ^ 1u)) {
+            atomicOr(args.status, HX_FLAG_WAIT_TIMEOUT);
+            break;
+          }
+          uint8_t* stage = smem + s * Config::kStageBytes;
+          mbar_expect_tx(&full_bar[s], Config::kStageBytes);
+          const int k = (kb_begin + i) * BK;
+          tma_load_2d(stage, &map_w, &full_bar[s], k, feature0);
+          if (DUAL)
+            tma_load_2d(stage + BM * BK * 2, &map_w, &full_bar[s], k, args.up_row_offset + feature0);
+          tma_load_2d(stage + Config::kWeightBytes, &map_x, &full_bar[s], k, token0);
+        }
+      }
+    } else if (warp == 1) {
+      // -------------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        constexpr uint32_t idesc = make_idesc(BM, BN);
+        bool ok = true;
+        for (int i = 0; i < n_k_blocks && ok; ++i) {
+          const int s = i % STAGES;
+          const uint32_t round = static_cast<uint32_t>(i / STAGES);
+          if (!mbar_wait(&full_bar[s], round & 1u)) {
+            atomicOr(args.status, HX_FLAG_WAIT_TIMEOUT);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t stage = smem_u32(smem + s * Config::kStageBytes);
+          const uint64_t desc_w = make_smem_desc(stage);
+          const uint64_t desc_w2 = make_smem_desc(stage + BM * BK * 2);
+          const uint64_t desc_x = make_smem_desc(stage + Config::kWeightBytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // stepping 16 k-elements = 32 bytes inside the swizzle span: +2 in 16-byte units
+            const uint64_t step = static_cast<uint64_t>(k * UMMA_K * 2 >> 4);
+            const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
+            umma_bf16(tmem_base, desc_w + step, desc_x + step, idesc, accumulate);
+            if (DUAL) umma_bf16(tmem_base + BN, desc_w2 + step, desc_x + step, idesc, accumulate);
+          }
+          umma_commit(&empty_bar[s]);   // the stage may be refilled once these MMAs have read it
+        }
+        umma_commit(accum_bar);         // the accumulator is complete
+      }
+    } else {
+      // ---------------------------------------------------------------- epilogue
+      const int quarter = warp & 3;     // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
+      const int feature = feature0 + quarter * 32 + lane;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(accum_bar, 0);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) {
+        if (lane == 0) atomicOr(args.status, HX_FLAG_WAIT_TIMEOUT);
+      } else {
+        tc_fence_after();
+        const uint32_t lane_address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        const bool feature_ok = feature < args.features;
+#pragma unroll 1
+        for (int column = 0; column < BN; column += 16) {
+          if (token0 + column >= args.tokens) break;   // uniform over the warp
+          float acc[16];
+          tmem_load16(lane_address + column, acc);
+          if (EPI == EPI_SWIGLU) {
+            float up[16];
+            tmem_load16(lane_address + BN + column, up);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] = hx_silu(acc[j]) * up[j];
+          }
+          if (feature_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int token = token0 + column + j;
+              if (token < args.tokens) {
+                const size_t index = static_cast<size_t>(token) * args.ldo + feature;
+                if (EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU) {
+                  static_cast<__nv_bfloat16*>(args.out)[index] = __float2bfloat16_rn(acc[j]);
+                } else if (EPI == EPI_STORE_F32) {
+                  static_cast<float*>(args.out)[index] = acc[j];
+                } else {
+                  float* target = static_cast<float*>(args.out) + index;
+                  if (gridDim.z == 1) {
+                    *target += acc[j];
+                  } else {
+                    atomicAdd(target, acc[j]);
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Config::kTmemColumns);
+  }
+}
+
+// ----------------------------------------------------------------- host side
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = [] {
+    void* symbol = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) !=
+            cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      return static_cast<EncodeTiled>(nullptr);
+    }
+    return reinterpret_cast<EncodeTiled>(symbol);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  uint64_t rows;
+  uint64_t depth;
+  uint64_t ld;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && depth == o.depth && ld == o.ld &&
+           box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h = h * 1315423911u ^ k.rows;
+    h = h * 1315423911u ^ k.depth;
+    h = h * 1315423911u ^ k.ld;
+    h = h * 1315423911u ^ k.box_rows;
+    return h;
+  }
+};
+
+// Tensor maps are pure functions of (address, shape, box); encoding one costs a few
+// microseconds, so they are cached for the life of the process.
+int get_tensor_map(const void* base, uint64_t rows, uint64_t depth, uint64_t ld, uint32_t box_rows,
+                   CUtensorMap* out) {
+  static std::mutex mutex;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, rows, depth, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mutex);
+  auto found = cache.find(key);
+  if (found != cache.end()) {
+    *out = found->second;
+    return HX_OK;
+  }
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) {
+    hx_set_error("hx_gemm_tc: the driver does not export cuTensorMapEncodeTiled");
+    return HX_ERR_UNSUPPORTED;
+  }
+  const cuuint64_t dims[2] = {depth, rows};
+  const cuuint64_t strides[1] = {ld * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), box_rows};
+  const cuuint32_t element_strides[2] = {1, 1};
+  CUtensorMap map;
+  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                             dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    hx_set_error("hx_gemm_tc: cuTensorMapEncodeTiled failed with %d (base %p rows %llu depth %llu "
+                 "ld %llu box %u)", static_cast<int>(rc), base,
+                 static_cast<unsigned long long>(rows), static_cast<unsigned long long>(depth),
+                 static_cast<unsigned long long>(ld), box_rows);
+    return HX_ERR_ARGUMENT;
+  }
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return HX_OK;
+}
+
+template <int BN, int EPI>
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmArgs& args, dim3 grid,
+           cudaStream_t stream) {
+  using Config = TileConfig<BN, EPI == EPI_SWIGLU>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Config::kSmemBytes) != cudaSuccess) {
+      hx_set_error("hx_gemm_tc: cannot reserve %d bytes of shared memory", Config::kSmemBytes);
+      cudaGetLastError();
+      return HX_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  gemm_tc_kernel<BN, EPI><<<grid, THREADS, Config::kSmemBytes, stream>>>(map_w, map_x, args);
+  return HX_OK;
+}
+
+template <int BN>
+int launch_epilogue(int epilogue, const CUtensorMap& map_w, const CUtensorMap& map_x,
+                    const GemmArgs& args, dim3 grid, cudaStream_t stream) {
+  switch (epilogue) {
+    case EPI_STORE_BF16: return launch<BN, EPI_STORE_BF16>(map_w, map_x, args, grid, stream);
+    case EPI_STORE_F32: return launch<BN, EPI_STORE_F32>(map_w, map_x, args, grid, stream);
+    case EPI_ADD_F32: return launch<BN, EPI_ADD_F32>(map_w, map_x, args, grid, stream);
+    case EPI_SWIGLU: return launch<BN, EPI_SWIGLU>(map_w, map_x, args, grid, stream);
+    default:
+      hx_set_error("hx_gemm_tc: unknown epilogue %d", epilogue);
+      return HX_ERR_ARGUMENT;
+  }
+}
+
+}  // namespace
+
+// Token tile the kernel would use for this many tokens (for tests and the bench's records).
+HX_API int hx_gemm_tc_token_tile(int tokens) {
+  if (tokens <= 16) return 16;
+  if (tokens <= 32) return 32;
+  if (tokens <= 64) return 64;
+  if (tokens <= 128) return 128;
+  return 256;
+}
+
+// 1 when the tensor-core kernel takes this shape; 0 when the caller must use hx_gemm_simt.
+HX_API int hx_gemm_tc_supports(int tokens, int features, int depth, int ldx, int ldw) {
+  return tokens > 0 && features > 0 && depth > 0 && depth % 8 == 0 && ldx % 8 == 0 &&
+         ldw % 8 == 0;
+}
+
+// x: [tokens, depth] bf16 (row stride ldx), w: [weight_rows, depth] bf16 (row stride ldw).
+// epilogue 0/1/2: `features` = weight_rows outputs per token.  epilogue 3 (SwiGLU): w is the
+// fused [gate; up] matrix, `features` = intermediate size, gate rows [0, features), up rows
+// [up_row_offset, up_row_offset + features).  k_splits > 1 only with epilogue 2.
+// x_capacity_rows: rows of the buffer behind x (the tensor map is made for the buffer, so it
+// can be reused for every batch size).
+HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                      int weight_rows, void* out, int ldo, int tokens, int features, int depth,
+                      int epilogue, int up_row_offset, int k_splits, int* status,
+                      cudaStream_t stream) {
+  HX_REQUIRE(hx_gemm_tc_supports(tokens, features, depth, ldx, ldw),
+             "hx_gemm_tc: shape tokens=%d features=%d depth=%d ldx=%d ldw=%d is not supported "
+             "(depth and strides must be multiples of 8)", tokens, features, depth, ldx, ldw);
+  HX_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+             "hx_gemm_tc: operands must be 16-byte aligned");
+  HX_REQUIRE(x_capacity_rows >= tokens, "hx_gemm_tc: buffer rows %d < tokens %d", x_capacity_rows,
+             tokens);
+  HX_REQUIRE(status != nullptr, "hx_gemm_tc: status word missing");
+  HX_REQUIRE(k_splits >= 1 && (k_splits == 1 || epilogue == EPI_ADD_F32),
+             "hx_gemm_tc: split-K needs the add epilogue");
+  HX_REQUIRE(epilogue != EPI_SWIGLU || up_row_offset + features <= weight_rows,
+             "hx_gemm_tc: up rows exceed the weight matrix");
+  HX_REQUIRE(epilogue == EPI_SWIGLU || features <= weight_rows,
+             "hx_gemm_tc: features exceed the weight matrix");
+  HX_REQUIRE(ldo >= features, "hx_gemm_tc: output stride too small");
+
+  const int bn = hx_gemm_tc_token_tile(tokens);
+  CUtensorMap map_w, map_x;
+  int rc = get_tensor_map(w, weight_rows, depth, ldw, BM, &map_w);
+  if (rc != HX_OK) return rc;
+  rc = get_tensor_map(x, x_capacity_rows, depth, ldx, bn, &map_x);
+  if (rc != HX_OK) return rc;
+
+  const int total_k_blocks = (depth + BK - 1) / BK;
+  if (k_splits > total_k_blocks) k_splits = total_k_blocks;
+  const int per_split = (total_k_blocks + k_splits - 1) / k_splits;
+  k_splits = (total_k_blocks + per_split - 1) / per_split;
+  GemmArgs args{out, ldo, tokens, features, depth, up_row_offset, per_split, status};
+  const dim3 grid((features + BM - 1) / BM, (tokens + bn - 1) / bn, k_splits);
+  HX_REQUIRE(grid.y <= 65535, "hx_gemm_tc: too many tokens (%d)", tokens);
+
+  switch (bn) {
+    case 16: rc = launch_epilogue<16>(epilogue, map_w, map_x, args, grid, stream); break;
+    case 32: rc = launch_epilogue<32>(epilogue, map_w, map_x, args, grid, stream); break;
+    case 64: rc = launch_epilogue<64>(epilogue, map_w, map_x, args, grid, stream); break;
+    case 128: rc = launch_epilogue<128>(epilogue, map_w, map_x, args, grid, stream); break;
+    default: rc = launch_epilogue<256>(epilogue, map_w, map_x, args, grid, stream); break;
+  }
+  if (rc != HX_OK) return rc;
+  HX_CHECK_LAUNCH("hx_gemm_tc");
+  return HX_OK;
+}

@@ -1,0 +1,12 @@
+from .engine import (Engine, EngineConfig, GenerationResult, IterationResult, load_model,
+                     parse_dtype, random_model, write_random_model)
+from .scheduler import (FifoScheduler, IterationBatch, Request, RequestState, ScheduledWork,
+                        SchedulerConfig, StopReason, WorkCompletion, WorkKind)
+from .step import StepEntry, StepError, StepFunction
+
+__all__ = [
+    "Engine", "EngineConfig", "FifoScheduler", "GenerationResult", "IterationBatch",
+    "IterationResult", "Request", "RequestState", "ScheduledWork", "SchedulerConfig",
+    "StepEntry", "StepError", "StepFunction", "StopReason", "WorkCompletion", "WorkKind",
+    "load_model", "parse_dtype", "random_model", "write_random_model",
+]

@@ -1,0 +1,318 @@
+"""The engine: a model, its cache, the step function, the scheduler and the sampler.
+
+This is the Python entry point.  Its surface follows the reference's runtime engine
+(``submit / run_iteration / cancel / stats``, include/helix/runtime/cpu_engine.hpp:70-98)
+and its one-sequence generator (``generate`` with ``max_new_tokens`` and an optional
+``eos_token``; results carry the generated ids, the stop reason and the number of
+cached tokens, include/helix/model/generation.hpp:22-63).
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+import time
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.registry import architecture_for, load_config, read_config_json
+from ..models.decoder import DecoderModel
+from ..sampling.sampler import Sampler, uniform_for
+from ..weights.loader import load_tensors
+from ..weights.random_init import random_tensors, write_model_folder
+from ..weights.safetensors_io import Checkpoint
+from .scheduler import (FifoScheduler, Request, RequestState, SchedulerConfig, StopReason,
+                        WorkCompletion)
+from .step import StepEntry, StepError, StepFunction
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+           "float32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(name: Union[str, torch.dtype]) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"unsupported dtype {name}")
+        return name
+    try:
+        return _DTYPES[name]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {name!r}; use bfloat16 or float32") from None
+
+
+def require_cuda(device: Union[str, torch.device]) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError("this engine runs on an NVIDIA B200 only; there is no CPU path")
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is available; this engine has no CPU path")
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return device
+
+
+def load_model(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16",
+               device: Union[str, torch.device] = "cuda:0") -> DecoderModel:
+    """Build the model that ``config.json`` names and bind the folder's weights."""
+    dtype = parse_dtype(dtype)
+    device = torch.device(device)
+    architecture, config = load_config(model_dir)
+    model = DecoderModel(architecture.build_spec(config))
+    model.config = config
+    tensors = load_tensors(Checkpoint(model_dir), model.tensor_requests(), dtype, device)
+    model.bind(tensors, dtype, device)
+    return model
+
+
+def random_model(config, seed: int, dtype: Union[str, torch.dtype] = "bfloat16",
+                 device: Union[str, torch.device] = "cuda:0", std: float = 0.02) -> DecoderModel:
+    """A model with seeded random weights made directly on the device (no folder): every
+    matrix N(0, std), norm weights one.  Used where writing gigabytes to disk would only
+    cost time; :func:`write_random_model` is the mode that writes a folder."""
+    dtype = parse_dtype(dtype)
+    device = torch.device(device)
+    architecture = architecture_for(config.to_dict())
+    model = DecoderModel(architecture.build_spec(config))
+    model.config = config
+    generator = torch.Generator(device=device)
+    generator.manual_seed(int(seed))
+    tensors: Dict[str, torch.Tensor] = {}
+    for request in model.tensor_requests():
+        if request.role == "scale":
+            tensors[request.name] = torch.ones(request.shape, dtype=torch.float32, device=device)
+        else:
+            value = torch.empty(request.shape, dtype=dtype, device=device)
+            value.normal_(0.0, std, generator=generator)
+            tensors[request.name] = value
+    model.bind(tensors, dtype, device)
+    return model
+
+
+def write_random_model(directory: str, config, seed: int, std: float = 0.02,
+                       scale_std: float = 0.0,
+                       storage_dtype: Union[str, torch.dtype] = "bfloat16") -> None:
+    """The random-weights mode: write ``config.json`` and ``model.safetensors``."""
+    architecture = architecture_for(config.to_dict())
+    model = DecoderModel(architecture.build_spec(config))
+    tensors = random_tensors(model.tensor_requests(), seed, std=std, scale_std=scale_std,
+                             storage_dtype=parse_dtype(storage_dtype))
+    write_model_folder(directory, config.to_dict(), tensors)
+
+
+@dataclasses.dataclass(frozen=True)
+class EngineConfig:
+    page_size: int = 16
+    num_pages: Optional[int] = None           # default: enough for max_running * max positions
+    max_running_requests: int = 8
+    max_tokens_per_iteration: int = 2048
+    max_prefill_chunk: Optional[int] = None
+    attention_split_keys: int = 256
+    poison_free_pages: bool = False           # debugging: fill free pages with NaN
+
+
+@dataclasses.dataclass
+class GenerationResult:
+    generated_tokens: List[int]
+    stop_reason: str
+    cached_token_count: int
+    request_id: int = -1
+
+
+@dataclasses.dataclass
+class IterationResult:
+    scheduled_tokens: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    sampled: int = 0
+    retired: List[int] = dataclasses.field(default_factory=list)
+    preempted: List[int] = dataclasses.field(default_factory=list)
+    kv_limited: bool = False
+    idle: bool = False
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, config: EngineConfig = EngineConfig()) -> None:
+        self.model = model
+        self.config = config
+        device = require_cuda(model.device)
+        kv_needs, state_needs = model.cache_needs()
+        pages_per_request = -(-model.max_positions // config.page_size)
+        num_pages = config.num_pages or pages_per_request * config.max_running_requests
+        self.cache = CacheManager(kv_needs, state_needs, config.page_size, num_pages,
+                                  config.max_running_requests, model.max_positions, model.dtype,
+                                  device, poison=config.poison_free_pages)
+        self.step_function = StepFunction(model, self.cache, config.max_tokens_per_iteration,
+                                          config.max_running_requests,
+                                          config.attention_split_keys)
+        self.scheduler = FifoScheduler(
+            SchedulerConfig(config.max_tokens_per_iteration, config.max_running_requests,
+                            config.max_prefill_chunk), config.page_size)
+        self.sampler = Sampler(device, config.max_running_requests)
+        self._cached_at_finish: Dict[int, int] = {}
+        self._release_later: List[int] = []
+
+    # ------------------------------------------------------------ construction
+
+    @classmethod
+    def from_pretrained(cls, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16",
+                        device: Union[str, torch.device] = "cuda:0",
+                        **engine_options) -> "Engine":
+        device = require_cuda(device)
+        return cls(load_model(model_dir, dtype, device), EngineConfig(**engine_options))
+
+    @classmethod
+    def from_random(cls, config, seed: int = 0, dtype: Union[str, torch.dtype] = "bfloat16",
+                    device: Union[str, torch.device] = "cuda:0", **engine_options) -> "Engine":
+        device = require_cuda(device)
+        return cls(random_model(config, seed, dtype, device), EngineConfig(**engine_options))
+
+    # ----------------------------------------------------------------- requests
+
+    def submit(self, prompt: Sequence[int], max_new_tokens: int = 32,
+               eos_token: Optional[int] = None, temperature: float = 0.0, seed: int = 0) -> int:
+        """Queue a request; refuse what could never run (src/runtime/cpu_engine.cpp:85-119)."""
+        vocab = self.model.vocab_size
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise ValueError("at least one prompt token ID is required")
+        for token in prompt:
+            if not 0 <= token < vocab:
+                raise ValueError(f"prompt token {token} is outside the vocabulary of {vocab}")
+        if eos_token is not None and not 0 <= int(eos_token) < vocab:
+            raise ValueError(f"eos token {eos_token} is outside the vocabulary of {vocab}")
+        if len(prompt) > self.model.max_positions:
+            raise ValueError(f"prompt of {len(prompt)} tokens exceeds the model's "
+                             f"{self.model.max_positions} positions")
+        if max_new_tokens < 0:
+            raise ValueError("max_new_tokens must not be negative")
+        # the last generated token is never fed back, so it needs no cache row
+        rows = min(len(prompt) + max(max_new_tokens - 1, 0), self.model.max_positions)
+        pages = -(-rows // self.config.page_size)
+        for group in self.cache.groups:
+            if pages > group.pool.num_pages:
+                raise ValueError(f"the request needs {pages} cache pages, the pool has "
+                                 f"{group.pool.num_pages}; it could never run")
+        return self.scheduler.submit(prompt, max_new_tokens, eos_token, temperature, seed,
+                                     now=time.monotonic())
+
+    def cancel(self, request_id: int) -> bool:
+        cancelled = self.scheduler.cancel(request_id, now=time.monotonic())
+        if cancelled and self.cache.has(request_id):
+            self._finish_cache(request_id)
+        return cancelled
+
+    def request(self, request_id: int) -> Request:
+        return self.scheduler.request(request_id)
+
+    def _finish_cache(self, request_id: int) -> None:
+        self._cached_at_finish[request_id] = self.cache.length(request_id)
+        self.cache.release(request_id)
+
+    # ---------------------------------------------------------------- iteration
+
+    def run_iteration(self) -> IterationResult:
+        """Schedule one batch, run it as one step, sample, complete, free what retired."""
+        result = IterationResult()
+        batch = self.scheduler.schedule_iteration(self.cache, admit=self.cache.admit,
+                                                  release=self.cache.release)
+        if batch is None:
+            result.idle = True
+            return result
+        result.preempted = list(batch.preempted)
+        result.kv_limited = batch.kv_limited
+        entries: List[StepEntry] = []
+        temperatures: List[float] = []
+        uniforms: List[float] = []
+        for work in batch.work:
+            request = self.scheduler.request(work.request_id)
+            tokens = request.feed[work.token_offset:work.token_offset + work.token_count]
+            want = [work.token_count - 1] if work.samples and request.max_new_tokens > 0 else []
+            entries.append(StepEntry(work.request_id, tokens, want))
+            if want:
+                temperatures.append(request.temperature)
+                uniforms.append(uniform_for(request.seed, len(request.generated)))
+            if work.kind.value == "prefill":
+                result.prefill_tokens += work.token_count
+            else:
+                result.decode_tokens += work.token_count
+        result.scheduled_tokens = batch.scheduled_tokens
+
+        completions: List[WorkCompletion] = []
+        try:
+            logits = self.step_function.run(entries, check_status=False)
+            sampled: List[int] = []
+            if logits is not None:
+                tokens = self.sampler.sample(logits, temperatures, uniforms,
+                                             self.step_function.status)
+                sampled = self.sampler.to_host(tokens)
+            flags = int(self.step_function.status.item())
+            if flags & ~8:       # anything but per-row non-finite logits condemns the whole step
+                self.step_function.raise_on_status()
+            if flags:
+                self.step_function.status.zero_()
+            cursor = 0
+            for work, entry in zip(batch.work, entries):
+                token = None
+                if entry.want:
+                    token = sampled[cursor]
+                    cursor += 1
+                    if token < 0:
+                        completions.append(WorkCompletion(
+                            work.request_id, False,
+                            error="logits contain a non-finite value"))
+                        continue
+                elif work.samples:
+                    token = 0   # max_new_tokens == 0: nothing is sampled, nothing is used
+                completions.append(WorkCompletion(work.request_id, True, token=token))
+            result.sampled = cursor
+        except StepError as error:
+            completions = [WorkCompletion(work.request_id, False, error=str(error))
+                           for work in batch.work]
+        retired = self.scheduler.complete_iteration(batch.id, completions,
+                                                    self.model.max_positions,
+                                                    now=time.monotonic())
+        for request in retired:
+            if self.cache.has(request.id):
+                self._finish_cache(request.id)
+            result.retired.append(request.id)
+        return result
+
+    def run_until_done(self, max_iterations: Optional[int] = None) -> int:
+        iterations = 0
+        while self.scheduler.has_unfinished():
+            outcome = self.run_iteration()
+            iterations += 1
+            if outcome.idle:
+                raise RuntimeError("the scheduler has unfinished requests but can plan no work")
+            if max_iterations is not None and iterations >= max_iterations:
+                break
+        return iterations
+
+    # ----------------------------------------------------------------- generate
+
+    def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
+                 max_new_tokens: int = 32, eos_token: Optional[int] = None,
+                 temperature: float = 0.0, seed: int = 0) -> List[GenerationResult]:
+        """Generate for one prompt or a list of prompts (token ids in, token ids out)."""
+        if len(prompts) > 0 and isinstance(prompts[0], int):
+            prompts = [prompts]           # a single prompt
+        ids = [self.submit(prompt, max_new_tokens, eos_token, temperature, seed + index)
+               for index, prompt in enumerate(prompts)]
+        self.run_until_done()
+        results = []
+        for request_id in ids:
+            request = self.scheduler.request(request_id)
+            if request.state is RequestState.FAILED:
+                raise RuntimeError(f"request {request_id} failed: {request.error}")
+            results.append(GenerationResult(
+                generated_tokens=list(request.generated),
+                stop_reason=request.stop_reason.value if request.stop_reason else "",
+                cached_token_count=self._cached_at_finish.get(request_id, 0),
+                request_id=request_id))
+        return results
+
+    def stats(self) -> Dict[str, object]:
+        return {"scheduler": dict(self.scheduler.stats), "cache": self.cache.stats(),
+                "steps": self.step_function.steps_run, "tokens": self.step_function.tokens_run,
+                "workspace_bytes": self.step_function.workspace.bytes()}

@@ -1,0 +1,197 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step holds, for every request in it, the next tokens of that request: a portion of
+a prompt (cut anywhere) or a single decoded token.  All of them run as ONE flattened
+batch against the cache that earlier steps left, and the logits at the wanted
+positions come back.  The reference has no such function; its engine runs the work
+items of an iteration one after the other (src/runtime/cpu_engine.cpp:344-361).
+
+Transaction: pages are reserved before the launch and lengths are published after
+it; if anything raises, reserved pages go back and no length moves
+(src/runtime/cpu_engine.cpp:191, 207, 235).
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..models.decoder import DecoderModel
+from ..ops import library as ops
+from ..parts.base import StepContext, Workspace
+
+
+@dataclasses.dataclass
+class StepEntry:
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()          # places among ``tokens`` whose logits are asked for
+
+
+class StepError(RuntimeError):
+    """The batch is not runnable (bad token, too long, unknown request) or a kernel failed."""
+
+
+class StepFunction:
+    def __init__(self, model: DecoderModel, cache: CacheManager, max_tokens: int,
+                 max_requests: int, attention_split_keys: int = 256) -> None:
+        if model.device is None:
+            raise StepError("the model has no weights bound")
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.dtype = model.dtype
+        self.max_tokens = int(max_tokens)
+        self.max_requests = int(max_requests)
+        self.attention_split_keys = int(attention_split_keys)
+        self.workspace = Workspace(self.device)
+        cap, req = self.max_tokens, self.max_requests
+        # one packed int32 block: a single host-to-device copy per step
+        self._layout = {}
+        cursor = 0
+        for name, size in (("token_ids", cap), ("positions", cap), ("token_request", cap),
+                           ("want_rows", cap), ("request_slot", req), ("request_start", req + 1),
+                           ("request_context", req)):
+            self._layout[name] = (cursor, cursor + size)
+            cursor += size
+        pin = self.device.type == "cuda"
+        self._host = torch.zeros(cursor, dtype=torch.int32, pin_memory=pin)
+        self._host_np = self._host.numpy()
+        self._device = torch.zeros(cursor, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._uploaded = torch.cuda.Event() if pin else None
+        self.last_context: Optional[StepContext] = None
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    def _view(self, name: str, device: bool):
+        begin, end = self._layout[name]
+        return (self._device if device else self._host_np)[begin:end]
+
+    # --------------------------------------------------------------------- run
+
+    def prepare(self, entries: Sequence[StepEntry]):
+        """Validate, reserve pages, fill and upload the batch description.
+        Returns ``(context, want_rows_device, n_want, new_lengths)``."""
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        if len(entries) > self.max_requests:
+            raise StepError(f"{len(entries)} requests in one step, at most {self.max_requests}")
+        total = sum(len(entry.tokens) for entry in entries)
+        if total > self.max_tokens:
+            raise StepError(f"{total} tokens in one step, at most {self.max_tokens}")
+        seen = set()
+        vocab = self.model.vocab_size
+        for entry in entries:
+            if entry.request in seen:
+                raise StepError(f"request {entry.request!r} appears twice in one step")
+            seen.add(entry.request)
+            if not self.cache.has(entry.request):
+                raise StepError(f"request {entry.request!r} is not admitted to the cache")
+            if len(entry.tokens) == 0:
+                raise StepError(f"request {entry.request!r} brings no tokens")
+            for token in entry.tokens:
+                if not 0 <= int(token) < vocab:
+                    raise StepError(f"token id {token} of request {entry.request!r} is outside "
+                                    f"the vocabulary of {vocab}")
+            for place in entry.want:
+                if not 0 <= int(place) < len(entry.tokens):
+                    raise StepError(f"wanted place {place} of request {entry.request!r} is "
+                                    f"outside its {len(entry.tokens)} tokens")
+            if self.cache.length(entry.request) + len(entry.tokens) > self.model.max_positions:
+                raise StepError(f"request {entry.request!r} would exceed the model's "
+                                f"{self.model.max_positions} positions")
+
+        if self._uploaded is not None:
+            self._uploaded.synchronize()    # the last upload has left the pinned block
+        token_ids = self._view("token_ids", False)
+        positions = self._view("positions", False)
+        token_request = self._view("token_request", False)
+        want_rows = self._view("want_rows", False)
+        request_slot = self._view("request_slot", False)
+        request_start = self._view("request_start", False)
+        request_context = self._view("request_context", False)
+
+        new_lengths: List[int] = []
+        reserved: List[Hashable] = []
+        cursor = 0
+        n_want = 0
+        max_query = 0
+        max_context = 0
+        try:
+            for index, entry in enumerate(entries):
+                count = len(entry.tokens)
+                before = self.cache.length(entry.request)
+                self.cache.extend(entry.request, before + count)
+                reserved.append(entry.request)
+                token_ids[cursor:cursor + count] = np.asarray(entry.tokens, dtype=np.int32)
+                positions[cursor:cursor + count] = np.arange(before, before + count, dtype=np.int32)
+                token_request[cursor:cursor + count] = index
+                request_slot[index] = self.cache.slot(entry.request)
+                request_start[index] = cursor
+                request_context[index] = before
+                for place in entry.want:
+                    want_rows[n_want] = cursor + int(place)
+                    n_want += 1
+                cursor += count
+                new_lengths.append(before + count)
+                max_query = max(max_query, count)
+                max_context = max(max_context, before + count)
+            request_start[len(entries)] = cursor
+        except Exception:
+            for request in reserved:
+                self.cache.rollback(request)
+            raise
+
+        self._device.copy_(self._host, non_blocking=True)
+        if self._uploaded is not None:
+            self._uploaded.record()
+        self.cache.sync_tables()
+        ctx = StepContext(
+            dtype=self.dtype, device=self.device, workspace=self.workspace,
+            capacity=self.max_tokens, n_tokens=cursor, n_requests=len(entries),
+            token_ids=self._view("token_ids", True), positions=self._view("positions", True),
+            token_request=self._view("token_request", True),
+            request_slot=self._view("request_slot", True),
+            request_start=self._view("request_start", True),
+            request_context=self._view("request_context", True),
+            status=self.status, max_query_len=max_query, max_context_len=max_context,
+            attention_split_keys=self.attention_split_keys,
+            host_request_slots=[int(v) for v in request_slot[:len(entries)]],
+            host_request_starts=[int(v) for v in request_start[:len(entries) + 1]],
+            host_request_contexts=[int(v) for v in request_context[:len(entries)]],
+        )
+        return ctx, self._view("want_rows", True), n_want, new_lengths
+
+    def run(self, entries: Sequence[StepEntry], check_status: bool = True) -> Optional[torch.Tensor]:
+        """Run one step.  Returns float32 logits ``[wanted, vocab]`` in the order of the entries
+        and of their ``want`` lists (a view that the next step overwrites), or None."""
+        ctx, want_rows, n_want, new_lengths = self.prepare(entries)
+        try:
+            logits = self.model.forward(ctx, self.cache, want_rows, n_want)
+            if check_status:
+                self.raise_on_status()
+        except Exception:
+            for entry in entries:
+                self.cache.rollback(entry.request)
+            raise
+        for entry, length in zip(entries, new_lengths):
+            self.cache.commit(entry.request, length)
+        self.last_context = ctx
+        self.steps_run += 1
+        self.tokens_run += ctx.n_tokens
+        return logits
+
+    def raise_on_status(self) -> None:
+        """Read the device status word (synchronises) and raise if a kernel flagged a fault."""
+        flags = int(self.status.item())
+        if flags:
+            self.status.zero_()
+            names = [name for bit, name in ((ops.FLAG_BAD_TOKEN, "token id outside the vocabulary"),
+                                            (ops.FLAG_BAD_PAGE, "block table entry outside the pool"),
+                                            (ops.FLAG_WAIT_TIMEOUT, "a bounded kernel wait ran out"),
+                                            (ops.FLAG_NONFINITE, "non-finite logits")) if flags & bit]
+            raise StepError("the step's kernels reported: " + "; ".join(names))

@@ -1,0 +1,151 @@
+"""A decoder assembled from a :class:`ModelSpec`: embedding, scheduled blocks, norm, head.
+
+The model owns the parts and the order in which they run; it owns no cache and no
+batch.  ``forward`` runs exactly the tokens of the step's context through every
+schedule entry and returns float32 logits at the wanted rows.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager, KvNeed, StateNeed
+from ..config.spec import BlockSpec, ModelSpec
+from ..parts.base import (FeedForward, LayerCache, Mixer, Norm, StepContext, build_part)
+from ..weights.loader import TensorRequest
+
+
+class Block:
+    """One decoder layer: norm, mixer, norm, feed-forward, wired by ``arrangement``."""
+
+    def __init__(self, spec: BlockSpec, hidden_size: int) -> None:
+        if spec.arrangement != "pre_norm":
+            raise ValueError(f"unknown block arrangement {spec.arrangement!r}; known: pre_norm")
+        self.arrangement = spec.arrangement
+        self.mixer_norm: Norm = build_part("norm", spec.mixer_norm, hidden_size)
+        self.mixer: Mixer = build_part("mixer", spec.mixer, hidden_size)
+        self.feed_forward_norm: Norm = build_part("norm", spec.feed_forward_norm, hidden_size)
+        self.feed_forward: FeedForward = build_part("feed_forward", spec.feed_forward, hidden_size)
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+
+    def forward(self, ctx: StepContext, cache: LayerCache, residual: torch.Tensor,
+                normed: torch.Tensor) -> None:
+        # x += mixer(norm(x)); x += ff(norm(x))   (src/model/cpu_llama.cpp:62-98)
+        self.mixer_norm.forward(ctx, residual, normed)
+        self.mixer.forward(ctx, cache, normed, residual)
+        self.feed_forward_norm.forward(ctx, residual, normed)
+        self.feed_forward.forward(ctx, normed, residual)
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec) -> None:
+        spec.validate()
+        self.spec = spec
+        self.hidden_size = spec.hidden_size
+        self.vocab_size = spec.vocab_size
+        self.max_positions = spec.max_positions
+        self.embedding = build_part("embedding", spec.embedding, spec.hidden_size)
+        self.blocks: List[Block] = [Block(block, spec.hidden_size) for block in spec.blocks]
+        self.schedule = spec.schedule
+        self.final_norm: Norm = build_part("norm", spec.final_norm, spec.hidden_size)
+        self.lm_head = build_part("lm_head", spec.lm_head, spec.hidden_size)
+        self.dtype: Optional[torch.dtype] = None
+        self.device: Optional[torch.device] = None
+
+    # ------------------------------------------------------------------ weights
+
+    def all_parts(self):
+        yield self.embedding
+        for block in self.blocks:
+            yield from block.parts()
+        yield self.final_norm
+        yield self.lm_head
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        requests: List[TensorRequest] = []
+        seen = set()
+        for part in self.all_parts():
+            for request in part.tensor_requests():
+                if request.name not in seen:
+                    seen.add(request.name)
+                    requests.append(request)
+        return requests
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype,
+             device: torch.device) -> None:
+        for part in self.all_parts():
+            part.bind(tensors, dtype, device)
+        self.dtype = dtype
+        self.device = device
+
+    def weight_bytes_per_step(self) -> int:
+        """Bytes of weights one step reads: every matrix and norm of every scheduled layer once,
+        plus the head (the embedding is gathered, not streamed)."""
+        total = self.final_norm.weight_bytes() + self.lm_head.weight_bytes()
+        for entry in self.schedule:
+            total += sum(part.weight_bytes() for part in self.blocks[entry.block].parts())
+        return total
+
+    # -------------------------------------------------------------------- cache
+
+    def cache_needs(self):
+        """``(kv_needs, state_needs)`` keyed by the schedule entries that own a cache."""
+        kv: Dict[int, KvNeed] = {}
+        state: Dict[int, StateNeed] = {}
+        for index, entry in enumerate(self.schedule):
+            if entry.cache_from is not None:
+                continue
+            mixer = self.blocks[entry.block].mixer
+            need = mixer.kv_need()
+            if need is not None:
+                kv[index] = need
+            state_need = mixer.state_need()
+            if state_need is not None:
+                state[index] = state_need
+        for index, entry in enumerate(self.schedule):
+            if entry.cache_from is None:
+                continue
+            own = self.blocks[entry.block].mixer.kv_need()
+            other = self.blocks[self.schedule[entry.cache_from].block].mixer.kv_need()
+            if own != other:
+                raise ValueError(f"schedule entry {index} reads the cache of entry "
+                                 f"{entry.cache_from}, whose geometry differs")
+        return kv, state
+
+    def layer_cache(self, cache: CacheManager, index: int) -> LayerCache:
+        entry = self.schedule[index]
+        owner = index if entry.cache_from is None else entry.cache_from
+        view = LayerCache(entry=owner, owns=entry.cache_from is None)
+        if owner in cache._entry_place:
+            group = cache.group_of(owner)
+            view.keys, view.values = cache.layer_storage(owner)
+            view.block_tables = group.device_tables
+            view.page_size = group.page_size
+            view.num_pages = group.pool.num_pages
+            view.window = group.need.window
+        if owner in cache.states:
+            view.state = cache.state(owner)
+        return view
+
+    # ------------------------------------------------------------------ forward
+
+    def forward(self, ctx: StepContext, cache: CacheManager, want_rows: Optional[torch.Tensor],
+                n_want: int) -> Optional[torch.Tensor]:
+        """Run the step's tokens; return logits ``[n_want, vocab]`` float32 for the flattened
+        token indices in ``want_rows`` (device int32), or None when nothing is wanted."""
+        h = self.hidden_size
+        residual = ctx.workspace.get("model.residual", (ctx.capacity, h), torch.float32)
+        normed = ctx.workspace.get("model.normed", (ctx.capacity, h), ctx.dtype)
+        self.embedding.forward(ctx, residual)
+        for index, entry in enumerate(self.schedule):
+            self.blocks[entry.block].forward(ctx, self.layer_cache(cache, index), residual, normed)
+        if n_want == 0:
+            return None
+        wanted = ctx.workspace.get("model.wanted", (ctx.capacity, h), ctx.dtype)
+        logits = ctx.workspace.get("model.logits", (ctx.capacity, self.vocab_size), torch.float32)
+        self.final_norm.forward(ctx, residual, wanted, rows=want_rows, n_rows=n_want)
+        self.lm_head.forward(ctx, wanted, logits, n_want)
+        return logits[:n_want]

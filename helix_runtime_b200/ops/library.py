@@ -1,0 +1,233 @@
+"""Python face of the CUDA kernel library: one function per entry point.
+
+The functions take ``torch`` tensors, check dtypes and contiguity, and pass raw
+device pointers plus the current CUDA stream to the C interface.  Nothing here
+computes: there is no CPU path and no library stand-in.  If the shared object
+cannot be built or loaded the import of this module's :func:`lib` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+from ..csrc import build as _build
+
+HX_F32 = 0
+HX_BF16 = 1
+
+EPI_STORE = 0        # compute dtype out
+EPI_STORE_F32 = 1    # float32 out
+EPI_ADD_F32 = 2      # float32 out += product
+EPI_SWIGLU = 3       # tensor-core kernel only
+
+FLAG_BAD_TOKEN = 1
+FLAG_BAD_PAGE = 2
+FLAG_WAIT_TIMEOUT = 4
+FLAG_NONFINITE = 8
+
+_c_int = ctypes.c_int
+_c_ptr = ctypes.c_void_p
+_c_float = ctypes.c_float
+
+_lock = threading.Lock()
+_library: Optional[ctypes.CDLL] = None
+
+
+class KernelError(RuntimeError):
+    """A kernel entry point refused its arguments or failed to launch."""
+
+
+def _declare(library: ctypes.CDLL) -> None:
+    library.hx_last_error.restype = ctypes.c_char_p
+    library.hx_last_error.argtypes = []
+    library.hx_abi_version.restype = _c_int
+    library.hx_embed.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
+    library.hx_rmsnorm.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_float, _c_ptr]
+    library.hx_swiglu.argtypes = [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_rope_append.argtypes = [
+        _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
+        _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+        _c_ptr, _c_ptr]
+    library.hx_gemm_simt.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int,
+                                     _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_gemm_tc.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_int,
+                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
+    library.hx_gemm_tc_supports.argtypes = [_c_int] * 5
+    library.hx_gemm_tc_token_tile.argtypes = [_c_int]
+    library.hx_paged_attention.argtypes = [
+        _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
+        _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+        _c_int, _c_ptr, _c_ptr]
+    library.hx_paged_attention_scratch_floats.restype = ctypes.c_longlong
+    library.hx_paged_attention_scratch_floats.argtypes = [_c_int] * 4
+    library.hx_argmax.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]
+    library.hx_sample.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr]
+    for name in ("hx_embed", "hx_rmsnorm", "hx_swiglu", "hx_rope_append", "hx_gemm_simt",
+                 "hx_gemm_tc", "hx_gemm_tc_supports", "hx_gemm_tc_token_tile",
+                 "hx_paged_attention", "hx_argmax", "hx_sample"):
+        getattr(library, name).restype = _c_int
+
+
+def lib() -> ctypes.CDLL:
+    """Load (building at first use) the kernel library; raise if that is impossible."""
+    global _library
+    if _library is None:
+        with _lock:
+            if _library is None:
+                path = _build.build()
+                library = ctypes.CDLL(path)
+                _declare(library)
+                _library = library
+    return _library
+
+
+def library_file() -> str:
+    lib()
+    return _build.library_path()
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        raise KernelError(lib().hx_last_error().decode("utf-8", "replace") or f"kernel error {code}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return HX_F32
+    if dtype == torch.bfloat16:
+        return HX_BF16
+    raise KernelError(f"unsupported compute dtype {dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _need(tensor: torch.Tensor, dtype: torch.dtype, name: str, last_dim_contiguous: bool = True) -> None:
+    if not tensor.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+    if last_dim_contiguous and tensor.dim() > 0 and tensor.stride(-1) != 1:
+        raise KernelError(f"{name} must be contiguous in its last dimension")
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t] (float32) = table[ids[t]]."""
+    _need(ids, torch.int32, "ids")
+    _need(out, torch.float32, "out")
+    vocab, hidden = table.shape
+    tokens = ids.shape[0]
+    assert table.is_contiguous() and out.is_contiguous() and out.shape[1] == hidden
+    _check(lib().hx_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
+                          tokens, hidden, vocab, _ptr(status), _stream()))
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight; x and weight float32."""
+    _need(x, torch.float32, "x")
+    _need(weight, torch.float32, "weight")
+    assert x.is_contiguous() and out.is_contiguous()
+    hidden = x.shape[-1]
+    n_rows = out.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        assert rows.shape[0] >= n_rows
+    else:
+        assert x.shape[0] >= n_rows
+    _check(lib().hx_rmsnorm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+                            _ptr(rows), n_rows, hidden, float(eps), _stream()))
+
+
+def swiglu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
+    """act[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    tokens, intermediate = act.shape
+    assert gate_up.dtype == act.dtype and gate_up.stride(-1) == 1 and act.is_contiguous()
+    _check(lib().hx_swiglu(gate_up.data_ptr(), act.data_ptr(), dtype_code(act.dtype), tokens,
+                           intermediate, gate_up.stride(0), _stream()))
+
+
+def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_request: torch.Tensor,
+                request_table_row: torch.Tensor, block_tables: torch.Tensor,
+                k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                cos_table: torch.Tensor, sin_table: torch.Tensor, tokens: int, heads: int,
+                kv_heads: int, head_dim: int, rotary_dim: int, pairing: int, page_size: int,
+                num_pages: int, status: torch.Tensor) -> None:
+    """Rotate q and k of ``qkv[:tokens]`` in place and write k, v into their pages."""
+    write = k_cache is not None
+    _check(lib().hx_rope_append(
+        qkv.data_ptr(), dtype_code(qkv.dtype), qkv.stride(0), positions.data_ptr(),
+        token_request.data_ptr(), request_table_row.data_ptr(), block_tables.data_ptr(),
+        block_tables.stride(0), _ptr(k_cache), _ptr(v_cache), 1 if write else 0,
+        cos_table.data_ptr(), sin_table.data_ptr(), cos_table.shape[0], tokens, heads, kv_heads,
+        head_dim, rotary_dim, pairing, page_size, num_pages, _ptr(status), _stream()))
+
+
+def gemm_tc_supports(tokens: int, features: int, depth: int, ldx: int, ldw: int) -> bool:
+    return bool(lib().hx_gemm_tc_supports(tokens, features, depth, ldx, ldw))
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tokens: int, epilogue: int) -> None:
+    """out[:tokens] (op)= x[:tokens] @ w.T on the CUDA cores (float32 or bfloat16 storage)."""
+    assert x.dtype == w.dtype and x.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
+    features, depth = w.shape
+    _check(lib().hx_gemm_simt(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                              out.stride(0), dtype_code(x.dtype), tokens, features, depth, epilogue,
+                              _stream()))
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tokens: int, features: int,
+            epilogue: int, status: torch.Tensor, up_row_offset: int = 0, k_splits: int = 1) -> None:
+    """out[:tokens, :features] (op)= x[:tokens] @ w.T on the tensor cores (bfloat16)."""
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    depth = w.shape[1]
+    _check(lib().hx_gemm_tc(x.data_ptr(), x.stride(0), x.shape[0], w.data_ptr(), w.stride(0),
+                            w.shape[0], out.data_ptr(), out.stride(0), tokens, features, depth,
+                            epilogue, up_row_offset, k_splits, status.data_ptr(), _stream()))
+
+
+def attention_scratch_floats(tokens: int, heads: int, head_dim: int, max_splits: int) -> int:
+    return int(lib().hx_paged_attention_scratch_floats(tokens, heads, head_dim, max_splits))
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    positions: torch.Tensor, token_request: torch.Tensor,
+                    request_table_row: torch.Tensor, block_tables: torch.Tensor, out: torch.Tensor,
+                    partial: Optional[torch.Tensor], tokens: int, heads: int, kv_heads: int,
+                    head_dim: int, page_size: int, num_pages: int, window: int, scale: float,
+                    split_keys: int, max_splits: int, status: torch.Tensor) -> None:
+    """out[t, h*D:(h+1)*D] = attention of query (t, h) over its request's pages."""
+    _check(lib().hx_paged_attention(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), dtype_code(q.dtype),
+        positions.data_ptr(), token_request.data_ptr(), request_table_row.data_ptr(),
+        block_tables.data_ptr(), block_tables.stride(0), out.data_ptr(), out.stride(0),
+        _ptr(partial), tokens, heads, kv_heads, head_dim, page_size, num_pages, window,
+        float(scale), split_keys, max_splits, _ptr(status), _stream()))
+
+
+def argmax(logits: torch.Tensor, tokens_out: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+    _need(logits, torch.float32, "logits")
+    _need(tokens_out, torch.int32, "tokens_out")
+    rows, vocab = logits.shape
+    _check(lib().hx_argmax(logits.data_ptr(), logits.stride(0), rows, vocab, tokens_out.data_ptr(),
+                           _ptr(status), _stream()))
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+           tokens_out: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+    _need(logits, torch.float32, "logits")
+    _need(temperature, torch.float32, "temperature")
+    _need(uniform, torch.float32, "uniform")
+    _need(tokens_out, torch.int32, "tokens_out")
+    rows, vocab = logits.shape
+    _check(lib().hx_sample(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
+                           uniform.data_ptr(), tokens_out.data_ptr(), _ptr(status), _stream()))

@@ -1,0 +1,117 @@
+"""Causal multi-head attention over the paged cache.
+
+Parameters: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale`` (default
+``1/sqrt(head_dim)``, src/attention/reference.cpp:152), ``window`` (None: all earlier
+keys), ``position`` (a position-encoding spec), ``checkpoint_pairing`` (how the
+checkpoint's q/k rows are ordered for rotation).  Tensors: ``q``, ``k``, ``v``
+``[heads*head_dim, hidden]`` and ``o`` ``[hidden, heads*head_dim]``, all ``[out, in]``.
+
+At load the three projections are fused into one ``[(A + 2 Akv) D, H]`` matrix and,
+when the checkpoint rotates half-split pairs while the encoding rotates adjacent
+pairs, the rows of q and k are permuted per head to ``[0, D/2, 1, D/2+1, ...]``
+(the reference's converter does the same, tools/convert_hf_llama.py:535-542).
+Steps: fused projection, rotary encoding + cache append, paged attention, output
+projection added into the residual (src/model/cpu_llama.cpp:65-91).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Mapping, Optional
+
+import torch
+
+from ..cache.manager import KvNeed
+from ..config.spec import PartSpec
+from ..ops import library as ops
+from ..weights.loader import TensorRequest
+from .base import LayerCache, Mixer, StepContext, build_part, register_part
+from .linear import project
+
+
+def rotary_row_permutation(heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
+    """Row order that turns half-split rotary rows into adjacent-pair rows, per head."""
+    half = rotary_dim // 2
+    order: List[int] = []
+    for head in range(heads):
+        base = head * head_dim
+        for frequency in range(half):
+            order.extend((base + frequency, base + half + frequency))
+        order.extend(range(base + rotary_dim, base + head_dim))
+    return torch.tensor(order, dtype=torch.long)
+
+
+class PagedAttention(Mixer):
+    def __init__(self, spec: PartSpec, hidden_size: int) -> None:
+        super().__init__(spec, hidden_size)
+        self.heads = int(spec["num_heads"])
+        self.kv_heads = int(spec["num_kv_heads"])
+        self.head_dim = int(spec["head_dim"])
+        if self.heads % self.kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        self.scale = float(spec.get("scale") or 1.0 / math.sqrt(float(self.head_dim)))
+        window = spec.get("window")
+        self.window: Optional[int] = int(window) if window else None
+        self.position = build_part("position", spec["position"], hidden_size)
+        self.checkpoint_pairing = spec.get("checkpoint_pairing", self.position.pairing)
+        self.names = dict(spec.tensors)
+        self.q_size = self.heads * self.head_dim
+        self.kv_size = self.kv_heads * self.head_dim
+        self.qkv_size = self.q_size + 2 * self.kv_size
+        self.w_qkv: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+
+    def kv_need(self) -> Optional[KvNeed]:
+        return KvNeed(self.kv_heads, self.head_dim, self.window)
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        h = self.hidden_size
+        return [
+            TensorRequest(self.names["q"], (self.q_size, h)),
+            TensorRequest(self.names["k"], (self.kv_size, h)),
+            TensorRequest(self.names["v"], (self.kv_size, h)),
+            TensorRequest(self.names["o"], (h, self.q_size)),
+        ]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
+        q = tensors[self.names["q"]]
+        k = tensors[self.names["k"]]
+        v = tensors[self.names["v"]]
+        if self.checkpoint_pairing != self.position.pairing:
+            if self.checkpoint_pairing == "half_split" and self.position.pairing == "adjacent":
+                rotary = self.position.rotary_dim
+                q = q[rotary_row_permutation(self.heads, self.head_dim, rotary).to(q.device)]
+                k = k[rotary_row_permutation(self.kv_heads, self.head_dim, rotary).to(k.device)]
+            else:
+                raise ValueError(f"no row permutation from {self.checkpoint_pairing!r} to "
+                                 f"{self.position.pairing!r}")
+        self.w_qkv = torch.cat([q, k, v], dim=0).to(device=device, dtype=dtype).contiguous()
+        self.w_o = tensors[self.names["o"]].to(device=device, dtype=dtype).contiguous()
+        self.position.bind(tensors, dtype, device)
+
+    def weight_bytes(self) -> int:
+        return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()
+
+    def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
+                residual: torch.Tensor) -> None:
+        n = ctx.n_tokens
+        qkv = ctx.workspace.get("attention.qkv", (ctx.capacity, self.qkv_size), ctx.dtype)
+        context = ctx.workspace.get("attention.context", (ctx.capacity, self.q_size), ctx.dtype)
+        project(x, self.w_qkv, qkv, n, ops.EPI_STORE, ctx.status)
+        self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
+
+        window = cache.window or 0
+        longest = ctx.max_context_len if not window else min(ctx.max_context_len, window)
+        split_keys = ctx.attention_split_keys
+        max_splits = max(1, -(-longest // split_keys))
+        partial = None
+        if max_splits > 1:
+            floats = ops.attention_scratch_floats(n, self.heads, self.head_dim, max_splits)
+            partial = ctx.workspace.at_least("attention.partial", floats, torch.float32)
+        ops.paged_attention(qkv, cache.keys, cache.values, ctx.positions, ctx.token_request,
+                            ctx.request_slot, cache.block_tables, context, partial, n, self.heads,
+                            self.kv_heads, self.head_dim, cache.page_size, cache.num_pages, window,
+                            self.scale, split_keys, max_splits, ctx.status)
+        project(context, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status)
+
+
+register_part("mixer", "paged_attention", PagedAttention)

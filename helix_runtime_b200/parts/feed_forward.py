@@ -1,0 +1,55 @@
+"""Gated feed-forward: ``down(act(gate(x)) * up(x))`` (src/model/cpu_llama.cpp:93-98).
+
+Parameters: ``intermediate_size``, ``activation`` (``silu``).  Tensors: ``gate``, ``up``
+``[intermediate, hidden]`` and ``down`` ``[hidden, intermediate]``.  gate and up are
+fused into one ``[2I, H]`` matrix at load so that both products read the input once;
+on the tensor cores SwiGLU is the epilogue of that product.
+"""
+from __future__ import annotations
+
+from typing import List, Mapping, Optional
+
+import torch
+
+from ..config.spec import PartSpec
+from ..ops import library as ops
+from ..weights.loader import TensorRequest
+from .base import FeedForward, StepContext, register_part
+from .linear import project, project_swiglu
+
+
+class GatedMlp(FeedForward):
+    def __init__(self, spec: PartSpec, hidden_size: int) -> None:
+        super().__init__(spec, hidden_size)
+        self.intermediate = int(spec["intermediate_size"])
+        activation = spec.get("activation", "silu")
+        if activation != "silu":
+            raise ValueError(f"activation {activation!r} has no kernel; only 'silu'")
+        self.names = dict(spec.tensors)
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        h, i = self.hidden_size, self.intermediate
+        return [TensorRequest(self.names["gate"], (i, h)), TensorRequest(self.names["up"], (i, h)),
+                TensorRequest(self.names["down"], (h, i))]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
+        self.w_gate_up = torch.cat([tensors[self.names["gate"]], tensors[self.names["up"]]],
+                                   dim=0).to(device=device, dtype=dtype).contiguous()
+        self.w_down = tensors[self.names["down"]].to(device=device, dtype=dtype).contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, residual: torch.Tensor) -> None:
+        n = ctx.n_tokens
+        act = ctx.workspace.get("mlp.act", (ctx.capacity, self.intermediate), ctx.dtype)
+        project_swiglu(
+            x, self.w_gate_up, self.intermediate, act,
+            lambda: ctx.workspace.get("mlp.gate_up", (ctx.capacity, 2 * self.intermediate), ctx.dtype),
+            n, ctx.status)
+        project(act, self.w_down, residual, n, ops.EPI_ADD_F32, ctx.status)
+
+
+register_part("feed_forward", "gated_mlp", GatedMlp)

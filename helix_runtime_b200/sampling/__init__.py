@@ -1,0 +1,3 @@
+from .sampler import Sampler, uniform_for
+
+__all__ = ["Sampler", "uniform_for"]

@@ -1,0 +1,68 @@
+"""Greedy and temperature sampling of the step's wanted logits, on the device.
+
+Greedy is the reference's rule: lowest id among the maxima, non-finite logits fail the
+request (src/model/cpu_generation.cpp:82-97).  The reference samples with nothing else
+(docs/MODEL_SUPPORT.md:669-671); temperature sampling is this engine's own:
+``p = softmax(logits / T)`` in float32 and the inverse cumulative distribution at a
+uniform number drawn from the request's own counter-based stream, keyed by the
+request's seed and the index of the token being generated, so a draw never depends
+on what else is in the batch or on how the work was cut into steps.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..ops import library as ops
+
+_MASK = (1 << 64) - 1
+
+
+def _splitmix64(value: int) -> int:
+    value = (value + 0x9E3779B97F4A7C15) & _MASK
+    value = ((value ^ (value >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    value = ((value ^ (value >> 27)) * 0x94D049BB133111EB) & _MASK
+    return value ^ (value >> 31)
+
+
+def uniform_for(seed: int, token_index: int) -> float:
+    """The uniform number in [0, 1) for the ``token_index``-th generated token of a request
+    with ``seed``: 24 bits of a splitmix64 hash, exact in float32."""
+    mixed = _splitmix64((_splitmix64(seed & _MASK) ^ (token_index & _MASK)) & _MASK)
+    return (mixed >> 40) / float(1 << 24)
+
+
+class Sampler:
+    def __init__(self, device: torch.device, max_rows: int) -> None:
+        self.device = device
+        self.max_rows = max_rows
+        pin = device.type == "cuda"
+        self._host_params = torch.zeros((2, max_rows), dtype=torch.float32, pin_memory=pin)
+        self._device_params = torch.zeros((2, max_rows), dtype=torch.float32, device=device)
+        self.tokens = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self._host_tokens = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+
+    def sample(self, logits: torch.Tensor, temperatures: Sequence[float],
+               uniforms: Sequence[float], status: Optional[torch.Tensor]) -> torch.Tensor:
+        """Select one token per row; returns the device tensor of ids (-1: non-finite row)."""
+        rows = logits.shape[0]
+        if rows > self.max_rows:
+            raise ValueError(f"{rows} rows to sample, at most {self.max_rows}")
+        out = self.tokens[:rows]
+        if all(t <= 0.0 for t in temperatures):
+            ops.argmax(logits, out, status)
+            return out
+        params = self._host_params.numpy()
+        params[0, :rows] = np.asarray(temperatures, dtype=np.float32)
+        params[1, :rows] = np.asarray(uniforms, dtype=np.float32)
+        self._device_params.copy_(self._host_params, non_blocking=True)
+        ops.sample(logits, self._device_params[0, :rows], self._device_params[1, :rows], out, status)
+        return out
+
+    def to_host(self, tokens: torch.Tensor) -> List[int]:
+        rows = tokens.shape[0]
+        self._host_tokens[:rows].copy_(tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return [int(t) for t in self._host_tokens[:rows]]

@@ -1,0 +1,35 @@
+"""The two tiny configurations every test uses, and how their model folders are made.
+
+They differ in every size and option: layers 2/3, hidden 64/120, heads 4/5, head size
+16/24, intermediate 176/320 (neither a multiple of 64), vocabulary 256/384, rope theta
+1e4/5e5, eps 1e-5/1e-6, positions 128/256, page size 8/16.  Norm weights are drawn
+around one (not exactly one) so that a norm that forgot its weight would show.
+"""
+from __future__ import annotations
+
+import os
+
+from helix_runtime_b200 import LlamaConfig, write_random_model
+
+TINY_A = dict(vocab_size=256, hidden_size=64, intermediate_size=176, num_hidden_layers=2,
+              num_attention_heads=4, num_key_value_heads=4, head_dim=16,
+              max_position_embeddings=128, rms_norm_eps=1e-5, rope_theta=10000.0)
+TINY_B = dict(vocab_size=384, hidden_size=120, intermediate_size=320, num_hidden_layers=3,
+              num_attention_heads=5, num_key_value_heads=5, head_dim=24,
+              max_position_embeddings=256, rms_norm_eps=1e-6, rope_theta=500000.0)
+PAGE_SIZE = {"A": 8, "B": 16}
+SEED = {"A": 0, "B": 1}
+
+
+def tiny_config(name: str) -> LlamaConfig:
+    return LlamaConfig(**{"A": TINY_A, "B": TINY_B}[name])
+
+
+def make_folder(directory: str, name: str, storage_dtype: str = "float32",
+                scale_std: float = 0.1, std: float = 0.02) -> str:
+    """Write the model folder of tiny configuration ``name`` under ``directory``."""
+    path = os.path.join(directory, f"tiny_{name}_{storage_dtype}")
+    if not os.path.exists(os.path.join(path, "model.safetensors")):
+        write_random_model(path, tiny_config(name), SEED[name], std=std, scale_std=scale_std,
+                           storage_dtype=storage_dtype)
+    return path
