@@ -91,12 +91,13 @@ def random_model(config, seed: int, dtype: Union[str, torch.dtype] = "bfloat16",
 
 def write_random_model(directory: str, config, seed: int, std: float = 0.02,
                        scale_std: float = 0.0,
-                       storage_dtype: Union[str, torch.dtype] = "bfloat16") -> None:
+                       storage_dtype: Union[str, torch.dtype] = "bfloat16",
+                       gains=None) -> None:
     """The random-weights mode: write ``config.json`` and ``model.safetensors``."""
     architecture = architecture_for(config.to_dict())
     model = DecoderModel(architecture.build_spec(config))
     tensors = random_tensors(model.tensor_requests(), seed, std=std, scale_std=scale_std,
-                             storage_dtype=parse_dtype(storage_dtype))
+                             storage_dtype=parse_dtype(storage_dtype), gains=gains)
     write_model_folder(directory, config.to_dict(), tensors)
 
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Dict, Sequence
+from typing import Dict, Mapping, Optional, Sequence
 
 import torch
 
@@ -20,11 +20,14 @@ from .safetensors_io import write_safetensors
 
 def random_tensors(requests: Sequence[TensorRequest], seed: int, std: float = 0.02,
                    scale_std: float = 0.0,
-                   storage_dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
+                   storage_dtype: torch.dtype = torch.bfloat16,
+                   gains: Optional[Mapping[str, float]] = None) -> Dict[str, torch.Tensor]:
     """Draw every requested tensor from one generator, in request order.
 
     Matrices and tables of embeddings are N(0, std) in ``storage_dtype``; scale
-    vectors (norm weights) are ``1 + N(0, scale_std)`` stored in float32.
+    vectors (norm weights) are ``1 + N(0, scale_std)`` stored in float32.  ``gains``
+    multiplies every matrix whose name contains a key by that key's factor (tests
+    sharpen the attention of tiny models this way, so that a misplaced key shows).
     """
     generator = torch.Generator(device="cpu")
     generator.manual_seed(int(seed))
@@ -40,6 +43,9 @@ def random_tensors(requests: Sequence[TensorRequest], seed: int, std: float = 0.
             raise ValueError("integer tables have no random initialisation")
         else:
             value = torch.randn(request.shape, generator=generator, dtype=torch.float32) * std
+            for key, factor in (gains or {}).items():
+                if key in request.name:
+                    value = value * factor
             tensors[request.name] = value.to(storage_dtype)
     return tensors
 

@@ -1,0 +1,413 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the engine's.
+
+References are the NumPy functions of ``plain_llama`` (double accumulators) or a few lines of
+NumPy written here from the same formulas.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+from engine_harness import assert_close
+from helix_runtime_b200.ops import library as ops
+
+pytestmark = pytest.mark.gpu
+
+DEVICE = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def dev(array, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(array)).to(device=DEVICE, dtype=dtype).contiguous()
+
+
+def host(tensor):
+    return tensor.detach().float().cpu().numpy()
+
+
+def status_word():
+    return torch.zeros(1, dtype=torch.int32, device=DEVICE)
+
+
+def rounded(array, dtype):
+    """The values a tensor of ``dtype`` actually holds, as float32."""
+    return host(dev(array, dtype))
+
+
+# ------------------------------------------------------------------- embedding
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_gathers_rows_and_flags_bad_ids(dtype):
+    rng = np.random.default_rng(0)
+    vocab, hidden = 1000, 72
+    table = dev(rng.normal(size=(vocab, hidden)), dtype)
+    ids = torch.tensor([0, 999, 17, 17, 500], dtype=torch.int32, device=DEVICE)
+    out = torch.empty((5, hidden), dtype=torch.float32, device=DEVICE)
+    status = status_word()
+    ops.embed(table, ids, out, status)
+    np.testing.assert_array_equal(host(out), host(table)[[0, 999, 17, 17, 500]])
+    assert int(status.item()) == 0
+    bad = torch.tensor([3, 1000, -1], dtype=torch.int32, device=DEVICE)
+    out = torch.zeros((3, hidden), dtype=torch.float32, device=DEVICE)
+    ops.embed(table, bad, out, status)
+    result = host(out)
+    np.testing.assert_array_equal(result[0], host(table)[3])
+    assert np.isnan(result[1]).all() and np.isnan(result[2]).all()
+    assert int(status.item()) & ops.FLAG_BAD_TOKEN
+
+
+# --------------------------------------------------------------------- RMSNorm
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,eps", [(200, 1e-5), (4104, 1e-6), (24, 1e-3)])
+def test_rmsnorm(dtype, hidden, eps):
+    rng = np.random.default_rng(1)
+    x = (rng.normal(size=(7, hidden)) * 3.0).astype(np.float32)
+    w = (1.0 + 0.3 * rng.normal(size=hidden)).astype(np.float32)
+    out = torch.empty((7, hidden), dtype=dtype, device=DEVICE)
+    ops.rmsnorm(dev(x), dev(w), out, eps)
+    expected = plain.rms_norm(x, w, eps)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=1e-2, rtol=8e-3)
+    assert_close(host(out), expected, "rmsnorm", **tol)
+    # gathered rows (the final norm runs on the wanted rows only)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEVICE)
+    out = torch.empty((3, hidden), dtype=dtype, device=DEVICE)
+    ops.rmsnorm(dev(x), dev(w), out, eps, rows)
+    assert_close(host(out), expected[[6, 0, 3]], "rmsnorm gathered", **tol)
+
+
+# ---------------------------------------------------------------------- SwiGLU
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    rng = np.random.default_rng(2)
+    tokens, inter = 9, 176
+    gate_up = (rng.normal(size=(tokens, 2 * inter)) * 4.0).astype(np.float32)
+    gate_up[0, :4] = [-100.0, 100.0, 0.0, -20.0]
+    held = rounded(gate_up, dtype)
+    act = torch.empty((tokens, inter), dtype=dtype, device=DEVICE)
+    ops.swiglu(dev(gate_up, dtype), act)
+    expected = plain.swiglu(held[:, :inter], held[:, inter:])
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=1e-2, rtol=8e-3)
+    assert_close(host(act), expected, "swiglu", **tol)
+
+
+# -------------------------------------------------------------- matrix products
+
+def product_reference(x, w):
+    return (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,features,depth", [(37, 83, 45), (1, 130, 257), (130, 64, 64)])
+def test_gemm_on_cuda_cores(dtype, tokens, features, depth):
+    rng = np.random.default_rng(3)
+    x = rounded(rng.normal(size=(tokens, depth)), dtype)
+    w = rounded(rng.normal(size=(features, depth)) * 0.1, dtype)
+    expected = product_reference(x, w)
+    tight = dict(atol=2e-5, rtol=2e-5)
+    out = torch.empty((tokens, features), dtype=dtype, device=DEVICE)
+    ops.gemm_simt(dev(x, dtype), dev(w, dtype), out, tokens, ops.EPI_STORE)
+    assert_close(host(out), expected, "store",
+                 **(tight if dtype == torch.float32 else dict(atol=2e-2, rtol=8e-3)))
+    out32 = torch.empty((tokens, features), dtype=torch.float32, device=DEVICE)
+    ops.gemm_simt(dev(x, dtype), dev(w, dtype), out32, tokens, ops.EPI_STORE_F32)
+    assert_close(host(out32), expected, "store f32", **tight)
+    base = rng.normal(size=(tokens, features)).astype(np.float32)
+    acc = dev(base)
+    ops.gemm_simt(dev(x, dtype), dev(w, dtype), acc, tokens, ops.EPI_ADD_F32)
+    assert_close(host(acc), base + expected, "add f32", **tight)
+
+
+TC_SHAPES = [
+    # tokens, features, depth: every token tile (16..256), ragged edges in all three sizes
+    (1, 64, 64), (5, 200, 120), (16, 384, 328), (17, 128, 1024), (40, 136, 72),
+    (100, 256, 4096), (130, 384, 200), (300, 520, 328), (513, 128, 64),
+]
+
+
+@pytest.mark.parametrize("tokens,features,depth", TC_SHAPES)
+def test_gemm_on_tensor_cores(tokens, features, depth):
+    rng = np.random.default_rng(4)
+    x = rounded(rng.normal(size=(tokens, depth)), torch.bfloat16)
+    w = rounded(rng.normal(size=(features, depth)) * 0.1, torch.bfloat16)
+    expected = product_reference(x, w)
+    status = status_word()
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    assert ops.gemm_tc_supports(tokens, features, depth, depth, depth)
+    tight = dict(atol=1e-4 * math.sqrt(depth / 64), rtol=2e-5)
+
+    out32 = torch.full((tokens, features), float("nan"), dtype=torch.float32, device=DEVICE)
+    ops.gemm_tc(xd, wd, out32, tokens, features, ops.EPI_STORE_F32, status)
+    assert_close(host(out32), expected, "store f32", **tight)
+
+    out16 = torch.full((tokens, features), float("nan"), dtype=torch.bfloat16, device=DEVICE)
+    ops.gemm_tc(xd, wd, out16, tokens, features, ops.EPI_STORE, status)
+    assert_close(host(out16), expected, "store bf16", atol=2e-2, rtol=8e-3)
+
+    base = rng.normal(size=(tokens, features)).astype(np.float32)
+    for splits in (1, 3):
+        acc = dev(base)
+        ops.gemm_tc(xd, wd, acc, tokens, features, ops.EPI_ADD_F32, status, k_splits=splits)
+        assert_close(host(acc), base + expected, f"add f32 with {splits} k-splits", **tight)
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("tokens,inter,depth", [(3, 176, 64), (33, 320, 120), (200, 1000, 264),
+                                                 (64, 128, 512)])
+def test_gemm_with_swiglu_epilogue(tokens, inter, depth):
+    rng = np.random.default_rng(5)
+    x = rounded(rng.normal(size=(tokens, depth)), torch.bfloat16)
+    w = rounded(rng.normal(size=(2 * inter, depth)) * 0.2, torch.bfloat16)
+    gate = product_reference(x, w[:inter])
+    up = product_reference(x, w[inter:])
+    expected = plain.swiglu(gate, up)
+    status = status_word()
+    act = torch.full((tokens, inter), float("nan"), dtype=torch.bfloat16, device=DEVICE)
+    ops.gemm_tc(dev(x, torch.bfloat16), dev(w, torch.bfloat16), act, tokens, inter,
+                ops.EPI_SWIGLU, status, up_row_offset=inter)
+    assert_close(host(act), expected, "swiglu epilogue", atol=2e-2, rtol=8e-3)
+    assert int(status.item()) == 0
+
+
+def test_tensor_core_gemm_refuses_depths_it_cannot_load():
+    x = torch.zeros((4, 44), dtype=torch.bfloat16, device=DEVICE)
+    w = torch.zeros((8, 44), dtype=torch.bfloat16, device=DEVICE)
+    out = torch.zeros((4, 8), dtype=torch.float32, device=DEVICE)
+    assert not ops.gemm_tc_supports(4, 8, 44, 44, 44)
+    with pytest.raises(ops.KernelError, match="not supported"):
+        ops.gemm_tc(x, w, out, 4, 8, ops.EPI_STORE_F32, status_word())
+
+
+# ------------------------------------------------- rotary encoding + cache append
+
+def rope_reference(x, positions, theta, rotary_dim, pairing):
+    """x [T, heads, D]; the plain rotation applied to the first ``rotary_dim`` coordinates."""
+    out = x.copy()
+    for t, position in enumerate(positions):
+        cosine, sine = plain.rope_table(1, rotary_dim, theta, offset=int(position))
+        part = x[t:t + 1, :, :rotary_dim]
+        rotate = plain.rope_adjacent if pairing == "adjacent" else plain.rope_half_split
+        out[t:t + 1, :, :rotary_dim] = rotate(part, cosine, sine)
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim,pairing", [
+    (4, 4, 16, 16, "adjacent"), (6, 2, 24, 24, "half_split"), (3, 1, 32, 16, "adjacent"),
+    (5, 5, 100, 100, "adjacent"), (2, 2, 48, 32, "half_split")])
+def test_rope_and_cache_append(dtype, heads, kv_heads, head_dim, rotary_dim, pairing):
+    rng = np.random.default_rng(6)
+    page_size, num_pages, theta, max_positions = 8, 12, 50000.0, 96
+    # two requests: one continues at position 13 (inside a page), one starts at 0
+    positions = np.array([13, 14, 15, 16, 17, 0, 1, 2], dtype=np.int32)
+    token_request = np.array([0, 0, 0, 0, 0, 1, 1, 1], dtype=np.int32)
+    slots = np.array([2, 0], dtype=np.int32)
+    tables = np.full((3, 12), -1, dtype=np.int32)
+    tables[2, :3] = [7, 3, 9]
+    tables[0, :1] = [5]
+    tokens = len(positions)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = rounded(rng.normal(size=(tokens, width)), dtype)
+    half = max(rotary_dim // 2, 1)
+    exponent = -2.0 * np.arange(half) / rotary_dim
+    angle = np.arange(max_positions)[:, None] * np.power(np.float64(np.float32(theta)), exponent)[None, :]
+    cos, sin = dev(np.cos(angle)), dev(np.sin(angle))
+    k_cache = torch.full((num_pages, kv_heads, page_size, head_dim), float("nan"), dtype=dtype, device=DEVICE)
+    v_cache = torch.full_like(k_cache, float("nan"))
+    buffer = dev(qkv, dtype)
+    status = status_word()
+    ops.rope_append(buffer, dev(positions, torch.int32), dev(token_request, torch.int32),
+                    dev(slots, torch.int32), dev(tables, torch.int32), k_cache, v_cache, cos, sin,
+                    tokens, heads, kv_heads, head_dim, rotary_dim,
+                    {"adjacent": 0, "half_split": 1}[pairing], page_size, num_pages, status)
+    assert int(status.item()) == 0
+    q = qkv[:, :heads * head_dim].reshape(tokens, heads, head_dim)
+    k = qkv[:, heads * head_dim:(heads + kv_heads) * head_dim].reshape(tokens, kv_heads, head_dim)
+    v = qkv[:, (heads + kv_heads) * head_dim:].reshape(tokens, kv_heads, head_dim)
+    q_expected = rope_reference(q, positions, theta, rotary_dim, pairing)
+    k_expected = rope_reference(k, positions, theta, rotary_dim, pairing)
+    tol = dict(atol=2e-6, rtol=2e-6) if dtype == torch.float32 else dict(atol=2e-2, rtol=8e-3)
+    result = host(buffer)
+    assert_close(result[:, :heads * head_dim].reshape(q.shape), q_expected, "rotated queries", **tol)
+    np.testing.assert_array_equal(result[:, (heads + kv_heads) * head_dim:],
+                                  qkv[:, (heads + kv_heads) * head_dim:])
+    keys, values = host(k_cache), host(v_cache)
+    written = np.zeros((num_pages, page_size), dtype=bool)
+    for t in range(tokens):
+        page = tables[slots[token_request[t]], positions[t] // page_size]
+        slot = positions[t] % page_size
+        written[page, slot] = True
+        assert_close(keys[page, :, slot], k_expected[t], f"key of token {t}", **tol)
+        np.testing.assert_array_equal(values[page, :, slot], v[t])
+    # nothing else was touched
+    assert np.isnan(keys[~written]).all() and np.isnan(values[~written]).all()
+
+
+# ------------------------------------------------------------------- attention
+
+def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, new_tokens,
+                   window, split_keys, dominant=None):
+    """Build a paged cache holding ``contexts[r] + new_tokens[r]`` keys per request in shuffled
+    pages and the queries of the new tokens; return kernel output and plain reference."""
+    requests = len(contexts)
+    totals = [c + n for c, n in zip(contexts, new_tokens)]
+    pages_per = [-(-t // page_size) for t in totals]
+    num_pages = sum(pages_per) + 3
+    order = rng.permutation(num_pages)
+    max_pages = max(pages_per) + 1
+    tables = np.full((requests + 2, max_pages), -1, dtype=np.int32)
+    slots = rng.permutation(requests + 2)[:requests].astype(np.int32)
+    cursor = 0
+    keys = [rounded(rng.normal(size=(kv_heads, t, head_dim)), dtype) for t in totals]
+    values = [rounded(rng.normal(size=(kv_heads, t, head_dim)), dtype) for t in totals]
+    queries = [rounded(rng.normal(size=(heads, n, head_dim)), dtype) for n in new_tokens]
+    if dominant is not None:
+        # make one far key win: its direction equals the query's, scaled up
+        for r, key_position in dominant.items():
+            for head in range(heads):
+                kv = head // (heads // kv_heads)
+                direction = queries[r][head, -1] / np.linalg.norm(queries[r][head, -1])
+                keys[r][kv, key_position] = rounded(direction * 40.0, dtype)
+    k_cache = np.full((num_pages, kv_heads, page_size, head_dim), np.nan, dtype=np.float32)
+    v_cache = np.full_like(k_cache, np.nan)
+    for r in range(requests):
+        for p in range(pages_per[r]):
+            page = order[cursor]
+            cursor += 1
+            tables[slots[r], p] = page
+            lo, hi = p * page_size, min((p + 1) * page_size, totals[r])
+            k_cache[page, :, :hi - lo] = keys[r][:, lo:hi]
+            v_cache[page, :, :hi - lo] = values[r][:, lo:hi]
+    positions, token_request, q_rows = [], [], []
+    for r in range(requests):
+        for i in range(new_tokens[r]):
+            positions.append(contexts[r] + i)
+            token_request.append(r)
+            q_rows.append(queries[r][:, i].reshape(-1))
+    tokens = len(positions)
+    q = np.stack(q_rows)
+    scale = 1.0 / math.sqrt(head_dim)
+    longest = max(totals) if not window else min(max(totals), window)
+    max_splits = max(1, -(-longest // split_keys))
+    partial = None
+    if max_splits > 1:
+        partial = torch.empty(ops.attention_scratch_floats(tokens, heads, head_dim, max_splits),
+                              dtype=torch.float32, device=DEVICE)
+    out = torch.full((tokens, heads * head_dim), float("nan"), dtype=dtype, device=DEVICE)
+    status = status_word()
+    ops.paged_attention(dev(q, dtype), dev(k_cache, dtype), dev(v_cache, dtype),
+                        dev(positions, torch.int32), dev(token_request, torch.int32),
+                        dev(slots, torch.int32), dev(tables, torch.int32), out, partial, tokens,
+                        heads, kv_heads, head_dim, page_size, num_pages, window or 0, scale,
+                        split_keys, max_splits, status)
+    assert int(status.item()) == 0
+    expected = []
+    for r in range(requests):
+        context = plain.causal_attention(queries[r], keys[r], values[r], query_offset=contexts[r],
+                                         window=window or None)
+        expected.append(context.transpose(1, 0, 2).reshape(new_tokens[r], heads * head_dim))
+    return host(out), np.concatenate(expected), values, positions, token_request
+
+
+ATTENTION_SHAPES = [
+    # heads, kv_heads, head_dim, page_size
+    (4, 4, 16, 8), (5, 5, 24, 16), (6, 2, 64, 16), (5, 1, 100, 8), (8, 8, 128, 16), (2, 1, 256, 32),
+    (3, 3, 80, 4),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", ATTENTION_SHAPES)
+def test_paged_attention_mixed_batch(dtype, heads, kv_heads, head_dim, page_size):
+    rng = np.random.default_rng(7)
+    # a prompt from scratch, a continued portion, two single decode tokens (one exactly on a
+    # page edge), long enough for several key splits
+    contexts = [0, 37, 4 * page_size - 1, 150]
+    new_tokens = [45, 19, 1, 1]
+    out, expected, *_ = attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts,
+                                       new_tokens, window=None, split_keys=64)
+    tol = dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=8e-3)
+    assert_close(out, expected, "attention", **tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 16, 33])
+def test_paged_attention_window_edges(dtype, window):
+    rng = np.random.default_rng(8)
+    out, expected, *_ = attention_case(rng, dtype, 4, 2, 32, 8, [0, 50, 15], [40, 3, 1],
+                                       window=window, split_keys=16)
+    tol = dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=8e-3)
+    assert_close(out, expected, f"window {window}", **tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key_position", [0, 15, 16, 255, 256, 299])
+def test_one_far_key_stands_out(dtype, key_position):
+    """One key among 300 is scaled so that it takes all the weight: the output must be that
+    key's value, wherever it lies (first key, page edges, split edges, last key)."""
+    rng = np.random.default_rng(9)
+    out, expected, values, *_ = attention_case(rng, dtype, 4, 4, 32, 16, [299], [1], window=None,
+                                               split_keys=64, dominant={0: key_position})
+    tol = dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=8e-3)
+    assert_close(out, expected, "attention", **tol)
+    wanted = values[0][:, key_position].reshape(1, -1)
+    assert_close(out, wanted, "dominant key's value", atol=2e-2, rtol=1e-2)
+
+
+def test_attention_refuses_odd_head_sizes():
+    with pytest.raises(ops.KernelError, match="head_dim"):
+        q = torch.zeros((1, 2 * 130), dtype=torch.bfloat16, device=DEVICE)
+        cache = torch.zeros((2, 2, 8, 130), dtype=torch.bfloat16, device=DEVICE)
+        zeros = torch.zeros(4, dtype=torch.int32, device=DEVICE)
+        ops.paged_attention(q, cache, cache, zeros, zeros, zeros, zeros.view(1, 4), q.clone(), None,
+                            1, 2, 2, 130, 8, 2, 0, 1.0, 64, 1, status_word())
+
+
+# -------------------------------------------------------------------- sampling
+
+def test_greedy_takes_the_lowest_id_among_maxima_and_flags_nonfinite_rows():
+    rng = np.random.default_rng(10)
+    vocab = 1003
+    logits = rng.normal(size=(4, vocab)).astype(np.float32)
+    logits[0, [700, 30, 999]] = 9.0
+    logits[1, vocab - 1] = 50.0
+    logits[2, 5] = np.nan
+    logits[3, 0] = 11.0
+    tokens = torch.zeros(4, dtype=torch.int32, device=DEVICE)
+    status = status_word()
+    ops.argmax(dev(logits), tokens, status)
+    assert tokens.cpu().tolist() == [30, vocab - 1, -1, 0]
+    assert int(status.item()) & ops.FLAG_NONFINITE
+
+
+def test_temperature_sampling_follows_the_inverse_cumulative_distribution():
+    rng = np.random.default_rng(11)
+    vocab = 777
+    rows = 64
+    logits = (rng.normal(size=(rows, vocab)) * 2.0).astype(np.float32)
+    temperature = np.full(rows, 0.8, dtype=np.float32)
+    temperature[0] = 0.0                       # greedy row
+    uniform = rng.random(rows).astype(np.float32)
+    uniform[1], uniform[2] = 0.0, np.float32(0.999)
+    tokens = torch.zeros(rows, dtype=torch.int32, device=DEVICE)
+    ops.sample(dev(logits), dev(temperature), dev(uniform), tokens, status_word())
+    got = tokens.cpu().numpy()
+    assert got[0] == int(np.argmax(logits[0]))
+    for row in range(1, rows):
+        scaled = (logits[row].astype(np.float64) - logits[row].max()) / temperature[row]
+        weights = np.exp(scaled)
+        cumulative = np.cumsum(weights)
+        target = float(uniform[row]) * cumulative[-1]
+        want = int(np.searchsorted(cumulative, target, side="right"))
+        want = min(want, vocab - 1)
+        if got[row] != want:
+            # float32 sums may put a target that lies within rounding of a boundary on the
+            # other side of it: accept the neighbour only then
+            boundary = cumulative[min(got[row], want)]
+            assert abs(got[row] - want) == 1 and abs(target - boundary) < 1e-4 * cumulative[-1], \
+                f"row {row}: sampled {got[row]}, expected {want}"

@@ -1,0 +1,155 @@
+"""The engine's model, cache and step function against the plain implementation, in process.
+
+Every way of cutting the same requests into steps must give the plain implementation's
+logits at every position: whole, tail decoded one by one, portions of changing size, and
+mixed batches over a pool so small that pages are used again (free pages are filled with
+NaN, so reading a page that was given back shows at once).
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import traces
+from conftest import random_tokens
+from engine_harness import Harness, assert_close, tolerance
+from tiny_configs import PAGE_SIZE, tiny_config
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": (5, 17, 31, 77), "B": (1, 9, 40, 64, 100)}
+CASES = [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16")]
+
+
+def make_requests(name: str, extra: int = 0):
+    vocab = tiny_config(name).vocab_size
+    return {f"r{index}": random_tokens(vocab, length + extra, seed=1000 * (ord(name)) + index)
+            for index, length in enumerate(LENGTHS[name])}
+
+
+def replay(harness: Harness, steps, expected, dtype: str, what: str):
+    positions = {}
+    for step in steps:
+        rows = traces.labels(step, positions)
+        out = harness.run([(e["id"], e["tokens"], e["want"]) for e in step["entries"]])
+        for name in step["end"]:
+            harness.end(name)
+        if rows:
+            want = np.stack([expected[name][position] for name, position in rows])
+            assert_close(out, want, f"{what} step {step['step']} rows {rows[:4]}...",
+                         **tolerance(dtype))
+    harness.cache.check()
+    assert not harness.cache.live_requests()
+
+
+@pytest.fixture(scope="module")
+def expectations(plain_models):
+    cache = {}
+
+    def get(name: str, dtype: str, extra: int = 0):
+        key = (name, dtype, extra)
+        if key not in cache:
+            plain = plain_models(name, dtype)
+            cache[key] = {request: plain.logits(tokens)
+                          for request, tokens in make_requests(name, extra).items()}
+        return cache[key]
+    return get
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_requests(name, dtype, folders, expectations):
+    harness = Harness(folders(name, dtype), dtype, PAGE_SIZE[name], num_pages=64)
+    replay(harness, traces.whole(make_requests(name)), expectations(name, dtype), dtype,
+           f"whole {name} {dtype}")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_tail_decoded_one_by_one(name, dtype, folders, expectations):
+    harness = Harness(folders(name, dtype), dtype, PAGE_SIZE[name], num_pages=64)
+    replay(harness, traces.tail_decoded(make_requests(name, extra=20)),
+           expectations(name, dtype, 20), dtype, f"tail {name} {dtype}")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_portions_of_changing_size(name, dtype, folders, expectations):
+    harness = Harness(folders(name, dtype), dtype, PAGE_SIZE[name], num_pages=64)
+    replay(harness, traces.chunked(make_requests(name, extra=20)),
+           expectations(name, dtype, 20), dtype, f"portions {name} {dtype}")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_mixed_batches_with_page_reuse(name, dtype, folders, expectations):
+    requests = make_requests(name, extra=20)
+    # twice the same requests under new names, so that later ones run in recycled pages
+    doubled = dict(requests)
+    doubled.update({f"again_{key}": value for key, value in requests.items()})
+    expected = dict(expectations(name, dtype, 20))
+    expected.update({f"again_{key}": value for key, value in expectations(name, dtype, 20).items()})
+    steps = traces.mixed(doubled, max_live=4, seed=7)
+    page = PAGE_SIZE[name]
+    need = traces.live_token_need(steps, round_to=page)
+    harness = Harness(folders(name, dtype), dtype, page, num_pages=need // page)
+    replay(harness, steps, expected, dtype, f"mixed {name} {dtype}")
+    group = harness.cache.groups[0]
+    assert group.pool.reuse_count > 0, "the pool was large enough that no page was used again"
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16")])
+def test_long_decoding_to_the_last_position(name, dtype, folders, plain_models):
+    config = tiny_config(name)
+    tokens = random_tokens(config.vocab_size, config.max_position_embeddings, seed=5)
+    expected = plain_models(name, dtype).logits(tokens)
+    harness = Harness(folders(name, dtype), dtype, PAGE_SIZE[name], num_pages=32, split_keys=32)
+    out = harness.run([("long", tokens[:3], [0, 1, 2])])
+    assert_close(out, expected[:3], "prompt", **tolerance(dtype))
+    for position in range(3, len(tokens)):
+        out = harness.run([("long", [tokens[position]], [0])])
+        assert_close(out, expected[position:position + 1], f"decode position {position}",
+                     **tolerance(dtype))
+    harness.end("long")
+    harness.cache.check()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_first_tokens_of_a_sequence(name, dtype, folders, plain_models):
+    vocab = tiny_config(name).vocab_size
+    plain = plain_models(name, dtype)
+    harness = Harness(folders(name, dtype), dtype, PAGE_SIZE[name], num_pages=16)
+    for length in (1, 2, 3):
+        tokens = random_tokens(vocab, length, seed=length)
+        assert_close(harness.whole(f"w{length}", tokens), plain.logits(tokens),
+                     f"whole prompt of {length}", **tolerance(dtype))
+    tokens = random_tokens(vocab, 4, seed=9)
+    expected = plain.logits(tokens)
+    for position, token in enumerate(tokens):
+        out = harness.run([("one", [token], [0])])
+        assert_close(out, expected[position:position + 1], f"token {position} alone",
+                     **tolerance(dtype))
+    harness.end("one")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_key_among_hundreds(dtype, folders, plain_models):
+    """Sharp attention (query/key projections scaled up) over 250 positions of tiny B: the
+    decoded tail must still see every far key, across many pages and several key splits."""
+    config = tiny_config("B")
+    tokens = random_tokens(config.vocab_size, 250, seed=77)
+    expected = plain_models("B", dtype).logits(tokens)
+    harness = Harness(folders("B", dtype), dtype, PAGE_SIZE["B"], num_pages=20, split_keys=64)
+    out = harness.run([("far", tokens[:200], range(200))])
+    assert_close(out, expected[:200], "prompt of 200", **tolerance(dtype))
+    for position in range(200, 250):
+        out = harness.run([("far", [tokens[position]], [0])])
+        assert_close(out, expected[position:position + 1], f"decode position {position}",
+                     **tolerance(dtype))
+    harness.end("far")
+
+
+def test_wanting_nothing_returns_nothing_and_still_fills_the_cache(folders, plain_models):
+    tokens = random_tokens(tiny_config("A").vocab_size, 20, seed=3)
+    expected = plain_models("A", "float32").logits(tokens)
+    harness = Harness(folders("A", "float32"), "float32", PAGE_SIZE["A"], num_pages=16)
+    assert harness.run([("q", tokens[:19], [])]) is None
+    out = harness.run([("q", tokens[19:], [0])])
+    assert_close(out, expected[19:], "after a silent prompt", **tolerance("float32"))
+    harness.end("q")

@@ -25,11 +25,17 @@ def tiny_config(name: str) -> LlamaConfig:
     return LlamaConfig(**{"A": TINY_A, "B": TINY_B}[name])
 
 
+# Attention of a tiny N(0, 0.02) model is almost uniform, which would hide a key that is
+# missing or misplaced.  The sharp variant multiplies the query and key projections so that
+# scores have a spread of about one and single keys matter.
+SHARP_GAINS = {"q_proj": 8.0, "k_proj": 8.0}
+
+
 def make_folder(directory: str, name: str, storage_dtype: str = "float32",
-                scale_std: float = 0.1, std: float = 0.02) -> str:
+                scale_std: float = 0.1, std: float = 0.02, sharp: bool = False) -> str:
     """Write the model folder of tiny configuration ``name`` under ``directory``."""
-    path = os.path.join(directory, f"tiny_{name}_{storage_dtype}")
+    path = os.path.join(directory, f"tiny_{name}_{storage_dtype}" + ("_sharp" if sharp else ""))
     if not os.path.exists(os.path.join(path, "model.safetensors")):
         write_random_model(path, tiny_config(name), SEED[name], std=std, scale_std=scale_std,
-                           storage_dtype=storage_dtype)
+                           storage_dtype=storage_dtype, gains=SHARP_GAINS if sharp else None)
     return path
