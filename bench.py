@@ -1,0 +1,302 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Llama-2-7B shape, bfloat16, one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at the default batch of 8
+(512-token prompts, decoding from there), timed on the device with CUDA events around K
+replays of the captured decode step (forward, sampling and feeding the sampled token back,
+all on the device).  ``e2e`` is the same quantity through the Python entry point
+(``Engine.submit`` / ``Engine.run_iteration``): every step copies that step's inputs from
+pinned host memory to the device and reads the sampled tokens back.  ``prefill`` is one
+2,048-token prompt in one step.  ``roofline`` relates the decode step to the HBM bandwidth:
+the bytes it has to read (every weight once, the cache of the live requests) over its time.
+``points`` holds decoding at batch 1 and 64.
+
+Weights are random, N(0, 0.02) from a fixed seed, made on the device; prompts are seeded
+uniform token ids.  Every step streams more weight bytes than the L2 cache holds, so no L2
+flush is needed between timed iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# Llama-2-7B shape (the benchmark configuration)
+SHAPE = dict(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+             num_attention_heads=32, num_key_value_heads=32, head_dim=128,
+             max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0)
+PROMPT_LEN = 512
+PAGE_SIZE = 16
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path, "r", encoding="utf-8") as source:
+            data = json.load(source)
+        peaks = dict(FALLBACK_PEAKS)
+        for key in peaks:
+            if isinstance(data.get(key), (int, float)):
+                peaks[key] = float(data[key])
+        peaks["source"] = "measured"
+        return peaks
+    except (OSError, ValueError):
+        return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, path: str) -> None:
+        self.path = path
+        self.process = None
+
+    def start(self) -> None:
+        try:
+            self.handle = open(self.path, "w")
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=self.handle, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.process = None
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        self.handle.close()
+        clocks, maxima, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        with open(self.path, "r") as source:
+            for line in source:
+                fields = [f.strip() for f in line.split(",")]
+                if len(fields) < 8:
+                    continue
+                try:
+                    clocks.append(float(fields[0]))
+                    maxima.append(float(fields[1]))
+                except ValueError:
+                    continue
+                for name, value in zip(names, fields[4:8]):
+                    if value.lower().startswith("active"):
+                        reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+                "sm_max_mhz": max(maxima) if maxima else None,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def reference_arm() -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "pip install of the reference fails: it is a C++/CMake project with no "
+                       "setup.py or pyproject.toml; its CUDA path has never run on a GPU and its "
+                       "validated path is single-threaded FP32 on the CPU, which cannot run the "
+                       "Llama-2-7B benchmark configuration in minutes"}))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=192)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"],
+                        help="run fewer layers of the same sizes (recorded in config)")
+    parser.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    options = parser.parse_args()
+    if options.impl == "reference":
+        return reference_arm()
+    if options.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {options.gpus} is not supported")
+        return 2
+    if options.warmup < 3:
+        options.warmup = 3
+
+    import numpy as np
+    import torch
+
+    from helix_runtime_b200 import Engine, EngineConfig, LlamaConfig, random_model
+    from helix_runtime_b200.cache.manager import CacheManager
+    from helix_runtime_b200.engine.graphs import DecodeGraphs
+    from helix_runtime_b200.engine.step import StepEntry, StepFunction
+    from helix_runtime_b200.ops import library as ops
+    from helix_runtime_b200.sampling import Sampler
+
+    peaks = load_peaks()
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    ops.lib()
+    shape = dict(SHAPE, num_hidden_layers=options.layers)
+    config = LlamaConfig(**shape)
+    model = random_model(config, seed=0, dtype="bfloat16", device=device)
+    rng = np.random.default_rng(0)
+    out_dir = os.path.join(ROOT, "gpurun_out")
+    os.makedirs(out_dir, exist_ok=True)
+    steps, warmup = options.steps, options.warmup
+
+    def fresh(batch: int, total_len: int, capacity: int):
+        kv, state = model.cache_needs()
+        pages = batch * -(-total_len // PAGE_SIZE) + 8
+        cache = CacheManager(kv, state, PAGE_SIZE, pages, batch, config.max_position_embeddings,
+                             model.dtype, device)
+        step = StepFunction(model, cache, max_tokens=capacity, max_requests=batch)
+        sampler = Sampler(device, max(batch, 1))
+        return cache, step, sampler
+
+    def timed(fn, count: int) -> float:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(count):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop)
+
+    def decode_device_loop(batch: int, n_steps: int, n_warmup: int):
+        """Device-timed decoding: returns (tokens/s, ms/step, kernels/step, mean context)."""
+        final = PROMPT_LEN + n_warmup + n_steps + 2
+        cache, step, sampler = fresh(batch, final, max(PREFILL_TOKENS, batch))
+        prompts = [[int(t) for t in rng.integers(0, config.vocab_size, PROMPT_LEN)]
+                   for _ in range(batch)]
+        first = []
+        per_step = max(1, PREFILL_TOKENS // PROMPT_LEN)
+        for begin in range(0, batch, per_step):
+            entries = []
+            for index in range(begin, min(begin + per_step, batch)):
+                cache.admit(index)
+                entries.append(StepEntry(index, prompts[index], [PROMPT_LEN - 1]))
+            logits = step.run(entries)
+            tokens = sampler.launch(logits, True, step.status)
+            first.extend(sampler.to_host(tokens))
+        # the decode step, replayed on the device: pages for every future position are reserved
+        entries = [StepEntry(index, [first[index]], [0]) for index in range(batch)]
+        ctx, want_rows, n_want, _ = step.prepare(entries, context_hint=final)
+        for index in range(batch):
+            cache.extend(index, final)
+        cache.sync_tables()
+        graphs = DecodeGraphs(step, sampler)
+        graphs.run(ctx, want_rows, n_want, True, advance=True)          # eager, sizes workspaces
+        graph = graphs.capture_only(ctx, want_rows, n_want, True, advance=True)
+        kernels = graphs.kernels_per_graph[graphs.key_for(ctx, n_want, True) + (True,)]
+        for _ in range(n_warmup - 1):
+            graph.replay()
+        elapsed = timed(graph.replay, n_steps)
+        step.raise_on_status()
+        mean_context = PROMPT_LEN + n_warmup + (n_steps + 1) / 2.0
+        return batch * n_steps / (elapsed / 1e3), elapsed / n_steps, kernels, mean_context
+
+    # ------------------------------------------------------------------ decode, batch B
+    sampler_clock = ClockSampler(os.path.join(out_dir, "bench_clocks.csv"))
+    sampler_clock.start()
+    value, ms_per_step, kernels_per_step, mean_context = decode_device_loop(
+        options.batch, steps, warmup)
+    clocks = sampler_clock.stop()
+    weight_bytes = model.weight_bytes_per_step()
+    kv_bytes_per_token = sum(2 * need.kv_heads * need.head_dim * 2
+                             for need in model.cache_needs()[0].values())
+    step_bytes = weight_bytes + options.batch * mean_context * kv_bytes_per_token
+    achieved_gbs = step_bytes / (ms_per_step / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peaks["hbm_gbs"],
+                "unit": "GB/s", "frac": round(achieved_gbs / peaks["hbm_gbs"], 4),
+                "peak_source": peaks["source"]}
+
+    # ------------------------------------------------------------------ prefill, 2,048 tokens
+    cache, step, sampler = fresh(1, PREFILL_TOKENS, PREFILL_TOKENS)
+    prompt = [int(t) for t in rng.integers(0, config.vocab_size, PREFILL_TOKENS)]
+
+    def prefill_once():
+        cache.admit("p")
+        step.run([StepEntry("p", prompt, [PREFILL_TOKENS - 1])], check_status=False)
+        cache.release("p")
+
+    for _ in range(3):
+        prefill_once()
+    reps = 5
+    prefill_ms = timed(prefill_once, reps) / reps
+    step.raise_on_status()
+    h, i, layers, t = config.hidden_size, config.intermediate_size, options.layers, PREFILL_TOKENS
+    prefill_flops = 2.0 * t * layers * (4 * h * h + 3 * h * i) + 2.0 * h * config.vocab_size \
+        + 2.0 * layers * t * (t + 1) * h
+    prefill = {"value": round(t / (prefill_ms / 1e3), 1), "tokens": t, "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+    del cache, step, sampler
+
+    # ------------------------------------------------------------------ end to end
+    engine = Engine(model, EngineConfig(page_size=PAGE_SIZE, max_running_requests=options.batch,
+                                        max_tokens_per_iteration=PREFILL_TOKENS,
+                                        num_pages=options.batch * -(-(PROMPT_LEN + warmup + steps + 8)
+                                                                    // PAGE_SIZE) + 8))
+    for _ in range(options.batch):
+        engine.submit([int(t) for t in rng.integers(0, config.vocab_size, PROMPT_LEN)],
+                      max_new_tokens=warmup + steps + 4)
+    while any(engine.request(r).state.value != "decoding" for r in range(options.batch)):
+        engine.run_iteration()
+    for _ in range(warmup):
+        engine.run_iteration()
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    decoded = 0
+    for _ in range(steps):
+        decoded += engine.run_iteration().sampled
+    torch.cuda.synchronize()
+    e2e_seconds = time.perf_counter() - begin
+    h2d = engine.step_function._host.numel() * 4
+    e2e = {"value": round(decoded / e2e_seconds, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": options.batch * 4 + 4,
+           "ms_per_step": round(e2e_seconds / steps * 1e3, 4),
+           "graph_replays": engine.graphs.replays if engine.graphs else 0}
+    del engine
+
+    # ------------------------------------------------------------------ batch 1 and 64
+    points = {}
+    if not options.no_points:
+        for batch in (1, 64):
+            tokens_per_s, _, _, _ = decode_device_loop(batch, min(steps, 96), warmup)
+            points[f"decode_b{batch}"] = round(tokens_per_s, 1)
+
+    line = {
+        "metric": "decode tokens/s (Llama-2-7B shape, bf16, batch 8)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random N(0,0.02) weights from seed 0, uniform random token ids",
+        "config": {"model": "llama-2-7b-shape", "layers": options.layers,
+                   "layers_full": SHAPE["num_hidden_layers"], "hidden": h, "heads": 32,
+                   "kv_heads": 32, "head_dim": 128, "intermediate": i, "vocab": config.vocab_size,
+                   "global_batch": options.batch, "seq_len": PROMPT_LEN, "gen_len": steps,
+                   "context": config.max_position_embeddings, "page_size": PAGE_SIZE,
+                   "parallelism": "single-gpu",
+                   "l2": "each step streams >126MB of weights; no flush needed"},
+        "e2e": e2e, "gpu_launches": int(kernels_per_step * steps),
+        "kernels_per_step": int(kernels_per_step),
+        "prefill": prefill, "roofline": roofline, "points": points, "clocks": clocks,
+        "step_bytes": int(step_bytes), "impl": "ours",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

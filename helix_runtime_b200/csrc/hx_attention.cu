@@ -296,6 +296,7 @@ int dispatch(const AttentionArgs& a, cudaStream_t stream) {
     const long long pairs = static_cast<long long>(a.tokens) * a.heads;
     const int blocks = static_cast<int>((pairs + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
     attention_merge_kernel<T><<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>(a);
+    hx_count_launches(1);
   }
   return HX_OK;
 }

@@ -32,6 +32,8 @@ enum HxDeviceFlag : int {
 };
 
 void hx_set_error(const char* format, ...);
+// Every entry point counts the kernels it launches (read with hx_launch_count()).
+void hx_count_launches(int kernels);
 
 #define HX_REQUIRE(cond, ...)            \
   do {                                   \
@@ -43,6 +45,7 @@ void hx_set_error(const char* format, ...);
 
 #define HX_CHECK_LAUNCH(name)                                              \
   do {                                                                     \
+    hx_count_launches(1);                                                  \
     cudaError_t hx_err__ = cudaGetLastError();                             \
     if (hx_err__ != cudaSuccess) {                                         \
       hx_set_error("%s: launch failed: %s", name, cudaGetErrorString(hx_err__)); \

@@ -4,6 +4,7 @@
 // it, RMSNorm reads it and writes the compute dtype for the next matrix product.
 #include "hx_common.cuh"
 
+#include <atomic>
 #include <cstdarg>
 #include <cstring>
 
@@ -19,6 +20,14 @@ void hx_set_error(const char* format, ...) {
 }
 
 HX_API const char* hx_last_error() { return g_hx_error; }
+
+static std::atomic<long long> g_hx_launches{0};
+
+void hx_count_launches(int kernels) { g_hx_launches.fetch_add(kernels, std::memory_order_relaxed); }
+
+// Kernels launched by this library since it was loaded (a launch recorded into a CUDA graph
+// counts once, when it is captured).
+HX_API long long hx_launch_count() { return g_hx_launches.load(std::memory_order_relaxed); }
 
 HX_API int hx_abi_version() { return 3; }
 
@@ -106,40 +115,38 @@ HX_API int hx_rmsnorm(const float* x, const float* weight, void* y, int out_dtyp
 
 // ---------------------------------------------------------------------- SwiGLU
 
-// act[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; sigmoid and both products in
-// float32 (src/kernels/cuda/transformer.cu:68-83).
-template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ act, int tokens,
+// act[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate and up arrive as float32
+// accumulators, sigmoid and both products are float32, one rounding into the compute dtype
+// (src/kernels/cuda/transformer.cu:68-83).  This is the path of the CUDA-core product;
+// the tensor-core product applies the same formula in its epilogue.
+template <typename TOut>
+__global__ void swiglu_kernel(const float* __restrict__ gate_up, TOut* __restrict__ act, int tokens,
                               int intermediate, int ld_in) {
   const size_t total = static_cast<size_t>(tokens) * intermediate;
   for (size_t index = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; index < total;
        index += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const size_t t = index / intermediate;
     const int i = static_cast<int>(index - t * intermediate);
-    const T* row = gate_up + t * ld_in;
-    const float g = hx_to_float<T>(row[i]);
-    const float u = hx_to_float<T>(row[intermediate + i]);
-    act[index] = hx_from_float<T>(hx_silu(g) * u);
+    const float* row = gate_up + t * ld_in;
+    act[index] = hx_from_float<TOut>(hx_silu(row[i]) * row[intermediate + i]);
   }
 }
 
-HX_API int hx_swiglu(const void* gate_up, void* act, int dtype, int tokens, int intermediate,
+HX_API int hx_swiglu(const float* gate_up, void* act, int out_dtype, int tokens, int intermediate,
                      int ld_in, cudaStream_t stream) {
   HX_REQUIRE(tokens >= 0 && intermediate > 0 && ld_in >= 2 * intermediate, "hx_swiglu: bad sizes");
   if (tokens == 0) return HX_OK;
   const size_t total = static_cast<size_t>(tokens) * intermediate;
   const int threads = 256;
   const int blocks = static_cast<int>(total / threads + 1 < 148 * 16 ? total / threads + 1 : 148 * 16);
-  if (dtype == HX_F32) {
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(gate_up),
-                                                         static_cast<float*>(act), tokens,
+  if (out_dtype == HX_F32) {
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>(gate_up, static_cast<float*>(act), tokens,
                                                          intermediate, ld_in);
-  } else if (dtype == HX_BF16) {
+  } else if (out_dtype == HX_BF16) {
     swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(act), tokens,
-        intermediate, ld_in);
+        gate_up, static_cast<__nv_bfloat16*>(act), tokens, intermediate, ld_in);
   } else {
-    HX_REQUIRE(false, "hx_swiglu: unknown dtype %d", dtype);
+    HX_REQUIRE(false, "hx_swiglu: unknown dtype %d", out_dtype);
   }
   HX_CHECK_LAUNCH("hx_swiglu");
   return HX_OK;
@@ -217,9 +224,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
     float a = hx_to_float<T>(vec[i0]);
     float b = hx_to_float<T>(vec[i1]);
     if (rotate) {
-      const int f = pairing == 0 ? pair : pair;
-      const float c = cos_row[f];
-      const float s = sin_row[f];
+      const float c = cos_row[pair];
+      const float s = sin_row[pair];
       const float ra = a * c - b * s;
       const float rb = a * s + b * c;
       a = ra;
@@ -286,5 +292,28 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
     HX_REQUIRE(false, "hx_rope_append: unknown dtype %d", dtype);
   }
   HX_CHECK_LAUNCH("hx_rope_append");
+  return HX_OK;
+}
+
+// ------------------------------------------------------- decode loop on the device
+
+// After a step that sampled one token per request: feed each sampled token back as the
+// next step's input and move every position on by one, without a round trip to the host.
+__global__ void advance_decode_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
+                                      const int* __restrict__ sampled, int count) {
+  const int index = blockIdx.x * blockDim.x + threadIdx.x;
+  if (index < count) {
+    token_ids[index] = sampled[index];
+    positions[index] += 1;
+  }
+}
+
+HX_API int hx_advance_decode(int* token_ids, int* positions, const int* sampled, int count,
+                             cudaStream_t stream) {
+  HX_REQUIRE(count >= 0, "hx_advance_decode: bad count");
+  if (count == 0) return HX_OK;
+  advance_decode_kernel<<<(count + 127) / 128, 128, 0, stream>>>(token_ids, positions, sampled,
+                                                                 count);
+  HX_CHECK_LAUNCH("hx_advance_decode");
   return HX_OK;
 }

@@ -24,6 +24,7 @@ from ..weights.random_init import random_tensors, write_model_folder
 from ..weights.safetensors_io import Checkpoint
 from .scheduler import (FifoScheduler, Request, RequestState, SchedulerConfig, StopReason,
                         WorkCompletion)
+from .graphs import DecodeGraphs
 from .step import StepEntry, StepError, StepFunction
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -110,6 +111,7 @@ class EngineConfig:
     max_prefill_chunk: Optional[int] = None
     attention_split_keys: int = 256
     poison_free_pages: bool = False           # debugging: fill free pages with NaN
+    cuda_graphs: bool = True                  # replay decode-only steps as CUDA graphs
 
 
 @dataclasses.dataclass
@@ -150,6 +152,7 @@ class Engine:
             SchedulerConfig(config.max_tokens_per_iteration, config.max_running_requests,
                             config.max_prefill_chunk), config.page_size)
         self.sampler = Sampler(device, config.max_running_requests)
+        self.graphs = DecodeGraphs(self.step_function, self.sampler) if config.cuda_graphs else None
         self._cached_at_finish: Dict[int, int] = {}
         self._release_later: List[int] = []
 
@@ -240,18 +243,31 @@ class Engine:
         result.scheduled_tokens = batch.scheduled_tokens
 
         completions: List[WorkCompletion] = []
+        step = self.step_function
         try:
-            logits = self.step_function.run(entries, check_status=False)
-            sampled: List[int] = []
-            if logits is not None:
-                tokens = self.sampler.sample(logits, temperatures, uniforms,
-                                             self.step_function.status)
-                sampled = self.sampler.to_host(tokens)
-            flags = int(self.step_function.status.item())
-            if flags & ~8:       # anything but per-row non-finite logits condemns the whole step
-                self.step_function.raise_on_status()
-            if flags:
-                self.step_function.status.zero_()
+            ctx, want_rows, n_want, new_lengths = step.prepare(entries)
+            try:
+                sampled: List[int] = []
+                decode_only = n_want == ctx.n_tokens == len(entries)
+                if n_want:
+                    greedy = self.sampler.prepare(temperatures, uniforms)
+                    if self.graphs is not None and decode_only:
+                        tokens = self.graphs.run(ctx, want_rows, n_want, greedy)
+                    else:
+                        logits = self.model.forward(ctx, self.cache, want_rows, n_want)
+                        tokens = self.sampler.launch(logits, greedy, step.status)
+                    sampled = self.sampler.to_host(tokens)
+                else:
+                    self.model.forward(ctx, self.cache, want_rows, 0)
+                flags = int(step.status.item())
+                if flags & ~8:   # anything but per-row non-finite logits condemns the whole step
+                    step.raise_on_status()
+                if flags:
+                    step.status.zero_()
+            except Exception:
+                step.fail(entries)
+                raise
+            step.finish(entries, new_lengths, ctx)
             cursor = 0
             for work, entry in zip(batch.work, entries):
                 token = None

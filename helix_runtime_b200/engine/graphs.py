@@ -1,0 +1,90 @@
+"""CUDA graphs of decode steps: one launch for the whole forward pass and the sampling.
+
+A decode step of a given batch size launches the same few hundred small kernels every time
+with the same scalar arguments; only the contents of the step's device buffers change
+(token ids, positions, block tables).  Such a step is recorded once into a CUDA graph and
+replayed, which removes the launch overhead that otherwise dominates small batches.  The
+reference synchronises after every layer (src/model/cuda_llama.cpp:395); here nothing
+synchronises inside a step.
+
+A graph is keyed by everything that is baked into its launches: the number of tokens, the
+number of wanted rows, the number of key splits attention was launched for, and whether
+sampling is greedy.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..parts.base import StepContext
+
+
+class DecodeGraphs:
+    def __init__(self, step_function, sampler, max_graphs: int = 64) -> None:
+        self.step_function = step_function
+        self.sampler = sampler
+        self.max_graphs = max_graphs
+        self._graphs: Dict[Tuple[int, int, int, bool], torch.cuda.CUDAGraph] = {}
+        self._stream = torch.cuda.Stream(device=step_function.device)
+        self.replays = 0
+        self.captures = 0
+        self.kernels_per_graph: Dict[Tuple[int, int, int, bool], int] = {}
+
+    def key_for(self, ctx: StepContext, n_want: int, greedy: bool) -> Tuple[int, int, int, bool]:
+        splits = -(-ctx.max_context_len // ctx.attention_split_keys)
+        return (ctx.n_tokens, n_want, splits, greedy)
+
+    def run(self, ctx: StepContext, want_rows: torch.Tensor, n_want: int, greedy: bool,
+            advance: bool = False) -> torch.Tensor:
+        """Run the step (forward, then sampling of the wanted rows) and return the device
+        tensor of sampled ids.  The first time a key is seen the step runs eagerly and is
+        recorded afterwards; from then on it is replayed."""
+        from ..ops import library as ops
+        key = self.key_for(ctx, n_want, greedy) + ((advance,) if advance else ())
+        graph = self._graphs.get(key)
+        if graph is not None:
+            graph.replay()
+            self.replays += 1
+            return self.sampler.tokens[:n_want]
+
+        def body() -> torch.Tensor:
+            logits = self.step_function.model.forward(ctx, self.step_function.cache, want_rows,
+                                                      n_want)
+            tokens = self.sampler.launch(logits, greedy, ctx.status)
+            if advance:
+                ops.advance_decode(ctx.token_ids, ctx.positions, tokens, ctx.n_tokens)
+            return tokens
+
+        tokens = body()                      # eager: gives this step's result, sizes workspaces
+        if len(self._graphs) < self.max_graphs and not advance:
+            self._capture(key, body)
+        return tokens
+
+    def capture_only(self, ctx: StepContext, want_rows: torch.Tensor, n_want: int, greedy: bool,
+                     advance: bool) -> torch.cuda.CUDAGraph:
+        """Record the step without using its result (the caller has run it eagerly before, so
+        that every workspace buffer exists)."""
+        from ..ops import library as ops
+
+        def body() -> None:
+            logits = self.step_function.model.forward(ctx, self.step_function.cache, want_rows,
+                                                      n_want)
+            tokens = self.sampler.launch(logits, greedy, ctx.status)
+            if advance:
+                ops.advance_decode(ctx.token_ids, ctx.positions, tokens, ctx.n_tokens)
+
+        key = self.key_for(ctx, n_want, greedy) + (advance,)
+        return self._capture(key, body)
+
+    def _capture(self, key, body) -> torch.cuda.CUDAGraph:
+        from ..ops import library as ops
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.current_stream().synchronize()
+        before = ops.launch_count()
+        with torch.cuda.graph(graph, stream=self._stream):
+            body()
+        self.kernels_per_graph[key] = ops.launch_count() - before
+        self._graphs[key] = graph
+        self.captures += 1
+        return graph

@@ -73,9 +73,11 @@ class StepFunction:
 
     # --------------------------------------------------------------------- run
 
-    def prepare(self, entries: Sequence[StepEntry]):
+    def prepare(self, entries: Sequence[StepEntry], context_hint: int = 0):
         """Validate, reserve pages, fill and upload the batch description.
-        Returns ``(context, want_rows_device, n_want, new_lengths)``."""
+        Returns ``(context, want_rows_device, n_want, new_lengths)``.  ``context_hint`` raises
+        the context length that launches are sized for (a caller that will replay the step
+        while the requests grow passes the length they will reach)."""
         if not entries:
             raise StepError("a step needs at least one entry")
         if len(entries) > self.max_requests:
@@ -158,7 +160,8 @@ class StepFunction:
             request_slot=self._view("request_slot", True),
             request_start=self._view("request_start", True),
             request_context=self._view("request_context", True),
-            status=self.status, max_query_len=max_query, max_context_len=max_context,
+            status=self.status, max_query_len=max_query,
+            max_context_len=max(max_context, context_hint),
             attention_split_keys=self.attention_split_keys,
             host_request_slots=[int(v) for v in request_slot[:len(entries)]],
             host_request_starts=[int(v) for v in request_start[:len(entries) + 1]],
@@ -175,15 +178,25 @@ class StepFunction:
             if check_status:
                 self.raise_on_status()
         except Exception:
-            for entry in entries:
-                self.cache.rollback(entry.request)
+            self.fail(entries)
             raise
+        self.finish(entries, new_lengths, ctx)
+        return logits
+
+    def finish(self, entries: Sequence[StepEntry], new_lengths: Sequence[int],
+               ctx: StepContext) -> None:
+        """The step succeeded: publish the new lengths."""
         for entry, length in zip(entries, new_lengths):
             self.cache.commit(entry.request, length)
         self.last_context = ctx
         self.steps_run += 1
         self.tokens_run += ctx.n_tokens
-        return logits
+
+    def fail(self, entries: Sequence[StepEntry]) -> None:
+        """The step failed: give back what was reserved for it; no length moves."""
+        for entry in entries:
+            if self.cache.has(entry.request):
+                self.cache.rollback(entry.request)
 
     def raise_on_status(self) -> None:
         """Read the device status word (synchronises) and raise if a kernel flagged a fault."""

@@ -65,6 +65,10 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_paged_attention_scratch_floats.argtypes = [_c_int] * 4
     library.hx_argmax.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]
     library.hx_sample.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr]
+    library.hx_launch_count.restype = ctypes.c_longlong
+    library.hx_launch_count.argtypes = []
+    library.hx_advance_decode.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]
+    library.hx_advance_decode.restype = _c_int
     for name in ("hx_embed", "hx_rmsnorm", "hx_swiglu", "hx_rope_append", "hx_gemm_simt",
                  "hx_gemm_tc", "hx_gemm_tc_supports", "hx_gemm_tc_token_tile",
                  "hx_paged_attention", "hx_argmax", "hx_sample"):
@@ -148,9 +152,10 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
 
 
 def swiglu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
-    """act[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    """act[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up float32, act compute dtype."""
     tokens, intermediate = act.shape
-    assert gate_up.dtype == act.dtype and gate_up.stride(-1) == 1 and act.is_contiguous()
+    _need(gate_up, torch.float32, "gate_up")
+    assert act.is_contiguous()
     _check(lib().hx_swiglu(gate_up.data_ptr(), act.data_ptr(), dtype_code(act.dtype), tokens,
                            intermediate, gate_up.stride(0), _stream()))
 
@@ -231,3 +236,15 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     rows, vocab = logits.shape
     _check(lib().hx_sample(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
                            uniform.data_ptr(), tokens_out.data_ptr(), _ptr(status), _stream()))
+
+
+def advance_decode(token_ids: torch.Tensor, positions: torch.Tensor, sampled: torch.Tensor,
+                   count: int) -> None:
+    """token_ids[:count] = sampled[:count]; positions[:count] += 1 (the device-side decode loop)."""
+    _check(lib().hx_advance_decode(token_ids.data_ptr(), positions.data_ptr(), sampled.data_ptr(),
+                                   count, _stream()))
+
+
+def launch_count() -> int:
+    """Kernels this library has launched (or recorded into a graph) since it was loaded."""
+    return int(lib().hx_launch_count())

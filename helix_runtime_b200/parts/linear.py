@@ -49,8 +49,9 @@ def project_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, intermediate: int, 
     """``act[:tokens] = silu(x @ gate.T) * (x @ up.T)`` with ``w_gate_up = [gate; up]``.
 
     On the tensor cores the activation is the product's epilogue; otherwise the fused
-    product is stored (``gate_up_scratch()`` returns the ``[rows, 2I]`` buffer) and a
-    second kernel applies SwiGLU."""
+    product is stored as float32 (``gate_up_scratch()`` returns the ``[rows, 2I]`` float32
+    buffer) and a second kernel applies SwiGLU, so both paths round once, after the
+    activation."""
     if tokens == 0:
         return
     if uses_tensor_cores(x, w_gate_up, tokens):
@@ -58,5 +59,5 @@ def project_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, intermediate: int, 
                     up_row_offset=intermediate)
     else:
         scratch = gate_up_scratch()
-        ops.gemm_simt(x, w_gate_up, scratch, tokens, ops.EPI_STORE)
+        ops.gemm_simt(x, w_gate_up, scratch, tokens, ops.EPI_STORE_F32)
         ops.swiglu(scratch[:tokens], act[:tokens])

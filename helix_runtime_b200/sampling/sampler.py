@@ -44,22 +44,36 @@ class Sampler:
         self.tokens = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self._host_tokens = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
 
-    def sample(self, logits: torch.Tensor, temperatures: Sequence[float],
-               uniforms: Sequence[float], status: Optional[torch.Tensor]) -> torch.Tensor:
-        """Select one token per row; returns the device tensor of ids (-1: non-finite row)."""
-        rows = logits.shape[0]
+    def prepare(self, temperatures: Sequence[float], uniforms: Sequence[float]) -> bool:
+        """Upload the rows' temperatures and uniform numbers; return True when every row is
+        greedy (then nothing is uploaded and the arg-max kernel is enough)."""
+        rows = len(temperatures)
         if rows > self.max_rows:
             raise ValueError(f"{rows} rows to sample, at most {self.max_rows}")
-        out = self.tokens[:rows]
         if all(t <= 0.0 for t in temperatures):
-            ops.argmax(logits, out, status)
-            return out
+            return True
         params = self._host_params.numpy()
         params[0, :rows] = np.asarray(temperatures, dtype=np.float32)
         params[1, :rows] = np.asarray(uniforms, dtype=np.float32)
         self._device_params.copy_(self._host_params, non_blocking=True)
-        ops.sample(logits, self._device_params[0, :rows], self._device_params[1, :rows], out, status)
+        return False
+
+    def launch(self, logits: torch.Tensor, greedy: bool,
+               status: Optional[torch.Tensor]) -> torch.Tensor:
+        """Select one token per row of ``logits``; returns the device tensor of ids
+        (-1: the row held a non-finite logit)."""
+        rows = logits.shape[0]
+        out = self.tokens[:rows]
+        if greedy:
+            ops.argmax(logits, out, status)
+        else:
+            ops.sample(logits, self._device_params[0, :rows], self._device_params[1, :rows], out,
+                       status)
         return out
+
+    def sample(self, logits: torch.Tensor, temperatures: Sequence[float],
+               uniforms: Sequence[float], status: Optional[torch.Tensor]) -> torch.Tensor:
+        return self.launch(logits, self.prepare(temperatures, uniforms), status)
 
     def to_host(self, tokens: torch.Tensor) -> List[int]:
         rows = tokens.shape[0]

@@ -47,14 +47,16 @@ def folders(model_root):
 
 @pytest.fixture(scope="session")
 def plain_models(folders):
-    """``plain_models(name, storage_dtype, sharp)`` -> the plain implementation of that folder."""
+    """``plain_models(name, dtype, sharp)`` -> the plain implementation of that folder, with
+    activations rounded where a bfloat16 engine stores them when ``dtype`` is bfloat16."""
     import plain_llama
     cache = {}
 
     def get(name: str, storage_dtype: str = "float32", sharp: bool = True):
         key = (name, storage_dtype, sharp)
         if key not in cache:
-            cache[key] = plain_llama.PlainModel(folders(name, storage_dtype, sharp))
+            cache[key] = plain_llama.PlainModel(folders(name, storage_dtype, sharp),
+                                                precision=storage_dtype)
         return cache[key]
     return get
 

@@ -15,9 +15,10 @@ from helix_runtime_b200.engine.step import StepEntry, StepFunction
 # reference allows 5e-5 between its CPU model and its oracle and 2e-4 between CUDA and CPU
 # (tests/llama_model_test.cpp, tests/cuda_llama_model_test.cpp:20-21).
 F32_TOL = dict(atol=2e-5, rtol=1e-4)
-# bfloat16: unit roundoff 2^-9 on every activation between the float32 residual adds; about
-# ten roundings feed a logit, expected worst error a few 1e-3.
-BF16_TOL = dict(atol=1.5e-2, rtol=1.5e-2)
+# bfloat16: the plain implementation rounds activations to bfloat16 at the places where the
+# engine stores them, so what is left is float32-vs-double summation and the rare activation
+# that falls on the other side of a rounding boundary (one part in 256 of one activation).
+BF16_TOL = dict(atol=3e-3, rtol=3e-3)
 
 
 def tolerance(dtype: str) -> dict:

@@ -226,50 +226,71 @@ def swiglu(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
 
 # ------------------------------------------------------------------- the whole model
 
+def round_bfloat16(x: np.ndarray) -> np.ndarray:
+    """Round float32 values to the nearest bfloat16 (ties to even), kept as float32."""
+    bits = np.ascontiguousarray(x, dtype=F32).view(np.uint32)
+    rounded = (bits + np.uint32(0x7FFF) + ((bits >> np.uint32(16)) & np.uint32(1))) \
+        & np.uint32(0xFFFF0000)
+    return rounded.view(F32)
+
+
+def keep(x: np.ndarray) -> np.ndarray:
+    return x
+
+
 def attention_block(config: dict, weights: Dict[str, np.ndarray], layer: int,
-                    normed: np.ndarray, offset: int = 0) -> np.ndarray:
+                    normed: np.ndarray, offset: int = 0, store=keep) -> np.ndarray:
     """QKV projections, rotary encoding of Q and K, causal attention, output projection
-    (src/model/cpu_llama.cpp:65-90)."""
+    (src/model/cpu_llama.cpp:65-90).  ``store`` is applied wherever a bfloat16 engine keeps an
+    activation in 16 bits; for the float32 model it is the identity."""
     tokens = normed.shape[0]
     heads = config["num_attention_heads"]
     head_dim = config["hidden_size"] // heads
     cosine, sine = rope_table(tokens, head_dim, config.get("rope_theta", 10000.0), offset)
-    q = linear(normed, weights[f"layer.{layer}.query"]).reshape(tokens, heads, head_dim)
-    k = linear(normed, weights[f"layer.{layer}.key"]).reshape(tokens, heads, head_dim)
-    v = linear(normed, weights[f"layer.{layer}.value"]).reshape(tokens, heads, head_dim)
-    q = rope_adjacent(q, cosine, sine).transpose(1, 0, 2)
-    k = rope_adjacent(k, cosine, sine).transpose(1, 0, 2)
+    q = store(linear(normed, weights[f"layer.{layer}.query"])).reshape(tokens, heads, head_dim)
+    k = store(linear(normed, weights[f"layer.{layer}.key"])).reshape(tokens, heads, head_dim)
+    v = store(linear(normed, weights[f"layer.{layer}.value"])).reshape(tokens, heads, head_dim)
+    q = store(rope_adjacent(q, cosine, sine)).transpose(1, 0, 2)
+    k = store(rope_adjacent(k, cosine, sine)).transpose(1, 0, 2)
     v = v.transpose(1, 0, 2)
-    context = causal_attention(q, k, v, query_offset=offset)
+    context = store(causal_attention(q, k, v, query_offset=offset))
     merged = context.transpose(1, 0, 2).reshape(tokens, heads * head_dim)
     return linear(merged, weights[f"layer.{layer}.attention_output"])
 
 
-def mlp_block(weights: Dict[str, np.ndarray], layer: int, normed: np.ndarray) -> np.ndarray:
+def mlp_block(weights: Dict[str, np.ndarray], layer: int, normed: np.ndarray,
+              store=keep) -> np.ndarray:
     """gate/up projections, SwiGLU, down projection (src/model/cpu_llama.cpp:94-97)."""
     gate = linear(normed, weights[f"layer.{layer}.gate"])
     up = linear(normed, weights[f"layer.{layer}.up"])
-    return linear(swiglu(gate, up), weights[f"layer.{layer}.down"])
+    return linear(store(swiglu(gate, up)), weights[f"layer.{layer}.down"])
 
 
 def forward(config: dict, weights: Dict[str, np.ndarray], ids: Sequence[int],
-            return_hidden: bool = False):
+            return_hidden: bool = False, precision: str = "float32"):
     """Logits ``[T, V]`` at every position of one whole sequence
-    (src/model/cpu_llama.cpp:37-110).  ``weights`` are in Helix layout."""
+    (src/model/cpu_llama.cpp:37-110).  ``weights`` are in Helix layout.
+
+    ``precision="bfloat16"`` is the same model with the activations between the float32
+    residual sums rounded to bfloat16 where a bfloat16 engine stores them (after each norm,
+    after the Q/K/V projections and the rotation, after attention, after SwiGLU); all sums
+    stay in double.  The reference has no such mode (README.md:693); it is here so that a
+    bfloat16 engine can be held to a tolerance far below bfloat16's own rounding."""
     if len(ids) == 0:
         raise ValueError("token sequence must not be empty")
     if len(ids) > config["max_position_embeddings"]:
         raise ValueError("token sequence exceeds configured maximum")
+    store = {"float32": keep, "bfloat16": round_bfloat16}[precision]
     eps = config.get("rms_norm_eps", 1.0e-6)
     hidden = embedding_lookup(ids, weights["token_embedding"])
     states = []
     for layer in range(config["num_hidden_layers"]):
-        normed = rms_norm(hidden, weights[f"layer.{layer}.attention_norm"], eps)
-        hidden = (hidden + attention_block(config, weights, layer, normed)).astype(F32)
-        normed = rms_norm(hidden, weights[f"layer.{layer}.ffn_norm"], eps)
-        hidden = (hidden + mlp_block(weights, layer, normed)).astype(F32)
+        normed = store(rms_norm(hidden, weights[f"layer.{layer}.attention_norm"], eps))
+        hidden = (hidden + attention_block(config, weights, layer, normed, store=store)).astype(F32)
+        normed = store(rms_norm(hidden, weights[f"layer.{layer}.ffn_norm"], eps))
+        hidden = (hidden + mlp_block(weights, layer, normed, store=store)).astype(F32)
         states.append(hidden)
-    final = rms_norm(hidden, weights["final_norm"], eps)
+    final = store(rms_norm(hidden, weights["final_norm"], eps))
     logits = linear(final, weights["lm_head"])
     if return_hidden:
         return logits, states
@@ -318,13 +339,14 @@ def select_greedy_token(logits_row: np.ndarray) -> int:
 
 
 def greedy_generate(config: dict, weights: Dict[str, np.ndarray], prompt: Sequence[int],
-                    max_new_tokens: int, eos: Optional[int] = None) -> List[int]:
+                    max_new_tokens: int, eos: Optional[int] = None,
+                    precision: str = "float32") -> List[int]:
     """Greedy continuation by full recomputation each step; stops at ``eos`` (emitted), at
     ``max_new_tokens`` or when the context is full (src/model/cpu_generation.cpp:137-167)."""
     tokens = list(prompt)
     generated: List[int] = []
     while len(generated) < max_new_tokens:
-        token = select_greedy_token(forward(config, weights, tokens)[-1])
+        token = select_greedy_token(forward(config, weights, tokens, precision=precision)[-1])
         generated.append(token)
         if eos is not None and token == eos:
             break
@@ -337,13 +359,15 @@ def greedy_generate(config: dict, weights: Dict[str, np.ndarray], prompt: Sequen
 class PlainModel:
     """A model folder loaded for the plain implementation."""
 
-    def __init__(self, directory: str) -> None:
+    def __init__(self, directory: str, precision: str = "float32") -> None:
         self.config, self.source = read_model_folder(directory)
         self.weights = to_helix_layout(self.config, self.source)
+        self.precision = precision
 
     def logits(self, ids: Sequence[int]) -> np.ndarray:
-        return forward(self.config, self.weights, ids)
+        return forward(self.config, self.weights, ids, precision=self.precision)
 
     def greedy(self, prompt: Sequence[int], max_new_tokens: int,
                eos: Optional[int] = None) -> List[int]:
-        return greedy_generate(self.config, self.weights, prompt, max_new_tokens, eos)
+        return greedy_generate(self.config, self.weights, prompt, max_new_tokens, eos,
+                               precision=self.precision)

@@ -1,0 +1,154 @@
+"""Generation through the Python entry point and the command line, against the plain
+implementation: greedy and temperature sampling, many requests with chunked prompts mixed
+with decoding, stop reasons and the count of cached tokens."""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, random_tokens
+from helix_runtime_b200 import Engine
+from helix_runtime_b200.sampling import uniform_for
+from tiny_configs import PAGE_SIZE, tiny_config
+
+pytestmark = pytest.mark.gpu
+
+SLACK = {"float32": 1e-4, "bfloat16": 6e-3}
+
+
+def check_greedy(plain, prompt, generated, dtype):
+    """Teacher-forced: every generated token is a maximum of the plain logits for the prefix
+    the engine itself produced, up to the precision of the dtype."""
+    tokens = list(prompt)
+    for index, token in enumerate(generated):
+        row = plain.logits(tokens)[-1]
+        assert row[token] >= row.max() - SLACK[dtype], \
+            f"token {index}: engine chose {token}, plain prefers {int(np.argmax(row))}"
+        tokens.append(token)
+
+
+def check_sampled(plain, prompt, generated, temperature, seed, dtype):
+    tokens = list(prompt)
+    for index, token in enumerate(generated):
+        row = plain.logits(tokens)[-1].astype(np.float64)
+        weights = np.exp((row - row.max()) / temperature)
+        cumulative = np.cumsum(weights) / weights.sum()
+        u = uniform_for(seed, index)
+        want = min(int(np.searchsorted(cumulative, u, side="right")), len(row) - 1)
+        if token != want:
+            # the engine's logits differ from the plain ones by rounding: the draw may fall on
+            # the other side of a boundary that lies that close to u
+            low, high = sorted((token, want))
+            margin = 20 * SLACK[dtype] / temperature
+            assert high - low <= 2 and abs(cumulative[low] - u) < margin, \
+                f"token {index}: engine drew {token}, plain draws {want} (u={u})"
+        tokens.append(token)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"),
+                                        ("A", "bfloat16"), ("B", "bfloat16")])
+def test_greedy_generation(name, dtype, folders, plain_models):
+    plain = plain_models(name, dtype)
+    vocab = tiny_config(name).vocab_size
+    engine = Engine.from_pretrained(folders(name, dtype), dtype=dtype, page_size=PAGE_SIZE[name],
+                                    max_running_requests=4, max_tokens_per_iteration=64)
+    prompts = [random_tokens(vocab, length, seed=length) for length in (5, 17, 31)]
+    results = engine.generate(prompts, max_new_tokens=12)
+    for prompt, result in zip(prompts, results):
+        assert len(result.generated_tokens) == 12 and result.stop_reason == "max_new_tokens"
+        assert result.cached_token_count == len(prompt) + 12 - 1
+        check_greedy(plain, prompt, result.generated_tokens, dtype)
+    if dtype == "float32":
+        assert results[1].generated_tokens == plain.greedy(prompts[1], 12)
+    engine.cache.check()
+    assert not engine.cache.live_requests()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_requests_chunked_prompts_mixed_with_decoding(dtype, folders, plain_models):
+    """Tiny B's workload: prompts of 1/9/40/64/100 tokens, 20 new tokens, temperature 0.8 at a
+    fixed seed plus a greedy run, prompts cut at 32 tokens and mixed with decode tokens."""
+    plain = plain_models("B", dtype)
+    prompts = [random_tokens(384, length, seed=200 + length) for length in (1, 9, 40, 64, 100)]
+    engine = Engine.from_pretrained(folders("B", dtype), dtype=dtype, page_size=16,
+                                    max_running_requests=4, max_tokens_per_iteration=48,
+                                    max_prefill_chunk=32, num_pages=24, poison_free_pages=True)
+    greedy = engine.generate(prompts, max_new_tokens=20)
+    for prompt, result in zip(prompts, greedy):
+        check_greedy(plain, prompt, result.generated_tokens, dtype)
+    sampled = engine.generate(prompts, max_new_tokens=20, temperature=0.8, seed=11)
+    for index, (prompt, result) in enumerate(zip(prompts, sampled)):
+        assert len(result.generated_tokens) == 20
+        check_sampled(plain, prompt, result.generated_tokens, 0.8, 11 + index, dtype)
+    assert any(a.generated_tokens != b.generated_tokens for a, b in zip(greedy, sampled))
+    again = engine.generate(prompts, max_new_tokens=20, temperature=0.8, seed=11)
+    assert [r.generated_tokens for r in again] == [r.generated_tokens for r in sampled]
+    stats = engine.stats()
+    assert stats["scheduler"]["prefill_tokens"] > 0 and stats["scheduler"]["decode_tokens"] > 0
+    assert stats["cache"]["groups"][0]["reuses"] > 0
+    engine.cache.check()
+
+
+def test_stop_reasons_and_cached_token_count(folders, plain_models):
+    plain = plain_models("A", "float32")
+    engine = Engine.from_pretrained(folders("A", "float32"), dtype="float32", page_size=8,
+                                    max_running_requests=2, max_tokens_per_iteration=64)
+    prompt = random_tokens(256, 6, seed=1)
+    free_run = engine.generate([prompt], max_new_tokens=8)[0].generated_tokens
+    eos = free_run[3]
+    first = free_run.index(eos)
+    result = engine.generate([prompt], max_new_tokens=8, eos_token=eos)[0]
+    assert result.stop_reason == "eos_token" and result.generated_tokens == free_run[:first + 1]
+    assert result.cached_token_count == len(prompt) + first      # the eos token is not fed back
+    long_prompt = random_tokens(256, 126, seed=2)
+    result = engine.generate([long_prompt], max_new_tokens=10)[0]
+    assert result.stop_reason == "context_limit" and len(result.generated_tokens) == 3
+    assert result.cached_token_count == 128
+    check_greedy(plain, long_prompt, result.generated_tokens, "float32")
+    result = engine.generate([prompt], max_new_tokens=0)[0]
+    assert result.generated_tokens == [] and result.cached_token_count == len(prompt)
+
+
+def test_bad_submissions_are_refused(folders):
+    engine = Engine.from_pretrained(folders("A", "float32"), dtype="float32", page_size=8,
+                                    max_running_requests=2, num_pages=4)
+    with pytest.raises(ValueError, match="vocabulary"):
+        engine.submit([1, 256])
+    with pytest.raises(ValueError, match="eos token"):
+        engine.submit([1], eos_token=999)
+    with pytest.raises(ValueError, match="positions"):
+        engine.submit([1] * 129)
+    with pytest.raises(ValueError, match="never run"):
+        engine.submit([1] * 30, max_new_tokens=10)       # 39 rows > 4 pages of 8
+    with pytest.raises(ValueError, match="at least one"):
+        engine.submit([])
+
+
+def test_no_cpu_path():
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        Engine.from_pretrained("/nonexistent", device="cpu")
+
+
+def test_command_line(folders, plain_models):
+    folder = folders("A", "float32")
+    plain = plain_models("A", "float32")
+    prompt = [1, 42, 17, 5, 9]
+    completed = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "helix_generate"), "--model", folder,
+         "--dtype", "float32", "--max-new-tokens", "6", "--page-size", "8", *map(str, prompt)],
+        capture_output=True, text=True, cwd=ROOT)
+    assert completed.returncode == 0, completed.stderr
+    lines = completed.stdout.strip().splitlines()
+    assert lines[0].startswith("generated_token_ids:")
+    generated = [int(t) for t in lines[0].split(":", 1)[1].split()]
+    assert generated == plain.greedy(prompt, 6)
+    assert lines[1] == "stop_reason: max_new_tokens"
+    assert lines[2] == "cached_token_count: 10"        # 5 + 6 - 1, as the reference counts
+    failed = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "helix_generate"), "--model", folder,
+         "--dtype", "float32", "999999"], capture_output=True, text=True, cwd=ROOT)
+    assert failed.returncode == 1 and "helix_generate:" in failed.stderr
