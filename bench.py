@@ -114,6 +114,44 @@ def reference_arm() -> int:
     return 0
 
 
+def profile_region(options, model, config, fresh, rng) -> int:
+    """One eager step (no CUDA graph) inside a profiler range: a decode step of ``--batch``
+    requests at context ``--prompt-len``, or a prefill step of ``--prompt-len`` tokens."""
+    import torch
+
+    from helix_runtime_b200.engine.step import StepEntry
+
+    length = options.prompt_len
+    batch = options.batch if options.profile == "decode" else 1
+    cache, step, sampler = fresh(batch, length + 8, max(length, batch))
+    prompts = [[int(t) for t in rng.integers(0, config.vocab_size, length)] for _ in range(batch)]
+    for index in range(batch):
+        cache.admit(index)
+    if options.profile == "prefill":
+        step.run([StepEntry(0, prompts[0], [length - 1])])      # warm-up (sizes workspaces)
+        cache.release(0)
+        cache.admit(0)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        step.run([StepEntry(0, prompts[0], [length - 1])])
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return 0
+    per_step = max(1, PREFILL_TOKENS // length)
+    for begin in range(0, batch, per_step):
+        step.run([StepEntry(index, prompts[index], [length - 1])
+                  for index in range(begin, min(begin + per_step, batch))])
+    decode = [StepEntry(index, [1 + index], [0]) for index in range(batch)]
+    for _ in range(2):
+        sampler.launch(step.run(decode), True, step.status)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    sampler.launch(step.run(decode), True, step.status)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -124,6 +162,10 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"],
                         help="run fewer layers of the same sizes (recorded in config)")
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
+                        help="run one eager step of this kind between cudaProfilerStart/Stop "
+                             "(for ncu --profile-from-start off) and print nothing else")
+    parser.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     options = parser.parse_args()
     if options.impl == "reference":
         return reference_arm()
@@ -206,6 +248,9 @@ def main() -> int:
         step.raise_on_status()
         mean_context = PROMPT_LEN + n_warmup + (n_steps + 1) / 2.0
         return batch * n_steps / (elapsed / 1e3), elapsed / n_steps, kernels, mean_context
+
+    if options.profile is not None:
+        return profile_region(options, model, config, fresh, rng)
 
     # ------------------------------------------------------------------ decode, batch B
     sampler_clock = ClockSampler(os.path.join(out_dir, "bench_clocks.csv"))

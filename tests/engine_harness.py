@@ -16,9 +16,11 @@ from helix_runtime_b200.engine.step import StepEntry, StepFunction
 # (tests/llama_model_test.cpp, tests/cuda_llama_model_test.cpp:20-21).
 F32_TOL = dict(atol=2e-5, rtol=1e-4)
 # bfloat16: the plain implementation rounds activations to bfloat16 at the places where the
-# engine stores them, so what is left is float32-vs-double summation and the rare activation
-# that falls on the other side of a rounding boundary (one part in 256 of one activation).
-BF16_TOL = dict(atol=3e-3, rtol=3e-3)
+# engine stores them, so what is left is float32-vs-double summation and activations that fall
+# on the other side of a rounding boundary (one part in 256 of that activation), which the
+# sharpened attention and the final norm carry into the logits.  For scale: rounding to
+# bfloat16 itself moves the logits of these models by up to 2e-2.
+BF16_TOL = dict(atol=5e-3, rtol=5e-3)
 
 
 def tolerance(dtype: str) -> dict:

@@ -26,9 +26,17 @@ def tiny_config(name: str) -> LlamaConfig:
 
 
 # Attention of a tiny N(0, 0.02) model is almost uniform, which would hide a key that is
-# missing or misplaced.  The sharp variant multiplies the query and key projections so that
-# scores have a spread of about one and single keys matter.
-SHARP_GAINS = {"q_proj": 8.0, "k_proj": 8.0}
+# missing or misplaced.  The sharp variant multiplies the query and key projections by a gain
+# chosen so that attention scores have a spread (standard deviation) of about 1.5 whatever the
+# width: score spread = gain^2 * std^2 * hidden, so single keys matter but the softmax is
+# not one-hot.
+SCORE_SPREAD = 1.5
+
+
+def sharp_gains(name: str, std: float = 0.02):
+    hidden = {"A": TINY_A, "B": TINY_B}[name]["hidden_size"]
+    gain = (SCORE_SPREAD / (std * std * hidden)) ** 0.5
+    return {"q_proj": gain, "k_proj": gain}
 
 
 def make_folder(directory: str, name: str, storage_dtype: str = "float32",
@@ -37,5 +45,6 @@ def make_folder(directory: str, name: str, storage_dtype: str = "float32",
     path = os.path.join(directory, f"tiny_{name}_{storage_dtype}" + ("_sharp" if sharp else ""))
     if not os.path.exists(os.path.join(path, "model.safetensors")):
         write_random_model(path, tiny_config(name), SEED[name], std=std, scale_std=scale_std,
-                           storage_dtype=storage_dtype, gains=SHARP_GAINS if sharp else None)
+                           storage_dtype=storage_dtype,
+                           gains=sharp_gains(name, std) if sharp else None)
     return path
