@@ -123,7 +123,7 @@ def profile_region(options, model, config, fresh, rng) -> int:
 
     length = options.prompt_len
     batch = options.batch if options.profile == "decode" else 1
-    cache, step, sampler = fresh(batch, length + 8, max(length, batch))
+    cache, step, sampler = fresh(batch, length + 8, max(length, batch, PREFILL_TOKENS))
     prompts = [[int(t) for t in rng.integers(0, config.vocab_size, length)] for _ in range(batch)]
     for index in range(batch):
         cache.admit(index)

@@ -26,6 +26,7 @@ SOURCES = (
     "hx_gemm_simt.cu",
     "hx_gemm_tc.cu",
     "hx_attention.cu",
+    "hx_attention_mma.cu",
     "hx_sampling.cu",
 )
 HEADERS = ("hx_common.cuh",)
@@ -118,6 +119,13 @@ def build(verbose: bool = True, force: bool = False) -> str:
         partial = target + f".{os.getpid()}.tmp"
         _run([nvcc, "-shared", "-o", partial, *objects, "-cudart", "static"])
         os.replace(partial, target)
+        for name in os.listdir(build_dir):      # libraries of older sources
+            if name.startswith("libhelix_b200_") and name.endswith(".so") and \
+                    os.path.join(build_dir, name) != target:
+                try:
+                    os.remove(os.path.join(build_dir, name))
+                except OSError:
+                    pass
     finally:
         stop.set()
         for obj in objects:

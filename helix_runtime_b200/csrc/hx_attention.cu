@@ -78,6 +78,9 @@ struct AttentionArgs {
   const int* request_table_row;
   const int* block_tables;
   int table_stride;
+  const int* request_start;   // [requests + 1], needed only when skip_query_len > 0
+  int skip_query_len;         // > 0: leave requests with at least this many tokens to the
+                              // tensor-core kernel
   void* out;
   int ldo;
   float* partial;   // [tokens * heads][max_splits][head_dim + 2], only when max_splits > 1
@@ -94,6 +97,12 @@ struct AttentionArgs {
   int* status;
 };
 
+__device__ __forceinline__ bool skipped(const AttentionArgs& a, int token) {
+  if (a.skip_query_len <= 0) return false;
+  const int request = a.token_request[token];
+  return a.request_start[request + 1] - a.request_start[request] >= a.skip_query_len;
+}
+
 __device__ __forceinline__ void key_range(const AttentionArgs& a, int token, int& lo, int& hi) {
   const int position = a.positions[token];
   hi = position + 1;
@@ -101,8 +110,10 @@ __device__ __forceinline__ void key_range(const AttentionArgs& a, int token, int
 }
 
 // DPL: value coordinates per lane in the value phase (32 * DPL >= head_dim);
-// VEC: elements per load in the key phase.
-template <typename T, int DPL, int VEC>
+// VEC: elements per load in the key phase; HD: the head size when it is known at compile
+// time (0: read it from the arguments).  With HD known the loads of a key row are unrolled
+// and issued together, which is what lets one warp keep a whole row in flight.
+template <typename T, int DPL, int VEC, int HD>
 __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(AttentionArgs a) {
   __shared__ float q_shared[WARPS_PER_BLOCK][MAX_HEAD_DIM];
   const int warp = threadIdx.x >> 5;
@@ -114,6 +125,7 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
   const int token_head = static_cast<int>(item / a.max_splits);
   const int head = token_head % a.heads;
   const int token = token_head / a.heads;
+  if (skipped(a, token)) return;
 
   int lo, hi;
   key_range(a, token, lo, hi);
@@ -122,7 +134,7 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
   const int begin = lo + split * a.split_keys;
   const int end = min(begin + a.split_keys, hi);
 
-  const int D = a.head_dim;
+  const int D = HD > 0 ? HD : a.head_dim;
   const int kv_head = head / (a.heads / a.kv_heads);
   const T* q = static_cast<const T*>(a.q) + static_cast<size_t>(token) * a.ldq +
                static_cast<size_t>(head) * D;
@@ -159,11 +171,26 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
     if (valid) {
       const T* k = k_cache + static_cast<size_t>(row) * D;
       float dot = 0.0f;
-      for (int d = 0; d < D; d += VEC) {
-        float kv[VEC];
-        VecLoad<T, VEC>::load(k + d, kv);
+      if (HD > 0) {
+        constexpr int kLoads = HD > 0 ? HD / VEC : 1;
+        constexpr int kBatch = kLoads < 16 ? kLoads : 16;     // loads in flight per lane
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) dot = fmaf(qs[d + i], kv[i], dot);
+        for (int b = 0; b < kLoads; b += kBatch) {
+          float kv[kBatch][VEC];
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u) VecLoad<T, VEC>::load(k + (b + u) * VEC, kv[u]);
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) dot = fmaf(qs[(b + u) * VEC + i], kv[u][i], dot);
+        }
+      } else {
+        for (int d = 0; d < D; d += VEC) {
+          float kv[VEC];
+          VecLoad<T, VEC>::load(k + d, kv);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) dot = fmaf(qs[d + i], kv[i], dot);
+        }
       }
       score = dot * a.scale;
     }
@@ -185,16 +212,27 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] *= correction;
 
+    // values: eight keys at a time, their loads issued together.  A key with zero weight
+    // (masked, unreadable, or underflowed) is skipped, so a stale page is never read.
     const int keys_here = min(32, end - chunk);
-    for (int j = 0; j < keys_here; ++j) {
-      const float p = __shfl_sync(0xffffffffu, probability, j);
-      const int v_row = __shfl_sync(0xffffffffu, row, j);
-      if (p != 0.0f && my_dim < D) {
-        float vv[DPL];
-        VecLoad<T, DPL>::load(v_cache + static_cast<size_t>(v_row) * D + my_dim, vv);
+    for (int j0 = 0; j0 < keys_here; j0 += 8) {
+      float p8[8];
+      float vv[8][DPL];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p, vv[i], acc[i]);
+      for (int u = 0; u < 8; ++u) {
+        p8[u] = __shfl_sync(0xffffffffu, probability, j0 + u);
+        const int v_row = __shfl_sync(0xffffffffu, row, j0 + u);
+        if (p8[u] != 0.0f && my_dim < D) {
+          VecLoad<T, DPL>::load(v_cache + static_cast<size_t>(v_row) * D + my_dim, vv[u]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < DPL; ++i) vv[u][i] = 0.0f;
+        }
       }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p8[u], vv[u][i], acc[i]);
     }
   }
 
@@ -229,6 +267,7 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void attention_merge_kernel(A
   if (token_head >= static_cast<long long>(a.tokens) * a.heads) return;
   const int head = static_cast<int>(token_head % a.heads);
   const int token = static_cast<int>(token_head / a.heads);
+  if (skipped(a, token)) return;
   int lo, hi;
   key_range(a, token, lo, hi);
   const int n_splits = (hi - lo + a.split_keys - 1) / a.split_keys;
@@ -257,11 +296,11 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void attention_merge_kernel(A
   }
 }
 
-template <typename T, int DPL, int VEC>
+template <typename T, int DPL, int VEC, int HD = 0>
 void launch_main(const AttentionArgs& a, cudaStream_t stream) {
   const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
   const int blocks = static_cast<int>((items + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
-  paged_attention_kernel<T, DPL, VEC><<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>(a);
+  paged_attention_kernel<T, DPL, VEC, HD><<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>(a);
 }
 
 template <typename T, int DPL>
@@ -280,7 +319,14 @@ int dispatch_vec(const AttentionArgs& a, cudaStream_t stream) {
 template <typename T>
 int dispatch(const AttentionArgs& a, cudaStream_t stream) {
   int rc;
-  if (a.head_dim <= 64 && a.head_dim % 2 == 0) {
+  constexpr int kMaxVec = sizeof(T) == 2 ? 8 : 4;
+  if (a.head_dim == 128) {
+    launch_main<T, 4, kMaxVec, 128>(a, stream);
+    rc = HX_OK;
+  } else if (a.head_dim == 64) {
+    launch_main<T, 2, kMaxVec, 64>(a, stream);
+    rc = HX_OK;
+  } else if (a.head_dim <= 64 && a.head_dim % 2 == 0) {
     rc = dispatch_vec<T, 2>(a, stream);
   } else if (a.head_dim <= 128 && a.head_dim % 4 == 0) {
     rc = dispatch_vec<T, 4>(a, stream);
@@ -313,7 +359,8 @@ HX_API long long hx_paged_attention_scratch_floats(int tokens, int heads, int he
 HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,
                               int dtype, const int* positions, const int* token_request,
                               const int* request_table_row, const int* block_tables,
-                              int table_stride, void* out, int ldo, float* partial, int tokens,
+                              int table_stride, const int* request_start, int skip_query_len,
+                              void* out, int ldo, float* partial, int tokens,
                               int heads, int kv_heads, int head_dim, int page_size, int num_pages,
                               int window, float scale, int split_keys, int max_splits, int* status,
                               cudaStream_t stream) {
@@ -325,13 +372,16 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
   HX_REQUIRE(split_keys > 0 && max_splits > 0, "hx_paged_attention: bad split sizes");
   HX_REQUIRE(max_splits == 1 || partial != nullptr, "hx_paged_attention: scratch missing");
   HX_REQUIRE(window >= 0, "hx_paged_attention: window must not be negative");
+  HX_REQUIRE(skip_query_len <= 0 || request_start != nullptr,
+             "hx_paged_attention: request_start missing");
   HX_REQUIRE(ldq >= heads * head_dim && ldo >= heads * head_dim,
              "hx_paged_attention: row strides too small");
   HX_REQUIRE(static_cast<long long>(num_pages) * kv_heads * page_size < (1ll << 31),
              "hx_paged_attention: cache rows exceed 32-bit indexing");
   if (tokens == 0) return HX_OK;
   AttentionArgs a{q, ldq, k_cache, v_cache, positions, token_request, request_table_row,
-                  block_tables, table_stride, out, ldo, partial, tokens, heads, kv_heads, head_dim,
+                  block_tables, table_stride, request_start, skip_query_len, out, ldo, partial,
+                  tokens, heads, kv_heads, head_dim,
                   page_size, num_pages, window, scale, split_keys, max_splits, status};
   const long long items = static_cast<long long>(tokens) * heads * max_splits;
   HX_REQUIRE(items / WARPS_PER_BLOCK < (1ll << 31) - 1, "hx_paged_attention: grid too large");

@@ -1,0 +1,398 @@
+// Paged causal attention for prompt portions on the tensor cores (bfloat16 storage).
+//
+// One CTA takes 64 consecutive query tokens of one request and one head; its four warps own
+// 16 query rows each and walk the request's keys in tiles of 64, anchored at key 0, with
+// the online softmax of flash attention: S = Q K^T on the tensor cores (bf16 products,
+// float32 sums), running maximum, exp and running sum in float32 registers, O += P V on the
+// tensor cores.  The probabilities are fed to the second product as TWO bfloat16 terms
+// (P = hi + lo), so they keep about 16 bits instead of 8 and the softmax stays a float32
+// quantity as far as the result can tell.  The reference materialises a [heads, T, T] score
+// tensor for the same computation (src/attention/cuda.cu:31-77, src/model/cuda_llama.cpp:249).
+//
+// Keys and values come straight from the pages: each 64-key tile is gathered row by row
+// through the block table with cp.async into a swizzled shared-memory tile, two tiles in
+// flight.  Rows beyond the last key any query of the CTA may see are zero-filled, never
+// read, so a stale or poisoned page cannot leak in through a zero probability.
+//
+// A query row's result depends on its own position only: key tiles are anchored at key 0
+// and rows of a tile do not interact, so it does not matter which tile a token falls into
+// or what else is in the batch.
+//
+// Requests with fewer than `min_query_len` tokens in the step are left to the CUDA-core
+// kernel (hx_paged_attention skips the others), so decode tokens beside prompt portions
+// are each handled by the kernel that suits them.
+#include "hx_common.cuh"
+
+namespace {
+
+constexpr int BLOCK_M = 64;   // query rows per CTA
+constexpr int BLOCK_N = 64;   // keys per tile
+constexpr int THREADS = 128;
+
+struct PrefillArgs {
+  const __nv_bfloat16* q;
+  int ldq;
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  const int* request_start;     // [requests + 1] first token of each request in the batch
+  const int* request_context;   // [requests] tokens cached before this step
+  const int* request_table_row;
+  const int* block_tables;
+  int table_stride;
+  __nv_bfloat16* out;
+  int ldo;
+  int requests;
+  int heads;
+  int kv_heads;
+  int page_size;
+  int num_pages;
+  float scale;
+  int min_query_len;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// 16-byte copy global -> shared; `bytes` == 0 writes zeros and reads nothing.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// D (16x8, f32) += A (16x16, bf16, row) * B (16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Tiles are [rows][D] bf16 with the 16-byte chunks of a row XOR-swizzled by the row number,
+// so that the eight rows an ldmatrix touches fall into different banks.
+template <int D>
+__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
+  constexpr int kChunks = D / 8;
+  return static_cast<uint32_t>((row * kChunks + (chunk ^ (row & 7))) * 16);
+}
+
+template <int D>
+__global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs a) {
+  constexpr int kChunks = D / 8;          // 16-byte chunks per row
+  constexpr int kTileBytes = BLOCK_N * D * 2;
+  constexpr int kDSteps = D / 16;         // k-steps of Q K^T
+  constexpr int kOBlocks = D / 8;         // n-blocks of the output
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* q_tile = smem;                          // [64][D]
+  uint8_t* kv_tiles = smem + BLOCK_M * D * 2;      // 2 stages x (K tile, V tile)
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int head = blockIdx.y;
+  const int kv_head = head / (a.heads / a.kv_heads);
+
+  // which request and which 64-row tile of it is this CTA?
+  int request = -1, tile_in_request = 0;
+  {
+    int remaining = blockIdx.x;
+    for (int r = 0; r < a.requests; ++r) {
+      const int length = a.request_start[r + 1] - a.request_start[r];
+      if (length < a.min_query_len) continue;
+      const int tiles = (length + BLOCK_M - 1) / BLOCK_M;
+      if (remaining < tiles) {
+        request = r;
+        tile_in_request = remaining;
+        break;
+      }
+      remaining -= tiles;
+    }
+  }
+  if (request < 0) return;
+  const int q_begin = a.request_start[request];
+  const int q_len = a.request_start[request + 1] - q_begin;
+  const int context = a.request_context[request];
+  const int row0 = tile_in_request * BLOCK_M;                 // first query row of the tile
+  const int rows_here = min(BLOCK_M, q_len - row0);
+  const int last_key = context + row0 + rows_here - 1;        // last key any row here sees
+  const int n_tiles = last_key / BLOCK_N + 1;
+  const int* table = a.block_tables +
+                     static_cast<size_t>(a.request_table_row[request]) * a.table_stride;
+
+  // ---- Q tile -> shared memory (rows beyond the portion are zero)
+  for (int index = tid; index < BLOCK_M * kChunks; index += THREADS) {
+    const int row = index / kChunks;
+    const int chunk = index - row * kChunks;
+    const bool valid = row < rows_here;
+    const __nv_bfloat16* src = a.q + static_cast<size_t>(q_begin + row0 + (valid ? row : 0)) * a.ldq +
+                               static_cast<size_t>(head) * D + chunk * 8;
+    cp_async_16(smem_u32(q_tile) + tile_offset<D>(row, chunk), src, valid ? 16 : 0);
+  }
+
+  auto load_kv_tile = [&](int tile, int stage) {
+    const uint32_t k_dst = smem_u32(kv_tiles + stage * 2 * kTileBytes);
+    const uint32_t v_dst = k_dst + kTileBytes;
+    for (int index = tid; index < BLOCK_N * kChunks; index += THREADS) {
+      const int row = index / kChunks;
+      const int chunk = index - row * kChunks;
+      const int key = tile * BLOCK_N + row;
+      bool valid = key <= last_key;
+      size_t source_row = 0;
+      if (valid) {
+        const int page = table[key / a.page_size];
+        if (page < 0 || page >= a.num_pages) {
+          if (a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
+          valid = false;
+        } else {
+          source_row = (static_cast<size_t>(page) * a.kv_heads + kv_head) * a.page_size +
+                       key % a.page_size;
+        }
+      }
+      const size_t element = source_row * D + chunk * 8;
+      const uint32_t offset = tile_offset<D>(row, chunk);
+      cp_async_16(k_dst + offset, a.k_cache + element, valid ? 16 : 0);
+      cp_async_16(v_dst + offset, a.v_cache + element, valid ? 16 : 0);
+    }
+  };
+
+  load_kv_tile(0, 0);
+  cp_async_commit();      // group 0: Q and the first K/V tile
+
+  // ---- per-thread state: this thread owns rows (lane / 4) and (lane / 4 + 8) of its warp
+  float o_acc[kOBlocks][4];
+#pragma unroll
+  for (int n = 0; n < kOBlocks; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o_acc[n][e] = 0.0f;
+  float row_max[2] = {-INFINITY, -INFINITY};
+  float row_sum[2] = {0.0f, 0.0f};
+  uint32_t q_frag[kDSteps][4];
+  const int warp_row = warp * 16;
+  const int q_pos0 = context + row0 + warp_row + (lane >> 2);   // position of the first row
+  const int q_pos1 = q_pos0 + 8;
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int stage = tile & 1;
+    if (tile + 1 < n_tiles) {
+      load_kv_tile(tile + 1, stage ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    if (tile == 0) {
+#pragma unroll
+      for (int k = 0; k < kDSteps; ++k) {
+        const int row = warp_row + (lane & 15);
+        const int chunk = k * 2 + (lane >> 4);
+        ldmatrix_x4(q_frag[k], smem_u32(q_tile) + tile_offset<D>(row, chunk));
+      }
+    }
+
+    const uint32_t k_base = smem_u32(kv_tiles + stage * 2 * kTileBytes);
+    const uint32_t v_base = k_base + kTileBytes;
+
+    // ---- S = Q K^T for 16 rows x 64 keys: 8 n-blocks of 8 keys
+    float s[BLOCK_N / 8][4];
+#pragma unroll
+    for (int n = 0; n < BLOCK_N / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[n][e] = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kDSteps; ++k) {
+#pragma unroll
+      for (int pair = 0; pair < BLOCK_N / 16; ++pair) {
+        // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+        const int matrix = lane >> 3;
+        const int key_row = pair * 16 + (matrix >> 1) * 8 + (lane & 7);
+        const int chunk = k * 2 + (matrix & 1);
+        uint32_t b[4];
+        ldmatrix_x4(b, k_base + tile_offset<D>(key_row, chunk));
+        mma_bf16(s[pair * 2], q_frag[k], b[0], b[1]);
+        mma_bf16(s[pair * 2 + 1], q_frag[k], b[2], b[3]);
+      }
+    }
+
+    // ---- scale, causal mask, running maximum
+    const int key0 = tile * BLOCK_N + 2 * (lane & 3);
+    const bool needs_mask = tile * BLOCK_N + BLOCK_N - 1 > context + row0 + warp_row;
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < BLOCK_N / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float value = s[n][e] * a.scale;
+        if (needs_mask) {
+          const int key = key0 + n * 8 + (e & 1);
+          const int q_pos = (e & 2) ? q_pos1 : q_pos0;
+          if (key > q_pos) value = -INFINITY;
+        }
+        s[n][e] = value;
+        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], value);
+      }
+    }
+    float correction[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+      const float new_max = fmaxf(row_max[r], tile_max[r]);
+      // new_max is finite from the first tile on: key 0 is visible to every row
+      correction[r] = row_max[r] == -INFINITY ? 0.0f : __expf(row_max[r] - new_max);
+      row_max[r] = new_max;
+      row_sum[r] *= correction[r];
+    }
+#pragma unroll
+    for (int n = 0; n < kOBlocks; ++n) {
+      o_acc[n][0] *= correction[0];
+      o_acc[n][1] *= correction[0];
+      o_acc[n][2] *= correction[1];
+      o_acc[n][3] *= correction[1];
+    }
+
+    // ---- P = exp(S - max), O += P V with P = hi + lo in bfloat16
+#pragma unroll
+    for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+      float p[2][4];
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float value = __expf(s[kk * 2 + half][e] - row_max[e >> 1]);
+          p[half][e] = value;
+          row_sum[e >> 1] += value;
+        }
+      uint32_t p_hi[4], p_lo[4];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const float x0 = p[half][r * 2], x1 = p[half][r * 2 + 1];
+          const __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+          const __nv_bfloat162 hi = __halves2bfloat162(h0, h1);
+          p_hi[half * 2 + r] = *reinterpret_cast<const uint32_t*>(&hi);
+          p_lo[half * 2 + r] = pack_bf16(x0 - __bfloat162float(h0), x1 - __bfloat162float(h1));
+        }
+      }
+#pragma unroll
+      for (int nn = 0; nn < kOBlocks / 2; ++nn) {
+        // transposed load of V[keys kk*16 .. +15][d nn*16 .. +15]:
+        // matrices (keys 0-7, d lo), (keys 8-15, d lo), (keys 0-7, d hi), (keys 8-15, d hi)
+        const int matrix = lane >> 3;
+        const int key_row = kk * 16 + (matrix & 1) * 8 + (lane & 7);
+        const int chunk = nn * 2 + (matrix >> 1);
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, v_base + tile_offset<D>(key_row, chunk));
+        mma_bf16(o_acc[nn * 2], p_hi, b[0], b[1]);
+        mma_bf16(o_acc[nn * 2], p_lo, b[0], b[1]);
+        mma_bf16(o_acc[nn * 2 + 1], p_hi, b[2], b[3]);
+        mma_bf16(o_acc[nn * 2 + 1], p_lo, b[2], b[3]);
+      }
+    }
+    __syncthreads();      // every warp is done with this stage before it is refilled
+  }
+
+  // ---- finish: full row sums, normalise, store
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+    row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+  }
+  const float inverse[2] = {1.0f / row_sum[0], 1.0f / row_sum[1]};
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp_row + (lane >> 2) + r * 8;
+    if (row >= rows_here) continue;
+    __nv_bfloat16* dst = a.out + static_cast<size_t>(q_begin + row0 + row) * a.ldo +
+                         static_cast<size_t>(head) * D + 2 * (lane & 3);
+#pragma unroll
+    for (int n = 0; n < kOBlocks; ++n) {
+      const __nv_bfloat162 value = __floats2bfloat162_rn(o_acc[n][r * 2] * inverse[r],
+                                                         o_acc[n][r * 2 + 1] * inverse[r]);
+      *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = value;
+    }
+  }
+}
+
+template <int D>
+int launch(const PrefillArgs& a, int tiles, cudaStream_t stream) {
+  constexpr int kSmem = BLOCK_M * D * 2 + 2 * 2 * BLOCK_N * D * 2;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(prefill_attention_kernel<D>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
+      cudaGetLastError();
+      hx_set_error("hx_prefill_attention: cannot reserve %d bytes of shared memory", kSmem);
+      return HX_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  const dim3 grid(tiles, a.heads);
+  prefill_attention_kernel<D><<<grid, THREADS, kSmem, stream>>>(a);
+  return HX_OK;
+}
+
+}  // namespace
+
+// 1 when the tensor-core kernel takes this head size (bfloat16 only).
+HX_API int hx_prefill_attention_supports(int head_dim) { return head_dim == 64 || head_dim == 128; }
+
+// Attention of every request that brings at least `min_query_len` tokens to this step.
+// `tile_bound` is an upper bound of the number of 64-row query tiles over those requests
+// (tokens / 64 + requests is always enough).
+HX_API int hx_prefill_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                const int* request_start, const int* request_context,
+                                const int* request_table_row, const int* block_tables,
+                                int table_stride, void* out, int ldo, int requests, int tile_bound,
+                                int heads, int kv_heads, int head_dim, int page_size,
+                                int num_pages, float scale, int min_query_len, int* status,
+                                cudaStream_t stream) {
+  HX_REQUIRE(hx_prefill_attention_supports(head_dim),
+             "hx_prefill_attention: head_dim %d is not supported (64 or 128)", head_dim);
+  HX_REQUIRE(requests >= 0 && tile_bound >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+             "hx_prefill_attention: bad sizes");
+  HX_REQUIRE(heads <= 65535, "hx_prefill_attention: too many heads");
+  HX_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0,
+             "hx_prefill_attention: bad cache geometry");
+  HX_REQUIRE(ldq % 8 == 0 && ldo % 2 == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(out) & 3) == 0,
+             "hx_prefill_attention: operands must be 16-byte aligned");
+  if (requests == 0 || tile_bound == 0) return HX_OK;
+  PrefillArgs a{static_cast<const __nv_bfloat16*>(q), ldq,
+                static_cast<const __nv_bfloat16*>(k_cache),
+                static_cast<const __nv_bfloat16*>(v_cache), request_start, request_context,
+                request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(out),
+                ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status};
+  const int rc = head_dim == 128 ? launch<128>(a, tile_bound, stream)
+                                 : launch<64>(a, tile_bound, stream);
+  if (rc != HX_OK) return rc;
+  HX_CHECK_LAUNCH("hx_prefill_attention");
+  return HX_OK;
+}

@@ -165,6 +165,8 @@ HX_API int hx_swiglu(const float* gate_up, void* act, int out_dtype, int tokens,
 // qkv row: [q heads | k heads | v heads], each head `head_dim` wide.
 // pairing 0: pairs (2p, 2p+1); pairing 1: pairs (p, p + rotary_dim/2).
 // cache layer: [page][kv_head][slot in page][head_dim].
+constexpr int ROPE_HEADS_PER_BLOCK = 4;
+
 template <typename T>
 __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positions,
                                    const int* __restrict__ token_request,
@@ -196,63 +198,61 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
     }
   }
 
+  // blockIdx.y selects a group of HEADS_PER_BLOCK consecutive heads of the row
+  // [q heads | k heads | v heads]; one thread per coordinate pair of a q/k head, one per
+  // coordinate of a v head.
   const int pairs_per_head = head_dim / 2;
-  // queries and keys: one thread per coordinate pair
-  const int qk_pairs = (heads + kv_heads) * pairs_per_head;
-  for (int index = threadIdx.x; index < qk_pairs; index += blockDim.x) {
-    const int head = index / pairs_per_head;
-    const int pair = index - head * pairs_per_head;
+  const int first_head = blockIdx.y * ROPE_HEADS_PER_BLOCK;
+  const int total_heads = heads + 2 * kv_heads;
+  const int last_head = min(first_head + ROPE_HEADS_PER_BLOCK, total_heads);
+  for (int head = first_head; head < last_head; ++head) {
     T* vec = row + static_cast<size_t>(head) * head_dim;
-    int i0, i1;
-    bool rotate;
-    if (pairing == 0) {
-      i0 = 2 * pair;
-      i1 = i0 + 1;
-      rotate = i1 < rotary_dim;
-    } else {
-      // half-split pairs inside the rotary part; the rest are passed through two by two
-      if (pair < half) {
-        i0 = pair;
-        i1 = pair + half;
-        rotate = true;
-      } else {
-        i0 = rotary_dim + 2 * (pair - half);
-        i1 = i0 + 1;
-        rotate = false;
+    if (head < heads + kv_heads) {
+      for (int pair = threadIdx.x; pair < pairs_per_head; pair += blockDim.x) {
+        int i0, i1;
+        bool rotate;
+        if (pairing == 0) {
+          i0 = 2 * pair;
+          i1 = i0 + 1;
+          rotate = i1 < rotary_dim;
+        } else if (pair < half) {
+          // half-split pairs inside the rotary part; the rest pass through two by two
+          i0 = pair;
+          i1 = pair + half;
+          rotate = true;
+        } else {
+          i0 = rotary_dim + 2 * (pair - half);
+          i1 = i0 + 1;
+          rotate = false;
+        }
+        float a = hx_to_float<T>(vec[i0]);
+        float b = hx_to_float<T>(vec[i1]);
+        if (rotate) {
+          const float c = cos_row[pair];
+          const float s = sin_row[pair];
+          const float ra = a * c - b * s;
+          const float rb = a * s + b * c;
+          a = ra;
+          b = rb;
+        }
+        const T ta = hx_from_float<T>(a);
+        const T tb = hx_from_float<T>(b);
+        if (head < heads) {
+          vec[i0] = ta;
+          vec[i1] = tb;
+        } else if (page >= 0) {
+          const int kv_head = head - heads;
+          T* dst = k_cache +
+                   ((static_cast<size_t>(page) * kv_heads + kv_head) * page_size + slot) * head_dim;
+          dst[i0] = ta;
+          dst[i1] = tb;
+        }
       }
-    }
-    float a = hx_to_float<T>(vec[i0]);
-    float b = hx_to_float<T>(vec[i1]);
-    if (rotate) {
-      const float c = cos_row[pair];
-      const float s = sin_row[pair];
-      const float ra = a * c - b * s;
-      const float rb = a * s + b * c;
-      a = ra;
-      b = rb;
-    }
-    const T ta = hx_from_float<T>(a);
-    const T tb = hx_from_float<T>(b);
-    if (head < heads) {
-      vec[i0] = ta;
-      vec[i1] = tb;
     } else if (page >= 0) {
-      const int kv_head = head - heads;
-      T* dst = k_cache +
+      const int kv_head = head - heads - kv_heads;
+      T* dst = v_cache +
                ((static_cast<size_t>(page) * kv_heads + kv_head) * page_size + slot) * head_dim;
-      dst[i0] = ta;
-      dst[i1] = tb;
-    }
-  }
-  // values: straight copy into the page
-  if (page >= 0) {
-    const int v_elems = kv_heads * head_dim;
-    const T* v_row = row + static_cast<size_t>(heads + kv_heads) * head_dim;
-    for (int index = threadIdx.x; index < v_elems; index += blockDim.x) {
-      const int kv_head = index / head_dim;
-      const int d = index - kv_head * head_dim;
-      v_cache[((static_cast<size_t>(page) * kv_heads + kv_head) * page_size + slot) * head_dim + d] =
-          v_row[index];
+      for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = vec[d];
     }
   }
 }
@@ -275,15 +275,17 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
              "hx_rope_append: cache arguments missing");
   HX_REQUIRE(rotary_dim == 0 || table_positions > 0, "hx_rope_append: empty rotary table");
   if (tokens == 0) return HX_OK;
-  const int threads = 256;
+  const int threads = head_dim / 2 >= 64 ? 64 : 32;
+  const dim3 grid(tokens, (heads + 2 * kv_heads + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
+  HX_REQUIRE(grid.y <= 65535, "hx_rope_append: too many heads");
   if (dtype == HX_F32) {
-    rope_append_kernel<float><<<tokens, threads, 0, stream>>>(
+    rope_append_kernel<float><<<grid, threads, 0, stream>>>(
         static_cast<float*>(qkv), ld, positions, token_request, request_table_row, block_tables,
         table_stride, static_cast<float*>(k_cache), static_cast<float*>(v_cache), write_cache,
         cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing,
         page_size, num_pages, status);
   } else if (dtype == HX_BF16) {
-    rope_append_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
+    rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         static_cast<__nv_bfloat16*>(qkv), ld, positions, token_request, request_table_row,
         block_tables, table_stride, static_cast<__nv_bfloat16*>(k_cache),
         static_cast<__nv_bfloat16*>(v_cache), write_cache, cos_table, sin_table, table_positions,

@@ -24,7 +24,7 @@ from ..weights.random_init import random_tensors, write_model_folder
 from ..weights.safetensors_io import Checkpoint
 from .scheduler import (FifoScheduler, Request, RequestState, SchedulerConfig, StopReason,
                         WorkCompletion)
-from .graphs import DecodeGraphs
+from .graphs import DecodeGraphs, bucketed_context
 from .step import StepEntry, StepError, StepFunction
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -245,10 +245,13 @@ class Engine:
         completions: List[WorkCompletion] = []
         step = self.step_function
         try:
-            ctx, want_rows, n_want, new_lengths = step.prepare(entries)
+            decode_only = all(len(entry.tokens) == 1 and len(entry.want) == 1 for entry in entries)
+            hint = 0
+            if decode_only and self.graphs is not None:
+                hint = bucketed_context(1 + max(self.cache.length(e.request) for e in entries))
+            ctx, want_rows, n_want, new_lengths = step.prepare(entries, context_hint=hint)
             try:
                 sampled: List[int] = []
-                decode_only = n_want == ctx.n_tokens == len(entries)
                 if n_want:
                     greedy = self.sampler.prepare(temperatures, uniforms)
                     if self.graphs is not None and decode_only:

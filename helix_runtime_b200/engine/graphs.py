@@ -8,8 +8,8 @@ reference synchronises after every layer (src/model/cuda_llama.cpp:395); here no
 synchronises inside a step.
 
 A graph is keyed by everything that is baked into its launches: the number of tokens, the
-number of wanted rows, the number of key splits attention was launched for, and whether
-sampling is greedy.
+number of wanted rows, the context length attention was launched for (rounded up to a
+bucket, so that one graph serves 256 consecutive steps), and whether sampling is greedy.
 """
 from __future__ import annotations
 
@@ -18,6 +18,13 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from ..parts.base import StepContext
+
+
+CONTEXT_BUCKET = 256     # decode steps are prepared for a context rounded up to this
+
+
+def bucketed_context(length: int) -> int:
+    return -(-length // CONTEXT_BUCKET) * CONTEXT_BUCKET
 
 
 class DecodeGraphs:
@@ -32,8 +39,9 @@ class DecodeGraphs:
         self.kernels_per_graph: Dict[Tuple[int, int, int, bool], int] = {}
 
     def key_for(self, ctx: StepContext, n_want: int, greedy: bool) -> Tuple[int, int, int, bool]:
-        splits = -(-ctx.max_context_len // ctx.attention_split_keys)
-        return (ctx.n_tokens, n_want, splits, greedy)
+        # launches are sized from the token count and the context length the step was
+        # prepared for (callers round it up to a bucket, see CONTEXT_BUCKET)
+        return (ctx.n_tokens, n_want, ctx.max_context_len, greedy)
 
     def run(self, ctx: StepContext, want_rows: torch.Tensor, n_want: int, greedy: bool,
             advance: bool = False) -> torch.Tensor:

@@ -122,6 +122,7 @@ class StepFunction:
         cursor = 0
         n_want = 0
         max_query = 0
+        min_query = 1 << 30
         max_context = 0
         try:
             for index, entry in enumerate(entries):
@@ -141,6 +142,7 @@ class StepFunction:
                 cursor += count
                 new_lengths.append(before + count)
                 max_query = max(max_query, count)
+                min_query = min(min_query, count)
                 max_context = max(max_context, before + count)
             request_start[len(entries)] = cursor
         except Exception:
@@ -160,7 +162,7 @@ class StepFunction:
             request_slot=self._view("request_slot", True),
             request_start=self._view("request_start", True),
             request_context=self._view("request_context", True),
-            status=self.status, max_query_len=max_query,
+            status=self.status, max_query_len=max_query, min_query_len=min_query,
             max_context_len=max(max_context, context_hint),
             attention_split_keys=self.attention_split_keys,
             host_request_slots=[int(v) for v in request_slot[:len(entries)]],

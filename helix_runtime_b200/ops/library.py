@@ -59,8 +59,14 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_gemm_tc_token_tile.argtypes = [_c_int]
     library.hx_paged_attention.argtypes = [
         _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
-        _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
-        _c_int, _c_ptr, _c_ptr]
+        _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+        _c_float, _c_int, _c_int, _c_ptr, _c_ptr]
+    library.hx_prefill_attention.argtypes = [
+        _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int,
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr]
+    library.hx_prefill_attention.restype = _c_int
+    library.hx_prefill_attention_supports.argtypes = [_c_int]
+    library.hx_prefill_attention_supports.restype = _c_int
     library.hx_paged_attention_scratch_floats.restype = ctypes.c_longlong
     library.hx_paged_attention_scratch_floats.argtypes = [_c_int] * 4
     library.hx_argmax.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]
@@ -209,14 +215,41 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     request_table_row: torch.Tensor, block_tables: torch.Tensor, out: torch.Tensor,
                     partial: Optional[torch.Tensor], tokens: int, heads: int, kv_heads: int,
                     head_dim: int, page_size: int, num_pages: int, window: int, scale: float,
-                    split_keys: int, max_splits: int, status: torch.Tensor) -> None:
-    """out[t, h*D:(h+1)*D] = attention of query (t, h) over its request's pages."""
+                    split_keys: int, max_splits: int, status: torch.Tensor,
+                    request_start: Optional[torch.Tensor] = None, skip_query_len: int = 0) -> None:
+    """out[t, h*D:(h+1)*D] = attention of query (t, h) over its request's pages.  With
+    ``skip_query_len > 0`` tokens of requests that bring at least that many tokens are left
+    out (the tensor-core kernel takes them)."""
     _check(lib().hx_paged_attention(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), dtype_code(q.dtype),
         positions.data_ptr(), token_request.data_ptr(), request_table_row.data_ptr(),
-        block_tables.data_ptr(), block_tables.stride(0), out.data_ptr(), out.stride(0),
+        block_tables.data_ptr(), block_tables.stride(0), _ptr(request_start), skip_query_len,
+        out.data_ptr(), out.stride(0),
         _ptr(partial), tokens, heads, kv_heads, head_dim, page_size, num_pages, window,
         float(scale), split_keys, max_splits, _ptr(status), _stream()))
+
+
+def prefill_attention_supports(head_dim: int) -> bool:
+    return bool(lib().hx_prefill_attention_supports(head_dim))
+
+
+def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      request_start: torch.Tensor, request_context: torch.Tensor,
+                      request_table_row: torch.Tensor, block_tables: torch.Tensor,
+                      out: torch.Tensor, requests: int, tile_bound: int, heads: int,
+                      kv_heads: int, head_dim: int, page_size: int, num_pages: int, scale: float,
+                      min_query_len: int, status: torch.Tensor) -> None:
+    """Tensor-core attention (bfloat16) of every request that brings at least
+    ``min_query_len`` tokens; ``tile_bound`` bounds the number of 64-token query tiles."""
+    _need(q, torch.bfloat16, "q")
+    _need(k_cache, torch.bfloat16, "k_cache")
+    _need(out, torch.bfloat16, "out")
+    _check(lib().hx_prefill_attention(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), request_start.data_ptr(),
+        request_context.data_ptr(), request_table_row.data_ptr(), block_tables.data_ptr(),
+        block_tables.stride(0), out.data_ptr(), out.stride(0), requests, tile_bound, heads,
+        kv_heads, head_dim, page_size, num_pages, float(scale), min_query_len, _ptr(status),
+        _stream()))
 
 
 def argmax(logits: torch.Tensor, tokens_out: torch.Tensor, status: Optional[torch.Tensor]) -> None:

@@ -28,6 +28,9 @@ from .base import LayerCache, Mixer, StepContext, build_part, register_part
 from .linear import project
 
 
+TENSOR_CORE_MIN_QUERY = 16
+
+
 def rotary_row_permutation(heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
     """Row order that turns half-split rotary rows into adjacent-pair rows, per head."""
     half = rotary_dim // 2
@@ -91,6 +94,17 @@ class PagedAttention(Mixer):
     def weight_bytes(self) -> int:
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()
 
+    def split_keys_for(self, tokens: int, longest: int, limit: int) -> int:
+        """Keys per split.  One warp walks one (token, head, split); a step with few tokens
+        (decoding) gets narrower splits so that about sixteen warps per SM stream the cache,
+        a step with many tokens keeps ``limit``.  Splits are multiples of the 32-key chunk,
+        so the choice changes the order of float32 sums only."""
+        wanted_warps = 148 * 16
+        splits = max(1, wanted_warps // max(1, tokens * self.heads))
+        keys = -(-longest // splits)
+        keys = max(32, -(-keys // 32) * 32)
+        return min(keys, max(32, limit))
+
     def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
                 residual: torch.Tensor) -> None:
         n = ctx.n_tokens
@@ -100,17 +114,32 @@ class PagedAttention(Mixer):
         self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
 
         window = cache.window or 0
-        longest = ctx.max_context_len if not window else min(ctx.max_context_len, window)
-        split_keys = ctx.attention_split_keys
-        max_splits = max(1, -(-longest // split_keys))
-        partial = None
-        if max_splits > 1:
-            floats = ops.attention_scratch_floats(n, self.heads, self.head_dim, max_splits)
-            partial = ctx.workspace.at_least("attention.partial", floats, torch.float32)
-        ops.paged_attention(qkv, cache.keys, cache.values, ctx.positions, ctx.token_request,
-                            ctx.request_slot, cache.block_tables, context, partial, n, self.heads,
-                            self.kv_heads, self.head_dim, cache.page_size, cache.num_pages, window,
-                            self.scale, split_keys, max_splits, ctx.status)
+        # prompt portions of at least TENSOR_CORE_MIN_QUERY tokens go to the tensor-core
+        # kernel (bfloat16, no window, head sizes it has); the rest, decode tokens above all,
+        # to the CUDA-core kernel.  A step may need both.
+        tensor_cores = (ctx.dtype == torch.bfloat16 and not window
+                        and ctx.max_query_len >= TENSOR_CORE_MIN_QUERY
+                        and ops.prefill_attention_supports(self.head_dim))
+        if tensor_cores:
+            ops.prefill_attention(qkv, cache.keys, cache.values, ctx.request_start,
+                                  ctx.request_context, ctx.request_slot, cache.block_tables,
+                                  context, ctx.n_requests, n // 64 + ctx.n_requests, self.heads,
+                                  self.kv_heads, self.head_dim, cache.page_size, cache.num_pages,
+                                  self.scale, TENSOR_CORE_MIN_QUERY, ctx.status)
+        if not tensor_cores or ctx.min_query_len < TENSOR_CORE_MIN_QUERY:
+            longest = ctx.max_context_len if not window else min(ctx.max_context_len, window)
+            split_keys = self.split_keys_for(n, longest, ctx.attention_split_keys)
+            max_splits = max(1, -(-longest // split_keys))
+            partial = None
+            if max_splits > 1:
+                floats = ops.attention_scratch_floats(n, self.heads, self.head_dim, max_splits)
+                partial = ctx.workspace.at_least("attention.partial", floats, torch.float32)
+            ops.paged_attention(qkv, cache.keys, cache.values, ctx.positions, ctx.token_request,
+                                ctx.request_slot, cache.block_tables, context, partial, n,
+                                self.heads, self.kv_heads, self.head_dim, cache.page_size,
+                                cache.num_pages, window, self.scale, split_keys, max_splits,
+                                ctx.status, request_start=ctx.request_start,
+                                skip_query_len=TENSOR_CORE_MIN_QUERY if tensor_cores else 0)
         project(context, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status)
 
 

@@ -94,6 +94,7 @@ class StepContext:
     request_context: torch.Tensor       # [max requests] int32 tokens cached before this step
     status: torch.Tensor                # [1] int32 device status word
     max_query_len: int                  # host copies, for grid sizing
+    min_query_len: int                  # fewest tokens any request brings to this step
     max_context_len: int                # longest (cached + new) length in the batch
     attention_split_keys: int = 256
     # host-side copies for parts that are not kernels (tests' toy parts)

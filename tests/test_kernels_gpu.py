@@ -251,7 +251,7 @@ def test_rope_and_cache_append(dtype, heads, kv_heads, head_dim, rotary_dim, pai
 # ------------------------------------------------------------------- attention
 
 def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, new_tokens,
-                   window, split_keys, dominant=None):
+                   window, split_keys, dominant=None, tensor_core_min=0):
     """Build a paged cache holding ``contexts[r] + new_tokens[r]`` keys per request in shuffled
     pages and the queries of the new tokens; return kernel output and plain reference."""
     requests = len(contexts)
@@ -300,11 +300,22 @@ def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, n
                               dtype=torch.float32, device=DEVICE)
     out = torch.full((tokens, heads * head_dim), float("nan"), dtype=dtype, device=DEVICE)
     status = status_word()
-    ops.paged_attention(dev(q, dtype), dev(k_cache, dtype), dev(v_cache, dtype),
-                        dev(positions, torch.int32), dev(token_request, torch.int32),
-                        dev(slots, torch.int32), dev(tables, torch.int32), out, partial, tokens,
-                        heads, kv_heads, head_dim, page_size, num_pages, window or 0, scale,
-                        split_keys, max_splits, status)
+    starts = dev(np.concatenate([[0], np.cumsum(new_tokens)]), torch.int32)
+    if tensor_core_min:
+        # requests with at least that many tokens on the tensor cores, the rest (if any) on
+        # the CUDA cores: together they must fill every row
+        ops.prefill_attention(dev(q, dtype), dev(k_cache, dtype), dev(v_cache, dtype), starts,
+                              dev(contexts, torch.int32), dev(slots, torch.int32),
+                              dev(tables, torch.int32), out, requests, tokens // 64 + requests,
+                              heads, kv_heads, head_dim, page_size, num_pages, scale,
+                              tensor_core_min, status)
+    if not tensor_core_min or min(new_tokens) < tensor_core_min:
+        ops.paged_attention(dev(q, dtype), dev(k_cache, dtype), dev(v_cache, dtype),
+                            dev(positions, torch.int32), dev(token_request, torch.int32),
+                            dev(slots, torch.int32), dev(tables, torch.int32), out, partial, tokens,
+                            heads, kv_heads, head_dim, page_size, num_pages, window or 0, scale,
+                            split_keys, max_splits, status, request_start=starts,
+                            skip_query_len=tensor_core_min)
     assert int(status.item()) == 0
     expected = []
     for r in range(requests):
@@ -357,6 +368,32 @@ def test_one_far_key_stands_out(dtype, key_position):
     assert_close(out, expected, "attention", **tol)
     wanted = values[0][:, key_position].reshape(1, -1)
     assert_close(out, wanted, "dominant key's value", atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [
+    (4, 4, 128, 16), (6, 2, 64, 8), (3, 1, 128, 32), (2, 2, 64, 4)])
+def test_tensor_core_attention_for_prompt_portions(heads, kv_heads, head_dim, page_size):
+    rng = np.random.default_rng(12)
+    # whole prompts (one longer than two tiles, one a single row short of a tile), continued
+    # portions that start inside a page and inside a key tile, and two decode tokens that the
+    # CUDA-core kernel must fill in beside them
+    contexts = [0, 37, 0, 129, 4 * page_size - 1, 70]
+    new_tokens = [150, 19, 63, 64, 1, 1]
+    out, expected, *_ = attention_case(rng, torch.bfloat16, heads, kv_heads, head_dim, page_size,
+                                       contexts, new_tokens, window=None, split_keys=64,
+                                       tensor_core_min=16)
+    assert_close(out, expected, "tensor-core attention", atol=2e-2, rtol=8e-3)
+
+
+@pytest.mark.parametrize("key_position", [0, 63, 64, 200, 299])
+def test_tensor_core_attention_sees_one_far_key(key_position):
+    rng = np.random.default_rng(13)
+    out, expected, values, *_ = attention_case(rng, torch.bfloat16, 4, 4, 128, 16, [270], [30],
+                                               window=None, split_keys=64,
+                                               dominant={0: key_position}, tensor_core_min=16)
+    assert_close(out, expected, "attention", atol=2e-2, rtol=8e-3)
+    wanted = values[0][:, key_position].reshape(1, -1)
+    assert_close(out[-1:], wanted, "dominant key's value", atol=2e-2, rtol=1e-2)
 
 
 def test_attention_refuses_odd_head_sizes():
