@@ -120,20 +120,24 @@ HX_API int hx_rmsnorm(const float* x, const float* weight, void* y, int out_dtyp
 // (src/kernels/cuda/transformer.cu:68-83).  This is the path of the CUDA-core product;
 // the tensor-core product applies the same formula in its epilogue.
 template <typename TOut>
-__global__ void swiglu_kernel(const float* __restrict__ gate_up, TOut* __restrict__ act, int tokens,
-                              int intermediate, int ld_in) {
+__global__ void swiglu_kernel(float* __restrict__ gate_up, TOut* __restrict__ act, int tokens,
+                              int intermediate, int ld_in, int zero_input) {
   const size_t total = static_cast<size_t>(tokens) * intermediate;
   for (size_t index = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; index < total;
        index += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const size_t t = index / intermediate;
     const int i = static_cast<int>(index - t * intermediate);
-    const float* row = gate_up + t * ld_in;
+    float* row = gate_up + t * ld_in;
     act[index] = hx_from_float<TOut>(hx_silu(row[i]) * row[intermediate + i]);
+    if (zero_input) {      // the buffer is a split-K accumulator: leave it clear for its next use
+      row[i] = 0.0f;
+      row[intermediate + i] = 0.0f;
+    }
   }
 }
 
-HX_API int hx_swiglu(const float* gate_up, void* act, int out_dtype, int tokens, int intermediate,
-                     int ld_in, cudaStream_t stream) {
+HX_API int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int intermediate,
+                     int ld_in, int zero_input, cudaStream_t stream) {
   HX_REQUIRE(tokens >= 0 && intermediate > 0 && ld_in >= 2 * intermediate, "hx_swiglu: bad sizes");
   if (tokens == 0) return HX_OK;
   const size_t total = static_cast<size_t>(tokens) * intermediate;
@@ -141,10 +145,10 @@ HX_API int hx_swiglu(const float* gate_up, void* act, int out_dtype, int tokens,
   const int blocks = static_cast<int>(total / threads + 1 < 148 * 16 ? total / threads + 1 : 148 * 16);
   if (out_dtype == HX_F32) {
     swiglu_kernel<float><<<blocks, threads, 0, stream>>>(gate_up, static_cast<float*>(act), tokens,
-                                                         intermediate, ld_in);
+                                                         intermediate, ld_in, zero_input);
   } else if (out_dtype == HX_BF16) {
     swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-        gate_up, static_cast<__nv_bfloat16*>(act), tokens, intermediate, ld_in);
+        gate_up, static_cast<__nv_bfloat16*>(act), tokens, intermediate, ld_in, zero_input);
   } else {
     HX_REQUIRE(false, "hx_swiglu: unknown dtype %d", out_dtype);
   }
@@ -176,10 +180,15 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
                                    const float* __restrict__ cos_table,
                                    const float* __restrict__ sin_table, int table_positions,
                                    int heads, int kv_heads, int head_dim, int rotary_dim,
-                                   int pairing, int page_size, int num_pages, int* status) {
+                                   int pairing, int page_size, int num_pages, int* status,
+                                   float* __restrict__ accum, int ld_accum) {
   const int token = blockIdx.x;
   const int position = positions[token];
   T* row = qkv + static_cast<size_t>(token) * ld;
+  // When the projection was summed by split-K into a float32 accumulator, the values are
+  // taken from there, rounded to the storage type exactly as the projection's own store
+  // would have rounded them, and the accumulator is cleared for its next use.
+  float* accum_row = accum != nullptr ? accum + static_cast<size_t>(token) * ld_accum : nullptr;
   const int half = rotary_dim / 2;
   const int table_position = position < table_positions ? position : table_positions - 1;
   const float* cos_row = cos_table + static_cast<size_t>(table_position) * half;
@@ -225,8 +234,17 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
           i1 = i0 + 1;
           rotate = false;
         }
-        float a = hx_to_float<T>(vec[i0]);
-        float b = hx_to_float<T>(vec[i1]);
+        float a, b;
+        if (accum_row != nullptr) {
+          float* source = accum_row + static_cast<size_t>(head) * head_dim;
+          a = hx_to_float<T>(hx_from_float<T>(source[i0]));
+          b = hx_to_float<T>(hx_from_float<T>(source[i1]));
+          source[i0] = 0.0f;
+          source[i1] = 0.0f;
+        } else {
+          a = hx_to_float<T>(vec[i0]);
+          b = hx_to_float<T>(vec[i1]);
+        }
         if (rotate) {
           const float c = cos_row[pair];
           const float s = sin_row[pair];
@@ -248,11 +266,23 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
           dst[i1] = tb;
         }
       }
-    } else if (page >= 0) {
+    } else {
       const int kv_head = head - heads - kv_heads;
-      T* dst = v_cache +
-               ((static_cast<size_t>(page) * kv_heads + kv_head) * page_size + slot) * head_dim;
-      for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = vec[d];
+      T* dst = page >= 0 ? v_cache + ((static_cast<size_t>(page) * kv_heads + kv_head) * page_size +
+                                      slot) * head_dim
+                         : nullptr;
+      float* source = accum_row != nullptr ? accum_row + static_cast<size_t>(head) * head_dim
+                                           : nullptr;
+      for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        T value;
+        if (source != nullptr) {
+          value = hx_from_float<T>(source[d]);
+          source[d] = 0.0f;
+        } else {
+          value = vec[d];
+        }
+        if (dst != nullptr) dst[d] = value;
+      }
     }
   }
 }
@@ -263,7 +293,7 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
                           int write_cache, const float* cos_table, const float* sin_table,
                           int table_positions, int tokens, int heads, int kv_heads, int head_dim,
                           int rotary_dim, int pairing, int page_size, int num_pages, int* status,
-                          cudaStream_t stream) {
+                          float* accum, int ld_accum, cudaStream_t stream) {
   HX_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0, "hx_rope_append: bad sizes");
   HX_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "hx_rope_append: head_dim %d must be even", head_dim);
   HX_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
@@ -274,6 +304,8 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
   HX_REQUIRE(!write_cache || (page_size > 0 && num_pages > 0 && k_cache && v_cache),
              "hx_rope_append: cache arguments missing");
   HX_REQUIRE(rotary_dim == 0 || table_positions > 0, "hx_rope_append: empty rotary table");
+  HX_REQUIRE(accum == nullptr || ld_accum >= (heads + 2 * kv_heads) * head_dim,
+             "hx_rope_append: accumulator stride too small");
   if (tokens == 0) return HX_OK;
   const int threads = head_dim / 2 >= 64 ? 64 : 32;
   const dim3 grid(tokens, (heads + 2 * kv_heads + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
@@ -283,13 +315,14 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
         static_cast<float*>(qkv), ld, positions, token_request, request_table_row, block_tables,
         table_stride, static_cast<float*>(k_cache), static_cast<float*>(v_cache), write_cache,
         cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing,
-        page_size, num_pages, status);
+        page_size, num_pages, status, accum, ld_accum);
   } else if (dtype == HX_BF16) {
     rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         static_cast<__nv_bfloat16*>(qkv), ld, positions, token_request, request_table_row,
         block_tables, table_stride, static_cast<__nv_bfloat16*>(k_cache),
         static_cast<__nv_bfloat16*>(v_cache), write_cache, cos_table, sin_table, table_positions,
-        heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status);
+        heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status, accum,
+        ld_accum);
   } else {
     HX_REQUIRE(false, "hx_rope_append: unknown dtype %d", dtype);
   }

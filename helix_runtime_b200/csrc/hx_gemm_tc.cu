@@ -163,7 +163,9 @@ struct TileConfig {
   static constexpr int kWeightBytes = BM * BK * 2 * (DUAL ? 2 : 1);
   static constexpr int kTokenBytes = BN * BK * 2;
   static constexpr int kStageBytes = kWeightBytes + kTokenBytes;
-  static constexpr int kBudget = 200 * 1024;
+  // Small token tiles are the weight-streaming (decoding) case: two CTAs share an SM so that
+  // one CTA's pipeline fill and epilogue overlap the other's loads.  Large tiles take the SM.
+  static constexpr int kBudget = (BN <= 64 && !DUAL) ? 100 * 1024 : 200 * 1024;
   static constexpr int kStagesRaw = kBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
@@ -187,7 +189,7 @@ struct GemmArgs {
 };
 
 template <int BN, int EPI>
-__global__ __launch_bounds__(THREADS, 1) void gemm_tc_kernel(
+__global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     const GemmArgs args) {
   constexpr bool DUAL = EPI == EPI_SWIGLU;

@@ -196,6 +196,7 @@ class StepFunction:
 
     def fail(self, entries: Sequence[StepEntry]) -> None:
         """The step failed: give back what was reserved for it; no length moves."""
+        self.workspace.clear_accumulators()
         for entry in entries:
             if self.cache.has(entry.request):
                 self.cache.rollback(entry.request)

@@ -46,11 +46,11 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_abi_version.restype = _c_int
     library.hx_embed.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
     library.hx_rmsnorm.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_float, _c_ptr]
-    library.hx_swiglu.argtypes = [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_swiglu.argtypes = [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
     library.hx_rope_append.argtypes = [
         _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
         _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-        _c_ptr, _c_ptr]
+        _c_ptr, _c_ptr, _c_int, _c_ptr]
     library.hx_gemm_simt.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int,
                                      _c_int, _c_int, _c_int, _c_ptr]
     library.hx_gemm_tc.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_int,
@@ -157,13 +157,14 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
                             _ptr(rows), n_rows, hidden, float(eps), _stream()))
 
 
-def swiglu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
-    """act[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up float32, act compute dtype."""
+def swiglu(gate_up: torch.Tensor, act: torch.Tensor, zero_input: bool = False) -> None:
+    """act[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up float32, act compute dtype.
+    ``zero_input`` clears what was read (gate_up is a split-K accumulator)."""
     tokens, intermediate = act.shape
     _need(gate_up, torch.float32, "gate_up")
     assert act.is_contiguous()
     _check(lib().hx_swiglu(gate_up.data_ptr(), act.data_ptr(), dtype_code(act.dtype), tokens,
-                           intermediate, gate_up.stride(0), _stream()))
+                           intermediate, gate_up.stride(0), 1 if zero_input else 0, _stream()))
 
 
 def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_request: torch.Tensor,
@@ -171,15 +172,19 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_request: torch
                 k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
                 cos_table: torch.Tensor, sin_table: torch.Tensor, tokens: int, heads: int,
                 kv_heads: int, head_dim: int, rotary_dim: int, pairing: int, page_size: int,
-                num_pages: int, status: torch.Tensor) -> None:
-    """Rotate q and k of ``qkv[:tokens]`` in place and write k, v into their pages."""
+                num_pages: int, status: torch.Tensor,
+                accum: Optional[torch.Tensor] = None) -> None:
+    """Rotate q and k of ``qkv[:tokens]`` in place and write k, v into their pages.  With
+    ``accum`` (float32 ``[rows, width]``) the projection is read from there instead, rounded
+    to the storage type, and ``accum`` is cleared."""
     write = k_cache is not None
     _check(lib().hx_rope_append(
         qkv.data_ptr(), dtype_code(qkv.dtype), qkv.stride(0), positions.data_ptr(),
         token_request.data_ptr(), request_table_row.data_ptr(), block_tables.data_ptr(),
         block_tables.stride(0), _ptr(k_cache), _ptr(v_cache), 1 if write else 0,
         cos_table.data_ptr(), sin_table.data_ptr(), cos_table.shape[0], tokens, heads, kv_heads,
-        head_dim, rotary_dim, pairing, page_size, num_pages, _ptr(status), _stream()))
+        head_dim, rotary_dim, pairing, page_size, num_pages, _ptr(status), _ptr(accum),
+        0 if accum is None else accum.stride(0), _stream()))
 
 
 def gemm_tc_supports(tokens: int, features: int, depth: int, ldx: int, ldw: int) -> bool:

@@ -25,7 +25,8 @@ from ..config.spec import PartSpec
 from ..ops import library as ops
 from ..weights.loader import TensorRequest
 from .base import LayerCache, Mixer, StepContext, build_part, register_part
-from .linear import project
+from .linear import (STREAMING_MAX_TOKENS, is_weight_stream, project,
+                     project_into_accumulator)
 
 
 TENSOR_CORE_MIN_QUERY = 16
@@ -110,8 +111,16 @@ class PagedAttention(Mixer):
         n = ctx.n_tokens
         qkv = ctx.workspace.get("attention.qkv", (ctx.capacity, self.qkv_size), ctx.dtype)
         context = ctx.workspace.get("attention.context", (ctx.capacity, self.q_size), ctx.dtype)
-        project(x, self.w_qkv, qkv, n, ops.EPI_STORE, ctx.status)
-        self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
+        if is_weight_stream(x, self.w_qkv, n):
+            # few tokens: split-K into a float32 accumulator that the rotary kernel reads,
+            # rounds as the product's store would have, and clears
+            accumulator = ctx.workspace.accumulator("attention.qkv",
+                                                    (STREAMING_MAX_TOKENS, self.qkv_size))
+            project_into_accumulator(x, self.w_qkv, accumulator, n, ctx.status)
+            self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads, accum=accumulator)
+        else:
+            project(x, self.w_qkv, qkv, n, ops.EPI_STORE, ctx.status)
+            self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
 
         window = cache.window or 0
         # prompt portions of at least TENSOR_CORE_MIN_QUERY tokens go to the tensor-core

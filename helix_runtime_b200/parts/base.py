@@ -43,6 +43,7 @@ class Workspace:
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self._buffers: Dict[str, torch.Tensor] = {}
+        self._accumulators: Dict[str, torch.Tensor] = {}
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         buffer = self._buffers.get(name)
@@ -50,6 +51,20 @@ class Workspace:
             buffer = torch.empty(shape, dtype=dtype, device=self.device)
             self._buffers[name] = buffer
         return buffer
+
+    def accumulator(self, name: str, shape: Tuple[int, ...]) -> torch.Tensor:
+        """A float32 buffer that is all zero whenever nobody is using it: kernels that sum
+        into it (split-K products) are followed by a kernel that reads and clears it."""
+        buffer = self._accumulators.get(name)
+        if buffer is None or tuple(buffer.shape) != tuple(shape):
+            buffer = torch.zeros(shape, dtype=torch.float32, device=self.device)
+            self._accumulators[name] = buffer
+        return buffer
+
+    def clear_accumulators(self) -> None:
+        """After a step that failed half-way: restore the all-zero state."""
+        for buffer in self._accumulators.values():
+            buffer.zero_()
 
     def at_least(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """A flat buffer of at least ``numel`` elements; it only ever grows."""
@@ -60,7 +75,8 @@ class Workspace:
         return buffer
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self._buffers.values())
+        return sum(t.numel() * t.element_size()
+                   for t in (*self._buffers.values(), *self._accumulators.values()))
 
 
 @dataclasses.dataclass

@@ -45,11 +45,8 @@ class GatedMlp(FeedForward):
     def forward(self, ctx: StepContext, x: torch.Tensor, residual: torch.Tensor) -> None:
         n = ctx.n_tokens
         act = ctx.workspace.get("mlp.act", (ctx.capacity, self.intermediate), ctx.dtype)
-        project_swiglu(
-            x, self.w_gate_up, self.intermediate, act,
-            lambda: ctx.workspace.get("mlp.gate_up", (ctx.capacity, 2 * self.intermediate),
-                                      torch.float32),
-            n, ctx.status)
+        project_swiglu(x, self.w_gate_up, self.intermediate, act, ctx.workspace, ctx.capacity, n,
+                       ctx.status)
         project(act, self.w_down, residual, n, ops.EPI_ADD_F32, ctx.status)
 
 

@@ -49,15 +49,16 @@ class RotaryEncoding(PositionEncoding):
         self.sin = torch.sin(angle).to(torch.float32).to(device).contiguous()
 
     def apply(self, ctx: StepContext, cache: LayerCache, qkv: torch.Tensor, heads: int,
-              kv_heads: int) -> None:
+              kv_heads: int, accum: Optional[torch.Tensor] = None) -> None:
         """Encode queries and keys of ``qkv[:n_tokens]`` in place; write keys and values into
-        the pages when the entry owns its cache."""
+        the pages when the entry owns its cache.  With ``accum`` the projection is taken from
+        that float32 accumulator (and the accumulator cleared) instead of from ``qkv``."""
         write = cache.owns and cache.keys is not None
         ops.rope_append(qkv, ctx.positions, ctx.token_request, ctx.request_slot,
                         cache.block_tables, cache.keys if write else None,
                         cache.values if write else None, self.cos, self.sin, ctx.n_tokens, heads,
                         kv_heads, self.head_dim, self.rotary_dim, PAIRINGS[self.pairing],
-                        cache.page_size, cache.num_pages, ctx.status)
+                        cache.page_size, cache.num_pages, ctx.status, accum=accum)
 
 
 register_part("position", "rotary", RotaryEncoding)

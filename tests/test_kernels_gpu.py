@@ -95,6 +95,17 @@ def test_swiglu(dtype):
     assert_close(host(act), expected, "swiglu", **tol)
 
 
+def test_swiglu_clears_a_split_k_accumulator():
+    rng = np.random.default_rng(21)
+    gate_up = (rng.normal(size=(5, 2 * 88)) * 3.0).astype(np.float32)
+    buffer = dev(gate_up)
+    act = torch.empty((5, 88), dtype=torch.bfloat16, device=DEVICE)
+    ops.swiglu(buffer, act, zero_input=True)
+    assert_close(host(act), plain.swiglu(gate_up[:, :88], gate_up[:, 88:]), "swiglu",
+                 atol=1e-2, rtol=8e-3)
+    assert float(buffer.abs().sum()) == 0.0
+
+
 # -------------------------------------------------------------- matrix products
 
 def product_reference(x, w):
@@ -246,6 +257,39 @@ def test_rope_and_cache_append(dtype, heads, kv_heads, head_dim, rotary_dim, pai
     # nothing else was touched
     untouched = ~written[:, None, :].repeat(kv_heads, axis=1)
     assert np.isnan(keys[untouched]).all() and np.isnan(values[untouched]).all()
+
+
+def test_rope_reads_and_clears_a_split_k_accumulator():
+    """The projection may arrive as float32 sums: the kernel must round them to bfloat16 as
+    the projection's store would have, rotate, write the cache, and leave zeros behind."""
+    rng = np.random.default_rng(22)
+    heads, kv_heads, head_dim, page_size, num_pages = 3, 3, 32, 8, 4
+    tokens = 4
+    width = (heads + 2 * kv_heads) * head_dim
+    sums = rng.normal(size=(8, width)).astype(np.float32)
+    positions = np.array([5, 6, 7, 8], dtype=np.int32)
+    tables = np.array([[2, 0, -1, -1]], dtype=np.int32)
+    angle = np.arange(32)[:, None] * np.power(10000.0, -2.0 * np.arange(16) / 32)[None, :]
+    cos, sin = dev(np.cos(angle)), dev(np.sin(angle))
+    outputs = []
+    for use_accumulator in (False, True):
+        k_cache = torch.zeros((num_pages, kv_heads, page_size, head_dim), dtype=torch.bfloat16,
+                              device=DEVICE)
+        v_cache = torch.zeros_like(k_cache)
+        qkv = dev(sums[:tokens], torch.bfloat16) if not use_accumulator else \
+            torch.full((tokens, width), float("nan"), dtype=torch.bfloat16, device=DEVICE)
+        accum = dev(sums) if use_accumulator else None
+        ops.rope_append(qkv, dev(positions, torch.int32), dev(np.zeros(4), torch.int32),
+                        dev(np.zeros(1), torch.int32), dev(tables, torch.int32), k_cache, v_cache,
+                        cos, sin, tokens, heads, kv_heads, head_dim, head_dim, 0, page_size,
+                        num_pages, status_word(), accum=accum)
+        outputs.append((host(qkv)[:, :heads * head_dim], host(k_cache), host(v_cache)))
+        if use_accumulator:
+            cleared = host(accum)
+            assert np.abs(cleared[:tokens]).sum() == 0.0
+            np.testing.assert_array_equal(cleared[tokens:], sums[tokens:])   # other rows untouched
+    for direct, through_accumulator in zip(*outputs):
+        np.testing.assert_array_equal(direct, through_accumulator)
 
 
 # ------------------------------------------------------------------- attention
