@@ -116,6 +116,7 @@ __device__ __forceinline__ void key_range(const AttentionArgs& a, int token, int
 template <typename T, int DPL, int VEC, int HD>
 __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(AttentionArgs a) {
   __shared__ float q_shared[WARPS_PER_BLOCK][MAX_HEAD_DIM];
+  hx_pdl_prologue();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * WARPS_PER_BLOCK + warp;
@@ -261,6 +262,7 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
 // Combine the splits of one (token, head) in ascending order.
 template <typename T>
 __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void attention_merge_kernel(AttentionArgs a) {
+  hx_pdl_prologue();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const long long token_head = static_cast<long long>(blockIdx.x) * WARPS_PER_BLOCK + warp;
@@ -300,7 +302,7 @@ template <typename T, int DPL, int VEC, int HD = 0>
 void launch_main(const AttentionArgs& a, cudaStream_t stream) {
   const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
   const int blocks = static_cast<int>((items + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
-  paged_attention_kernel<T, DPL, VEC, HD><<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>(a);
+  hx_launch(paged_attention_kernel<T, DPL, VEC, HD>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
 }
 
 template <typename T, int DPL>
@@ -341,7 +343,7 @@ int dispatch(const AttentionArgs& a, cudaStream_t stream) {
   if (a.max_splits > 1) {
     const long long pairs = static_cast<long long>(a.tokens) * a.heads;
     const int blocks = static_cast<int>((pairs + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
-    attention_merge_kernel<T><<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>(a);
+    hx_launch(attention_merge_kernel<T>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
     hx_count_launches(1);
   }
   return HX_OK;

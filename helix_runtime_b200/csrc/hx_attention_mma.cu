@@ -108,6 +108,7 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* q_tile = smem;                          // [64][D]
   uint8_t* kv_tiles = smem + BLOCK_M * D * 2;      // 2 stages x (K tile, V tile)
+  hx_pdl_prologue();
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -353,7 +354,7 @@ int launch(const PrefillArgs& a, int tiles, cudaStream_t stream) {
     configured = true;
   }
   const dim3 grid(tiles, a.heads);
-  prefill_attention_kernel<D><<<grid, THREADS, kSmem, stream>>>(a);
+  hx_launch(prefill_attention_kernel<D>, grid, THREADS, kSmem, stream, a);
   return HX_OK;
 }
 

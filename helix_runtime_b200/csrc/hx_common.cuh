@@ -53,6 +53,44 @@ void hx_count_launches(int kernels);
     }                                                                      \
   } while (0)
 
+// ---------------------------------------------------------- programmatic dependent launch
+//
+// A step is a chain of a few hundred short kernels on one stream.  Every kernel is launched
+// with programmatic stream serialization: it may be scheduled while its predecessor is still
+// running, and calls hx_pdl_wait() before it touches anything a predecessor wrote.  What does
+// not depend on the predecessor (the weight tiles of a matrix product) is fetched before the
+// wait, so the memory system stays busy across kernel boundaries.  hx_pdl_trigger() lets the
+// NEXT kernel be scheduled; the wait of that kernel still holds it until this one has
+// completed and its writes are visible.
+__device__ __forceinline__ void hx_pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void hx_pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void hx_pdl_prologue() {
+  hx_pdl_trigger();
+  hx_pdl_wait();
+}
+
+bool hx_pdl_enabled();
+
+template <typename... KernelArgs, typename... Args>
+inline void hx_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared_bytes,
+                      cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = hx_pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 template <typename T> struct HxTraits;
 template <> struct HxTraits<float> {
   static __device__ __forceinline__ float load(const float* p) { return *p; }

@@ -21,6 +21,14 @@ void hx_set_error(const char* format, ...) {
 
 HX_API const char* hx_last_error() { return g_hx_error; }
 
+static std::atomic<int> g_hx_pdl{1};
+
+bool hx_pdl_enabled() { return g_hx_pdl.load(std::memory_order_relaxed) != 0; }
+
+// 0 launches every kernel fully serialised (for debugging); 1, the default, lets a kernel be
+// scheduled while its predecessor drains.
+HX_API void hx_set_dependent_launch(int enabled) { g_hx_pdl.store(enabled ? 1 : 0); }
+
 static std::atomic<long long> g_hx_launches{0};
 
 void hx_count_launches(int kernels) { g_hx_launches.fetch_add(kernels, std::memory_order_relaxed); }
@@ -39,6 +47,7 @@ HX_API int hx_abi_version() { return 3; }
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int hidden, int vocab, int* status) {
+  hx_pdl_prologue();
   const int token = blockIdx.x;
   const int id = ids[token];
   float* row_out = out + static_cast<size_t>(token) * hidden;
@@ -57,11 +66,9 @@ HX_API int hx_embed(const void* table, int dtype, const int* ids, float* out, in
   if (tokens == 0) return HX_OK;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == HX_F32) {
-    embed_kernel<float><<<tokens, threads, 0, stream>>>(static_cast<const float*>(table), ids, out,
-                                                        hidden, vocab, status);
+    hx_launch(embed_kernel<float>, tokens, threads, 0, stream, static_cast<const float*>(table), ids, out, hidden, vocab, status);
   } else if (dtype == HX_BF16) {
-    embed_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab, status);
+    hx_launch(embed_kernel<__nv_bfloat16>, tokens, threads, 0, stream,  static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab, status);
   } else {
     HX_REQUIRE(false, "hx_embed: unknown dtype %d", dtype);
   }
@@ -79,6 +86,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                TOut* __restrict__ y, const int* __restrict__ rows, int hidden,
                                float eps) {
   __shared__ float scratch[32];
+  hx_pdl_prologue();
   const int out_row = blockIdx.x;
   const int in_row = rows != nullptr ? rows[out_row] : out_row;
   const float* xr = x + static_cast<size_t>(in_row) * hidden;
@@ -101,11 +109,9 @@ HX_API int hx_rmsnorm(const float* x, const float* weight, void* y, int out_dtyp
   if (n_rows == 0) return HX_OK;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (out_dtype == HX_F32) {
-    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, weight, static_cast<float*>(y), rows,
-                                                          hidden, eps);
+    hx_launch(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, weight, static_cast<float*>(y), rows, hidden, eps);
   } else if (out_dtype == HX_BF16) {
-    rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
-        x, weight, static_cast<__nv_bfloat16*>(y), rows, hidden, eps);
+    hx_launch(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream,  x, weight, static_cast<__nv_bfloat16*>(y), rows, hidden, eps);
   } else {
     HX_REQUIRE(false, "hx_rmsnorm: unknown dtype %d", out_dtype);
   }
@@ -122,6 +128,7 @@ HX_API int hx_rmsnorm(const float* x, const float* weight, void* y, int out_dtyp
 template <typename TOut>
 __global__ void swiglu_kernel(float* __restrict__ gate_up, TOut* __restrict__ act, int tokens,
                               int intermediate, int ld_in, int zero_input) {
+  hx_pdl_prologue();
   const size_t total = static_cast<size_t>(tokens) * intermediate;
   for (size_t index = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; index < total;
        index += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -144,11 +151,9 @@ HX_API int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int i
   const int threads = 256;
   const int blocks = static_cast<int>(total / threads + 1 < 148 * 16 ? total / threads + 1 : 148 * 16);
   if (out_dtype == HX_F32) {
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>(gate_up, static_cast<float*>(act), tokens,
-                                                         intermediate, ld_in, zero_input);
+    hx_launch(swiglu_kernel<float>, blocks, threads, 0, stream, gate_up, static_cast<float*>(act), tokens, intermediate, ld_in, zero_input);
   } else if (out_dtype == HX_BF16) {
-    swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-        gate_up, static_cast<__nv_bfloat16*>(act), tokens, intermediate, ld_in, zero_input);
+    hx_launch(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream,  gate_up, static_cast<__nv_bfloat16*>(act), tokens, intermediate, ld_in, zero_input);
   } else {
     HX_REQUIRE(false, "hx_swiglu: unknown dtype %d", out_dtype);
   }
@@ -182,6 +187,7 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
                                    int heads, int kv_heads, int head_dim, int rotary_dim,
                                    int pairing, int page_size, int num_pages, int* status,
                                    float* __restrict__ accum, int ld_accum) {
+  hx_pdl_prologue();
   const int token = blockIdx.x;
   const int position = positions[token];
   T* row = qkv + static_cast<size_t>(token) * ld;
@@ -311,18 +317,9 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
   const dim3 grid(tokens, (heads + 2 * kv_heads + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
   HX_REQUIRE(grid.y <= 65535, "hx_rope_append: too many heads");
   if (dtype == HX_F32) {
-    rope_append_kernel<float><<<grid, threads, 0, stream>>>(
-        static_cast<float*>(qkv), ld, positions, token_request, request_table_row, block_tables,
-        table_stride, static_cast<float*>(k_cache), static_cast<float*>(v_cache), write_cache,
-        cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing,
-        page_size, num_pages, status, accum, ld_accum);
+    hx_launch(rope_append_kernel<float>, grid, threads, 0, stream,  static_cast<float*>(qkv), ld, positions, token_request, request_table_row, block_tables, table_stride, static_cast<float*>(k_cache), static_cast<float*>(v_cache), write_cache, cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status, accum, ld_accum);
   } else if (dtype == HX_BF16) {
-    rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(qkv), ld, positions, token_request, request_table_row,
-        block_tables, table_stride, static_cast<__nv_bfloat16*>(k_cache),
-        static_cast<__nv_bfloat16*>(v_cache), write_cache, cos_table, sin_table, table_positions,
-        heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status, accum,
-        ld_accum);
+    hx_launch(rope_append_kernel<__nv_bfloat16>, grid, threads, 0, stream,  static_cast<__nv_bfloat16*>(qkv), ld, positions, token_request, request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), write_cache, cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status, accum, ld_accum);
   } else {
     HX_REQUIRE(false, "hx_rope_append: unknown dtype %d", dtype);
   }
@@ -336,6 +333,7 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
 // next step's input and move every position on by one, without a round trip to the host.
 __global__ void advance_decode_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
                                       const int* __restrict__ sampled, int count) {
+  hx_pdl_prologue();
   const int index = blockIdx.x * blockDim.x + threadIdx.x;
   if (index < count) {
     token_ids[index] = sampled[index];
@@ -347,8 +345,7 @@ HX_API int hx_advance_decode(int* token_ids, int* positions, const int* sampled,
                              cudaStream_t stream) {
   HX_REQUIRE(count >= 0, "hx_advance_decode: bad count");
   if (count == 0) return HX_OK;
-  advance_decode_kernel<<<(count + 127) / 128, 128, 0, stream>>>(token_ids, positions, sampled,
-                                                                 count);
+  hx_launch(advance_decode_kernel, (count + 127) / 128, 128, 0, stream, token_ids, positions, sampled, count);
   HX_CHECK_LAUNCH("hx_advance_decode");
   return HX_OK;
 }

@@ -24,6 +24,7 @@ __global__ __launch_bounds__(256) void gemm_simt_kernel(const T* __restrict__ x,
                                                         int features, int depth) {
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
+  hx_pdl_prologue();
   const int tile_t = blockIdx.y * BM;
   const int tile_f = blockIdx.x * BN;
   const int tx = threadIdx.x & 15;   // feature group
@@ -92,16 +93,13 @@ int launch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, i
   const T* wp = static_cast<const T*>(w);
   switch (epilogue) {
     case EPI_STORE:
-      gemm_simt_kernel<T, EPI_STORE><<<grid, 256, 0, stream>>>(xp, ldx, wp, ldw, out, ldo, tokens,
-                                                               features, depth);
+      hx_launch(gemm_simt_kernel<T, EPI_STORE>, grid, 256, 0, stream, xp, ldx, wp, ldw, out, ldo, tokens, features, depth);
       break;
     case EPI_STORE_F32:
-      gemm_simt_kernel<T, EPI_STORE_F32><<<grid, 256, 0, stream>>>(xp, ldx, wp, ldw, out, ldo,
-                                                                   tokens, features, depth);
+      hx_launch(gemm_simt_kernel<T, EPI_STORE_F32>, grid, 256, 0, stream, xp, ldx, wp, ldw, out, ldo, tokens, features, depth);
       break;
     case EPI_ADD_F32:
-      gemm_simt_kernel<T, EPI_ADD_F32><<<grid, 256, 0, stream>>>(xp, ldx, wp, ldw, out, ldo, tokens,
-                                                                 features, depth);
+      hx_launch(gemm_simt_kernel<T, EPI_ADD_F32>, grid, 256, 0, stream, xp, ldx, wp, ldw, out, ldo, tokens, features, depth);
       break;
     default:
       hx_set_error("hx_gemm_simt: unknown epilogue %d", epilogue);

@@ -196,6 +196,7 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
   using Config = TileConfig<BN, DUAL>;
   constexpr int STAGES = Config::kStages;
 
+  hx_pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -232,7 +233,25 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
     if (warp == 0) {
       // ------------------------------------------------------------ TMA producer
       if (lane == 0) {
-        for (int i = 0; i < n_k_blocks; ++i) {
+        // The weight tiles do not depend on the kernel before this one: the first STAGES of
+        // them are requested at once, before the dependency wait, so that weights stream
+        // across the kernel boundary.  The token tiles follow after the wait.
+        const int eager = n_k_blocks < STAGES ? n_k_blocks : STAGES;
+        for (int i = 0; i < eager; ++i) {
+          uint8_t* stage = smem + i * Config::kStageBytes;
+          mbar_expect_tx(&full_bar[i], Config::kStageBytes);
+          const int k = (kb_begin + i) * BK;
+          tma_load_2d(stage, &map_w, &full_bar[i], k, feature0);
+          if (DUAL)
+            tma_load_2d(stage + BM * BK * 2, &map_w, &full_bar[i], k, args.up_row_offset + feature0);
+        }
+        hx_pdl_wait();
+        for (int i = 0; i < eager; ++i) {
+          uint8_t* stage = smem + i * Config::kStageBytes;
+          tma_load_2d(stage + Config::kWeightBytes, &map_x, &full_bar[i], (kb_begin + i) * BK,
+                      token0);
+        }
+        for (int i = eager; i < n_k_blocks; ++i) {
           const int s = i % STAGES;
           const uint32_t round = static_cast<uint32_t>(i / STAGES);
           if (!mbar_wait(&empty_bar[s], (round & 1u) ^ 1u)) {
@@ -280,6 +299,7 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
       }
     } else {
       // ---------------------------------------------------------------- epilogue
+      hx_pdl_wait();                    // the output may be something the last kernel read
       const int quarter = warp & 3;     // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
       const int feature = feature0 + quarter * 32 + lane;
       bool ok = true;
@@ -433,7 +453,7 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmArgs& a
     }
     configured = true;
   }
-  gemm_tc_kernel<BN, EPI><<<grid, THREADS, Config::kSmemBytes, stream>>>(map_w, map_x, args);
+  hx_launch(gemm_tc_kernel<BN, EPI>, grid, THREADS, Config::kSmemBytes, stream, map_w, map_x, args);
   return HX_OK;
 }
 

@@ -19,6 +19,7 @@ __global__ __launch_bounds__(THREADS) void argmax_kernel(const float* __restrict
   __shared__ float best_value[THREADS];
   __shared__ int best_index[THREADS];
   __shared__ int bad;
+  hx_pdl_prologue();
   const float* row = logits + static_cast<size_t>(blockIdx.x) * ld;
   if (threadIdx.x == 0) bad = 0;
   __syncthreads();
@@ -72,6 +73,7 @@ __global__ __launch_bounds__(THREADS) void sample_kernel(const float* __restrict
   __shared__ int best_index[THREADS];
   __shared__ int bad;
   __shared__ int chosen;
+  hx_pdl_prologue();
   const float* row = logits + static_cast<size_t>(blockIdx.x) * ld;
   const float temp = temperature[blockIdx.x];
   if (threadIdx.x == 0) {
@@ -170,7 +172,7 @@ HX_API int hx_argmax(const float* logits, int ld, int rows, int vocab, int* toke
                      cudaStream_t stream) {
   HX_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "hx_argmax: bad sizes");
   if (rows == 0) return HX_OK;
-  argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, vocab, tokens, status);
+  hx_launch(argmax_kernel, rows, THREADS, 0, stream, logits, ld, vocab, tokens, status);
   HX_CHECK_LAUNCH("hx_argmax");
   return HX_OK;
 }
@@ -180,8 +182,7 @@ HX_API int hx_sample(const float* logits, int ld, int rows, int vocab, const flo
   HX_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "hx_sample: bad sizes");
   HX_REQUIRE(temperature != nullptr && uniform != nullptr, "hx_sample: missing arguments");
   if (rows == 0) return HX_OK;
-  sample_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, vocab, temperature, uniform, tokens,
-                                              status);
+  hx_launch(sample_kernel, rows, THREADS, 0, stream, logits, ld, vocab, temperature, uniform, tokens, status);
   HX_CHECK_LAUNCH("hx_sample");
   return HX_OK;
 }

@@ -71,6 +71,8 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_paged_attention_scratch_floats.argtypes = [_c_int] * 4
     library.hx_argmax.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]
     library.hx_sample.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr]
+    library.hx_set_dependent_launch.argtypes = [_c_int]
+    library.hx_set_dependent_launch.restype = None
     library.hx_launch_count.restype = ctypes.c_longlong
     library.hx_launch_count.argtypes = []
     library.hx_advance_decode.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]
@@ -286,3 +288,8 @@ def advance_decode(token_ids: torch.Tensor, positions: torch.Tensor, sampled: to
 def launch_count() -> int:
     """Kernels this library has launched (or recorded into a graph) since it was loaded."""
     return int(lib().hx_launch_count())
+
+
+def set_dependent_launch(enabled: bool) -> None:
+    """Switch programmatic dependent launch of the kernels off (debugging) or on (default)."""
+    lib().hx_set_dependent_launch(1 if enabled else 0)
