@@ -9,9 +9,19 @@
 // walks the keys of one (token, head, key split) with an online softmax and never
 // stores a score.
 //
+// One chunk of 32 keys: lane j owns key j for the score (a whole key row per lane) and
+// a slice of the head dimension for the weighted value sum (lane-per-dimension).  For the
+// usual head sizes the loads of the key row AND of the 32 value slices are all issued
+// before anything is computed, so a chunk costs one trip to memory.
+//
+// Key splits.  A long context is cut into splits of `split_keys` keys, one warp each.
+// Every split writes its unnormalised sum, maximum and weight to scratch; the warp that
+// finishes LAST for a (token, head) combines them in ascending order (a counter per
+// (token, head) in scratch tells who is last, and is left at zero again).
+//
 // Exactness: dot products, the running maximum, exp, the running sum and the
 // weighted value sum are float32.  The order of every sum is a function of the
-// token's own position only (32-key chunks and `split_keys`-wide splits anchored at
+// token's own position and of split_keys only (32-key chunks and splits anchored at
 // lo, merged in ascending order), so a token's result does not depend on how the
 // batch was cut, what else is in it, or which pages hold the keys.
 #include "hx_common.cuh"
@@ -68,6 +78,20 @@ template <> struct VecLoad<__nv_bfloat16, 8> {
   }
 };
 
+// A value slice kept as raw bits until it is used, so that 32 of them fit in registers.
+template <typename T, int DPL> struct RawSlice;
+template <> struct RawSlice<__nv_bfloat16, 2> { using type = uint32_t; };
+template <> struct RawSlice<__nv_bfloat16, 4> { using type = uint2; };
+template <> struct RawSlice<__nv_bfloat16, 8> { using type = uint4; };
+template <> struct RawSlice<float, 2> { using type = float2; };
+template <> struct RawSlice<float, 4> { using type = float4; };
+template <> struct RawSlice<float, 8> { using type = float4; };   // never instantiated with HD
+
+template <typename T, int DPL>
+__device__ __forceinline__ void unpack(const typename RawSlice<T, DPL>::type& raw, float (&v)[DPL]) {
+  VecLoad<T, DPL>::load(reinterpret_cast<const T*>(&raw), v);
+}
+
 struct AttentionArgs {
   const void* q;
   int ldq;
@@ -84,6 +108,7 @@ struct AttentionArgs {
   void* out;
   int ldo;
   float* partial;   // [tokens * heads][max_splits][head_dim + 2], only when max_splits > 1
+  int* arrivals;    // [tokens * heads] counters, zero on entry and on exit
   int tokens;
   int heads;
   int kv_heads;
@@ -109,10 +134,60 @@ __device__ __forceinline__ void key_range(const AttentionArgs& a, int token, int
   lo = a.window > 0 ? max(0, hi - a.window) : 0;
 }
 
+// Combine the splits of one (token, head) in ascending order; run by one warp.
+template <typename T>
+__device__ void merge_splits(const AttentionArgs& a, long long token_head, int token, int head,
+                             int n_splits, int lane) {
+  const int D = a.head_dim;
+  const int stride = D + 2;
+  const float* part = a.partial + static_cast<size_t>(token_head) * a.max_splits * stride;
+  // maxima and weights of the splits, 32 at a time, read past the L1 (other SMs wrote them)
+  float total_max = -INFINITY;
+  for (int base = 0; base < n_splits; base += 32) {
+    const int s = base + lane;
+    float m = s < n_splits ? __ldcg(part + static_cast<size_t>(s) * stride + D) : -INFINITY;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, offset));
+    total_max = fmaxf(total_max, m);
+  }
+  // the total weight, split by split in ascending order
+  float total_sum = 0.0f;
+  for (int base = 0; base < n_splits; base += 32) {
+    const int s = base + lane;
+    float weighted = 0.0f;
+    if (s < n_splits) {
+      const float m = __ldcg(part + static_cast<size_t>(s) * stride + D);
+      const float l = __ldcg(part + static_cast<size_t>(s) * stride + D + 1);
+      weighted = m == -INFINITY ? 0.0f : l * expf(m - total_max);
+    }
+    const int here = min(32, n_splits - base);
+    for (int j = 0; j < here; ++j) total_sum += __shfl_sync(0xffffffffu, weighted, j);
+  }
+  const float inverse = 1.0f / total_sum;
+  T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
+           static_cast<size_t>(head) * D;
+  for (int d = lane; d < D; d += 32) {
+    float value = 0.0f;
+    for (int base = 0; base < n_splits; base += 4) {
+      float m[4], o[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int s = base + u;
+        m[u] = s < n_splits ? __ldcg(part + static_cast<size_t>(s) * stride + D) : -INFINITY;
+        o[u] = s < n_splits ? __ldcg(part + static_cast<size_t>(s) * stride + d) : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        value = fmaf(o[u], m[u] == -INFINITY ? 0.0f : expf(m[u] - total_max), value);
+    }
+    out[d] = hx_from_float<T>(value * inverse);
+  }
+}
+
 // DPL: value coordinates per lane in the value phase (32 * DPL >= head_dim);
 // VEC: elements per load in the key phase; HD: the head size when it is known at compile
-// time (0: read it from the arguments).  With HD known the loads of a key row are unrolled
-// and issued together, which is what lets one warp keep a whole row in flight.
+// time (0: read it from the arguments).
 template <typename T, int DPL, int VEC, int HD>
 __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(AttentionArgs a) {
   __shared__ float q_shared[WARPS_PER_BLOCK][MAX_HEAD_DIM];
@@ -123,9 +198,9 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
   const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
   if (item >= items) return;
   const int split = static_cast<int>(item % a.max_splits);
-  const int token_head = static_cast<int>(item / a.max_splits);
-  const int head = token_head % a.heads;
-  const int token = token_head / a.heads;
+  const long long token_head = item / a.max_splits;
+  const int head = static_cast<int>(token_head % a.heads);
+  const int token = static_cast<int>(token_head / a.heads);
   if (skipped(a, token)) return;
 
   int lo, hi;
@@ -158,7 +233,7 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
   for (int chunk = begin; chunk < end; chunk += 32) {
     const int key = chunk + lane;
     bool valid = key < end;
-    int row = 0;
+    int row = -1;
     if (valid) {
       const int page = table[key / a.page_size];
       if (page < 0 || page >= a.num_pages) {
@@ -168,76 +243,115 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
         row = (page * a.kv_heads + kv_head) * a.page_size + key % a.page_size;
       }
     }
+    const int keys_here = min(32, end - chunk);
     float score = -INFINITY;
-    if (valid) {
-      const T* k = k_cache + static_cast<size_t>(row) * D;
-      float dot = 0.0f;
-      if (HD > 0) {
-        constexpr int kLoads = HD > 0 ? HD / VEC : 1;
-        constexpr int kBatch = kLoads < 16 ? kLoads : 16;     // loads in flight per lane
+
+    if (HD > 0) {
+      // ---- known head size: every load of the chunk goes out before the arithmetic
+      using Raw = typename RawSlice<T, DPL>::type;
+      constexpr int kLoads = HD > 0 ? HD / VEC : 1;
+      float kv[kLoads][VEC];
+      if (valid) {
+        const T* k = k_cache + static_cast<size_t>(row) * D;
 #pragma unroll
-        for (int b = 0; b < kLoads; b += kBatch) {
-          float kv[kBatch][VEC];
+        for (int u = 0; u < kLoads; ++u) VecLoad<T, VEC>::load(k + u * VEC, kv[u]);
+      }
+      Raw values[32];
 #pragma unroll
-          for (int u = 0; u < kBatch; ++u) VecLoad<T, VEC>::load(k + (b + u) * VEC, kv[u]);
-#pragma unroll
-          for (int u = 0; u < kBatch; ++u)
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) dot = fmaf(qs[(b + u) * VEC + i], kv[u][i], dot);
+      for (int j = 0; j < 32; ++j) {
+        const int v_row = __shfl_sync(0xffffffffu, row, j);   // -1: masked or unreadable
+        if (v_row >= 0 && my_dim < D) {
+          values[j] = *reinterpret_cast<const Raw*>(v_cache + static_cast<size_t>(v_row) * D + my_dim);
+        } else {
+          values[j] = Raw{};
         }
-      } else {
+      }
+      if (valid) {
+        float dot = 0.0f;
+#pragma unroll
+        for (int u = 0; u < kLoads; ++u)
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) dot = fmaf(qs[u * VEC + i], kv[u][i], dot);
+        score = dot * a.scale;
+      }
+      float chunk_max = score;
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1)
+        chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, offset));
+      const float new_max = fmaxf(running_max, chunk_max);
+      if (new_max == -INFINITY) continue;   // every key of the chunk unreadable
+      const float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
+      const float probability = valid ? expf(score - new_max) : 0.0f;
+      float chunk_sum = probability;
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1)
+        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, offset);
+      running_sum = running_sum * correction + chunk_sum;
+      running_max = new_max;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) acc[i] *= correction;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float p = __shfl_sync(0xffffffffu, probability, j);
+        float vv[DPL];
+        unpack<T, DPL>(values[j], vv);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p, vv[i], acc[i]);
+      }
+    } else {
+      // ---- any head size
+      if (valid) {
+        const T* k = k_cache + static_cast<size_t>(row) * D;
+        float dot = 0.0f;
         for (int d = 0; d < D; d += VEC) {
           float kv[VEC];
           VecLoad<T, VEC>::load(k + d, kv);
 #pragma unroll
           for (int i = 0; i < VEC; ++i) dot = fmaf(qs[d + i], kv[i], dot);
         }
+        score = dot * a.scale;
       }
-      score = dot * a.scale;
-    }
-    float chunk_max = score;
+      float chunk_max = score;
 #pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1)
-      chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, offset));
-    const float new_max = fmaxf(running_max, chunk_max);
-    // a chunk whose keys are all unreadable leaves the state as it is
-    if (new_max == -INFINITY) continue;
-    const float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
-    const float probability = valid ? expf(score - new_max) : 0.0f;
-    float chunk_sum = probability;
+      for (int offset = 16; offset > 0; offset >>= 1)
+        chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, offset));
+      const float new_max = fmaxf(running_max, chunk_max);
+      if (new_max == -INFINITY) continue;
+      const float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
+      const float probability = valid ? expf(score - new_max) : 0.0f;
+      float chunk_sum = probability;
 #pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1)
-      chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, offset);
-    running_sum = running_sum * correction + chunk_sum;
-    running_max = new_max;
+      for (int offset = 16; offset > 0; offset >>= 1)
+        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, offset);
+      running_sum = running_sum * correction + chunk_sum;
+      running_max = new_max;
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) acc[i] *= correction;
-
-    // values: eight keys at a time, their loads issued together.  A key with zero weight
-    // (masked, unreadable, or underflowed) is skipped, so a stale page is never read.
-    const int keys_here = min(32, end - chunk);
-    for (int j0 = 0; j0 < keys_here; j0 += 8) {
-      float p8[8];
-      float vv[8][DPL];
+      for (int i = 0; i < DPL; ++i) acc[i] *= correction;
+      // values: eight keys at a time, their loads issued together; masked and unreadable
+      // keys are skipped, so a stale page is never read
+      for (int j0 = 0; j0 < keys_here; j0 += 8) {
+        float p8[8];
+        float vv[8][DPL];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        p8[u] = __shfl_sync(0xffffffffu, probability, j0 + u);
-        const int v_row = __shfl_sync(0xffffffffu, row, j0 + u);
-        if (p8[u] != 0.0f && my_dim < D) {
-          VecLoad<T, DPL>::load(v_cache + static_cast<size_t>(v_row) * D + my_dim, vv[u]);
-        } else {
+        for (int u = 0; u < 8; ++u) {
+          p8[u] = __shfl_sync(0xffffffffu, probability, j0 + u);
+          const int v_row = __shfl_sync(0xffffffffu, row, j0 + u);
+          if (v_row >= 0 && my_dim < D) {
+            VecLoad<T, DPL>::load(v_cache + static_cast<size_t>(v_row) * D + my_dim, vv[u]);
+          } else {
 #pragma unroll
-          for (int i = 0; i < DPL; ++i) vv[u][i] = 0.0f;
+            for (int i = 0; i < DPL; ++i) vv[u][i] = 0.0f;
+          }
         }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+          for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p8[u], vv[u][i], acc[i]);
       }
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p8[u], vv[u][i], acc[i]);
     }
   }
 
-  if (a.max_splits == 1 || n_splits == 1) {
+  if (n_splits == 1) {
     if (my_dim < D) {
       const float inverse = 1.0f / running_sum;
       T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
@@ -245,57 +359,27 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
 #pragma unroll
       for (int i = 0; i < DPL; ++i) out[i] = hx_from_float<T>(acc[i] * inverse);
     }
-  } else {
-    float* part = a.partial +
-                  (static_cast<size_t>(token_head) * a.max_splits + split) * (D + 2);
-    if (my_dim < D) {
+    return;
+  }
+  float* part = a.partial + (static_cast<size_t>(token_head) * a.max_splits + split) * (D + 2);
+  if (my_dim < D) {
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) part[my_dim + i] = acc[i];
-    }
-    if (lane == 0) {
-      part[D] = running_max;
-      part[D + 1] = running_sum;
-    }
+    for (int i = 0; i < DPL; ++i) part[my_dim + i] = acc[i];
   }
-}
-
-// Combine the splits of one (token, head) in ascending order.
-template <typename T>
-__global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void attention_merge_kernel(AttentionArgs a) {
-  hx_pdl_prologue();
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const long long token_head = static_cast<long long>(blockIdx.x) * WARPS_PER_BLOCK + warp;
-  if (token_head >= static_cast<long long>(a.tokens) * a.heads) return;
-  const int head = static_cast<int>(token_head % a.heads);
-  const int token = static_cast<int>(token_head / a.heads);
-  if (skipped(a, token)) return;
-  int lo, hi;
-  key_range(a, token, lo, hi);
-  const int n_splits = (hi - lo + a.split_keys - 1) / a.split_keys;
-  if (n_splits <= 1) return;
-  const int D = a.head_dim;
-  const float* part = a.partial + static_cast<size_t>(token_head) * a.max_splits * (D + 2);
-  float total_max = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) total_max = fmaxf(total_max, part[s * (D + 2) + D]);
-  float total_sum = 0.0f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float m = part[s * (D + 2) + D];
-    const float w = m == -INFINITY ? 0.0f : expf(m - total_max);
-    total_sum += part[s * (D + 2) + D + 1] * w;
+  if (lane == 0) {
+    part[D] = running_max;
+    part[D + 1] = running_sum;
   }
-  const float inverse = 1.0f / total_sum;
-  T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
-           static_cast<size_t>(head) * D;
-  for (int d = lane; d < D; d += 32) {
-    float value = 0.0f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float m = part[s * (D + 2) + D];
-      const float w = m == -INFINITY ? 0.0f : expf(m - total_max);
-      value = fmaf(part[s * (D + 2) + d], w, value);
-    }
-    out[d] = hx_from_float<T>(value * inverse);
-  }
+  // who finishes last for this (token, head) combines the splits
+  __threadfence();
+  __syncwarp();
+  int arrived = 0;
+  if (lane == 0) arrived = atomicAdd(a.arrivals + token_head, 1);
+  arrived = __shfl_sync(0xffffffffu, arrived, 0);
+  if (arrived != n_splits - 1) return;
+  __threadfence();
+  if (lane == 0) a.arrivals[token_head] = 0;     // ready for the next call
+  merge_splits<T>(a, token_head, token, head, n_splits, lane);
 }
 
 template <typename T, int DPL, int VEC, int HD = 0>
@@ -320,38 +404,27 @@ int dispatch_vec(const AttentionArgs& a, cudaStream_t stream) {
 
 template <typename T>
 int dispatch(const AttentionArgs& a, cudaStream_t stream) {
-  int rc;
   constexpr int kMaxVec = sizeof(T) == 2 ? 8 : 4;
-  if (a.head_dim == 128) {
+  if (a.head_dim == 128 && sizeof(T) == 2) {   // float32 rows of 128 would not fit in registers
     launch_main<T, 4, kMaxVec, 128>(a, stream);
-    rc = HX_OK;
-  } else if (a.head_dim == 64) {
+    return HX_OK;
+  }
+  if (a.head_dim == 64) {
     launch_main<T, 2, kMaxVec, 64>(a, stream);
-    rc = HX_OK;
-  } else if (a.head_dim <= 64 && a.head_dim % 2 == 0) {
-    rc = dispatch_vec<T, 2>(a, stream);
-  } else if (a.head_dim <= 128 && a.head_dim % 4 == 0) {
-    rc = dispatch_vec<T, 4>(a, stream);
-  } else if (a.head_dim <= 256 && a.head_dim % 8 == 0) {
-    rc = dispatch_vec<T, 8>(a, stream);
-  } else {
-    hx_set_error("hx_paged_attention: head_dim %d is not supported (even up to 64, a multiple of "
-                 "4 up to 128, a multiple of 8 up to 256)", a.head_dim);
-    return HX_ERR_UNSUPPORTED;
+    return HX_OK;
   }
-  if (rc != HX_OK) return rc;
-  if (a.max_splits > 1) {
-    const long long pairs = static_cast<long long>(a.tokens) * a.heads;
-    const int blocks = static_cast<int>((pairs + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
-    hx_launch(attention_merge_kernel<T>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
-    hx_count_launches(1);
-  }
-  return HX_OK;
+  if (a.head_dim <= 64 && a.head_dim % 2 == 0) return dispatch_vec<T, 2>(a, stream);
+  if (a.head_dim <= 128 && a.head_dim % 4 == 0) return dispatch_vec<T, 4>(a, stream);
+  if (a.head_dim <= 256 && a.head_dim % 8 == 0) return dispatch_vec<T, 8>(a, stream);
+  hx_set_error("hx_paged_attention: head_dim %d is not supported (even up to 64, a multiple of "
+               "4 up to 128, a multiple of 8 up to 256)", a.head_dim);
+  return HX_ERR_UNSUPPORTED;
 }
 
 }  // namespace
 
-// Floats of scratch the call needs in `partial` (0 when max_splits == 1).
+// Floats of scratch the call needs in `partial` (0 when max_splits == 1); the same call
+// needs tokens * heads ints of zeroed scratch in `arrivals`.
 HX_API long long hx_paged_attention_scratch_floats(int tokens, int heads, int head_dim,
                                                    int max_splits) {
   if (max_splits <= 1) return 0;
@@ -362,7 +435,7 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
                               int dtype, const int* positions, const int* token_request,
                               const int* request_table_row, const int* block_tables,
                               int table_stride, const int* request_start, int skip_query_len,
-                              void* out, int ldo, float* partial, int tokens,
+                              void* out, int ldo, float* partial, int* arrivals, int tokens,
                               int heads, int kv_heads, int head_dim, int page_size, int num_pages,
                               int window, float scale, int split_keys, int max_splits, int* status,
                               cudaStream_t stream) {
@@ -372,7 +445,8 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
   HX_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0,
              "hx_paged_attention: bad cache geometry");
   HX_REQUIRE(split_keys > 0 && max_splits > 0, "hx_paged_attention: bad split sizes");
-  HX_REQUIRE(max_splits == 1 || partial != nullptr, "hx_paged_attention: scratch missing");
+  HX_REQUIRE(max_splits == 1 || (partial != nullptr && arrivals != nullptr),
+             "hx_paged_attention: scratch missing");
   HX_REQUIRE(window >= 0, "hx_paged_attention: window must not be negative");
   HX_REQUIRE(skip_query_len <= 0 || request_start != nullptr,
              "hx_paged_attention: request_start missing");
@@ -383,8 +457,8 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
   if (tokens == 0) return HX_OK;
   AttentionArgs a{q, ldq, k_cache, v_cache, positions, token_request, request_table_row,
                   block_tables, table_stride, request_start, skip_query_len, out, ldo, partial,
-                  tokens, heads, kv_heads, head_dim,
-                  page_size, num_pages, window, scale, split_keys, max_splits, status};
+                  arrivals, tokens, heads, kv_heads, head_dim, page_size, num_pages, window, scale,
+                  split_keys, max_splits, status};
   const long long items = static_cast<long long>(tokens) * heads * max_splits;
   HX_REQUIRE(items / WARPS_PER_BLOCK < (1ll << 31) - 1, "hx_paged_attention: grid too large");
   int rc;

@@ -102,11 +102,86 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     yr[c] = hx_from_float<TOut>(xr[c] * inverse * weight[c]);
 }
 
+// The same for widths that are a multiple of four and fit in registers: each thread keeps up
+// to four float4 of the row, so the row is read once; the weight (which no earlier kernel
+// writes) is fetched before the dependency wait.
+constexpr int RMS_VECTORS = 4;
+
+template <typename TOut>
+__global__ __launch_bounds__(256) void rmsnorm_vector_kernel(
+    const float* __restrict__ x, const float* __restrict__ weight, TOut* __restrict__ y,
+    const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[32];
+  hx_pdl_trigger();
+  const int vectors = hidden >> 2;
+  float4 w[RMS_VECTORS];
+#pragma unroll
+  for (int i = 0; i < RMS_VECTORS; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < vectors) w[i] = reinterpret_cast<const float4*>(weight)[v];
+  }
+  hx_pdl_wait();
+  const int out_row = blockIdx.x;
+  const int in_row = rows != nullptr ? rows[out_row] : out_row;
+  const float4* xr = reinterpret_cast<const float4*>(x + static_cast<size_t>(in_row) * hidden);
+  float4 value[RMS_VECTORS];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < RMS_VECTORS; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < vectors) {
+      value[i] = xr[v];
+      sum = fmaf(value[i].x, value[i].x, sum);
+      sum = fmaf(value[i].y, value[i].y, sum);
+      sum = fmaf(value[i].z, value[i].z, sum);
+      sum = fmaf(value[i].w, value[i].w, sum);
+    }
+  }
+  const float total = hx_block_sum(sum, scratch);
+  const float inverse = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
+  TOut* yr = y + static_cast<size_t>(out_row) * hidden;
+#pragma unroll
+  for (int i = 0; i < RMS_VECTORS; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < vectors) {
+      const float a = value[i].x * inverse * w[i].x;
+      const float b = value[i].y * inverse * w[i].y;
+      const float c = value[i].z * inverse * w[i].z;
+      const float d = value[i].w * inverse * w[i].w;
+      if (sizeof(TOut) == 4) {
+        reinterpret_cast<float4*>(yr)[v] = make_float4(a, b, c, d);
+      } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(c, d);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(yr)[v] = packed;
+      }
+    }
+  }
+}
+
 HX_API int hx_rmsnorm(const float* x, const float* weight, void* y, int out_dtype, const int* rows,
                       int n_rows, int hidden, float eps, cudaStream_t stream) {
   HX_REQUIRE(n_rows >= 0 && hidden > 0, "hx_rmsnorm: bad sizes");
   HX_REQUIRE(eps > 0.0f, "hx_rmsnorm: eps must be positive");
   if (n_rows == 0) return HX_OK;
+  if (hidden % 4 == 0 && hidden <= 4 * 256 * RMS_VECTORS &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) |
+        reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+    if (out_dtype == HX_F32) {
+      hx_launch(rmsnorm_vector_kernel<float>, n_rows, 256, 0, stream, x, weight,
+                static_cast<float*>(y), rows, hidden, eps);
+    } else if (out_dtype == HX_BF16) {
+      hx_launch(rmsnorm_vector_kernel<__nv_bfloat16>, n_rows, 256, 0, stream, x, weight,
+                static_cast<__nv_bfloat16*>(y), rows, hidden, eps);
+    } else {
+      HX_REQUIRE(false, "hx_rmsnorm: unknown dtype %d", out_dtype);
+    }
+    HX_CHECK_LAUNCH("hx_rmsnorm");
+    return HX_OK;
+  }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (out_dtype == HX_F32) {
     hx_launch(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, weight, static_cast<float*>(y), rows, hidden, eps);

@@ -59,8 +59,8 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_gemm_tc_token_tile.argtypes = [_c_int]
     library.hx_paged_attention.argtypes = [
         _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
-        _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-        _c_float, _c_int, _c_int, _c_ptr, _c_ptr]
+        _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+        _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr]
     library.hx_prefill_attention.argtypes = [
         _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int,
         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr]
@@ -223,16 +223,21 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     partial: Optional[torch.Tensor], tokens: int, heads: int, kv_heads: int,
                     head_dim: int, page_size: int, num_pages: int, window: int, scale: float,
                     split_keys: int, max_splits: int, status: torch.Tensor,
-                    request_start: Optional[torch.Tensor] = None, skip_query_len: int = 0) -> None:
+                    request_start: Optional[torch.Tensor] = None, skip_query_len: int = 0,
+                    arrivals: Optional[torch.Tensor] = None) -> None:
     """out[t, h*D:(h+1)*D] = attention of query (t, h) over its request's pages.  With
     ``skip_query_len > 0`` tokens of requests that bring at least that many tokens are left
-    out (the tensor-core kernel takes them)."""
+    out (the tensor-core kernel takes them).  With ``max_splits > 1`` the call needs scratch:
+    ``partial`` (float32, see :func:`attention_scratch_floats`) and ``arrivals`` (int32, one
+    counter per (token, head), zero on entry; the kernel leaves it zero)."""
+    if max_splits > 1 and arrivals is None:
+        arrivals = torch.zeros(tokens * heads, dtype=torch.int32, device=q.device)
     _check(lib().hx_paged_attention(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), dtype_code(q.dtype),
         positions.data_ptr(), token_request.data_ptr(), request_table_row.data_ptr(),
         block_tables.data_ptr(), block_tables.stride(0), _ptr(request_start), skip_query_len,
         out.data_ptr(), out.stride(0),
-        _ptr(partial), tokens, heads, kv_heads, head_dim, page_size, num_pages, window,
+        _ptr(partial), _ptr(arrivals), tokens, heads, kv_heads, head_dim, page_size, num_pages, window,
         float(scale), split_keys, max_splits, _ptr(status), _stream()))
 
 

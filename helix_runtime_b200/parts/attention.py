@@ -139,16 +139,19 @@ class PagedAttention(Mixer):
             longest = ctx.max_context_len if not window else min(ctx.max_context_len, window)
             split_keys = self.split_keys_for(n, longest, ctx.attention_split_keys)
             max_splits = max(1, -(-longest // split_keys))
-            partial = None
+            partial = arrivals = None
             if max_splits > 1:
                 floats = ops.attention_scratch_floats(n, self.heads, self.head_dim, max_splits)
                 partial = ctx.workspace.at_least("attention.partial", floats, torch.float32)
+                arrivals = ctx.workspace.accumulator("attention.arrivals",
+                                                     (ctx.capacity * self.heads,), torch.int32)
             ops.paged_attention(qkv, cache.keys, cache.values, ctx.positions, ctx.token_request,
                                 ctx.request_slot, cache.block_tables, context, partial, n,
                                 self.heads, self.kv_heads, self.head_dim, cache.page_size,
                                 cache.num_pages, window, self.scale, split_keys, max_splits,
                                 ctx.status, request_start=ctx.request_start,
-                                skip_query_len=TENSOR_CORE_MIN_QUERY if tensor_cores else 0)
+                                skip_query_len=TENSOR_CORE_MIN_QUERY if tensor_cores else 0,
+                                arrivals=arrivals)
         project(context, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status)
 
 

@@ -52,12 +52,13 @@ class Workspace:
             self._buffers[name] = buffer
         return buffer
 
-    def accumulator(self, name: str, shape: Tuple[int, ...]) -> torch.Tensor:
-        """A float32 buffer that is all zero whenever nobody is using it: kernels that sum
-        into it (split-K products) are followed by a kernel that reads and clears it."""
+    def accumulator(self, name: str, shape: Tuple[int, ...],
+                    dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """A buffer that is all zero whenever nobody is using it: kernels that sum into it
+        (split-K products, arrival counters) are followed by code that clears it again."""
         buffer = self._accumulators.get(name)
-        if buffer is None or tuple(buffer.shape) != tuple(shape):
-            buffer = torch.zeros(shape, dtype=torch.float32, device=self.device)
+        if buffer is None or tuple(buffer.shape) != tuple(shape) or buffer.dtype != dtype:
+            buffer = torch.zeros(shape, dtype=dtype, device=self.device)
             self._accumulators[name] = buffer
         return buffer
 
