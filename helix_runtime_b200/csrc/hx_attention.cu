@@ -85,7 +85,7 @@ template <> struct RawSlice<__nv_bfloat16, 4> { using type = uint2; };
 template <> struct RawSlice<__nv_bfloat16, 8> { using type = uint4; };
 template <> struct RawSlice<float, 2> { using type = float2; };
 template <> struct RawSlice<float, 4> { using type = float4; };
-template <> struct RawSlice<float, 8> { using type = float4; };   // never instantiated with HD
+template <> struct RawSlice<float, 8> { using type = float4; };   // never used with a known head size
 
 template <typename T, int DPL>
 __device__ __forceinline__ void unpack(const typename RawSlice<T, DPL>::type& raw, float (&v)[DPL]) {
@@ -189,7 +189,8 @@ __device__ void merge_splits(const AttentionArgs& a, long long token_head, int t
 // VEC: elements per load in the key phase; HD: the head size when it is known at compile
 // time (0: read it from the arguments).
 template <typename T, int DPL, int VEC, int HD>
-__global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(AttentionArgs a) {
+__global__ __launch_bounds__(WARPS_PER_BLOCK * 32, HD > 0 ? 3 : 1) void paged_attention_kernel(
+    AttentionArgs a) {
   __shared__ float q_shared[WARPS_PER_BLOCK][MAX_HEAD_DIM];
   hx_pdl_prologue();
   const int warp = threadIdx.x >> 5;
@@ -233,32 +234,40 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
   for (int chunk = begin; chunk < end; chunk += 32) {
     const int key = chunk + lane;
     bool valid = key < end;
-    int row = -1;
+    int row = -1;            // value row of this lane's key: [page][kv_head][slot]
+    size_t key_offset = 0;   // element offset of chunk 0 of this lane's key (see hx_key_offset)
     if (valid) {
       const int page = table[key / a.page_size];
       if (page < 0 || page >= a.num_pages) {
         if (a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
         valid = false;
       } else {
-        row = (page * a.kv_heads + kv_head) * a.page_size + key % a.page_size;
+        const int slot = key % a.page_size;
+        row = (page * a.kv_heads + kv_head) * a.page_size + slot;
+        key_offset = hx_key_offset(page, kv_head, slot, 0, a.kv_heads, a.page_size, D, VEC);
       }
     }
+    const size_t chunk_stride = static_cast<size_t>(a.page_size) * VEC;
     const int keys_here = min(32, end - chunk);
     float score = -INFINITY;
 
     if (HD > 0) {
       // ---- known head size: every load of the chunk goes out before the arithmetic
       using Raw = typename RawSlice<T, DPL>::type;
+      using RawKey = typename RawSlice<T, VEC>::type;
       constexpr int kLoads = HD > 0 ? HD / VEC : 1;
-      float kv[kLoads][VEC];
+      RawKey key_raw[kLoads];
       if (valid) {
-        const T* k = k_cache + static_cast<size_t>(row) * D;
+        const T* k = k_cache + key_offset;
 #pragma unroll
-        for (int u = 0; u < kLoads; ++u) VecLoad<T, VEC>::load(k + u * VEC, kv[u]);
+        for (int u = 0; u < kLoads; ++u)
+          key_raw[u] = *reinterpret_cast<const RawKey*>(k + u * chunk_stride);
       }
-      Raw values[32];
+      // value slices of the first 16 keys go out with the key loads, the second 16 once the
+      // scores are being reduced: two trips to memory per chunk, half the registers
+      Raw values[16];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
+      for (int j = 0; j < 16; ++j) {
         const int v_row = __shfl_sync(0xffffffffu, row, j);   // -1: masked or unreadable
         if (v_row >= 0 && my_dim < D) {
           values[j] = *reinterpret_cast<const Raw*>(v_cache + static_cast<size_t>(v_row) * D + my_dim);
@@ -269,10 +278,24 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
       if (valid) {
         float dot = 0.0f;
 #pragma unroll
-        for (int u = 0; u < kLoads; ++u)
+        for (int u = 0; u < kLoads; ++u) {
+          float kv[VEC];
+          unpack<T, VEC>(key_raw[u], kv);
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) dot = fmaf(qs[u * VEC + i], kv[u][i], dot);
+          for (int i = 0; i < VEC; ++i) dot = fmaf(qs[u * VEC + i], kv[i], dot);
+        }
         score = dot * a.scale;
+      }
+      Raw more_values[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int v_row = __shfl_sync(0xffffffffu, row, 16 + j);
+        if (v_row >= 0 && my_dim < D) {
+          more_values[j] =
+              *reinterpret_cast<const Raw*>(v_cache + static_cast<size_t>(v_row) * D + my_dim);
+        } else {
+          more_values[j] = Raw{};
+        }
       }
       float chunk_max = score;
 #pragma unroll
@@ -294,18 +317,23 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
       for (int j = 0; j < 32; ++j) {
         const float p = __shfl_sync(0xffffffffu, probability, j);
         float vv[DPL];
-        unpack<T, DPL>(values[j], vv);
+        if (j < 16) {
+          unpack<T, DPL>(values[j], vv);
+        } else {
+          unpack<T, DPL>(more_values[j - 16], vv);
+        }
 #pragma unroll
         for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p, vv[i], acc[i]);
       }
     } else {
       // ---- any head size
       if (valid) {
-        const T* k = k_cache + static_cast<size_t>(row) * D;
+        const T* k = k_cache + key_offset;
         float dot = 0.0f;
         for (int d = 0; d < D; d += VEC) {
           float kv[VEC];
-          VecLoad<T, VEC>::load(k + d, kv);
+          VecLoad<T, VEC>::load(k, kv);
+          k += chunk_stride;
 #pragma unroll
           for (int i = 0; i < VEC; ++i) dot = fmaf(qs[d + i], kv[i], dot);
         }
@@ -405,9 +433,11 @@ int dispatch_vec(const AttentionArgs& a, cudaStream_t stream) {
 template <typename T>
 int dispatch(const AttentionArgs& a, cudaStream_t stream) {
   constexpr int kMaxVec = sizeof(T) == 2 ? 8 : 4;
-  if (a.head_dim == 128 && sizeof(T) == 2) {   // float32 rows of 128 would not fit in registers
-    launch_main<T, 4, kMaxVec, 128>(a, stream);
-    return HX_OK;
+  if constexpr (sizeof(T) == 2) {   // float32 rows of 128 would not fit in registers
+    if (a.head_dim == 128) {
+      launch_main<T, 4, kMaxVec, 128>(a, stream);
+      return HX_OK;
+    }
   }
   if (a.head_dim == 64) {
     launch_main<T, 2, kMaxVec, 64>(a, stream);

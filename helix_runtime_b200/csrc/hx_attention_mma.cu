@@ -161,21 +161,23 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
       const int chunk = index - row * kChunks;
       const int key = tile * BLOCK_N + row;
       bool valid = key <= last_key;
-      size_t source_row = 0;
+      size_t key_element = 0, value_element = 0;
       if (valid) {
         const int page = table[key / a.page_size];
         if (page < 0 || page >= a.num_pages) {
           if (a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
           valid = false;
         } else {
-          source_row = (static_cast<size_t>(page) * a.kv_heads + kv_head) * a.page_size +
-                       key % a.page_size;
+          const int slot = key % a.page_size;
+          // values: [page][kv_head][slot][D]; keys: 16-byte chunks, slot-major (hx_key_offset)
+          value_element = ((static_cast<size_t>(page) * a.kv_heads + kv_head) * a.page_size + slot) * D +
+                          chunk * 8;
+          key_element = hx_key_offset(page, kv_head, slot, chunk * 8, a.kv_heads, a.page_size, D, 8);
         }
       }
-      const size_t element = source_row * D + chunk * 8;
       const uint32_t offset = tile_offset<D>(row, chunk);
-      cp_async_16(k_dst + offset, a.k_cache + element, valid ? 16 : 0);
-      cp_async_16(v_dst + offset, a.v_cache + element, valid ? 16 : 0);
+      cp_async_16(k_dst + offset, a.k_cache + key_element, valid ? 16 : 0);
+      cp_async_16(v_dst + offset, a.v_cache + value_element, valid ? 16 : 0);
     }
   };
 

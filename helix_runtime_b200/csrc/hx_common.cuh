@@ -143,6 +143,28 @@ __device__ __forceinline__ float hx_block_max(float value, float* scratch) {
   return total;
 }
 
+// ------------------------------------------------------------------ key cache layout
+//
+// Values are stored [page][kv_head][slot][head_dim].  Keys are stored in chunks of
+// `chunk` elements (16 bytes where the head size allows): [page][kv_head][head_dim / chunk]
+// [slot][chunk], so that the lanes of a warp, each owning one key (one slot), read
+// consecutive 16-byte pieces: the key phase of attention is then a coalesced stream.
+__host__ __device__ __forceinline__ int hx_key_chunk(int element_bytes, int head_dim) {
+  const int widest = 16 / element_bytes;
+  if (head_dim % widest == 0) return widest;
+  if (widest >= 8 && head_dim % 4 == 0) return 4;
+  if (head_dim % 4 == 0 && widest >= 4) return 4;
+  return 2;
+}
+
+// Element offset of coordinate `dim` of the key in (page, kv_head, slot).
+__host__ __device__ __forceinline__ size_t hx_key_offset(int page, int kv_head, int slot, int dim,
+                                                         int kv_heads, int page_size,
+                                                         int head_dim, int chunk) {
+  const size_t page_head = static_cast<size_t>(page) * kv_heads + kv_head;
+  return ((page_head * (head_dim / chunk) + dim / chunk) * page_size + slot) * chunk + dim % chunk;
+}
+
 // silu(x) = x * sigmoid(x) with the branch-stable sigmoid of the reference
 // (src/kernels/cuda/transformer.cu:68-83).
 __device__ __forceinline__ float hx_silu(float x) {

@@ -341,10 +341,10 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
           vec[i1] = tb;
         } else if (page >= 0) {
           const int kv_head = head - heads;
-          T* dst = k_cache +
-                   ((static_cast<size_t>(page) * kv_heads + kv_head) * page_size + slot) * head_dim;
-          dst[i0] = ta;
-          dst[i1] = tb;
+          // keys are stored in 16-byte chunks, slot-major inside a chunk (see hx_key_offset)
+          const int key_chunk = hx_key_chunk(sizeof(T), head_dim);
+          k_cache[hx_key_offset(page, kv_head, slot, i0, kv_heads, page_size, head_dim, key_chunk)] = ta;
+          k_cache[hx_key_offset(page, kv_head, slot, i1, kv_heads, page_size, head_dim, key_chunk)] = tb;
         }
       }
     } else {
