@@ -185,6 +185,45 @@ __device__ void merge_splits(const AttentionArgs& a, long long token_head, int t
   }
 }
 
+// What a warp does with its finished (token, head, split): write the output if it is the only
+// split, else leave the partial result in scratch and, if it is the last to arrive, merge.
+template <typename T, int DPL>
+__device__ __forceinline__ void finish_item(const AttentionArgs& a, long long token_head, int token,
+                                            int head, int split, int n_splits, int lane, int D,
+                                            const float (&acc)[DPL], float running_max,
+                                            float running_sum) {
+  const int my_dim = lane * DPL;
+  if (n_splits == 1) {
+    if (my_dim < D) {
+      const float inverse = 1.0f / running_sum;
+      T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
+               static_cast<size_t>(head) * D + my_dim;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) out[i] = hx_from_float<T>(acc[i] * inverse);
+    }
+    return;
+  }
+  float* part = a.partial + (static_cast<size_t>(token_head) * a.max_splits + split) * (D + 2);
+  if (my_dim < D) {
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) part[my_dim + i] = acc[i];
+  }
+  if (lane == 0) {
+    part[D] = running_max;
+    part[D + 1] = running_sum;
+  }
+  // who finishes last for this (token, head) combines the splits
+  __threadfence();
+  __syncwarp();
+  int arrived = 0;
+  if (lane == 0) arrived = atomicAdd(a.arrivals + token_head, 1);
+  arrived = __shfl_sync(0xffffffffu, arrived, 0);
+  if (arrived != n_splits - 1) return;
+  __threadfence();
+  if (lane == 0) a.arrivals[token_head] = 0;     // ready for the next call
+  merge_splits<T>(a, token_head, token, head, n_splits, lane);
+}
+
 // DPL: value coordinates per lane in the value phase (32 * DPL >= head_dim);
 // VEC: elements per load in the key phase; HD: the head size when it is known at compile
 // time (0: read it from the arguments).
@@ -379,35 +418,270 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32, HD > 0 ? 3 : 1) void paged_at
     }
   }
 
-  if (n_splits == 1) {
-    if (my_dim < D) {
-      const float inverse = 1.0f / running_sum;
-      T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
-               static_cast<size_t>(head) * D + my_dim;
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) out[i] = hx_from_float<T>(acc[i] * inverse);
-    }
-    return;
+  finish_item<T, DPL>(a, token_head, token, head, split, n_splits, lane, D, acc, running_max,
+                      running_sum);
+}
+
+// ------------------------------------------------------------------ streaming variant
+//
+// bfloat16, head sizes 64 and 128, pages of 8, 16 or 32 keys, no window.  The keys of a
+// (page, head) are one contiguous block of the cache and so are its values, so a 32-key
+// chunk is fetched with a few bulk copies (cp.async.bulk, completion counted on an
+// mbarrier) into a ring of shared-memory slots that belongs to the warp.  The bytes in
+// flight no longer live in registers: two warps per CTA keep 96 KB of the cache on its way
+// to the SM, which is what it takes to stream the cache at memory speed.  Arithmetic, split
+// handling and the order of every sum are those of the kernel above.
+constexpr int STREAM_WARPS = 2;
+constexpr uint32_t STREAM_WAIT_LIMIT = 20u * 1000u * 1000u;
+
+__device__ __forceinline__ uint32_t shared_address(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ bool stream_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t address = shared_address(bar);
+  for (uint32_t spin = 0; spin < STREAM_WAIT_LIMIT; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(address), "r"(parity)
+        : "memory");
+    if (done) return true;
   }
-  float* part = a.partial + (static_cast<size_t>(token_head) * a.max_splits + split) * (D + 2);
-  if (my_dim < D) {
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) part[my_dim + i] = acc[i];
-  }
+  return false;
+}
+
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(shared_address(dst)), "l"(src), "r"(bytes), "r"(shared_address(bar))
+      : "memory");
+}
+
+template <int D>
+struct StreamConfig {
+  static constexpr int kChunkBytes = 32 * D * 2;     // keys (or values) of a 32-key chunk
+  static constexpr int kSlotBytes = 2 * kChunkBytes;
+  static constexpr int kRing = D == 128 ? 3 : 4;
+  static constexpr int kSharedBytes = STREAM_WARPS * kRing * kSlotBytes;
+};
+
+template <int D>
+__global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kernel(
+    AttentionArgs a) {
+  using T = __nv_bfloat16;
+  using Config = StreamConfig<D>;
+  constexpr int DPL = D / 32;
+  constexpr int RING = Config::kRing;
+  constexpr int kKeyLoads = D / 8;
+  extern __shared__ __align__(128) uint8_t stream_shared[];
+  __shared__ uint64_t full_bar[STREAM_WARPS][RING];
+  __shared__ float q_shared[STREAM_WARPS][D];
+  hx_pdl_prologue();
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * STREAM_WARPS + warp;
+  const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
+  if (item >= items) return;
+  const int split = static_cast<int>(item % a.max_splits);
+  const long long token_head = item / a.max_splits;
+  const int head = static_cast<int>(token_head % a.heads);
+  const int token = static_cast<int>(token_head / a.heads);
+  if (skipped(a, token)) return;
+
+  int lo, hi;
+  key_range(a, token, lo, hi);          // no window here: lo == 0
+  const int n_splits = (hi - lo + a.split_keys - 1) / a.split_keys;
+  if (split >= n_splits) return;
+  const int begin = lo + split * a.split_keys;      // a multiple of 32, hence of the page size
+  const int end = min(begin + a.split_keys, hi);
+  const int n_chunks = (end - begin + 31) / 32;
+
+  const int kv_head = head / (a.heads / a.kv_heads);
+  const T* q = static_cast<const T*>(a.q) + static_cast<size_t>(token) * a.ldq +
+               static_cast<size_t>(head) * D;
+  float* qs = q_shared[warp];
+  for (int d = lane; d < D; d += 32) qs[d] = __bfloat162float(q[d]);
+
+  const int page_size = a.page_size;
+  const int pages_per_chunk = 32 / page_size;
+  const uint32_t page_bytes = static_cast<uint32_t>(page_size) * D * 2;
+  const int table_row = a.request_table_row[a.token_request[token]];
+  const int* table = a.block_tables + static_cast<size_t>(table_row) * a.table_stride;
+  const int first_page = begin / page_size;
+  const int n_pages = (end - begin + page_size - 1) / page_size;
+  const uint8_t* k_cache = static_cast<const uint8_t*>(a.k_cache);
+  const uint8_t* v_cache = static_cast<const uint8_t*>(a.v_cache);
+  uint8_t* ring = stream_shared + static_cast<size_t>(warp) * RING * Config::kSlotBytes;
+  uint64_t* bars = full_bar[warp];
+
   if (lane == 0) {
-    part[D] = running_max;
-    part[D + 1] = running_sum;
+    for (int s = 0; s < RING; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(shared_address(&bars[s])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // who finishes last for this (token, head) combines the splits
-  __threadfence();
   __syncwarp();
-  int arrived = 0;
-  if (lane == 0) arrived = atomicAdd(a.arrivals + token_head, 1);
-  arrived = __shfl_sync(0xffffffffu, arrived, 0);
-  if (arrived != n_splits - 1) return;
-  __threadfence();
-  if (lane == 0) a.arrivals[token_head] = 0;     // ready for the next call
-  merge_splits<T>(a, token_head, token, head, n_splits, lane);
+
+  // the block table entries of up to 32 pages at a time, one per lane
+  int window_first = 0;                 // index (within the split) of the page lane 0 holds
+  int my_page = -1;
+  auto load_pages = [&](int from) {
+    window_first = from;
+    const int index = from + lane;
+    my_page = index < n_pages ? table[first_page + index] : -1;
+    if (my_page >= a.num_pages) my_page = -1;
+  };
+  load_pages(0);
+
+  // request the pages of chunk `c` into its ring slot (every lane runs this; lane 0 issues)
+  auto request_chunk = [&](int c) {
+    uint8_t* slot = ring + static_cast<size_t>(c % RING) * Config::kSlotBytes;
+    uint64_t* bar = &bars[c % RING];
+    int pages[4];
+    uint32_t expected = 0;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      pages[p] = -1;
+      if (p < pages_per_chunk) {
+        const int index = c * pages_per_chunk + p;
+        if (index >= window_first + 32) load_pages(index);
+        const int page = __shfl_sync(0xffffffffu, my_page, index - window_first);
+        if (index < n_pages && page >= 0) {
+          pages[p] = page;
+          expected += 2 * page_bytes;
+        }
+      }
+    }
+    if (lane == 0) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                       shared_address(bar)), "r"(expected) : "memory");
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        if (pages[p] >= 0) {
+          const size_t block = (static_cast<size_t>(pages[p]) * a.kv_heads + kv_head) * page_bytes;
+          bulk_copy(slot + p * page_bytes, k_cache + block, page_bytes, bar);
+          bulk_copy(slot + Config::kChunkBytes + p * page_bytes, v_cache + block, page_bytes, bar);
+        }
+      }
+    }
+  };
+  const int ahead = n_chunks < RING ? n_chunks : RING;
+  for (int c = 0; c < ahead; ++c) request_chunk(c);
+
+  float acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
+  float running_max = -INFINITY;
+  float running_sum = 0.0f;
+  bool bad_page = false;
+
+  for (int c = 0; c < n_chunks; ++c) {
+    // is this lane's key there, and is its page readable?
+    const int key = begin + c * 32 + lane;
+    const int page_index = c * pages_per_chunk + lane / page_size;
+    // the window of table entries may have moved on while requesting ahead: look it up again
+    int page = -1;
+    if (key < end) {
+      page = table[first_page + page_index];
+      if (page < 0 || page >= a.num_pages) {
+        page = -1;
+        bad_page = true;
+      }
+    }
+    const bool valid = page >= 0;
+
+    bool arrived = true;
+    if (lane == 0) arrived = stream_wait(&bars[c % RING], static_cast<uint32_t>(c / RING) & 1u);
+    arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
+    if (!arrived) {
+      if (lane == 0 && a.status != nullptr) atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
+      return;
+    }
+    const uint8_t* slot = ring + static_cast<size_t>(c % RING) * Config::kSlotBytes;
+
+    float score = -INFINITY;
+    if (valid) {
+      const uint8_t* k = slot + (lane / page_size) * page_bytes + (lane % page_size) * 16;
+      float dot = 0.0f;
+#pragma unroll
+      for (int u = 0; u < kKeyLoads; ++u) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(k + static_cast<size_t>(u) * page_size * 16);
+        float kv[8];
+        VecLoad<T, 8>::load(reinterpret_cast<const T*>(&raw), kv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(qs[u * 8 + i], kv[i], dot);
+      }
+      score = dot * a.scale;
+    }
+    float chunk_max = score;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+      chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, offset));
+    const float new_max = fmaxf(running_max, chunk_max);
+    if (new_max != -INFINITY) {
+      const float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
+      const float probability = valid ? expf(score - new_max) : 0.0f;
+      float chunk_sum = probability;
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1)
+        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, offset);
+      running_sum = running_sum * correction + chunk_sum;
+      running_max = new_max;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) acc[i] *= correction;
+      const uint8_t* v = slot + Config::kChunkBytes + lane * DPL * 2;
+#pragma unroll 8
+      for (int j = 0; j < 32; ++j) {
+        const float p = __shfl_sync(0xffffffffu, probability, j);
+        if (p != 0.0f) {      // masked and unreadable keys: their slots may hold anything
+          float vv[DPL];
+          VecLoad<T, DPL>::load(reinterpret_cast<const T*>(v + static_cast<size_t>(j) * D * 2), vv);
+#pragma unroll
+          for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p, vv[i], acc[i]);
+        }
+      }
+    }
+    __syncwarp();
+    if (c + RING < n_chunks) {
+      // the slot is free: order this warp's reads before the copy engine's writes
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      request_chunk(c + RING);
+    }
+  }
+  if (bad_page && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
+  finish_item<T, DPL>(a, token_head, token, head, split, n_splits, lane, D, acc, running_max,
+                      running_sum);
+}
+
+template <int D>
+int launch_stream(const AttentionArgs& a, cudaStream_t stream) {
+  using Config = StreamConfig<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(paged_attention_stream_kernel<D>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Config::kSharedBytes) != cudaSuccess) {
+      cudaGetLastError();
+      hx_set_error("hx_paged_attention: cannot reserve %d bytes of shared memory",
+                   Config::kSharedBytes);
+      return HX_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
+  const int blocks = static_cast<int>((items + STREAM_WARPS - 1) / STREAM_WARPS);
+  hx_launch(paged_attention_stream_kernel<D>, blocks, STREAM_WARPS * 32, Config::kSharedBytes,
+            stream, a);
+  return HX_OK;
+}
+
+bool stream_variant_applies(const AttentionArgs& a, int dtype) {
+  return dtype == HX_BF16 && (a.head_dim == 64 || a.head_dim == 128) && a.window == 0 &&
+         (a.page_size == 8 || a.page_size == 16 || a.page_size == 32) && a.split_keys % 32 == 0;
 }
 
 template <typename T, int DPL, int VEC, int HD = 0>
@@ -492,7 +766,9 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
   const long long items = static_cast<long long>(tokens) * heads * max_splits;
   HX_REQUIRE(items / WARPS_PER_BLOCK < (1ll << 31) - 1, "hx_paged_attention: grid too large");
   int rc;
-  if (dtype == HX_F32) {
+  if (stream_variant_applies(a, dtype)) {
+    rc = a.head_dim == 128 ? launch_stream<128>(a, stream) : launch_stream<64>(a, stream);
+  } else if (dtype == HX_F32) {
     rc = dispatch<float>(a, stream);
   } else if (dtype == HX_BF16) {
     rc = dispatch<__nv_bfloat16>(a, stream);
