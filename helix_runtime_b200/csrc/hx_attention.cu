@@ -1,4 +1,4 @@
-// Paged causal attention over block tables, float32 arithmetic, any batch shape.
+// Paged causal attention over block tables for decode tokens and short prompt portions.
 //
 // Every query token of the flattened batch attends to the keys of its own request at
 // absolute positions [lo, position], lo = 0 or position - window + 1; this step's
@@ -9,88 +9,38 @@
 // walks the keys of one (token, head, key split) with an online softmax and never
 // stores a score.
 //
-// One chunk of 32 keys: lane j owns key j for the score (a whole key row per lane) and
-// a slice of the head dimension for the weighted value sum (lane-per-dimension).  For the
-// usual head sizes the loads of the key row AND of the 32 value slices are all issued
-// before anything is computed, so a chunk costs one trip to memory.
+// Two kernels share the splitting and merging:
+//
+//  * the CUDA-core kernel takes every dtype, head size, page size and window: per chunk of
+//    32 keys, lane j owns key j for the score and a slice of the head dimension for the
+//    weighted value sum, all in float32;
+//  * the streaming kernel (bfloat16, head sizes 64 and 128, pages of 8, 16 or 32 keys, no
+//    window) is what decoding runs.  The keys of a (page, head) are one contiguous block of
+//    the cache and so are its values, so a 32-key chunk is fetched with a few bulk copies
+//    (cp.async.bulk counted on an mbarrier) into a ring of shared-memory slots that belongs
+//    to the warp, and both products run on the tensor cores straight out of those slots: the
+//    query is row 0 of a 16-row tile.  The bytes in flight live in shared memory, not in
+//    registers, and the instruction count per byte is a sixth of the CUDA-core kernel's,
+//    which is what it takes to stream the cache at memory speed.  Probabilities enter the
+//    second product as two bfloat16 terms (hi + lo), so the softmax stays a float32
+//    quantity as far as the result can tell.
 //
 // Key splits.  A long context is cut into splits of `split_keys` keys, one warp each.
 // Every split writes its unnormalised sum, maximum and weight to scratch; the warp that
 // finishes LAST for a (token, head) combines them in ascending order (a counter per
 // (token, head) in scratch tells who is last, and is left at zero again).
 //
-// Exactness: dot products, the running maximum, exp, the running sum and the
-// weighted value sum are float32.  The order of every sum is a function of the
-// token's own position and of split_keys only (32-key chunks and splits anchored at
-// lo, merged in ascending order), so a token's result does not depend on how the
-// batch was cut, what else is in it, or which pages hold the keys.
-#include "hx_common.cuh"
+// Exactness: the running maximum, exp, the running sum and the merge are float32; dot
+// products are float32 sums of exact products.  The order of every sum is a function of the
+// token's own position and of split_keys only (32-key chunks and splits anchored at lo,
+// merged in ascending order), so a token's result does not depend on how the batch was cut,
+// what else is in it, or which pages hold the keys.
+#include "hx_mma.cuh"
 
 namespace {
 
 constexpr int WARPS_PER_BLOCK = 4;
 constexpr int MAX_HEAD_DIM = 256;
-
-template <typename T, int VEC> struct VecLoad;
-template <> struct VecLoad<float, 4> {
-  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
-    const float4 r = *reinterpret_cast<const float4*>(p);
-    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
-  }
-};
-template <> struct VecLoad<float, 2> {
-  static __device__ __forceinline__ void load(const float* p, float (&v)[2]) {
-    const float2 r = *reinterpret_cast<const float2*>(p);
-    v[0] = r.x; v[1] = r.y;
-  }
-};
-template <> struct VecLoad<float, 8> {
-  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
-    const float4 a = *reinterpret_cast<const float4*>(p);
-    const float4 b = *reinterpret_cast<const float4*>(p + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  }
-};
-template <> struct VecLoad<__nv_bfloat16, 2> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[2]) {
-    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
-    v[0] = f.x; v[1] = f.y;
-  }
-};
-template <> struct VecLoad<__nv_bfloat16, 4> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
-    const uint2 r = *reinterpret_cast<const uint2*>(p);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-  }
-};
-template <> struct VecLoad<__nv_bfloat16, 8> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
-    const uint4 r = *reinterpret_cast<const uint4*>(p);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
-    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.z));
-    const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.w));
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-    v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
-  }
-};
-
-// A value slice kept as raw bits until it is used, so that 32 of them fit in registers.
-template <typename T, int DPL> struct RawSlice;
-template <> struct RawSlice<__nv_bfloat16, 2> { using type = uint32_t; };
-template <> struct RawSlice<__nv_bfloat16, 4> { using type = uint2; };
-template <> struct RawSlice<__nv_bfloat16, 8> { using type = uint4; };
-template <> struct RawSlice<float, 2> { using type = float2; };
-template <> struct RawSlice<float, 4> { using type = float4; };
-template <> struct RawSlice<float, 8> { using type = float4; };   // never used with a known head size
-
-template <typename T, int DPL>
-__device__ __forceinline__ void unpack(const typename RawSlice<T, DPL>::type& raw, float (&v)[DPL]) {
-  VecLoad<T, DPL>::load(reinterpret_cast<const T*>(&raw), v);
-}
 
 struct AttentionArgs {
   const void* q;
@@ -104,7 +54,7 @@ struct AttentionArgs {
   int table_stride;
   const int* request_start;   // [requests + 1], needed only when skip_query_len > 0
   int skip_query_len;         // > 0: leave requests with at least this many tokens to the
-                              // tensor-core kernel
+                              // tensor-core prompt kernel
   void* out;
   int ldo;
   float* partial;   // [tokens * heads][max_splits][head_dim + 2], only when max_splits > 1
@@ -134,14 +84,37 @@ __device__ __forceinline__ void key_range(const AttentionArgs& a, int token, int
   lo = a.window > 0 ? max(0, hi - a.window) : 0;
 }
 
+// Which (token, head, split) is this warp's, and which keys does it walk?  False: nothing to do.
+struct Item {
+  long long token_head;
+  int token, head, split, n_splits, begin, end;
+};
+
+__device__ __forceinline__ bool find_item(const AttentionArgs& a, long long index, Item& item) {
+  const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
+  if (index >= items) return false;
+  item.split = static_cast<int>(index % a.max_splits);
+  item.token_head = index / a.max_splits;
+  item.head = static_cast<int>(item.token_head % a.heads);
+  item.token = static_cast<int>(item.token_head / a.heads);
+  if (skipped(a, item.token)) return false;
+  int lo, hi;
+  key_range(a, item.token, lo, hi);
+  item.n_splits = (hi - lo + a.split_keys - 1) / a.split_keys;
+  if (item.split >= item.n_splits) return false;
+  item.begin = lo + item.split * a.split_keys;
+  item.end = min(item.begin + a.split_keys, hi);
+  return true;
+}
+
 // Combine the splits of one (token, head) in ascending order; run by one warp.
 template <typename T>
-__device__ void merge_splits(const AttentionArgs& a, long long token_head, int token, int head,
-                             int n_splits, int lane) {
+__device__ void merge_splits(const AttentionArgs& a, const Item& item, int lane) {
   const int D = a.head_dim;
   const int stride = D + 2;
-  const float* part = a.partial + static_cast<size_t>(token_head) * a.max_splits * stride;
-  // maxima and weights of the splits, 32 at a time, read past the L1 (other SMs wrote them)
+  const int n_splits = item.n_splits;
+  const float* part = a.partial + static_cast<size_t>(item.token_head) * a.max_splits * stride;
+  // maxima of the splits, 32 at a time, read past the L1 (other SMs wrote them)
   float total_max = -INFINITY;
   for (int base = 0; base < n_splits; base += 32) {
     const int s = base + lane;
@@ -165,8 +138,8 @@ __device__ void merge_splits(const AttentionArgs& a, long long token_head, int t
     for (int j = 0; j < here; ++j) total_sum += __shfl_sync(0xffffffffu, weighted, j);
   }
   const float inverse = 1.0f / total_sum;
-  T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
-           static_cast<size_t>(head) * D;
+  T* out = static_cast<T*>(a.out) + static_cast<size_t>(item.token) * a.ldo +
+           static_cast<size_t>(item.head) * D;
   for (int d = lane; d < D; d += 32) {
     float value = 0.0f;
     for (int base = 0; base < n_splits; base += 4) {
@@ -185,80 +158,67 @@ __device__ void merge_splits(const AttentionArgs& a, long long token_head, int t
   }
 }
 
-// What a warp does with its finished (token, head, split): write the output if it is the only
-// split, else leave the partial result in scratch and, if it is the last to arrive, merge.
-template <typename T, int DPL>
-__device__ __forceinline__ void finish_item(const AttentionArgs& a, long long token_head, int token,
-                                            int head, int split, int n_splits, int lane, int D,
-                                            const float (&acc)[DPL], float running_max,
-                                            float running_sum) {
-  const int my_dim = lane * DPL;
-  if (n_splits == 1) {
-    if (my_dim < D) {
-      const float inverse = 1.0f / running_sum;
-      T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
-               static_cast<size_t>(head) * D + my_dim;
+// What a warp does with its finished item.  The result arrives as `count` consecutive
+// coordinates per lane starting at `first_dim` (lanes that hold nothing pass count 0).  With
+// one split the output is written, else the partial result goes to scratch and the warp that
+// arrives last merges.
+template <typename T, int COUNT>
+__device__ __forceinline__ void finish_item(const AttentionArgs& a, const Item& item, int lane,
+                                            int first_dim, int count, const float (&acc)[COUNT],
+                                            float running_max, float running_sum) {
+  const int D = a.head_dim;
+  if (item.n_splits == 1) {
+    const float inverse = 1.0f / running_sum;
+    T* out = static_cast<T*>(a.out) + static_cast<size_t>(item.token) * a.ldo +
+             static_cast<size_t>(item.head) * D + first_dim;
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) out[i] = hx_from_float<T>(acc[i] * inverse);
-    }
+    for (int i = 0; i < COUNT; ++i)
+      if (i < count) out[i] = hx_from_float<T>(acc[i] * inverse);
     return;
   }
-  float* part = a.partial + (static_cast<size_t>(token_head) * a.max_splits + split) * (D + 2);
-  if (my_dim < D) {
+  float* part = a.partial +
+                (static_cast<size_t>(item.token_head) * a.max_splits + item.split) * (D + 2);
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) part[my_dim + i] = acc[i];
-  }
+  for (int i = 0; i < COUNT; ++i)
+    if (i < count) part[first_dim + i] = acc[i];
   if (lane == 0) {
     part[D] = running_max;
     part[D + 1] = running_sum;
   }
-  // who finishes last for this (token, head) combines the splits
   __threadfence();
   __syncwarp();
   int arrived = 0;
-  if (lane == 0) arrived = atomicAdd(a.arrivals + token_head, 1);
+  if (lane == 0) arrived = atomicAdd(a.arrivals + item.token_head, 1);
   arrived = __shfl_sync(0xffffffffu, arrived, 0);
-  if (arrived != n_splits - 1) return;
+  if (arrived != item.n_splits - 1) return;
   __threadfence();
-  if (lane == 0) a.arrivals[token_head] = 0;     // ready for the next call
-  merge_splits<T>(a, token_head, token, head, n_splits, lane);
+  if (lane == 0) a.arrivals[item.token_head] = 0;     // ready for the next call
+  merge_splits<T>(a, item, lane);
 }
 
-// DPL: value coordinates per lane in the value phase (32 * DPL >= head_dim);
-// VEC: elements per load in the key phase; HD: the head size when it is known at compile
-// time (0: read it from the arguments).
-template <typename T, int DPL, int VEC, int HD>
-__global__ __launch_bounds__(WARPS_PER_BLOCK * 32, HD > 0 ? 3 : 1) void paged_attention_kernel(
-    AttentionArgs a) {
+// ------------------------------------------------------------------ CUDA-core kernel
+
+// DPL: value coordinates per lane in the value phase (32 * DPL >= head_dim).  Cache elements
+// are read two at a time, which every chunk size and every even head size allows.
+template <typename T, int DPL>
+__global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(AttentionArgs a) {
   __shared__ float q_shared[WARPS_PER_BLOCK][MAX_HEAD_DIM];
   hx_pdl_prologue();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const long long item = static_cast<long long>(blockIdx.x) * WARPS_PER_BLOCK + warp;
-  const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
-  if (item >= items) return;
-  const int split = static_cast<int>(item % a.max_splits);
-  const long long token_head = item / a.max_splits;
-  const int head = static_cast<int>(token_head % a.heads);
-  const int token = static_cast<int>(token_head / a.heads);
-  if (skipped(a, token)) return;
+  Item item;
+  if (!find_item(a, static_cast<long long>(blockIdx.x) * WARPS_PER_BLOCK + warp, item)) return;
 
-  int lo, hi;
-  key_range(a, token, lo, hi);
-  const int n_splits = (hi - lo + a.split_keys - 1) / a.split_keys;
-  if (split >= n_splits) return;
-  const int begin = lo + split * a.split_keys;
-  const int end = min(begin + a.split_keys, hi);
-
-  const int D = HD > 0 ? HD : a.head_dim;
-  const int kv_head = head / (a.heads / a.kv_heads);
-  const T* q = static_cast<const T*>(a.q) + static_cast<size_t>(token) * a.ldq +
-               static_cast<size_t>(head) * D;
+  const int D = a.head_dim;
+  const int chunk_elems = hx_cache_chunk(sizeof(T), D);
+  const int kv_head = item.head / (a.heads / a.kv_heads);
+  const T* q = static_cast<const T*>(a.q) + static_cast<size_t>(item.token) * a.ldq +
+               static_cast<size_t>(item.head) * D;
   float* qs = q_shared[warp];
   for (int d = lane; d < D; d += 32) qs[d] = hx_to_float<T>(q[d]);
   __syncwarp();
 
-  const int table_row = a.request_table_row[a.token_request[token]];
+  const int table_row = a.request_table_row[a.token_request[item.token]];
   const int* table = a.block_tables + static_cast<size_t>(table_row) * a.table_stride;
   const T* k_cache = static_cast<const T*>(a.k_cache);
   const T* v_cache = static_cast<const T*>(a.v_cache);
@@ -270,176 +230,74 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32, HD > 0 ? 3 : 1) void paged_at
   float running_sum = 0.0f;
   const int my_dim = lane * DPL;
 
-  for (int chunk = begin; chunk < end; chunk += 32) {
+  for (int chunk = item.begin; chunk < item.end; chunk += 32) {
     const int key = chunk + lane;
-    bool valid = key < end;
-    int row = -1;            // value row of this lane's key: [page][kv_head][slot]
-    size_t key_offset = 0;   // element offset of chunk 0 of this lane's key (see hx_key_offset)
+    bool valid = key < item.end;
+    int page = -1, slot = 0;
     if (valid) {
-      const int page = table[key / a.page_size];
+      page = table[key / a.page_size];
+      slot = key % a.page_size;
       if (page < 0 || page >= a.num_pages) {
         if (a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
         valid = false;
-      } else {
-        const int slot = key % a.page_size;
-        row = (page * a.kv_heads + kv_head) * a.page_size + slot;
-        key_offset = hx_key_offset(page, kv_head, slot, 0, a.kv_heads, a.page_size, D, VEC);
+        page = -1;
       }
     }
-    const size_t chunk_stride = static_cast<size_t>(a.page_size) * VEC;
-    const int keys_here = min(32, end - chunk);
     float score = -INFINITY;
-
-    if (HD > 0) {
-      // ---- known head size: every load of the chunk goes out before the arithmetic
-      using Raw = typename RawSlice<T, DPL>::type;
-      using RawKey = typename RawSlice<T, VEC>::type;
-      constexpr int kLoads = HD > 0 ? HD / VEC : 1;
-      RawKey key_raw[kLoads];
-      if (valid) {
-        const T* k = k_cache + key_offset;
-#pragma unroll
-        for (int u = 0; u < kLoads; ++u)
-          key_raw[u] = *reinterpret_cast<const RawKey*>(k + u * chunk_stride);
+    if (valid) {
+      float dot = 0.0f;
+      for (int d = 0; d < D; d += 2) {
+        const T* k = k_cache + hx_cache_offset(page, kv_head, slot, d, a.kv_heads, a.page_size, D,
+                                               chunk_elems);
+        dot = fmaf(qs[d], hx_to_float<T>(k[0]), dot);
+        dot = fmaf(qs[d + 1], hx_to_float<T>(k[1]), dot);
       }
-      // value slices of the first 16 keys go out with the key loads, the second 16 once the
-      // scores are being reduced: two trips to memory per chunk, half the registers
-      Raw values[16];
+      score = dot * a.scale;
+    }
+    float chunk_max = score;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int v_row = __shfl_sync(0xffffffffu, row, j);   // -1: masked or unreadable
-        if (v_row >= 0 && my_dim < D) {
-          values[j] = *reinterpret_cast<const Raw*>(v_cache + static_cast<size_t>(v_row) * D + my_dim);
-        } else {
-          values[j] = Raw{};
+    for (int offset = 16; offset > 0; offset >>= 1)
+      chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, offset));
+    const float new_max = fmaxf(running_max, chunk_max);
+    if (new_max == -INFINITY) continue;   // every key of the chunk unreadable
+    const float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
+    const float probability = valid ? expf(score - new_max) : 0.0f;
+    float chunk_sum = probability;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+      chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, offset);
+    running_sum = running_sum * correction + chunk_sum;
+    running_max = new_max;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] *= correction;
+    // values: masked and unreadable keys are skipped, so a stale page is never read
+    const int keys_here = min(32, item.end - chunk);
+    for (int j = 0; j < keys_here; ++j) {
+      const float p = __shfl_sync(0xffffffffu, probability, j);
+      const int v_page = __shfl_sync(0xffffffffu, page, j);
+      const int v_slot = __shfl_sync(0xffffffffu, slot, j);
+      if (v_page >= 0 && my_dim < D) {
+#pragma unroll
+        for (int i = 0; i < DPL; i += 2) {
+          const T* v = v_cache + hx_cache_offset(v_page, kv_head, v_slot, my_dim + i, a.kv_heads,
+                                                 a.page_size, D, chunk_elems);
+          acc[i] = fmaf(p, hx_to_float<T>(v[0]), acc[i]);
+          acc[i + 1] = fmaf(p, hx_to_float<T>(v[1]), acc[i + 1]);
         }
-      }
-      if (valid) {
-        float dot = 0.0f;
-#pragma unroll
-        for (int u = 0; u < kLoads; ++u) {
-          float kv[VEC];
-          unpack<T, VEC>(key_raw[u], kv);
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) dot = fmaf(qs[u * VEC + i], kv[i], dot);
-        }
-        score = dot * a.scale;
-      }
-      Raw more_values[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int v_row = __shfl_sync(0xffffffffu, row, 16 + j);
-        if (v_row >= 0 && my_dim < D) {
-          more_values[j] =
-              *reinterpret_cast<const Raw*>(v_cache + static_cast<size_t>(v_row) * D + my_dim);
-        } else {
-          more_values[j] = Raw{};
-        }
-      }
-      float chunk_max = score;
-#pragma unroll
-      for (int offset = 16; offset > 0; offset >>= 1)
-        chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, offset));
-      const float new_max = fmaxf(running_max, chunk_max);
-      if (new_max == -INFINITY) continue;   // every key of the chunk unreadable
-      const float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
-      const float probability = valid ? expf(score - new_max) : 0.0f;
-      float chunk_sum = probability;
-#pragma unroll
-      for (int offset = 16; offset > 0; offset >>= 1)
-        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, offset);
-      running_sum = running_sum * correction + chunk_sum;
-      running_max = new_max;
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) acc[i] *= correction;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float p = __shfl_sync(0xffffffffu, probability, j);
-        float vv[DPL];
-        if (j < 16) {
-          unpack<T, DPL>(values[j], vv);
-        } else {
-          unpack<T, DPL>(more_values[j - 16], vv);
-        }
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p, vv[i], acc[i]);
-      }
-    } else {
-      // ---- any head size
-      if (valid) {
-        const T* k = k_cache + key_offset;
-        float dot = 0.0f;
-        for (int d = 0; d < D; d += VEC) {
-          float kv[VEC];
-          VecLoad<T, VEC>::load(k, kv);
-          k += chunk_stride;
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) dot = fmaf(qs[d + i], kv[i], dot);
-        }
-        score = dot * a.scale;
-      }
-      float chunk_max = score;
-#pragma unroll
-      for (int offset = 16; offset > 0; offset >>= 1)
-        chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, offset));
-      const float new_max = fmaxf(running_max, chunk_max);
-      if (new_max == -INFINITY) continue;
-      const float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
-      const float probability = valid ? expf(score - new_max) : 0.0f;
-      float chunk_sum = probability;
-#pragma unroll
-      for (int offset = 16; offset > 0; offset >>= 1)
-        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, offset);
-      running_sum = running_sum * correction + chunk_sum;
-      running_max = new_max;
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) acc[i] *= correction;
-      // values: eight keys at a time, their loads issued together; masked and unreadable
-      // keys are skipped, so a stale page is never read
-      for (int j0 = 0; j0 < keys_here; j0 += 8) {
-        float p8[8];
-        float vv[8][DPL];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          p8[u] = __shfl_sync(0xffffffffu, probability, j0 + u);
-          const int v_row = __shfl_sync(0xffffffffu, row, j0 + u);
-          if (v_row >= 0 && my_dim < D) {
-            VecLoad<T, DPL>::load(v_cache + static_cast<size_t>(v_row) * D + my_dim, vv[u]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) vv[u][i] = 0.0f;
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-#pragma unroll
-          for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p8[u], vv[u][i], acc[i]);
       }
     }
   }
-
-  finish_item<T, DPL>(a, token_head, token, head, split, n_splits, lane, D, acc, running_max,
+  finish_item<T, DPL>(a, item, lane, my_dim, my_dim < D ? DPL : 0, acc, running_max,
                       running_sum);
 }
 
-// ------------------------------------------------------------------ streaming variant
-//
-// bfloat16, head sizes 64 and 128, pages of 8, 16 or 32 keys, no window.  The keys of a
-// (page, head) are one contiguous block of the cache and so are its values, so a 32-key
-// chunk is fetched with a few bulk copies (cp.async.bulk, completion counted on an
-// mbarrier) into a ring of shared-memory slots that belongs to the warp.  The bytes in
-// flight no longer live in registers: two warps per CTA keep 96 KB of the cache on its way
-// to the SM, which is what it takes to stream the cache at memory speed.  Arithmetic, split
-// handling and the order of every sum are those of the kernel above.
+// ------------------------------------------------------------------ streaming kernel
+
 constexpr int STREAM_WARPS = 2;
 constexpr uint32_t STREAM_WAIT_LIMIT = 20u * 1000u * 1000u;
 
-__device__ __forceinline__ uint32_t shared_address(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
 __device__ __forceinline__ bool stream_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t address = shared_address(bar);
+  const uint32_t address = hx_shared_address(bar);
   for (uint32_t spin = 0; spin < STREAM_WAIT_LIMIT; ++spin) {
     uint32_t done;
     asm volatile(
@@ -458,7 +316,7 @@ __device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t b
                                           uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(shared_address(dst)), "l"(src), "r"(bytes), "r"(shared_address(bar))
+      ::"r"(hx_shared_address(dst)), "l"(src), "r"(bytes), "r"(hx_shared_address(bar))
       : "memory");
 }
 
@@ -470,47 +328,37 @@ struct StreamConfig {
   static constexpr int kSharedBytes = STREAM_WARPS * kRing * kSlotBytes;
 };
 
+// Shared-memory address of the 16-byte piece (key `key` of the chunk, coordinates 8c..8c+7)
+// inside a slot half that holds `32 / page_size` page blocks of [D/8][page_size][8].
+__device__ __forceinline__ uint32_t piece_address(uint32_t half_base, int key, int c,
+                                                  int page_size, uint32_t page_bytes) {
+  return half_base + (key / page_size) * page_bytes + ((c * page_size + key % page_size) << 4);
+}
+
 template <int D>
 __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kernel(
     AttentionArgs a) {
   using T = __nv_bfloat16;
   using Config = StreamConfig<D>;
-  constexpr int DPL = D / 32;
   constexpr int RING = Config::kRing;
-  constexpr int kKeyLoads = D / 8;
+  constexpr int kDSteps = D / 16;     // k-steps of q k^T
+  constexpr int kOBlocks = D / 8;     // 8-wide blocks of the output row
   extern __shared__ __align__(128) uint8_t stream_shared[];
   __shared__ uint64_t full_bar[STREAM_WARPS][RING];
-  __shared__ float q_shared[STREAM_WARPS][D];
   hx_pdl_prologue();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const long long item = static_cast<long long>(blockIdx.x) * STREAM_WARPS + warp;
-  const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
-  if (item >= items) return;
-  const int split = static_cast<int>(item % a.max_splits);
-  const long long token_head = item / a.max_splits;
-  const int head = static_cast<int>(token_head % a.heads);
-  const int token = static_cast<int>(token_head / a.heads);
-  if (skipped(a, token)) return;
-
-  int lo, hi;
-  key_range(a, token, lo, hi);          // no window here: lo == 0
-  const int n_splits = (hi - lo + a.split_keys - 1) / a.split_keys;
-  if (split >= n_splits) return;
-  const int begin = lo + split * a.split_keys;      // a multiple of 32, hence of the page size
-  const int end = min(begin + a.split_keys, hi);
+  Item item;
+  if (!find_item(a, static_cast<long long>(blockIdx.x) * STREAM_WARPS + warp, item)) return;
+  const int begin = item.begin;       // no window: a multiple of 32, hence of the page size
+  const int end = item.end;
   const int n_chunks = (end - begin + 31) / 32;
 
-  const int kv_head = head / (a.heads / a.kv_heads);
-  const T* q = static_cast<const T*>(a.q) + static_cast<size_t>(token) * a.ldq +
-               static_cast<size_t>(head) * D;
-  float* qs = q_shared[warp];
-  for (int d = lane; d < D; d += 32) qs[d] = __bfloat162float(q[d]);
-
+  const int kv_head = item.head / (a.heads / a.kv_heads);
   const int page_size = a.page_size;
   const int pages_per_chunk = 32 / page_size;
   const uint32_t page_bytes = static_cast<uint32_t>(page_size) * D * 2;
-  const int table_row = a.request_table_row[a.token_request[token]];
+  const int table_row = a.request_table_row[a.token_request[item.token]];
   const int* table = a.block_tables + static_cast<size_t>(table_row) * a.table_stride;
   const int first_page = begin / page_size;
   const int n_pages = (end - begin + page_size - 1) / page_size;
@@ -521,24 +369,15 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
 
   if (lane == 0) {
     for (int s = 0; s < RING; ++s)
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(shared_address(&bars[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(hx_shared_address(&bars[s])));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
 
-  // the block table entries of up to 32 pages at a time, one per lane
-  int window_first = 0;                 // index (within the split) of the page lane 0 holds
-  int my_page = -1;
-  auto load_pages = [&](int from) {
-    window_first = from;
-    const int index = from + lane;
-    my_page = index < n_pages ? table[first_page + index] : -1;
-    if (my_page >= a.num_pages) my_page = -1;
-  };
-  load_pages(0);
-
-  // request the pages of chunk `c` into its ring slot (every lane runs this; lane 0 issues)
+  // request the pages of chunk `c` into its ring slot; `bad` collects unreadable pages
+  bool bad = false;
   auto request_chunk = [&](int c) {
+    if (lane != 0) return;
     uint8_t* slot = ring + static_cast<size_t>(c % RING) * Config::kSlotBytes;
     uint64_t* bar = &bars[c % RING];
     int pages[4];
@@ -546,54 +385,57 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       pages[p] = -1;
-      if (p < pages_per_chunk) {
-        const int index = c * pages_per_chunk + p;
-        if (index >= window_first + 32) load_pages(index);
-        const int page = __shfl_sync(0xffffffffu, my_page, index - window_first);
-        if (index < n_pages && page >= 0) {
+      const int index = c * pages_per_chunk + p;
+      if (p < pages_per_chunk && index < n_pages) {
+        const int page = table[first_page + index];
+        if (page >= 0 && page < a.num_pages) {
           pages[p] = page;
           expected += 2 * page_bytes;
+        } else {
+          bad = true;
         }
       }
     }
-    if (lane == 0) {
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
-                       shared_address(bar)), "r"(expected) : "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                     hx_shared_address(bar)), "r"(expected) : "memory");
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        if (pages[p] >= 0) {
-          const size_t block = (static_cast<size_t>(pages[p]) * a.kv_heads + kv_head) * page_bytes;
-          bulk_copy(slot + p * page_bytes, k_cache + block, page_bytes, bar);
-          bulk_copy(slot + Config::kChunkBytes + p * page_bytes, v_cache + block, page_bytes, bar);
-        }
+    for (int p = 0; p < 4; ++p) {
+      if (pages[p] >= 0) {
+        const size_t block = (static_cast<size_t>(pages[p]) * a.kv_heads + kv_head) * page_bytes;
+        bulk_copy(slot + p * page_bytes, k_cache + block, page_bytes, bar);
+        bulk_copy(slot + Config::kChunkBytes + p * page_bytes, v_cache + block, page_bytes, bar);
       }
     }
   };
   const int ahead = n_chunks < RING ? n_chunks : RING;
   for (int c = 0; c < ahead; ++c) request_chunk(c);
+  bad = __shfl_sync(0xffffffffu, bad ? 1 : 0, 0) != 0;      // lane 0 looked the pages up
 
-  float acc[DPL];
+  // the query is row 0 of a 16-row tile: only lanes 0..3 hold non-zero A fragments
+  uint32_t q_frag[kDSteps][4];
+  {
+    const T* q = static_cast<const T*>(a.q) + static_cast<size_t>(item.token) * a.ldq +
+                 static_cast<size_t>(item.head) * D;
 #pragma unroll
-  for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
-  float running_max = -INFINITY;
-  float running_sum = 0.0f;
-  bool bad_page = false;
-
-  for (int c = 0; c < n_chunks; ++c) {
-    // is this lane's key there, and is its page readable?
-    const int key = begin + c * 32 + lane;
-    const int page_index = c * pages_per_chunk + lane / page_size;
-    // the window of table entries may have moved on while requesting ahead: look it up again
-    int page = -1;
-    if (key < end) {
-      page = table[first_page + page_index];
-      if (page < 0 || page >= a.num_pages) {
-        page = -1;
-        bad_page = true;
+    for (int k = 0; k < kDSteps; ++k) {
+      q_frag[k][0] = q_frag[k][1] = q_frag[k][2] = q_frag[k][3] = 0u;
+      if (lane < 4) {
+        q_frag[k][0] = *reinterpret_cast<const uint32_t*>(q + k * 16 + 2 * lane);
+        q_frag[k][2] = *reinterpret_cast<const uint32_t*>(q + k * 16 + 8 + 2 * lane);
       }
     }
-    const bool valid = page >= 0;
+  }
 
+  // row 0 of the output lives in c0, c1 of lanes 0..3: coordinates 8 n + 2 lane + {0, 1}
+  float o_acc[kOBlocks][4];
+#pragma unroll
+  for (int n = 0; n < kOBlocks; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o_acc[n][e] = 0.0f;
+  float running_max = -INFINITY;
+  float running_sum = 0.0f;      // this lane's share of the row sum (lanes 0..3)
+
+  for (int c = 0; c < n_chunks; ++c) {
     bool arrived = true;
     if (lane == 0) arrived = stream_wait(&bars[c % RING], static_cast<uint32_t>(c / RING) & 1u);
     arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
@@ -601,47 +443,106 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
       if (lane == 0 && a.status != nullptr) atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
       return;
     }
-    const uint8_t* slot = ring + static_cast<size_t>(c % RING) * Config::kSlotBytes;
+    const uint32_t k_half = hx_shared_address(ring + static_cast<size_t>(c % RING) * Config::kSlotBytes);
+    const uint32_t v_half = k_half + Config::kChunkBytes;
+    const int keys_here = min(32, end - (begin + c * 32));
 
-    float score = -INFINITY;
-    if (valid) {
-      const uint8_t* k = slot + (lane / page_size) * page_bytes + (lane % page_size) * 16;
-      float dot = 0.0f;
-#pragma unroll
-      for (int u = 0; u < kKeyLoads; ++u) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(k + static_cast<size_t>(u) * page_size * 16);
-        float kv[8];
-        VecLoad<T, 8>::load(reinterpret_cast<const T*>(&raw), kv);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) dot = fmaf(qs[u * 8 + i], kv[i], dot);
+    // Whatever lies behind the last key of the request in its last page, and pages that
+    // could not be read, must not reach the second product (0 * NaN is NaN): clear those
+    // value rows.  Keys need no clearing: their scores are masked by selection.
+    if (keys_here < 32 || bad) {
+      for (int index = lane; index < 32 * (D / 8); index += 32) {
+        const int key = index / (D / 8);
+        const int piece = index - key * (D / 8);
+        bool clear = key >= keys_here;
+        if (!clear && bad) {
+          const int page = table[first_page + c * pages_per_chunk + key / page_size];
+          clear = page < 0 || page >= a.num_pages;
+        }
+        if (clear) {
+          const uint32_t address = piece_address(v_half, key, piece, page_size, page_bytes);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(address), "r"(0u) : "memory");
+        }
       }
-      score = dot * a.scale;
+      __syncwarp();
     }
-    float chunk_max = score;
+
+    // ---- s = q k^T for the 32 keys: 4 blocks of 8 keys
+    float s[4][4];
 #pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1)
-      chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, offset));
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[n][e] = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kDSteps; ++k) {
+#pragma unroll
+      for (int pair = 0; pair < 2; ++pair) {
+        // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+        const int matrix = lane >> 3;
+        const int key = pair * 16 + (matrix >> 1) * 8 + (lane & 7);
+        uint32_t b[4];
+        hx_ldmatrix_x4(b, piece_address(k_half, key, k * 2 + (matrix & 1), page_size, page_bytes));
+        hx_mma_bf16(s[pair * 2], q_frag[k], b[0], b[1]);
+        hx_mma_bf16(s[pair * 2 + 1], q_frag[k], b[2], b[3]);
+      }
+    }
+
+    // ---- scale, mask, online softmax of row 0 (held by lanes 0..3 in c0, c1)
+    float chunk_max = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = n * 8 + 2 * (lane & 3) + e;
+        bool visible = key < keys_here;
+        if (visible && bad) {
+          const int page = table[first_page + c * pages_per_chunk + key / page_size];
+          visible = page >= 0 && page < a.num_pages;
+        }
+        const float value = visible ? s[n][e] * a.scale : -INFINITY;
+        s[n][e] = value;
+        chunk_max = fmaxf(chunk_max, value);
+      }
+    }
+    chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 1));
+    chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 2));
+    chunk_max = __shfl_sync(0xffffffffu, chunk_max, 0);      // every lane follows row 0
     const float new_max = fmaxf(running_max, chunk_max);
     if (new_max != -INFINITY) {
       const float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
-      const float probability = valid ? expf(score - new_max) : 0.0f;
-      float chunk_sum = probability;
-#pragma unroll
-      for (int offset = 16; offset > 0; offset >>= 1)
-        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, offset);
-      running_sum = running_sum * correction + chunk_sum;
       running_max = new_max;
+      running_sum *= correction;
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) acc[i] *= correction;
-      const uint8_t* v = slot + Config::kChunkBytes + lane * DPL * 2;
-#pragma unroll 8
-      for (int j = 0; j < 32; ++j) {
-        const float p = __shfl_sync(0xffffffffu, probability, j);
-        if (p != 0.0f) {      // masked and unreadable keys: their slots may hold anything
-          float vv[DPL];
-          VecLoad<T, DPL>::load(reinterpret_cast<const T*>(v + static_cast<size_t>(j) * D * 2), vv);
+      for (int n = 0; n < kOBlocks; ++n) {
+        o_acc[n][0] *= correction;
+        o_acc[n][1] *= correction;
+      }
+      // ---- o += p v with p = hi + lo; rows 1..15 of p are zero
 #pragma unroll
-          for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p, vv[i], acc[i]);
+      for (int kk = 0; kk < 2; ++kk) {
+        uint32_t p_hi[4] = {0u, 0u, 0u, 0u}, p_lo[4] = {0u, 0u, 0u, 0u};
+        if (lane < 4) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const float x0 = expf(s[kk * 2 + half][0] - new_max);
+            const float x1 = expf(s[kk * 2 + half][1] - new_max);
+            running_sum += x0 + x1;
+            hx_split_bf16(x0, x1, p_hi[half * 2], p_lo[half * 2]);
+          }
+        }
+#pragma unroll
+        for (int nn = 0; nn < kOBlocks / 2; ++nn) {
+          // transposed load of v[keys kk*16 .. +15][d nn*16 .. +15]:
+          // matrices (keys 0-7, d lo), (keys 8-15, d lo), (keys 0-7, d hi), (keys 8-15, d hi)
+          const int matrix = lane >> 3;
+          const int key = kk * 16 + (matrix & 1) * 8 + (lane & 7);
+          uint32_t b[4];
+          hx_ldmatrix_x4_trans(b, piece_address(v_half, key, nn * 2 + (matrix >> 1), page_size,
+                                                page_bytes));
+          hx_mma_bf16(o_acc[nn * 2], p_hi, b[0], b[1]);
+          hx_mma_bf16(o_acc[nn * 2], p_lo, b[0], b[1]);
+          hx_mma_bf16(o_acc[nn * 2 + 1], p_hi, b[2], b[3]);
+          hx_mma_bf16(o_acc[nn * 2 + 1], p_lo, b[2], b[3]);
         }
       }
     }
@@ -650,11 +551,52 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
       // the slot is free: order this warp's reads before the copy engine's writes
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       request_chunk(c + RING);
+      bad = __shfl_sync(0xffffffffu, bad ? 1 : 0, 0) != 0;
     }
   }
-  if (bad_page && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
-  finish_item<T, DPL>(a, token_head, token, head, split, n_splits, lane, D, acc, running_max,
-                      running_sum);
+  if (lane == 0 && bad && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
+
+  // the row sum is spread over lanes 0..3; the output row over the same lanes, two
+  // coordinates of every 8-wide block each: hand each lane's share to finish_item as
+  // kOBlocks pieces of two coordinates
+  running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 1);
+  running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 2);
+  running_sum = __shfl_sync(0xffffffffu, running_sum, 0);
+
+  if (item.n_splits == 1) {
+    if (lane < 4) {
+      const float inverse = 1.0f / running_sum;
+      T* out = static_cast<T*>(a.out) + static_cast<size_t>(item.token) * a.ldo +
+               static_cast<size_t>(item.head) * D + 2 * lane;
+#pragma unroll
+      for (int n = 0; n < kOBlocks; ++n)
+        *reinterpret_cast<__nv_bfloat162*>(out + n * 8) =
+            __floats2bfloat162_rn(o_acc[n][0] * inverse, o_acc[n][1] * inverse);
+    }
+    return;
+  }
+  float* part = a.partial +
+                (static_cast<size_t>(item.token_head) * a.max_splits + item.split) * (D + 2);
+  if (lane < 4) {
+#pragma unroll
+    for (int n = 0; n < kOBlocks; ++n) {
+      part[n * 8 + 2 * lane] = o_acc[n][0];
+      part[n * 8 + 2 * lane + 1] = o_acc[n][1];
+    }
+  }
+  if (lane == 0) {
+    part[D] = running_max;
+    part[D + 1] = running_sum;
+  }
+  __threadfence();
+  __syncwarp();
+  int arrived_count = 0;
+  if (lane == 0) arrived_count = atomicAdd(a.arrivals + item.token_head, 1);
+  arrived_count = __shfl_sync(0xffffffffu, arrived_count, 0);
+  if (arrived_count != item.n_splits - 1) return;
+  __threadfence();
+  if (lane == 0) a.arrivals[item.token_head] = 0;
+  merge_splits<T>(a, item, lane);
 }
 
 template <int D>
@@ -679,53 +621,40 @@ int launch_stream(const AttentionArgs& a, cudaStream_t stream) {
   return HX_OK;
 }
 
-bool stream_variant_applies(const AttentionArgs& a, int dtype) {
+bool stream_kernel_applies(const AttentionArgs& a, int dtype) {
   return dtype == HX_BF16 && (a.head_dim == 64 || a.head_dim == 128) && a.window == 0 &&
          (a.page_size == 8 || a.page_size == 16 || a.page_size == 32) && a.split_keys % 32 == 0;
 }
 
-template <typename T, int DPL, int VEC, int HD = 0>
-void launch_main(const AttentionArgs& a, cudaStream_t stream) {
+template <typename T>
+int launch_cuda_cores(const AttentionArgs& a, cudaStream_t stream) {
   const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
   const int blocks = static_cast<int>((items + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
-  hx_launch(paged_attention_kernel<T, DPL, VEC, HD>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
-}
-
-template <typename T, int DPL>
-int dispatch_vec(const AttentionArgs& a, cudaStream_t stream) {
-  constexpr int kMaxVec = sizeof(T) == 2 ? 8 : 4;
-  if (kMaxVec == 8 && a.head_dim % 8 == 0) {
-    launch_main<T, DPL, 8>(a, stream);
-  } else if (a.head_dim % 4 == 0) {
-    launch_main<T, DPL, 4>(a, stream);
+  if (a.head_dim % 2 != 0 || a.head_dim > MAX_HEAD_DIM) {
+    hx_set_error("hx_paged_attention: head_dim %d is not supported (even, at most %d)",
+                 a.head_dim, MAX_HEAD_DIM);
+    return HX_ERR_UNSUPPORTED;
+  }
+  if (a.head_dim <= 64) {
+    hx_launch(paged_attention_kernel<T, 2>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
+  } else if (a.head_dim <= 128 && a.head_dim % 4 == 0) {
+    hx_launch(paged_attention_kernel<T, 4>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
+  } else if (a.head_dim % 8 == 0) {
+    hx_launch(paged_attention_kernel<T, 8>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
   } else {
-    launch_main<T, DPL, 2>(a, stream);
+    hx_set_error("hx_paged_attention: head_dim %d is not supported (above 64 a multiple of 4, "
+                 "above 128 a multiple of 8)", a.head_dim);
+    return HX_ERR_UNSUPPORTED;
   }
   return HX_OK;
 }
 
-template <typename T>
-int dispatch(const AttentionArgs& a, cudaStream_t stream) {
-  constexpr int kMaxVec = sizeof(T) == 2 ? 8 : 4;
-  if constexpr (sizeof(T) == 2) {   // float32 rows of 128 would not fit in registers
-    if (a.head_dim == 128) {
-      launch_main<T, 4, kMaxVec, 128>(a, stream);
-      return HX_OK;
-    }
-  }
-  if (a.head_dim == 64) {
-    launch_main<T, 2, kMaxVec, 64>(a, stream);
-    return HX_OK;
-  }
-  if (a.head_dim <= 64 && a.head_dim % 2 == 0) return dispatch_vec<T, 2>(a, stream);
-  if (a.head_dim <= 128 && a.head_dim % 4 == 0) return dispatch_vec<T, 4>(a, stream);
-  if (a.head_dim <= 256 && a.head_dim % 8 == 0) return dispatch_vec<T, 8>(a, stream);
-  hx_set_error("hx_paged_attention: head_dim %d is not supported (even up to 64, a multiple of "
-               "4 up to 128, a multiple of 8 up to 256)", a.head_dim);
-  return HX_ERR_UNSUPPORTED;
-}
-
 }  // namespace
+
+// Elements per chunk of the cache layout for this dtype and head size (see hx_cache_offset).
+HX_API int hx_cache_chunk_elements(int dtype, int head_dim) {
+  return hx_cache_chunk(dtype == HX_F32 ? 4 : 2, head_dim);
+}
 
 // Floats of scratch the call needs in `partial` (0 when max_splits == 1); the same call
 // needs tokens * heads ints of zeroed scratch in `arrivals`.
@@ -756,24 +685,21 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
              "hx_paged_attention: request_start missing");
   HX_REQUIRE(ldq >= heads * head_dim && ldo >= heads * head_dim,
              "hx_paged_attention: row strides too small");
-  HX_REQUIRE(static_cast<long long>(num_pages) * kv_heads * page_size < (1ll << 31),
-             "hx_paged_attention: cache rows exceed 32-bit indexing");
+  HX_REQUIRE(dtype == HX_F32 || dtype == HX_BF16, "hx_paged_attention: unknown dtype %d", dtype);
   if (tokens == 0) return HX_OK;
   AttentionArgs a{q, ldq, k_cache, v_cache, positions, token_request, request_table_row,
                   block_tables, table_stride, request_start, skip_query_len, out, ldo, partial,
                   arrivals, tokens, heads, kv_heads, head_dim, page_size, num_pages, window, scale,
                   split_keys, max_splits, status};
   const long long items = static_cast<long long>(tokens) * heads * max_splits;
-  HX_REQUIRE(items / WARPS_PER_BLOCK < (1ll << 31) - 1, "hx_paged_attention: grid too large");
+  HX_REQUIRE(items / STREAM_WARPS < (1ll << 31) - 1, "hx_paged_attention: grid too large");
   int rc;
-  if (stream_variant_applies(a, dtype)) {
-    rc = a.head_dim == 128 ? launch_stream<128>(a, stream) : launch_stream<64>(a, stream);
+  if (stream_kernel_applies(a, dtype)) {
+    rc = head_dim == 128 ? launch_stream<128>(a, stream) : launch_stream<64>(a, stream);
   } else if (dtype == HX_F32) {
-    rc = dispatch<float>(a, stream);
-  } else if (dtype == HX_BF16) {
-    rc = dispatch<__nv_bfloat16>(a, stream);
+    rc = launch_cuda_cores<float>(a, stream);
   } else {
-    HX_REQUIRE(false, "hx_paged_attention: unknown dtype %d", dtype);
+    rc = launch_cuda_cores<__nv_bfloat16>(a, stream);
   }
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_paged_attention");

@@ -21,7 +21,7 @@
 // Requests with fewer than `min_query_len` tokens in the step are left to the CUDA-core
 // kernel (hx_paged_attention skips the others), so decode tokens beside prompt portions
 // are each handled by the kernel that suits them.
-#include "hx_common.cuh"
+#include "hx_mma.cuh"
 
 namespace {
 
@@ -50,46 +50,6 @@ struct PrefillArgs {
   int min_query_len;
   int* status;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-// 16-byte copy global -> shared; `bytes` == 0 writes zeros and reads nothing.
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-
-// D (16x8, f32) += A (16x16, bf16, row) * B (16x8, bf16, col)
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
-      "{%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
 
 // Tiles are [rows][D] bf16 with the 16-byte chunks of a row XOR-swizzled by the row number,
 // so that the eight rows an ldmatrix touches fall into different banks.
@@ -150,18 +110,18 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
     const bool valid = row < rows_here;
     const __nv_bfloat16* src = a.q + static_cast<size_t>(q_begin + row0 + (valid ? row : 0)) * a.ldq +
                                static_cast<size_t>(head) * D + chunk * 8;
-    cp_async_16(smem_u32(q_tile) + tile_offset<D>(row, chunk), src, valid ? 16 : 0);
+    hx_cp_async_16(hx_shared_address(q_tile) + tile_offset<D>(row, chunk), src, valid ? 16 : 0);
   }
 
   auto load_kv_tile = [&](int tile, int stage) {
-    const uint32_t k_dst = smem_u32(kv_tiles + stage * 2 * kTileBytes);
+    const uint32_t k_dst = hx_shared_address(kv_tiles + stage * 2 * kTileBytes);
     const uint32_t v_dst = k_dst + kTileBytes;
     for (int index = tid; index < BLOCK_N * kChunks; index += THREADS) {
       const int row = index / kChunks;
       const int chunk = index - row * kChunks;
       const int key = tile * BLOCK_N + row;
       bool valid = key <= last_key;
-      size_t key_element = 0, value_element = 0;
+      size_t cache_element = 0;
       if (valid) {
         const int page = table[key / a.page_size];
         if (page < 0 || page >= a.num_pages) {
@@ -169,20 +129,18 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
           valid = false;
         } else {
           const int slot = key % a.page_size;
-          // values: [page][kv_head][slot][D]; keys: 16-byte chunks, slot-major (hx_key_offset)
-          value_element = ((static_cast<size_t>(page) * a.kv_heads + kv_head) * a.page_size + slot) * D +
-                          chunk * 8;
-          key_element = hx_key_offset(page, kv_head, slot, chunk * 8, a.kv_heads, a.page_size, D, 8);
+          // keys and values share one layout: 16-byte chunks, slot-major (hx_cache_offset)
+          cache_element = hx_cache_offset(page, kv_head, slot, chunk * 8, a.kv_heads, a.page_size, D, 8);
         }
       }
       const uint32_t offset = tile_offset<D>(row, chunk);
-      cp_async_16(k_dst + offset, a.k_cache + key_element, valid ? 16 : 0);
-      cp_async_16(v_dst + offset, a.v_cache + value_element, valid ? 16 : 0);
+      hx_cp_async_16(k_dst + offset, a.k_cache + cache_element, valid ? 16 : 0);
+      hx_cp_async_16(v_dst + offset, a.v_cache + cache_element, valid ? 16 : 0);
     }
   };
 
   load_kv_tile(0, 0);
-  cp_async_commit();      // group 0: Q and the first K/V tile
+  hx_cp_async_commit();      // group 0: Q and the first K/V tile
 
   // ---- per-thread state: this thread owns rows (lane / 4) and (lane / 4 + 8) of its warp
   float o_acc[kOBlocks][4];
@@ -201,10 +159,10 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
     const int stage = tile & 1;
     if (tile + 1 < n_tiles) {
       load_kv_tile(tile + 1, stage ^ 1);
-      cp_async_commit();
-      cp_async_wait<1>();
+      hx_cp_async_commit();
+      hx_cp_async_wait<1>();
     } else {
-      cp_async_wait<0>();
+      hx_cp_async_wait<0>();
     }
     __syncthreads();
 
@@ -213,11 +171,11 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
       for (int k = 0; k < kDSteps; ++k) {
         const int row = warp_row + (lane & 15);
         const int chunk = k * 2 + (lane >> 4);
-        ldmatrix_x4(q_frag[k], smem_u32(q_tile) + tile_offset<D>(row, chunk));
+        hx_ldmatrix_x4(q_frag[k], hx_shared_address(q_tile) + tile_offset<D>(row, chunk));
       }
     }
 
-    const uint32_t k_base = smem_u32(kv_tiles + stage * 2 * kTileBytes);
+    const uint32_t k_base = hx_shared_address(kv_tiles + stage * 2 * kTileBytes);
     const uint32_t v_base = k_base + kTileBytes;
 
     // ---- S = Q K^T for 16 rows x 64 keys: 8 n-blocks of 8 keys
@@ -235,9 +193,9 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
         const int key_row = pair * 16 + (matrix >> 1) * 8 + (lane & 7);
         const int chunk = k * 2 + (matrix & 1);
         uint32_t b[4];
-        ldmatrix_x4(b, k_base + tile_offset<D>(key_row, chunk));
-        mma_bf16(s[pair * 2], q_frag[k], b[0], b[1]);
-        mma_bf16(s[pair * 2 + 1], q_frag[k], b[2], b[3]);
+        hx_ldmatrix_x4(b, k_base + tile_offset<D>(key_row, chunk));
+        hx_mma_bf16(s[pair * 2], q_frag[k], b[0], b[1]);
+        hx_mma_bf16(s[pair * 2 + 1], q_frag[k], b[2], b[3]);
       }
     }
 
@@ -292,16 +250,10 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
         }
       uint32_t p_hi[4], p_lo[4];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int half = 0; half < 2; ++half)
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const float x0 = p[half][r * 2], x1 = p[half][r * 2 + 1];
-          const __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
-          const __nv_bfloat162 hi = __halves2bfloat162(h0, h1);
-          p_hi[half * 2 + r] = *reinterpret_cast<const uint32_t*>(&hi);
-          p_lo[half * 2 + r] = pack_bf16(x0 - __bfloat162float(h0), x1 - __bfloat162float(h1));
-        }
-      }
+        for (int r = 0; r < 2; ++r)
+          hx_split_bf16(p[half][r * 2], p[half][r * 2 + 1], p_hi[half * 2 + r], p_lo[half * 2 + r]);
 #pragma unroll
       for (int nn = 0; nn < kOBlocks / 2; ++nn) {
         // transposed load of V[keys kk*16 .. +15][d nn*16 .. +15]:
@@ -310,11 +262,11 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
         const int key_row = kk * 16 + (matrix & 1) * 8 + (lane & 7);
         const int chunk = nn * 2 + (matrix >> 1);
         uint32_t b[4];
-        ldmatrix_x4_trans(b, v_base + tile_offset<D>(key_row, chunk));
-        mma_bf16(o_acc[nn * 2], p_hi, b[0], b[1]);
-        mma_bf16(o_acc[nn * 2], p_lo, b[0], b[1]);
-        mma_bf16(o_acc[nn * 2 + 1], p_hi, b[2], b[3]);
-        mma_bf16(o_acc[nn * 2 + 1], p_lo, b[2], b[3]);
+        hx_ldmatrix_x4_trans(b, v_base + tile_offset<D>(key_row, chunk));
+        hx_mma_bf16(o_acc[nn * 2], p_hi, b[0], b[1]);
+        hx_mma_bf16(o_acc[nn * 2], p_lo, b[0], b[1]);
+        hx_mma_bf16(o_acc[nn * 2 + 1], p_hi, b[2], b[3]);
+        hx_mma_bf16(o_acc[nn * 2 + 1], p_lo, b[2], b[3]);
       }
     }
     __syncthreads();      // every warp is done with this stage before it is refilled

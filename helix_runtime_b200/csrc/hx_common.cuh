@@ -143,24 +143,25 @@ __device__ __forceinline__ float hx_block_max(float value, float* scratch) {
   return total;
 }
 
-// ------------------------------------------------------------------ key cache layout
+// ---------------------------------------------------------------------- cache layout
 //
-// Values are stored [page][kv_head][slot][head_dim].  Keys are stored in chunks of
-// `chunk` elements (16 bytes where the head size allows): [page][kv_head][head_dim / chunk]
-// [slot][chunk], so that the lanes of a warp, each owning one key (one slot), read
-// consecutive 16-byte pieces: the key phase of attention is then a coalesced stream.
-__host__ __device__ __forceinline__ int hx_key_chunk(int element_bytes, int head_dim) {
+// Keys and values of one layer are stored alike, in chunks of `chunk` elements (16 bytes
+// where the head size allows): [page][kv_head][head_dim / chunk][slot][chunk].  All keys
+// (or values) of a (page, head) are one contiguous block that a single bulk copy brings to
+// shared memory; inside it the 16-byte pieces of consecutive slots are adjacent, which is
+// the row order the tensor-core loads (ldmatrix) want and what lets a warp whose lanes each
+// own one key read a coalesced stream.
+__host__ __device__ __forceinline__ int hx_cache_chunk(int element_bytes, int head_dim) {
   const int widest = 16 / element_bytes;
   if (head_dim % widest == 0) return widest;
-  if (widest >= 8 && head_dim % 4 == 0) return 4;
-  if (head_dim % 4 == 0 && widest >= 4) return 4;
+  if (widest > 4 && head_dim % 4 == 0) return 4;
   return 2;
 }
 
-// Element offset of coordinate `dim` of the key in (page, kv_head, slot).
-__host__ __device__ __forceinline__ size_t hx_key_offset(int page, int kv_head, int slot, int dim,
-                                                         int kv_heads, int page_size,
-                                                         int head_dim, int chunk) {
+// Element offset of coordinate `dim` of the key (or value) in (page, kv_head, slot).
+__host__ __device__ __forceinline__ size_t hx_cache_offset(int page, int kv_head, int slot,
+                                                           int dim, int kv_heads, int page_size,
+                                                           int head_dim, int chunk) {
   const size_t page_head = static_cast<size_t>(page) * kv_heads + kv_head;
   return ((page_head * (head_dim / chunk) + dim / chunk) * page_size + slot) * chunk + dim % chunk;
 }

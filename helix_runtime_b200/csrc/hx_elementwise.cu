@@ -248,7 +248,8 @@ HX_API int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int i
 //
 // qkv row: [q heads | k heads | v heads], each head `head_dim` wide.
 // pairing 0: pairs (2p, 2p+1); pairing 1: pairs (p, p + rotary_dim/2).
-// cache layer: [page][kv_head][slot in page][head_dim].
+// cache layer (keys and values alike): [page][kv_head][head_dim / chunk][slot][chunk],
+// see hx_cache_offset.
 constexpr int ROPE_HEADS_PER_BLOCK = 4;
 
 template <typename T>
@@ -341,17 +342,15 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
           vec[i1] = tb;
         } else if (page >= 0) {
           const int kv_head = head - heads;
-          // keys are stored in 16-byte chunks, slot-major inside a chunk (see hx_key_offset)
-          const int key_chunk = hx_key_chunk(sizeof(T), head_dim);
-          k_cache[hx_key_offset(page, kv_head, slot, i0, kv_heads, page_size, head_dim, key_chunk)] = ta;
-          k_cache[hx_key_offset(page, kv_head, slot, i1, kv_heads, page_size, head_dim, key_chunk)] = tb;
+          // 16-byte chunks, slot-major inside a chunk (see hx_cache_offset)
+          const int chunk = hx_cache_chunk(sizeof(T), head_dim);
+          k_cache[hx_cache_offset(page, kv_head, slot, i0, kv_heads, page_size, head_dim, chunk)] = ta;
+          k_cache[hx_cache_offset(page, kv_head, slot, i1, kv_heads, page_size, head_dim, chunk)] = tb;
         }
       }
     } else {
       const int kv_head = head - heads - kv_heads;
-      T* dst = page >= 0 ? v_cache + ((static_cast<size_t>(page) * kv_heads + kv_head) * page_size +
-                                      slot) * head_dim
-                         : nullptr;
+      const int chunk = hx_cache_chunk(sizeof(T), head_dim);
       float* source = accum_row != nullptr ? accum_row + static_cast<size_t>(head) * head_dim
                                            : nullptr;
       for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
@@ -362,7 +361,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
         } else {
           value = vec[d];
         }
-        if (dst != nullptr) dst[d] = value;
+        if (page >= 0)
+          v_cache[hx_cache_offset(page, kv_head, slot, d, kv_heads, page_size, head_dim, chunk)] = value;
       }
     }
   }

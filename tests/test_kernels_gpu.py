@@ -33,8 +33,8 @@ def status_word():
     return torch.zeros(1, dtype=torch.int32, device=DEVICE)
 
 
-def key_chunk(dtype, head_dim):
-    """Elements per 16-byte chunk of the key cache (the widest of 16 bytes, 4 or 2 elements
+def cache_chunk(dtype, head_dim):
+    """Elements per 16-byte chunk of the cache layout (the widest of 16 bytes, 4 or 2 elements
     that divides the head size)."""
     widest = 8 if dtype == torch.bfloat16 else 4
     for chunk in (widest, 4, 2):
@@ -43,17 +43,17 @@ def key_chunk(dtype, head_dim):
     raise ValueError(head_dim)
 
 
-def keys_to_cache_layout(keys, dtype):
+def to_cache_layout(keys, dtype):
     """[page, kv_head, slot, dim] -> the cache's [page, kv_head, dim / chunk, slot, chunk]
     (kept in an array of the same shape)."""
     pages, heads, slots, dim = keys.shape
-    c = key_chunk(dtype, dim)
+    c = cache_chunk(dtype, dim)
     return keys.reshape(pages, heads, slots, dim // c, c).transpose(0, 1, 3, 2, 4).reshape(keys.shape)
 
 
-def keys_from_cache_layout(cache, dtype):
+def from_cache_layout(cache, dtype):
     pages, heads, slots, dim = cache.shape
-    c = key_chunk(dtype, dim)
+    c = cache_chunk(dtype, dim)
     return cache.reshape(pages, heads, dim // c, slots, c).transpose(0, 1, 3, 2, 4).reshape(cache.shape)
 
 
@@ -270,7 +270,7 @@ def test_rope_and_cache_append(dtype, heads, kv_heads, head_dim, rotary_dim, pai
     assert_close(result[:, :heads * head_dim].reshape(q.shape), q_expected, "rotated queries", **tol)
     np.testing.assert_array_equal(result[:, (heads + kv_heads) * head_dim:],
                                   qkv[:, (heads + kv_heads) * head_dim:])
-    keys, values = keys_from_cache_layout(host(k_cache), dtype), host(v_cache)
+    keys, values = from_cache_layout(host(k_cache), dtype), from_cache_layout(host(v_cache), dtype)
     written = np.zeros((num_pages, page_size), dtype=bool)
     for t in range(tokens):
         page = tables[slots[token_request[t]], positions[t] // page_size]
@@ -372,15 +372,15 @@ def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, n
     if tensor_core_min:
         # requests with at least that many tokens on the tensor cores, the rest (if any) on
         # the CUDA cores: together they must fill every row
-        ops.prefill_attention(dev(q, dtype), dev(keys_to_cache_layout(k_cache, dtype), dtype),
-                              dev(v_cache, dtype), starts,
+        ops.prefill_attention(dev(q, dtype), dev(to_cache_layout(k_cache, dtype), dtype),
+                              dev(to_cache_layout(v_cache, dtype), dtype), starts,
                               dev(contexts, torch.int32), dev(slots, torch.int32),
                               dev(tables, torch.int32), out, requests, tokens // 64 + requests,
                               heads, kv_heads, head_dim, page_size, num_pages, scale,
                               tensor_core_min, status)
     if not tensor_core_min or min(new_tokens) < tensor_core_min:
-        ops.paged_attention(dev(q, dtype), dev(keys_to_cache_layout(k_cache, dtype), dtype),
-                            dev(v_cache, dtype),
+        ops.paged_attention(dev(q, dtype), dev(to_cache_layout(k_cache, dtype), dtype),
+                            dev(to_cache_layout(v_cache, dtype), dtype),
                             dev(positions, torch.int32), dev(token_request, torch.int32),
                             dev(slots, torch.int32), dev(tables, torch.int32), out, partial, tokens,
                             heads, kv_heads, head_dim, page_size, num_pages, window or 0, scale,
