@@ -324,7 +324,7 @@ template <int D>
 struct StreamConfig {
   static constexpr int kChunkBytes = 32 * D * 2;     // keys (or values) of a 32-key chunk
   static constexpr int kSlotBytes = 2 * kChunkBytes;
-  static constexpr int kRing = D == 128 ? 3 : 4;
+  static constexpr int kRing = 2;     // 64 KB (32 KB) per CTA: three (six) CTAs share an SM
   static constexpr int kSharedBytes = STREAM_WARPS * kRing * kSlotBytes;
 };
 
@@ -426,6 +426,21 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
     }
   }
 
+  // Where this lane's ldmatrix rows sit inside a slot half never changes from chunk to chunk:
+  // work the offsets out once.  Keys: matrices (keys 0-7, d lo), (keys 0-7, d hi),
+  // (keys 8-15, d lo), (keys 8-15, d hi) of each 16-key pair; values (transposed load):
+  // (keys 0-7, d lo), (keys 8-15, d lo), (keys 0-7, d hi), (keys 8-15, d hi).
+  const int matrix = lane >> 3;
+  const uint32_t piece_step = static_cast<uint32_t>(page_size) * 32;   // two 16-byte pieces on
+  uint32_t k_offset[2], v_offset[2];
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int k_key = half * 16 + (matrix >> 1) * 8 + (lane & 7);
+    k_offset[half] = piece_address(0, k_key, matrix & 1, page_size, page_bytes);
+    const int v_key = half * 16 + (matrix & 1) * 8 + (lane & 7);
+    v_offset[half] = piece_address(0, v_key, matrix >> 1, page_size, page_bytes);
+  }
+
   // row 0 of the output lives in c0, c1 of lanes 0..3: coordinates 8 n + 2 lane + {0, 1}
   float o_acc[kOBlocks][4];
 #pragma unroll
@@ -477,11 +492,8 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
     for (int k = 0; k < kDSteps; ++k) {
 #pragma unroll
       for (int pair = 0; pair < 2; ++pair) {
-        // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
-        const int matrix = lane >> 3;
-        const int key = pair * 16 + (matrix >> 1) * 8 + (lane & 7);
         uint32_t b[4];
-        hx_ldmatrix_x4(b, piece_address(k_half, key, k * 2 + (matrix & 1), page_size, page_bytes));
+        hx_ldmatrix_x4(b, k_half + k_offset[pair] + k * piece_step);
         hx_mma_bf16(s[pair * 2], q_frag[k], b[0], b[1]);
         hx_mma_bf16(s[pair * 2 + 1], q_frag[k], b[2], b[3]);
       }
@@ -489,19 +501,30 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
 
     // ---- scale, mask, online softmax of row 0 (held by lanes 0..3 in c0, c1)
     float chunk_max = -INFINITY;
+    if (keys_here == 32 && !bad) {
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
+      for (int n = 0; n < 4; ++n) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int key = n * 8 + 2 * (lane & 3) + e;
-        bool visible = key < keys_here;
-        if (visible && bad) {
-          const int page = table[first_page + c * pages_per_chunk + key / page_size];
-          visible = page >= 0 && page < a.num_pages;
+        for (int e = 0; e < 2; ++e) {
+          s[n][e] *= a.scale;
+          chunk_max = fmaxf(chunk_max, s[n][e]);
         }
-        const float value = visible ? s[n][e] * a.scale : -INFINITY;
-        s[n][e] = value;
-        chunk_max = fmaxf(chunk_max, value);
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = n * 8 + 2 * (lane & 3) + e;
+          bool visible = key < keys_here;
+          if (visible && bad) {
+            const int page = table[first_page + c * pages_per_chunk + key / page_size];
+            visible = page >= 0 && page < a.num_pages;
+          }
+          const float value = visible ? s[n][e] * a.scale : -INFINITY;
+          s[n][e] = value;
+          chunk_max = fmaxf(chunk_max, value);
+        }
       }
     }
     chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 1));
@@ -509,7 +532,7 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
     chunk_max = __shfl_sync(0xffffffffu, chunk_max, 0);      // every lane follows row 0
     const float new_max = fmaxf(running_max, chunk_max);
     if (new_max != -INFINITY) {
-      const float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
+      const float correction = running_max == -INFINITY ? 0.0f : __expf(running_max - new_max);
       running_max = new_max;
       running_sum *= correction;
 #pragma unroll
@@ -524,21 +547,16 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
         if (lane < 4) {
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
-            const float x0 = expf(s[kk * 2 + half][0] - new_max);
-            const float x1 = expf(s[kk * 2 + half][1] - new_max);
+            const float x0 = __expf(s[kk * 2 + half][0] - new_max);
+            const float x1 = __expf(s[kk * 2 + half][1] - new_max);
             running_sum += x0 + x1;
             hx_split_bf16(x0, x1, p_hi[half * 2], p_lo[half * 2]);
           }
         }
 #pragma unroll
         for (int nn = 0; nn < kOBlocks / 2; ++nn) {
-          // transposed load of v[keys kk*16 .. +15][d nn*16 .. +15]:
-          // matrices (keys 0-7, d lo), (keys 8-15, d lo), (keys 0-7, d hi), (keys 8-15, d hi)
-          const int matrix = lane >> 3;
-          const int key = kk * 16 + (matrix & 1) * 8 + (lane & 7);
-          uint32_t b[4];
-          hx_ldmatrix_x4_trans(b, piece_address(v_half, key, nn * 2 + (matrix >> 1), page_size,
-                                                page_bytes));
+          uint32_t b[4];      // v[keys kk*16 .. +15][d nn*16 .. +15], transposed
+          hx_ldmatrix_x4_trans(b, v_half + v_offset[kk] + nn * piece_step);
           hx_mma_bf16(o_acc[nn * 2], p_hi, b[0], b[1]);
           hx_mma_bf16(o_acc[nn * 2], p_lo, b[0], b[1]);
           hx_mma_bf16(o_acc[nn * 2 + 1], p_hi, b[2], b[3]);
