@@ -29,7 +29,7 @@ SOURCES = (
     "hx_attention_mma.cu",
     "hx_sampling.cu",
 )
-HEADERS = ("hx_common.cuh",)
+HEADERS = ("hx_common.cuh", "hx_mma.cuh", "hx_no_alloc.h")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

@@ -723,3 +723,102 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
   HX_CHECK_LAUNCH("hx_paged_attention");
   return HX_OK;
 }
+
+// ------------------------------------------------ the same attention, scratch built in
+//
+// hx_paged_attention() wants two pieces of scratch memory from its caller when a context is
+// cut into key splits.  Not every caller can provide them.  A serving process that has
+// handed all of its device memory to weights and the cache pool at start-up has nothing
+// left to allocate from, and must not find that out in the middle of a request.  A caller on
+// a latency-critical path cannot afford cudaMalloc or cudaFree there, because both make the
+// whole device wait.  And a caller from plain C, or through a foreign-function interface,
+// has no caching allocator to lean on and would have to size and keep such a buffer itself.
+// For them the scratch lives in the library: one array in device memory, fixed at
+// HX_NO_ALLOC_SCRATCH_WORDS 32-bit words (4.25 MiB), which every GPU that loads the library
+// holds until the process ends.  See hx_no_alloc.h for the contract.
+#include "hx_no_alloc.h"
+
+#include <mutex>
+
+static __device__ __align__(256) unsigned int hx_static_attention_scratch[HX_NO_ALLOC_SCRATCH_WORDS];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch[kMaxDevices] = {};
+
+// The array's name is only a host-side handle; the kernels need its address on the device
+// that is current.  It is looked up once per device and remembered.
+int static_scratch_of_current_device(void** address) {
+  int device = -1;
+  cudaError_t rc = cudaGetDevice(&device);
+  if (rc != cudaSuccess) {
+    hx_set_error("hx_paged_attention_no_alloc: cudaGetDevice failed: %s", cudaGetErrorString(rc));
+    return HX_ERR_LAUNCH;
+  }
+  if (device < 0 || device >= kMaxDevices) {
+    hx_set_error("hx_paged_attention_no_alloc: device %d is outside the supported range", device);
+    return HX_ERR_UNSUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch[device] == nullptr) {
+    void* found = nullptr;
+    rc = cudaGetSymbolAddress(&found, hx_static_attention_scratch);
+    if (rc != cudaSuccess || found == nullptr) {
+      hx_set_error("hx_paged_attention_no_alloc: cudaGetSymbolAddress failed on device %d: %s",
+                   device, cudaGetErrorString(rc));
+      return HX_ERR_LAUNCH;
+    }
+    g_static_scratch[device] = found;
+  }
+  *address = g_static_scratch[device];
+  return HX_OK;
+}
+
+}  // namespace
+
+HX_API int hx_paged_attention_no_alloc(const void* q, int ldq, const void* k_cache,
+                                       const void* v_cache, int dtype, const int* positions,
+                                       const int* token_request, const int* request_table_row,
+                                       const int* block_tables, int table_stride,
+                                       const int* request_start, int skip_query_len, void* out,
+                                       int ldo, int tokens, int heads, int kv_heads, int head_dim,
+                                       int page_size, int num_pages, int window, float scale,
+                                       int split_keys, int max_splits, int* status,
+                                       cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && heads > 0 && head_dim > 0 && max_splits > 0,
+             "hx_paged_attention_no_alloc: bad sizes");
+  const long long floats = hx_paged_attention_scratch_floats(tokens, heads, head_dim, max_splits);
+  const long long counters = max_splits > 1 ? static_cast<long long>(tokens) * heads : 0;
+  HX_REQUIRE(floats <= HX_NO_ALLOC_PARTIAL_WORDS,
+             "hx_paged_attention_no_alloc: %d tokens x %d heads x %d splits of head size %d need "
+             "%lld words of scratch, the built-in array holds %d; use fewer splits or tokens, or "
+             "call hx_paged_attention with scratch of your own", tokens, heads, max_splits,
+             head_dim, floats, HX_NO_ALLOC_PARTIAL_WORDS);
+  HX_REQUIRE(counters <= HX_NO_ALLOC_COUNTER_WORDS,
+             "hx_paged_attention_no_alloc: %d tokens x %d heads need %lld arrival counters, the "
+             "built-in array holds %d", tokens, heads, counters, HX_NO_ALLOC_COUNTER_WORDS);
+  void* base = nullptr;
+  const int found = static_scratch_of_current_device(&base);
+  if (found != HX_OK) return found;
+  float* partial = static_cast<float*>(base);
+  int* arrivals = reinterpret_cast<int*>(static_cast<unsigned int*>(base) + HX_NO_ALLOC_PARTIAL_WORDS);
+  if (counters > 0) {
+    // The array keeps whatever the last call left.  Partial results are overwritten before
+    // they are read; the arrival counters must start at zero, so they are cleared here, in
+    // stream order, in case an earlier call was cut short.
+    const cudaError_t rc = cudaMemsetAsync(arrivals, 0, static_cast<size_t>(counters) * sizeof(int),
+                                           stream);
+    if (rc != cudaSuccess) {
+      hx_set_error("hx_paged_attention_no_alloc: clearing the counters failed: %s",
+                   cudaGetErrorString(rc));
+      return HX_ERR_LAUNCH;
+    }
+  }
+  return hx_paged_attention(q, ldq, k_cache, v_cache, dtype, positions, token_request,
+                            request_table_row, block_tables, table_stride, request_start,
+                            skip_query_len, out, ldo, partial, arrivals, tokens, heads, kv_heads,
+                            head_dim, page_size, num_pages, window, scale, split_keys, max_splits,
+                            status, stream);
+}
