@@ -9,8 +9,10 @@ as the window has passed them.  The reference has one geometry for all layers
 engine's own.
 
 A page id is valid in every layer of its group (as in the reference, where a block
-spans all layers).  Storage of one group:
-``[layer, key|value, page, kv_head, slot in page, head_dim]``.
+spans all layers).  Storage of one group is ``[layer, key|value, page, kv_head, ...]``; the
+last two axes hold ``page_size x head_dim`` elements in the kernels' chunked order
+``[head_dim / c, slot, c]`` (``c`` elements = 16 bytes), so that everything a (page, head)
+holds is one contiguous block.
 
 Pages are reserved before a step (:meth:`CacheManager.extend`) and a request's
 length is published after it (:meth:`CacheManager.commit`), which is the reference's
