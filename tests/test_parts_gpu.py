@@ -25,6 +25,16 @@ DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 TOL = {"float32": dict(atol=2e-5, rtol=1e-4), "bfloat16": dict(atol=4e-2, rtol=4e-2)}
 
 
+def scaled_tolerance(dtype, increment):
+    """These tests feed unit-variance data through 0.2-variance weights, so outputs are tens of
+    times larger than a model's; the plain functions here do not round intermediates.  For
+    bfloat16 (8 significant bits per stored activation) allow 1 % of the output's own scale."""
+    if dtype == "float32":
+        scale = max(1.0, float(np.abs(increment).max()))
+        return dict(atol=2e-5 * scale, rtol=1e-4)
+    return dict(atol=0.01 * float(np.abs(increment).max()), rtol=2e-2)
+
+
 def context_for(dtype, kv_needs, entries, page_size=8, num_pages=32, max_positions=128):
     """A step context for hand-made entries ``[(request, n_tokens)]`` (tokens do not matter)."""
     stub = types.SimpleNamespace(device=DEVICE, dtype=dtype, vocab_size=1 << 20,
@@ -138,7 +148,8 @@ def test_attention_part(dtype, heads, kv_heads, head_dim, window, checkpoint_pai
     w = {"q": weights["wq"], "k": weights["wk"], "v": weights["wv"], "o": weights["wo"]}
     expected = attention_reference(x_all, w, heads, kv_heads, head_dim, theta, contexts, lengths,
                                    window, pairing)
-    assert_close(as_numpy(residual[:30]), base + expected, "attention part", **TOL[dtype])
+    assert_close(as_numpy(residual[:30]), base + expected, "attention part",
+                 **scaled_tolerance(dtype, expected))
     cache.check()
 
 
@@ -166,7 +177,8 @@ def test_feed_forward_part(dtype, hidden, intermediate, tokens):
     part.forward(ctx, buffer, residual)
     expected = plain.linear(plain.swiglu(plain.linear(x, weights["g"].T),
                                          plain.linear(x, weights["u"].T)), weights["d"].T)
-    assert_close(as_numpy(residual[:tokens]), base + expected, "feed-forward part", **TOL[dtype])
+    assert_close(as_numpy(residual[:tokens]), base + expected, "feed-forward part",
+                 **scaled_tolerance(dtype, expected))
     with pytest.raises(ValueError, match="silu"):
         build_part("feed_forward", PartSpec("gated_mlp", {"intermediate_size": 8,
                                                           "activation": "gelu"}, spec.tensors), 8)
