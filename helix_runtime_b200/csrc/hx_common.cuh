@@ -178,3 +178,9 @@ __device__ __forceinline__ float hx_silu(float x) {
   }
   return x * sigmoid;
 }
+
+// The same with the hardware exponential (relative error about 2^-21): for results that are
+// stored in bfloat16 right away.
+__device__ __forceinline__ float hx_silu_fast(float x) {
+  return x >= 0.0f ? __fdividef(x, 1.0f + __expf(-x)) : __fdividef(x * __expf(x), 1.0f + __expf(x));
+}
