@@ -36,6 +36,9 @@ NVCC_FLAGS = (
     "-Xcompiler", "-fPIC",
     "-Xcompiler", "-fvisibility=hidden",
     "--expt-relaxed-constexpr",
+    # kernel developers: more flags (for instance -D switches of a kernel under study); they
+    # enter the library's name like the sources do
+    *os.environ.get("HELIX_NVCC_FLAGS", "").split(),
 )
 
 
@@ -121,7 +124,8 @@ def build(verbose: bool = True, force: bool = False) -> str:
         os.replace(partial, target)
         for name in os.listdir(build_dir):      # libraries of older sources
             if name.startswith("libhelix_b200_") and name.endswith(".so") and \
-                    os.path.join(build_dir, name) != target:
+                    os.path.join(build_dir, name) != target and \
+                    not os.environ.get("HELIX_NVCC_FLAGS"):
                 try:
                     os.remove(os.path.join(build_dir, name))
                 except OSError:

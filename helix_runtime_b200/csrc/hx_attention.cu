@@ -25,16 +25,23 @@
 //    second product as two bfloat16 terms (hi + lo), so the softmax stays a float32
 //    quantity as far as the result can tell.
 //
-// Key splits.  A long context is cut into splits of `split_keys` keys, one warp each.
-// Every split writes its unnormalised sum, maximum and weight to scratch; the warp that
-// finishes LAST for a (token, head) combines them in ascending order (a counter per
-// (token, head) in scratch tells who is last, and is left at zero again).
+// Sharing a long context between warps.  The CUDA-core kernel cuts a context into splits of
+// `split_keys` keys, one warp each.  The streaming kernel lays all 32-key chunks of all rows
+// (token, head) end to end and gives every warp of a grid that fills the GPU once an equal
+// run of that list, whatever the mix of context lengths; a run may end one row and begin
+// another, and the copies of the chunks ahead stay in flight across that border.  Either
+// way a warp that holds only part of a row writes its unnormalised sum, maximum and weight
+// to scratch; the warp that finishes LAST for a (token, head) combines the parts in
+// ascending order (a counter per (token, head) in scratch tells who is last, and is left at
+// zero again).
 //
 // Exactness: the running maximum, exp, the running sum and the merge are float32; dot
-// products are float32 sums of exact products.  The order of every sum is a function of the
-// token's own position and of split_keys only (32-key chunks and splits anchored at lo,
-// merged in ascending order), so a token's result does not depend on how the batch was cut,
-// what else is in it, or which pages hold the keys.
+// products are float32 sums of exact products.  Keys are always taken in 32-key chunks
+// anchored at the first key and parts are merged in ascending order.  Where a row is cut
+// into parts depends on split_keys (CUDA-core kernel) or on what else is in the batch
+// (streaming kernel); that changes the grouping of float32 sums, hence the result by
+// float32 rounding only, and nothing else about the batch, the cut of the prompt or the
+// pages reaches a token's result.
 #include "hx_mma.cuh"
 
 namespace {
@@ -57,7 +64,7 @@ struct AttentionArgs {
                               // tensor-core prompt kernel
   void* out;
   int ldo;
-  float* partial;   // [tokens * heads][max_splits][head_dim + 2], only when max_splits > 1
+  float* partial;   // scratch of hx_paged_attention_scratch_floats() floats
   int* arrivals;    // [tokens * heads] counters, zero on entry and on exit
   int tokens;
   int heads;
@@ -294,6 +301,7 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
 // ------------------------------------------------------------------ streaming kernel
 
 constexpr int STREAM_WARPS = 2;
+constexpr int STREAM_RING = 2;      // chunks in flight per warp
 constexpr uint32_t STREAM_WAIT_LIMIT = 20u * 1000u * 1000u;
 
 __device__ __forceinline__ bool stream_wait(uint64_t* bar, uint32_t parity) {
@@ -320,48 +328,227 @@ __device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t b
       : "memory");
 }
 
-template <int D>
+// KEYS: keys per chunk, the unit a warp fetches and works through at a time (16 or 32).
+template <int D, int KEYS>
 struct StreamConfig {
-  static constexpr int kChunkBytes = 32 * D * 2;     // keys (or values) of a 32-key chunk
+  static constexpr int kChunkBytes = KEYS * D * 2;     // keys (or values) of a chunk
   static constexpr int kSlotBytes = 2 * kChunkBytes;
-  static constexpr int kRing = 2;     // 64 KB (32 KB) per CTA: three (six) CTAs share an SM
+  static constexpr int kRing = STREAM_RING;
   static constexpr int kSharedBytes = STREAM_WARPS * kRing * kSlotBytes;
+  static constexpr int kPartStride = D + 4;            // floats; keeps parts 16-byte aligned
+  // CTAs that share an SM as far as shared memory goes (the register budget follows it)
+  static constexpr int kResident = (227 * 1024 / (kSharedBytes + 1024)) < 8
+                                       ? (227 * 1024 / (kSharedBytes + 1024)) : 8;
 };
 
 // Shared-memory address of the 16-byte piece (key `key` of the chunk, coordinates 8c..8c+7)
-// inside a slot half that holds `32 / page_size` page blocks of [D/8][page_size][8].
+// inside a slot half that holds `KEYS / page_size` page blocks of [D/8][page_size][8].
 __device__ __forceinline__ uint32_t piece_address(uint32_t half_base, int key, int c,
                                                   int page_size, uint32_t page_bytes) {
   return half_base + (key / page_size) * page_bytes + ((c * page_size + key % page_size) << 4);
 }
 
-template <int D>
-__global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kernel(
+// Keys that `token` sees; 0 for tokens another kernel serves and past the end of the batch.
+__device__ __forceinline__ int row_keys(const AttentionArgs& a, int token) {
+  if (token >= a.tokens || skipped(a, token)) return 0;
+  return a.positions[token] + 1;
+}
+
+// A place in the flat list of chunks: rows (token, head) in ascending order, the chunks of a
+// row in ascending order of their keys.
+struct ChunkCursor {
+  int token, head, chunk;
+  int n;                  // chunks in a row of this token
+  int keys;               // keys this token sees
+  int table_row;          // row of the block table that holds the token's pages
+  long long row_begin;    // flat index of the row's first chunk
+};
+
+template <int KEYS>
+__device__ __forceinline__ void cursor_next(const AttentionArgs& a, ChunkCursor& c) {
+  if (++c.chunk < c.n) return;
+  c.chunk = 0;
+  c.row_begin += c.n;
+  if (++c.head < a.heads) return;
+  c.head = 0;
+  do {
+    ++c.token;
+    c.keys = row_keys(a, c.token);
+    c.n = (c.keys + KEYS - 1) / KEYS;
+  } while (c.n == 0 && c.token < a.tokens);
+  if (c.token < a.tokens) {
+    c.table_row = a.request_table_row[a.token_request[c.token]];
+  } else {
+    c.n = 1;      // past the end: never used, but keeps the walk finite
+  }
+}
+
+// Combine the parts of one row, written by the warps first_warp .. first_warp + n_parts - 1,
+// in ascending order; run by one warp.  A warp keeps the part of the row that holds its first
+// chunk in its slot 0, that of a row that begins inside its range in slot 1.  All loads of a
+// batch of 32 parts are in flight together: the merge is a few round trips to the L2.
+template <typename T, int D, int STRIDE>
+__device__ void merge_parts(const AttentionArgs& a, int token, int head, long long row_begin,
+                            long long per_warp, int first_warp, int n_parts, int lane) {
+  constexpr int PER_LANE = D / 32;      // consecutive coordinates per lane (2 or 4)
+  auto part_of = [&](int index) {
+    const long long w = first_warp + index;
+    const int slot = row_begin <= w * per_warp ? 0 : 1;
+    return a.partial + static_cast<size_t>(w * 2 + slot) * STRIDE;
+  };
+  auto load_slice = [&](const float* part, float (&o)[PER_LANE]) {
+    if constexpr (PER_LANE == 4) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(part + 4 * lane));
+      o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    } else {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(part + 2 * lane));
+      o[0] = v.x; o[1] = v.y;
+    }
+  };
+  float total_max = -INFINITY;
+  float total_sum = 0.0f;
+  float acc[PER_LANE];
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) acc[i] = 0.0f;
+  for (int base = 0; base < n_parts; base += 32) {
+    const int here = min(32, n_parts - base);
+    // lane s: maximum and weight of part base + s
+    float m = -INFINITY, l = 0.0f;
+    if (lane < here) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_of(base + lane) + D));
+      m = ml.x;
+      l = ml.y;
+    }
+    float batch_max = m;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+      batch_max = fmaxf(batch_max, __shfl_xor_sync(0xffffffffu, batch_max, offset));
+    const float new_max = fmaxf(total_max, batch_max);
+    const float rescale = total_max == -INFINITY ? 0.0f : __expf(total_max - new_max);
+    total_max = new_max;
+    total_sum *= rescale;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) acc[i] *= rescale;
+    const float factor = m == -INFINITY ? 0.0f : __expf(m - new_max);
+    for (int first = 0; first < here; first += 4) {
+      float o[4][PER_LANE];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (first + u < here) load_slice(part_of(base + first + u), o[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (first + u < here) {
+          const float f = __shfl_sync(0xffffffffu, factor, first + u);
+          total_sum = fmaf(__shfl_sync(0xffffffffu, l, first + u), f, total_sum);
+#pragma unroll
+          for (int i = 0; i < PER_LANE; ++i) acc[i] = fmaf(o[u][i], f, acc[i]);
+        }
+      }
+    }
+  }
+  const float inverse = 1.0f / total_sum;
+  T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
+           static_cast<size_t>(head) * D + PER_LANE * lane;
+#pragma unroll
+  for (int i = 0; i < PER_LANE; i += 2)
+    *reinterpret_cast<__nv_bfloat162*>(out + i) =
+        __floats2bfloat162_rn(acc[i] * inverse, acc[i + 1] * inverse);
+}
+
+// The flat list of chunks is cut into equal runs, one per warp of the grid, so a warp's run
+// may end one row in the middle, cover some rows wholly and begin another: the copies of the
+// next chunks are always in flight, across rows too, and every warp has the same amount of
+// work whatever the mix of context lengths.  A row that is wholly inside a run is written
+// straight to the output; a row cut by run borders is left as parts in scratch (at most two
+// per warp) and the warp that finishes last combines them.
+template <int D, int KEYS>
+__global__ __launch_bounds__(STREAM_WARPS * 32, StreamConfig<D, KEYS>::kResident)
+void paged_attention_stream_kernel(
     AttentionArgs a) {
   using T = __nv_bfloat16;
-  using Config = StreamConfig<D>;
+  using Config = StreamConfig<D, KEYS>;
   constexpr int RING = Config::kRing;
-  constexpr int kDSteps = D / 16;     // k-steps of q k^T
-  constexpr int kOBlocks = D / 8;     // 8-wide blocks of the output row
+  constexpr int kDSteps = D / 16;       // k-steps of the scores
+  constexpr int kDTiles = D / 16;       // 16-row tiles of the output
+  constexpr int kTiles = KEYS / 16;     // 16-key tiles of a chunk
+  constexpr int kMaxPages = KEYS / 8;   // pages of a chunk at the smallest page size
   extern __shared__ __align__(128) uint8_t stream_shared[];
   __shared__ uint64_t full_bar[STREAM_WARPS][RING];
   hx_pdl_prologue();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  Item item;
-  if (!find_item(a, static_cast<long long>(blockIdx.x) * STREAM_WARPS + warp, item)) return;
-  const int begin = item.begin;       // no window: a multiple of 32, hence of the page size
-  const int end = item.end;
-  const int n_chunks = (end - begin + 31) / 32;
+  const long long n_warps = static_cast<long long>(gridDim.x) * STREAM_WARPS;
+  const long long me = static_cast<long long>(blockIdx.x) * STREAM_WARPS + warp;
 
-  const int kv_head = item.head / (a.heads / a.kv_heads);
+  // ---- this warp's run of the flat chunk list.  Lane t looks at token base + t: its chunk
+  // count and, at the same time, the row of the block table its pages are in.
+  int first_keys = 0, first_table_row = 0, first_inclusive = 0;      // of the first 32 tokens
+  long long total = 0;
+  for (int base = 0; base < a.tokens; base += 32) {
+    const int token = base + lane;
+    const int keys = row_keys(a, token);
+    int table_row = 0;
+    if (base == 0 && token < a.tokens) table_row = a.request_table_row[a.token_request[token]];
+    int inclusive = (keys + KEYS - 1) / KEYS;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+      if (lane >= offset) inclusive += other;
+    }
+    if (base == 0) {
+      first_keys = keys;
+      first_table_row = table_row;
+      first_inclusive = inclusive;
+    }
+    total += __shfl_sync(0xffffffffu, inclusive, 31);
+  }
+  total *= a.heads;
+  const long long per_warp = (total + n_warps - 1) / n_warps;
+  const long long my_begin = me * per_warp;
+  const long long my_end = min(my_begin + per_warp, total);
+  if (my_begin >= my_end) return;
+
+  // the row that holds chunk my_begin: among the first 32 tokens straight from the registers
+  ChunkCursor at;
+  {
+    long long before = 0;      // chunks of one head of all earlier tokens
+    int found = -1;
+    for (int base = 0; base < a.tokens && found < 0; base += 32) {
+      int keys = first_keys, inclusive = first_inclusive, table_row = first_table_row;
+      if (base > 0) {
+        keys = row_keys(a, base + lane);
+        inclusive = (keys + KEYS - 1) / KEYS;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1) {
+          const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+          if (lane >= offset) inclusive += other;
+        }
+      }
+      const unsigned beyond = __ballot_sync(0xffffffffu, (before + inclusive) * a.heads > my_begin);
+      if (beyond != 0u) {
+        const int source = __ffs(beyond) - 1;
+        found = base + source;
+        at.keys = __shfl_sync(0xffffffffu, keys, source);
+        at.n = (at.keys + KEYS - 1) / KEYS;
+        before += __shfl_sync(0xffffffffu, inclusive, source) - at.n;
+        at.table_row = base == 0 ? __shfl_sync(0xffffffffu, table_row, source)
+                                 : a.request_table_row[a.token_request[found]];
+      } else {
+        before += __shfl_sync(0xffffffffu, inclusive, 31);
+      }
+    }
+    at.token = found;
+    const long long inside = my_begin - before * a.heads;
+    at.head = static_cast<int>(inside / at.n);
+    at.chunk = static_cast<int>(inside - static_cast<long long>(at.head) * at.n);
+    at.row_begin = my_begin - at.chunk;
+  }
+  ChunkCursor ahead = at;      // the chunk whose copies are requested next
+
   const int page_size = a.page_size;
-  const int pages_per_chunk = 32 / page_size;
+  const int pages_per_chunk = KEYS / page_size;
   const uint32_t page_bytes = static_cast<uint32_t>(page_size) * D * 2;
-  const int table_row = a.request_table_row[a.token_request[item.token]];
-  const int* table = a.block_tables + static_cast<size_t>(table_row) * a.table_stride;
-  const int first_page = begin / page_size;
-  const int n_pages = (end - begin + page_size - 1) / page_size;
+  const int heads_per_kv = a.heads / a.kv_heads;
   const uint8_t* k_cache = static_cast<const uint8_t*>(a.k_cache);
   const uint8_t* v_cache = static_cast<const uint8_t*>(a.v_cache);
   uint8_t* ring = stream_shared + static_cast<size_t>(warp) * RING * Config::kSlotBytes;
@@ -374,107 +561,134 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
   }
   __syncwarp();
 
-  // request the pages of chunk `c` into its ring slot; `bad` collects unreadable pages
-  bool bad = false;
-  auto request_chunk = [&](int c) {
-    if (lane != 0) return;
-    uint8_t* slot = ring + static_cast<size_t>(c % RING) * Config::kSlotBytes;
-    uint64_t* bar = &bars[c % RING];
-    int pages[4];
+  // Page numbers come 32 at a time, one per lane, from the block table of the token the
+  // requests have reached; a chunk's pages never straddle two such windows.
+  int window_token = -1, window_base = 0, window_pages = -1;
+  unsigned unreadable = 0u;      // per ring slot, one bit per page of the chunk in it
+  bool any_unreadable = false;
+
+  // request the copies of the chunk at `ahead` into ring slot `slot`; every lane follows,
+  // lane 0 issues
+  auto request_chunk = [&](int slot) {
+    const int first = ahead.chunk * pages_per_chunk;
+    if (ahead.token != window_token || first < window_base || first >= window_base + 32) {
+      window_token = ahead.token;
+      window_base = first & ~31;
+      const int index = window_base + lane;
+      window_pages = -1;
+      if (index < a.table_stride && index * page_size < ahead.keys)
+        window_pages = a.block_tables[static_cast<size_t>(ahead.table_row) * a.table_stride + index];
+    }
+    uint8_t* slot_base = ring + static_cast<size_t>(slot) * Config::kSlotBytes;
+    uint64_t* bar = &bars[slot];
+    const int kv_head = ahead.head / heads_per_kv;
+    int pages[kMaxPages];
     uint32_t expected = 0;
+    unsigned bits = 0u;
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
+    for (int p = 0; p < kMaxPages; ++p) {
       pages[p] = -1;
-      const int index = c * pages_per_chunk + p;
-      if (p < pages_per_chunk && index < n_pages) {
-        const int page = table[first_page + index];
+      if (p < pages_per_chunk && (first + p) * page_size < ahead.keys) {
+        const int page = __shfl_sync(0xffffffffu, window_pages, first + p - window_base);
         if (page >= 0 && page < a.num_pages) {
           pages[p] = page;
           expected += 2 * page_bytes;
         } else {
-          bad = true;
+          bits |= 1u << p;
         }
       }
     }
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
-                     hx_shared_address(bar)), "r"(expected) : "memory");
+    unreadable = (unreadable & ~(0xfu << (4 * slot))) | (bits << (4 * slot));
+    any_unreadable = any_unreadable || bits != 0u;
+    if (lane == 0) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                       hx_shared_address(bar)), "r"(expected) : "memory");
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      if (pages[p] >= 0) {
-        const size_t block = (static_cast<size_t>(pages[p]) * a.kv_heads + kv_head) * page_bytes;
-        bulk_copy(slot + p * page_bytes, k_cache + block, page_bytes, bar);
-        bulk_copy(slot + Config::kChunkBytes + p * page_bytes, v_cache + block, page_bytes, bar);
+      for (int p = 0; p < kMaxPages; ++p) {
+        if (pages[p] >= 0) {
+          const size_t block = (static_cast<size_t>(pages[p]) * a.kv_heads + kv_head) * page_bytes;
+          bulk_copy(slot_base + p * page_bytes, k_cache + block, page_bytes, bar);
+          bulk_copy(slot_base + Config::kChunkBytes + p * page_bytes, v_cache + block, page_bytes,
+                    bar);
+        }
       }
     }
   };
-  const int ahead = n_chunks < RING ? n_chunks : RING;
-  for (int c = 0; c < ahead; ++c) request_chunk(c);
-  bad = __shfl_sync(0xffffffffu, bad ? 1 : 0, 0) != 0;      // lane 0 looked the pages up
-
-  // the query is row 0 of a 16-row tile: only lanes 0..3 hold non-zero A fragments
-  uint32_t q_frag[kDSteps][4];
-  {
-    const T* q = static_cast<const T*>(a.q) + static_cast<size_t>(item.token) * a.ldq +
-                 static_cast<size_t>(item.head) * D;
-#pragma unroll
-    for (int k = 0; k < kDSteps; ++k) {
-      q_frag[k][0] = q_frag[k][1] = q_frag[k][2] = q_frag[k][3] = 0u;
-      if (lane < 4) {
-        q_frag[k][0] = *reinterpret_cast<const uint32_t*>(q + k * 16 + 2 * lane);
-        q_frag[k][2] = *reinterpret_cast<const uint32_t*>(q + k * 16 + 8 + 2 * lane);
-      }
-    }
+  const long long run = my_end - my_begin;
+  for (int i = 0; i < RING && i < run; ++i) {
+    request_chunk(i);
+    cursor_next<KEYS>(a, ahead);
   }
 
-  // Where this lane's ldmatrix rows sit inside a slot half never changes from chunk to chunk:
-  // work the offsets out once.  Keys: matrices (keys 0-7, d lo), (keys 0-7, d hi),
-  // (keys 8-15, d lo), (keys 8-15, d hi) of each 16-key pair; values (transposed load):
-  // (keys 0-7, d lo), (keys 8-15, d lo), (keys 0-7, d hi), (keys 8-15, d hi).
+  // Both products put the cache on the 16-row side of the tensor-core tile, where none of it
+  // is wasted, and the single query (or probability) vector on the 8-column side:
+  //   scores  S[16 keys x 8]  = K[16 keys x 16 d] q[16 d x 8]      (all 8 columns equal)
+  //   output  O[16 d x 8]    += V^T[16 d x 16 keys] P[16 keys x 8]  (column 0: hi part of the
+  //                                                    probabilities, column 1: lo part)
+  // Where this lane's ldmatrix rows sit inside a slot half never changes from chunk to
+  // chunk: work the offsets out once.  Keys (plain load): matrices (keys 0-7, d lo),
+  // (keys 8-15, d lo), (keys 0-7, d hi), (keys 8-15, d hi) of a 16-key tile; values
+  // (transposed load): (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi).
   const int matrix = lane >> 3;
+  const int group = lane >> 2;       // row of the tile this lane holds in c0, c1 (and +8 in c2, c3)
+  const int quad = lane & 3;
   const uint32_t piece_step = static_cast<uint32_t>(page_size) * 32;   // two 16-byte pieces on
-  uint32_t k_offset[2], v_offset[2];
+  uint32_t k_offset[kTiles], v_offset[kTiles];
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int k_key = half * 16 + (matrix >> 1) * 8 + (lane & 7);
-    k_offset[half] = piece_address(0, k_key, matrix & 1, page_size, page_bytes);
-    const int v_key = half * 16 + (matrix & 1) * 8 + (lane & 7);
-    v_offset[half] = piece_address(0, v_key, matrix >> 1, page_size, page_bytes);
+  for (int tile = 0; tile < kTiles; ++tile) {
+    const int k_key = tile * 16 + (matrix & 1) * 8 + (lane & 7);
+    k_offset[tile] = piece_address(0, k_key, matrix >> 1, page_size, page_bytes);
+    const int v_key = tile * 16 + (matrix >> 1) * 8 + (lane & 7);
+    v_offset[tile] = piece_address(0, v_key, matrix & 1, page_size, page_bytes);
   }
 
-  // row 0 of the output lives in c0, c1 of lanes 0..3: coordinates 8 n + 2 lane + {0, 1}
-  float o_acc[kOBlocks][4];
-#pragma unroll
-  for (int n = 0; n < kOBlocks; ++n)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) o_acc[n][e] = 0.0f;
+  uint32_t q_frag[kDSteps][2];       // the query as B operand: d 16k + 2 quad (+8), +1
+  float o_acc[kDTiles][4];           // lanes with quad 0: d 16m + group (c0 hi, c1 lo), +8 (c2, c3)
   float running_max = -INFINITY;
-  float running_sum = 0.0f;      // this lane's share of the row sum (lanes 0..3)
+  float running_sum = 0.0f;          // over this lane's own keys; lanes of a group hold copies
+#pragma unroll
+  for (int k = 0; k < kDSteps; ++k) q_frag[k][0] = q_frag[k][1] = 0u;
 
-  for (int c = 0; c < n_chunks; ++c) {
+  for (long long i = 0; i < run; ++i) {
+    const int slot = static_cast<int>(i % RING);
+    if (i == 0 || at.chunk == 0) {
+      // a row begins (or goes on from another warp's run): its query, an empty sum
+      const T* q = static_cast<const T*>(a.q) + static_cast<size_t>(at.token) * a.ldq +
+                   static_cast<size_t>(at.head) * D + 2 * quad;
+#pragma unroll
+      for (int k = 0; k < kDSteps; ++k) {
+        q_frag[k][0] = *reinterpret_cast<const uint32_t*>(q + k * 16);
+        q_frag[k][1] = *reinterpret_cast<const uint32_t*>(q + k * 16 + 8);
+      }
+#pragma unroll
+      for (int m = 0; m < kDTiles; ++m)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o_acc[m][e] = 0.0f;
+      running_max = -INFINITY;
+      running_sum = 0.0f;
+    }
+
     bool arrived = true;
-    if (lane == 0) arrived = stream_wait(&bars[c % RING], static_cast<uint32_t>(c / RING) & 1u);
+    if (lane == 0)
+      arrived = stream_wait(&bars[slot], static_cast<uint32_t>(i / RING) & 1u);
     arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
     if (!arrived) {
       if (lane == 0 && a.status != nullptr) atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
       return;
     }
-    const uint32_t k_half = hx_shared_address(ring + static_cast<size_t>(c % RING) * Config::kSlotBytes);
+    const uint32_t k_half = hx_shared_address(ring + static_cast<size_t>(slot) * Config::kSlotBytes);
     const uint32_t v_half = k_half + Config::kChunkBytes;
-    const int keys_here = min(32, end - (begin + c * 32));
+    const int keys_here = min(KEYS, at.keys - at.chunk * KEYS);
+    const unsigned bad_pages = (unreadable >> (4 * slot)) & 0xfu;
 
     // Whatever lies behind the last key of the request in its last page, and pages that
     // could not be read, must not reach the second product (0 * NaN is NaN): clear those
     // value rows.  Keys need no clearing: their scores are masked by selection.
-    if (keys_here < 32 || bad) {
-      for (int index = lane; index < 32 * (D / 8); index += 32) {
+    if (keys_here < KEYS || bad_pages != 0u) {
+      for (int index = lane; index < KEYS * (D / 8); index += 32) {
         const int key = index / (D / 8);
         const int piece = index - key * (D / 8);
-        bool clear = key >= keys_here;
-        if (!clear && bad) {
-          const int page = table[first_page + c * pages_per_chunk + key / page_size];
-          clear = page < 0 || page >= a.num_pages;
-        }
-        if (clear) {
+        if (key >= keys_here || ((bad_pages >> (key / page_size)) & 1u)) {
           const uint32_t address = piece_address(v_half, key, piece, page_size, page_bytes);
           asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(address), "r"(0u) : "memory");
         }
@@ -482,166 +696,197 @@ __global__ __launch_bounds__(STREAM_WARPS * 32) void paged_attention_stream_kern
       __syncwarp();
     }
 
-    // ---- s = q k^T for the 32 keys: 4 blocks of 8 keys
-    float s[4][4];
+    // ---- scores: this lane ends up with keys group and group + 8 of every tile, each twice
+    // (c0 = c1, c2 = c3)
+    float s[kTiles][4];
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int tile = 0; tile < kTiles; ++tile)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) s[n][e] = 0.0f;
+      for (int e = 0; e < 4; ++e) s[tile][e] = 0.0f;
 #pragma unroll
     for (int k = 0; k < kDSteps; ++k) {
 #pragma unroll
-      for (int pair = 0; pair < 2; ++pair) {
-        uint32_t b[4];
-        hx_ldmatrix_x4(b, k_half + k_offset[pair] + k * piece_step);
-        hx_mma_bf16(s[pair * 2], q_frag[k], b[0], b[1]);
-        hx_mma_bf16(s[pair * 2 + 1], q_frag[k], b[2], b[3]);
+      for (int tile = 0; tile < kTiles; ++tile) {
+        uint32_t keys_a[4];
+        hx_ldmatrix_x4(keys_a, k_half + k_offset[tile] + k * piece_step);
+        hx_mma_bf16(s[tile], keys_a, q_frag[k][0], q_frag[k][1]);
       }
     }
 
-    // ---- scale, mask, online softmax of row 0 (held by lanes 0..3 in c0, c1)
+    // ---- scale, mask, online softmax
+    float score[2 * kTiles];      // keys group + 8 j
+#pragma unroll
+    for (int tile = 0; tile < kTiles; ++tile) {
+      score[2 * tile] = s[tile][0];
+      score[2 * tile + 1] = s[tile][2];
+    }
     float chunk_max = -INFINITY;
-    if (keys_here == 32 && !bad) {
+    if (keys_here == KEYS && bad_pages == 0u) {
 #pragma unroll
-      for (int n = 0; n < 4; ++n) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          s[n][e] *= a.scale;
-          chunk_max = fmaxf(chunk_max, s[n][e]);
-        }
+      for (int j = 0; j < 2 * kTiles; ++j) {
+        score[j] *= a.scale;
+        chunk_max = fmaxf(chunk_max, score[j]);
       }
     } else {
 #pragma unroll
-      for (int n = 0; n < 4; ++n) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int key = n * 8 + 2 * (lane & 3) + e;
-          bool visible = key < keys_here;
-          if (visible && bad) {
-            const int page = table[first_page + c * pages_per_chunk + key / page_size];
-            visible = page >= 0 && page < a.num_pages;
-          }
-          const float value = visible ? s[n][e] * a.scale : -INFINITY;
-          s[n][e] = value;
-          chunk_max = fmaxf(chunk_max, value);
-        }
+      for (int j = 0; j < 2 * kTiles; ++j) {
+        const int key = group + 8 * j;
+        const bool visible = key < keys_here && !((bad_pages >> (key / page_size)) & 1u);
+        score[j] = visible ? score[j] * a.scale : -INFINITY;
+        chunk_max = fmaxf(chunk_max, score[j]);
       }
     }
-    chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 1));
-    chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 2));
-    chunk_max = __shfl_sync(0xffffffffu, chunk_max, 0);      // every lane follows row 0
+    chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 4));
+    chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 8));
+    chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, 16));
     const float new_max = fmaxf(running_max, chunk_max);
     if (new_max != -INFINITY) {
-      const float correction = running_max == -INFINITY ? 0.0f : __expf(running_max - new_max);
-      running_max = new_max;
-      running_sum *= correction;
+      if (new_max != running_max) {      // the same in every lane
+        const float correction = running_max == -INFINITY ? 0.0f : __expf(running_max - new_max);
+        running_max = new_max;
+        running_sum *= correction;
 #pragma unroll
-      for (int n = 0; n < kOBlocks; ++n) {
-        o_acc[n][0] *= correction;
-        o_acc[n][1] *= correction;
+        for (int m = 0; m < kDTiles; ++m)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o_acc[m][e] *= correction;
       }
-      // ---- o += p v with p = hi + lo; rows 1..15 of p are zero
+      // probabilities as (hi, lo) bfloat16 pairs, one 32-bit word per key
+      uint32_t split[2 * kTiles];
 #pragma unroll
-      for (int kk = 0; kk < 2; ++kk) {
-        uint32_t p_hi[4] = {0u, 0u, 0u, 0u}, p_lo[4] = {0u, 0u, 0u, 0u};
-        if (lane < 4) {
+      for (int j = 0; j < 2 * kTiles; ++j) {
+        const float x = __expf(score[j] - new_max);
+        running_sum += x;
+        const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+        const __nv_bfloat16 lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+        split[j] = static_cast<uint32_t>(__bfloat16_as_ushort(hi)) |
+                   (static_cast<uint32_t>(__bfloat16_as_ushort(lo)) << 16);
+      }
+      // ---- o += V^T p.  The B operand wants, in this lane, keys 2 quad, 2 quad + 1 (b0) and
+      // 8 more (b1) of each tile: they sit in the lanes of groups 2 quad and 2 quad + 1.
+      // Even columns (group even) take the hi parts, odd columns the lo parts; only columns
+      // 0 and 1 are read back.
+      const int source = 8 * quad;                         // first lane of group 2 quad
+      const uint32_t pick = (group & 1) ? 0x7632u : 0x5410u;      // lo halves : hi halves
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const float x0 = __expf(s[kk * 2 + half][0] - new_max);
-            const float x1 = __expf(s[kk * 2 + half][1] - new_max);
-            running_sum += x0 + x1;
-            hx_split_bf16(x0, x1, p_hi[half * 2], p_lo[half * 2]);
-          }
-        }
+      for (int tile = 0; tile < kTiles; ++tile) {
+        const uint32_t e0 = __shfl_sync(0xffffffffu, split[tile * 2], source);
+        const uint32_t e1 = __shfl_sync(0xffffffffu, split[tile * 2], source + 4);
+        const uint32_t f0 = __shfl_sync(0xffffffffu, split[tile * 2 + 1], source);
+        const uint32_t f1 = __shfl_sync(0xffffffffu, split[tile * 2 + 1], source + 4);
+        const uint32_t b0 = __byte_perm(e0, e1, pick);
+        const uint32_t b1 = __byte_perm(f0, f1, pick);
 #pragma unroll
-        for (int nn = 0; nn < kOBlocks / 2; ++nn) {
-          uint32_t b[4];      // v[keys kk*16 .. +15][d nn*16 .. +15], transposed
-          hx_ldmatrix_x4_trans(b, v_half + v_offset[kk] + nn * piece_step);
-          hx_mma_bf16(o_acc[nn * 2], p_hi, b[0], b[1]);
-          hx_mma_bf16(o_acc[nn * 2], p_lo, b[0], b[1]);
-          hx_mma_bf16(o_acc[nn * 2 + 1], p_hi, b[2], b[3]);
-          hx_mma_bf16(o_acc[nn * 2 + 1], p_lo, b[2], b[3]);
+        for (int m = 0; m < kDTiles; ++m) {
+          uint32_t values_a[4];      // V^T[d 16m .. +15][keys of the tile]
+          hx_ldmatrix_x4_trans(values_a, v_half + v_offset[tile] + m * piece_step);
+          hx_mma_bf16(o_acc[m], values_a, b0, b1);
         }
       }
     }
     __syncwarp();
-    if (c + RING < n_chunks) {
+    if (i + RING < run) {
       // the slot is free: order this warp's reads before the copy engine's writes
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      request_chunk(c + RING);
-      bad = __shfl_sync(0xffffffffu, bad ? 1 : 0, 0) != 0;
+      request_chunk(slot);
+      cursor_next<KEYS>(a, ahead);
     }
-  }
-  if (lane == 0 && bad && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
 
-  // the row sum is spread over lanes 0..3; the output row over the same lanes, two
-  // coordinates of every 8-wide block each: hand each lane's share to finish_item as
-  // kOBlocks pieces of two coordinates
-  running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 1);
-  running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 2);
-  running_sum = __shfl_sync(0xffffffffu, running_sum, 0);
-
-  if (item.n_splits == 1) {
-    if (lane < 4) {
-      const float inverse = 1.0f / running_sum;
-      T* out = static_cast<T*>(a.out) + static_cast<size_t>(item.token) * a.ldo +
-               static_cast<size_t>(item.head) * D + 2 * lane;
+    if (at.chunk == at.n - 1 || i == run - 1) {
+      // ---- the row, or this run's share of it, is done.  Every group of lanes holds the
+      // sum over its own keys; the output row sits in the lanes with quad 0.
+      float row_sum = running_sum;
+      row_sum += __shfl_xor_sync(0xffffffffu, row_sum, 4);
+      row_sum += __shfl_xor_sync(0xffffffffu, row_sum, 8);
+      row_sum += __shfl_xor_sync(0xffffffffu, row_sum, 16);
+      const long long row_end = at.row_begin + at.n;
+      if (at.row_begin >= my_begin && row_end <= my_end) {
+        if (quad == 0) {
+          const float inverse = 1.0f / row_sum;
+          T* out = static_cast<T*>(a.out) + static_cast<size_t>(at.token) * a.ldo +
+                   static_cast<size_t>(at.head) * D + group;
 #pragma unroll
-      for (int n = 0; n < kOBlocks; ++n)
-        *reinterpret_cast<__nv_bfloat162*>(out + n * 8) =
-            __floats2bfloat162_rn(o_acc[n][0] * inverse, o_acc[n][1] * inverse);
-    }
-    return;
-  }
-  float* part = a.partial +
-                (static_cast<size_t>(item.token_head) * a.max_splits + item.split) * (D + 2);
-  if (lane < 4) {
+          for (int m = 0; m < kDTiles; ++m) {
+            out[m * 16] = __float2bfloat16_rn((o_acc[m][0] + o_acc[m][1]) * inverse);
+            out[m * 16 + 8] = __float2bfloat16_rn((o_acc[m][2] + o_acc[m][3]) * inverse);
+          }
+        }
+      } else {
+        const int my_slot = at.row_begin <= my_begin ? 0 : 1;
+        float* part = a.partial + static_cast<size_t>(me * 2 + my_slot) * Config::kPartStride;
+        if (quad == 0) {
 #pragma unroll
-    for (int n = 0; n < kOBlocks; ++n) {
-      part[n * 8 + 2 * lane] = o_acc[n][0];
-      part[n * 8 + 2 * lane + 1] = o_acc[n][1];
+          for (int m = 0; m < kDTiles; ++m) {
+            part[m * 16 + group] = o_acc[m][0] + o_acc[m][1];
+            part[m * 16 + group + 8] = o_acc[m][2] + o_acc[m][3];
+          }
+        }
+        if (lane == 0) *reinterpret_cast<float2*>(part + D) = make_float2(running_max, row_sum);
+        __threadfence();
+        __syncwarp();
+        const int first_warp = static_cast<int>(at.row_begin / per_warp);
+        const int n_parts = static_cast<int>((row_end - 1) / per_warp) - first_warp + 1;
+        const long long counter = static_cast<long long>(at.token) * a.heads + at.head;
+        int arrived_count = 0;
+        if (lane == 0) arrived_count = atomicAdd(a.arrivals + counter, 1);
+        arrived_count = __shfl_sync(0xffffffffu, arrived_count, 0);
+        if (arrived_count == n_parts - 1) {
+          __threadfence();
+          if (lane == 0) a.arrivals[counter] = 0;      // ready for the next call
+          merge_parts<T, D, Config::kPartStride>(a, at.token, at.head, at.row_begin, per_warp,
+                                                 first_warp, n_parts, lane);
+        }
+      }
     }
+    cursor_next<KEYS>(a, at);
   }
-  if (lane == 0) {
-    part[D] = running_max;
-    part[D + 1] = running_sum;
-  }
-  __threadfence();
-  __syncwarp();
-  int arrived_count = 0;
-  if (lane == 0) arrived_count = atomicAdd(a.arrivals + item.token_head, 1);
-  arrived_count = __shfl_sync(0xffffffffu, arrived_count, 0);
-  if (arrived_count != item.n_splits - 1) return;
-  __threadfence();
-  if (lane == 0) a.arrivals[item.token_head] = 0;
-  merge_splits<T>(a, item, lane);
+  if (lane == 0 && any_unreadable && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
 }
 
-template <int D>
+// Warps the streaming kernel's grid may hold: the scratch keeps two parts per warp.
+constexpr int STREAM_MAX_WARPS = 2048;
+
+template <int D, int KEYS>
 int launch_stream(const AttentionArgs& a, cudaStream_t stream) {
-  using Config = StreamConfig<D>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(paged_attention_stream_kernel<D>,
+  using Config = StreamConfig<D, KEYS>;
+  static int resident_warps[64] = {};      // per device: warps the whole GPU holds at once
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 64) device = 0;
+  if (resident_warps[device] == 0) {
+    int sms = 0, blocks_per_sm = 0;
+    if (cudaFuncSetAttribute(paged_attention_stream_kernel<D, KEYS>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Config::kSharedBytes) != cudaSuccess) {
+                             Config::kSharedBytes) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+            &blocks_per_sm, paged_attention_stream_kernel<D, KEYS>, STREAM_WARPS * 32,
+            Config::kSharedBytes) != cudaSuccess || sms <= 0 || blocks_per_sm <= 0) {
       cudaGetLastError();
       hx_set_error("hx_paged_attention: cannot reserve %d bytes of shared memory",
                    Config::kSharedBytes);
       return HX_ERR_LAUNCH;
     }
-    configured = true;
+    resident_warps[device] = min(STREAM_MAX_WARPS, sms * blocks_per_sm * STREAM_WARPS);
   }
-  const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
-  const int blocks = static_cast<int>((items + STREAM_WARPS - 1) / STREAM_WARPS);
-  hx_launch(paged_attention_stream_kernel<D>, blocks, STREAM_WARPS * 32, Config::kSharedBytes,
-            stream, a);
+  // one warp per chunk at most (the bound on chunks comes from the caller's split sizes)
+  const long long chunk_bound =
+      static_cast<long long>(a.tokens) * a.heads *
+      ((static_cast<long long>(a.split_keys) * a.max_splits + KEYS - 1) / KEYS);
+  const long long warps = min(static_cast<long long>(resident_warps[device]), max(1ll, chunk_bound));
+  const int blocks = static_cast<int>((warps + STREAM_WARPS - 1) / STREAM_WARPS);
+  hx_launch(paged_attention_stream_kernel<D, KEYS>, blocks, STREAM_WARPS * 32,
+            Config::kSharedBytes, stream, a);
   return HX_OK;
 }
 
 bool stream_kernel_applies(const AttentionArgs& a, int dtype) {
   return dtype == HX_BF16 && (a.head_dim == 64 || a.head_dim == 128) && a.window == 0 &&
-         (a.page_size == 8 || a.page_size == 16 || a.page_size == 32) && a.split_keys % 32 == 0;
+         (a.page_size == 8 || a.page_size == 16 || a.page_size == 32);
+}
+
+int launch_stream_for(const AttentionArgs& a, cudaStream_t stream) {
+  // 32-key chunks: the largest page the kernel takes is one block of the cache
+  return a.head_dim == 128 ? launch_stream<128, 32>(a, stream) : launch_stream<64, 32>(a, stream);
 }
 
 template <typename T>
@@ -674,12 +919,15 @@ HX_API int hx_cache_chunk_elements(int dtype, int head_dim) {
   return hx_cache_chunk(dtype == HX_F32 ? 4 : 2, head_dim);
 }
 
-// Floats of scratch the call needs in `partial` (0 when max_splits == 1); the same call
-// needs tokens * heads ints of zeroed scratch in `arrivals`.
+// Floats of scratch the call needs in `partial`: room for every key split of every row
+// (the CUDA-core kernel) and for two parts per warp of the streaming kernel's grid.  The same
+// call needs tokens * heads ints of zeroed scratch in `arrivals`.
 HX_API long long hx_paged_attention_scratch_floats(int tokens, int heads, int head_dim,
                                                    int max_splits) {
-  if (max_splits <= 1) return 0;
-  return static_cast<long long>(tokens) * heads * max_splits * (head_dim + 2);
+  const long long by_split =
+      max_splits <= 1 ? 0 : static_cast<long long>(tokens) * heads * max_splits * (head_dim + 2);
+  const long long by_warp = 2ll * STREAM_MAX_WARPS * (head_dim + 4);
+  return by_split > by_warp ? by_split : by_warp;
 }
 
 HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,
@@ -696,8 +944,7 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
   HX_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0,
              "hx_paged_attention: bad cache geometry");
   HX_REQUIRE(split_keys > 0 && max_splits > 0, "hx_paged_attention: bad split sizes");
-  HX_REQUIRE(max_splits == 1 || (partial != nullptr && arrivals != nullptr),
-             "hx_paged_attention: scratch missing");
+  HX_REQUIRE(partial != nullptr && arrivals != nullptr, "hx_paged_attention: scratch missing");
   HX_REQUIRE(window >= 0, "hx_paged_attention: window must not be negative");
   HX_REQUIRE(skip_query_len <= 0 || request_start != nullptr,
              "hx_paged_attention: request_start missing");
@@ -713,7 +960,7 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
   HX_REQUIRE(items / STREAM_WARPS < (1ll << 31) - 1, "hx_paged_attention: grid too large");
   int rc;
   if (stream_kernel_applies(a, dtype)) {
-    rc = head_dim == 128 ? launch_stream<128>(a, stream) : launch_stream<64>(a, stream);
+    rc = launch_stream_for(a, stream);
   } else if (dtype == HX_F32) {
     rc = launch_cuda_cores<float>(a, stream);
   } else {
@@ -790,7 +1037,7 @@ HX_API int hx_paged_attention_no_alloc(const void* q, int ldq, const void* k_cac
   HX_REQUIRE(tokens >= 0 && heads > 0 && head_dim > 0 && max_splits > 0,
              "hx_paged_attention_no_alloc: bad sizes");
   const long long floats = hx_paged_attention_scratch_floats(tokens, heads, head_dim, max_splits);
-  const long long counters = max_splits > 1 ? static_cast<long long>(tokens) * heads : 0;
+  const long long counters = static_cast<long long>(tokens) * heads;
   HX_REQUIRE(floats <= HX_NO_ALLOC_PARTIAL_WORDS,
              "hx_paged_attention_no_alloc: %d tokens x %d heads x %d splits of head size %d need "
              "%lld words of scratch, the built-in array holds %d; use fewer splits or tokens, or "

@@ -9,10 +9,12 @@
 // quantity as far as the result can tell.  The reference materialises a [heads, T, T] score
 // tensor for the same computation (src/attention/cuda.cu:31-77, src/model/cuda_llama.cpp:249).
 //
-// Keys and values come straight from the pages: each 64-key tile is gathered row by row
-// through the block table with cp.async into a swizzled shared-memory tile, two tiles in
-// flight.  Rows beyond the last key any query of the CTA may see are zero-filled, never
-// read, so a stale or poisoned page cannot leak in through a zero probability.
+// Keys and values come straight from the pages: the keys of a (page, head) are one contiguous
+// block of the cache and so are its values, so a 64-key tile is a handful of bulk copies
+// (cp.async.bulk counted on an mbarrier) issued by one thread, two tiles in flight, and the
+// tensor-core loads (ldmatrix) read the page blocks as they lie.  Value rows beyond the last
+// key any query of the CTA may see are cleared in shared memory, so a stale or poisoned page
+// cannot leak in through a zero probability.
 //
 // A query row's result depends on its own position only: key tiles are anchored at key 0
 // and rows of a tile do not interact, so it does not matter which tile a token falls into
@@ -51,23 +53,49 @@ struct PrefillArgs {
   int* status;
 };
 
-// Tiles are [rows][D] bf16 with the 16-byte chunks of a row XOR-swizzled by the row number,
-// so that the eight rows an ldmatrix touches fall into different banks.
-template <int D>
-__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
-  constexpr int kChunks = D / 8;
-  return static_cast<uint32_t>((row * kChunks + (chunk ^ (row & 7))) * 16);
+constexpr int RING = 2;                         // key/value tiles in flight per CTA
+constexpr uint32_t WAIT_LIMIT = 20u * 1000u * 1000u;
+
+__device__ __forceinline__ bool tile_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t address = hx_shared_address(bar);
+  for (uint32_t spin = 0; spin < WAIT_LIMIT; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(address), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(hx_shared_address(bar))
+      : "memory");
+}
+
+// Byte offset, inside the key (or value) half of a tile, of the 16-byte piece that holds
+// coordinates 8c..8c+7 of key `key`: the half is 64 / page_size page blocks, each laid out
+// [D/8][page_size][8] exactly as in the cache.
+__device__ __forceinline__ uint32_t piece_offset(int key, int c, int page_size,
+                                                 uint32_t page_bytes) {
+  return (key / page_size) * page_bytes + ((c * page_size + key % page_size) << 4);
 }
 
 template <int D>
-__global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs a) {
-  constexpr int kChunks = D / 8;          // 16-byte chunks per row
-  constexpr int kTileBytes = BLOCK_N * D * 2;
-  constexpr int kDSteps = D / 16;         // k-steps of Q K^T
-  constexpr int kOBlocks = D / 8;         // n-blocks of the output
+__global__ __launch_bounds__(THREADS, 3) void prefill_attention_kernel(PrefillArgs a) {
+  constexpr int kHalfBytes = BLOCK_N * D * 2;      // keys (or values) of a 64-key tile
+  constexpr int kDSteps = D / 16;                  // k-steps of Q K^T
+  constexpr int kOBlocks = D / 8;                  // n-blocks of the output
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* q_tile = smem;                          // [64][D]
-  uint8_t* kv_tiles = smem + BLOCK_M * D * 2;      // 2 stages x (K tile, V tile)
+  __shared__ uint64_t full_bar[RING];
+  __shared__ int tile_state[RING];                 // 1: a page of the tile could not be read
   hx_pdl_prologue();
 
   const int tid = threadIdx.x;
@@ -102,47 +130,92 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
   const int n_tiles = last_key / BLOCK_N + 1;
   const int* table = a.block_tables +
                      static_cast<size_t>(a.request_table_row[request]) * a.table_stride;
+  const int page_size = a.page_size;
+  const int pages_per_tile = BLOCK_N / page_size;
+  const uint32_t page_bytes = static_cast<uint32_t>(page_size) * D * 2;
+  const int last_page = last_key / page_size;
 
-  // ---- Q tile -> shared memory (rows beyond the portion are zero)
-  for (int index = tid; index < BLOCK_M * kChunks; index += THREADS) {
-    const int row = index / kChunks;
-    const int chunk = index - row * kChunks;
-    const bool valid = row < rows_here;
-    const __nv_bfloat16* src = a.q + static_cast<size_t>(q_begin + row0 + (valid ? row : 0)) * a.ldq +
-                               static_cast<size_t>(head) * D + chunk * 8;
-    hx_cp_async_16(hx_shared_address(q_tile) + tile_offset<D>(row, chunk), src, valid ? 16 : 0);
+  if (tid == 0) {
+    for (int s = 0; s < RING; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(hx_shared_address(&full_bar[s])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  __syncthreads();
 
-  auto load_kv_tile = [&](int tile, int stage) {
-    const uint32_t k_dst = hx_shared_address(kv_tiles + stage * 2 * kTileBytes);
-    const uint32_t v_dst = k_dst + kTileBytes;
-    for (int index = tid; index < BLOCK_N * kChunks; index += THREADS) {
-      const int row = index / kChunks;
-      const int chunk = index - row * kChunks;
-      const int key = tile * BLOCK_N + row;
-      bool valid = key <= last_key;
-      size_t cache_element = 0;
-      if (valid) {
-        const int page = table[key / a.page_size];
-        if (page < 0 || page >= a.num_pages) {
-          if (a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
-          valid = false;
+  // one thread asks for the pages of a tile: two bulk copies (keys, values) per page
+  auto request_tile = [&](int tile) {
+    const int stage = tile % RING;
+    const uint32_t base = hx_shared_address(smem) + stage * 2 * kHalfBytes;
+    int pages[8];
+    uint32_t expected = 0;
+    int unreadable = 0;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      pages[p] = -1;
+      const int index = tile * pages_per_tile + p;
+      if (p < pages_per_tile && index <= last_page) {
+        const int page = table[index];
+        if (page >= 0 && page < a.num_pages) {
+          pages[p] = page;
+          expected += 2 * page_bytes;
         } else {
-          const int slot = key % a.page_size;
-          // keys and values share one layout: 16-byte chunks, slot-major (hx_cache_offset)
-          cache_element = hx_cache_offset(page, kv_head, slot, chunk * 8, a.kv_heads, a.page_size, D, 8);
+          unreadable = 1;
         }
       }
-      const uint32_t offset = tile_offset<D>(row, chunk);
-      hx_cp_async_16(k_dst + offset, a.k_cache + cache_element, valid ? 16 : 0);
-      hx_cp_async_16(v_dst + offset, a.v_cache + cache_element, valid ? 16 : 0);
+    }
+    tile_state[stage] = unreadable;
+    if (unreadable && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                     hx_shared_address(&full_bar[stage])), "r"(expected) : "memory");
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      if (pages[p] >= 0) {
+        const size_t block = (static_cast<size_t>(pages[p]) * a.kv_heads + kv_head) * page_bytes;
+        bulk_copy(base + p * page_bytes, reinterpret_cast<const uint8_t*>(a.k_cache) + block,
+                  page_bytes, &full_bar[stage]);
+        bulk_copy(base + kHalfBytes + p * page_bytes,
+                  reinterpret_cast<const uint8_t*>(a.v_cache) + block, page_bytes, &full_bar[stage]);
+      }
     }
   };
+  if (tid == 0) {
+    for (int t = 0; t < RING && t < n_tiles; ++t) request_tile(t);
+  }
+  __syncthreads();      // tile_state of the first tiles is visible to every warp
 
-  load_kv_tile(0, 0);
-  hx_cp_async_commit();      // group 0: Q and the first K/V tile
+  // ---- the query rows of this warp, straight from global memory into A fragments:
+  // this thread owns rows (lane / 4) and (lane / 4 + 8) of its warp's 16
+  const int warp_row = warp * 16;
+  uint32_t q_frag[kDSteps][4];
+  {
+    const int r0 = warp_row + (lane >> 2), r1 = r0 + 8;
+    const __nv_bfloat16* q0 = a.q + static_cast<size_t>(q_begin + row0 + min(r0, rows_here - 1)) * a.ldq +
+                              static_cast<size_t>(head) * D + 2 * (lane & 3);
+    const __nv_bfloat16* q1 = a.q + static_cast<size_t>(q_begin + row0 + min(r1, rows_here - 1)) * a.ldq +
+                              static_cast<size_t>(head) * D + 2 * (lane & 3);
+#pragma unroll
+    for (int k = 0; k < kDSteps; ++k) {
+      q_frag[k][0] = *reinterpret_cast<const uint32_t*>(q0 + k * 16);
+      q_frag[k][1] = *reinterpret_cast<const uint32_t*>(q1 + k * 16);
+      q_frag[k][2] = *reinterpret_cast<const uint32_t*>(q0 + k * 16 + 8);
+      q_frag[k][3] = *reinterpret_cast<const uint32_t*>(q1 + k * 16 + 8);
+    }
+  }
 
-  // ---- per-thread state: this thread owns rows (lane / 4) and (lane / 4 + 8) of its warp
+  // where this lane's ldmatrix rows sit inside a tile half (the same for every tile)
+  const int matrix = lane >> 3;
+  const uint32_t piece_step = static_cast<uint32_t>(page_size) * 32;   // two 16-byte pieces on
+  uint32_t k_offset[BLOCK_N / 16], v_offset[BLOCK_N / 16];
+#pragma unroll
+  for (int g = 0; g < BLOCK_N / 16; ++g) {
+    // keys: matrices (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+    k_offset[g] = piece_offset(g * 16 + (matrix >> 1) * 8 + (lane & 7), matrix & 1, page_size,
+                               page_bytes);
+    // values, transposed: (keys 0-7, d lo), (keys 8-15, d lo), (keys 0-7, d hi), (keys 8-15, d hi)
+    v_offset[g] = piece_offset(g * 16 + (matrix & 1) * 8 + (lane & 7), matrix >> 1, page_size,
+                               page_bytes);
+  }
+
   float o_acc[kOBlocks][4];
 #pragma unroll
   for (int n = 0; n < kOBlocks; ++n)
@@ -150,33 +223,36 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
     for (int e = 0; e < 4; ++e) o_acc[n][e] = 0.0f;
   float row_max[2] = {-INFINITY, -INFINITY};
   float row_sum[2] = {0.0f, 0.0f};
-  uint32_t q_frag[kDSteps][4];
-  const int warp_row = warp * 16;
   const int q_pos0 = context + row0 + warp_row + (lane >> 2);   // position of the first row
   const int q_pos1 = q_pos0 + 8;
 
   for (int tile = 0; tile < n_tiles; ++tile) {
-    const int stage = tile & 1;
-    if (tile + 1 < n_tiles) {
-      load_kv_tile(tile + 1, stage ^ 1);
-      hx_cp_async_commit();
-      hx_cp_async_wait<1>();
-    } else {
-      hx_cp_async_wait<0>();
+    const int stage = tile % RING;
+    bool arrived = true;
+    if (lane == 0) arrived = tile_wait(&full_bar[stage], static_cast<uint32_t>(tile / RING) & 1u);
+    arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
+    if (!arrived) {
+      if (lane == 0 && a.status != nullptr) atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
+      return;      // no block-wide barrier follows a failed wait in any warp: all warps fail alike
     }
-    __syncthreads();
+    const uint32_t k_base = hx_shared_address(smem) + stage * 2 * kHalfBytes;
+    const uint32_t v_base = k_base + kHalfBytes;
 
-    if (tile == 0) {
-#pragma unroll
-      for (int k = 0; k < kDSteps; ++k) {
-        const int row = warp_row + (lane & 15);
-        const int chunk = k * 2 + (lane >> 4);
-        hx_ldmatrix_x4(q_frag[k], hx_shared_address(q_tile) + tile_offset<D>(row, chunk));
+    // Behind the last key the tile holds whatever the pages (or an earlier tile) left there.
+    // Scores of such keys are masked by selection, but a value of NaN would survive a zero
+    // probability, so those value rows are cleared; likewise everything of an unreadable tile.
+    const int first_stale = tile_state[stage] ? 0 : last_key + 1 - tile * BLOCK_N;
+    if (first_stale < BLOCK_N) {
+      for (int index = tid; index < BLOCK_N * (D / 8); index += THREADS) {
+        const int key = index / (D / 8);
+        const int piece = index - key * (D / 8);
+        if (key >= first_stale) {
+          const uint32_t address = v_base + piece_offset(key, piece, page_size, page_bytes);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(address), "r"(0u) : "memory");
+        }
       }
+      __syncthreads();
     }
-
-    const uint32_t k_base = hx_shared_address(kv_tiles + stage * 2 * kTileBytes);
-    const uint32_t v_base = k_base + kTileBytes;
 
     // ---- S = Q K^T for 16 rows x 64 keys: 8 n-blocks of 8 keys
     float s[BLOCK_N / 8][4];
@@ -188,12 +264,8 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
     for (int k = 0; k < kDSteps; ++k) {
 #pragma unroll
       for (int pair = 0; pair < BLOCK_N / 16; ++pair) {
-        // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
-        const int matrix = lane >> 3;
-        const int key_row = pair * 16 + (matrix >> 1) * 8 + (lane & 7);
-        const int chunk = k * 2 + (matrix & 1);
         uint32_t b[4];
-        hx_ldmatrix_x4(b, k_base + tile_offset<D>(key_row, chunk));
+        hx_ldmatrix_x4(b, k_base + k_offset[pair] + k * piece_step);
         hx_mma_bf16(s[pair * 2], q_frag[k], b[0], b[1]);
         hx_mma_bf16(s[pair * 2 + 1], q_frag[k], b[2], b[3]);
       }
@@ -256,13 +328,8 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
           hx_split_bf16(p[half][r * 2], p[half][r * 2 + 1], p_hi[half * 2 + r], p_lo[half * 2 + r]);
 #pragma unroll
       for (int nn = 0; nn < kOBlocks / 2; ++nn) {
-        // transposed load of V[keys kk*16 .. +15][d nn*16 .. +15]:
-        // matrices (keys 0-7, d lo), (keys 8-15, d lo), (keys 0-7, d hi), (keys 8-15, d hi)
-        const int matrix = lane >> 3;
-        const int key_row = kk * 16 + (matrix & 1) * 8 + (lane & 7);
-        const int chunk = nn * 2 + (matrix >> 1);
-        uint32_t b[4];
-        hx_ldmatrix_x4_trans(b, v_base + tile_offset<D>(key_row, chunk));
+        uint32_t b[4];      // V[keys kk*16 .. +15][d nn*16 .. +15], transposed
+        hx_ldmatrix_x4_trans(b, v_base + v_offset[kk] + nn * piece_step);
         hx_mma_bf16(o_acc[nn * 2], p_hi, b[0], b[1]);
         hx_mma_bf16(o_acc[nn * 2], p_lo, b[0], b[1]);
         hx_mma_bf16(o_acc[nn * 2 + 1], p_hi, b[2], b[3]);
@@ -270,6 +337,10 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
       }
     }
     __syncthreads();      // every warp is done with this stage before it is refilled
+    if (tid == 0 && tile + RING < n_tiles) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      request_tile(tile + RING);
+    }
   }
 
   // ---- finish: full row sums, normalise, store
@@ -296,7 +367,7 @@ __global__ __launch_bounds__(THREADS) void prefill_attention_kernel(PrefillArgs 
 
 template <int D>
 int launch(const PrefillArgs& a, int tiles, cudaStream_t stream) {
-  constexpr int kSmem = BLOCK_M * D * 2 + 2 * 2 * BLOCK_N * D * 2;
+  constexpr int kSmem = RING * 2 * BLOCK_N * D * 2;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(prefill_attention_kernel<D>,
@@ -314,8 +385,11 @@ int launch(const PrefillArgs& a, int tiles, cudaStream_t stream) {
 
 }  // namespace
 
-// 1 when the tensor-core kernel takes this head size (bfloat16 only).
-HX_API int hx_prefill_attention_supports(int head_dim) { return head_dim == 64 || head_dim == 128; }
+// 1 when the tensor-core kernel takes this head size and page size (bfloat16 only).
+HX_API int hx_prefill_attention_supports(int head_dim, int page_size) {
+  return (head_dim == 64 || head_dim == 128) &&
+         (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
+}
 
 // Attention of every request that brings at least `min_query_len` tokens to this step.
 // `tile_bound` is an upper bound of the number of 64-row query tiles over those requests
@@ -327,8 +401,9 @@ HX_API int hx_prefill_attention(const void* q, int ldq, const void* k_cache, con
                                 int heads, int kv_heads, int head_dim, int page_size,
                                 int num_pages, float scale, int min_query_len, int* status,
                                 cudaStream_t stream) {
-  HX_REQUIRE(hx_prefill_attention_supports(head_dim),
-             "hx_prefill_attention: head_dim %d is not supported (64 or 128)", head_dim);
+  HX_REQUIRE(hx_prefill_attention_supports(head_dim, page_size),
+             "hx_prefill_attention: head_dim %d with pages of %d is not supported (head sizes 64 "
+             "and 128, pages of 8, 16, 32 or 64)", head_dim, page_size);
   HX_REQUIRE(requests >= 0 && tile_bound >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
              "hx_prefill_attention: bad sizes");
   HX_REQUIRE(heads <= 65535, "hx_prefill_attention: too many heads");

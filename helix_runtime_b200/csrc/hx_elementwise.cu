@@ -263,7 +263,11 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
                                    int heads, int kv_heads, int head_dim, int rotary_dim,
                                    int pairing, int page_size, int num_pages, int* status,
                                    float* __restrict__ accum, int ld_accum) {
-  hx_pdl_prologue();
+    // The attention kernel that follows fills the GPU with one resident grid of warps that
+  // all start on equal runs of work; let in early, they would all leave the wait in the same
+  // instant and stay in step, fetching and computing in bursts (measured: twice the time at
+  // batch 64).  So it is launched when this kernel is done.
+  hx_pdl_prologue_keep_successor_out();
   const int token = blockIdx.x;
   const int position = positions[token];
   T* row = qkv + static_cast<size_t>(token) * ld;

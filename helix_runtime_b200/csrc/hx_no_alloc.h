@@ -16,7 +16,8 @@
 // that allocates.
 //
 // Limits.  The array holds HX_NO_ALLOC_PARTIAL_WORDS floats of partial sums
-// (tokens * heads * max_splits * (head_dim + 2) must fit) and HX_NO_ALLOC_COUNTER_WORDS
+// (hx_paged_attention_scratch_floats(): tokens * heads * max_splits * (head_dim + 2), and a
+// fixed amount for the streaming kernel, must fit) and HX_NO_ALLOC_COUNTER_WORDS
 // counters (tokens * heads must fit): 4.25 MiB in all, resident on every GPU that loads the
 // library until the process exits.  A call that needs more is refused with an error message
 // that says how much it needed; nothing is launched then.

@@ -65,7 +65,7 @@ def _declare(library: ctypes.CDLL) -> None:
         _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int,
         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr]
     library.hx_prefill_attention.restype = _c_int
-    library.hx_prefill_attention_supports.argtypes = [_c_int]
+    library.hx_prefill_attention_supports.argtypes = [_c_int, _c_int]
     library.hx_prefill_attention_supports.restype = _c_int
     library.hx_paged_attention_scratch_floats.restype = ctypes.c_longlong
     library.hx_paged_attention_scratch_floats.argtypes = [_c_int] * 4
@@ -227,11 +227,15 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     arrivals: Optional[torch.Tensor] = None) -> None:
     """out[t, h*D:(h+1)*D] = attention of query (t, h) over its request's pages.  With
     ``skip_query_len > 0`` tokens of requests that bring at least that many tokens are left
-    out (the tensor-core kernel takes them).  With ``max_splits > 1`` the call needs scratch:
-    ``partial`` (float32, see :func:`attention_scratch_floats`) and ``arrivals`` (int32, one
-    counter per (token, head), zero on entry; the kernel leaves it zero)."""
-    if max_splits > 1 and arrivals is None:
-        arrivals = torch.zeros(tokens * heads, dtype=torch.int32, device=q.device)
+    out (the tensor-core kernel takes them).  The call needs scratch, made here when it is
+    not given: ``partial`` (float32, :func:`attention_scratch_floats` elements) and
+    ``arrivals`` (int32, one counter per (token, head), zero on entry; the kernel leaves it
+    zero)."""
+    if arrivals is None:
+        arrivals = torch.zeros(max(1, tokens * heads), dtype=torch.int32, device=q.device)
+    if partial is None:
+        partial = torch.empty(attention_scratch_floats(tokens, heads, head_dim, max_splits),
+                              dtype=torch.float32, device=q.device)
     _check(lib().hx_paged_attention(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), dtype_code(q.dtype),
         positions.data_ptr(), token_request.data_ptr(), request_table_row.data_ptr(),
@@ -241,8 +245,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         float(scale), split_keys, max_splits, _ptr(status), _stream()))
 
 
-def prefill_attention_supports(head_dim: int) -> bool:
-    return bool(lib().hx_prefill_attention_supports(head_dim))
+def prefill_attention_supports(head_dim: int, page_size: int) -> bool:
+    return bool(lib().hx_prefill_attention_supports(head_dim, page_size))
 
 
 def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -128,7 +128,7 @@ class PagedAttention(Mixer):
         # to the CUDA-core kernel.  A step may need both.
         tensor_cores = (ctx.dtype == torch.bfloat16 and not window
                         and ctx.max_query_len >= TENSOR_CORE_MIN_QUERY
-                        and ops.prefill_attention_supports(self.head_dim))
+                        and ops.prefill_attention_supports(self.head_dim, cache.page_size))
         if tensor_cores:
             ops.prefill_attention(qkv, cache.keys, cache.values, ctx.request_start,
                                   ctx.request_context, ctx.request_slot, cache.block_tables,
@@ -139,12 +139,10 @@ class PagedAttention(Mixer):
             longest = ctx.max_context_len if not window else min(ctx.max_context_len, window)
             split_keys = self.split_keys_for(n, longest, ctx.attention_split_keys)
             max_splits = max(1, -(-longest // split_keys))
-            partial = arrivals = None
-            if max_splits > 1:
-                floats = ops.attention_scratch_floats(n, self.heads, self.head_dim, max_splits)
-                partial = ctx.workspace.at_least("attention.partial", floats, torch.float32)
-                arrivals = ctx.workspace.accumulator("attention.arrivals",
-                                                     (ctx.capacity * self.heads,), torch.int32)
+            floats = ops.attention_scratch_floats(n, self.heads, self.head_dim, max_splits)
+            partial = ctx.workspace.at_least("attention.partial", floats, torch.float32)
+            arrivals = ctx.workspace.accumulator("attention.arrivals",
+                                                 (ctx.capacity * self.heads,), torch.int32)
             ops.paged_attention(qkv, cache.keys, cache.values, ctx.positions, ctx.token_request,
                                 ctx.request_slot, cache.block_tables, context, partial, n,
                                 self.heads, self.kv_heads, self.head_dim, cache.page_size,

@@ -319,9 +319,11 @@ def test_rope_reads_and_clears_a_split_k_accumulator():
 # ------------------------------------------------------------------- attention
 
 def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, new_tokens,
-                   window, split_keys, dominant=None, tensor_core_min=0):
+                   window, split_keys, dominant=None, tensor_core_min=0, lost_page=None):
     """Build a paged cache holding ``contexts[r] + new_tokens[r]`` keys per request in shuffled
-    pages and the queries of the new tokens; return kernel output and plain reference."""
+    pages and the queries of the new tokens; return kernel output and plain reference.
+    ``lost_page=(request, index)`` points that entry of the block table outside the pool: the
+    kernel has to raise the bad-page flag and go on without those keys."""
     requests = len(contexts)
     totals = [c + n for c, n in zip(contexts, new_tokens)]
     pages_per = [-(-t // page_size) for t in totals]
@@ -351,6 +353,11 @@ def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, n
             lo, hi = p * page_size, min((p + 1) * page_size, totals[r])
             k_cache[page, :, :hi - lo] = keys[r][:, lo:hi]
             v_cache[page, :, :hi - lo] = values[r][:, lo:hi]
+    lost_keys = None
+    if lost_page is not None:
+        r, p = lost_page
+        tables[slots[r], p] = num_pages + 5
+        lost_keys = (r, p * page_size, min((p + 1) * page_size, totals[r]))
     positions, token_request, q_rows = [], [], []
     for r in range(requests):
         for i in range(new_tokens[r]):
@@ -386,10 +393,16 @@ def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, n
                             heads, kv_heads, head_dim, page_size, num_pages, window or 0, scale,
                             split_keys, max_splits, status, request_start=starts,
                             skip_query_len=tensor_core_min)
-    assert int(status.item()) == 0
+    assert int(status.item()) == (0 if lost_page is None else ops.FLAG_BAD_PAGE)
     expected = []
     for r in range(requests):
-        context = plain.causal_attention(queries[r], keys[r], values[r], query_offset=contexts[r],
+        k_r, v_r, offset = keys[r], values[r], contexts[r]
+        if lost_keys is not None and lost_keys[0] == r:
+            # decode token: it sees every key that is left
+            assert new_tokens[r] == 1 and lost_keys[2] <= contexts[r]
+            keep = np.r_[0:lost_keys[1], lost_keys[2]:totals[r]]
+            k_r, v_r, offset = k_r[:, keep], v_r[:, keep], len(keep) - 1
+        context = plain.causal_attention(queries[r], k_r, v_r, query_offset=offset,
                                          window=window or None)
         expected.append(context.transpose(1, 0, 2).reshape(new_tokens[r], heads * head_dim))
     return host(out), np.concatenate(expected), values, positions, token_request
@@ -414,6 +427,45 @@ def test_paged_attention_mixed_batch(dtype, heads, kv_heads, head_dim, page_size
                                        new_tokens, window=None, split_keys=64)
     tol = dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=8e-3)
     assert_close(out, expected, "attention", **tol)
+
+
+def test_streaming_attention_row_shared_by_hundreds_of_warps():
+    """One decode token over 30,000 keys: each of its rows is cut into a few hundred parts
+    (more than one merge batch), and one key far inside takes all the weight."""
+    rng = np.random.default_rng(21)
+    key_position = 12345
+    out, expected, values, *_ = attention_case(rng, torch.bfloat16, 2, 2, 128, 16, [29999], [1],
+                                               window=None, split_keys=64,
+                                               dominant={0: key_position})
+    assert_close(out, expected, "attention", atol=2e-2, rtol=8e-3)
+    wanted = values[0][:, key_position].reshape(1, -1)
+    assert_close(out, wanted, "dominant key's value", atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [(3, 3, 64, 8), (4, 2, 128, 32)])
+def test_streaming_attention_many_requests_of_mixed_length(heads, kv_heads, head_dim, page_size):
+    """Seventy requests (more than one group of 32 tokens) with contexts from 0 to 700 keys,
+    most decoding one token, some bringing two or three: runs of chunks cross rows, tokens
+    and requests everywhere."""
+    rng = np.random.default_rng(22)
+    contexts = [int(c) for c in rng.integers(0, 700, size=70)]
+    contexts[0], contexts[5], contexts[40] = 0, 31, 32
+    new_tokens = [1] * 70
+    new_tokens[3], new_tokens[33], new_tokens[69] = 2, 3, 2
+    out, expected, *_ = attention_case(rng, torch.bfloat16, heads, kv_heads, head_dim, page_size,
+                                       contexts, new_tokens, window=None, split_keys=64)
+    assert_close(out, expected, "attention", atol=2e-2, rtol=8e-3)
+
+
+@pytest.mark.parametrize("dtype,head_dim", [(torch.bfloat16, 128), (torch.bfloat16, 32),
+                                            (torch.float32, 64)])
+def test_attention_flags_a_page_outside_the_pool_and_leaves_its_keys_out(dtype, head_dim):
+    rng = np.random.default_rng(23)
+    out, expected, *_ = attention_case(rng, dtype, 4, 2, head_dim, 16, [10, 200, 70], [1, 1, 1],
+                                       window=None, split_keys=64, lost_page=(1, 5))
+    assert np.isfinite(out).all()
+    tol = dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=8e-3)
+    assert_close(out, expected, "attention without the lost page", **tol)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -441,7 +493,7 @@ def test_one_far_key_stands_out(dtype, key_position):
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [
-    (4, 4, 128, 16), (6, 2, 64, 8), (3, 1, 128, 32), (2, 2, 64, 4)])
+    (4, 4, 128, 16), (6, 2, 64, 8), (3, 1, 128, 32), (2, 2, 64, 64)])
 def test_tensor_core_attention_for_prompt_portions(heads, kv_heads, head_dim, page_size):
     rng = np.random.default_rng(12)
     # whole prompts (one longer than two tiles, one a single row short of a tile), continued
@@ -464,6 +516,20 @@ def test_tensor_core_attention_sees_one_far_key(key_position):
     assert_close(out, expected, "attention", atol=2e-2, rtol=8e-3)
     wanted = values[0][:, key_position].reshape(1, -1)
     assert_close(out[-1:], wanted, "dominant key's value", atol=2e-2, rtol=1e-2)
+
+
+def test_tensor_core_attention_refuses_what_it_cannot_tile():
+    assert ops.prefill_attention_supports(128, 16) and ops.prefill_attention_supports(64, 64)
+    # pages of 4 or 24 keys do not tile its 64-key steps, and a head of 80 is not built: the
+    # mixer then takes the CUDA-core kernel, and a direct call is an error, not a wrong result
+    for head_dim, page_size in ((64, 4), (128, 24), (80, 16)):
+        assert not ops.prefill_attention_supports(head_dim, page_size)
+    q = torch.zeros((16, 2 * 64), dtype=torch.bfloat16, device=DEVICE)
+    cache = torch.zeros((8, 2, 4, 64), dtype=torch.bfloat16, device=DEVICE)
+    zeros = torch.zeros(8, dtype=torch.int32, device=DEVICE)
+    with pytest.raises(ops.KernelError, match="pages of 4"):
+        ops.prefill_attention(q, cache, cache, zeros, zeros, zeros, zeros.view(1, 8), q.clone(),
+                              1, 16, 2, 2, 64, 4, 8, 0.125, 16, status_word())
 
 
 def test_attention_refuses_odd_head_sizes():
