@@ -372,6 +372,133 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
   }
 }
 
+// The same for bfloat16 rows whose heads are made of whole 16-byte pieces (8 coordinates):
+// one thread per piece, every access 16 bytes wide (32 for the float32 accumulator), and a
+// piece of a key or value is exactly one 16-byte chunk of the cache layout.  With half-split
+// pairs the thread of a piece in the first half of the rotary part also takes the partner
+// piece in the second half, whose own thread idles.
+__global__ void rope_append_pieces_kernel(
+    __nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ positions,
+    const int* __restrict__ token_request, const int* __restrict__ request_table_row,
+    const int* __restrict__ block_tables, int table_stride, __nv_bfloat16* __restrict__ k_cache,
+    __nv_bfloat16* __restrict__ v_cache, int write_cache, const float* __restrict__ cos_table,
+    const float* __restrict__ sin_table, int table_positions, int heads, int kv_heads,
+    int head_dim, int rotary_dim, int pairing, int page_size, int num_pages, int* status,
+    float* __restrict__ accum, int ld_accum) {
+  // the attention kernel that follows is launched when this one is done (see above)
+  hx_pdl_prologue_keep_successor_out();
+  const int token = blockIdx.x;
+  const int pieces_per_head = head_dim / 8;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;
+  const int head = item / pieces_per_head;
+  const int piece = item - head * pieces_per_head;
+  if (head >= heads + 2 * kv_heads) return;
+
+  const int position = positions[token];
+  int page = -1, slot = 0;
+  if (write_cache && head >= heads) {
+    const int table_row = request_table_row[token_request[token]];
+    page = block_tables[static_cast<size_t>(table_row) * table_stride + position / page_size];
+    slot = position % page_size;
+    if (page < 0 || page >= num_pages) {
+      if (status != nullptr) atomicOr(status, HX_FLAG_BAD_PAGE);
+      page = -1;
+    }
+  }
+
+  // eight coordinates starting at d0, from the accumulator (rounded as the projection's own
+  // store would have rounded them; the accumulator is cleared) or from the row
+  auto load = [&](int d0, float (&x)[8]) {
+    if (accum != nullptr) {
+      float4* source = reinterpret_cast<float4*>(accum + static_cast<size_t>(token) * ld_accum +
+                                                 static_cast<size_t>(head) * head_dim + d0);
+      const float4 lo = source[0], hi = source[1];
+      source[0] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      source[1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      const float raw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = __bfloat162float(__float2bfloat16_rn(raw[i]));
+    } else {
+      const uint4 packed = *reinterpret_cast<const uint4*>(
+          qkv + static_cast<size_t>(token) * ld + static_cast<size_t>(head) * head_dim + d0);
+      const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&packed);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(pairs[i]);
+        x[2 * i] = v.x;
+        x[2 * i + 1] = v.y;
+      }
+    }
+  };
+  auto store = [&](int d0, const float (&x)[8]) {
+    uint4 packed;
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pairs[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    if (head < heads) {
+      *reinterpret_cast<uint4*>(qkv + static_cast<size_t>(token) * ld +
+                                static_cast<size_t>(head) * head_dim + d0) = packed;
+    } else if (page >= 0) {
+      const bool is_key = head < heads + kv_heads;
+      const int kv_head = is_key ? head - heads : head - heads - kv_heads;
+      __nv_bfloat16* cache = is_key ? k_cache : v_cache;
+      *reinterpret_cast<uint4*>(
+          cache + hx_cache_offset(page, kv_head, slot, d0, kv_heads, page_size, head_dim, 8)) = packed;
+    }
+  };
+
+  const int d0 = piece * 8;
+  const int half = rotary_dim / 2;
+  const bool rotates = head < heads + kv_heads && d0 < rotary_dim;
+  if (!rotates) {
+    // values, and coordinates behind the rotary part: moved as they are (a query piece that
+    // came from the row is already where it belongs)
+    if (accum == nullptr && head < heads) return;
+    float x[8];
+    load(d0, x);
+    store(d0, x);
+    return;
+  }
+  const int table_position = position < table_positions ? position : table_positions - 1;
+  const float* cos_row = cos_table + static_cast<size_t>(table_position) * half;
+  const float* sin_row = sin_table + static_cast<size_t>(table_position) * half;
+  if (pairing == 0) {
+    // pairs (2p, 2p + 1): this piece holds pairs d0 / 2 .. d0 / 2 + 3
+    float x[8];
+    load(d0, x);
+    const float4 c = *reinterpret_cast<const float4*>(cos_row + d0 / 2);
+    const float4 sn = *reinterpret_cast<const float4*>(sin_row + d0 / 2);
+    const float cs[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = x[2 * i], b = x[2 * i + 1];
+      x[2 * i] = a * cs[i] - b * ss[i];
+      x[2 * i + 1] = a * ss[i] + b * cs[i];
+    }
+    store(d0, x);
+  } else {
+    // pairs (p, p + half): the thread of the first-half piece rotates both pieces
+    if (d0 >= half) return;
+    float x[8], y[8];
+    load(d0, x);
+    load(d0 + half, y);
+    const float4 c0 = *reinterpret_cast<const float4*>(cos_row + d0);
+    const float4 c1 = *reinterpret_cast<const float4*>(cos_row + d0 + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sin_row + d0);
+    const float4 s1 = *reinterpret_cast<const float4*>(sin_row + d0 + 4);
+    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float a = x[i], b = y[i];
+      x[i] = a * cs[i] - b * ss[i];
+      y[i] = a * ss[i] + b * cs[i];
+    }
+    store(d0, x);
+    store(d0 + half, y);
+  }
+}
+
 HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
                           const int* token_request, const int* request_table_row,
                           const int* block_tables, int table_stride, void* k_cache, void* v_cache,
@@ -395,7 +522,22 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
   const int threads = head_dim / 2 >= 64 ? 64 : 32;
   const dim3 grid(tokens, (heads + 2 * kv_heads + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
   HX_REQUIRE(grid.y <= 65535, "hx_rope_append: too many heads");
-  if (dtype == HX_F32) {
+  const int half = rotary_dim / 2;
+  const bool whole_pieces =
+      dtype == HX_BF16 && head_dim % 8 == 0 && ld % 8 == 0 && (accum == nullptr || ld_accum % 4 == 0) &&
+      (pairing == 0 ? rotary_dim % 8 == 0 : half % 8 == 0);
+  if (whole_pieces) {
+    const int items = (heads + 2 * kv_heads) * (head_dim / 8);
+    const int block = items >= 256 ? 256 : ((items + 31) / 32) * 32;
+    const dim3 piece_grid(tokens, (items + block - 1) / block);
+    HX_REQUIRE(piece_grid.y <= 65535, "hx_rope_append: too many heads");
+    hx_launch(rope_append_pieces_kernel, piece_grid, block, 0, stream,
+              static_cast<__nv_bfloat16*>(qkv), ld, positions, token_request, request_table_row,
+              block_tables, table_stride, static_cast<__nv_bfloat16*>(k_cache),
+              static_cast<__nv_bfloat16*>(v_cache), write_cache, cos_table, sin_table,
+              table_positions, heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages,
+              status, accum, ld_accum);
+  } else if (dtype == HX_F32) {
     hx_launch(rope_append_kernel<float>, grid, threads, 0, stream,  static_cast<float*>(qkv), ld, positions, token_request, request_table_row, block_tables, table_stride, static_cast<float*>(k_cache), static_cast<float*>(v_cache), write_cache, cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status, accum, ld_accum);
   } else if (dtype == HX_BF16) {
     hx_launch(rope_append_kernel<__nv_bfloat16>, grid, threads, 0, stream,  static_cast<__nv_bfloat16*>(qkv), ld, positions, token_request, request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), write_cache, cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status, accum, ld_accum);
