@@ -29,6 +29,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 namespace {
@@ -154,6 +155,44 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_address) {
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// One epilogue warp's share of a finished tile: its 32 features (tensor-memory lanes) for all
+// BN token columns, 16 columns at a time.  With SwiGLU the up accumulator sits BN columns on.
+template <int BN, int EPI>
+__device__ __forceinline__ void write_tile(void* out, int ldo, int tokens, int features,
+                                           uint32_t lane_address, int feature, int token0) {
+  const bool feature_ok = feature < features;
+#pragma unroll 1
+  for (int column = 0; column < BN; column += 16) {
+    if (token0 + column >= tokens) break;   // uniform over the warp
+    float acc[16];
+    tmem_load16(lane_address + column, acc);
+    if (EPI == EPI_SWIGLU) {
+      float up[16];
+      tmem_load16(lane_address + BN + column, up);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] = hx_silu_fast(acc[j]) * up[j];
+    }
+    if (feature_ok) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int token = token0 + column + j;
+        if (token < tokens) {
+          const size_t index = static_cast<size_t>(token) * ldo + feature;
+          if (EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU) {
+            static_cast<__nv_bfloat16*>(out)[index] = __float2bfloat16_rn(acc[j]);
+          } else if (EPI == EPI_STORE_F32) {
+            static_cast<float*>(out)[index] = acc[j];
+          } else {
+            // a reduction at the memory side: nothing to wait for.  With one writer per
+            // element the sum is still deterministic.
+            atomicAdd(static_cast<float*>(out) + index, acc[j]);
+          }
+        }
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------- kernel
@@ -312,37 +351,348 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
       } else {
         tc_fence_after();
         const uint32_t lane_address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        const bool feature_ok = feature < args.features;
+        write_tile<BN, EPI>(args.out, args.ldo, args.tokens, args.features, lane_address, feature,
+                            token0);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Config::kTmemColumns);
+  }
+}
+
+// ------------------------------------------------- persistent kernel for prompt portions
+//
+// With hundreds of tokens the product is compute bound, and the tile's epilogue (reading a
+// 128 x 256 accumulator back, converting, storing) takes a good part of the time of its main
+// loop.  Here one CTA per SM walks a list of work units: all of shared memory is one ring of
+// operand stages that runs on across units, tensor memory holds TWO accumulators of 256
+// columns, and the epilogue warps drain one while the MMA warp fills the other.
+//
+// The tile is turned round with respect to the kernel above: 128 TOKENS are the MMA's M
+// side and 256 weight rows its N side, so a thread of the epilogue owns one token and finds
+// 256 consecutive features of it in its lane of tensor memory: it writes them 16 at a time
+// with 16-byte stores (or 16-byte reductions into the float32 residual), which the memory
+// system takes several times faster than the two-byte stores of a feature-per-thread layout.
+// For SwiGLU the N side is 128 gate rows followed by the matching 128 up rows of the fused
+// matrix: gate and up of a feature sit side by side in the thread's own lane.
+//
+// The add epilogue does not add at the memory side here (float32 reductions reach only about
+// 1.8 TB/s in the L2, a quarter of what this product would need): while the MMA warp works on
+// one accumulator, the epilogue warps load the output tile of the unit after it INTO the other
+// accumulator (tcgen05.st), the products then accumulate on top of it, and the epilogue
+// stores the sum.  One writer per element: the result is deterministic.
+//
+// Tiles are dealt round-robin with the token tile varying fastest, so the CTAs that run side
+// by side read the same weight tiles at the same time, once from DRAM.
+
+struct PersistentConfig {
+  static constexpr int kRowsA = BM;              // tokens
+  static constexpr int kRowsB = 2 * BM;          // weight rows: the accumulator's columns
+  static constexpr int kBytesA = kRowsA * BK * 2;
+  static constexpr int kBytesB = kRowsB * BK * 2;
+  static constexpr int kStageBytes = kBytesA + kBytesB;
+  static constexpr int kStages = 200 * 1024 / kStageBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int kBufferColumns = 256;     // one accumulator per half of tensor memory
+  static constexpr int kTmemColumns = 512;
+};
+
+struct PersistentArgs {
+  void* out;
+  int ldo;
+  int tokens;
+  int features;
+  int depth;
+  int up_row_offset;
+  int token_tiles;            // tiles along the tokens
+  int units;                  // token_tiles * feature tiles
+  int k_blocks;               // per tile
+  int* status;
+};
+
+struct Unit {
+  int token_tile, feature_tile, kb_begin, kb_end;
+};
+
+__device__ __forceinline__ bool unit_at(const PersistentArgs& a, int iteration, Unit& u) {
+  const int index = blockIdx.x + iteration * gridDim.x;
+  if (index >= a.units) return false;
+  u.token_tile = index % a.token_tiles;
+  u.feature_tile = index / a.token_tiles;
+  u.kb_begin = 0;
+  u.kb_end = a.k_blocks;
+  return true;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 32 lanes x 16 consecutive columns of float32 into tensor memory: thread i writes lane
+// (base lane + i).
+__device__ __forceinline__ void tmem_store16(uint32_t address, const float (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(address),
+      "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+      "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+      "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+      "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+      "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+      "r"(__float_as_uint(v[15]))
+      : "memory");
+}
+
+// The add epilogue's preparation: this thread's token, 256 columns of the float32 output
+// into its lane of the accumulator (zeros where the tile hangs over the output's edge).
+__device__ __forceinline__ void load_row_into_accumulator(const float* out, int ldo, int features,
+                                                          uint32_t lane_address, int token,
+                                                          int tokens, int feature0) {
+  const bool wide = (ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  const float* row = out + static_cast<size_t>(token < tokens ? token : 0) * ldo + feature0;
 #pragma unroll 1
-        for (int column = 0; column < BN; column += 16) {
-          if (token0 + column >= args.tokens) break;   // uniform over the warp
-          float acc[16];
-          tmem_load16(lane_address + column, acc);
-          if (EPI == EPI_SWIGLU) {
-            float up[16];
-            tmem_load16(lane_address + BN + column, up);
+  for (int group = 0; group < 2 * BM; group += 64) {
+    float v[4][16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] = hx_silu_fast(acc[j]) * up[j];
-          }
-          if (feature_ok) {
+    for (int c = 0; c < 4; ++c) {
+      const int column = group + c * 16;
+      if (token < tokens && wide && feature0 + column + 16 <= features) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int token = token0 + column + j;
-              if (token < args.tokens) {
-                const size_t index = static_cast<size_t>(token) * args.ldo + feature;
-                if (EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU) {
-                  static_cast<__nv_bfloat16*>(args.out)[index] = __float2bfloat16_rn(acc[j]);
-                } else if (EPI == EPI_STORE_F32) {
-                  static_cast<float*>(args.out)[index] = acc[j];
-                } else {
-                  // a reduction at the memory side: nothing to wait for.  With one k-split
-                  // each element has a single writer, so the sum is still deterministic.
-                  atomicAdd(static_cast<float*>(args.out) + index, acc[j]);
-                }
-              }
-            }
+        for (int j = 0; j < 4; ++j) {
+          const float4 x = *reinterpret_cast<const float4*>(row + column + 4 * j);
+          v[c][4 * j] = x.x;
+          v[c][4 * j + 1] = x.y;
+          v[c][4 * j + 2] = x.z;
+          v[c][4 * j + 3] = x.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          v[c][j] = (token < tokens && feature0 + column + j < features) ? row[column + j] : 0.0f;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) tmem_store16(lane_address + group + c * 16, v[c]);
+  }
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// This thread's token: `columns` features starting at feature0, 16 at a time, from its lane of
+// the accumulator.  With SwiGLU the accumulator holds 128 gate columns, then 128 up columns.
+template <int EPI>
+__device__ __forceinline__ void write_row(void* out, int ldo, int features, uint32_t lane_address,
+                                          int token, int tokens, int feature0) {
+  using Element = typename std::conditional<EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU,
+                                            __nv_bfloat16, float>::type;
+  constexpr int kColumns = EPI == EPI_SWIGLU ? BM : 2 * BM;
+  const bool wide = (ldo % (16 / static_cast<int>(sizeof(Element))) == 0) &&
+                    ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+#pragma unroll 1
+  for (int column = 0; column < kColumns; column += 16) {
+    if (feature0 + column >= features) break;      // uniform over the warp
+    float acc[16];
+    tmem_load16(lane_address + column, acc);
+    if (EPI == EPI_SWIGLU) {
+      float up[16];
+      tmem_load16(lane_address + BM + column, up);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] = hx_silu_fast(acc[j]) * up[j];
+    }
+    if (token >= tokens) continue;
+    Element* row = static_cast<Element*>(out) + static_cast<size_t>(token) * ldo + feature0 + column;
+    if (wide && feature0 + column + 16 <= features) {
+      if constexpr (std::is_same<Element, __nv_bfloat16>::value) {
+        uint4 packed[2];
+        __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(packed);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) pairs[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        reinterpret_cast<uint4*>(row)[0] = packed[0];
+        reinterpret_cast<uint4*>(row)[1] = packed[1];
+      } else {
+        // the add epilogue too: the accumulator began as the output's old value
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          reinterpret_cast<float4*>(row)[j] =
+              make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (feature0 + column + j < features) {
+          if constexpr (std::is_same<Element, __nv_bfloat16>::value) {
+            row[j] = __float2bfloat16_rn(acc[j]);
+          } else {
+            row[j] = acc[j];
           }
         }
+      }
+    }
+  }
+}
+
+template <int EPI>
+__global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
+    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+    const PersistentArgs args) {
+  using Config = PersistentConfig;
+  constexpr int STAGES = Config::kStages;
+  // features of the output per tile, and where the second half of the N operand comes from
+  constexpr int FEATURES = EPI == EPI_SWIGLU ? BM : 2 * BM;
+
+  hx_pdl_trigger();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Config::kStageBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full_bar = empty_bar + STAGES;      // [2]: the accumulator is complete
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;      // [2]: the epilogue has read it
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 4);      // one arrival per epilogue warp
+    }
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_holder, Config::kTmemColumns);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  hx_pdl_wait();
+
+  if (warp == 0) {
+    // -------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t fill = 0;      // stages filled so far, over all units
+      Unit unit;
+      for (int iteration = 0; unit_at(args, iteration, unit) && !*failed; ++iteration) {
+        const int feature0 = unit.feature_tile * FEATURES;
+        const int second_half = EPI == EPI_SWIGLU ? args.up_row_offset + feature0 : feature0 + BM;
+        const int token0 = unit.token_tile * BM;
+        for (int kb = unit.kb_begin; kb < unit.kb_end; ++kb, ++fill) {
+          const int s = fill % STAGES;
+          const uint32_t round = fill / STAGES;
+          if (!mbar_wait(&empty_bar[s], (round & 1u) ^ 1u)) {
+            atomicOr(args.status, HX_FLAG_WAIT_TIMEOUT);
+            *failed = 1;
+            break;
+          }
+          uint8_t* stage = smem + s * Config::kStageBytes;
+          mbar_expect_tx(&full_bar[s], Config::kStageBytes);
+          const int k = kb * BK;
+          tma_load_2d(stage, &map_x, &full_bar[s], k, token0);
+          tma_load_2d(stage + Config::kBytesA, &map_w, &full_bar[s], k, feature0);
+          tma_load_2d(stage + Config::kBytesA + BM * BK * 2, &map_w, &full_bar[s], k, second_half);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, Config::kRowsB);
+      uint32_t drained = 0;      // stages consumed so far, over all units
+      Unit unit;
+      for (int iteration = 0; unit_at(args, iteration, unit) && !*failed; ++iteration) {
+        const int buffer = iteration & 1;
+        const uint32_t use = static_cast<uint32_t>(iteration >> 1);
+        // the epilogue must have read this accumulator's previous unit (and, for the add
+        // epilogue, have loaded this unit's old output into it: one more arrival)
+        if (!mbar_wait(&tmem_empty_bar[buffer], EPI == EPI_ADD_F32 ? (use & 1u) : (use & 1u) ^ 1u)) {
+          atomicOr(args.status, HX_FLAG_WAIT_TIMEOUT);
+          *failed = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t accumulator = tmem_base + buffer * Config::kBufferColumns;
+        for (int kb = unit.kb_begin; kb < unit.kb_end; ++kb, ++drained) {
+          const int s = drained % STAGES;
+          const uint32_t round = drained / STAGES;
+          if (!mbar_wait(&full_bar[s], round & 1u)) {
+            atomicOr(args.status, HX_FLAG_WAIT_TIMEOUT);
+            *failed = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t stage = smem_u32(smem + s * Config::kStageBytes);
+          const uint64_t desc_a = make_smem_desc(stage);
+          const uint64_t desc_b = make_smem_desc(stage + Config::kBytesA);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t step = static_cast<uint64_t>(k * UMMA_K * 2 >> 4);
+            const uint32_t accumulate =
+                (EPI == EPI_ADD_F32 || kb > unit.kb_begin || k > 0) ? 1u : 0u;
+            umma_bf16(accumulator, desc_a + step, desc_b + step, idesc, accumulate);
+          }
+          umma_commit(&empty_bar[s]);
+        }
+        if (*failed) break;
+        umma_commit(&tmem_full_bar[buffer]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;     // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    Unit unit;
+    // add epilogue: the old output of unit `iteration` goes into its accumulator, which is
+    // then handed to the MMA warp
+    auto prepare = [&](int iteration) {
+      if (EPI != EPI_ADD_F32 || !unit_at(args, iteration, unit)) return;
+      const int buffer = iteration & 1;
+      load_row_into_accumulator(static_cast<const float*>(args.out), args.ldo, args.features,
+                                lane_base + buffer * Config::kBufferColumns,
+                                unit.token_tile * BM + quarter * 32 + lane, args.tokens,
+                                unit.feature_tile * FEATURES);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
+    };
+    prepare(0);
+    prepare(1);
+    for (int iteration = 0; unit_at(args, iteration, unit) && !*failed; ++iteration) {
+      const int buffer = iteration & 1;
+      const uint32_t use = static_cast<uint32_t>(iteration >> 1);
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(&tmem_full_bar[buffer], use & 1u);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) {
+        if (lane == 0) {
+          atomicOr(args.status, HX_FLAG_WAIT_TIMEOUT);
+          *failed = 1;
+        }
+        break;
+      }
+      tc_fence_after();
+      write_row<EPI>(args.out, args.ldo, args.features,
+                     lane_base + buffer * Config::kBufferColumns,
+                     unit.token_tile * BM + quarter * 32 + lane, args.tokens,
+                     unit.feature_tile * FEATURES);
+      // every lane's tcgen05.ld has completed (the loads are waited for where they are
+      // issued): hand the accumulator back
+      if (EPI == EPI_ADD_F32) {
+        prepare(iteration + 2);
+      } else {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
       }
     }
   }
@@ -470,6 +820,51 @@ int launch_epilogue(int epilogue, const CUtensorMap& map_w, const CUtensorMap& m
   }
 }
 
+template <int EPI>
+int launch_persistent(const CUtensorMap& map_w, const CUtensorMap& map_x, PersistentArgs args,
+                      cudaStream_t stream) {
+  using Config = PersistentConfig;
+  static bool configured = false;
+  static int sms = 0;
+  if (!configured) {
+    int device = 0;
+    if (cudaFuncSetAttribute(gemm_tc_persistent_kernel<EPI>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Config::kSmemBytes) != cudaSuccess ||
+        cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        sms <= 0) {
+      hx_set_error("hx_gemm_tc: cannot reserve %d bytes of shared memory", Config::kSmemBytes);
+      cudaGetLastError();
+      return HX_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  constexpr int kFeatures = EPI == EPI_SWIGLU ? BM : 2 * BM;
+  const int feature_tiles = (args.features + kFeatures - 1) / kFeatures;
+  args.token_tiles = (args.tokens + BM - 1) / BM;
+  const long long tiles = static_cast<long long>(args.token_tiles) * feature_tiles;
+  HX_REQUIRE(tiles < (1ll << 30), "hx_gemm_tc: too many tiles");
+  args.units = static_cast<int>(tiles);
+  const int ctas = args.units < sms ? args.units : sms;
+  hx_launch(gemm_tc_persistent_kernel<EPI>, ctas, THREADS, Config::kSmemBytes, stream, map_w,
+            map_x, args);
+  return HX_OK;
+}
+
+int launch_persistent_epilogue(int epilogue, const CUtensorMap& map_w, const CUtensorMap& map_x,
+                               const PersistentArgs& args, cudaStream_t stream) {
+  switch (epilogue) {
+    case EPI_STORE_BF16: return launch_persistent<EPI_STORE_BF16>(map_w, map_x, args, stream);
+    case EPI_STORE_F32: return launch_persistent<EPI_STORE_F32>(map_w, map_x, args, stream);
+    case EPI_ADD_F32: return launch_persistent<EPI_ADD_F32>(map_w, map_x, args, stream);
+    case EPI_SWIGLU: return launch_persistent<EPI_SWIGLU>(map_w, map_x, args, stream);
+    default:
+      hx_set_error("hx_gemm_tc: unknown epilogue %d", epilogue);
+      return HX_ERR_ARGUMENT;
+  }
+}
+
 }  // namespace
 
 // Token tile the kernel would use for this many tokens (for tests and the bench's records).
@@ -514,13 +909,23 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
   HX_REQUIRE(ldo >= features, "hx_gemm_tc: output stride too small");
 
   const int bn = hx_gemm_tc_token_tile(tokens);
+  // prompt portions: the persistent kernel, whose tiles have 128 tokens on the M side
+  const bool persistent = bn >= 128 && k_splits == 1;
   CUtensorMap map_w, map_x;
   int rc = get_tensor_map(w, weight_rows, depth, ldw, BM, &map_w);
   if (rc != HX_OK) return rc;
-  rc = get_tensor_map(x, x_capacity_rows, depth, ldx, bn, &map_x);
+  rc = get_tensor_map(x, x_capacity_rows, depth, ldx, persistent ? BM : bn, &map_x);
   if (rc != HX_OK) return rc;
 
   const int total_k_blocks = (depth + BK - 1) / BK;
+  if (persistent) {
+    PersistentArgs args{out, ldo, tokens, features, depth, up_row_offset, 0, 0, total_k_blocks,
+                        status};
+    rc = launch_persistent_epilogue(epilogue, map_w, map_x, args, stream);
+    if (rc != HX_OK) return rc;
+    HX_CHECK_LAUNCH("hx_gemm_tc");
+    return HX_OK;
+  }
   if (k_splits > total_k_blocks) k_splits = total_k_blocks;
   const int per_split = (total_k_blocks + k_splits - 1) / k_splits;
   k_splits = (total_k_blocks + per_split - 1) / per_split;

@@ -161,6 +161,9 @@ TC_SHAPES = [
     # tokens, features, depth: every token tile (16..256), ragged edges in all three sizes
     (1, 64, 64), (5, 200, 120), (16, 384, 328), (17, 128, 1024), (40, 136, 72),
     (100, 256, 4096), (130, 384, 200), (300, 520, 328), (513, 128, 64),
+    # more tiles than SMs: CTAs of the persistent kernel take three tiles and more, so both
+    # accumulators in tensor memory are used again
+    (1100, 9000, 136),
 ]
 
 
@@ -192,7 +195,7 @@ def test_gemm_on_tensor_cores(tokens, features, depth):
 
 
 @pytest.mark.parametrize("tokens,inter,depth", [(3, 176, 64), (33, 320, 120), (200, 1000, 264),
-                                                 (64, 128, 512)])
+                                                 (64, 128, 512), (1100, 4600, 72)])
 def test_gemm_with_swiglu_epilogue(tokens, inter, depth):
     rng = np.random.default_rng(5)
     x = rounded(rng.normal(size=(tokens, depth)), torch.bfloat16)
