@@ -110,6 +110,8 @@ class CacheManager:
             for entry, need in state_needs.items()}
         self._free_slots: Deque[int] = deque(range(self.max_requests))
         self._requests: Dict[Hashable, RequestCache] = {}
+        # page lists held without a request (published prefixes): per anchor, per group
+        self._anchors: Dict[Hashable, Tuple[int, List[List[int]]]] = {}
 
     # ------------------------------------------------------------------ lookups
 
@@ -300,6 +302,68 @@ class CacheManager:
         record.reserved = tokens
         return slot
 
+    # ------------------------------------------------------------------ anchors
+    #
+    # An anchor keeps the whole pages of a prefix alive after the request that computed them
+    # has gone (src/kv_cache/prefix.cpp holds block references the same way).  It has no
+    # state slot and no block-table row: it is only a holder of pages.
+
+    @property
+    def can_share(self) -> bool:
+        """Whole-page sharing needs every key of the prefix to stay in its page: no group
+        with a window, no per-request state."""
+        return not self.states and all(group.need.window is None for group in self.groups)
+
+    def hold(self, anchor: Hashable, source: Hashable, tokens: int) -> int:
+        """Keep the first ``tokens`` positions (whole pages) of ``source`` under ``anchor``;
+        returns the pages it now holds per group."""
+        if anchor in self._anchors:
+            raise KeyError(f"anchor {anchor!r} exists")
+        if tokens <= 0 or tokens % self.page_size != 0:
+            raise ValueError("a shared prefix must be a positive multiple of the page size")
+        if not self.can_share:
+            raise ValueError("this cache cannot share prefixes (windows or per-request state)")
+        parent = self._requests[source]
+        if tokens > parent.length:
+            raise ValueError("cannot share more than the source has published")
+        count = tokens // self.page_size
+        held = []
+        for index, group in enumerate(self.groups):
+            pages = list(parent.tables[index][:count])
+            group.pool.share(pages)
+            held.append(pages)
+        self._anchors[anchor] = (tokens, held)
+        return count
+
+    def adopt(self, request: Hashable, anchor: Hashable, tokens: Optional[int] = None) -> int:
+        """Admit ``request`` with the first ``tokens`` positions (default: all) of ``anchor``
+        already in its cache; returns its slot."""
+        held_tokens, held = self._anchors[anchor]
+        tokens = held_tokens if tokens is None else tokens
+        if tokens <= 0 or tokens % self.page_size != 0 or tokens > held_tokens:
+            raise ValueError("a request adopts a positive number of whole pages of the anchor")
+        slot = self.admit(request)
+        record = self._requests[request]
+        count = tokens // self.page_size
+        for index, group in enumerate(self.groups):
+            pages = held[index][:count]
+            group.pool.share(pages)
+            record.tables[index] = list(pages)
+            group.host_tables[slot, :count] = pages
+            group.dirty = True
+        record.length = tokens
+        record.reserved = tokens
+        return slot
+
+    def drop(self, anchor: Hashable) -> int:
+        """Forget the anchor; returns the pages that became free."""
+        _, held = self._anchors.pop(anchor)
+        return sum(self._give_back(group, pages) for group, pages in zip(self.groups, held))
+
+    def anchor_pages(self) -> int:
+        """Pages (per group, summed) that anchors hold references to."""
+        return sum(len(pages) for _, held in self._anchors.values() for pages in held)
+
     def _give_back(self, group: CacheGroup, pages: List[int]) -> int:
         if not pages:
             return 0
@@ -342,6 +406,10 @@ class CacheManager:
                 row = group.host_tables[record.slot]
                 assert list(row[:len(table)]) == table, "host block table out of date"
                 assert (row[len(table):] == -1).all(), "stale block table entries"
+            for _, held in self._anchors.values():
+                assert len(held[index]) == len(set(held[index])), "an anchor holds a page twice"
+                for page in held[index]:
+                    holders[page] += 1
             for page in range(group.pool.num_pages):
                 assert holders[page] == group.pool.refcount(page), \
                     f"group {index} page {page}: {holders[page]} holders, " \
@@ -351,6 +419,8 @@ class CacheManager:
         return {
             "requests": len(self._requests),
             "free_slots": len(self._free_slots),
+            "anchors": len(self._anchors),
+            "anchor_pages": self.anchor_pages(),
             "groups": [{
                 "window": group.need.window,
                 "layers": len(group.entries),

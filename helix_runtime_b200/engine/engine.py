@@ -16,6 +16,7 @@ from typing import Dict, List, Optional, Sequence, Union
 import torch
 
 from ..cache.manager import CacheManager
+from ..cache.prefix import PrefixIndex, PrefixMatch
 from ..config.registry import architecture_for, load_config, read_config_json
 from ..models.decoder import DecoderModel
 from ..sampling.sampler import Sampler, uniform_for
@@ -111,6 +112,10 @@ class EngineConfig:
     max_prefill_chunk: Optional[int] = None
     attention_split_keys: int = 256
     poison_free_pages: bool = False           # debugging: fill free pages with NaN
+    prefix_cache_entries: int = 0             # > 0: prompts of one namespace share the pages
+                                              # of their common beginning (this many prefixes kept)
+    prefix_cache_pages: Optional[int] = None  # page references the kept prefixes may hold
+                                              # (default: half the pool)
     cuda_graphs: bool = True                  # replay decode-only steps as CUDA graphs
 
 
@@ -155,6 +160,14 @@ class Engine:
         self.graphs = DecodeGraphs(self.step_function, self.sampler) if config.cuda_graphs else None
         self._cached_at_finish: Dict[int, int] = {}
         self._release_later: List[int] = []
+        self.prefix: Optional[PrefixIndex] = None
+        if config.prefix_cache_entries > 0:
+            if not self.cache.can_share:
+                raise ValueError("prefix sharing needs a cache without windows and without "
+                                 "per-request state")
+            self.prefix = PrefixIndex(self.cache, config.prefix_cache_entries,
+                                      config.prefix_cache_pages)
+        self._matches: Dict[int, PrefixMatch] = {}      # lookups of the iteration being planned
 
     # ------------------------------------------------------------ construction
 
@@ -174,8 +187,11 @@ class Engine:
     # ----------------------------------------------------------------- requests
 
     def submit(self, prompt: Sequence[int], max_new_tokens: int = 32,
-               eos_token: Optional[int] = None, temperature: float = 0.0, seed: int = 0) -> int:
-        """Queue a request; refuse what could never run (src/runtime/cpu_engine.cpp:85-119)."""
+               eos_token: Optional[int] = None, temperature: float = 0.0, seed: int = 0,
+               cache_namespace: Optional[str] = "") -> int:
+        """Queue a request; refuse what could never run (src/runtime/cpu_engine.cpp:85-119).
+        With the prefix index on, requests of the same ``cache_namespace`` share the pages of
+        a common beginning; ``None`` keeps a request out of it."""
         vocab = self.model.vocab_size
         prompt = [int(t) for t in prompt]
         if not prompt:
@@ -198,7 +214,8 @@ class Engine:
                 raise ValueError(f"the request needs {pages} cache pages, the pool has "
                                  f"{group.pool.num_pages}; it could never run")
         return self.scheduler.submit(prompt, max_new_tokens, eos_token, temperature, seed,
-                                     now=time.monotonic())
+                                     now=time.monotonic(),
+                                     namespace=cache_namespace if self.prefix is not None else None)
 
     def cancel(self, request_id: int) -> bool:
         cancelled = self.scheduler.cancel(request_id, now=time.monotonic())
@@ -213,13 +230,40 @@ class Engine:
         self._cached_at_finish[request_id] = self.cache.length(request_id)
         self.cache.release(request_id)
 
+    # ------------------------------------------------------------- prefix index
+
+    def _reusable(self, request: Request) -> int:
+        """Tokens a request about to be admitted finds in the prefix index."""
+        if self.prefix is None or request.namespace is None:
+            return 0
+        if request.id not in self._matches:
+            match = self.prefix.lookup(request.namespace, request.feed)
+            if match is None:
+                return 0
+            self._matches[request.id] = match
+        return self._matches[request.id].tokens
+
+    def _admit(self, request_id: int) -> None:
+        match = self._matches.pop(request_id, None)
+        if match is None:
+            self.cache.admit(request_id)
+        else:
+            self.cache.adopt(request_id, match.anchor, match.tokens)
+
+    def _reclaim(self) -> bool:
+        """Pages ran out and nobody can move: drop the coldest kept prefix."""
+        self._matches.clear()          # an anchor that was looked up may be the one that goes
+        return self.prefix is not None and self.prefix.evict_for_pressure()
+
     # ---------------------------------------------------------------- iteration
 
     def run_iteration(self) -> IterationResult:
         """Schedule one batch, run it as one step, sample, complete, free what retired."""
         result = IterationResult()
-        batch = self.scheduler.schedule_iteration(self.cache, admit=self.cache.admit,
-                                                  release=self.cache.release)
+        self._matches.clear()
+        batch = self.scheduler.schedule_iteration(self.cache, admit=self._admit,
+                                                  release=self.cache.release,
+                                                  reusable=self._reusable, reclaim=self._reclaim)
         if batch is None:
             result.idle = True
             return result
@@ -271,6 +315,16 @@ class Engine:
                 step.fail(entries)
                 raise
             step.finish(entries, new_lengths, ctx)
+            if self.prefix is not None:
+                # a request whose LAST prompt portion has just succeeded leaves its longest
+                # aligned prefix to later requests (src/runtime/cpu_engine.cpp:136-160)
+                for work in batch.work:
+                    request = self.scheduler.request(work.request_id)
+                    prompt_tokens = len(request.prompt)
+                    if (work.kind.value == "prefill" and request.namespace is not None
+                            and work.token_offset < prompt_tokens
+                            <= work.token_offset + work.token_count):
+                        self.prefix.publish(request.namespace, request.id, request.prompt)
             cursor = 0
             for work, entry in zip(batch.work, entries):
                 token = None
@@ -313,11 +367,13 @@ class Engine:
 
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
                  max_new_tokens: int = 32, eos_token: Optional[int] = None,
-                 temperature: float = 0.0, seed: int = 0) -> List[GenerationResult]:
+                 temperature: float = 0.0, seed: int = 0,
+                 cache_namespace: Optional[str] = "") -> List[GenerationResult]:
         """Generate for one prompt or a list of prompts (token ids in, token ids out)."""
         if len(prompts) > 0 and isinstance(prompts[0], int):
             prompts = [prompts]           # a single prompt
-        ids = [self.submit(prompt, max_new_tokens, eos_token, temperature, seed + index)
+        ids = [self.submit(prompt, max_new_tokens, eos_token, temperature, seed + index,
+                           cache_namespace)
                for index, prompt in enumerate(prompts)]
         self.run_until_done()
         results = []
@@ -334,5 +390,8 @@ class Engine:
 
     def stats(self) -> Dict[str, object]:
         return {"scheduler": dict(self.scheduler.stats), "cache": self.cache.stats(),
+                "prefix": dict(self.prefix.stats, entries=len(self.prefix),
+                               page_references=self.prefix.page_references)
+                if self.prefix is not None else None,
                 "steps": self.step_function.steps_run, "tokens": self.step_function.tokens_run,
                 "workspace_bytes": self.step_function.workspace.bytes()}

@@ -74,6 +74,8 @@ class Request:
     first_token_at: Optional[float] = None
     finished_at: Optional[float] = None
     resumed_from: int = 0              # generated tokens that were folded into the prompt
+    namespace: Optional[str] = None    # prefix sharing: only prompts of one namespace share
+    reused_tokens: int = 0             # tokens taken from the prefix index at (re)admission
 
     @property
     def feed(self) -> List[int]:
@@ -169,7 +171,8 @@ class FifoScheduler:
     # ------------------------------------------------------------------ submit
 
     def submit(self, prompt: Sequence[int], max_new_tokens: int, eos_token: Optional[int] = None,
-               temperature: float = 0.0, seed: int = 0, now: float = 0.0) -> int:
+               temperature: float = 0.0, seed: int = 0, now: float = 0.0,
+               namespace: Optional[str] = None) -> int:
         if len(prompt) == 0:
             raise ValueError("a request needs at least one prompt token")
         if max_new_tokens < 0:
@@ -178,7 +181,8 @@ class FifoScheduler:
             raise ValueError("temperature must not be negative")
         request = Request(id=self._next_request, prompt=[int(t) for t in prompt],
                           max_new_tokens=int(max_new_tokens), eos_token=eos_token,
-                          temperature=float(temperature), seed=int(seed), created_at=now)
+                          temperature=float(temperature), seed=int(seed), created_at=now,
+                          namespace=namespace)
         self._next_request += 1
         self.requests[request.id] = request
         self.waiting.append(request.id)
@@ -194,15 +198,27 @@ class FifoScheduler:
 
     def schedule_iteration(self, ledger: PageLedger,
                            admit: Callable[[int], None],
-                           release: Callable[[int], None]) -> Optional[IterationBatch]:
+                           release: Callable[[int], None],
+                           reusable: Optional[Callable[[Request], int]] = None,
+                           reclaim: Optional[Callable[[], bool]] = None
+                           ) -> Optional[IterationBatch]:
         """Plan one iteration.  ``admit(id)`` / ``release(id)`` let the caller give a request
-        its cache slot when it starts and take its pages back when it is preempted."""
+        its cache slot when it starts and take its pages back when it is preempted.
+        ``reusable(request)`` says how many leading tokens admission will find in the cache
+        already (a shared prefix; whole pages), which then count as progress
+        (src/scheduler/fifo_scheduler.cpp:229-239).  ``reclaim()`` is asked for pages when
+        nobody can move, before anybody is preempted (the reference's engine evicts prefix
+        anchors there, src/runtime/cpu_engine.cpp:323-331); True means: plan again."""
         if self.active is not None:
             raise RuntimeError("an iteration is already in flight")
         preempted: List[int] = []
         while True:
-            batch = self._plan(ledger, admit)
-            if batch.work or not self.running:
+            batch = self._plan(ledger, admit, reusable)
+            if batch.work:
+                break
+            if reclaim is not None and (self.running or self.waiting) and reclaim():
+                continue
+            if not self.running:
                 break
             # nobody can move and somebody holds pages: preempt the youngest running request
             victim = self.running.pop()
@@ -228,7 +244,8 @@ class FifoScheduler:
             self.stats[key] += work.token_count
         return batch
 
-    def _plan(self, ledger: PageLedger, admit: Callable[[int], None]) -> IterationBatch:
+    def _plan(self, ledger: PageLedger, admit: Callable[[int], None],
+              reusable: Optional[Callable[[Request], int]] = None) -> IterationBatch:
         batch = IterationBatch(id=self._next_iteration, work=[])
         remaining_tokens = self.config.max_tokens_per_iteration
         available = list(ledger.free_pages())
@@ -237,7 +254,12 @@ class FifoScheduler:
         def plan(request: Request, waiting: bool) -> bool:
             nonlocal remaining_tokens, stop
             prefill = waiting or request.state is RequestState.PREFILL
-            desired = request.remaining_feed
+            start = request.processed
+            if waiting and reusable is not None:
+                start = reusable(request)
+                if start % self.page_size != 0 or not 0 <= start < len(request.feed):
+                    raise ValueError("a reused prefix is whole pages and leaves a token to run")
+            desired = len(request.feed) - start
             assert desired > 0, "an active request always has something to feed"
             if prefill and self.config.max_prefill_chunk is not None:
                 desired = min(desired, self.config.max_prefill_chunk)
@@ -252,6 +274,8 @@ class FifoScheduler:
                 return False
             if waiting:
                 admit(request.id)
+                request.processed = start
+                request.reused_tokens = start
             needed = ledger.pages_to_extend(request.id, request.processed + granted)
             for index, count in enumerate(needed):
                 available[index] -= count

@@ -113,6 +113,48 @@ def test_stop_reasons_and_cached_token_count(folders, plain_models):
     assert result.generated_tokens == [] and result.cached_token_count == len(prompt)
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16")])
+def test_prompts_that_begin_alike_share_pages_and_generate_the_same(name, dtype, folders,
+                                                                    plain_models):
+    """With the prefix index on, later requests adopt the pages of a common beginning and run
+    only the rest of their prompt; what they generate is checked against the plain
+    implementation exactly as without sharing.  The pool is small, so kept prefixes are also
+    dropped under pressure while others are still being shared."""
+    plain = plain_models(name, dtype)
+    vocab = tiny_config(name).vocab_size
+    page = PAGE_SIZE[name]
+    stem = random_tokens(vocab, 3 * page + 3, seed=77)
+    prompts = [stem + random_tokens(vocab, extra, seed=100 + extra) for extra in (2, 9, 1, 20)]
+    prompts.insert(2, stem[:2 * page + 1] + random_tokens(vocab, 4, seed=6))  # shares two pages
+    prompts.append(random_tokens(vocab, 4 * page, seed=5))                    # shares nothing
+    engine = Engine.from_pretrained(folders(name, dtype), dtype=dtype, page_size=page,
+                                    max_running_requests=2, max_tokens_per_iteration=48,
+                                    num_pages=14, poison_free_pages=True,
+                                    prefix_cache_entries=3)
+    results = []
+    for prompt in prompts:        # one after the other, so that each finds what the last left
+        results += engine.generate([prompt], max_new_tokens=6)
+    for prompt, result in zip(prompts, results):
+        check_greedy(plain, prompt, result.generated_tokens, dtype)
+    stats = engine.stats()
+    assert stats["prefix"]["hits"] >= 4
+    assert stats["prefix"]["reused_tokens"] >= 3 * (3 * page) + 2 * page
+    assert [engine.request(i).reused_tokens for i in range(6)] == \
+        [0, 3 * page, 2 * page, 3 * page, 3 * page, 0]
+    # requests that ran together while sharing: same answers
+    together = engine.generate(prompts[:4], max_new_tokens=6)
+    for prompt, result in zip(prompts, together):
+        check_greedy(plain, prompt, result.generated_tokens, dtype)
+    engine.cache.check()
+    # a request may keep out of the index
+    before = engine.stats()["prefix"]["lookups"]
+    engine.generate([prompts[0]], max_new_tokens=2, cache_namespace=None)
+    assert engine.stats()["prefix"]["lookups"] == before
+    engine.prefix.clear()
+    engine.cache.check()
+    assert all(group.pool.pages_in_use == 0 for group in engine.cache.groups)
+
+
 def test_bad_submissions_are_refused(folders):
     engine = Engine.from_pretrained(folders("A", "float32"), dtype="float32", page_size=8,
                                     max_running_requests=2, num_pages=4)
