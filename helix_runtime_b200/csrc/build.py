@@ -27,9 +27,10 @@ SOURCES = (
     "hx_gemm_tc.cu",
     "hx_attention.cu",
     "hx_attention_mma.cu",
+    "hx_attention_tc.cu",
     "hx_sampling.cu",
 )
-HEADERS = ("hx_common.cuh", "hx_mma.cuh", "hx_no_alloc.h")
+HEADERS = ("hx_common.cuh", "hx_mma.cuh", "hx_tcgen05.cuh", "hx_no_alloc.h")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

@@ -1,0 +1,591 @@
+// Paged causal attention for prompt portions on the 5th-generation tensor cores (tcgen05),
+// bfloat16 storage.  The same computation as hx_attention_mma.cu (the reference materialises
+// a [heads, T, T] score tensor for it, src/attention/cuda.cu:31-77), with both products as
+// tcgen05.mma and the scores and partial outputs in tensor memory.
+//
+// One CTA takes 128 consecutive query tokens of one request and one head and walks the
+// request's keys in tiles of 64, anchored at key 0.  Warp roles:
+//   warp 0      one lane asks for the pages of each tile: the keys of a (page, head) are one
+//               contiguous block of the cache and so are its values, so a tile is a handful
+//               of bulk copies (cp.async.bulk counted on an mbarrier) into a ring of stages;
+//   warp 1      one lane issues the products: S = Q K^T into one of two score buffers in
+//               tensor memory (running two tiles ahead of the softmax), then O_tile = P V;
+//   warp 6      rewrites the keys of a landed tile piece-major over all 64 keys (see below);
+//   warps 2..5  softmax: thread r owns query row r.  It reads its row of S from tensor memory,
+//               keeps the running maximum, sum and output row in float32 registers, writes
+//               the probabilities to shared memory as TWO bfloat16 terms (P = hi + lo, so the
+//               softmax stays a float32 quantity as far as the result can tell), and adds
+//               each O_tile to its output row.
+//
+// Operand layouts.  Nothing is swizzled: every operand is made of "core matrices" of 8 rows
+// x 16 bytes (128 contiguous bytes), which is exactly what a page block of the cache is made
+// of ([head_dim / 8][slot][8 elements]: eight consecutive slots of one 16-byte piece).  For
+// O = P V a page block is used as it lies: 16 keys are the K dimension of an MN-major operand
+// (a row of a core matrix is 8 consecutive coordinates of one key, its 8 rows are 8 keys).
+// For S = Q K^T the keys are the N operand (K-major), and one product should cover all 64
+// keys of the tile, which needs one stride from 8 keys to the next across pages: a warp
+// rewrites the tile as [piece][64 keys][16 bytes] (products of one page each measured 4 times
+// slower, and so did asking the copy engine for each piece column by itself).  Q and P are
+// written to shared memory by the CTA itself in the same core-matrix form.
+//
+// A query row's result depends on its own position only (tiles are anchored at key 0, rows do
+// not interact).  Requests with fewer than `min_query_len` tokens are left to
+// hx_paged_attention.  Every wait is bounded; a wait that runs out sets a status bit, and
+// the CTA frees its tensor memory and returns.
+#include "hx_tcgen05.cuh"
+
+namespace {
+
+constexpr int BLOCK_M = 128;   // query rows per CTA (the MMA's M)
+constexpr int BLOCK_N = 64;    // keys per tile
+constexpr int K_STAGES = 2;    // key tiles in shared memory as they land (rewritten at once)
+constexpr int V_STAGES = 4;    // value tiles in shared memory (held until their product is done)
+constexpr int THREADS = 224;
+constexpr int GROUP_STRIDE = 128;             // bytes from one 8-row core matrix to the next row group
+constexpr int CHUNK_STRIDE = BLOCK_M * 16;    // bytes from one 16-byte column of Q or P to the next
+
+struct TcPrefillArgs {
+  const __nv_bfloat16* q;
+  int ldq;
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  const int* request_start;     // [requests + 1] first token of each request in the batch
+  const int* request_context;   // [requests] tokens cached before this step
+  const int* request_table_row;
+  const int* block_tables;
+  int table_stride;
+  __nv_bfloat16* out;
+  int ldo;
+  int requests;
+  int heads;
+  int kv_heads;
+  int page_size;
+  int num_pages;
+  float scale;
+  int min_query_len;
+  int* status;
+};
+
+template <int D>
+struct TcConfig {
+  static constexpr int kQBytes = BLOCK_M * D * 2;
+  static constexpr int kHalfBytes = BLOCK_N * D * 2;          // keys (or values) of a tile
+  static constexpr int kPBytes = BLOCK_M * BLOCK_N * 2;       // one term of the probabilities
+  static constexpr int kSmemBytes =
+      kQBytes + (K_STAGES + V_STAGES + 2) * kHalfBytes + 2 * kPBytes + 1024 + 256;
+  static constexpr int kScoreColumns = BLOCK_N;               // per score buffer (two of them)
+  static constexpr int kOutputColumn = 2 * BLOCK_N;           // O_tile starts here
+  static constexpr int kTmemColumns = 256;                    // 2 * 64 + D <= 256
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+template <int D>
+__global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPrefillArgs a) {
+  using Config = TcConfig<D>;
+  constexpr int kDSteps = D / 16;      // k-steps of Q K^T
+  hx_pdl_trigger();
+
+  // which request and which 128-row tile of it is this CTA?
+  int request = -1, tile_in_request = 0;
+  {
+    int remaining = blockIdx.x;
+    for (int r = 0; r < a.requests; ++r) {
+      const int length = a.request_start[r + 1] - a.request_start[r];
+      if (length < a.min_query_len) continue;
+      const int tiles = (length + BLOCK_M - 1) / BLOCK_M;
+      if (remaining < tiles) {
+        request = r;
+        // the last rows of a request see the most keys: their CTAs are started first, so the
+        // short ones fill the gaps at the end
+        tile_in_request = tiles - 1 - remaining;
+        break;
+      }
+      remaining -= tiles;
+    }
+  }
+  if (request < 0) return;      // before any barrier or allocation: the whole CTA leaves
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* q_tile = smem;
+  uint8_t* k_stages = q_tile + Config::kQBytes;
+  uint8_t* v_stages = k_stages + K_STAGES * Config::kHalfBytes;
+  uint8_t* keys_by_piece = v_stages + V_STAGES * Config::kHalfBytes;      // [2]: see warp 6
+  uint8_t* p_hi = keys_by_piece + 2 * Config::kHalfBytes;
+  uint8_t* p_lo = p_hi + Config::kPBytes;
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(p_lo + Config::kPBytes);
+  uint64_t* k_empty = k_full + K_STAGES;
+  uint64_t* v_full = k_empty + K_STAGES;
+  uint64_t* v_empty = v_full + V_STAGES;
+  uint64_t* s_full = v_empty + V_STAGES;      // [2]
+  uint64_t* p_full = s_full + 2;
+  uint64_t* o_full = p_full + 1;
+  uint64_t* k_ready = o_full + 1;             // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(k_ready + 2);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int kv_head = head / (a.heads / a.kv_heads);
+  const int q_begin = a.request_start[request];
+  const int q_len = a.request_start[request + 1] - q_begin;
+  const int context = a.request_context[request];
+  const int row0 = tile_in_request * BLOCK_M;                 // first query row of the tile
+  const int rows_here = min(BLOCK_M, q_len - row0);
+  const int last_key = context + row0 + rows_here - 1;        // last key any row here sees
+  const int n_tiles = last_key / BLOCK_N + 1;
+  const int page_size = a.page_size;
+  const int pages_per_tile = BLOCK_N / page_size;
+  const uint32_t page_bytes = static_cast<uint32_t>(page_size) * D * 2;
+  const uint32_t piece_stride = static_cast<uint32_t>(page_size) * 16;   // next 16-byte piece of a key
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < K_STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < V_STAGES; ++s) {
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(p_full, 4);       // one arrival per softmax warp
+    mbar_init(o_full, 1);
+    mbar_init(&k_ready[0], 1);
+    mbar_init(&k_ready[1], 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_holder, Config::kTmemColumns);
+  hx_pdl_wait();
+
+  // ---- the query tile, by everybody: [D / 8 pieces][16 row groups][8 rows][16 bytes]
+  for (int index = threadIdx.x; index < BLOCK_M * (D / 8); index += THREADS) {
+    const int row = index / (D / 8);
+    const int piece = index - row * (D / 8);
+    uint4 value = make_uint4(0u, 0u, 0u, 0u);
+    if (row < rows_here)
+      value = *reinterpret_cast<const uint4*>(a.q + static_cast<size_t>(q_begin + row0 + row) * a.ldq +
+                                              static_cast<size_t>(head) * D + piece * 8);
+    *reinterpret_cast<uint4*>(q_tile + piece * CHUNK_STRIDE + (row >> 3) * GROUP_STRIDE +
+                              (row & 7) * 16) = value;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ page requests
+    if (lane == 0) {
+      const int* table = a.block_tables +
+                         static_cast<size_t>(a.request_table_row[request]) * a.table_stride;
+      const int last_page = last_key / page_size;
+      auto pages_of = [&](int tile, int (&pages)[4]) {
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const int index = tile * pages_per_tile + p;
+          pages[p] = (p < pages_per_tile && index <= last_page) ? table[index] : -2;   // -2: none
+        }
+      };
+      int pages[4], next_pages[4];
+      pages_of(0, pages);
+      for (int tile = 0; tile < n_tiles && !*failed; ++tile) {
+        if (tile + 1 < n_tiles) pages_of(tile + 1, next_pages);      // in flight during the waits
+        const int ks = tile % K_STAGES, vs = tile % V_STAGES;
+        if (!mbar_wait(&k_empty[ks], (static_cast<uint32_t>(tile / K_STAGES) & 1u) ^ 1u) ||
+            !mbar_wait(&v_empty[vs], (static_cast<uint32_t>(tile / V_STAGES) & 1u) ^ 1u)) {
+          atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
+          *failed = 1;
+          break;
+        }
+        uint32_t expected = 0;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          if (pages[p] >= a.num_pages || pages[p] == -1) {
+            atomicOr(a.status, HX_FLAG_BAD_PAGE);
+            pages[p] = -2;
+          }
+          if (pages[p] >= 0) expected += page_bytes;
+        }
+        mbar_expect_tx(&k_full[ks], expected);
+        mbar_expect_tx(&v_full[vs], expected);
+        const uint32_t k_base = smem_u32(k_stages + ks * Config::kHalfBytes);
+        const uint32_t v_base = smem_u32(v_stages + vs * Config::kHalfBytes);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          if (pages[p] >= 0) {
+            const size_t block = (static_cast<size_t>(pages[p]) * a.kv_heads + kv_head) * page_bytes;
+            bulk_copy(k_base + p * page_bytes, reinterpret_cast<const uint8_t*>(a.k_cache) + block,
+                      page_bytes, &k_full[ks]);
+            bulk_copy(v_base + p * page_bytes, reinterpret_cast<const uint8_t*>(a.v_cache) + block,
+                      page_bytes, &v_full[vs]);
+          }
+        }
+#pragma unroll
+        for (int p = 0; p < 4; ++p) pages[p] = next_pages[p];
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------ keys, piece by piece
+    // The score product wants all 64 keys of the tile at one stride, but every page block
+    // holds its own keys piece-major: this warp rewrites a landed tile as
+    // [piece][64 keys][16 bytes] into one of two buffers, 32 pieces at a time.
+    bool ok = true;
+    for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
+      if (lane == 0) {
+        ok = mbar_wait(&k_full[tile % K_STAGES], static_cast<uint32_t>(tile / K_STAGES) & 1u);
+        // the product that read this buffer two tiles ago is done when its scores are
+        if (ok && tile >= 2)
+          ok = mbar_wait(&s_full[tile & 1], static_cast<uint32_t>((tile - 2) >> 1) & 1u);
+        if (!ok) {
+          atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
+          *failed = 1;
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      const uint8_t* source = k_stages + (tile % K_STAGES) * Config::kHalfBytes;
+      uint8_t* target = keys_by_piece + (tile & 1) * Config::kHalfBytes;
+#pragma unroll 4
+      for (int index = lane; index < BLOCK_N * (D / 8); index += 32) {
+        const int piece = index / BLOCK_N;
+        const int key = index - piece * BLOCK_N;
+        const uint4 value = *reinterpret_cast<const uint4*>(
+            source + (key / page_size) * page_bytes + piece * piece_stride + (key % page_size) * 16);
+        *reinterpret_cast<uint4*>(target + index * 16) = value;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&k_ready[tile & 1]);
+        mbar_arrive(&k_empty[tile % K_STAGES]);      // the landed copy may be overwritten
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- products
+    if (lane == 0) {
+      constexpr uint32_t idesc_scores = make_idesc(BLOCK_M, BLOCK_N);
+      constexpr uint32_t idesc_output = make_idesc_b_mn_major(BLOCK_M, D);
+      // Descriptors differ from product to product only in their start address (the low 14
+      // bits, in units of 16 bytes): build one of each kind and add offsets.
+      const uint64_t desc_q0 = make_smem_desc_plain(smem_u32(q_tile), CHUNK_STRIDE, GROUP_STRIDE);
+      const uint64_t desc_k0 =
+          make_smem_desc_plain(smem_u32(keys_by_piece), BLOCK_N * 16, GROUP_STRIDE);
+      constexpr uint32_t kKeyBufferStep = Config::kHalfBytes >> 4;
+      // values: MN-major, the next 8 keys are 128 bytes on, the next 8 coordinates one piece on
+      const uint64_t desc_v0 = make_smem_desc_plain(smem_u32(v_stages), GROUP_STRIDE, piece_stride);
+      const uint64_t desc_hi0 = make_smem_desc_plain(smem_u32(p_hi), CHUNK_STRIDE, GROUP_STRIDE);
+      const uint64_t desc_lo0 = make_smem_desc_plain(smem_u32(p_lo), CHUNK_STRIDE, GROUP_STRIDE);
+      constexpr uint32_t kStageStep = Config::kHalfBytes >> 4;
+      constexpr uint32_t kChunkPairStep = (2 * CHUNK_STRIDE) >> 4;      // 16 coordinates of Q or P on
+      constexpr uint32_t kKeyPiecePairStep = (2 * BLOCK_N * 16) >> 4;   // 16 coordinates of the keys on
+      bool ok = true;
+      // S[tile & 1] = Q K_tile^T: one product of 64 keys per 16 coordinates
+      auto scores = [&](int tile) {
+        if (!mbar_wait(&k_ready[tile & 1], static_cast<uint32_t>(tile >> 1) & 1u)) {
+          atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
+          *failed = 1;
+          ok = false;
+          return;
+        }
+        tc_fence_after();
+        const uint64_t desc_k = desc_k0 + (tile & 1) * kKeyBufferStep;
+        const uint32_t target = tmem_base + (tile & 1) * Config::kScoreColumns;
+#pragma unroll
+        for (int k = 0; k < kDSteps; ++k)
+          umma_bf16(target, desc_q0 + k * kChunkPairStep, desc_k + k * kKeyPiecePairStep,
+                    idesc_scores, k > 0 ? 1u : 0u);
+        umma_commit(&s_full[tile & 1]);
+      };
+      scores(0);
+      if (ok && n_tiles > 1) scores(1);
+      // where the 16 keys of each product of P V start inside a stage's value half
+      uint32_t value_step[BLOCK_N / 16];
+#pragma unroll
+      for (int g = 0; g < BLOCK_N / 16; ++g) {
+        const int key = g * 16;
+        value_step[g] = ((key / page_size) * page_bytes + (key % page_size) * 16) >> 4;
+      }
+      for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
+        // the probabilities of this tile are in shared memory (and the softmax warps have
+        // read its scores and the previous partial output)
+        if (!mbar_wait(p_full, static_cast<uint32_t>(tile) & 1u)) {
+          atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
+          *failed = 1;
+          break;
+        }
+        tc_fence_after();
+        const int s = tile % V_STAGES;
+        if (!mbar_wait(&v_full[s], static_cast<uint32_t>(tile / V_STAGES) & 1u)) {
+          atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
+          *failed = 1;
+          break;
+        }
+        const uint64_t desc_v = desc_v0 + s * kStageStep;
+        const uint32_t target = tmem_base + Config::kOutputColumn;
+        // O_tile = P V_tile: 16 keys per product, the hi and the lo term of P against them
+#pragma unroll
+        for (int g = 0; g < BLOCK_N / 16; ++g) {
+          umma_bf16(target, desc_hi0 + g * kChunkPairStep, desc_v + value_step[g], idesc_output,
+                    g > 0 ? 1u : 0u);
+          umma_bf16(target, desc_lo0 + g * kChunkPairStep, desc_v + value_step[g], idesc_output,
+                    1u);
+        }
+        umma_commit(&v_empty[s]);       // the stage may be refilled
+        umma_commit(o_full);            // O_tile is complete, P may be overwritten
+        if (tile + 2 < n_tiles) scores(tile + 2);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax
+    const int quarter = warp & 3;      // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int q_position = context + row0 + row;      // the last key this row sees
+    const uint32_t p_offset = (row >> 3) * GROUP_STRIDE + (row & 7) * 16;
+    float o_acc[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) o_acc[d] = 0.0f;
+    float row_max = -INFINITY;      // in units of log2(e), like the scores
+    float row_sum = 0.0f;
+    const float scale_log2 = a.scale * 1.4426950408889634f;
+    bool ok = true;
+
+    auto wait_for = [&](uint64_t* bar, uint32_t parity) {
+      bool done = true;
+      if (lane == 0) done = mbar_wait(bar, parity);
+      done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
+      if (!done && lane == 0) {
+        atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
+        *failed = 1;
+      }
+      return done;
+    };
+    // O_tile of the previous tile (same maximum as o_acc) is added to the output row
+    auto add_partial_output = [&]() {
+#pragma unroll
+      for (int d0 = 0; d0 < D; d0 += 32) {
+        uint32_t r0[16], r1[16];
+        tmem_load16_issue(lane_base + Config::kOutputColumn + d0, r0);
+        tmem_load16_issue(lane_base + Config::kOutputColumn + d0 + 16, r1);
+        tmem_load_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          o_acc[d0 + i] += __uint_as_float(r0[i]);
+          o_acc[d0 + 16 + i] += __uint_as_float(r1[i]);
+        }
+      }
+    };
+
+    for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
+      ok = wait_for(&s_full[tile & 1], static_cast<uint32_t>(tile >> 1) & 1u);
+      if (!ok) break;
+      tc_fence_after();
+      // ---- this row's scores of the tile, in units of log2(e) so that exp is one ex2
+      float p[BLOCK_N];
+      {
+        uint32_t r[4][16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          tmem_load16_issue(lane_base + (tile & 1) * Config::kScoreColumns + c * 16, r[c]);
+        tmem_load_wait();
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) p[c * 16 + i] = __uint_as_float(r[c][i]) * scale_log2;
+      }
+      const int key0 = tile * BLOCK_N;
+      if (key0 + BLOCK_N - 1 > q_position) {
+#pragma unroll
+        for (int i = 0; i < BLOCK_N; ++i)
+          if (key0 + i > q_position) p[i] = -INFINITY;
+      }
+      float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < BLOCK_N; i += 4)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) part_max[u] = fmaxf(part_max[u], p[i + u]);
+      const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
+      // key 0 is visible to every row, so the maximum is finite from the first tile on
+      const float new_max = fmaxf(row_max, tile_max);
+      const float correction = row_max == -INFINITY ? 0.0f : fast_exp2(row_max - new_max);
+      row_max = new_max;
+      float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int i = 0; i < BLOCK_N; i += 4)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          p[i + u] = fast_exp2(p[i + u] - new_max);
+          part_sum[u] += p[i + u];
+        }
+      row_sum = row_sum * correction + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
+
+      // ---- the previous tile's partial output, then the new maximum's correction
+      if (tile > 0) {
+        ok = wait_for(o_full, static_cast<uint32_t>(tile - 1) & 1u);
+        if (!ok) break;
+        tc_fence_after();
+        add_partial_output();
+      }
+      if (__any_sync(0xffffffffu, correction != 1.0f)) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) o_acc[d] *= correction;
+      }
+
+      // ---- P = hi + lo into shared memory (the product that read the old P is done: its
+      // commit is what o_full waited for).  hi is p cut to its upper 16 bits (a bfloat16
+      // exactly), lo is p - hi (exact in float32) cut the same way: together 16 bits of p.
+#pragma unroll
+      for (int c = 0; c < BLOCK_N / 8; ++c) {
+        uint4 hi, lo;
+        uint32_t* hi_words = reinterpret_cast<uint32_t*>(&hi);
+        uint32_t* lo_words = reinterpret_cast<uint32_t*>(&lo);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t x0 = __float_as_uint(p[c * 8 + 2 * i]);
+          const uint32_t x1 = __float_as_uint(p[c * 8 + 2 * i + 1]);
+          const float rest0 = p[c * 8 + 2 * i] - __uint_as_float(x0 & 0xffff0000u);
+          const float rest1 = p[c * 8 + 2 * i + 1] - __uint_as_float(x1 & 0xffff0000u);
+          hi_words[i] = __byte_perm(x0, x1, 0x7632);
+          lo_words[i] = __byte_perm(__float_as_uint(rest0), __float_as_uint(rest1), 0x7632);
+        }
+        *reinterpret_cast<uint4*>(p_hi + c * CHUNK_STRIDE + p_offset) = hi;
+        *reinterpret_cast<uint4*>(p_lo + c * CHUNK_STRIDE + p_offset) = lo;
+      }
+
+      // ---- value rows behind the last key hold whatever the pages (or an earlier tile)
+      // left there; a NaN would survive a zero probability, so they are cleared
+      const int first_stale = last_key + 1 - key0;
+      if (first_stale < BLOCK_N) {
+        ok = wait_for(&v_full[tile % V_STAGES], static_cast<uint32_t>(tile / V_STAGES) & 1u);
+        if (!ok) break;
+        uint8_t* v_half = v_stages + (tile % V_STAGES) * Config::kHalfBytes;
+        for (int index = threadIdx.x - 64; index < BLOCK_N * (D / 8); index += 128) {
+          const int key = index / (D / 8);
+          const int piece = index - key * (D / 8);
+          if (key >= first_stale)
+            *reinterpret_cast<uint4*>(v_half + (key / page_size) * page_bytes +
+                                      (piece * page_size + key % page_size) * 16) =
+                make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+
+    if (ok && !*failed) {
+      ok = wait_for(o_full, static_cast<uint32_t>(n_tiles - 1) & 1u);
+      if (ok) {
+        tc_fence_after();
+        add_partial_output();
+        if (row < rows_here) {
+          const float inverse = 1.0f / row_sum;
+          __nv_bfloat16* out = a.out + static_cast<size_t>(q_begin + row0 + row) * a.ldo +
+                               static_cast<size_t>(head) * D;
+#pragma unroll
+          for (int d = 0; d < D; d += 8) {
+            uint4 packed;
+            __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              pairs[i] = __floats2bfloat162_rn(o_acc[d + 2 * i] * inverse,
+                                               o_acc[d + 2 * i + 1] * inverse);
+            *reinterpret_cast<uint4*>(out + d) = packed;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Config::kTmemColumns);
+  }
+}
+
+template <int D>
+int launch(const TcPrefillArgs& a, int tiles, cudaStream_t stream) {
+  using Config = TcConfig<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(prefill_attention_tc_kernel<D>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Config::kSmemBytes) != cudaSuccess) {
+      cudaGetLastError();
+      hx_set_error("hx_prefill_attention_tc: cannot reserve %d bytes of shared memory",
+                   Config::kSmemBytes);
+      return HX_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  hx_launch(prefill_attention_tc_kernel<D>, dim3(tiles, a.heads), THREADS, Config::kSmemBytes,
+            stream, a);
+  return HX_OK;
+}
+
+}  // namespace
+
+// 1 when the tcgen05 kernel takes this head size and page size: a page is the N operand of a
+// product, so it has at least 16 keys.
+HX_API int hx_prefill_attention_tc_supports(int head_dim, int page_size) {
+  return (head_dim == 64 || head_dim == 128) &&
+         (page_size == 16 || page_size == 32 || page_size == 64);
+}
+
+// The arguments of hx_prefill_attention; tile_bound bounds the number of 128-token query tiles
+// (a larger bound only launches CTAs that leave at once).
+HX_API int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache,
+                                   const void* v_cache, const int* request_start,
+                                   const int* request_context, const int* request_table_row,
+                                   const int* block_tables, int table_stride, void* out, int ldo,
+                                   int requests, int tile_bound, int heads, int kv_heads,
+                                   int head_dim, int page_size, int num_pages, float scale,
+                                   int min_query_len, int* status, cudaStream_t stream) {
+  HX_REQUIRE(hx_prefill_attention_tc_supports(head_dim, page_size),
+             "hx_prefill_attention_tc: head_dim %d with pages of %d is not supported (head sizes "
+             "64 and 128, pages of 16, 32 or 64)", head_dim, page_size);
+  HX_REQUIRE(requests >= 0 && tile_bound >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+             "hx_prefill_attention_tc: bad sizes");
+  HX_REQUIRE(heads <= 65535, "hx_prefill_attention_tc: too many heads");
+  HX_REQUIRE(num_pages > 0 && table_stride > 0, "hx_prefill_attention_tc: bad cache geometry");
+  HX_REQUIRE(status != nullptr, "hx_prefill_attention_tc: status word missing");
+  HX_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+             "hx_prefill_attention_tc: operands must be 16-byte aligned, row strides multiples of 8");
+  if (requests == 0 || tile_bound == 0) return HX_OK;
+  TcPrefillArgs a{static_cast<const __nv_bfloat16*>(q), ldq,
+                  static_cast<const __nv_bfloat16*>(k_cache),
+                  static_cast<const __nv_bfloat16*>(v_cache), request_start, request_context,
+                  request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(out),
+                  ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status};
+  const int rc = head_dim == 128 ? launch<128>(a, tile_bound, stream)
+                                 : launch<64>(a, tile_bound, stream);
+  if (rc != HX_OK) return rc;
+  HX_CHECK_LAUNCH("hx_prefill_attention_tc");
+  return HX_OK;
+}

@@ -67,6 +67,10 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_prefill_attention.restype = _c_int
     library.hx_prefill_attention_supports.argtypes = [_c_int, _c_int]
     library.hx_prefill_attention_supports.restype = _c_int
+    library.hx_prefill_attention_tc.argtypes = library.hx_prefill_attention.argtypes
+    library.hx_prefill_attention_tc.restype = _c_int
+    library.hx_prefill_attention_tc_supports.argtypes = [_c_int, _c_int]
+    library.hx_prefill_attention_tc_supports.restype = _c_int
     library.hx_paged_attention_scratch_floats.restype = ctypes.c_longlong
     library.hx_paged_attention_scratch_floats.argtypes = [_c_int] * 4
     library.hx_argmax.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]
@@ -249,18 +253,28 @@ def prefill_attention_supports(head_dim: int, page_size: int) -> bool:
     return bool(lib().hx_prefill_attention_supports(head_dim, page_size))
 
 
+def prefill_attention_tc_supports(head_dim: int, page_size: int) -> bool:
+    return bool(lib().hx_prefill_attention_tc_supports(head_dim, page_size))
+
+
 def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       request_start: torch.Tensor, request_context: torch.Tensor,
                       request_table_row: torch.Tensor, block_tables: torch.Tensor,
                       out: torch.Tensor, requests: int, tile_bound: int, heads: int,
                       kv_heads: int, head_dim: int, page_size: int, num_pages: int, scale: float,
-                      min_query_len: int, status: torch.Tensor) -> None:
+                      min_query_len: int, status: torch.Tensor,
+                      tensor_memory: Optional[bool] = None) -> None:
     """Tensor-core attention (bfloat16) of every request that brings at least
-    ``min_query_len`` tokens; ``tile_bound`` bounds the number of 64-token query tiles."""
+    ``min_query_len`` tokens; ``tile_bound`` bounds the number of 64-token query tiles.
+    ``tensor_memory``: take the tcgen05 kernel (scores and partial outputs in tensor memory;
+    pages of at least 16 keys) or the ``mma.sync`` kernel; default: tcgen05 where it applies."""
     _need(q, torch.bfloat16, "q")
     _need(k_cache, torch.bfloat16, "k_cache")
     _need(out, torch.bfloat16, "out")
-    _check(lib().hx_prefill_attention(
+    if tensor_memory is None:
+        tensor_memory = prefill_attention_tc_supports(head_dim, page_size)
+    entry = lib().hx_prefill_attention_tc if tensor_memory else lib().hx_prefill_attention
+    _check(entry(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), request_start.data_ptr(),
         request_context.data_ptr(), request_table_row.data_ptr(), block_tables.data_ptr(),
         block_tables.stride(0), out.data_ptr(), out.stride(0), requests, tile_bound, heads,

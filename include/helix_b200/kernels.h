@@ -118,6 +118,15 @@ int hx_prefill_attention(const void* q, int ldq, const void* k_cache, const void
                          int head_dim, int page_size, int num_pages, float scale, int min_query_len,
                          int* status, cudaStream_t stream);
 
+/* the same on tcgen05, scores and partial outputs in tensor memory (pages of 16, 32, 64) */
+int hx_prefill_attention_tc_supports(int head_dim, int page_size);
+int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                            const int* request_start, const int* request_context,
+                            const int* request_table_row, const int* block_tables,
+                            int table_stride, void* out, int ldo, int requests, int tile_bound,
+                            int heads, int kv_heads, int head_dim, int page_size, int num_pages,
+                            float scale, int min_query_len, int* status, cudaStream_t stream);
+
 /* ---- sampling --------------------------------------------------------------------------- */
 /* lowest id among the maxima; -1 and HX_STATUS_NONFINITE for a row with a non-finite logit */
 int hx_argmax(const float* logits, int ld, int rows, int vocab, int* tokens, int* status,

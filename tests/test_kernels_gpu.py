@@ -322,7 +322,8 @@ def test_rope_reads_and_clears_a_split_k_accumulator():
 # ------------------------------------------------------------------- attention
 
 def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, new_tokens,
-                   window, split_keys, dominant=None, tensor_core_min=0, lost_page=None):
+                   window, split_keys, dominant=None, tensor_core_min=0, lost_page=None,
+                   tensor_memory=None):
     """Build a paged cache holding ``contexts[r] + new_tokens[r]`` keys per request in shuffled
     pages and the queries of the new tokens; return kernel output and plain reference.
     ``lost_page=(request, index)`` points that entry of the block table outside the pool: the
@@ -387,7 +388,7 @@ def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, n
                               dev(contexts, torch.int32), dev(slots, torch.int32),
                               dev(tables, torch.int32), out, requests, tokens // 64 + requests,
                               heads, kv_heads, head_dim, page_size, num_pages, scale,
-                              tensor_core_min, status)
+                              tensor_core_min, status, tensor_memory=tensor_memory)
     if not tensor_core_min or min(new_tokens) < tensor_core_min:
         ops.paged_attention(dev(q, dtype), dev(to_cache_layout(k_cache, dtype), dtype),
                             dev(to_cache_layout(v_cache, dtype), dtype),
@@ -495,9 +496,13 @@ def test_one_far_key_stands_out(dtype, key_position):
     assert_close(out, wanted, "dominant key's value", atol=2e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("tensor_memory", [False, True])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [
-    (4, 4, 128, 16), (6, 2, 64, 8), (3, 1, 128, 32), (2, 2, 64, 64)])
-def test_tensor_core_attention_for_prompt_portions(heads, kv_heads, head_dim, page_size):
+    (4, 4, 128, 16), (6, 2, 64, 8), (3, 1, 128, 32), (2, 2, 64, 64), (2, 1, 64, 16)])
+def test_tensor_core_attention_for_prompt_portions(heads, kv_heads, head_dim, page_size,
+                                                   tensor_memory):
+    if tensor_memory and not ops.prefill_attention_tc_supports(head_dim, page_size):
+        pytest.skip("the tcgen05 kernel needs pages of at least 16 keys")
     rng = np.random.default_rng(12)
     # whole prompts (one longer than two tiles, one a single row short of a tile), continued
     # portions that start inside a page and inside a key tile, and two decode tokens that the
@@ -506,16 +511,18 @@ def test_tensor_core_attention_for_prompt_portions(heads, kv_heads, head_dim, pa
     new_tokens = [150, 19, 63, 64, 1, 1]
     out, expected, *_ = attention_case(rng, torch.bfloat16, heads, kv_heads, head_dim, page_size,
                                        contexts, new_tokens, window=None, split_keys=64,
-                                       tensor_core_min=16)
+                                       tensor_core_min=16, tensor_memory=tensor_memory)
     assert_close(out, expected, "tensor-core attention", atol=2e-2, rtol=8e-3)
 
 
+@pytest.mark.parametrize("tensor_memory", [False, True])
 @pytest.mark.parametrize("key_position", [0, 63, 64, 200, 299])
-def test_tensor_core_attention_sees_one_far_key(key_position):
+def test_tensor_core_attention_sees_one_far_key(key_position, tensor_memory):
     rng = np.random.default_rng(13)
     out, expected, values, *_ = attention_case(rng, torch.bfloat16, 4, 4, 128, 16, [270], [30],
                                                window=None, split_keys=64,
-                                               dominant={0: key_position}, tensor_core_min=16)
+                                               dominant={0: key_position}, tensor_core_min=16,
+                                               tensor_memory=tensor_memory)
     assert_close(out, expected, "attention", atol=2e-2, rtol=8e-3)
     wanted = values[0][:, key_position].reshape(1, -1)
     assert_close(out[-1:], wanted, "dominant key's value", atol=2e-2, rtol=1e-2)
