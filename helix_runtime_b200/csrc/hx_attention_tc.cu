@@ -250,6 +250,10 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     // holds its own keys piece-major: this warp rewrites a landed tile as
     // [piece][64 keys][16 bytes] into one of two buffers, 32 pieces at a time.
     bool ok = true;
+    // where keys `lane` and `lane + 32` of a tile sit inside the landed page blocks
+    const uint32_t source_low = (lane / page_size) * page_bytes + (lane % page_size) * 16;
+    const uint32_t source_high =
+        ((lane + 32) / page_size) * page_bytes + ((lane + 32) % page_size) * 16;
     for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
       if (lane == 0) {
         ok = mbar_wait(&k_full[tile % K_STAGES], static_cast<uint32_t>(tile / K_STAGES) & 1u);
@@ -263,15 +267,24 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
-      const uint8_t* source = k_stages + (tile % K_STAGES) * Config::kHalfBytes;
-      uint8_t* target = keys_by_piece + (tile & 1) * Config::kHalfBytes;
-#pragma unroll 4
-      for (int index = lane; index < BLOCK_N * (D / 8); index += 32) {
-        const int piece = index / BLOCK_N;
-        const int key = index - piece * BLOCK_N;
-        const uint4 value = *reinterpret_cast<const uint4*>(
-            source + (key / page_size) * page_bytes + piece * piece_stride + (key % page_size) * 16);
-        *reinterpret_cast<uint4*>(target + index * 16) = value;
+      // piece c of keys lane and lane + 32: the two reads are a page apart at most, the two
+      // writes 512 bytes; from piece to piece both move by a constant
+      const uint32_t source = smem_u32(k_stages + (tile % K_STAGES) * Config::kHalfBytes);
+      const uint32_t target = smem_u32(keys_by_piece + (tile & 1) * Config::kHalfBytes) + lane * 16;
+#pragma unroll
+      for (int piece = 0; piece < D / 8; ++piece) {
+        uint4 low, high;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(low.x), "=r"(low.y), "=r"(low.z), "=r"(low.w)
+                     : "r"(source + source_low + piece * piece_stride));
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(high.x), "=r"(high.y), "=r"(high.z), "=r"(high.w)
+                     : "r"(source + source_high + piece * piece_stride));
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(target + piece * (BLOCK_N * 16)),
+                     "r"(low.x), "r"(low.y), "r"(low.z), "r"(low.w) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(
+                         target + piece * (BLOCK_N * 16) + 512),
+                     "r"(high.x), "r"(high.y), "r"(high.z), "r"(high.w) : "memory");
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
