@@ -41,6 +41,20 @@ constexpr int THREADS = 192;
 
 enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
 
+// Where the [128 rows x 64 k] box of the weights that begins at row `row`, k-block `kb`, is.
+// Row-major weights: a box is 128 row segments of 128 bytes, one per row of the matrix.  Tiled
+// weights (k_tiles > 0) store every such box as 16 contiguous kilobytes, box after box along
+// k, then along the rows: a product that streams its weights once then reads DRAM in long
+// runs instead of 128-byte pieces (measured: 4 % less time for the decode products).
+__device__ __forceinline__ void load_weight_box(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                                int row, int kb, int k_tiles) {
+  if (k_tiles > 0) {
+    tma_load_2d(dst, map, bar, 0, ((row / BM) * k_tiles + kb) * BM);
+  } else {
+    tma_load_2d(dst, map, bar, kb * BK, row);
+  }
+}
+
 // One epilogue warp's share of a finished tile: its 32 features (tensor-memory lanes) for all
 // BN token columns, 16 columns at a time.  With SwiGLU the up accumulator sits BN columns on.
 template <int BN, int EPI>
@@ -108,6 +122,7 @@ struct GemmArgs {
   int depth;        // K
   int up_row_offset;  // SwiGLU: row of the first up-projection feature in the weight matrix
   int k_blocks_per_split;
+  int k_tiles;        // > 0: the weights are stored as tiles, this many along k
   int* status;
 };
 
@@ -165,10 +180,10 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
         for (int i = 0; i < eager; ++i) {
           uint8_t* stage = smem + i * Config::kStageBytes;
           mbar_expect_tx(&full_bar[i], Config::kStageBytes);
-          const int k = (kb_begin + i) * BK;
-          tma_load_2d(stage, &map_w, &full_bar[i], k, feature0);
+          load_weight_box(stage, &map_w, &full_bar[i], feature0, kb_begin + i, args.k_tiles);
           if (DUAL)
-            tma_load_2d(stage + BM * BK * 2, &map_w, &full_bar[i], k, args.up_row_offset + feature0);
+            load_weight_box(stage + BM * BK * 2, &map_w, &full_bar[i],
+                            args.up_row_offset + feature0, kb_begin + i, args.k_tiles);
         }
         hx_pdl_wait();
         for (int i = 0; i < eager; ++i) {
@@ -186,9 +201,10 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
           uint8_t* stage = smem + s * Config::kStageBytes;
           mbar_expect_tx(&full_bar[s], Config::kStageBytes);
           const int k = (kb_begin + i) * BK;
-          tma_load_2d(stage, &map_w, &full_bar[s], k, feature0);
+          load_weight_box(stage, &map_w, &full_bar[s], feature0, kb_begin + i, args.k_tiles);
           if (DUAL)
-            tma_load_2d(stage + BM * BK * 2, &map_w, &full_bar[s], k, args.up_row_offset + feature0);
+            load_weight_box(stage + BM * BK * 2, &map_w, &full_bar[s],
+                            args.up_row_offset + feature0, kb_begin + i, args.k_tiles);
           tma_load_2d(stage + Config::kWeightBytes, &map_x, &full_bar[s], k, token0);
         }
       }
@@ -293,6 +309,7 @@ struct PersistentArgs {
   int features;
   int depth;
   int up_row_offset;
+  int k_tiles;                // > 0: the weights are stored as tiles, this many along k
   int token_tiles;            // tiles along the tokens
   int units;                  // token_tiles * feature tiles
   int k_blocks;               // per tile
@@ -464,8 +481,9 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
           mbar_expect_tx(&full_bar[s], Config::kStageBytes);
           const int k = kb * BK;
           tma_load_2d(stage, &map_x, &full_bar[s], k, token0);
-          tma_load_2d(stage + Config::kBytesA, &map_w, &full_bar[s], k, feature0);
-          tma_load_2d(stage + Config::kBytesA + BM * BK * 2, &map_w, &full_bar[s], k, second_half);
+          load_weight_box(stage + Config::kBytesA, &map_w, &full_bar[s], feature0, kb, args.k_tiles);
+          load_weight_box(stage + Config::kBytesA + BM * BK * 2, &map_w, &full_bar[s], second_half,
+                          kb, args.k_tiles);
         }
       }
     }
@@ -751,12 +769,17 @@ HX_API int hx_gemm_tc_supports(int tokens, int features, int depth, int ldx, int
 // epilogue 0/1/2: `features` = weight_rows outputs per token.  epilogue 3 (SwiGLU): w is the
 // fused [gate; up] matrix, `features` = intermediate size, gate rows [0, features), up rows
 // [up_row_offset, up_row_offset + features).  k_splits > 1 only with epilogue 2.
+// weight_tiles != 0: w holds the matrix as [ceil(weight_rows / 128)][ceil(depth / 64)] tiles of
+// [128][64] elements, zero padded (ldw is ignored; up_row_offset is then a multiple of 128).
 // x_capacity_rows: rows of the buffer behind x (the tensor map is made for the buffer, so it
 // can be reused for every batch size).
 HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
                       int weight_rows, void* out, int ldo, int tokens, int features, int depth,
-                      int epilogue, int up_row_offset, int k_splits, int* status,
+                      int epilogue, int up_row_offset, int k_splits, int weight_tiles, int* status,
                       cudaStream_t stream) {
+  if (weight_tiles) ldw = 8;      // not a stride of anything here
+  HX_REQUIRE(!weight_tiles || epilogue != EPI_SWIGLU || up_row_offset % BM == 0,
+             "hx_gemm_tc: with tiled weights the up rows must start on a multiple of %d", BM);
   HX_REQUIRE(hx_gemm_tc_supports(tokens, features, depth, ldx, ldw),
              "hx_gemm_tc: shape tokens=%d features=%d depth=%d ldx=%d ldw=%d is not supported "
              "(depth and strides must be multiples of 8)", tokens, features, depth, ldx, ldw);
@@ -777,15 +800,19 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
   // prompt portions: the persistent kernel, whose tiles have 128 tokens on the M side
   const bool persistent = bn >= 128 && k_splits == 1;
   CUtensorMap map_w, map_x;
-  int rc = get_tensor_map(w, weight_rows, depth, ldw, BM, &map_w);
+  const int total_k_blocks = (depth + BK - 1) / BK;
+  const int k_tiles = weight_tiles ? total_k_blocks : 0;
+  int rc = weight_tiles
+               ? get_tensor_map(w, static_cast<uint64_t>((weight_rows + BM - 1) / BM) * k_tiles * BM,
+                                BK, BK, BM, &map_w)
+               : get_tensor_map(w, weight_rows, depth, ldw, BM, &map_w);
   if (rc != HX_OK) return rc;
   rc = get_tensor_map(x, x_capacity_rows, depth, ldx, persistent ? BM : bn, &map_x);
   if (rc != HX_OK) return rc;
 
-  const int total_k_blocks = (depth + BK - 1) / BK;
   if (persistent) {
-    PersistentArgs args{out, ldo, tokens, features, depth, up_row_offset, 0, 0, total_k_blocks,
-                        status};
+    PersistentArgs args{out, ldo, tokens, features, depth, up_row_offset, k_tiles, 0, 0,
+                        total_k_blocks, status};
     rc = launch_persistent_epilogue(epilogue, map_w, map_x, args, stream);
     if (rc != HX_OK) return rc;
     HX_CHECK_LAUNCH("hx_gemm_tc");
@@ -794,7 +821,7 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
   if (k_splits > total_k_blocks) k_splits = total_k_blocks;
   const int per_split = (total_k_blocks + k_splits - 1) / k_splits;
   k_splits = (total_k_blocks + per_split - 1) / per_split;
-  GemmArgs args{out, ldo, tokens, features, depth, up_row_offset, per_split, status};
+  GemmArgs args{out, ldo, tokens, features, depth, up_row_offset, per_split, k_tiles, status};
   const dim3 grid((tokens + bn - 1) / bn, (features + BM - 1) / BM, k_splits);
   HX_REQUIRE(grid.y <= 65535, "hx_gemm_tc: too many features (%d)", features);
 

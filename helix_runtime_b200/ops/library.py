@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -54,7 +54,8 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_gemm_simt.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int,
                                      _c_int, _c_int, _c_int, _c_ptr]
     library.hx_gemm_tc.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_int,
-                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
+                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                                   _c_ptr]
     library.hx_gemm_tc_supports.argtypes = [_c_int] * 5
     library.hx_gemm_tc_token_tile.argtypes = [_c_int]
     library.hx_paged_attention.argtypes = [
@@ -206,15 +207,46 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tokens: int, 
                               _stream()))
 
 
+WEIGHT_TILE_ROWS, WEIGHT_TILE_DEPTH = 128, 64
+
+
+def tile_weights(matrix: torch.Tensor) -> torch.Tensor:
+    """``[rows, depth]`` -> ``[ceil(rows / 128), ceil(depth / 64), 128, 64]``, zero padded:
+    every [128 x 64] box the tensor-core product loads becomes 16 contiguous kilobytes."""
+    rows, depth = matrix.shape
+    row_tiles = -(-rows // WEIGHT_TILE_ROWS)
+    k_tiles = -(-depth // WEIGHT_TILE_DEPTH)
+    padded = torch.zeros((row_tiles * WEIGHT_TILE_ROWS, k_tiles * WEIGHT_TILE_DEPTH),
+                         dtype=matrix.dtype, device=matrix.device)
+    padded[:rows, :depth] = matrix
+    return padded.view(row_tiles, WEIGHT_TILE_ROWS, k_tiles, WEIGHT_TILE_DEPTH) \
+        .permute(0, 2, 1, 3).contiguous()
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tokens: int, features: int,
-            epilogue: int, status: torch.Tensor, up_row_offset: int = 0, k_splits: int = 1) -> None:
-    """out[:tokens, :features] (op)= x[:tokens] @ w.T on the tensor cores (bfloat16)."""
+            epilogue: int, status: torch.Tensor, up_row_offset: int = 0, k_splits: int = 1,
+            weight_shape: Optional[Tuple[int, int]] = None) -> None:
+    """out[:tokens, :features] (op)= x[:tokens] @ w.T on the tensor cores (bfloat16).  ``w``
+    is the matrix ``[rows, depth]`` or its tiles from :func:`tile_weights` (then
+    ``weight_shape`` gives rows and depth)."""
     _need(x, torch.bfloat16, "x")
     _need(w, torch.bfloat16, "w")
-    depth = w.shape[1]
-    _check(lib().hx_gemm_tc(x.data_ptr(), x.stride(0), x.shape[0], w.data_ptr(), w.stride(0),
-                            w.shape[0], out.data_ptr(), out.stride(0), tokens, features, depth,
-                            epilogue, up_row_offset, k_splits, status.data_ptr(), _stream()))
+    tiled = w.dim() == 4
+    if tiled:
+        if weight_shape is None:
+            raise ValueError("tiled weights need weight_shape=(rows, depth)")
+        rows, depth = weight_shape
+        if tuple(w.shape) != (-(-rows // WEIGHT_TILE_ROWS), -(-depth // WEIGHT_TILE_DEPTH),
+                              WEIGHT_TILE_ROWS, WEIGHT_TILE_DEPTH) or not w.is_contiguous():
+            raise ValueError(f"tiles of shape {tuple(w.shape)} do not hold a {rows} x {depth} matrix")
+        ldw = 0
+    else:
+        rows, depth = w.shape
+        ldw = w.stride(0)
+    _check(lib().hx_gemm_tc(x.data_ptr(), x.stride(0), x.shape[0], w.data_ptr(), ldw, rows,
+                            out.data_ptr(), out.stride(0), tokens, features, depth, epilogue,
+                            up_row_offset, k_splits, 1 if tiled else 0, status.data_ptr(),
+                            _stream()))
 
 
 def attention_scratch_floats(tokens: int, heads: int, head_dim: int, max_splits: int) -> int:

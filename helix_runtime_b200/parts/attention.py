@@ -25,7 +25,7 @@ from ..config.spec import PartSpec
 from ..ops import library as ops
 from ..weights.loader import TensorRequest
 from .base import LayerCache, Mixer, StepContext, build_part, register_part
-from .linear import (STREAMING_MAX_TOKENS, is_weight_stream, project,
+from .linear import (STREAMING_MAX_TOKENS, Weight, is_weight_stream, project,
                      project_into_accumulator)
 
 
@@ -61,8 +61,8 @@ class PagedAttention(Mixer):
         self.q_size = self.heads * self.head_dim
         self.kv_size = self.kv_heads * self.head_dim
         self.qkv_size = self.q_size + 2 * self.kv_size
-        self.w_qkv: Optional[torch.Tensor] = None
-        self.w_o: Optional[torch.Tensor] = None
+        self.w_qkv: Optional[Weight] = None
+        self.w_o: Optional[Weight] = None
 
     def kv_need(self) -> Optional[KvNeed]:
         return KvNeed(self.kv_heads, self.head_dim, self.window)
@@ -88,12 +88,12 @@ class PagedAttention(Mixer):
             else:
                 raise ValueError(f"no row permutation from {self.checkpoint_pairing!r} to "
                                  f"{self.position.pairing!r}")
-        self.w_qkv = torch.cat([q, k, v], dim=0).to(device=device, dtype=dtype).contiguous()
-        self.w_o = tensors[self.names["o"]].to(device=device, dtype=dtype).contiguous()
+        self.w_qkv = Weight(torch.cat([q, k, v], dim=0).to(device=device, dtype=dtype).contiguous())
+        self.w_o = Weight(tensors[self.names["o"]].to(device=device, dtype=dtype).contiguous())
         self.position.bind(tensors, dtype, device)
 
     def weight_bytes(self) -> int:
-        return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()
+        return self.w_qkv.nbytes() + self.w_o.nbytes()
 
     def split_keys_for(self, tokens: int, longest: int, limit: int) -> int:
         """Keys per split.  One warp walks one (token, head, split); a step with few tokens

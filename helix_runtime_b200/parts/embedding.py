@@ -15,7 +15,7 @@ from ..config.spec import PartSpec
 from ..ops import library as ops
 from ..weights.loader import TensorRequest
 from .base import Part, StepContext, register_part
-from .linear import project
+from .linear import Weight, project
 
 
 class TokenEmbedding(Part):
@@ -41,17 +41,17 @@ class LmHead(Part):
         self.vocab_size = int(spec["vocab_size"])
         self.name = spec.tensors["weight"]
         self.fallback = spec.tensors.get("tied_to") if spec.get("tied", False) else None
-        self.weight: Optional[torch.Tensor] = None
+        self.weight: Optional[Weight] = None
 
     def tensor_requests(self) -> List[TensorRequest]:
         return [TensorRequest(self.name, (self.vocab_size, self.hidden_size),
                               fallback=self.fallback)]
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
-        self.weight = tensors[self.name].to(device=device, dtype=dtype).contiguous()
+        self.weight = Weight(tensors[self.name].to(device=device, dtype=dtype).contiguous())
 
     def weight_bytes(self) -> int:
-        return self.weight.numel() * self.weight.element_size()
+        return self.weight.nbytes()
 
     def forward(self, ctx: StepContext, x: torch.Tensor, logits: torch.Tensor, rows: int) -> None:
         project(x, self.weight, logits, rows, ops.EPI_STORE_F32, ctx.status)

@@ -15,7 +15,7 @@ from ..config.spec import PartSpec
 from ..ops import library as ops
 from ..weights.loader import TensorRequest
 from .base import FeedForward, StepContext, register_part
-from .linear import project, project_swiglu
+from .linear import Weight, project, project_swiglu
 
 
 class GatedMlp(FeedForward):
@@ -26,8 +26,8 @@ class GatedMlp(FeedForward):
         if activation != "silu":
             raise ValueError(f"activation {activation!r} has no kernel; only 'silu'")
         self.names = dict(spec.tensors)
-        self.w_gate_up: Optional[torch.Tensor] = None
-        self.w_down: Optional[torch.Tensor] = None
+        self.w_gate_up: Optional[Weight] = None
+        self.w_down: Optional[Weight] = None
 
     def tensor_requests(self) -> List[TensorRequest]:
         h, i = self.hidden_size, self.intermediate
@@ -35,12 +35,14 @@ class GatedMlp(FeedForward):
                 TensorRequest(self.names["down"], (h, i))]
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
-        self.w_gate_up = torch.cat([tensors[self.names["gate"]], tensors[self.names["up"]]],
-                                   dim=0).to(device=device, dtype=dtype).contiguous()
-        self.w_down = tensors[self.names["down"]].to(device=device, dtype=dtype).contiguous()
+        fused = torch.cat([tensors[self.names["gate"]], tensors[self.names["up"]]],
+                          dim=0).to(device=device, dtype=dtype).contiguous()
+        # tiles of 128 rows: the up rows begin on one only when the intermediate size allows
+        self.w_gate_up = Weight(fused, tile=self.intermediate % ops.WEIGHT_TILE_ROWS == 0)
+        self.w_down = Weight(tensors[self.names["down"]].to(device=device, dtype=dtype).contiguous())
 
     def weight_bytes(self) -> int:
-        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+        return self.w_gate_up.nbytes() + self.w_down.nbytes()
 
     def forward(self, ctx: StepContext, x: torch.Tensor, residual: torch.Tensor) -> None:
         n = ctx.n_tokens

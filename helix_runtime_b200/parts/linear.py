@@ -15,6 +15,8 @@ product's own store would have, and clears again.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from ..ops import library as ops
@@ -25,12 +27,59 @@ WORK_UNITS = 4 * SM_COUNT      # units a weight stream is cut into (two CTAs sha
 MIN_K_BLOCKS = 8               # 64-wide reduction blocks per unit, at least
 
 
-def uses_tensor_cores(x: torch.Tensor, w: torch.Tensor, tokens: int) -> bool:
-    return (x.dtype == torch.bfloat16 and tokens > 0 and
-            ops.gemm_tc_supports(tokens, w.shape[0], w.shape[1], x.stride(0), w.stride(0)))
+class Weight:
+    """A matrix ``[out, in]`` held the way its product kernel reads it best.
+
+    bfloat16 matrices whose depth the tensor-core kernel takes are stored as tiles (every
+    [128 x 64] box the kernel loads is 16 contiguous kilobytes, so a product that streams its
+    weights once reads DRAM in long runs); ``tile=False`` keeps such a matrix row-major (the
+    fused gate/up matrix needs that when the up rows do not start on a tile).  Everything else
+    (float32, depths that are no multiple of 8) stays row-major for the CUDA-core kernel."""
+
+    def __init__(self, matrix: torch.Tensor, tile: bool = True) -> None:
+        if matrix.dim() != 2:
+            raise ValueError("a weight is a matrix")
+        self.rows, self.depth = int(matrix.shape[0]), int(matrix.shape[1])
+        self.dtype = matrix.dtype
+        self.tensor_cores = (matrix.dtype == torch.bfloat16 and matrix.is_cuda and
+                             ops.gemm_tc_supports(1, self.rows, self.depth, self.depth, self.depth))
+        self.tiles: Optional[torch.Tensor] = None
+        self.matrix: Optional[torch.Tensor] = None
+        if self.tensor_cores and tile:
+            self.tiles = ops.tile_weights(matrix)
+        else:
+            self.matrix = matrix.contiguous()
+
+    @property
+    def shape(self):
+        return (self.rows, self.depth)
+
+    def nbytes(self) -> int:
+        held = self.tiles if self.tiles is not None else self.matrix
+        return held.numel() * held.element_size()
 
 
-def is_weight_stream(x: torch.Tensor, w: torch.Tensor, tokens: int) -> bool:
+def uses_tensor_cores(x: torch.Tensor, w: Weight, tokens: int) -> bool:
+    return (w.tensor_cores and x.dtype == torch.bfloat16 and tokens > 0 and
+            x.stride(0) % 8 == 0)
+
+
+def _gemm_tc(x, w: Weight, out, tokens, features, epilogue, status, **options) -> None:
+    if w.tiles is not None:
+        ops.gemm_tc(x, w.tiles, out, tokens, features, epilogue, status, weight_shape=w.shape,
+                    **options)
+    else:
+        ops.gemm_tc(x, w.matrix, out, tokens, features, epilogue, status, **options)
+
+
+def _gemm_simt(x, w: Weight, out, tokens, epilogue) -> None:
+    if w.matrix is None:
+        raise RuntimeError("this product needs the CUDA-core kernel, but the weight is held as "
+                           "tiles for the tensor cores")
+    ops.gemm_simt(x, w.matrix, out, tokens, epilogue)
+
+
+def is_weight_stream(x: torch.Tensor, w: Weight, tokens: int) -> bool:
     return tokens <= STREAMING_MAX_TOKENS and uses_tensor_cores(x, w, tokens)
 
 
@@ -44,28 +93,28 @@ def split_k_for(tokens: int, features: int, depth: int) -> int:
     return max(1, min(splits, k_blocks // MIN_K_BLOCKS))
 
 
-def project(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tokens: int, epilogue: int,
+def project(x: torch.Tensor, w: Weight, out: torch.Tensor, tokens: int, epilogue: int,
             status: torch.Tensor) -> None:
     """``out[:tokens] (op)= x[:tokens] @ w.T``; epilogue is one of ops.EPI_STORE,
     ops.EPI_STORE_F32, ops.EPI_ADD_F32."""
     if tokens == 0:
         return
     if uses_tensor_cores(x, w, tokens):
-        splits = split_k_for(tokens, w.shape[0], w.shape[1]) if epilogue == ops.EPI_ADD_F32 else 1
-        ops.gemm_tc(x, w, out, tokens, w.shape[0], epilogue, status, k_splits=splits)
+        splits = split_k_for(tokens, w.rows, w.depth) if epilogue == ops.EPI_ADD_F32 else 1
+        _gemm_tc(x, w, out, tokens, w.rows, epilogue, status, k_splits=splits)
     else:
-        ops.gemm_simt(x, w, out, tokens, epilogue)
+        _gemm_simt(x, w, out, tokens, epilogue)
 
 
-def project_into_accumulator(x: torch.Tensor, w: torch.Tensor, accumulator: torch.Tensor,
+def project_into_accumulator(x: torch.Tensor, w: Weight, accumulator: torch.Tensor,
                              tokens: int, status: torch.Tensor) -> None:
     """``accumulator[:tokens] += x[:tokens] @ w.T`` as a split-K weight stream (float32; the
     accumulator is clear on entry and its reader clears it again)."""
-    splits = split_k_for(tokens, w.shape[0], w.shape[1])
-    ops.gemm_tc(x, w, accumulator, tokens, w.shape[0], ops.EPI_ADD_F32, status, k_splits=splits)
+    splits = split_k_for(tokens, w.rows, w.depth)
+    _gemm_tc(x, w, accumulator, tokens, w.rows, ops.EPI_ADD_F32, status, k_splits=splits)
 
 
-def project_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, intermediate: int, act: torch.Tensor,
+def project_swiglu(x: torch.Tensor, w_gate_up: Weight, intermediate: int, act: torch.Tensor,
                    workspace, capacity: int, tokens: int, status: torch.Tensor) -> None:
     """``act[:tokens] = silu(x @ gate.T) * (x @ up.T)`` with ``w_gate_up = [gate; up]``.
 
@@ -80,9 +129,9 @@ def project_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, intermediate: int, 
         project_into_accumulator(x, w_gate_up, accumulator, tokens, status)
         ops.swiglu(accumulator[:tokens], act[:tokens], zero_input=True)
     elif uses_tensor_cores(x, w_gate_up, tokens):
-        ops.gemm_tc(x, w_gate_up, act, tokens, intermediate, ops.EPI_SWIGLU, status,
-                    up_row_offset=intermediate)
+        _gemm_tc(x, w_gate_up, act, tokens, intermediate, ops.EPI_SWIGLU, status,
+                 up_row_offset=intermediate)
     else:
         scratch = workspace.get("mlp.gate_up", (capacity, 2 * intermediate), torch.float32)
-        ops.gemm_simt(x, w_gate_up, scratch, tokens, ops.EPI_STORE_F32)
+        _gemm_simt(x, w_gate_up, scratch, tokens, ops.EPI_STORE_F32)
         ops.swiglu(scratch[:tokens], act[:tokens])

@@ -83,12 +83,15 @@ int hx_advance_decode(int* token_ids, int* positions, const int* sampled, int co
 /* CUDA cores, float32 accumulate in a fixed order; both dtypes; the true 32-bit path */
 int hx_gemm_simt(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int dtype,
                  int tokens, int features, int depth, int epilogue, cudaStream_t stream);
-/* tcgen05 tensor cores, bfloat16 operands, float32 accumulate in tensor memory */
+/* tcgen05 tensor cores, bfloat16 operands, float32 accumulate in tensor memory.
+ * weight_tiles != 0: w holds the matrix as [ceil(rows / 128)][ceil(depth / 64)] tiles of
+ * [128][64] elements, zero padded, each tile 16 contiguous kilobytes (ldw is ignored). */
 int hx_gemm_tc_supports(int tokens, int features, int depth, int ldx, int ldw);
 int hx_gemm_tc_token_tile(int tokens);
 int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
                int weight_rows, void* out, int ldo, int tokens, int features, int depth,
-               int epilogue, int up_row_offset, int k_splits, int* status, cudaStream_t stream);
+               int epilogue, int up_row_offset, int k_splits, int weight_tiles, int* status,
+               cudaStream_t stream);
 
 /* ---- attention over the paged cache ----------------------------------------------------- */
 int hx_cache_chunk_elements(int dtype, int head_dim);

@@ -167,35 +167,48 @@ TC_SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("tiled", [False, True])
 @pytest.mark.parametrize("tokens,features,depth", TC_SHAPES)
-def test_gemm_on_tensor_cores(tokens, features, depth):
+def test_gemm_on_tensor_cores(tokens, features, depth, tiled):
+    """``tiled``: the weights are handed over as [128 x 64] tiles (how the engine stores the
+    matrices of its tensor-core products), zero padded in both directions."""
     rng = np.random.default_rng(4)
     x = rounded(rng.normal(size=(tokens, depth)), torch.bfloat16)
     w = rounded(rng.normal(size=(features, depth)) * 0.1, torch.bfloat16)
     expected = product_reference(x, w)
     status = status_word()
     xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    if tiled:
+        tiles = ops.tile_weights(wd)
+        assert tiles.shape == (-(-features // 128), -(-depth // 64), 128, 64)
+        row_major = ops.gemm_tc
+
+        def gemm_tc(x_, w_, *args, **kwargs):
+            return row_major(x_, tiles, *args, weight_shape=(features, depth), **kwargs)
+    else:
+        gemm_tc = ops.gemm_tc
     assert ops.gemm_tc_supports(tokens, features, depth, depth, depth)
     tight = dict(atol=1e-4 * math.sqrt(depth / 64), rtol=2e-5)
 
     out32 = torch.full((tokens, features), float("nan"), dtype=torch.float32, device=DEVICE)
-    ops.gemm_tc(xd, wd, out32, tokens, features, ops.EPI_STORE_F32, status)
+    gemm_tc(xd, wd, out32, tokens, features, ops.EPI_STORE_F32, status)
     assert_close(host(out32), expected, "store f32", **tight)
 
     out16 = torch.full((tokens, features), float("nan"), dtype=torch.bfloat16, device=DEVICE)
-    ops.gemm_tc(xd, wd, out16, tokens, features, ops.EPI_STORE, status)
+    gemm_tc(xd, wd, out16, tokens, features, ops.EPI_STORE, status)
     assert_close(host(out16), expected, "store bf16", atol=2e-2, rtol=8e-3)
 
     base = rng.normal(size=(tokens, features)).astype(np.float32)
     for splits in (1, 3):
         acc = dev(base)
-        ops.gemm_tc(xd, wd, acc, tokens, features, ops.EPI_ADD_F32, status, k_splits=splits)
+        gemm_tc(xd, wd, acc, tokens, features, ops.EPI_ADD_F32, status, k_splits=splits)
         assert_close(host(acc), base + expected, f"add f32 with {splits} k-splits", **tight)
     assert int(status.item()) == 0
 
 
 @pytest.mark.parametrize("tokens,inter,depth", [(3, 176, 64), (33, 320, 120), (200, 1000, 264),
-                                                 (64, 128, 512), (1100, 4600, 72)])
+                                                 (64, 128, 512), (1100, 4600, 72),
+                                                 (300, 1024, 200), (20, 256, 72)])
 def test_gemm_with_swiglu_epilogue(tokens, inter, depth):
     rng = np.random.default_rng(5)
     x = rounded(rng.normal(size=(tokens, depth)), torch.bfloat16)
@@ -208,6 +221,17 @@ def test_gemm_with_swiglu_epilogue(tokens, inter, depth):
     ops.gemm_tc(dev(x, torch.bfloat16), dev(w, torch.bfloat16), act, tokens, inter,
                 ops.EPI_SWIGLU, status, up_row_offset=inter)
     assert_close(host(act), expected, "swiglu epilogue", atol=2e-2, rtol=8e-3)
+    if inter % 128 == 0:       # up rows begin on a tile: the same from tiled weights
+        act.fill_(float("nan"))
+        ops.gemm_tc(dev(x, torch.bfloat16), ops.tile_weights(dev(w, torch.bfloat16)), act, tokens,
+                    inter, ops.EPI_SWIGLU, status, up_row_offset=inter,
+                    weight_shape=(2 * inter, depth))
+        assert_close(host(act), expected, "swiglu epilogue, tiled weights", atol=2e-2, rtol=8e-3)
+    else:
+        with pytest.raises(ops.KernelError, match="multiple of 128"):
+            ops.gemm_tc(dev(x, torch.bfloat16), ops.tile_weights(dev(w, torch.bfloat16)), act,
+                        tokens, inter, ops.EPI_SWIGLU, status, up_row_offset=inter,
+                        weight_shape=(2 * inter, depth))
     assert int(status.item()) == 0
 
 

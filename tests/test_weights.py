@@ -131,7 +131,7 @@ def test_tied_head_falls_back_to_the_embedding(tmp_path, model_root):
     (tied / "config.json").write_text(json.dumps(config.to_dict()))
     write_safetensors(str(tied / "model.safetensors"), tensors)
     model = load_model(str(tied), "float32", "cpu")
-    assert torch.equal(model.lm_head.weight, model.embedding.table)
+    assert torch.equal(model.lm_head.weight.matrix, model.embedding.table)
     untied = tmp_path / "untied"
     untied.mkdir()
     (untied / "config.json").write_text(json.dumps(tiny_config("A").to_dict()))
