@@ -167,7 +167,7 @@ def test_rotary_row_permutation_matches_the_plain_conversion(model_root):
     folder = make_folder(model_root, "B", storage_dtype="float32")
     model = load_model(folder, "float32", "cpu")
     plain = plain_llama.PlainModel(folder)
-    fused = model.blocks[1].mixer.w_qkv.numpy()
+    fused = model.blocks[1].mixer.w_qkv.matrix.numpy()
     np.testing.assert_array_equal(fused[:120], plain.weights["layer.1.query"].T)
     np.testing.assert_array_equal(fused[120:240], plain.weights["layer.1.key"].T)
     np.testing.assert_array_equal(fused[240:], plain.weights["layer.1.value"].T)
