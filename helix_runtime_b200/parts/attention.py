@@ -74,13 +74,15 @@ class PagedAttention(Mixer):
             TensorRequest(self.names["k"], (self.kv_size, h)),
             TensorRequest(self.names["v"], (self.kv_size, h)),
             TensorRequest(self.names["o"], (h, self.q_size)),
+            *self.position.tensor_requests(),
         ]
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
         q = tensors[self.names["q"]]
         k = tensors[self.names["k"]]
         v = tensors[self.names["v"]]
-        if self.checkpoint_pairing != self.position.pairing:
+        if (self.checkpoint_pairing is not None and self.position.pairing is not None
+                and self.checkpoint_pairing != self.position.pairing):
             if self.checkpoint_pairing == "half_split" and self.position.pairing == "adjacent":
                 rotary = self.position.rotary_dim
                 q = q[rotary_row_permutation(self.heads, self.head_dim, rotary).to(q.device)]

@@ -144,7 +144,19 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    pass
+    """Owned by a mixer, which calls :meth:`apply` on the projected rows of a step."""
+
+    # How the encoding pairs coordinates, if it pairs them at all ("adjacent", "half_split"):
+    # a mixer whose checkpoint rows are laid out for another pairing permutes them at load.
+    pairing: Optional[str] = None
+
+    def apply(self, ctx: "StepContext", cache: "LayerCache", qkv: torch.Tensor, heads: int,
+              kv_heads: int, accum: Optional[torch.Tensor] = None) -> None:
+        """Encode queries and keys of ``qkv[:ctx.n_tokens]`` (rows ``[q heads | k heads |
+        v heads]``) in place and store keys and values into the entry's pages when
+        ``cache.owns``.  With ``accum`` the projection arrives in that float32 accumulator
+        instead of ``qkv`` and the accumulator must be left cleared."""
+        raise NotImplementedError
 
 
 class Mixer(Part):
