@@ -21,10 +21,17 @@ F32_TOL = dict(atol=2e-5, rtol=1e-4)
 # sharpened attention and the final norm carry into the logits.  For scale: rounding to
 # bfloat16 itself moves the logits of these models by up to 2e-2.
 BF16_TOL = dict(atol=5e-3, rtol=5e-3)
+# The wider model C has larger logits (spread 0.32) and more terms per sum, and rounding to
+# bfloat16 itself moves its logits more: measured with the plain implementation (float32
+# against rounded, 150 and 300 tokens) the largest change is 3.6e-3 for A, 6.6e-3 for B and
+# 1.14e-2 for C.  Its absolute tolerance is 0.8 of that change, as for B.
+BF16_ATOL_BY_MODEL = {"C": 9e-3}
 
 
-def tolerance(dtype: str) -> dict:
-    return F32_TOL if dtype == "float32" else BF16_TOL
+def tolerance(dtype: str, name: str = "") -> dict:
+    if dtype == "float32":
+        return F32_TOL
+    return dict(BF16_TOL, atol=BF16_ATOL_BY_MODEL.get(name, BF16_TOL["atol"]))
 
 
 class Harness:

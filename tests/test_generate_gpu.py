@@ -50,7 +50,8 @@ def check_sampled(plain, prompt, generated, temperature, seed, dtype):
 
 
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"),
-                                        ("A", "bfloat16"), ("B", "bfloat16")])
+                                        ("A", "bfloat16"), ("B", "bfloat16"),
+                                        ("C", "bfloat16")])
 def test_greedy_generation(name, dtype, folders, plain_models):
     plain = plain_models(name, dtype)
     vocab = tiny_config(name).vocab_size

@@ -22,7 +22,7 @@ from tiny_configs import tiny_config
 pytestmark = pytest.mark.gpu
 
 TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
-LENGTHS = {"A": (33, 60, 97), "B": (40, 100, 160)}
+LENGTHS = {"A": (33, 60, 97), "B": (40, 100, 160), "C": (50, 130, 260)}
 
 
 def requests_for(name):
@@ -49,7 +49,7 @@ def run_trace(folder, dtype, steps, out_dir, max_tokens):
             process.kill()
 
 
-def check(folder, plain, dtype, steps, tmp_path, what):
+def check(folder, plain, dtype, steps, tmp_path, what, name=""):
     out_dir = str(tmp_path / what.replace(" ", "_"))
     run_trace(folder, dtype, steps, out_dir, traces.live_token_need(steps, 64))
     vocab = plain.config["vocab_size"]
@@ -63,31 +63,34 @@ def check(folder, plain, dtype, steps, tmp_path, what):
             continue
         data = np.fromfile(path, dtype="<f4").reshape(len(rows), vocab)
         want = []
-        for name, position in rows:
-            if name not in expected:
-                expected[name] = plain.logits(what_tokens[name])
-            want.append(expected[name][position])
-        assert_close(data, np.stack(want), f"{what}, step {step['step']}", **tolerance(dtype))
+        for request, position in rows:
+            if request not in expected:
+                expected[request] = plain.logits(what_tokens[request])
+            want.append(expected[request][position])
+        assert_close(data, np.stack(want), f"{what}, step {step['step']}",
+                     **tolerance(dtype, name))
 
 
 what_tokens = {}
 
 
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"),
-                                        ("A", "bfloat16"), ("B", "bfloat16")])
+                                        ("A", "bfloat16"), ("B", "bfloat16"),
+                                        ("C", "bfloat16")])
 def test_replay_every_way_of_cutting(name, dtype, folders, plain_models, tmp_path):
     folder = folders(name, dtype)
     plain = plain_models(name, dtype)
     requests = requests_for(name)
     what_tokens.clear()
     what_tokens.update(requests)
-    check(folder, plain, dtype, traces.whole(requests), tmp_path, "whole")
-    check(folder, plain, dtype, traces.tail_decoded(requests, 32), tmp_path, "tail decoded")
-    check(folder, plain, dtype, traces.chunked(requests), tmp_path, "portions")
+    check(folder, plain, dtype, traces.whole(requests), tmp_path, "whole", name)
+    check(folder, plain, dtype, traces.tail_decoded(requests, 32), tmp_path, "tail decoded", name)
+    check(folder, plain, dtype, traces.chunked(requests), tmp_path, "portions", name)
     doubled = dict(requests)
     doubled.update({f"again_{key}": value for key, value in requests.items()})
     what_tokens.update(doubled)
-    check(folder, plain, dtype, traces.mixed(doubled, max_live=4, seed=3), tmp_path, "mixed")
+    check(folder, plain, dtype, traces.mixed(doubled, max_live=4, seed=3), tmp_path, "mixed",
+          name)
 
 
 def test_steps_that_want_nothing_write_no_file_and_requests_may_pause(folders, plain_models, tmp_path):
