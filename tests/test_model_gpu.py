@@ -155,3 +155,69 @@ def test_wanting_nothing_returns_nothing_and_still_fills_the_cache(folders, plai
     out = harness.run([("q", tokens[19:], [0])])
     assert_close(out, expected[19:], "after a silent prompt", **tolerance("float32"))
     harness.end("q")
+
+
+def test_llama_7b_layer_sizes_bfloat16_against_the_float32_path():
+    """Two layers with the layer sizes of the benchmark model (hidden 4096, 32 heads of 128,
+    intermediate 11008, vocabulary 32000): the bfloat16 engine (tcgen05 products on tiled
+    weights, tcgen05 prompt attention, streaming decode attention, split-K weight streams)
+    against the engine's own float32 path on the same (rounded) weights: CUDA-core kernels, no
+    kernel in common.  A prompt in two portions, then token by token.  The plain
+    implementation is too slow at this size; the float32 path is what the other tests hold
+    against it.
+
+    This is a detector of gross errors, not of rounding: a wrong tile, page, head or split
+    changes the logits of the rows it touches by about their spread (1.3 here).  What
+    bfloat16 storage of the activations does to them is far smaller but not tiny: about a
+    hundredth of the spread (0.017 root mean square, 0.08 at most among 800,000 values), the
+    same for every row, prompt or decoded.  The bounds are twice that."""
+    import torch
+
+    from helix_runtime_b200 import LlamaConfig, random_model
+    from helix_runtime_b200.cache.manager import CacheManager
+    from helix_runtime_b200.engine.step import StepEntry, StepFunction
+
+    config = LlamaConfig(vocab_size=32000, hidden_size=4096, intermediate_size=11008,
+                         num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=32,
+                         head_dim=128, max_position_embeddings=1024, rms_norm_eps=1e-5,
+                         rope_theta=10000.0)
+    tokens = random_tokens(32000, 400, seed=77)
+    results = {}
+    for dtype in ("float32", "bfloat16"):
+        model = random_model(config, 0, dtype, torch.device("cuda:0"))
+        if dtype == "float32":
+            # the same weights as the bfloat16 model holds: rounded, then kept in 32 bits
+            matrices = [model.embedding.table, model.lm_head.weight.matrix]
+            for block in model.blocks:
+                matrices += [block.mixer.w_qkv.matrix, block.mixer.w_o.matrix,
+                             block.feed_forward.w_gate_up.matrix, block.feed_forward.w_down.matrix]
+            for matrix in matrices:
+                matrix.copy_(matrix.to(torch.bfloat16).to(torch.float32))
+        kv, state = model.cache_needs()
+        cache = CacheManager(kv, state, 16, 64, 2, 1024, model.dtype, torch.device("cuda:0"),
+                             poison=True)
+        step = StepFunction(model, cache, max_tokens=512, max_requests=2)
+        cache.admit("r")
+        rows = []
+        rows.append(step.run([StepEntry("r", tokens[:300], [0, 150, 299])]).float().cpu().numpy().copy())
+        rows.append(step.run([StepEntry("r", tokens[300:380], [0, 79])]).float().cpu().numpy().copy())
+        for position in range(380, 400):
+            rows.append(step.run([StepEntry("r", [tokens[position]], [0])]).float().cpu().numpy().copy())
+        results[dtype] = np.concatenate(rows)
+        cache.release("r")
+        cache.check()
+        del model, cache, step
+        torch.cuda.empty_cache()
+    exact, fast = results["float32"], results["bfloat16"]
+    assert np.isfinite(fast).all()
+    spread = float(exact.std())
+    assert 0.3 < spread < 3.0, spread
+    difference = np.abs(exact - fast)
+    per_row = np.sqrt((difference ** 2).mean(axis=-1))
+    assert (per_row < 0.025 * spread).all(), \
+        f"root mean square difference per row {np.round(per_row, 4).tolist()} (spread {spread})"
+    assert difference.max() < 0.12 * spread, f"largest difference {difference.max()}"
+    # and the two agree on which token is best where the best is clear
+    top2 = np.sort(exact, axis=-1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 0.1
+    assert (np.argmax(exact, axis=-1)[clear] == np.argmax(fast, axis=-1)[clear]).all()
