@@ -24,6 +24,7 @@ import json
 import os
 import subprocess
 import sys
+import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -166,6 +167,9 @@ def main() -> int:
                         help="run one eager step of this kind between cudaProfilerStart/Stop "
                              "(for ncu --profile-from-start off) and print nothing else")
     parser.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    parser.add_argument("--log-dir", default=None,
+                        help="where the clock samples of the timed region are kept "
+                             "(default: a temporary folder)")
     options = parser.parse_args()
     if options.impl == "reference":
         return reference_arm()
@@ -193,7 +197,7 @@ def main() -> int:
     config = LlamaConfig(**shape)
     model = random_model(config, seed=0, dtype="bfloat16", device=device)
     rng = np.random.default_rng(0)
-    out_dir = os.path.join(ROOT, "gpurun_out")
+    out_dir = options.log_dir or tempfile.mkdtemp(prefix="helix_bench_")
     os.makedirs(out_dir, exist_ok=True)
     steps, warmup = options.steps, options.warmup
 

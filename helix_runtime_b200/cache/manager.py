@@ -119,7 +119,8 @@ class CacheManager:
         return self.groups[self._entry_place[entry][0]]
 
     def layer_storage(self, entry: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        """Key and value storage ``[page, kv_head, slot, head_dim]`` of one schedule entry."""
+        """Key and value storage of one schedule entry: ``[page, kv_head, page_size, head_dim]`` in
+        shape, the last two axes in the kernels' chunked order (see the module's docstring)."""
         group_index, layer = self._entry_place[entry]
         storage = self.groups[group_index].storage
         return storage[layer, 0], storage[layer, 1]

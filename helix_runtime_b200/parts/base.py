@@ -85,7 +85,7 @@ class LayerCache:
     """What one schedule entry sees of the cache manager."""
     entry: int                                  # the schedule entry that owns the storage
     owns: bool                                  # False: reads another entry's cache, writes nothing
-    keys: Optional[torch.Tensor] = None         # [page, kv_head, slot, head_dim]
+    keys: Optional[torch.Tensor] = None         # [page, kv_head, (head_dim/c, slot, c)]: chunked
     values: Optional[torch.Tensor] = None
     block_tables: Optional[torch.Tensor] = None  # [state slot, page index] int32
     page_size: int = 0
