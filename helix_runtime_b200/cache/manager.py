@@ -63,8 +63,23 @@ class CacheGroup:
         else:
             self.storage = torch.zeros(shape, dtype=dtype, device=device)
         self.host_tables = np.full((max_requests, max_pages_per_request), -1, dtype=np.int32)
+        # uploads go through a pinned copy, so that they queue behind the step in flight
+        # instead of waiting for it; the event says when the pinned copy may be rewritten
+        pinned = device.type == "cuda"
+        self._staging = torch.full((max_requests, max_pages_per_request), -1, dtype=torch.int32,
+                                   pin_memory=pinned)
+        self._staged = torch.cuda.Event() if pinned else None
         self.device_tables = torch.full((max_requests, max_pages_per_request), -1,
                                         dtype=torch.int32, device=device)
+        self.dirty = False
+
+    def upload_tables(self) -> None:
+        if self._staged is not None:
+            self._staged.synchronize()       # the last upload has left the pinned copy
+        self._staging.numpy()[:] = self.host_tables
+        self.device_tables.copy_(self._staging, non_blocking=True)
+        if self._staged is not None:
+            self._staged.record()
         self.dirty = False
 
     @property
@@ -136,6 +151,10 @@ class CacheManager:
 
     def length(self, request: Hashable) -> int:
         return self._requests[request].length
+
+    def reserved(self, request: Hashable) -> int:
+        """Positions the request has pages for: its length plus what steps in flight add."""
+        return self._requests[request].reserved
 
     def live_requests(self) -> List[Hashable]:
         return list(self._requests)
@@ -250,10 +269,16 @@ class CacheManager:
                 group.dirty = True
                 record.first_live[index] = dead_pages
 
-    def rollback(self, request: Hashable) -> None:
-        """Give back pages reserved beyond the published length (a step that failed)."""
+    def rollback(self, request: Hashable, keep_length: Optional[int] = None) -> None:
+        """Give back pages reserved beyond the published length (a step that failed), or
+        beyond ``keep_length`` when an earlier step that reserved up to there is still in
+        flight."""
         record = self._requests[request]
-        keep = self.pages_for(record.length)
+        target = record.length if keep_length is None else keep_length
+        if not record.length <= target <= record.reserved:
+            raise ValueError(f"cannot roll back to {target}: published {record.length}, "
+                             f"reserved {record.reserved}")
+        keep = self.pages_for(target)
         for index, group in enumerate(self.groups):
             table = record.tables[index]
             if len(table) > keep:
@@ -262,7 +287,7 @@ class CacheManager:
                 group.host_tables[record.slot, keep:len(table)] = -1
                 del table[keep:]
                 group.dirty = True
-        record.reserved = record.length
+        record.reserved = target
 
     def release(self, request: Hashable) -> int:
         """The request is over: give back its pages (in table order) and its slot."""
@@ -383,8 +408,7 @@ class CacheManager:
         """Copy block tables that changed since the last step to the device."""
         for group in self.groups:
             if group.dirty:
-                group.device_tables.copy_(torch.from_numpy(group.host_tables), non_blocking=True)
-                group.dirty = False
+                group.upload_tables()
 
     # -------------------------------------------------------------------- audit
 

@@ -37,7 +37,7 @@ void hx_count_launches(int kernels) { g_hx_launches.fetch_add(kernels, std::memo
 // counts once, when it is captured).
 HX_API long long hx_launch_count() { return g_hx_launches.load(std::memory_order_relaxed); }
 
-HX_API int hx_abi_version() { return 4; }
+HX_API int hx_abi_version() { return 5; }
 
 // ------------------------------------------------------------------- embedding
 
@@ -568,5 +568,29 @@ HX_API int hx_advance_decode(int* token_ids, int* positions, const int* sampled,
   if (count == 0) return HX_OK;
   hx_launch(advance_decode_kernel, (count + 127) / 128, 128, 0, stream, token_ids, positions, sampled, count);
   HX_CHECK_LAUNCH("hx_advance_decode");
+  return HX_OK;
+}
+
+// A step that was prepared before the host knew what the step before it sampled takes its
+// tokens from that step's output on the device: token_ids[i] = sampled[rows[i]].  A row whose
+// logits were not finite (-1) feeds token 0: its request has failed and the host drops the row.
+__global__ void feed_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
+                                   const int* __restrict__ rows, int count, int sampled_rows) {
+  hx_pdl_prologue();
+  const int index = blockIdx.x * blockDim.x + threadIdx.x;
+  if (index < count) {
+    const int row = rows[index];
+    const int token = row >= 0 && row < sampled_rows ? sampled[row] : 0;
+    token_ids[index] = token < 0 ? 0 : token;
+  }
+}
+
+HX_API int hx_feed_tokens(int* token_ids, const int* sampled, const int* rows, int count,
+                          int sampled_rows, cudaStream_t stream) {
+  HX_REQUIRE(count >= 0 && sampled_rows >= 0, "hx_feed_tokens: bad count");
+  if (count == 0) return HX_OK;
+  hx_launch(feed_tokens_kernel, (count + 127) / 128, 128, 0, stream, token_ids, sampled, rows,
+            count, sampled_rows);
+  HX_CHECK_LAUNCH("hx_feed_tokens");
   return HX_OK;
 }

@@ -23,8 +23,9 @@ from ..sampling.sampler import Sampler, uniform_for
 from ..weights.loader import load_tensors
 from ..weights.random_init import random_tensors, write_model_folder
 from ..weights.safetensors_io import Checkpoint
-from .scheduler import (FifoScheduler, Request, RequestState, SchedulerConfig, StopReason,
-                        WorkCompletion)
+from ..ops import library as ops
+from .scheduler import (FifoScheduler, IterationBatch, Request, RequestState, SchedulerConfig,
+                        StopReason, WorkCompletion, WorkKind)
 from .graphs import DecodeGraphs, bucketed_context
 from .step import StepEntry, StepError, StepFunction
 
@@ -117,6 +118,8 @@ class EngineConfig:
     prefix_cache_pages: Optional[int] = None  # page references the kept prefixes may hold
                                               # (default: half the pool)
     cuda_graphs: bool = True                  # replay decode-only steps as CUDA graphs
+    lookahead: bool = True                    # queue the next decode step before this one's
+                                              # tokens have been read (needs cuda_graphs)
 
 
 @dataclasses.dataclass
@@ -125,6 +128,23 @@ class GenerationResult:
     stop_reason: str
     cached_token_count: int
     request_id: int = -1
+
+
+@dataclasses.dataclass
+class _Flight:
+    """A step that has been queued on the device and not yet completed."""
+    batch: IterationBatch
+    slot: int                                         # the sampler's result slot it reports to
+    entries: List[StepEntry] = dataclasses.field(default_factory=list)
+    result: "IterationResult" = None
+    ctx: object = None
+    n_want: int = 0
+    new_lengths: List[int] = dataclasses.field(default_factory=list)
+    decode_only: bool = False
+    error: Optional[str] = None
+
+    def __post_init__(self) -> None:
+        self.result = IterationResult()
 
 
 @dataclasses.dataclass
@@ -168,6 +188,8 @@ class Engine:
             self.prefix = PrefixIndex(self.cache, config.prefix_cache_entries,
                                       config.prefix_cache_pages)
         self._matches: Dict[int, PrefixMatch] = {}      # lookups of the iteration being planned
+        self._flight: Optional[_Flight] = None          # the step queued ahead, if any
+        self.steps_queued_ahead = 0
 
     # ------------------------------------------------------------ construction
 
@@ -258,70 +280,119 @@ class Engine:
     # ---------------------------------------------------------------- iteration
 
     def run_iteration(self) -> IterationResult:
-        """Schedule one batch, run it as one step, sample, complete, free what retired."""
-        result = IterationResult()
-        self._matches.clear()
-        batch = self.scheduler.schedule_iteration(self.cache, admit=self._admit,
-                                                  release=self.cache.release,
-                                                  reusable=self._reusable, reclaim=self._reclaim)
-        if batch is None:
-            result.idle = True
-            return result
+        """Complete one iteration: schedule a batch, run it as one step, sample, complete, free
+        what retired.  With ``lookahead`` the call also queues the decode step that follows
+        behind the one it waits for, when the scheduler can plan it before the tokens are
+        known, so the device runs the next step while the host reads this one's tokens,
+        completes it and plans again; that step is completed by the next call."""
+        flight, self._flight = self._flight, None
+        if flight is None:
+            self._matches.clear()
+            batch = self.scheduler.schedule_iteration(self.cache, admit=self._admit,
+                                                      release=self.cache.release,
+                                                      reusable=self._reusable,
+                                                      reclaim=self._reclaim)
+            if batch is None:
+                return IterationResult(idle=True)
+            flight = self._launch(batch, None)
+        if self.config.lookahead and self.graphs is not None and flight.decode_only \
+                and flight.error is None:
+            ahead = self.scheduler.schedule_ahead(self.cache, self.model.max_positions)
+            if ahead is not None:
+                self._flight = self._launch(ahead, flight)
+                self.steps_queued_ahead += 1
+        return self._complete(flight)
+
+    def _launch(self, batch: IterationBatch, previous: Optional["_Flight"]) -> "_Flight":
+        """Queue the batch's step on the device.  ``previous``: the step in flight whose
+        sampled tokens this one reads on the device (same requests, one token each)."""
+        flight = _Flight(batch=batch, slot=0 if previous is None else 1 - previous.slot)
+        result = flight.result
         result.preempted = list(batch.preempted)
         result.kv_limited = batch.kv_limited
-        entries: List[StepEntry] = []
+        result.scheduled_tokens = batch.scheduled_tokens
+        entries = flight.entries
         temperatures: List[float] = []
         uniforms: List[float] = []
+        feed_rows: Optional[List[int]] = None
+        if previous is not None:
+            row_of = {entry.request: row for row, entry in enumerate(previous.entries)}
+            feed_rows = [row_of[work.request_id] for work in batch.work]
         for work in batch.work:
             request = self.scheduler.request(work.request_id)
-            tokens = request.feed[work.token_offset:work.token_offset + work.token_count]
+            if previous is None:
+                tokens = request.feed_slice(work.token_offset, work.token_count)
+            else:
+                tokens = [0]             # the device puts the token of ``previous`` here
             want = [work.token_count - 1] if work.samples and request.max_new_tokens > 0 else []
             entries.append(StepEntry(work.request_id, tokens, want))
             if want:
                 temperatures.append(request.temperature)
-                uniforms.append(uniform_for(request.seed, len(request.generated)))
-            if work.kind.value == "prefill":
+                uniforms.append(uniform_for(request.seed, len(request.generated)
+                                            + (0 if previous is None else 1)))
+            if work.kind is WorkKind.PREFILL:
                 result.prefill_tokens += work.token_count
             else:
                 result.decode_tokens += work.token_count
-        result.scheduled_tokens = batch.scheduled_tokens
-
-        completions: List[WorkCompletion] = []
         step = self.step_function
+        flight.decode_only = all(len(entry.tokens) == 1 and len(entry.want) == 1
+                                 for entry in entries)
         try:
-            decode_only = all(len(entry.tokens) == 1 and len(entry.want) == 1 for entry in entries)
             hint = 0
-            if decode_only and self.graphs is not None:
-                hint = bucketed_context(1 + max(self.cache.length(e.request) for e in entries))
-            ctx, want_rows, n_want, new_lengths = step.prepare(entries, context_hint=hint)
+            if flight.decode_only and self.graphs is not None:
+                hint = bucketed_context(1 + max(self.cache.reserved(e.request) for e in entries))
+            flight.ctx, want_rows, flight.n_want, flight.new_lengths = step.prepare(
+                entries, context_hint=hint, feed_rows=feed_rows)
             try:
-                sampled: List[int] = []
-                if n_want:
+                tokens = None
+                if flight.n_want:
                     greedy = self.sampler.prepare(temperatures, uniforms)
-                    if self.graphs is not None and decode_only:
-                        tokens = self.graphs.run(ctx, want_rows, n_want, greedy)
+                    if self.graphs is not None and flight.decode_only:
+                        tokens = self.graphs.run(
+                            flight.ctx, want_rows, flight.n_want, greedy,
+                            feed_rows=None if feed_rows is None else step.feed_rows)
                     else:
-                        logits = self.model.forward(ctx, self.cache, want_rows, n_want)
+                        logits = self.model.forward(flight.ctx, self.cache, want_rows,
+                                                    flight.n_want)
                         tokens = self.sampler.launch(logits, greedy, step.status)
-                    sampled = self.sampler.to_host(tokens)
                 else:
-                    self.model.forward(ctx, self.cache, want_rows, 0)
-                flags = int(step.status.item())
-                if flags & ~8:   # anything but per-row non-finite logits condemns the whole step
-                    step.raise_on_status()
-                if flags:
-                    step.status.zero_()
+                    self.model.forward(flight.ctx, self.cache, want_rows, 0)
+                self.sampler.fetch(flight.slot, tokens, step.status)
             except Exception:
-                step.fail(entries)
+                # what a step still in flight reserved stays; this step's pages go back
+                step.fail(entries, [length - len(entry.tokens) for entry, length
+                                    in zip(entries, flight.new_lengths)])
                 raise
-            step.finish(entries, new_lengths, ctx)
+        except StepError as error:
+            flight.error = str(error)
+        return flight
+
+    def _complete(self, flight: "_Flight") -> IterationResult:
+        """Wait for the step's results and apply them."""
+        batch, entries, result = flight.batch, flight.entries, flight.result
+        step = self.step_function
+        completions: List[WorkCompletion] = []
+        if flight.error is None:
+            sampled, flags = self.sampler.collect(flight.slot, flight.n_want)
+            if flags:
+                step.status.zero_()
+            if flags & ~ops.FLAG_NONFINITE:
+                # anything but per-row non-finite logits condemns the whole step, and with it a
+                # step that was queued behind it and has read what this one left
+                step.fail(entries)
+                flight.error = StepFunction.describe_status(flags)
+                if self._flight is not None:
+                    self._flight.error = flight.error
+        if flight.error is None:
+            step.finish(entries, flight.new_lengths, flight.ctx)
             if self.prefix is not None:
                 # a request whose LAST prompt portion has just succeeded leaves its longest
                 # aligned prefix to later requests (src/runtime/cpu_engine.cpp:136-160)
                 for work in batch.work:
                     request = self.scheduler.request(work.request_id)
                     prompt_tokens = len(request.prompt)
-                    if (work.kind.value == "prefill" and request.namespace is not None
+                    if (work.kind is WorkKind.PREFILL and request.namespace is not None
+                            and not request.is_terminal
                             and work.token_offset < prompt_tokens
                             <= work.token_offset + work.token_count):
                         self.prefix.publish(request.namespace, request.id, request.prompt)
@@ -340,8 +411,8 @@ class Engine:
                     token = 0   # max_new_tokens == 0: nothing is sampled, nothing is used
                 completions.append(WorkCompletion(work.request_id, True, token=token))
             result.sampled = cursor
-        except StepError as error:
-            completions = [WorkCompletion(work.request_id, False, error=str(error))
+        else:
+            completions = [WorkCompletion(work.request_id, False, error=flight.error)
                            for work in batch.work]
         retired = self.scheduler.complete_iteration(batch.id, completions,
                                                     self.model.max_positions,
@@ -354,7 +425,8 @@ class Engine:
 
     def run_until_done(self, max_iterations: Optional[int] = None) -> int:
         iterations = 0
-        while self.scheduler.has_unfinished():
+        # a step queued ahead is completed even when every request ended in the one before it
+        while self.scheduler.has_unfinished() or self._flight is not None:
             outcome = self.run_iteration()
             iterations += 1
             if outcome.idle:
@@ -394,4 +466,5 @@ class Engine:
                                page_references=self.prefix.page_references)
                 if self.prefix is not None else None,
                 "steps": self.step_function.steps_run, "tokens": self.step_function.tokens_run,
+                "steps_queued_ahead": self.steps_queued_ahead,
                 "workspace_bytes": self.step_function.workspace.bytes()}

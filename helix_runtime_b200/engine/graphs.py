@@ -44,12 +44,15 @@ class DecodeGraphs:
         return (ctx.n_tokens, n_want, ctx.max_context_len, greedy)
 
     def run(self, ctx: StepContext, want_rows: torch.Tensor, n_want: int, greedy: bool,
-            advance: bool = False) -> torch.Tensor:
+            advance: bool = False, feed_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run the step (forward, then sampling of the wanted rows) and return the device
         tensor of sampled ids.  The first time a key is seen the step runs eagerly and is
-        recorded afterwards; from then on it is replayed."""
+        recorded afterwards; from then on it is replayed.  ``feed_rows`` (device, one per
+        token): the step's tokens are the ids the previous step sampled in these rows, put in
+        place by the first kernel of the graph."""
         from ..ops import library as ops
-        key = self.key_for(ctx, n_want, greedy) + ((advance,) if advance else ())
+        key = self.key_for(ctx, n_want, greedy) + ((advance,) if advance else ()) \
+            + (("fed",) if feed_rows is not None else ())
         graph = self._graphs.get(key)
         if graph is not None:
             graph.replay()
@@ -57,6 +60,8 @@ class DecodeGraphs:
             return self.sampler.tokens[:n_want]
 
         def body() -> torch.Tensor:
+            if feed_rows is not None:
+                ops.feed_tokens(ctx.token_ids, self.sampler.tokens, feed_rows, ctx.n_tokens)
             logits = self.step_function.model.forward(ctx, self.step_function.cache, want_rows,
                                                       n_want)
             tokens = self.sampler.launch(logits, greedy, ctx.status)

@@ -10,7 +10,10 @@ Policy, after the reference's ``FifoScheduler`` (src/scheduler/fifo_scheduler.cp
   (this engine's own knob) and by the pages that are free;
 * a request that gets nothing, or less than the budget allowed, because pages ran
   out stops the planning of this iteration (``kv_limited``);
-* one iteration is in flight at a time and is completed as a whole.
+* one iteration is in flight at a time and is completed as a whole; a second one may be
+  planned *ahead* of its completion when it is known beforehand who takes part in it
+  (``schedule_ahead``: every running request decodes one more token), so that the device
+  need not wait for the host between two decode steps.
 
 Sampling happens at the end of the step that produced the logits, so a request's
 last token needs no step of its own: a request with prompt P and N new tokens runs
@@ -81,6 +84,20 @@ class Request:
     def feed(self) -> List[int]:
         """Everything the model has to read before it can produce the next new token."""
         return self.prompt + self.generated
+
+    @property
+    def feed_length(self) -> int:
+        return len(self.prompt) + len(self.generated)
+
+    def feed_slice(self, offset: int, count: int) -> List[int]:
+        """``feed[offset:offset + count]`` without building the whole list."""
+        prompt_tokens = len(self.prompt)
+        end = offset + count
+        if end <= prompt_tokens:
+            return self.prompt[offset:end]
+        if offset >= prompt_tokens:
+            return self.generated[offset - prompt_tokens:end - prompt_tokens]
+        return self.prompt[offset:] + self.generated[:end - prompt_tokens]
 
     @property
     def remaining_feed(self) -> int:
@@ -162,6 +179,7 @@ class FifoScheduler:
         self.waiting: Deque[int] = deque()
         self.running: List[int] = []
         self.active: Optional[IterationBatch] = None
+        self.ahead: Optional[IterationBatch] = None      # planned before ``active`` completed
         self._next_request = 0
         self._next_iteration = 0
         self.stats = {"iterations": 0, "prefill_tokens": 0, "decode_tokens": 0,
@@ -244,6 +262,49 @@ class FifoScheduler:
             self.stats[key] += work.token_count
         return batch
 
+    def schedule_ahead(self, ledger: PageLedger, max_positions: int) -> Optional[IterationBatch]:
+        """Plan the iteration after the one in flight before that one's tokens are known, or
+        return None when its make-up depends on them.
+
+        It is planned when the iteration in flight decodes one token for every running
+        request, none of them can end in it by its count of new tokens or by the context
+        limit, nobody waits who could be admitted, and every request has a page for one more
+        token.  What cannot be known is an end-of-sequence token: a request that samples one
+        in the iteration in flight retires there, and its row of the iteration planned ahead
+        is computed for nothing and dropped at completion (as for a request cancelled in
+        flight).  The reference completes every iteration before it plans the next
+        (src/scheduler/fifo_scheduler.cpp:149-304); this is this engine's own."""
+        batch = self.active
+        if batch is None or self.ahead is not None:
+            return None
+        if self.waiting and len(self.running) < self.config.max_running_requests:
+            return None
+        if len(self.running) > self.config.max_tokens_per_iteration:
+            return None
+        if [work.request_id for work in batch.work] != self.running:
+            return None
+        available = list(ledger.free_pages())
+        work_ahead: List[ScheduledWork] = []
+        for work in batch.work:
+            request = self.requests[work.request_id]
+            if (work.kind is not WorkKind.DECODE or not work.samples or work.token_count != 1
+                    or request.is_terminal or request.remaining_generation < 2
+                    or request.processed + 2 > max_positions):
+                return None
+            if ledger.max_extend(request.id, 1, available) < 1:
+                return None
+            needed = ledger.pages_to_extend(request.id, request.processed + 2)
+            for index, count in enumerate(needed):
+                available[index] -= count
+            work_ahead.append(ScheduledWork(request_id=request.id, kind=WorkKind.DECODE,
+                                            token_offset=request.processed + 1, token_count=1,
+                                            samples=True))
+        self.ahead = IterationBatch(id=batch.id + 1, work=work_ahead,
+                                    scheduled_tokens=len(work_ahead))
+        self.stats["iterations"] += 1
+        self.stats["decode_tokens"] += len(work_ahead)
+        return self.ahead
+
     def _plan(self, ledger: PageLedger, admit: Callable[[int], None],
               reusable: Optional[Callable[[Request], int]] = None) -> IterationBatch:
         batch = IterationBatch(id=self._next_iteration, work=[])
@@ -257,9 +318,9 @@ class FifoScheduler:
             start = request.processed
             if waiting and reusable is not None:
                 start = reusable(request)
-                if start % self.page_size != 0 or not 0 <= start < len(request.feed):
+                if start % self.page_size != 0 or not 0 <= start < request.feed_length:
                     raise ValueError("a reused prefix is whole pages and leaves a token to run")
-            desired = len(request.feed) - start
+            desired = request.feed_length - start
             assert desired > 0, "an active request always has something to feed"
             if prefill and self.config.max_prefill_chunk is not None:
                 desired = min(desired, self.config.max_prefill_chunk)
@@ -355,7 +416,7 @@ class FifoScheduler:
                 self._retire(request, RequestState.FINISHED, StopReason.CONTEXT_LIMIT, now)
             if request.is_terminal:
                 retired.append(request)
-        self.active = None
+        self.active, self.ahead = self.ahead, None
         self._next_iteration += 1
         return retired
 

@@ -13,7 +13,7 @@ it; if anything raises, reserved pages go back and no length moves
 from __future__ import annotations
 
 import dataclasses
-from typing import Hashable, List, Optional, Sequence
+from typing import Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -54,7 +54,7 @@ class StepFunction:
         cursor = 0
         for name, size in (("token_ids", cap), ("positions", cap), ("token_request", cap),
                            ("want_rows", cap), ("request_slot", req), ("request_start", req + 1),
-                           ("request_context", req)):
+                           ("request_context", req), ("feed_rows", req)):
             self._layout[name] = (cursor, cursor + size)
             cursor += size
         pin = self.device.type == "cuda"
@@ -73,16 +73,27 @@ class StepFunction:
 
     # --------------------------------------------------------------------- run
 
-    def prepare(self, entries: Sequence[StepEntry], context_hint: int = 0):
+    @property
+    def feed_rows(self) -> torch.Tensor:
+        """Device view of the rows named by ``prepare(..., feed_rows=...)``."""
+        return self._view("feed_rows", True)
+
+    def prepare(self, entries: Sequence[StepEntry], context_hint: int = 0,
+                feed_rows: Optional[Sequence[int]] = None):
         """Validate, reserve pages, fill and upload the batch description.
         Returns ``(context, want_rows_device, n_want, new_lengths)``.  ``context_hint`` raises
         the context length that launches are sized for (a caller that will replay the step
-        while the requests grow passes the length they will reach)."""
+        while the requests grow passes the length they will reach).  ``feed_rows``: the step
+        is prepared before the host knows its tokens; every entry brings one placeholder token
+        and names the row of the previous step's sampled tokens that the device puts in its
+        place (:func:`helix_runtime_b200.ops.library.feed_tokens`)."""
         if not entries:
             raise StepError("a step needs at least one entry")
         if len(entries) > self.max_requests:
             raise StepError(f"{len(entries)} requests in one step, at most {self.max_requests}")
         total = sum(len(entry.tokens) for entry in entries)
+        if feed_rows is not None and (len(feed_rows) != len(entries) or total != len(entries)):
+            raise StepError("a step fed on the device has one token and one row per request")
         if total > self.max_tokens:
             raise StepError(f"{total} tokens in one step, at most {self.max_tokens}")
         seen = set()
@@ -103,7 +114,7 @@ class StepFunction:
                 if not 0 <= int(place) < len(entry.tokens):
                     raise StepError(f"wanted place {place} of request {entry.request!r} is "
                                     f"outside its {len(entry.tokens)} tokens")
-            if self.cache.length(entry.request) + len(entry.tokens) > self.model.max_positions:
+            if self.cache.reserved(entry.request) + len(entry.tokens) > self.model.max_positions:
                 raise StepError(f"request {entry.request!r} would exceed the model's "
                                 f"{self.model.max_positions} positions")
 
@@ -118,7 +129,7 @@ class StepFunction:
         request_context = self._view("request_context", False)
 
         new_lengths: List[int] = []
-        reserved: List[Hashable] = []
+        reserved: List[Tuple[Hashable, int]] = []
         cursor = 0
         n_want = 0
         max_query = 0
@@ -127,9 +138,10 @@ class StepFunction:
         try:
             for index, entry in enumerate(entries):
                 count = len(entry.tokens)
-                before = self.cache.length(entry.request)
+                # a step still in flight has reserved its positions already: go on from there
+                before = self.cache.reserved(entry.request)
                 self.cache.extend(entry.request, before + count)
-                reserved.append(entry.request)
+                reserved.append((entry.request, before))
                 token_ids[cursor:cursor + count] = np.asarray(entry.tokens, dtype=np.int32)
                 positions[cursor:cursor + count] = np.arange(before, before + count, dtype=np.int32)
                 token_request[cursor:cursor + count] = index
@@ -145,9 +157,11 @@ class StepFunction:
                 min_query = min(min_query, count)
                 max_context = max(max_context, before + count)
             request_start[len(entries)] = cursor
+            if feed_rows is not None:
+                self._view("feed_rows", False)[:len(entries)] = np.asarray(feed_rows, dtype=np.int32)
         except Exception:
-            for request in reserved:
-                self.cache.rollback(request)
+            for request, before in reserved:
+                self.cache.rollback(request, keep_length=before)
             raise
 
         self._device.copy_(self._host, non_blocking=True)
@@ -189,25 +203,34 @@ class StepFunction:
                ctx: StepContext) -> None:
         """The step succeeded: publish the new lengths."""
         for entry, length in zip(entries, new_lengths):
-            self.cache.commit(entry.request, length)
+            if self.cache.has(entry.request):    # a request may have ended while in flight
+                self.cache.commit(entry.request, length)
         self.last_context = ctx
         self.steps_run += 1
         self.tokens_run += ctx.n_tokens
 
-    def fail(self, entries: Sequence[StepEntry]) -> None:
-        """The step failed: give back what was reserved for it; no length moves."""
+    def fail(self, entries: Sequence[StepEntry],
+             keep_lengths: Optional[Sequence[int]] = None) -> None:
+        """The step failed: give back what was reserved for it; no length moves.
+        ``keep_lengths``: what an earlier step that is still in flight has reserved for each
+        entry, which stays."""
         self.workspace.clear_accumulators()
-        for entry in entries:
+        for index, entry in enumerate(entries):
             if self.cache.has(entry.request):
-                self.cache.rollback(entry.request)
+                self.cache.rollback(entry.request,
+                                    None if keep_lengths is None else keep_lengths[index])
+
+    @staticmethod
+    def describe_status(flags: int) -> str:
+        names = [name for bit, name in ((ops.FLAG_BAD_TOKEN, "token id outside the vocabulary"),
+                                        (ops.FLAG_BAD_PAGE, "block table entry outside the pool"),
+                                        (ops.FLAG_WAIT_TIMEOUT, "a bounded kernel wait ran out"),
+                                        (ops.FLAG_NONFINITE, "non-finite logits")) if flags & bit]
+        return "the step's kernels reported: " + "; ".join(names)
 
     def raise_on_status(self) -> None:
         """Read the device status word (synchronises) and raise if a kernel flagged a fault."""
         flags = int(self.status.item())
         if flags:
             self.status.zero_()
-            names = [name for bit, name in ((ops.FLAG_BAD_TOKEN, "token id outside the vocabulary"),
-                                            (ops.FLAG_BAD_PAGE, "block table entry outside the pool"),
-                                            (ops.FLAG_WAIT_TIMEOUT, "a bounded kernel wait ran out"),
-                                            (ops.FLAG_NONFINITE, "non-finite logits")) if flags & bit]
-            raise StepError("the step's kernels reported: " + "; ".join(names))
+            raise StepError(self.describe_status(flags))

@@ -82,6 +82,8 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_launch_count.argtypes = []
     library.hx_advance_decode.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]
     library.hx_advance_decode.restype = _c_int
+    library.hx_feed_tokens.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr]
+    library.hx_feed_tokens.restype = _c_int
     for name in ("hx_embed", "hx_rmsnorm", "hx_swiglu", "hx_rope_append", "hx_gemm_simt",
                  "hx_gemm_tc", "hx_gemm_tc_supports", "hx_gemm_tc_token_tile",
                  "hx_paged_attention", "hx_argmax", "hx_sample"):
@@ -339,6 +341,17 @@ def advance_decode(token_ids: torch.Tensor, positions: torch.Tensor, sampled: to
     """token_ids[:count] = sampled[:count]; positions[:count] += 1 (the device-side decode loop)."""
     _check(lib().hx_advance_decode(token_ids.data_ptr(), positions.data_ptr(), sampled.data_ptr(),
                                    count, _stream()))
+
+
+def feed_tokens(token_ids: torch.Tensor, sampled: torch.Tensor, rows: torch.Tensor,
+                count: int) -> None:
+    """token_ids[i] = max(sampled[rows[i]], 0) for i < count: the tokens of a step that was
+    prepared before the host had read what the step before it sampled."""
+    _need(token_ids, torch.int32, "token_ids")
+    _need(sampled, torch.int32, "sampled")
+    _need(rows, torch.int32, "rows")
+    _check(lib().hx_feed_tokens(token_ids.data_ptr(), sampled.data_ptr(), rows.data_ptr(), count,
+                                sampled.shape[0], _stream()))
 
 
 def launch_count() -> int:

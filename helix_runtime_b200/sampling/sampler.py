@@ -43,6 +43,12 @@ class Sampler:
         self._device_params = torch.zeros((2, max_rows), dtype=torch.float32, device=device)
         self.tokens = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self._host_tokens = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+        self._params_uploaded = torch.cuda.Event() if pin else None
+        # results of steps in flight: [tokens..., status word] per slot, with the event that
+        # says when the slot has arrived
+        self._results = [torch.zeros(max_rows + 1, dtype=torch.int32, pin_memory=pin)
+                         for _ in range(2)]
+        self._arrived = [torch.cuda.Event() if pin else None for _ in range(2)]
 
     def prepare(self, temperatures: Sequence[float], uniforms: Sequence[float]) -> bool:
         """Upload the rows' temperatures and uniform numbers; return True when every row is
@@ -52,10 +58,14 @@ class Sampler:
             raise ValueError(f"{rows} rows to sample, at most {self.max_rows}")
         if all(t <= 0.0 for t in temperatures):
             return True
+        if self._params_uploaded is not None:
+            self._params_uploaded.synchronize()     # the last upload has left the pinned block
         params = self._host_params.numpy()
         params[0, :rows] = np.asarray(temperatures, dtype=np.float32)
         params[1, :rows] = np.asarray(uniforms, dtype=np.float32)
         self._device_params.copy_(self._host_params, non_blocking=True)
+        if self._params_uploaded is not None:
+            self._params_uploaded.record()
         return False
 
     def launch(self, logits: torch.Tensor, greedy: bool,
@@ -79,4 +89,21 @@ class Sampler:
         rows = tokens.shape[0]
         self._host_tokens[:rows].copy_(tokens, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        return [int(t) for t in self._host_tokens[:rows]]
+        return self._host_tokens.numpy()[:rows].tolist()
+
+    def fetch(self, slot: int, tokens: Optional[torch.Tensor], status: torch.Tensor) -> None:
+        """Queue the copy of a step's sampled ids (if it sampled) and of the status word to
+        the host, behind the step on the current stream; ``collect(slot)`` waits for it.  Two
+        slots, so that a step can be queued before the one before it has been collected."""
+        result = self._results[slot]
+        rows = 0 if tokens is None else tokens.shape[0]
+        if rows:
+            result[:rows].copy_(tokens, non_blocking=True)
+        result[self.max_rows:].copy_(status, non_blocking=True)
+        self._arrived[slot].record()
+
+    def collect(self, slot: int, rows: int):
+        """Wait for ``fetch(slot, ...)``; returns ``(sampled ids, status flags)``."""
+        self._arrived[slot].synchronize()
+        values = self._results[slot].numpy()
+        return values[:rows].tolist(), int(values[self.max_rows])

@@ -78,6 +78,10 @@ int hx_rope_append(void* qkv, int dtype, int ld, const int* positions, const int
                    int* status, float* accum, int ld_accum, cudaStream_t stream);
 int hx_advance_decode(int* token_ids, int* positions, const int* sampled, int count,
                       cudaStream_t stream);
+/* token_ids[i] = max(sampled[rows[i]], 0): a step takes its tokens from the output of the
+ * step before it without a round trip to the host */
+int hx_feed_tokens(int* token_ids, const int* sampled, const int* rows, int count,
+                   int sampled_rows, cudaStream_t stream);
 
 /* ---- matrix products: out[t, f] (+)= sum_k x[t, k] * w[f, k] ---------------------------- */
 /* CUDA cores, float32 accumulate in a fixed order; both dtypes; the true 32-bit path */

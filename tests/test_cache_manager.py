@@ -69,6 +69,31 @@ def test_reserve_commit_and_rollback():
     cache.check()
 
 
+def test_two_steps_in_flight_reserve_on_top_of_each_other():
+    cache = manager()
+    cache.admit("a")
+    cache.extend("a", 4)
+    cache.commit("a", 4)
+    cache.extend("a", 5)                         # a step in flight
+    cache.extend("a", 9)                         # the step queued behind it
+    assert cache.reserved("a") == 9 and cache.length("a") == 4
+    assert cache.max_extend("a", 100, [0]) == 3  # counted from what is reserved
+    cache.rollback("a", keep_length=5)           # the second failed before it ran
+    assert cache.reserved("a") == 5 and cache.groups[0].pool.pages_in_use == 2
+    cache.extend("a", 9)
+    cache.commit("a", 5)                         # the first succeeded
+    assert cache.length("a") == 5 and cache.reserved("a") == 9
+    with pytest.raises(ValueError, match="cannot roll back"):
+        cache.rollback("a", keep_length=4)
+    with pytest.raises(ValueError, match="cannot roll back"):
+        cache.rollback("a", keep_length=10)
+    cache.rollback("a")                          # the first's successor failed on the device
+    assert cache.reserved("a") == 5 and cache.groups[0].pool.pages_in_use == 2
+    cache.check()
+    cache.release("a")
+    cache.check()
+
+
 def test_running_out_of_pages_takes_nothing():
     cache = manager(num_pages=4)
     cache.admit("a")

@@ -156,6 +156,64 @@ def test_prompts_that_begin_alike_share_pages_and_generate_the_same(name, dtype,
     assert all(group.pool.pages_in_use == 0 for group in engine.cache.groups)
 
 
+def run_requests(engine, prompts, budgets, eos, temperatures, cancel_after=None):
+    ids = [engine.submit(prompt, max_new_tokens=budget, eos_token=eos, temperature=temperature,
+                         seed=40 + index)
+           for index, (prompt, budget, temperature) in enumerate(zip(prompts, budgets, temperatures))]
+    iterations = 0
+    while engine.scheduler.has_unfinished() or engine._flight is not None:
+        engine.run_iteration()
+        iterations += 1
+        if cancel_after is not None and iterations == cancel_after[0]:
+            assert engine.cancel(ids[cancel_after[1]])
+            engine.cache.check()
+    engine.cache.check()
+    assert not engine.cache.live_requests()
+    return [(list(engine.request(i).generated), engine.request(i).stop_reason.value,
+             engine._cached_at_finish.get(i)) for i in ids]
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("C", "bfloat16")])
+def test_steps_queued_ahead_change_nothing(name, dtype, folders, plain_models):
+    """The engine queues the next decode step before it has read the tokens of the one in
+    flight.  Requests that end at different times (an end-of-sequence token nobody could
+    foresee, their count of new tokens, the context limit), greedy and sampled, more requests
+    than run at once and a pool that makes them wait: token for token, stop reason and cached
+    count as without looking ahead, and as the plain implementation says."""
+    plain = plain_models(name, dtype)
+    config = tiny_config(name)
+    page = PAGE_SIZE[name]
+    limit = config.max_position_embeddings
+    prompts = [random_tokens(config.vocab_size, length, seed=300 + length)
+               for length in (5, 33, 12, limit - 6, 20, 3)]
+    budgets = [24, 40, 7, 30, 18, 33]
+    temperatures = [0.0, 0.7, 0.0, 0.0, 0.9, 0.0]
+    options = dict(dtype=dtype, page_size=page, max_running_requests=3,
+                   max_tokens_per_iteration=64, num_pages=-(-limit // page) + 8,
+                   poison_free_pages=True)
+    free = Engine.from_pretrained(folders(name, dtype), lookahead=False, **options)
+    free_run = run_requests(free, prompts, budgets, None, temperatures)
+    eos = free_run[0][0][9]                     # the first request meets it at its tenth token
+    outcomes = {}
+    for lookahead in (False, True):
+        engine = Engine.from_pretrained(folders(name, dtype), lookahead=lookahead, **options)
+        outcomes[lookahead] = run_requests(engine, prompts, budgets, eos, temperatures)
+        ahead = engine.stats()["steps_queued_ahead"]
+        assert (ahead > 20) if lookahead else (ahead == 0)
+    assert outcomes[True] == outcomes[False]
+    reasons = [reason for _, reason, _ in outcomes[True]]
+    assert reasons[0] == "eos_token" and "max_new_tokens" in reasons and reasons[3] == "context_limit"
+    for prompt, temperature, (generated, _, _) in zip(prompts, temperatures, outcomes[True]):
+        if temperature == 0.0:
+            check_greedy(plain, prompt, generated, dtype)
+    # a request cancelled while its row of the step queued ahead is in flight
+    engine = Engine.from_pretrained(folders(name, dtype), lookahead=True, **options)
+    cancelled = run_requests(engine, prompts, budgets, eos, temperatures, cancel_after=(6, 1))
+    assert cancelled[1][1] == "cancelled"
+    for index in (0, 2):                         # those that ran beside it are untouched
+        assert cancelled[index] == outcomes[True][index]
+
+
 def test_bad_submissions_are_refused(folders):
     engine = Engine.from_pretrained(folders("A", "float32"), dtype="float32", page_size=8,
                                     max_running_requests=2, num_pages=4)

@@ -230,3 +230,137 @@ def test_many_requests_through_a_small_pool_all_finish_and_nothing_leaks():
         assert len(request.generated) == 1 + (i * 3) % 6
     assert rig.cache.free_pages() == [8] and rig.cache.free_slots == 4
     assert rig.cache.groups[0].pool.reuse_count > 0
+
+
+# ----------------------------------------------------------------- planning ahead
+
+class AheadRig(Rig):
+    """Drives the scheduler the way the engine does with lookahead: the iteration after the
+    one in flight is planned (and its cache rows reserved) before that one is completed."""
+
+    def launch(self, batch):
+        for work in batch.work:
+            reserved = self.cache.reserved(work.request_id)
+            assert reserved == work.token_offset
+            self.cache.extend(work.request_id, reserved + work.token_count)
+
+    def complete(self, batch, tokens):
+        completions = []
+        for work in batch.work:
+            request = self.scheduler.request(work.request_id)
+            if self.cache.has(work.request_id):
+                self.cache.commit(work.request_id, work.token_offset + work.token_count)
+            completions.append(WorkCompletion(work.request_id, True,
+                                              token=tokens.get(request.id, 7)))
+        retired = self.scheduler.complete_iteration(batch.id, completions, self.max_positions)
+        for request in retired:
+            if self.cache.has(request.id):
+                self.cache.release(request.id)
+        self.cache.check()
+        return retired
+
+
+def decoding_rig(**options):
+    rig = AheadRig(**options)
+    ids = [rig.scheduler.submit([1, 2, 3], max_new_tokens=6, eos_token=9) for _ in range(2)]
+    rig.step()                                     # both prompts whole; first tokens sampled
+    return rig, ids
+
+
+def test_the_next_decode_iteration_is_planned_before_the_one_in_flight_completes():
+    rig, ids = decoding_rig()
+    first = rig.scheduler.schedule_iteration(rig.cache, rig.cache.admit, rig.cache.release)
+    rig.launch(first)
+    ahead = rig.scheduler.schedule_ahead(rig.cache, rig.max_positions)
+    assert summary(ahead) == [(ids[0], WorkKind.DECODE, 4, 1, True),
+                              (ids[1], WorkKind.DECODE, 4, 1, True)]
+    assert ahead.id == first.id + 1
+    assert rig.scheduler.schedule_ahead(rig.cache, rig.max_positions) is None   # only one ahead
+    rig.launch(ahead)
+    assert rig.complete(first, {}) == []
+    assert rig.scheduler.active is ahead and rig.scheduler.ahead is None
+    with pytest.raises(RuntimeError, match="in flight"):
+        rig.scheduler.schedule_iteration(rig.cache, rig.cache.admit, rig.cache.release)
+    rig.complete(ahead, {})
+    for rid in ids:
+        request = rig.scheduler.request(rid)
+        assert request.generated == [7, 7, 7] and request.processed == 5
+        assert rig.cache.length(rid) == 5
+
+
+def test_a_request_that_ends_in_flight_loses_its_row_of_the_iteration_planned_ahead():
+    rig, ids = decoding_rig()
+    first = rig.scheduler.schedule_iteration(rig.cache, rig.cache.admit, rig.cache.release)
+    rig.launch(first)
+    ahead = rig.scheduler.schedule_ahead(rig.cache, rig.max_positions)
+    rig.launch(ahead)
+    retired = rig.complete(first, {ids[0]: 9})              # end of sequence for the first
+    assert [r.id for r in retired] == [ids[0]]
+    assert not rig.cache.has(ids[0])                        # pages back while its row is in flight
+    assert rig.complete(ahead, {}) == []
+    gone, stays = rig.scheduler.request(ids[0]), rig.scheduler.request(ids[1])
+    assert gone.generated == [7, 9] and gone.stop_reason is StopReason.EOS_TOKEN
+    assert stays.generated == [7, 7, 7]
+    # the next plan ahead holds the remaining request only
+    second = rig.scheduler.schedule_iteration(rig.cache, rig.cache.admit, rig.cache.release)
+    rig.launch(second)
+    assert summary(rig.scheduler.schedule_ahead(rig.cache, rig.max_positions)) == \
+        [(ids[1], WorkKind.DECODE, 6, 1, True)]
+
+
+def test_nothing_is_planned_ahead_when_its_make_up_depends_on_the_tokens_in_flight():
+    # a request that reaches its count of new tokens in the iteration in flight
+    rig = AheadRig()
+    rid = rig.scheduler.submit([1, 2, 3], max_new_tokens=3)
+    rig.step()
+    batch = rig.scheduler.schedule_iteration(rig.cache, rig.cache.admit, rig.cache.release)
+    rig.launch(batch)
+    assert rig.scheduler.request(rid).remaining_generation == 2
+    assert rig.scheduler.schedule_ahead(rig.cache, rig.max_positions) is not None
+    rig.launch(rig.scheduler.ahead)
+    rig.complete(batch, {})
+    assert rig.scheduler.schedule_ahead(rig.cache, rig.max_positions) is None   # last token next
+    assert [r.id for r in rig.complete(rig.scheduler.active, {})] == [rid]
+
+    # a prompt portion in the batch
+    rig = AheadRig(max_tokens=2)
+    rig.scheduler.submit([1, 2, 3], max_new_tokens=4)
+    batch = rig.scheduler.schedule_iteration(rig.cache, rig.cache.admit, rig.cache.release)
+    rig.launch(batch)
+    assert rig.scheduler.schedule_ahead(rig.cache, rig.max_positions) is None
+
+    # somebody waits who could be admitted
+    rig, ids = decoding_rig()
+    rig.scheduler.submit([4, 5], max_new_tokens=2)
+    batch = rig.scheduler.schedule_iteration(rig.cache, rig.cache.admit, rig.cache.release)
+    assert len(batch.work) == 3
+
+    # the context limit ends the request in the iteration in flight
+    rig = AheadRig(max_positions=5)
+    rig.scheduler.submit([1, 2, 3], max_new_tokens=10)
+    rig.step()
+    batch = rig.scheduler.schedule_iteration(rig.cache, rig.cache.admit, rig.cache.release)
+    rig.launch(batch)                                           # position 3
+    assert rig.scheduler.schedule_ahead(rig.cache, rig.max_positions) is not None  # position 4
+    rig.launch(rig.scheduler.ahead)
+    rig.complete(batch, {})
+    assert rig.scheduler.schedule_ahead(rig.cache, rig.max_positions) is None   # no position 5
+
+    # no page for one more token: the ordinary plan decides who waits
+    rig = AheadRig(num_pages=2, page_size=4, max_running=2)
+    ids = [rig.scheduler.submit([1, 2, 3], max_new_tokens=8) for _ in range(2)]
+    rig.step()
+    batch = rig.scheduler.schedule_iteration(rig.cache, rig.cache.admit, rig.cache.release)
+    rig.launch(batch)                                           # both fill their only page
+    assert rig.scheduler.schedule_ahead(rig.cache, rig.max_positions) is None
+    rig.complete(batch, {})
+
+
+def test_a_full_house_plans_ahead_although_others_wait():
+    rig = AheadRig(max_running=2)
+    ids = [rig.scheduler.submit([1, 2, 3], max_new_tokens=6) for _ in range(3)]
+    rig.step()                                                  # two run, the third waits
+    batch = rig.scheduler.schedule_iteration(rig.cache, rig.cache.admit, rig.cache.release)
+    assert [w.request_id for w in batch.work] == ids[:2]
+    rig.launch(batch)
+    assert rig.scheduler.schedule_ahead(rig.cache, rig.max_positions) is not None
