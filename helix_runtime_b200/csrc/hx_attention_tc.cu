@@ -12,10 +12,14 @@
 //               tensor memory (running two tiles ahead of the softmax), then O_tile = P V;
 //   warp 6      rewrites the keys of a landed tile piece-major over all 64 keys (see below);
 //   warps 2..5  softmax: thread r owns query row r.  It reads its row of S from tensor memory,
-//               keeps the running maximum, sum and output row in float32 registers, writes
-//               the probabilities to shared memory as TWO bfloat16 terms (P = hi + lo, so the
-//               softmax stays a float32 quantity as far as the result can tell), and adds
-//               each O_tile to its output row.
+//               keeps the running maximum and sum in float32 registers and writes the
+//               probabilities back over the scores it has read, as TWO bfloat16 terms
+//               (P = hi + lo, so the softmax stays a float32 quantity as far as the result can
+//               tell).  P is the A operand of O += P V straight from tensor memory, and O
+//               stays in tensor memory over all tiles.  The maximum a row's exponentials are
+//               taken against is only raised when a tile exceeds it by more than 2^8 (any
+//               fixed reference gives the same quotient; float32 has the range), so the pass
+//               over O that a new maximum costs is rare.
 //
 // Operand layouts.  Nothing is swizzled: every operand is made of "core matrices" of 8 rows
 // x 16 bytes (128 contiguous bytes), which is exactly what a page block of the cache is made
@@ -25,8 +29,8 @@
 // For S = Q K^T the keys are the N operand (K-major), and one product should cover all 64
 // keys of the tile, which needs one stride from 8 keys to the next across pages: a warp
 // rewrites the tile as [piece][64 keys][16 bytes] (products of one page each measured 4 times
-// slower, and so did asking the copy engine for each piece column by itself).  Q and P are
-// written to shared memory by the CTA itself in the same core-matrix form.
+// slower, and so did asking the copy engine for each piece column by itself).  Q is written
+// to shared memory by the CTA itself in the same core-matrix form.
 //
 // A query row's result depends on its own position only (tiles are anchored at key 0, rows do
 // not interact).  Requests with fewer than `min_query_len` tokens are left to
@@ -42,7 +46,8 @@ constexpr int K_STAGES = 2;    // key tiles in shared memory as they land (rewri
 constexpr int V_STAGES = 4;    // value tiles in shared memory (held until their product is done)
 constexpr int THREADS = 224;
 constexpr int GROUP_STRIDE = 128;             // bytes from one 8-row core matrix to the next row group
-constexpr int CHUNK_STRIDE = BLOCK_M * 16;    // bytes from one 16-byte column of Q or P to the next
+constexpr float RAISE_MAXIMUM_BY = 8.0f;      // log2 units a tile must exceed a row's reference by
+constexpr int CHUNK_STRIDE = BLOCK_M * 16;    // bytes from one 16-byte column of Q to the next
 
 struct TcPrefillArgs {
   const __nv_bfloat16* q;
@@ -70,11 +75,10 @@ template <int D>
 struct TcConfig {
   static constexpr int kQBytes = BLOCK_M * D * 2;
   static constexpr int kHalfBytes = BLOCK_N * D * 2;          // keys (or values) of a tile
-  static constexpr int kPBytes = BLOCK_M * BLOCK_N * 2;       // one term of the probabilities
-  static constexpr int kSmemBytes =
-      kQBytes + (K_STAGES + V_STAGES + 2) * kHalfBytes + 2 * kPBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kQBytes + (K_STAGES + V_STAGES + 2) * kHalfBytes + 1024 + 256;
   static constexpr int kScoreColumns = BLOCK_N;               // per score buffer (two of them)
-  static constexpr int kOutputColumn = 2 * BLOCK_N;           // O_tile starts here
+  static constexpr int kLowTermColumn = BLOCK_N / 2;          // P: hi in columns [0, 32), lo after
+  static constexpr int kOutputColumn = 2 * BLOCK_N;           // O starts here
   static constexpr int kTmemColumns = 256;                    // 2 * 64 + D <= 256
 };
 
@@ -125,15 +129,13 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   uint8_t* k_stages = q_tile + Config::kQBytes;
   uint8_t* v_stages = k_stages + K_STAGES * Config::kHalfBytes;
   uint8_t* keys_by_piece = v_stages + V_STAGES * Config::kHalfBytes;      // [2]: see warp 6
-  uint8_t* p_hi = keys_by_piece + 2 * Config::kHalfBytes;
-  uint8_t* p_lo = p_hi + Config::kPBytes;
-  uint64_t* k_full = reinterpret_cast<uint64_t*>(p_lo + Config::kPBytes);
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(keys_by_piece + 2 * Config::kHalfBytes);
   uint64_t* k_empty = k_full + K_STAGES;
   uint64_t* v_full = k_empty + K_STAGES;
   uint64_t* v_empty = v_full + V_STAGES;
   uint64_t* s_full = v_empty + V_STAGES;      // [2]
-  uint64_t* p_full = s_full + 2;
-  uint64_t* o_full = p_full + 1;
+  uint64_t* p_full = s_full + 2;              // [2]
+  uint64_t* o_full = p_full + 2;
   uint64_t* k_ready = o_full + 1;             // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(k_ready + 2);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -165,7 +167,8 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
-    mbar_init(p_full, 4);       // one arrival per softmax warp
+    mbar_init(&p_full[0], 4);   // one arrival per softmax warp
+    mbar_init(&p_full[1], 4);
     mbar_init(o_full, 1);
     mbar_init(&k_ready[0], 1);
     mbar_init(&k_ready[1], 1);
@@ -306,8 +309,6 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       constexpr uint32_t kKeyBufferStep = Config::kHalfBytes >> 4;
       // values: MN-major, the next 8 keys are 128 bytes on, the next 8 coordinates one piece on
       const uint64_t desc_v0 = make_smem_desc_plain(smem_u32(v_stages), GROUP_STRIDE, piece_stride);
-      const uint64_t desc_hi0 = make_smem_desc_plain(smem_u32(p_hi), CHUNK_STRIDE, GROUP_STRIDE);
-      const uint64_t desc_lo0 = make_smem_desc_plain(smem_u32(p_lo), CHUNK_STRIDE, GROUP_STRIDE);
       constexpr uint32_t kStageStep = Config::kHalfBytes >> 4;
       constexpr uint32_t kChunkPairStep = (2 * CHUNK_STRIDE) >> 4;      // 16 coordinates of Q or P on
       constexpr uint32_t kKeyPiecePairStep = (2 * BLOCK_N * 16) >> 4;   // 16 coordinates of the keys on
@@ -339,9 +340,8 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         value_step[g] = ((key / page_size) * page_bytes + (key % page_size) * 16) >> 4;
       }
       for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
-        // the probabilities of this tile are in shared memory (and the softmax warps have
-        // read its scores and the previous partial output)
-        if (!mbar_wait(p_full, static_cast<uint32_t>(tile) & 1u)) {
+        // the probabilities of this tile lie where its scores were
+        if (!mbar_wait(&p_full[tile & 1], static_cast<uint32_t>(tile >> 1) & 1u)) {
           atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
           *failed = 1;
           break;
@@ -355,16 +355,17 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         }
         const uint64_t desc_v = desc_v0 + s * kStageStep;
         const uint32_t target = tmem_base + Config::kOutputColumn;
-        // O_tile = P V_tile: 16 keys per product, the hi and the lo term of P against them
+        const uint32_t p_hi = tmem_base + (tile & 1) * Config::kScoreColumns;
+        const uint32_t p_lo = p_hi + Config::kLowTermColumn;
+        // O += P V_tile: 16 keys (8 columns of P) per product, the hi and the lo term of P
 #pragma unroll
         for (int g = 0; g < BLOCK_N / 16; ++g) {
-          umma_bf16(target, desc_hi0 + g * kChunkPairStep, desc_v + value_step[g], idesc_output,
-                    g > 0 ? 1u : 0u);
-          umma_bf16(target, desc_lo0 + g * kChunkPairStep, desc_v + value_step[g], idesc_output,
-                    1u);
+          umma_bf16_a_tmem(target, p_hi + g * 8, desc_v + value_step[g], idesc_output,
+                           (tile > 0 || g > 0) ? 1u : 0u);
+          umma_bf16_a_tmem(target, p_lo + g * 8, desc_v + value_step[g], idesc_output, 1u);
         }
         umma_commit(&v_empty[s]);       // the stage may be refilled
-        umma_commit(o_full);            // O_tile is complete, P may be overwritten
+        umma_commit(o_full);            // O holds this tile; its P has been read
         if (tile + 2 < n_tiles) scores(tile + 2);
       }
     }
@@ -374,11 +375,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const int q_position = context + row0 + row;      // the last key this row sees
-    const uint32_t p_offset = (row >> 3) * GROUP_STRIDE + (row & 7) * 16;
-    float o_acc[D];
-#pragma unroll
-    for (int d = 0; d < D; ++d) o_acc[d] = 0.0f;
-    float row_max = -INFINITY;      // in units of log2(e), like the scores
+    float row_max = -INFINITY;      // the reference of this row's exponentials, in log2 units
     float row_sum = 0.0f;
     const float scale_log2 = a.scale * 1.4426950408889634f;
     bool ok = true;
@@ -393,33 +390,18 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       }
       return done;
     };
-    // O_tile of the previous tile (same maximum as o_acc) is added to the output row
-    auto add_partial_output = [&]() {
-#pragma unroll
-      for (int d0 = 0; d0 < D; d0 += 32) {
-        uint32_t r0[16], r1[16];
-        tmem_load16_issue(lane_base + Config::kOutputColumn + d0, r0);
-        tmem_load16_issue(lane_base + Config::kOutputColumn + d0 + 16, r1);
-        tmem_load_wait();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          o_acc[d0 + i] += __uint_as_float(r0[i]);
-          o_acc[d0 + 16 + i] += __uint_as_float(r1[i]);
-        }
-      }
-    };
 
     for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
       ok = wait_for(&s_full[tile & 1], static_cast<uint32_t>(tile >> 1) & 1u);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t score_base = lane_base + (tile & 1) * Config::kScoreColumns;
       // ---- this row's scores of the tile, in units of log2(e) so that exp is one ex2
       float p[BLOCK_N];
       {
         uint32_t r[4][16];
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-          tmem_load16_issue(lane_base + (tile & 1) * Config::kScoreColumns + c * 16, r[c]);
+        for (int c = 0; c < 4; ++c) tmem_load16_issue(score_base + c * 16, r[c]);
         tmem_load_wait();
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -438,52 +420,66 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
 #pragma unroll
         for (int u = 0; u < 4; ++u) part_max[u] = fmaxf(part_max[u], p[i + u]);
       const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
-      // key 0 is visible to every row, so the maximum is finite from the first tile on
-      const float new_max = fmaxf(row_max, tile_max);
-      const float correction = row_max == -INFINITY ? 0.0f : fast_exp2(row_max - new_max);
-      row_max = new_max;
+      // key 0 is visible to every row, so the reference is finite from the first tile on
+      if (tile == 0) {
+        row_max = tile_max;
+      } else if (__any_sync(0xffffffffu, tile_max > row_max + RAISE_MAXIMUM_BY)) {
+        // ---- a new reference: what O and the sum hold was taken against the old one.  The
+        // product of the previous tile must have landed; the product of this tile waits for
+        // this warp's arrival below.
+        const float new_max = fmaxf(row_max, tile_max);
+        const float correction = fast_exp2(row_max - new_max);
+        row_max = new_max;
+        row_sum *= correction;
+        // (the scores of this tile prove the product of tile - 2 done, so the barrier is in
+        // the phase of tile - 1 or past it)
+        ok = wait_for(o_full, static_cast<uint32_t>(tile - 1) & 1u);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int d0 = 0; d0 < D; d0 += 32) {
+          uint32_t r0[16], r1[16];
+          tmem_load16_issue(lane_base + Config::kOutputColumn + d0, r0);
+          tmem_load16_issue(lane_base + Config::kOutputColumn + d0 + 16, r1);
+          tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            r0[i] = __float_as_uint(__uint_as_float(r0[i]) * correction);
+            r1[i] = __float_as_uint(__uint_as_float(r1[i]) * correction);
+          }
+          tmem_store16_raw(lane_base + Config::kOutputColumn + d0, r0);
+          tmem_store16_raw(lane_base + Config::kOutputColumn + d0 + 16, r1);
+        }
+      }
       float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int i = 0; i < BLOCK_N; i += 4)
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          p[i + u] = fast_exp2(p[i + u] - new_max);
+          p[i + u] = fast_exp2(p[i + u] - row_max);
           part_sum[u] += p[i + u];
         }
-      row_sum = row_sum * correction + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
+      row_sum += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
 
-      // ---- the previous tile's partial output, then the new maximum's correction
-      if (tile > 0) {
-        ok = wait_for(o_full, static_cast<uint32_t>(tile - 1) & 1u);
-        if (!ok) break;
-        tc_fence_after();
-        add_partial_output();
-      }
-      if (__any_sync(0xffffffffu, correction != 1.0f)) {
+      // ---- P = hi + lo over the scores just read: hi is p cut to its upper 16 bits (a
+      // bfloat16 exactly), lo is p - hi (exact in float32) cut the same way: together 16
+      // bits of p.  Two keys per column, the earlier key in the lower half.
 #pragma unroll
-        for (int d = 0; d < D; ++d) o_acc[d] *= correction;
-      }
-
-      // ---- P = hi + lo into shared memory (the product that read the old P is done: its
-      // commit is what o_full waited for).  hi is p cut to its upper 16 bits (a bfloat16
-      // exactly), lo is p - hi (exact in float32) cut the same way: together 16 bits of p.
+      for (int c = 0; c < 2; ++c) {
+        uint32_t hi[16], lo[16];
 #pragma unroll
-      for (int c = 0; c < BLOCK_N / 8; ++c) {
-        uint4 hi, lo;
-        uint32_t* hi_words = reinterpret_cast<uint32_t*>(&hi);
-        uint32_t* lo_words = reinterpret_cast<uint32_t*>(&lo);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t x0 = __float_as_uint(p[c * 8 + 2 * i]);
-          const uint32_t x1 = __float_as_uint(p[c * 8 + 2 * i + 1]);
-          const float rest0 = p[c * 8 + 2 * i] - __uint_as_float(x0 & 0xffff0000u);
-          const float rest1 = p[c * 8 + 2 * i + 1] - __uint_as_float(x1 & 0xffff0000u);
-          hi_words[i] = __byte_perm(x0, x1, 0x7632);
-          lo_words[i] = __byte_perm(__float_as_uint(rest0), __float_as_uint(rest1), 0x7632);
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = p[c * 32 + 2 * i], p1 = p[c * 32 + 2 * i + 1];
+          const uint32_t x0 = __float_as_uint(p0), x1 = __float_as_uint(p1);
+          const float rest0 = p0 - __uint_as_float(x0 & 0xffff0000u);
+          const float rest1 = p1 - __uint_as_float(x1 & 0xffff0000u);
+          hi[i] = __byte_perm(x0, x1, 0x7632);
+          lo[i] = __byte_perm(__float_as_uint(rest0), __float_as_uint(rest1), 0x7632);
         }
-        *reinterpret_cast<uint4*>(p_hi + c * CHUNK_STRIDE + p_offset) = hi;
-        *reinterpret_cast<uint4*>(p_lo + c * CHUNK_STRIDE + p_offset) = lo;
+        tmem_store16_raw(score_base + c * 16, hi);
+        tmem_store16_raw(score_base + Config::kLowTermColumn + c * 16, lo);
       }
+      tmem_store_wait();
 
       // ---- value rows behind the last key hold whatever the pages (or an earlier tile)
       // left there; a NaN would survive a zero probability, so they are cleared
@@ -500,31 +496,42 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
                                       (piece * page_size + key % page_size) * 16) =
                 make_uint4(0u, 0u, 0u, 0u);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[tile & 1]);
     }
 
     if (ok && !*failed) {
-      ok = wait_for(o_full, static_cast<uint32_t>(n_tiles - 1) & 1u);
+      // o_full completes a phase per tile and this warp has not followed them all: the scores
+      // of the last tile prove the product of tile n-3 done, so wait for n-2, then for n-1
+      if (n_tiles > 1) ok = wait_for(o_full, static_cast<uint32_t>(n_tiles - 2) & 1u);
+      if (ok) ok = wait_for(o_full, static_cast<uint32_t>(n_tiles - 1) & 1u);
       if (ok) {
         tc_fence_after();
-        add_partial_output();
-        if (row < rows_here) {
-          const float inverse = 1.0f / row_sum;
-          __nv_bfloat16* out = a.out + static_cast<size_t>(q_begin + row0 + row) * a.ldo +
-                               static_cast<size_t>(head) * D;
+        const float inverse = 1.0f / row_sum;
+        __nv_bfloat16* out = a.out + static_cast<size_t>(q_begin + row0 + row) * a.ldo +
+                             static_cast<size_t>(head) * D;
 #pragma unroll
-          for (int d = 0; d < D; d += 8) {
-            uint4 packed;
-            __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+        for (int d0 = 0; d0 < D; d0 += 32) {
+          uint32_t r[2][16];
+          tmem_load16_issue(lane_base + Config::kOutputColumn + d0, r[0]);
+          tmem_load16_issue(lane_base + Config::kOutputColumn + d0 + 16, r[1]);
+          tmem_load_wait();
+          if (row < rows_here) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              pairs[i] = __floats2bfloat162_rn(o_acc[d + 2 * i] * inverse,
-                                               o_acc[d + 2 * i + 1] * inverse);
-            *reinterpret_cast<uint4*>(out + d) = packed;
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int d = 0; d < 16; d += 8) {
+                uint4 packed;
+                __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  pairs[i] = __floats2bfloat162_rn(__uint_as_float(r[h][d + 2 * i]) * inverse,
+                                                   __uint_as_float(r[h][d + 2 * i + 1]) * inverse);
+                *reinterpret_cast<uint4*>(out + d0 + h * 16 + d) = packed;
+              }
           }
         }
       }
