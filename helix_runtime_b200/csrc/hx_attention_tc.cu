@@ -32,6 +32,11 @@
 // slower, and so did asking the copy engine for each piece column by itself).  Q is written
 // to shared memory by the CTA itself in the same core-matrix form.
 //
+// What bounds the kernel: a tcgen05.mma with M = 128 takes the tensor pipe about 100 cycles
+// whatever its N from 16 to 128 (measured with one and with two issuing threads), so the time
+// goes with the NUMBER of products: 8 for the scores of 64 keys and 8 for their part of the
+// output (4 steps of 16 keys, hi and lo), about 0.85 us per tile of a 1.3 us tile period.
+//
 // A query row's result depends on its own position only (tiles are anchored at key 0, rows do
 // not interact).  Requests with fewer than `min_query_len` tokens are left to
 // hx_paged_attention.  Every wait is bounded; a wait that runs out sets a status bit, and
@@ -105,15 +110,15 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   // which request and which 128-row tile of it is this CTA?
   int request = -1, tile_in_request = 0;
   {
-    int remaining = blockIdx.x;
+    int remaining = blockIdx.y;
     for (int r = 0; r < a.requests; ++r) {
       const int length = a.request_start[r + 1] - a.request_start[r];
       if (length < a.min_query_len) continue;
       const int tiles = (length + BLOCK_M - 1) / BLOCK_M;
       if (remaining < tiles) {
         request = r;
-        // the last rows of a request see the most keys: their CTAs are started first, so the
-        // short ones fill the gaps at the end
+        // the last rows of a request see the most keys: their CTAs are started first (the grid
+        // is walked heads first, then tiles), so the short ones fill the gaps at the end
         tile_in_request = tiles - 1 - remaining;
         break;
       }
@@ -142,7 +147,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int head = blockIdx.y;
+  const int head = blockIdx.x;
   const int kv_head = head / (a.heads / a.kv_heads);
   const int q_begin = a.request_start[request];
   const int q_len = a.request_start[request + 1] - q_begin;
@@ -274,20 +279,28 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       // writes 512 bytes; from piece to piece both move by a constant
       const uint32_t source = smem_u32(k_stages + (tile % K_STAGES) * Config::kHalfBytes);
       const uint32_t target = smem_u32(keys_by_piece + (tile & 1) * Config::kHalfBytes) + lane * 16;
+      // eight pieces at a time: all their loads are in flight before the first store
 #pragma unroll
-      for (int piece = 0; piece < D / 8; ++piece) {
-        uint4 low, high;
-        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(low.x), "=r"(low.y), "=r"(low.z), "=r"(low.w)
-                     : "r"(source + source_low + piece * piece_stride));
-        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(high.x), "=r"(high.y), "=r"(high.z), "=r"(high.w)
-                     : "r"(source + source_high + piece * piece_stride));
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(target + piece * (BLOCK_N * 16)),
-                     "r"(low.x), "r"(low.y), "r"(low.z), "r"(low.w) : "memory");
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(
-                         target + piece * (BLOCK_N * 16) + 512),
-                     "r"(high.x), "r"(high.y), "r"(high.z), "r"(high.w) : "memory");
+      for (int piece0 = 0; piece0 < D / 8; piece0 += 8) {
+        uint4 low[8], high[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(low[i].x), "=r"(low[i].y), "=r"(low[i].z), "=r"(low[i].w)
+                       : "r"(source + source_low + (piece0 + i) * piece_stride));
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(high[i].x), "=r"(high[i].y), "=r"(high[i].z), "=r"(high[i].w)
+                       : "r"(source + source_high + (piece0 + i) * piece_stride));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(
+                           target + (piece0 + i) * (BLOCK_N * 16)),
+                       "r"(low[i].x), "r"(low[i].y), "r"(low[i].z), "r"(low[i].w) : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(
+                           target + (piece0 + i) * (BLOCK_N * 16) + 512),
+                       "r"(high[i].x), "r"(high[i].y), "r"(high[i].z), "r"(high[i].w) : "memory");
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
@@ -561,7 +574,7 @@ int launch(const TcPrefillArgs& a, int tiles, cudaStream_t stream) {
     }
     configured = true;
   }
-  hx_launch(prefill_attention_tc_kernel<D>, dim3(tiles, a.heads), THREADS, Config::kSmemBytes,
+  hx_launch(prefill_attention_tc_kernel<D>, dim3(a.heads, tiles), THREADS, Config::kSmemBytes,
             stream, a);
   return HX_OK;
 }
@@ -589,7 +602,7 @@ HX_API int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache,
              "64 and 128, pages of 16, 32 or 64)", head_dim, page_size);
   HX_REQUIRE(requests >= 0 && tile_bound >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
              "hx_prefill_attention_tc: bad sizes");
-  HX_REQUIRE(heads <= 65535, "hx_prefill_attention_tc: too many heads");
+  HX_REQUIRE(tile_bound <= 65535, "hx_prefill_attention_tc: too many query tiles");
   HX_REQUIRE(num_pages > 0 && table_stride > 0, "hx_prefill_attention_tc: bad cache geometry");
   HX_REQUIRE(status != nullptr, "hx_prefill_attention_tc: status word missing");
   HX_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
