@@ -5,9 +5,10 @@
 //
 // One CTA takes 128 consecutive query tokens of one request and one head and walks the
 // request's keys in tiles of 64, anchored at key 0.  Warp roles:
-//   warp 0      one lane asks for the pages of each tile: the keys of a (page, head) are one
-//               contiguous block of the cache and so are its values, so a tile is a handful
-//               of bulk copies (cp.async.bulk counted on an mbarrier) into a ring of stages;
+//   warps 0, 7  one lane of each asks for the pages of each tile, warp 0 for the keys and
+//               warp 7 for the values: the keys of a (page, head) are one contiguous block of
+//               the cache and so are its values, so a tile is a handful of bulk copies
+//               (cp.async.bulk counted on an mbarrier) into a ring of stages;
 //   warp 1      one lane issues the products: S = Q K^T into one of two score buffers in
 //               tensor memory (running two tiles ahead of the softmax), then O_tile = P V;
 //   warp 6      rewrites the keys of a landed tile piece-major over all 64 keys (see below);
@@ -49,7 +50,8 @@ constexpr int BLOCK_M = 128;   // query rows per CTA (the MMA's M)
 constexpr int BLOCK_N = 64;    // keys per tile
 constexpr int K_STAGES = 2;    // key tiles in shared memory as they land (rewritten at once)
 constexpr int V_STAGES = 4;    // value tiles in shared memory (held until their product is done)
-constexpr int THREADS = 224;
+constexpr int S_BUFFERS = 3;   // score tiles in tensor memory: the score products run this far ahead
+constexpr int THREADS = 288;
 constexpr int GROUP_STRIDE = 128;             // bytes from one 8-row core matrix to the next row group
 constexpr float RAISE_MAXIMUM_BY = 8.0f;      // log2 units a tile must exceed a row's reference by
 constexpr int CHUNK_STRIDE = BLOCK_M * 16;    // bytes from one 16-byte column of Q to the next
@@ -80,11 +82,12 @@ template <int D>
 struct TcConfig {
   static constexpr int kQBytes = BLOCK_M * D * 2;
   static constexpr int kHalfBytes = BLOCK_N * D * 2;          // keys (or values) of a tile
-  static constexpr int kSmemBytes = kQBytes + (K_STAGES + V_STAGES + 2) * kHalfBytes + 1024 + 256;
-  static constexpr int kScoreColumns = BLOCK_N;               // per score buffer (two of them)
+  static constexpr int kSmemBytes =
+      kQBytes + (K_STAGES + V_STAGES + S_BUFFERS) * kHalfBytes + 1024 + 256;
+  static constexpr int kScoreColumns = BLOCK_N;               // per score buffer
   static constexpr int kLowTermColumn = BLOCK_N / 2;          // P: hi in columns [0, 32), lo after
-  static constexpr int kOutputColumn = 2 * BLOCK_N;           // O starts here
-  static constexpr int kTmemColumns = 256;                    // 2 * 64 + D <= 256
+  static constexpr int kOutputColumn = S_BUFFERS * BLOCK_N;   // O starts here
+  static constexpr int kTmemColumns = 512;                    // 3 * 64 + D = 320, a power of two
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -133,16 +136,16 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   uint8_t* q_tile = smem;
   uint8_t* k_stages = q_tile + Config::kQBytes;
   uint8_t* v_stages = k_stages + K_STAGES * Config::kHalfBytes;
-  uint8_t* keys_by_piece = v_stages + V_STAGES * Config::kHalfBytes;      // [2]: see warp 6
-  uint64_t* k_full = reinterpret_cast<uint64_t*>(keys_by_piece + 2 * Config::kHalfBytes);
+  uint8_t* keys_by_piece = v_stages + V_STAGES * Config::kHalfBytes;      // [S_BUFFERS]: see warp 6
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(keys_by_piece + S_BUFFERS * Config::kHalfBytes);
   uint64_t* k_empty = k_full + K_STAGES;
   uint64_t* v_full = k_empty + K_STAGES;
   uint64_t* v_empty = v_full + V_STAGES;
-  uint64_t* s_full = v_empty + V_STAGES;      // [2]
-  uint64_t* p_full = s_full + 2;              // [2]
-  uint64_t* o_full = p_full + 2;
-  uint64_t* k_ready = o_full + 1;             // [2]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(k_ready + 2);
+  uint64_t* s_full = v_empty + V_STAGES;      // [S_BUFFERS]
+  uint64_t* p_full = s_full + S_BUFFERS;      // [S_BUFFERS]
+  uint64_t* o_full = p_full + S_BUFFERS;      // [S_BUFFERS]: by tile, so that a phase is never skipped
+  uint64_t* k_ready = o_full + S_BUFFERS;     // [S_BUFFERS]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(k_ready + S_BUFFERS);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -170,13 +173,12 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    mbar_init(&s_full[0], 1);
-    mbar_init(&s_full[1], 1);
-    mbar_init(&p_full[0], 4);   // one arrival per softmax warp
-    mbar_init(&p_full[1], 4);
-    mbar_init(o_full, 1);
-    mbar_init(&k_ready[0], 1);
-    mbar_init(&k_ready[1], 1);
+    for (int b = 0; b < S_BUFFERS; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&p_full[b], 4);   // one arrival per softmax warp
+      mbar_init(&o_full[b], 1);
+      mbar_init(&k_ready[b], 1);
+    }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -201,9 +203,18 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 7) {
     // ------------------------------------------------------------ page requests
+    // Warp 0 asks for keys, warp 7 for values, each as far ahead as its own ring allows: the
+    // keys of a tile are wanted S_BUFFERS tiles before its values (they are rewritten, then
+    // multiplied, then the softmax runs), and one ring must not hold up the other.
     if (lane == 0) {
+      const bool values = warp == 7;
+      const int stages = values ? V_STAGES : K_STAGES;
+      uint64_t* full = values ? v_full : k_full;
+      uint64_t* empty = values ? v_empty : k_empty;
+      uint8_t* ring = values ? v_stages : k_stages;
+      const uint8_t* cache = reinterpret_cast<const uint8_t*>(values ? a.v_cache : a.k_cache);
       const int* table = a.block_tables +
                          static_cast<size_t>(a.request_table_row[request]) * a.table_stride;
       const int last_page = last_key / page_size;
@@ -217,10 +228,9 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       int pages[4], next_pages[4];
       pages_of(0, pages);
       for (int tile = 0; tile < n_tiles && !*failed; ++tile) {
-        if (tile + 1 < n_tiles) pages_of(tile + 1, next_pages);      // in flight during the waits
-        const int ks = tile % K_STAGES, vs = tile % V_STAGES;
-        if (!mbar_wait(&k_empty[ks], (static_cast<uint32_t>(tile / K_STAGES) & 1u) ^ 1u) ||
-            !mbar_wait(&v_empty[vs], (static_cast<uint32_t>(tile / V_STAGES) & 1u) ^ 1u)) {
+        if (tile + 1 < n_tiles) pages_of(tile + 1, next_pages);      // in flight during the wait
+        const int stage = tile % stages;
+        if (!mbar_wait(&empty[stage], (static_cast<uint32_t>(tile / stages) & 1u) ^ 1u)) {
           atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
           *failed = 1;
           break;
@@ -234,18 +244,13 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
           }
           if (pages[p] >= 0) expected += page_bytes;
         }
-        mbar_expect_tx(&k_full[ks], expected);
-        mbar_expect_tx(&v_full[vs], expected);
-        const uint32_t k_base = smem_u32(k_stages + ks * Config::kHalfBytes);
-        const uint32_t v_base = smem_u32(v_stages + vs * Config::kHalfBytes);
+        mbar_expect_tx(&full[stage], expected);
+        const uint32_t base = smem_u32(ring + stage * Config::kHalfBytes);
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
           if (pages[p] >= 0) {
             const size_t block = (static_cast<size_t>(pages[p]) * a.kv_heads + kv_head) * page_bytes;
-            bulk_copy(k_base + p * page_bytes, reinterpret_cast<const uint8_t*>(a.k_cache) + block,
-                      page_bytes, &k_full[ks]);
-            bulk_copy(v_base + p * page_bytes, reinterpret_cast<const uint8_t*>(a.v_cache) + block,
-                      page_bytes, &v_full[vs]);
+            bulk_copy(base + p * page_bytes, cache + block, page_bytes, &full[stage]);
           }
         }
 #pragma unroll
@@ -265,9 +270,10 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
       if (lane == 0) {
         ok = mbar_wait(&k_full[tile % K_STAGES], static_cast<uint32_t>(tile / K_STAGES) & 1u);
-        // the product that read this buffer two tiles ago is done when its scores are
-        if (ok && tile >= 2)
-          ok = mbar_wait(&s_full[tile & 1], static_cast<uint32_t>((tile - 2) >> 1) & 1u);
+        // the product that read this buffer S_BUFFERS tiles ago is done when its scores are
+        if (ok && tile >= S_BUFFERS)
+          ok = mbar_wait(&s_full[tile % S_BUFFERS],
+                         static_cast<uint32_t>((tile - S_BUFFERS) / S_BUFFERS) & 1u);
         if (!ok) {
           atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
           *failed = 1;
@@ -278,7 +284,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       // piece c of keys lane and lane + 32: the two reads are a page apart at most, the two
       // writes 512 bytes; from piece to piece both move by a constant
       const uint32_t source = smem_u32(k_stages + (tile % K_STAGES) * Config::kHalfBytes);
-      const uint32_t target = smem_u32(keys_by_piece + (tile & 1) * Config::kHalfBytes) + lane * 16;
+      const uint32_t target = smem_u32(keys_by_piece + (tile % S_BUFFERS) * Config::kHalfBytes) + lane * 16;
       // eight pieces at a time: all their loads are in flight before the first store
 #pragma unroll
       for (int piece0 = 0; piece0 < D / 8; piece0 += 8) {
@@ -305,7 +311,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&k_ready[tile & 1]);
+        mbar_arrive(&k_ready[tile % S_BUFFERS]);
         mbar_arrive(&k_empty[tile % K_STAGES]);      // the landed copy may be overwritten
       }
     }
@@ -313,38 +319,42 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     // ---------------------------------------------------------------- products
     if (lane == 0) {
       constexpr uint32_t idesc_scores = make_idesc(BLOCK_M, BLOCK_N);
-      constexpr uint32_t idesc_output = make_idesc_b_mn_major(BLOCK_M, D);
       // Descriptors differ from product to product only in their start address (the low 14
       // bits, in units of 16 bytes): build one of each kind and add offsets.
       const uint64_t desc_q0 = make_smem_desc_plain(smem_u32(q_tile), CHUNK_STRIDE, GROUP_STRIDE);
       const uint64_t desc_k0 =
           make_smem_desc_plain(smem_u32(keys_by_piece), BLOCK_N * 16, GROUP_STRIDE);
       constexpr uint32_t kKeyBufferStep = Config::kHalfBytes >> 4;
-      // values: MN-major, the next 8 keys are 128 bytes on, the next 8 coordinates one piece on
-      const uint64_t desc_v0 = make_smem_desc_plain(smem_u32(v_stages), GROUP_STRIDE, piece_stride);
-      constexpr uint32_t kStageStep = Config::kHalfBytes >> 4;
       constexpr uint32_t kChunkPairStep = (2 * CHUNK_STRIDE) >> 4;      // 16 coordinates of Q or P on
       constexpr uint32_t kKeyPiecePairStep = (2 * BLOCK_N * 16) >> 4;   // 16 coordinates of the keys on
-      bool ok = true;
-      // S[tile & 1] = Q K_tile^T: one product of 64 keys per 16 coordinates
-      auto scores = [&](int tile) {
-        if (!mbar_wait(&k_ready[tile & 1], static_cast<uint32_t>(tile >> 1) & 1u)) {
+      // S[tile % S_BUFFERS] = Q K_tile^T: one product of 64 keys per 16 coordinates.  The
+      // buffer held the probabilities of tile - S_BUFFERS, which their product must have read.
+      for (int tile = 0; tile < n_tiles && !*failed; ++tile) {
+        const int b = tile % S_BUFFERS;
+        if (!mbar_wait(&k_ready[b], static_cast<uint32_t>(tile / S_BUFFERS) & 1u) ||
+            (tile >= S_BUFFERS &&
+             !mbar_wait(&o_full[b], static_cast<uint32_t>((tile - S_BUFFERS) / S_BUFFERS) & 1u))) {
           atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
           *failed = 1;
-          ok = false;
-          return;
+          break;
         }
         tc_fence_after();
-        const uint64_t desc_k = desc_k0 + (tile & 1) * kKeyBufferStep;
-        const uint32_t target = tmem_base + (tile & 1) * Config::kScoreColumns;
+        const uint64_t desc_k = desc_k0 + b * kKeyBufferStep;
+        const uint32_t target = tmem_base + b * Config::kScoreColumns;
 #pragma unroll
         for (int k = 0; k < kDSteps; ++k)
           umma_bf16(target, desc_q0 + k * kChunkPairStep, desc_k + k * kKeyPiecePairStep,
                     idesc_scores, k > 0 ? 1u : 0u);
-        umma_commit(&s_full[tile & 1]);
-      };
-      scores(0);
-      if (ok && n_tiles > 1) scores(1);
+        umma_commit(&s_full[b]);
+      }
+    }
+  } else if (warp == 8) {
+    // ----------------------------------------------------------- output products
+    if (lane == 0) {
+      constexpr uint32_t idesc_output = make_idesc_b_mn_major(BLOCK_M, D);
+      // values: MN-major, the next 8 keys are 128 bytes on, the next 8 coordinates one piece on
+      const uint64_t desc_v0 = make_smem_desc_plain(smem_u32(v_stages), GROUP_STRIDE, piece_stride);
+      constexpr uint32_t kStageStep = Config::kHalfBytes >> 4;
       // where the 16 keys of each product of P V start inside a stage's value half
       uint32_t value_step[BLOCK_N / 16];
 #pragma unroll
@@ -352,23 +362,19 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         const int key = g * 16;
         value_step[g] = ((key / page_size) * page_bytes + (key % page_size) * 16) >> 4;
       }
-      for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
+      for (int tile = 0; tile < n_tiles && !*failed; ++tile) {
         // the probabilities of this tile lie where its scores were
-        if (!mbar_wait(&p_full[tile & 1], static_cast<uint32_t>(tile >> 1) & 1u)) {
+        const int s = tile % V_STAGES;
+        if (!mbar_wait(&p_full[tile % S_BUFFERS], static_cast<uint32_t>(tile / S_BUFFERS) & 1u) ||
+            !mbar_wait(&v_full[s], static_cast<uint32_t>(tile / V_STAGES) & 1u)) {
           atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
           *failed = 1;
           break;
         }
         tc_fence_after();
-        const int s = tile % V_STAGES;
-        if (!mbar_wait(&v_full[s], static_cast<uint32_t>(tile / V_STAGES) & 1u)) {
-          atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
-          *failed = 1;
-          break;
-        }
         const uint64_t desc_v = desc_v0 + s * kStageStep;
         const uint32_t target = tmem_base + Config::kOutputColumn;
-        const uint32_t p_hi = tmem_base + (tile & 1) * Config::kScoreColumns;
+        const uint32_t p_hi = tmem_base + (tile % S_BUFFERS) * Config::kScoreColumns;
         const uint32_t p_lo = p_hi + Config::kLowTermColumn;
         // O += P V_tile: 16 keys (8 columns of P) per product, the hi and the lo term of P
 #pragma unroll
@@ -377,9 +383,8 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
                            (tile > 0 || g > 0) ? 1u : 0u);
           umma_bf16_a_tmem(target, p_lo + g * 8, desc_v + value_step[g], idesc_output, 1u);
         }
-        umma_commit(&v_empty[s]);       // the stage may be refilled
-        umma_commit(o_full);            // O holds this tile; its P has been read
-        if (tile + 2 < n_tiles) scores(tile + 2);
+        umma_commit(&v_empty[s]);                    // the stage may be refilled
+        umma_commit(&o_full[tile % S_BUFFERS]);      // O holds this tile; its P has been read
       }
     }
   } else {
@@ -405,10 +410,10 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     };
 
     for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
-      ok = wait_for(&s_full[tile & 1], static_cast<uint32_t>(tile >> 1) & 1u);
+      ok = wait_for(&s_full[tile % S_BUFFERS], static_cast<uint32_t>(tile / S_BUFFERS) & 1u);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t score_base = lane_base + (tile & 1) * Config::kScoreColumns;
+      const uint32_t score_base = lane_base + (tile % S_BUFFERS) * Config::kScoreColumns;
       // ---- this row's scores of the tile, in units of log2(e) so that exp is one ex2
       float p[BLOCK_N];
       {
@@ -444,9 +449,10 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         const float correction = fast_exp2(row_max - new_max);
         row_max = new_max;
         row_sum *= correction;
-        // (the scores of this tile prove the product of tile - 2 done, so the barrier is in
-        // the phase of tile - 1 or past it)
-        ok = wait_for(o_full, static_cast<uint32_t>(tile - 1) & 1u);
+        // (o_full[b] completes a phase for every S_BUFFERS-th tile; its previous phase was
+        // complete before the scores of this tile were started, so no phase is mistaken)
+        ok = wait_for(&o_full[(tile - 1) % S_BUFFERS],
+                      static_cast<uint32_t>((tile - 1) / S_BUFFERS) & 1u);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -513,14 +519,13 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[tile & 1]);
+      if (lane == 0) mbar_arrive(&p_full[tile % S_BUFFERS]);
     }
 
     if (ok && !*failed) {
-      // o_full completes a phase per tile and this warp has not followed them all: the scores
-      // of the last tile prove the product of tile n-3 done, so wait for n-2, then for n-1
-      if (n_tiles > 1) ok = wait_for(o_full, static_cast<uint32_t>(n_tiles - 2) & 1u);
-      if (ok) ok = wait_for(o_full, static_cast<uint32_t>(n_tiles - 1) & 1u);
+      // a commit covers every product issued before it: the last tile's says all are done
+      ok = wait_for(&o_full[(n_tiles - 1) % S_BUFFERS],
+                    static_cast<uint32_t>((n_tiles - 1) / S_BUFFERS) & 1u);
       if (ok) {
         tc_fence_after();
         const float inverse = 1.0f / row_sum;
