@@ -1,26 +1,39 @@
 // Paged causal attention for prompt portions on the 5th-generation tensor cores (tcgen05),
 // bfloat16 storage.  The same computation as hx_attention_mma.cu (the reference materialises
 // a [heads, T, T] score tensor for it, src/attention/cuda.cu:31-77), with both products as
-// tcgen05.mma and the scores and partial outputs in tensor memory.
+// tcgen05.mma and the scores, the probabilities and the output in tensor memory.
 //
 // One CTA takes 128 consecutive query tokens of one request and one head and walks the
-// request's keys in tiles of 64, anchored at key 0.  Warp roles:
-//   warps 0, 7  one lane of each asks for the pages of each tile, warp 0 for the keys and
-//               warp 7 for the values: the keys of a (page, head) are one contiguous block of
+// request's keys in tiles of 64, anchored at key 0.  Tiles with an even number and tiles with
+// an odd number go down two lanes that share nothing but the keys and values in shared memory:
+// each lane has its own thread issuing score products, its own four softmax warps, its own
+// thread issuing output products and its own output accumulator; the two accumulators are
+// combined at the end.  Warp roles:
+//   warps 0, 1  one lane of each asks for the pages of each tile, warp 0 for the keys and
+//               warp 1 for the values: the keys of a (page, head) are one contiguous block of
 //               the cache and so are its values, so a tile is a handful of bulk copies
 //               (cp.async.bulk counted on an mbarrier) into a ring of stages;
-//   warp 1      one lane issues the products: S = Q K^T into one of two score buffers in
-//               tensor memory (running two tiles ahead of the softmax), then O_tile = P V;
-//   warp 6      rewrites the keys of a landed tile piece-major over all 64 keys (see below);
-//   warps 2..5  softmax: thread r owns query row r.  It reads its row of S from tensor memory,
-//               keeps the running maximum and sum in float32 registers and writes the
-//               probabilities back over the scores it has read, as TWO bfloat16 terms
-//               (P = hi + lo, so the softmax stays a float32 quantity as far as the result can
-//               tell).  P is the A operand of O += P V straight from tensor memory, and O
-//               stays in tensor memory over all tiles.  The maximum a row's exponentials are
-//               taken against is only raised when a tile exceeds it by more than 2^8 (any
-//               fixed reference gives the same quotient; float32 has the range), so the pass
-//               over O that a new maximum costs is rare.
+//   warp 2      rewrites the keys of a landed tile piece-major over all 64 keys (see below);
+//   warps 3, 4  one lane each issues S = Q K^T for the even / odd tiles into one of four score
+//               buffers in tensor memory, up to two tiles of its lane ahead of the softmax;
+//   warps 5, 6  one lane each issues O_lane += P V for the even / odd tiles;
+//   warp 7      idles (the softmax groups start at a multiple of four warps, which is what
+//               selects their lanes of tensor memory);
+//   warps 8-11, 12-15  softmax of the even / odd tiles: thread r owns query row r.  It reads
+//               its row of S from tensor memory, keeps the running maximum and sum of its lane
+//               in float32 registers and writes the probabilities back over the scores it has
+//               read, as TWO bfloat16 terms (P = hi + lo, so the softmax stays a float32
+//               quantity as far as the result can tell).  P is the A operand of O += P V
+//               straight from tensor memory.  The maximum a row's exponentials are taken
+//               against is only raised when a tile exceeds it by more than 2^8 (any fixed
+//               reference gives the same quotient; float32 has the range), so the pass over O
+//               that a new maximum costs is rare.
+//
+// Why so many issuing threads: a thread needs 55 ns and more to issue one tcgen05.mma,
+// whatever its size, while the tensor pipe finishes a product of 64 or 128 columns in 30 to
+// 35 ns (measured: one to four threads issuing side by side each keep their own rate until
+// the pipe is full).  And one softmax group alone leaves its four schedulers waiting on the
+// latencies of tensor-memory loads and stores and on the exponential unit.
 //
 // Operand layouts.  Nothing is swizzled: every operand is made of "core matrices" of 8 rows
 // x 16 bytes (128 contiguous bytes), which is exactly what a page block of the cache is made
@@ -29,14 +42,8 @@
 // (a row of a core matrix is 8 consecutive coordinates of one key, its 8 rows are 8 keys).
 // For S = Q K^T the keys are the N operand (K-major), and one product should cover all 64
 // keys of the tile, which needs one stride from 8 keys to the next across pages: a warp
-// rewrites the tile as [piece][64 keys][16 bytes] (products of one page each measured 4 times
-// slower, and so did asking the copy engine for each piece column by itself).  Q is written
-// to shared memory by the CTA itself in the same core-matrix form.
-//
-// What bounds the kernel: a tcgen05.mma with M = 128 takes the tensor pipe about 100 cycles
-// whatever its N from 16 to 128 (measured with one and with two issuing threads), so the time
-// goes with the NUMBER of products: 8 for the scores of 64 keys and 8 for their part of the
-// output (4 steps of 16 keys, hi and lo), about 0.85 us per tile of a 1.3 us tile period.
+// rewrites the tile as [piece][64 keys][16 bytes] (products of one page each are four times
+// as many).  Q is written to shared memory by the CTA itself in the same core-matrix form.
 //
 // A query row's result depends on its own position only (tiles are anchored at key 0, rows do
 // not interact).  Requests with fewer than `min_query_len` tokens are left to
@@ -50,11 +57,13 @@ constexpr int BLOCK_M = 128;   // query rows per CTA (the MMA's M)
 constexpr int BLOCK_N = 64;    // keys per tile
 constexpr int K_STAGES = 2;    // key tiles in shared memory as they land (rewritten at once)
 constexpr int V_STAGES = 4;    // value tiles in shared memory (held until their product is done)
-constexpr int S_BUFFERS = 3;   // score tiles in tensor memory: the score products run this far ahead
-constexpr int THREADS = 288;
+constexpr int S_BUFFERS = 4;   // score tiles in tensor memory and rewritten key tiles: two per lane
+constexpr int THREADS = 512;
+constexpr int WARP_KEYS = 0, WARP_VALUES = 1, WARP_REWRITE = 2, WARP_SCORES = 3, WARP_OUTPUT = 5,
+              WARP_SOFTMAX = 8;
 constexpr int GROUP_STRIDE = 128;             // bytes from one 8-row core matrix to the next row group
-constexpr float RAISE_MAXIMUM_BY = 8.0f;      // log2 units a tile must exceed a row's reference by
 constexpr int CHUNK_STRIDE = BLOCK_M * 16;    // bytes from one 16-byte column of Q to the next
+constexpr float RAISE_MAXIMUM_BY = 8.0f;      // log2 units a tile must exceed a row's reference by
 
 struct TcPrefillArgs {
   const __nv_bfloat16* q;
@@ -82,12 +91,14 @@ template <int D>
 struct TcConfig {
   static constexpr int kQBytes = BLOCK_M * D * 2;
   static constexpr int kHalfBytes = BLOCK_N * D * 2;          // keys (or values) of a tile
+  static constexpr int kStatBytes = 2 * BLOCK_M * 2 * 4;      // (maximum, sum) per lane and row
   static constexpr int kSmemBytes =
-      kQBytes + (K_STAGES + V_STAGES + S_BUFFERS) * kHalfBytes + 1024 + 256;
+      kQBytes + (K_STAGES + V_STAGES + S_BUFFERS) * kHalfBytes + kStatBytes + 1024 + 512;
   static constexpr int kScoreColumns = BLOCK_N;               // per score buffer
   static constexpr int kLowTermColumn = BLOCK_N / 2;          // P: hi in columns [0, 32), lo after
-  static constexpr int kOutputColumn = S_BUFFERS * BLOCK_N;   // O starts here
-  static constexpr int kTmemColumns = 512;                    // 3 * 64 + D = 320, a power of two
+  static constexpr int kOutputColumn = S_BUFFERS * BLOCK_N;   // the even lane's O; the odd lane's follows
+  static constexpr int kTmemColumns = 512;
+  static_assert(S_BUFFERS * BLOCK_N + 2 * D <= 512, "tensor memory has 512 columns");
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -102,6 +113,10 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
+}
+
+__device__ __forceinline__ void softmax_groups_sync() {
+  asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
 template <int D>
@@ -136,15 +151,16 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   uint8_t* q_tile = smem;
   uint8_t* k_stages = q_tile + Config::kQBytes;
   uint8_t* v_stages = k_stages + K_STAGES * Config::kHalfBytes;
-  uint8_t* keys_by_piece = v_stages + V_STAGES * Config::kHalfBytes;      // [S_BUFFERS]: see warp 6
-  uint64_t* k_full = reinterpret_cast<uint64_t*>(keys_by_piece + S_BUFFERS * Config::kHalfBytes);
+  uint8_t* keys_by_piece = v_stages + V_STAGES * Config::kHalfBytes;      // [S_BUFFERS]
+  float2* lane_stats = reinterpret_cast<float2*>(keys_by_piece + S_BUFFERS * Config::kHalfBytes);
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(lane_stats + 2 * BLOCK_M);
   uint64_t* k_empty = k_full + K_STAGES;
   uint64_t* v_full = k_empty + K_STAGES;
   uint64_t* v_empty = v_full + V_STAGES;
-  uint64_t* s_full = v_empty + V_STAGES;      // [S_BUFFERS]
-  uint64_t* p_full = s_full + S_BUFFERS;      // [S_BUFFERS]
-  uint64_t* o_full = p_full + S_BUFFERS;      // [S_BUFFERS]: by tile, so that a phase is never skipped
-  uint64_t* k_ready = o_full + S_BUFFERS;     // [S_BUFFERS]
+  uint64_t* s_full = v_empty + V_STAGES;      // [S_BUFFERS] scores of tile t in buffer t % S_BUFFERS
+  uint64_t* p_full = s_full + S_BUFFERS;      // [S_BUFFERS] its probabilities are in place
+  uint64_t* o_full = p_full + S_BUFFERS;      // [S_BUFFERS] its output product is done
+  uint64_t* k_ready = o_full + S_BUFFERS;     // [S_BUFFERS] its keys are rewritten
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(k_ready + S_BUFFERS);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -175,7 +191,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     }
     for (int b = 0; b < S_BUFFERS; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], 4);   // one arrival per softmax warp
+      mbar_init(&p_full[b], 4);   // one arrival per softmax warp of the tile's lane
       mbar_init(&o_full[b], 1);
       mbar_init(&k_ready[b], 1);
     }
@@ -183,7 +199,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_holder, Config::kTmemColumns);
+  if (warp == WARP_SCORES) tmem_alloc(tmem_holder, Config::kTmemColumns);
   hx_pdl_wait();
 
   // ---- the query tile, by everybody: [D / 8 pieces][16 row groups][8 rows][16 bytes]
@@ -203,13 +219,13 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0 || warp == 7) {
+  if (warp == WARP_KEYS || warp == WARP_VALUES) {
     // ------------------------------------------------------------ page requests
-    // Warp 0 asks for keys, warp 7 for values, each as far ahead as its own ring allows: the
-    // keys of a tile are wanted S_BUFFERS tiles before its values (they are rewritten, then
-    // multiplied, then the softmax runs), and one ring must not hold up the other.
+    // Each as far ahead as its own ring allows: the keys of a tile are wanted well before
+    // its values (they are rewritten, then multiplied, then the softmax runs), and one ring
+    // must not hold up the other.
     if (lane == 0) {
-      const bool values = warp == 7;
+      const bool values = warp == WARP_VALUES;
       const int stages = values ? V_STAGES : K_STAGES;
       uint64_t* full = values ? v_full : k_full;
       uint64_t* empty = values ? v_empty : k_empty;
@@ -257,11 +273,11 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         for (int p = 0; p < 4; ++p) pages[p] = next_pages[p];
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == WARP_REWRITE) {
     // ------------------------------------------------------ keys, piece by piece
     // The score product wants all 64 keys of the tile at one stride, but every page block
     // holds its own keys piece-major: this warp rewrites a landed tile as
-    // [piece][64 keys][16 bytes] into one of two buffers, 32 pieces at a time.
+    // [piece][64 keys][16 bytes] into buffer tile % S_BUFFERS.
     bool ok = true;
     // where keys `lane` and `lane + 32` of a tile sit inside the landed page blocks
     const uint32_t source_low = (lane / page_size) * page_bytes + (lane % page_size) * 16;
@@ -281,10 +297,9 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
-      // piece c of keys lane and lane + 32: the two reads are a page apart at most, the two
-      // writes 512 bytes; from piece to piece both move by a constant
       const uint32_t source = smem_u32(k_stages + (tile % K_STAGES) * Config::kHalfBytes);
-      const uint32_t target = smem_u32(keys_by_piece + (tile % S_BUFFERS) * Config::kHalfBytes) + lane * 16;
+      const uint32_t target =
+          smem_u32(keys_by_piece + (tile % S_BUFFERS) * Config::kHalfBytes) + lane * 16;
       // eight pieces at a time: all their loads are in flight before the first store
 #pragma unroll
       for (int piece0 = 0; piece0 < D / 8; piece0 += 8) {
@@ -315,8 +330,8 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         mbar_arrive(&k_empty[tile % K_STAGES]);      // the landed copy may be overwritten
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- products
+  } else if (warp == WARP_SCORES || warp == WARP_SCORES + 1) {
+    // ------------------------------------------------------------ score products
     if (lane == 0) {
       constexpr uint32_t idesc_scores = make_idesc(BLOCK_M, BLOCK_N);
       // Descriptors differ from product to product only in their start address (the low 14
@@ -325,11 +340,11 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       const uint64_t desc_k0 =
           make_smem_desc_plain(smem_u32(keys_by_piece), BLOCK_N * 16, GROUP_STRIDE);
       constexpr uint32_t kKeyBufferStep = Config::kHalfBytes >> 4;
-      constexpr uint32_t kChunkPairStep = (2 * CHUNK_STRIDE) >> 4;      // 16 coordinates of Q or P on
+      constexpr uint32_t kChunkPairStep = (2 * CHUNK_STRIDE) >> 4;      // 16 coordinates of Q on
       constexpr uint32_t kKeyPiecePairStep = (2 * BLOCK_N * 16) >> 4;   // 16 coordinates of the keys on
       // S[tile % S_BUFFERS] = Q K_tile^T: one product of 64 keys per 16 coordinates.  The
       // buffer held the probabilities of tile - S_BUFFERS, which their product must have read.
-      for (int tile = 0; tile < n_tiles && !*failed; ++tile) {
+      for (int tile = warp - WARP_SCORES; tile < n_tiles && !*failed; tile += 2) {
         const int b = tile % S_BUFFERS;
         if (!mbar_wait(&k_ready[b], static_cast<uint32_t>(tile / S_BUFFERS) & 1u) ||
             (tile >= S_BUFFERS &&
@@ -348,9 +363,10 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         umma_commit(&s_full[b]);
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == WARP_OUTPUT || warp == WARP_OUTPUT + 1) {
     // ----------------------------------------------------------- output products
     if (lane == 0) {
+      const int parity = warp - WARP_OUTPUT;
       constexpr uint32_t idesc_output = make_idesc_b_mn_major(BLOCK_M, D);
       // values: MN-major, the next 8 keys are 128 bytes on, the next 8 coordinates one piece on
       const uint64_t desc_v0 = make_smem_desc_plain(smem_u32(v_stages), GROUP_STRIDE, piece_stride);
@@ -362,7 +378,8 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         const int key = g * 16;
         value_step[g] = ((key / page_size) * page_bytes + (key % page_size) * 16) >> 4;
       }
-      for (int tile = 0; tile < n_tiles && !*failed; ++tile) {
+      const uint32_t target = tmem_base + Config::kOutputColumn + parity * D;
+      for (int tile = parity; tile < n_tiles && !*failed; tile += 2) {
         // the probabilities of this tile lie where its scores were
         const int s = tile % V_STAGES;
         if (!mbar_wait(&p_full[tile % S_BUFFERS], static_cast<uint32_t>(tile / S_BUFFERS) & 1u) ||
@@ -373,43 +390,47 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         }
         tc_fence_after();
         const uint64_t desc_v = desc_v0 + s * kStageStep;
-        const uint32_t target = tmem_base + Config::kOutputColumn;
         const uint32_t p_hi = tmem_base + (tile % S_BUFFERS) * Config::kScoreColumns;
         const uint32_t p_lo = p_hi + Config::kLowTermColumn;
-        // O += P V_tile: 16 keys (8 columns of P) per product, the hi and the lo term of P
+        // O_lane += P V_tile: 16 keys (8 columns of P) per product, the hi and the lo term of P
 #pragma unroll
         for (int g = 0; g < BLOCK_N / 16; ++g) {
           umma_bf16_a_tmem(target, p_hi + g * 8, desc_v + value_step[g], idesc_output,
-                           (tile > 0 || g > 0) ? 1u : 0u);
+                           (tile >= 2 || g > 0) ? 1u : 0u);
           umma_bf16_a_tmem(target, p_lo + g * 8, desc_v + value_step[g], idesc_output, 1u);
         }
         umma_commit(&v_empty[s]);                    // the stage may be refilled
         umma_commit(&o_full[tile % S_BUFFERS]);      // O holds this tile; its P has been read
       }
     }
-  } else {
+  } else if (warp >= WARP_SOFTMAX) {
     // ------------------------------------------------------------------ softmax
+    const int parity = (warp - WARP_SOFTMAX) >> 2;      // which lane of tiles this group serves
     const int quarter = warp & 3;      // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
     const int row = quarter * 32 + lane;
+    const int group_thread = threadIdx.x - (WARP_SOFTMAX + 4 * parity) * 32;      // 0..127
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t output_base = lane_base + Config::kOutputColumn + parity * D;
     const int q_position = context + row0 + row;      // the last key this row sees
     float row_max = -INFINITY;      // the reference of this row's exponentials, in log2 units
     float row_sum = 0.0f;
     const float scale_log2 = a.scale * 1.4426950408889634f;
     bool ok = true;
 
-    auto wait_for = [&](uint64_t* bar, uint32_t parity) {
-      bool done = true;
-      if (lane == 0) done = mbar_wait(bar, parity);
-      done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
-      if (!done && lane == 0) {
+    // One lane waits and looks at the failure flag, all lanes get the same answer (what
+    // follows a wait is warp-wide: tensor-memory loads and stores need the warp together).
+    auto wait_for = [&](uint64_t* bar, uint32_t parity_bit) {
+      int state = 0;      // 0: go on, 1: this wait ran out, 2: somebody else failed
+      if (lane == 0) state = *failed ? 2 : (mbar_wait(bar, parity_bit) ? 0 : 1);
+      state = __shfl_sync(0xffffffffu, state, 0);
+      if (state == 1 && lane == 0) {
         atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
         *failed = 1;
       }
-      return done;
+      return state == 0;
     };
 
-    for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
+    for (int tile = parity; tile < n_tiles && ok; tile += 2) {
       ok = wait_for(&s_full[tile % S_BUFFERS], static_cast<uint32_t>(tile / S_BUFFERS) & 1u);
       if (!ok) break;
       tc_fence_after();
@@ -438,44 +459,46 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
 #pragma unroll
         for (int u = 0; u < 4; ++u) part_max[u] = fmaxf(part_max[u], p[i + u]);
       const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
-      // key 0 is visible to every row, so the reference is finite from the first tile on
-      if (tile == 0) {
+      // Key 0 is visible to every row, so the even lane's reference is finite from tile 0 on.
+      // A row may see nothing of the odd lane's first tile (or of any of its tiles): its
+      // reference then stays -inf for now, and its exponentials are taken against 0.
+      if (tile < 2) {
         row_max = tile_max;
       } else if (__any_sync(0xffffffffu, tile_max > row_max + RAISE_MAXIMUM_BY)) {
         // ---- a new reference: what O and the sum hold was taken against the old one.  The
-        // product of the previous tile must have landed; the product of this tile waits for
-        // this warp's arrival below.
+        // lane's previous product must have landed; the product of this tile waits for this
+        // warp's arrival below.  (o_full[b] completes a phase for every S_BUFFERS-th tile; its
+        // previous phase was complete before the scores of this tile were started.)
         const float new_max = fmaxf(row_max, tile_max);
-        const float correction = fast_exp2(row_max - new_max);
+        const float correction = row_max == -INFINITY ? 0.0f : fast_exp2(row_max - new_max);
         row_max = new_max;
         row_sum *= correction;
-        // (o_full[b] completes a phase for every S_BUFFERS-th tile; its previous phase was
-        // complete before the scores of this tile were started, so no phase is mistaken)
-        ok = wait_for(&o_full[(tile - 1) % S_BUFFERS],
-                      static_cast<uint32_t>((tile - 1) / S_BUFFERS) & 1u);
+        ok = wait_for(&o_full[(tile - 2) % S_BUFFERS],
+                      static_cast<uint32_t>((tile - 2) / S_BUFFERS) & 1u);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int d0 = 0; d0 < D; d0 += 32) {
           uint32_t r0[16], r1[16];
-          tmem_load16_issue(lane_base + Config::kOutputColumn + d0, r0);
-          tmem_load16_issue(lane_base + Config::kOutputColumn + d0 + 16, r1);
+          tmem_load16_issue(output_base + d0, r0);
+          tmem_load16_issue(output_base + d0 + 16, r1);
           tmem_load_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             r0[i] = __float_as_uint(__uint_as_float(r0[i]) * correction);
             r1[i] = __float_as_uint(__uint_as_float(r1[i]) * correction);
           }
-          tmem_store16_raw(lane_base + Config::kOutputColumn + d0, r0);
-          tmem_store16_raw(lane_base + Config::kOutputColumn + d0 + 16, r1);
+          tmem_store16_raw(output_base + d0, r0);
+          tmem_store16_raw(output_base + d0 + 16, r1);
         }
       }
+      const float reference = row_max == -INFINITY ? 0.0f : row_max;
       float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int i = 0; i < BLOCK_N; i += 4)
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          p[i + u] = fast_exp2(p[i + u] - row_max);
+          p[i + u] = fast_exp2(p[i + u] - reference);
           part_sum[u] += p[i + u];
         }
       row_sum += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
@@ -507,7 +530,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         ok = wait_for(&v_full[tile % V_STAGES], static_cast<uint32_t>(tile / V_STAGES) & 1u);
         if (!ok) break;
         uint8_t* v_half = v_stages + (tile % V_STAGES) * Config::kHalfBytes;
-        for (int index = threadIdx.x - 64; index < BLOCK_N * (D / 8); index += 128) {
+        for (int index = group_thread; index < BLOCK_N * (D / 8); index += 128) {
           const int key = index / (D / 8);
           const int piece = index - key * (D / 8);
           if (key >= first_stale)
@@ -522,35 +545,61 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       if (lane == 0) mbar_arrive(&p_full[tile % S_BUFFERS]);
     }
 
-    if (ok && !*failed) {
-      // a commit covers every product issued before it: the last tile's says all are done
-      ok = wait_for(&o_full[(n_tiles - 1) % S_BUFFERS],
-                    static_cast<uint32_t>((n_tiles - 1) / S_BUFFERS) & 1u);
-      if (ok) {
-        tc_fence_after();
-        const float inverse = 1.0f / row_sum;
-        __nv_bfloat16* out = a.out + static_cast<size_t>(q_begin + row0 + row) * a.ldo +
-                             static_cast<size_t>(head) * D;
+    // ---- the lane's last product, then the two lanes together.  A commit covers every
+    // product its thread issued before it, so the lane's last tile says all of them are done.
+    const int lane_tiles = (n_tiles - parity + 1) / 2;
+    if (ok && lane_tiles > 0) {
+      const int last_tile = parity + 2 * (lane_tiles - 1);
+      ok = wait_for(&o_full[last_tile % S_BUFFERS],
+                    static_cast<uint32_t>(last_tile / S_BUFFERS) & 1u);
+    }
+    lane_stats[parity * BLOCK_M + row] = make_float2(row_max, row_sum);
+    tc_fence_before();
+    softmax_groups_sync();      // both groups come here, whatever happened to them
+    tc_fence_after();
+    if (__shfl_sync(0xffffffffu, (ok && !*failed) ? 1 : 0, 0) != 0) {
+      // out = (O_even 2^(m_even - m) + O_odd 2^(m_odd - m)) / (l_even 2^(m_even - m) + ...);
+      // a lane that saw nothing of this row has the reference -inf and the weight 0.  The even
+      // group writes the first half of the coordinates, the odd group the second.
+      const float2 even = lane_stats[row], odd = lane_stats[BLOCK_M + row];
+      const float top = fmaxf(even.x, odd.x);
+      const float weight_even = fast_exp2(even.x - top);
+      const float weight_odd = (n_tiles > 1 && odd.x != -INFINITY) ? fast_exp2(odd.x - top) : 0.0f;
+      const float inverse = 1.0f / (even.y * weight_even + odd.y * weight_odd);
+      const float scale_even = weight_even * inverse, scale_odd = weight_odd * inverse;
+      const bool use_odd = weight_odd != 0.0f;      // the odd accumulator may never have been written
+      const bool any_odd = __any_sync(0xffffffffu, use_odd);
+      __nv_bfloat16* out = a.out + static_cast<size_t>(q_begin + row0 + row) * a.ldo +
+                           static_cast<size_t>(head) * D;
 #pragma unroll
-        for (int d0 = 0; d0 < D; d0 += 32) {
-          uint32_t r[2][16];
-          tmem_load16_issue(lane_base + Config::kOutputColumn + d0, r[0]);
-          tmem_load16_issue(lane_base + Config::kOutputColumn + d0 + 16, r[1]);
-          tmem_load_wait();
-          if (row < rows_here) {
+      for (int d0 = parity * (D / 2); d0 < (parity + 1) * (D / 2); d0 += 32) {
+        uint32_t e[2][16], o[2][16];
+        tmem_load16_issue(lane_base + Config::kOutputColumn + d0, e[0]);
+        tmem_load16_issue(lane_base + Config::kOutputColumn + d0 + 16, e[1]);
+        if (any_odd) {
+          tmem_load16_issue(lane_base + Config::kOutputColumn + D + d0, o[0]);
+          tmem_load16_issue(lane_base + Config::kOutputColumn + D + d0 + 16, o[1]);
+        }
+        tmem_load_wait();
+        if (row < rows_here) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+          for (int h = 0; h < 2; ++h)
 #pragma unroll
-              for (int d = 0; d < 16; d += 8) {
-                uint4 packed;
-                __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+            for (int d = 0; d < 16; d += 8) {
+              uint4 packed;
+              __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                  pairs[i] = __floats2bfloat162_rn(__uint_as_float(r[h][d + 2 * i]) * inverse,
-                                                   __uint_as_float(r[h][d + 2 * i + 1]) * inverse);
-                *reinterpret_cast<uint4*>(out + d0 + h * 16 + d) = packed;
+              for (int i = 0; i < 4; ++i) {
+                float x0 = __uint_as_float(e[h][d + 2 * i]) * scale_even;
+                float x1 = __uint_as_float(e[h][d + 2 * i + 1]) * scale_even;
+                if (use_odd) {
+                  x0 += __uint_as_float(o[h][d + 2 * i]) * scale_odd;
+                  x1 += __uint_as_float(o[h][d + 2 * i + 1]) * scale_odd;
+                }
+                pairs[i] = __floats2bfloat162_rn(x0, x1);
               }
-          }
+              *reinterpret_cast<uint4*>(out + d0 + h * 16 + d) = packed;
+            }
         }
       }
     }
@@ -558,7 +607,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == WARP_SCORES) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Config::kTmemColumns);
   }
