@@ -3,37 +3,40 @@
 // a [heads, T, T] score tensor for it, src/attention/cuda.cu:31-77), with both products as
 // tcgen05.mma and the scores, the probabilities and the output in tensor memory.
 //
-// One CTA takes 128 consecutive query tokens of one request and one head and walks the
-// request's keys in tiles of 64, anchored at key 0.  Tiles with an even number and tiles with
-// an odd number go down two lanes that share nothing but the keys and values in shared memory:
-// each lane has its own thread issuing score products, its own four softmax warps, its own
-// thread issuing output products and its own output accumulator; the two accumulators are
-// combined at the end.  Warp roles:
+// One CTA takes 256 consecutive query tokens of one request and one head, as two lanes of 128
+// rows (the M of a product), and walks the request's keys in tiles of 64, anchored at key 0.
+// The lanes share the keys and values in shared memory and nothing else: each has its own
+// thread issuing score products, its own four softmax warps, its own thread issuing output
+// products and its own accumulators in tensor memory.  The second lane's rows see up to two
+// key tiles more than the first's; a short request may leave it empty.  Warp roles:
 //   warps 0, 1  one lane of each asks for the pages of each tile, warp 0 for the keys and
 //               warp 1 for the values: the keys of a (page, head) are one contiguous block of
 //               the cache and so are its values, so a tile is a handful of bulk copies
 //               (cp.async.bulk counted on an mbarrier) into a ring of stages;
 //   warp 2      rewrites the keys of a landed tile piece-major over all 64 keys (see below);
-//   warps 3, 4  one lane each issues S = Q K^T for the even / odd tiles into one of four score
-//               buffers in tensor memory, up to two tiles of its lane ahead of the softmax;
-//   warps 5, 6  one lane each issues O_lane += P V for the even / odd tiles;
+//   warps 3, 4  one lane each issues S_l = Q_l K^T for lane l into one of the lane's two score
+//               buffers in tensor memory, a tile ahead of the softmax;
+//   warps 5, 6  one lane each issues O_l += P_l V;
 //   warp 7      idles (the softmax groups start at a multiple of four warps, which is what
-//               selects their lanes of tensor memory);
-//   warps 8-11, 12-15  softmax of the even / odd tiles: thread r owns query row r.  It reads
-//               its row of S from tensor memory, keeps the running maximum and sum of its lane
-//               in float32 registers and writes the probabilities back over the scores it has
+//               selects their rows of tensor memory);
+//   warps 8-11, 12-15  softmax of lane 0 / lane 1: thread r owns query row r of its lane.  It
+//               reads its row of S from tensor memory, keeps the running maximum and sum in
+//               float32 registers and writes the probabilities back over the scores it has
 //               read, as TWO bfloat16 terms (P = hi + lo, so the softmax stays a float32
 //               quantity as far as the result can tell).  P is the A operand of O += P V
-//               straight from tensor memory.  The maximum a row's exponentials are taken
-//               against is only raised when a tile exceeds it by more than 2^8 (any fixed
-//               reference gives the same quotient; float32 has the range), so the pass over O
-//               that a new maximum costs is rare.
+//               straight from tensor memory, and O stays in tensor memory over all tiles.  The
+//               maximum a row's exponentials are taken against is only raised when a tile
+//               exceeds it by more than 2^8 (any fixed reference gives the same quotient;
+//               float32 has the range), so the pass over O that a new maximum costs is rare.
 //
-// Why so many issuing threads: a thread needs 55 ns and more to issue one tcgen05.mma,
-// whatever its size, while the tensor pipe finishes a product of 64 or 128 columns in 30 to
-// 35 ns (measured: one to four threads issuing side by side each keep their own rate until
-// the pipe is full).  And one softmax group alone leaves its four schedulers waiting on the
-// latencies of tensor-memory loads and stores and on the exponential unit.
+// Why two lanes and four issuing threads: a thread needs 55 ns and more to issue one
+// tcgen05.mma, whatever its size, while the tensor pipe finishes a product of 64 or 128
+// columns in 30 to 35 ns (measured: one to four threads issuing side by side each keep their
+// own rate until the pipe is full); one softmax group alone leaves its four schedulers waiting
+// on the latencies of tensor-memory loads and stores and on the exponential unit; and what a
+// CTA spends before its first and after its last tile (about 10 us: page table, first pages,
+// rewrite, the chain of first products; the last product, the output) is spent once for 256
+// rows, and every key tile is fetched and rewritten once for them.
 //
 // Operand layouts.  Nothing is swizzled: every operand is made of "core matrices" of 8 rows
 // x 16 bytes (128 contiguous bytes), which is exactly what a page block of the cache is made
@@ -53,11 +56,13 @@
 
 namespace {
 
-constexpr int BLOCK_M = 128;   // query rows per CTA (the MMA's M)
+constexpr int BLOCK_M = 128;   // query rows per lane (the MMA's M)
+constexpr int LANES = 2;       // lanes per CTA: 256 query rows
 constexpr int BLOCK_N = 64;    // keys per tile
 constexpr int K_STAGES = 2;    // key tiles in shared memory as they land (rewritten at once)
-constexpr int V_STAGES = 4;    // value tiles in shared memory (held until their product is done)
-constexpr int S_BUFFERS = 4;   // score tiles in tensor memory and rewritten key tiles: two per lane
+constexpr int V_STAGES = 4;    // value tiles in shared memory (held until both products are done)
+constexpr int KEY_BUFFERS = 3; // rewritten key tiles in shared memory
+constexpr int S_BUFFERS = 2;   // score tiles in tensor memory per lane
 constexpr int THREADS = 512;
 constexpr int WARP_KEYS = 0, WARP_VALUES = 1, WARP_REWRITE = 2, WARP_SCORES = 3, WARP_OUTPUT = 5,
               WARP_SOFTMAX = 8;
@@ -89,16 +94,15 @@ struct TcPrefillArgs {
 
 template <int D>
 struct TcConfig {
-  static constexpr int kQBytes = BLOCK_M * D * 2;
+  static constexpr int kQBytes = BLOCK_M * D * 2;              // per lane
   static constexpr int kHalfBytes = BLOCK_N * D * 2;          // keys (or values) of a tile
-  static constexpr int kStatBytes = 2 * BLOCK_M * 2 * 4;      // (maximum, sum) per lane and row
   static constexpr int kSmemBytes =
-      kQBytes + (K_STAGES + V_STAGES + S_BUFFERS) * kHalfBytes + kStatBytes + 1024 + 512;
+      LANES * kQBytes + (K_STAGES + V_STAGES + KEY_BUFFERS) * kHalfBytes + 1024 + 512;
   static constexpr int kScoreColumns = BLOCK_N;               // per score buffer
   static constexpr int kLowTermColumn = BLOCK_N / 2;          // P: hi in columns [0, 32), lo after
-  static constexpr int kOutputColumn = S_BUFFERS * BLOCK_N;   // the even lane's O; the odd lane's follows
+  static constexpr int kOutputColumn = LANES * S_BUFFERS * BLOCK_N;   // lane 0's O; lane 1's follows
   static constexpr int kTmemColumns = 512;
-  static_assert(S_BUFFERS * BLOCK_N + 2 * D <= 512, "tensor memory has 512 columns");
+  static_assert(LANES * (S_BUFFERS * BLOCK_N + D) <= 512, "tensor memory has 512 columns");
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -115,10 +119,6 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
       : "memory");
 }
 
-__device__ __forceinline__ void softmax_groups_sync() {
-  asm volatile("bar.sync 1, 256;" ::: "memory");
-}
-
 template <int D>
 __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPrefillArgs a) {
   using Config = TcConfig<D>;
@@ -132,7 +132,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     for (int r = 0; r < a.requests; ++r) {
       const int length = a.request_start[r + 1] - a.request_start[r];
       if (length < a.min_query_len) continue;
-      const int tiles = (length + BLOCK_M - 1) / BLOCK_M;
+      const int tiles = (length + LANES * BLOCK_M - 1) / (LANES * BLOCK_M);
       if (remaining < tiles) {
         request = r;
         // the last rows of a request see the most keys: their CTAs are started first (the grid
@@ -149,19 +149,19 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* q_tile = smem;
-  uint8_t* k_stages = q_tile + Config::kQBytes;
+  uint8_t* k_stages = q_tile + LANES * Config::kQBytes;
   uint8_t* v_stages = k_stages + K_STAGES * Config::kHalfBytes;
-  uint8_t* keys_by_piece = v_stages + V_STAGES * Config::kHalfBytes;      // [S_BUFFERS]
-  float2* lane_stats = reinterpret_cast<float2*>(keys_by_piece + S_BUFFERS * Config::kHalfBytes);
-  uint64_t* k_full = reinterpret_cast<uint64_t*>(lane_stats + 2 * BLOCK_M);
+  uint8_t* keys_by_piece = v_stages + V_STAGES * Config::kHalfBytes;      // [KEY_BUFFERS]
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(keys_by_piece + KEY_BUFFERS * Config::kHalfBytes);
   uint64_t* k_empty = k_full + K_STAGES;
   uint64_t* v_full = k_empty + K_STAGES;
-  uint64_t* v_empty = v_full + V_STAGES;
-  uint64_t* s_full = v_empty + V_STAGES;      // [S_BUFFERS] scores of tile t in buffer t % S_BUFFERS
-  uint64_t* p_full = s_full + S_BUFFERS;      // [S_BUFFERS] its probabilities are in place
-  uint64_t* o_full = p_full + S_BUFFERS;      // [S_BUFFERS] its output product is done
-  uint64_t* k_ready = o_full + S_BUFFERS;     // [S_BUFFERS] its keys are rewritten
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(k_ready + S_BUFFERS);
+  uint64_t* v_empty = v_full + V_STAGES;              // [LANES][V_STAGES]: a lane's product has read it
+  uint64_t* s_full = v_empty + LANES * V_STAGES;      // [LANES][S_BUFFERS] scores of tile t in buffer t % 2
+  uint64_t* p_full = s_full + LANES * S_BUFFERS;      // [LANES][S_BUFFERS] its probabilities are in place
+  uint64_t* o_full = p_full + LANES * S_BUFFERS;      // [LANES][S_BUFFERS] its output product is done
+  uint64_t* k_ready = o_full + LANES * S_BUFFERS;     // [KEY_BUFFERS] the tile's keys are rewritten
+  uint64_t* k_done = k_ready + KEY_BUFFERS;           // [LANES][KEY_BUFFERS] a lane's scores have read them
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(k_done + LANES * KEY_BUFFERS);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -171,10 +171,16 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   const int q_begin = a.request_start[request];
   const int q_len = a.request_start[request + 1] - q_begin;
   const int context = a.request_context[request];
-  const int row0 = tile_in_request * BLOCK_M;                 // first query row of the tile
-  const int rows_here = min(BLOCK_M, q_len - row0);
+  const int row0 = tile_in_request * LANES * BLOCK_M;         // first query row of the CTA
+  const int rows_here = min(LANES * BLOCK_M, q_len - row0);
   const int last_key = context + row0 + rows_here - 1;        // last key any row here sees
-  const int n_tiles = last_key / BLOCK_N + 1;
+  const int n_tiles = last_key / BLOCK_N + 1;                 // key tiles somebody here sees
+  // lane l has rows [row0 + 128 l, ...) and sees the tiles before lane_tiles(l); lane 1 may be empty
+  auto lane_rows = [&](int l) { return max(0, min(BLOCK_M, rows_here - l * BLOCK_M)); };
+  auto lane_tiles = [&](int l) {
+    const int rows = lane_rows(l);
+    return rows > 0 ? (context + row0 + l * BLOCK_M + rows - 1) / BLOCK_N + 1 : 0;
+  };
   const int page_size = a.page_size;
   const int pages_per_tile = BLOCK_N / page_size;
   const uint32_t page_bytes = static_cast<uint32_t>(page_size) * D * 2;
@@ -185,16 +191,15 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
     }
-    for (int s = 0; s < V_STAGES; ++s) {
-      mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
-    }
-    for (int b = 0; b < S_BUFFERS; ++b) {
+    for (int s = 0; s < V_STAGES; ++s) mbar_init(&v_full[s], 1);
+    for (int s = 0; s < LANES * V_STAGES; ++s) mbar_init(&v_empty[s], 1);
+    for (int b = 0; b < LANES * S_BUFFERS; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], 4);   // one arrival per softmax warp of the tile's lane
+      mbar_init(&p_full[b], 4);   // one arrival per softmax warp of the lane
       mbar_init(&o_full[b], 1);
-      mbar_init(&k_ready[b], 1);
     }
+    for (int b = 0; b < KEY_BUFFERS; ++b) mbar_init(&k_ready[b], 1);
+    for (int b = 0; b < LANES * KEY_BUFFERS; ++b) mbar_init(&k_done[b], 1);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -202,16 +207,17 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   if (warp == WARP_SCORES) tmem_alloc(tmem_holder, Config::kTmemColumns);
   hx_pdl_wait();
 
-  // ---- the query tile, by everybody: [D / 8 pieces][16 row groups][8 rows][16 bytes]
-  for (int index = threadIdx.x; index < BLOCK_M * (D / 8); index += THREADS) {
-    const int row = index / (D / 8);
+  // ---- the query tiles, by everybody: per lane [D / 8 pieces][16 row groups][8 rows][16 bytes]
+  for (int index = threadIdx.x; index < LANES * BLOCK_M * (D / 8); index += THREADS) {
+    const int row = index / (D / 8);      // among the CTA's 256
     const int piece = index - row * (D / 8);
     uint4 value = make_uint4(0u, 0u, 0u, 0u);
     if (row < rows_here)
       value = *reinterpret_cast<const uint4*>(a.q + static_cast<size_t>(q_begin + row0 + row) * a.ldq +
                                               static_cast<size_t>(head) * D + piece * 8);
-    *reinterpret_cast<uint4*>(q_tile + piece * CHUNK_STRIDE + (row >> 3) * GROUP_STRIDE +
-                              (row & 7) * 16) = value;
+    const int in_lane = row & (BLOCK_M - 1);
+    *reinterpret_cast<uint4*>(q_tile + (row / BLOCK_M) * Config::kQBytes + piece * CHUNK_STRIDE +
+                              (in_lane >> 3) * GROUP_STRIDE + (in_lane & 7) * 16) = value;
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   tc_fence_before();
@@ -228,7 +234,6 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       const bool values = warp == WARP_VALUES;
       const int stages = values ? V_STAGES : K_STAGES;
       uint64_t* full = values ? v_full : k_full;
-      uint64_t* empty = values ? v_empty : k_empty;
       uint8_t* ring = values ? v_stages : k_stages;
       const uint8_t* cache = reinterpret_cast<const uint8_t*>(values ? a.v_cache : a.k_cache);
       const int* table = a.block_tables +
@@ -246,7 +251,18 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       for (int tile = 0; tile < n_tiles && !*failed; ++tile) {
         if (tile + 1 < n_tiles) pages_of(tile + 1, next_pages);      // in flight during the wait
         const int stage = tile % stages;
-        if (!mbar_wait(&empty[stage], (static_cast<uint32_t>(tile / stages) & 1u) ^ 1u)) {
+        bool free = true;
+        if (!values) {
+          free = mbar_wait(&k_empty[stage], (static_cast<uint32_t>(tile / stages) & 1u) ^ 1u);
+        } else if (tile >= V_STAGES) {
+          // the stage held tile - V_STAGES: every lane that saw that tile has multiplied by it
+          const int before = tile - V_STAGES;
+          for (int l = 0; l < LANES && free; ++l)
+            if (before < lane_tiles(l))
+              free = mbar_wait(&v_empty[l * V_STAGES + stage],
+                               static_cast<uint32_t>(before / V_STAGES) & 1u);
+        }
+        if (!free) {
           atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
           *failed = 1;
           break;
@@ -277,7 +293,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     // ------------------------------------------------------ keys, piece by piece
     // The score product wants all 64 keys of the tile at one stride, but every page block
     // holds its own keys piece-major: this warp rewrites a landed tile as
-    // [piece][64 keys][16 bytes] into buffer tile % S_BUFFERS.
+    // [piece][64 keys][16 bytes] into buffer tile % KEY_BUFFERS.
     bool ok = true;
     // where keys `lane` and `lane + 32` of a tile sit inside the landed page blocks
     const uint32_t source_low = (lane / page_size) * page_bytes + (lane % page_size) * 16;
@@ -286,10 +302,16 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     for (int tile = 0; tile < n_tiles && ok && !*failed; ++tile) {
       if (lane == 0) {
         ok = mbar_wait(&k_full[tile % K_STAGES], static_cast<uint32_t>(tile / K_STAGES) & 1u);
-        // the product that read this buffer S_BUFFERS tiles ago is done when its scores are
-        if (ok && tile >= S_BUFFERS)
-          ok = mbar_wait(&s_full[tile % S_BUFFERS],
-                         static_cast<uint32_t>((tile - S_BUFFERS) / S_BUFFERS) & 1u);
+        // the score products that read this buffer KEY_BUFFERS tiles ago are done (one per
+        // lane that saw that tile; a barrier of its own per lane and buffer, whose next phase
+        // needs this very rewrite, so that no phase can be mistaken for another)
+        if (tile >= KEY_BUFFERS) {
+          const int before = tile - KEY_BUFFERS;
+          for (int l = 0; l < LANES && ok; ++l)
+            if (before < lane_tiles(l))
+              ok = mbar_wait(&k_done[l * KEY_BUFFERS + tile % KEY_BUFFERS],
+                             static_cast<uint32_t>(before / KEY_BUFFERS) & 1u);
+        }
         if (!ok) {
           atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
           *failed = 1;
@@ -299,7 +321,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       if (!ok) break;
       const uint32_t source = smem_u32(k_stages + (tile % K_STAGES) * Config::kHalfBytes);
       const uint32_t target =
-          smem_u32(keys_by_piece + (tile % S_BUFFERS) * Config::kHalfBytes) + lane * 16;
+          smem_u32(keys_by_piece + (tile % KEY_BUFFERS) * Config::kHalfBytes) + lane * 16;
       // eight pieces at a time: all their loads are in flight before the first store
 #pragma unroll
       for (int piece0 = 0; piece0 < D / 8; piece0 += 8) {
@@ -326,7 +348,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&k_ready[tile % S_BUFFERS]);
+        mbar_arrive(&k_ready[tile % KEY_BUFFERS]);
         mbar_arrive(&k_empty[tile % K_STAGES]);      // the landed copy may be overwritten
       }
     }
@@ -342,11 +364,14 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       constexpr uint32_t kKeyBufferStep = Config::kHalfBytes >> 4;
       constexpr uint32_t kChunkPairStep = (2 * CHUNK_STRIDE) >> 4;      // 16 coordinates of Q on
       constexpr uint32_t kKeyPiecePairStep = (2 * BLOCK_N * 16) >> 4;   // 16 coordinates of the keys on
-      // S[tile % S_BUFFERS] = Q K_tile^T: one product of 64 keys per 16 coordinates.  The
-      // buffer held the probabilities of tile - S_BUFFERS, which their product must have read.
-      for (int tile = warp - WARP_SCORES; tile < n_tiles && !*failed; tile += 2) {
-        const int b = tile % S_BUFFERS;
-        if (!mbar_wait(&k_ready[b], static_cast<uint32_t>(tile / S_BUFFERS) & 1u) ||
+      // S_l[tile % 2] = Q_l K_tile^T: one product of 64 keys per 16 coordinates.  The buffer
+      // held the probabilities of tile - 2, which the lane's output product must have read.
+      const int l = warp - WARP_SCORES;
+      const int my_tiles = lane_tiles(l);
+      const uint64_t desc_q = desc_q0 + l * (Config::kQBytes >> 4);
+      for (int tile = 0; tile < my_tiles && !*failed; ++tile) {
+        const int b = l * S_BUFFERS + tile % S_BUFFERS;
+        if (!mbar_wait(&k_ready[tile % KEY_BUFFERS], static_cast<uint32_t>(tile / KEY_BUFFERS) & 1u) ||
             (tile >= S_BUFFERS &&
              !mbar_wait(&o_full[b], static_cast<uint32_t>((tile - S_BUFFERS) / S_BUFFERS) & 1u))) {
           atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
@@ -354,19 +379,21 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
           break;
         }
         tc_fence_after();
-        const uint64_t desc_k = desc_k0 + b * kKeyBufferStep;
+        const uint64_t desc_k = desc_k0 + (tile % KEY_BUFFERS) * kKeyBufferStep;
         const uint32_t target = tmem_base + b * Config::kScoreColumns;
 #pragma unroll
         for (int k = 0; k < kDSteps; ++k)
-          umma_bf16(target, desc_q0 + k * kChunkPairStep, desc_k + k * kKeyPiecePairStep,
+          umma_bf16(target, desc_q + k * kChunkPairStep, desc_k + k * kKeyPiecePairStep,
                     idesc_scores, k > 0 ? 1u : 0u);
         umma_commit(&s_full[b]);
+        umma_commit(&k_done[l * KEY_BUFFERS + tile % KEY_BUFFERS]);
       }
     }
   } else if (warp == WARP_OUTPUT || warp == WARP_OUTPUT + 1) {
     // ----------------------------------------------------------- output products
     if (lane == 0) {
-      const int parity = warp - WARP_OUTPUT;
+      const int l = warp - WARP_OUTPUT;
+      const int my_tiles = lane_tiles(l);
       constexpr uint32_t idesc_output = make_idesc_b_mn_major(BLOCK_M, D);
       // values: MN-major, the next 8 keys are 128 bytes on, the next 8 coordinates one piece on
       const uint64_t desc_v0 = make_smem_desc_plain(smem_u32(v_stages), GROUP_STRIDE, piece_stride);
@@ -378,11 +405,12 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         const int key = g * 16;
         value_step[g] = ((key / page_size) * page_bytes + (key % page_size) * 16) >> 4;
       }
-      const uint32_t target = tmem_base + Config::kOutputColumn + parity * D;
-      for (int tile = parity; tile < n_tiles && !*failed; tile += 2) {
+      const uint32_t target = tmem_base + Config::kOutputColumn + l * D;
+      for (int tile = 0; tile < my_tiles && !*failed; ++tile) {
         // the probabilities of this tile lie where its scores were
         const int s = tile % V_STAGES;
-        if (!mbar_wait(&p_full[tile % S_BUFFERS], static_cast<uint32_t>(tile / S_BUFFERS) & 1u) ||
+        const int b = l * S_BUFFERS + tile % S_BUFFERS;
+        if (!mbar_wait(&p_full[b], static_cast<uint32_t>(tile / S_BUFFERS) & 1u) ||
             !mbar_wait(&v_full[s], static_cast<uint32_t>(tile / V_STAGES) & 1u)) {
           atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
           *failed = 1;
@@ -390,28 +418,30 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         }
         tc_fence_after();
         const uint64_t desc_v = desc_v0 + s * kStageStep;
-        const uint32_t p_hi = tmem_base + (tile % S_BUFFERS) * Config::kScoreColumns;
+        const uint32_t p_hi = tmem_base + b * Config::kScoreColumns;
         const uint32_t p_lo = p_hi + Config::kLowTermColumn;
-        // O_lane += P V_tile: 16 keys (8 columns of P) per product, the hi and the lo term of P
+        // O_l += P V_tile: 16 keys (8 columns of P) per product, the hi and the lo term of P
 #pragma unroll
         for (int g = 0; g < BLOCK_N / 16; ++g) {
           umma_bf16_a_tmem(target, p_hi + g * 8, desc_v + value_step[g], idesc_output,
-                           (tile >= 2 || g > 0) ? 1u : 0u);
+                           (tile > 0 || g > 0) ? 1u : 0u);
           umma_bf16_a_tmem(target, p_lo + g * 8, desc_v + value_step[g], idesc_output, 1u);
         }
-        umma_commit(&v_empty[s]);                    // the stage may be refilled
-        umma_commit(&o_full[tile % S_BUFFERS]);      // O holds this tile; its P has been read
+        umma_commit(&v_empty[l * V_STAGES + s]);     // this lane is done with the stage
+        umma_commit(&o_full[b]);                     // O holds this tile; its P has been read
       }
     }
   } else if (warp >= WARP_SOFTMAX) {
     // ------------------------------------------------------------------ softmax
-    const int parity = (warp - WARP_SOFTMAX) >> 2;      // which lane of tiles this group serves
+    const int l = (warp - WARP_SOFTMAX) >> 2;      // the lane this group serves
+    const int my_tiles = lane_tiles(l);
+    const int my_rows = lane_rows(l);
     const int quarter = warp & 3;      // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
     const int row = quarter * 32 + lane;
-    const int group_thread = threadIdx.x - (WARP_SOFTMAX + 4 * parity) * 32;      // 0..127
+    const int group_thread = threadIdx.x - (WARP_SOFTMAX + 4 * l) * 32;      // 0..127
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t output_base = lane_base + Config::kOutputColumn + parity * D;
-    const int q_position = context + row0 + row;      // the last key this row sees
+    const uint32_t output_base = lane_base + Config::kOutputColumn + l * D;
+    const int q_position = context + row0 + l * BLOCK_M + row;      // the last key this row sees
     float row_max = -INFINITY;      // the reference of this row's exponentials, in log2 units
     float row_sum = 0.0f;
     const float scale_log2 = a.scale * 1.4426950408889634f;
@@ -430,11 +460,12 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       return state == 0;
     };
 
-    for (int tile = parity; tile < n_tiles && ok; tile += 2) {
-      ok = wait_for(&s_full[tile % S_BUFFERS], static_cast<uint32_t>(tile / S_BUFFERS) & 1u);
+    for (int tile = 0; tile < my_tiles && ok; ++tile) {
+      const int b = l * S_BUFFERS + tile % S_BUFFERS;
+      ok = wait_for(&s_full[b], static_cast<uint32_t>(tile / S_BUFFERS) & 1u);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t score_base = lane_base + (tile % S_BUFFERS) * Config::kScoreColumns;
+      const uint32_t score_base = lane_base + b * Config::kScoreColumns;
       // ---- this row's scores of the tile, in units of log2(e) so that exp is one ex2
       float p[BLOCK_N];
       {
@@ -459,22 +490,20 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
 #pragma unroll
         for (int u = 0; u < 4; ++u) part_max[u] = fmaxf(part_max[u], p[i + u]);
       const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
-      // Key 0 is visible to every row, so the even lane's reference is finite from tile 0 on.
-      // A row may see nothing of the odd lane's first tile (or of any of its tiles): its
-      // reference then stays -inf for now, and its exponentials are taken against 0.
-      if (tile < 2) {
+      // key 0 is visible to every row, so the reference is finite from the first tile on
+      if (tile == 0) {
         row_max = tile_max;
       } else if (__any_sync(0xffffffffu, tile_max > row_max + RAISE_MAXIMUM_BY)) {
         // ---- a new reference: what O and the sum hold was taken against the old one.  The
-        // lane's previous product must have landed; the product of this tile waits for this
-        // warp's arrival below.  (o_full[b] completes a phase for every S_BUFFERS-th tile; its
+        // product of the previous tile must have landed; the product of this tile waits for
+        // this warp's arrival below.  (o_full[b] completes a phase for every other tile; its
         // previous phase was complete before the scores of this tile were started.)
         const float new_max = fmaxf(row_max, tile_max);
-        const float correction = row_max == -INFINITY ? 0.0f : fast_exp2(row_max - new_max);
+        const float correction = fast_exp2(row_max - new_max);
         row_max = new_max;
         row_sum *= correction;
-        ok = wait_for(&o_full[(tile - 2) % S_BUFFERS],
-                      static_cast<uint32_t>((tile - 2) / S_BUFFERS) & 1u);
+        ok = wait_for(&o_full[l * S_BUFFERS + (tile - 1) % S_BUFFERS],
+                      static_cast<uint32_t>((tile - 1) / S_BUFFERS) & 1u);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -492,13 +521,12 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
           tmem_store16_raw(output_base + d0 + 16, r1);
         }
       }
-      const float reference = row_max == -INFINITY ? 0.0f : row_max;
       float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int i = 0; i < BLOCK_N; i += 4)
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          p[i + u] = fast_exp2(p[i + u] - reference);
+          p[i + u] = fast_exp2(p[i + u] - row_max);
           part_sum[u] += p[i + u];
         }
       row_sum += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
@@ -524,7 +552,9 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       tmem_store_wait();
 
       // ---- value rows behind the last key hold whatever the pages (or an earlier tile)
-      // left there; a NaN would survive a zero probability, so they are cleared
+      // left there; a NaN would survive a zero probability, so they are cleared (by the group
+      // that is first to need the tile: the other waits for its own arrival barrier only, but
+      // the tile with the last key is seen by the last lane alone, or by lane 0 alone)
       const int first_stale = last_key + 1 - key0;
       if (first_stale < BLOCK_N) {
         ok = wait_for(&v_full[tile % V_STAGES], static_cast<uint32_t>(tile / V_STAGES) & 1u);
@@ -542,64 +572,40 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[tile % S_BUFFERS]);
+      if (lane == 0) mbar_arrive(&p_full[b]);
     }
 
-    // ---- the lane's last product, then the two lanes together.  A commit covers every
-    // product its thread issued before it, so the lane's last tile says all of them are done.
-    const int lane_tiles = (n_tiles - parity + 1) / 2;
-    if (ok && lane_tiles > 0) {
-      const int last_tile = parity + 2 * (lane_tiles - 1);
-      ok = wait_for(&o_full[last_tile % S_BUFFERS],
-                    static_cast<uint32_t>(last_tile / S_BUFFERS) & 1u);
-    }
-    lane_stats[parity * BLOCK_M + row] = make_float2(row_max, row_sum);
-    tc_fence_before();
-    softmax_groups_sync();      // both groups come here, whatever happened to them
-    tc_fence_after();
-    if (__shfl_sync(0xffffffffu, (ok && !*failed) ? 1 : 0, 0) != 0) {
-      // out = (O_even 2^(m_even - m) + O_odd 2^(m_odd - m)) / (l_even 2^(m_even - m) + ...);
-      // a lane that saw nothing of this row has the reference -inf and the weight 0.  The even
-      // group writes the first half of the coordinates, the odd group the second.
-      const float2 even = lane_stats[row], odd = lane_stats[BLOCK_M + row];
-      const float top = fmaxf(even.x, odd.x);
-      const float weight_even = fast_exp2(even.x - top);
-      const float weight_odd = (n_tiles > 1 && odd.x != -INFINITY) ? fast_exp2(odd.x - top) : 0.0f;
-      const float inverse = 1.0f / (even.y * weight_even + odd.y * weight_odd);
-      const float scale_even = weight_even * inverse, scale_odd = weight_odd * inverse;
-      const bool use_odd = weight_odd != 0.0f;      // the odd accumulator may never have been written
-      const bool any_odd = __any_sync(0xffffffffu, use_odd);
-      __nv_bfloat16* out = a.out + static_cast<size_t>(q_begin + row0 + row) * a.ldo +
-                           static_cast<size_t>(head) * D;
+    // ---- a commit covers every product its thread issued before it: the lane's last tile
+    // says all of them are done
+    if (ok && my_tiles > 0) {
+      ok = wait_for(&o_full[l * S_BUFFERS + (my_tiles - 1) % S_BUFFERS],
+                    static_cast<uint32_t>((my_tiles - 1) / S_BUFFERS) & 1u);
+      if (ok) {
+        tc_fence_after();
+        const float inverse = 1.0f / row_sum;
+        __nv_bfloat16* out = a.out +
+                             static_cast<size_t>(q_begin + row0 + l * BLOCK_M + row) * a.ldo +
+                             static_cast<size_t>(head) * D;
 #pragma unroll
-      for (int d0 = parity * (D / 2); d0 < (parity + 1) * (D / 2); d0 += 32) {
-        uint32_t e[2][16], o[2][16];
-        tmem_load16_issue(lane_base + Config::kOutputColumn + d0, e[0]);
-        tmem_load16_issue(lane_base + Config::kOutputColumn + d0 + 16, e[1]);
-        if (any_odd) {
-          tmem_load16_issue(lane_base + Config::kOutputColumn + D + d0, o[0]);
-          tmem_load16_issue(lane_base + Config::kOutputColumn + D + d0 + 16, o[1]);
-        }
-        tmem_load_wait();
-        if (row < rows_here) {
+        for (int d0 = 0; d0 < D; d0 += 32) {
+          uint32_t r[2][16];
+          tmem_load16_issue(output_base + d0, r[0]);
+          tmem_load16_issue(output_base + d0 + 16, r[1]);
+          tmem_load_wait();
+          if (row < my_rows) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
+            for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int d = 0; d < 16; d += 8) {
-              uint4 packed;
-              __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+              for (int d = 0; d < 16; d += 8) {
+                uint4 packed;
+                __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                float x0 = __uint_as_float(e[h][d + 2 * i]) * scale_even;
-                float x1 = __uint_as_float(e[h][d + 2 * i + 1]) * scale_even;
-                if (use_odd) {
-                  x0 += __uint_as_float(o[h][d + 2 * i]) * scale_odd;
-                  x1 += __uint_as_float(o[h][d + 2 * i + 1]) * scale_odd;
-                }
-                pairs[i] = __floats2bfloat162_rn(x0, x1);
+                for (int i = 0; i < 4; ++i)
+                  pairs[i] = __floats2bfloat162_rn(__uint_as_float(r[h][d + 2 * i]) * inverse,
+                                                   __uint_as_float(r[h][d + 2 * i + 1]) * inverse);
+                *reinterpret_cast<uint4*>(out + d0 + h * 16 + d) = packed;
               }
-              *reinterpret_cast<uint4*>(out + d0 + h * 16 + d) = packed;
-            }
+          }
         }
       }
     }
@@ -642,7 +648,7 @@ HX_API int hx_prefill_attention_tc_supports(int head_dim, int page_size) {
          (page_size == 16 || page_size == 32 || page_size == 64);
 }
 
-// The arguments of hx_prefill_attention; tile_bound bounds the number of 128-token query tiles
+// The arguments of hx_prefill_attention; tile_bound bounds the number of 256-token query tiles
 // (a larger bound only launches CTAs that leave at once).
 HX_API int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache,
                                    const void* v_cache, const int* request_start,
