@@ -38,18 +38,30 @@ class Workspace:
 
     A buffer is created at its first use with the capacity the step function was
     built for and handed out again under the same name, so a captured CUDA graph can
-    be replayed against the same memory."""
+    be replayed against the same memory.  A buffer that has to be replaced (another
+    shape under the same name, a flat buffer that must grow) is kept alive beside its
+    successor: graphs recorded earlier still point at it, and it is as large as they
+    need."""
 
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self._buffers: Dict[str, torch.Tensor] = {}
         self._accumulators: Dict[str, torch.Tensor] = {}
+        self._retired: List[torch.Tensor] = []
+        self._retired_accumulators: List[torch.Tensor] = []
+
+    def _replace(self, table: Dict[str, torch.Tensor], name: str, buffer: torch.Tensor) -> None:
+        old = table.get(name)
+        if old is not None:
+            (self._retired_accumulators if table is self._accumulators
+             else self._retired).append(old)
+        table[name] = buffer
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         buffer = self._buffers.get(name)
         if buffer is None or buffer.dtype != dtype or tuple(buffer.shape) != tuple(shape):
             buffer = torch.empty(shape, dtype=dtype, device=self.device)
-            self._buffers[name] = buffer
+            self._replace(self._buffers, name, buffer)
         return buffer
 
     def accumulator(self, name: str, shape: Tuple[int, ...],
@@ -59,25 +71,29 @@ class Workspace:
         buffer = self._accumulators.get(name)
         if buffer is None or tuple(buffer.shape) != tuple(shape) or buffer.dtype != dtype:
             buffer = torch.zeros(shape, dtype=dtype, device=self.device)
-            self._accumulators[name] = buffer
+            self._replace(self._accumulators, name, buffer)
         return buffer
 
     def clear_accumulators(self) -> None:
         """After a step that failed half-way: restore the all-zero state."""
-        for buffer in self._accumulators.values():
+        for buffer in (*self._accumulators.values(), *self._retired_accumulators):
             buffer.zero_()
 
     def at_least(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
-        """A flat buffer of at least ``numel`` elements; it only ever grows."""
+        """A flat buffer of at least ``numel`` elements.  It grows by doubling at least, so
+        that the buffers it leaves behind stay a fraction of its size."""
         buffer = self._buffers.get(name)
         if buffer is None or buffer.dtype != dtype or buffer.numel() < numel:
+            if buffer is not None and buffer.dtype == dtype:
+                numel = max(numel, 2 * buffer.numel())
             buffer = torch.empty((numel,), dtype=dtype, device=self.device)
-            self._buffers[name] = buffer
+            self._replace(self._buffers, name, buffer)
         return buffer
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size()
-                   for t in (*self._buffers.values(), *self._accumulators.values()))
+                   for t in (*self._buffers.values(), *self._accumulators.values(),
+                             *self._retired, *self._retired_accumulators))
 
 
 @dataclasses.dataclass
