@@ -34,9 +34,10 @@
 // columns in 30 to 35 ns (measured: one to four threads issuing side by side each keep their
 // own rate until the pipe is full); one softmax group alone leaves its four schedulers waiting
 // on the latencies of tensor-memory loads and stores and on the exponential unit; and what a
-// CTA spends before its first and after its last tile (about 10 us: page table, first pages,
-// rewrite, the chain of first products; the last product, the output) is spent once for 256
-// rows, and every key tile is fetched and rewritten once for them.
+// CTA spends before its first and after its last tile (about 12 us: some 3 us until its first
+// loads from global memory are back, queries and page table alike, then first pages, rewrite,
+// the chain of first products; at the end the last product and the output) is spent once for
+// 256 rows, and every key tile is fetched and rewritten once for them.
 //
 // Operand layouts.  Nothing is swizzled: every operand is made of "core matrices" of 8 rows
 // x 16 bytes (128 contiguous bytes), which is exactly what a page block of the cache is made
@@ -161,7 +162,8 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   uint64_t* o_full = p_full + LANES * S_BUFFERS;      // [LANES][S_BUFFERS] its output product is done
   uint64_t* k_ready = o_full + LANES * S_BUFFERS;     // [KEY_BUFFERS] the tile's keys are rewritten
   uint64_t* k_done = k_ready + KEY_BUFFERS;           // [LANES][KEY_BUFFERS] a lane's scores have read them
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(k_done + LANES * KEY_BUFFERS);
+  uint64_t* q_ready = k_done + LANES * KEY_BUFFERS;   // the query tiles are in shared memory
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(q_ready + 1);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -200,6 +202,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     }
     for (int b = 0; b < KEY_BUFFERS; ++b) mbar_init(&k_ready[b], 1);
     for (int b = 0; b < LANES * KEY_BUFFERS; ++b) mbar_init(&k_done[b], 1);
+    mbar_init(q_ready, THREADS / 32 - WARP_SCORES);      // one arrival per warp that loads queries
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -207,23 +210,45 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   if (warp == WARP_SCORES) tmem_alloc(tmem_holder, Config::kTmemColumns);
   hx_pdl_wait();
 
-  // ---- the query tiles, by everybody: per lane [D / 8 pieces][16 row groups][8 rows][16 bytes]
-  for (int index = threadIdx.x; index < LANES * BLOCK_M * (D / 8); index += THREADS) {
-    const int row = index / (D / 8);      // among the CTA's 256
-    const int piece = index - row * (D / 8);
-    uint4 value = make_uint4(0u, 0u, 0u, 0u);
-    if (row < rows_here)
-      value = *reinterpret_cast<const uint4*>(a.q + static_cast<size_t>(q_begin + row0 + row) * a.ldq +
-                                              static_cast<size_t>(head) * D + piece * 8);
-    const int in_lane = row & (BLOCK_M - 1);
-    *reinterpret_cast<uint4*>(q_tile + (row / BLOCK_M) * Config::kQBytes + piece * CHUNK_STRIDE +
-                              (in_lane >> 3) * GROUP_STRIDE + (in_lane & 7) * 16) = value;
-  }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   tc_fence_before();
-  __syncthreads();
+  __syncthreads();      // barriers and tensor memory are there; nothing else is waited for here
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+
+  // ---- the query tiles: per lane [D / 8 pieces][16 row groups][8 rows][16 bytes], written by
+  // the warps from WARP_SCORES on while the first pages are on their way.  All of a thread's
+  // loads are in flight together (one after the other they cost the CTA 6 us).
+  if (warp >= WARP_SCORES) {
+    constexpr int kLoaders = THREADS - WARP_SCORES * 32;
+    constexpr int kPieces = LANES * BLOCK_M * (D / 8);
+    constexpr int kPerThread = (kPieces + kLoaders - 1) / kLoaders;
+    const int loader = threadIdx.x - WARP_SCORES * 32;
+    uint4 values[kPerThread];
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int index = loader + i * kLoaders;
+      const int row = index / (D / 8);      // among the CTA's 256
+      const int piece = index - row * (D / 8);
+      values[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (index < kPieces && row < rows_here)
+        values[i] = *reinterpret_cast<const uint4*>(
+            a.q + static_cast<size_t>(q_begin + row0 + row) * a.ldq + static_cast<size_t>(head) * D +
+            piece * 8);
+    }
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int index = loader + i * kLoaders;
+      const int row = index / (D / 8);
+      const int piece = index - row * (D / 8);
+      const int in_lane = row & (BLOCK_M - 1);
+      if (index < kPieces)
+        *reinterpret_cast<uint4*>(q_tile + (row / BLOCK_M) * Config::kQBytes + piece * CHUNK_STRIDE +
+                                  (in_lane >> 3) * GROUP_STRIDE + (in_lane & 7) * 16) = values[i];
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive(q_ready);
+  }
 
   if (warp == WARP_KEYS || warp == WARP_VALUES) {
     // ------------------------------------------------------------ page requests
@@ -369,6 +394,10 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       const int l = warp - WARP_SCORES;
       const int my_tiles = lane_tiles(l);
       const uint64_t desc_q = desc_q0 + l * (Config::kQBytes >> 4);
+      if (!mbar_wait(q_ready, 0)) {
+        atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
+        *failed = 1;
+      }
       for (int tile = 0; tile < my_tiles && !*failed; ++tile) {
         const int b = l * S_BUFFERS + tile % S_BUFFERS;
         if (!mbar_wait(&k_ready[tile % KEY_BUFFERS], static_cast<uint32_t>(tile / KEY_BUFFERS) & 1u) ||
