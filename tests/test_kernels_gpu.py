@@ -260,17 +260,31 @@ def rope_reference(x, positions, theta, rotary_dim, pairing):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim,pairing", [
     (4, 4, 16, 16, "adjacent"), (6, 2, 24, 24, "half_split"), (3, 1, 32, 16, "adjacent"),
-    (5, 5, 100, 100, "adjacent"), (2, 2, 48, 32, "half_split")])
-def test_rope_and_cache_append(dtype, heads, kv_heads, head_dim, rotary_dim, pairing):
+    (5, 5, 100, 100, "adjacent"), (2, 2, 48, 32, "half_split"),
+    (12, 12, 128, 128, "adjacent"), (48, 8, 64, 64, "adjacent"), (20, 10, 96, 64, "adjacent")])
+@pytest.mark.parametrize("long_portions", [False, True])
+def test_rope_and_cache_append(dtype, heads, kv_heads, head_dim, rotary_dim, pairing, long_portions):
     rng = np.random.default_rng(6)
-    page_size, num_pages, theta, max_positions = 8, 12, 50000.0, 96
-    # two requests: one continues at position 13 (inside a page), one starts at 0
-    positions = np.array([13, 14, 15, 16, 17, 0, 1, 2], dtype=np.int32)
-    token_request = np.array([0, 0, 0, 0, 0, 1, 1, 1], dtype=np.int32)
-    slots = np.array([2, 0], dtype=np.int32)
-    tables = np.full((3, 12), -1, dtype=np.int32)
-    tables[2, :3] = [7, 3, 9]
-    tables[0, :1] = [5]
+    theta, max_positions = 50000.0, 96
+    if not long_portions:
+        page_size, num_pages = 8, 12
+        # two requests: one continues at position 13 (inside a page), one starts at 0
+        positions = np.array([13, 14, 15, 16, 17, 0, 1, 2], dtype=np.int32)
+        token_request = np.array([0, 0, 0, 0, 0, 1, 1, 1], dtype=np.int32)
+        slots = np.array([2, 0], dtype=np.int32)
+        tables = np.full((3, 12), -1, dtype=np.int32)
+        tables[2, :3] = [7, 3, 9]
+        tables[0, :1] = [5]
+    else:
+        # portions of 37 and 21 tokens over several pages: one continues at position 13,
+        # inside a page
+        page_size, num_pages = 16, 12
+        positions = np.array(list(range(13, 50)) + list(range(0, 21)), dtype=np.int32)
+        token_request = np.array([0] * 37 + [1] * 21, dtype=np.int32)
+        slots = np.array([2, 0], dtype=np.int32)
+        tables = np.full((3, 6), -1, dtype=np.int32)
+        tables[2, :4] = [7, 3, 9, 1]
+        tables[0, :2] = [5, 10]
     tokens = len(positions)
     width = (heads + 2 * kv_heads) * head_dim
     qkv = rounded(rng.normal(size=(tokens, width)), dtype)
