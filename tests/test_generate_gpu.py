@@ -243,6 +243,40 @@ def test_graphs_recorded_before_the_scratch_grew_stay_valid(folders, plain_model
     engine.cache.check()
 
 
+def test_everything_at_once_under_page_pressure(folders, plain_models):
+    """Twenty requests with prompts of 20 to 300 tokens, half of them with a common beginning,
+    over a pool that holds three of them: requests wait, are preempted and recomputed, kept
+    prefixes are dropped under pressure, decode steps are replayed as graphs for ever new
+    subsets of requests and queued ahead where that is possible.  Every greedy token must be
+    the plain implementation's."""
+    plain = plain_models("C", "bfloat16")
+    vocab = tiny_config("C").vocab_size
+    rng = np.random.default_rng(5)
+    stem = random_tokens(vocab, 64, seed=99)
+    prompts = []
+    for index in range(20):
+        body = random_tokens(vocab, int(rng.integers(20, 301)), seed=400 + index)
+        prompts.append(stem + body if index % 2 == 0 else body)
+    engine = Engine.from_pretrained(folders("C", "bfloat16"), dtype="bfloat16", page_size=16,
+                                    max_running_requests=8, max_tokens_per_iteration=512,
+                                    max_prefill_chunk=128, num_pages=64, poison_free_pages=True,
+                                    prefix_cache_entries=4)
+    ids = [engine.submit(prompt, max_new_tokens=24, cache_namespace="x") for prompt in prompts]
+    engine.run_until_done()
+    engine.cache.check()
+    stats = engine.stats()
+    assert stats["scheduler"]["finished"] == 20 and stats["scheduler"]["failed"] == 0
+    assert stats["scheduler"]["preemptions"] > 0 and stats["scheduler"]["kv_limited_iterations"] > 0
+    assert stats["prefix"]["hits"] > 0 and stats["steps_queued_ahead"] > 0
+    assert engine.graphs.captures > 3
+    for prompt, request in zip(prompts, ids):
+        generated = engine.request(request).generated
+        assert len(generated) == 24
+        check_greedy(plain, prompt, generated, "bfloat16")
+    engine.prefix.clear()
+    assert all(group.pool.pages_in_use == 0 for group in engine.cache.groups)
+
+
 def test_bad_submissions_are_refused(folders):
     engine = Engine.from_pretrained(folders("A", "float32"), dtype="float32", page_size=8,
                                     max_running_requests=2, num_pages=4)
