@@ -300,9 +300,10 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       tensor_memory: Optional[bool] = None) -> None:
     """Tensor-core attention (bfloat16) of every request that brings at least
     ``min_query_len`` tokens; ``tile_bound`` bounds the number of query tiles of 64 tokens
-    (the tensor-memory kernel, whose tiles hold 128 tokens, needs no more).
-    ``tensor_memory``: take the tcgen05 kernel (scores and partial outputs in tensor memory;
-    pages of at least 16 keys) or the ``mma.sync`` kernel; default: tcgen05 where it applies."""
+    (the tensor-memory kernel, whose tiles hold 256 tokens, needs no more).
+    ``tensor_memory``: take the tcgen05 kernel (scores, probabilities and output in tensor
+    memory; pages of at least 16 keys) or the ``mma.sync`` kernel; default: tcgen05 where it
+    applies."""
     _need(q, torch.bfloat16, "q")
     _need(k_cache, torch.bfloat16, "k_cache")
     _need(out, torch.bfloat16, "out")
