@@ -930,6 +930,20 @@ HX_API long long hx_paged_attention_scratch_floats(int tokens, int heads, int he
   return by_split > by_warp ? by_split : by_warp;
 }
 
+// The same for a caller that says which case it has: the streaming kernel (bfloat16, head
+// sizes 64 and 128, pages of 8 to 32 keys, no window) needs its two parts per warp only,
+// whatever the number of tokens and splits.
+HX_API long long hx_paged_attention_scratch_floats_for(int dtype, int tokens, int heads,
+                                                       int head_dim, int page_size, int window,
+                                                       int max_splits) {
+  AttentionArgs a{};
+  a.head_dim = head_dim;
+  a.page_size = page_size;
+  a.window = window;
+  if (stream_kernel_applies(a, dtype)) return 2ll * STREAM_MAX_WARPS * (head_dim + 4);
+  return hx_paged_attention_scratch_floats(tokens, heads, head_dim, max_splits);
+}
+
 HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,
                               int dtype, const int* positions, const int* token_request,
                               const int* request_table_row, const int* block_tables,

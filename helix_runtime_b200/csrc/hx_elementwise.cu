@@ -37,7 +37,7 @@ void hx_count_launches(int kernels) { g_hx_launches.fetch_add(kernels, std::memo
 // counts once, when it is captured).
 HX_API long long hx_launch_count() { return g_hx_launches.load(std::memory_order_relaxed); }
 
-HX_API int hx_abi_version() { return 5; }
+HX_API int hx_abi_version() { return 6; }
 
 // ------------------------------------------------------------------- embedding
 

@@ -74,6 +74,8 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_prefill_attention_tc_supports.restype = _c_int
     library.hx_paged_attention_scratch_floats.restype = ctypes.c_longlong
     library.hx_paged_attention_scratch_floats.argtypes = [_c_int] * 4
+    library.hx_paged_attention_scratch_floats_for.restype = ctypes.c_longlong
+    library.hx_paged_attention_scratch_floats_for.argtypes = [_c_int] * 7
     library.hx_argmax.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]
     library.hx_sample.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr]
     library.hx_set_dependent_launch.argtypes = [_c_int]
@@ -251,8 +253,15 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tokens: int, fe
                             _stream()))
 
 
-def attention_scratch_floats(tokens: int, heads: int, head_dim: int, max_splits: int) -> int:
-    return int(lib().hx_paged_attention_scratch_floats(tokens, heads, head_dim, max_splits))
+def attention_scratch_floats(tokens: int, heads: int, head_dim: int, max_splits: int,
+                             dtype: Optional[torch.dtype] = None, page_size: int = 0,
+                             window: int = 0) -> int:
+    """Floats of scratch ``paged_attention`` needs; with ``dtype`` and ``page_size`` given, what
+    the kernel that will run for them needs (the streaming kernel: a fixed few megabytes)."""
+    if dtype is None:
+        return int(lib().hx_paged_attention_scratch_floats(tokens, heads, head_dim, max_splits))
+    return int(lib().hx_paged_attention_scratch_floats_for(
+        dtype_code(dtype), tokens, heads, head_dim, page_size, window, max_splits))
 
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -272,7 +281,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if arrivals is None:
         arrivals = torch.zeros(max(1, tokens * heads), dtype=torch.int32, device=q.device)
     if partial is None:
-        partial = torch.empty(attention_scratch_floats(tokens, heads, head_dim, max_splits),
+        partial = torch.empty(attention_scratch_floats(tokens, heads, head_dim, max_splits,
+                                                       q.dtype, page_size, window),
                               dtype=torch.float32, device=q.device)
     _check(lib().hx_paged_attention(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), dtype_code(q.dtype),

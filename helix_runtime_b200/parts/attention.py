@@ -141,7 +141,8 @@ class PagedAttention(Mixer):
             longest = ctx.max_context_len if not window else min(ctx.max_context_len, window)
             split_keys = self.split_keys_for(n, longest, ctx.attention_split_keys)
             max_splits = max(1, -(-longest // split_keys))
-            floats = ops.attention_scratch_floats(n, self.heads, self.head_dim, max_splits)
+            floats = ops.attention_scratch_floats(n, self.heads, self.head_dim, max_splits,
+                                                  ctx.dtype, cache.page_size, window)
             partial = ctx.workspace.at_least("attention.partial", floats, torch.float32)
             arrivals = ctx.workspace.accumulator("attention.arrivals",
                                                  (ctx.capacity * self.heads,), torch.int32)

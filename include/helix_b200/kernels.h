@@ -100,6 +100,9 @@ int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w, int l
 /* ---- attention over the paged cache ----------------------------------------------------- */
 int hx_cache_chunk_elements(int dtype, int head_dim);
 long long hx_paged_attention_scratch_floats(int tokens, int heads, int head_dim, int max_splits);
+/* the same when the caller says which case it has (the streaming kernel needs less) */
+long long hx_paged_attention_scratch_floats_for(int dtype, int tokens, int heads, int head_dim,
+                                                int page_size, int window, int max_splits);
 /* every query token over the keys [position - window + 1 (or 0), position] of its request */
 int hx_paged_attention(const void* q, int ldq, const void* k_cache, const void* v_cache, int dtype,
                        const int* positions, const int* token_request,
