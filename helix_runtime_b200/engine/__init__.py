@@ -1,12 +1,15 @@
 from .engine import (Engine, EngineConfig, GenerationResult, IterationResult, load_model,
                      parse_dtype, random_model, write_random_model)
+from .metrics import DurationStatistics, SchedulerMetrics, summarize_request_metrics
 from .scheduler import (FifoScheduler, IterationBatch, Request, RequestState, ScheduledWork,
                         SchedulerConfig, StopReason, WorkCompletion, WorkKind)
 from .step import StepEntry, StepError, StepFunction
 
 __all__ = [
-    "Engine", "EngineConfig", "FifoScheduler", "GenerationResult", "IterationBatch",
+    "DurationStatistics", "Engine", "EngineConfig", "FifoScheduler", "GenerationResult", "IterationBatch",
     "IterationResult", "Request", "RequestState", "ScheduledWork", "SchedulerConfig",
+    "SchedulerMetrics",
     "StepEntry", "StepError", "StepFunction", "StopReason", "WorkCompletion", "WorkKind",
-    "load_model", "parse_dtype", "random_model", "write_random_model",
+    "load_model", "parse_dtype", "random_model", "summarize_request_metrics",
+    "write_random_model",
 ]

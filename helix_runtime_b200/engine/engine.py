@@ -27,6 +27,7 @@ from ..ops import library as ops
 from .scheduler import (FifoScheduler, IterationBatch, Request, RequestState, SchedulerConfig,
                         StopReason, WorkCompletion, WorkKind)
 from .graphs import DecodeGraphs, bucketed_context
+from .metrics import SchedulerMetrics, summarize_request_metrics
 from .step import StepEntry, StepError, StepFunction
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -291,7 +292,8 @@ class Engine:
             batch = self.scheduler.schedule_iteration(self.cache, admit=self._admit,
                                                       release=self.cache.release,
                                                       reusable=self._reusable,
-                                                      reclaim=self._reclaim)
+                                                      reclaim=self._reclaim,
+                                                      now=time.monotonic())
             if batch is None:
                 return IterationResult(idle=True)
             flight = self._launch(batch, None)
@@ -459,6 +461,12 @@ class Engine:
                 cached_token_count=self._cached_at_finish.get(request_id, 0),
                 request_id=request_id))
         return results
+
+    def metrics(self, observed_at: Optional[float] = None) -> SchedulerMetrics:
+        """Counts, rates and latency distributions over every request this engine has seen
+        (include/helix/runtime/cpu_engine.hpp:91); times are ``time.monotonic()`` seconds."""
+        return summarize_request_metrics(self.scheduler.requests.values(),
+                                         time.monotonic() if observed_at is None else observed_at)
 
     def stats(self) -> Dict[str, object]:
         return {"scheduler": dict(self.scheduler.stats), "cache": self.cache.stats(),

@@ -74,8 +74,10 @@ class Request:
     error: Optional[str] = None
     preemptions: int = 0
     created_at: float = 0.0
+    first_scheduled_at: Optional[float] = None   # first time the request was given work
     first_token_at: Optional[float] = None
     finished_at: Optional[float] = None
+    token_times: List[float] = dataclasses.field(default_factory=list)   # per generated token
     resumed_from: int = 0              # generated tokens that were folded into the prompt
     namespace: Optional[str] = None    # prefix sharing: only prompts of one namespace share
     reused_tokens: int = 0             # tokens taken from the prefix index at (re)admission
@@ -84,6 +86,18 @@ class Request:
     def feed(self) -> List[int]:
         """Everything the model has to read before it can produce the next new token."""
         return self.prompt + self.generated
+
+    @property
+    def prompt_tokens_processed(self) -> int:
+        """Prompt tokens whose keys and values are in the cache (reused ones included)."""
+        return min(self.processed, len(self.prompt))
+
+    @property
+    def latest_event_at(self) -> float:
+        """The latest time anything was recorded for the request."""
+        return max(self.created_at, self.first_scheduled_at or self.created_at,
+                   self.token_times[-1] if self.token_times else self.created_at,
+                   self.finished_at or self.created_at)
 
     @property
     def feed_length(self) -> int:
@@ -218,8 +232,8 @@ class FifoScheduler:
                            admit: Callable[[int], None],
                            release: Callable[[int], None],
                            reusable: Optional[Callable[[Request], int]] = None,
-                           reclaim: Optional[Callable[[], bool]] = None
-                           ) -> Optional[IterationBatch]:
+                           reclaim: Optional[Callable[[], bool]] = None,
+                           now: float = 0.0) -> Optional[IterationBatch]:
         """Plan one iteration.  ``admit(id)`` / ``release(id)`` let the caller give a request
         its cache slot when it starts and take its pages back when it is preempted.
         ``reusable(request)`` says how many leading tokens admission will find in the cache
@@ -260,6 +274,9 @@ class FifoScheduler:
         for work in batch.work:
             key = "prefill_tokens" if work.kind is WorkKind.PREFILL else "decode_tokens"
             self.stats[key] += work.token_count
+            request = self.requests[work.request_id]
+            if request.first_scheduled_at is None:
+                request.first_scheduled_at = max(now, request.created_at)
         return batch
 
     def schedule_ahead(self, ledger: PageLedger, max_positions: int) -> Optional[IterationBatch]:
@@ -405,9 +422,10 @@ class FifoScheduler:
                 retired.append(request)
                 continue
             request.generated.append(int(completion.token))
+            request.token_times.append(max(now, request.latest_event_at))
             request.state = RequestState.DECODING
             if request.first_token_at is None:
-                request.first_token_at = now
+                request.first_token_at = request.token_times[-1]
             if request.eos_token is not None and completion.token == request.eos_token:
                 self._retire(request, RequestState.FINISHED, StopReason.EOS_TOKEN, now)
             elif request.remaining_generation == 0:
@@ -432,7 +450,7 @@ class FifoScheduler:
         request.state = state
         request.stop_reason = reason
         request.error = error
-        request.finished_at = now
+        request.finished_at = max(now, request.latest_event_at)
         if request.id in self.running:
             self.running.remove(request.id)
         if request.id in self.waiting:

@@ -274,6 +274,12 @@ def test_everything_at_once_under_page_pressure(folders, plain_models):
         generated = engine.request(request).generated
         assert len(generated) == 24
         check_greedy(plain, prompt, generated, "bfloat16")
+    metrics = engine.metrics()
+    assert metrics.finished_count == 20 and metrics.generated_tokens == 20 * 24
+    assert metrics.time_to_first_token.sample_count == 20
+    assert metrics.inter_token_latency.sample_count == 20 * 23
+    assert metrics.throughput_defined and metrics.generated_tokens_per_second > 0.0
+    assert metrics.waiting_time.maximum_seconds <= metrics.request_latency.maximum_seconds
     engine.prefix.clear()
     assert all(group.pool.pages_in_use == 0 for group in engine.cache.groups)
 
