@@ -157,6 +157,9 @@ class IterationResult:
     retired: List[int] = dataclasses.field(default_factory=list)
     preempted: List[int] = dataclasses.field(default_factory=list)
     kv_limited: bool = False
+    budget_exhausted: bool = False
+    free_pages_before: List[int] = dataclasses.field(default_factory=list)   # per cache group,
+    free_pages_after: List[int] = dataclasses.field(default_factory=list)    # around the iteration
     idle: bool = False
 
 
@@ -312,7 +315,9 @@ class Engine:
         result = flight.result
         result.preempted = list(batch.preempted)
         result.kv_limited = batch.kv_limited
+        result.budget_exhausted = batch.budget_exhausted
         result.scheduled_tokens = batch.scheduled_tokens
+        result.free_pages_before = self.cache.free_pages()
         entries = flight.entries
         temperatures: List[float] = []
         uniforms: List[float] = []
@@ -423,6 +428,7 @@ class Engine:
             if self.cache.has(request.id):
                 self._finish_cache(request.id)
             result.retired.append(request.id)
+        result.free_pages_after = self.cache.free_pages()
         return result
 
     def run_until_done(self, max_iterations: Optional[int] = None) -> int:
