@@ -109,6 +109,9 @@ def write_random_model(directory: str, config, seed: int, std: float = 0.02,
 class EngineConfig:
     page_size: int = 16
     num_pages: Optional[int] = None           # default: enough for max_running * max positions
+    cache_memory_fraction: Optional[float] = None   # instead of num_pages: this share of the
+                                              # device memory that is free once the weights are
+                                              # loaded goes to the cache pool
     max_running_requests: int = 8
     max_tokens_per_iteration: int = 2048
     max_prefill_chunk: Optional[int] = None
@@ -171,6 +174,16 @@ class Engine:
         kv_needs, state_needs = model.cache_needs()
         pages_per_request = -(-model.max_positions // config.page_size)
         num_pages = config.num_pages or pages_per_request * config.max_running_requests
+        if config.num_pages is None and config.cache_memory_fraction is not None:
+            if not 0.0 < config.cache_memory_fraction <= 1.0:
+                raise ValueError("cache_memory_fraction must be in (0, 1]")
+            element = torch.empty((), dtype=model.dtype).element_size()
+            page_bytes = sum(2 * need.kv_heads * need.head_dim * element * config.page_size
+                             for need in kv_needs.values())
+            free_bytes, _ = torch.cuda.mem_get_info(device)
+            num_pages = int(free_bytes * config.cache_memory_fraction) // max(page_bytes, 1)
+            if num_pages < 1:
+                raise ValueError("cache_memory_fraction leaves no room for a single page")
         self.cache = CacheManager(kv_needs, state_needs, config.page_size, num_pages,
                                   config.max_running_requests, model.max_positions, model.dtype,
                                   device, poison=config.poison_free_pages)

@@ -284,6 +284,21 @@ def test_everything_at_once_under_page_pressure(folders, plain_models):
     assert all(group.pool.pages_in_use == 0 for group in engine.cache.groups)
 
 
+def test_the_pool_can_be_sized_from_free_memory(folders, plain_models):
+    import torch
+    free_bytes, _ = torch.cuda.mem_get_info()
+    engine = Engine.from_pretrained(folders("A", "float32"), dtype="float32", page_size=8,
+                                    max_running_requests=2, cache_memory_fraction=0.001)
+    group = engine.cache.groups[0]
+    page_bytes = 2 * 2 * 4 * 16 * 4 * 8      # layers, keys and values, heads, head size, float32, page
+    assert abs(group.pool.num_pages * page_bytes - 0.001 * free_bytes) < 0.1 * 0.001 * free_bytes
+    prompt = [1, 42, 17, 5, 9]
+    assert engine.generate([prompt], max_new_tokens=6)[0].generated_tokens == \
+        plain_models("A", "float32").greedy(prompt, 6)
+    with pytest.raises(ValueError, match="cache_memory_fraction"):
+        Engine.from_pretrained(folders("A", "float32"), dtype="float32", cache_memory_fraction=1.5)
+
+
 def test_bad_submissions_are_refused(folders):
     engine = Engine.from_pretrained(folders("A", "float32"), dtype="float32", page_size=8,
                                     max_running_requests=2, num_pages=4)
