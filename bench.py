@@ -115,6 +115,48 @@ def reference_arm() -> int:
     return 0
 
 
+def serving_workload(options, model, config, rng) -> int:
+    """Continuous batching through the Python entry point, not part of the contract line:
+    ``--serving N`` requests with prompts of 128 to 2,048 tokens and 256 new tokens each, prompt
+    portions of 512 tokens interleaved with decoding, the cache pool sized from free memory
+    (the shape of the reference's largest serving benchmark).  Prints one JSON line."""
+    import torch
+
+    from helix_runtime_b200 import Engine, EngineConfig
+
+    requests = options.serving
+    prompts = [[int(t) for t in rng.integers(0, config.vocab_size, int(rng.integers(128, 2049)))]
+               for _ in range(requests)]
+    engine = Engine(model, EngineConfig(page_size=PAGE_SIZE, max_running_requests=min(requests, 64),
+                                        max_tokens_per_iteration=PREFILL_TOKENS,
+                                        max_prefill_chunk=512, cache_memory_fraction=0.5))
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    for prompt in prompts:
+        engine.submit(prompt, max_new_tokens=256)
+    iterations = engine.run_until_done()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - begin
+    metrics, stats = engine.metrics(), engine.stats()
+    print(json.dumps({
+        "metric": "serving: generated tokens/s over the whole run (Llama-2-7B shape, bf16)",
+        "value": round(metrics.generated_tokens / seconds, 1), "unit": "tokens/s",
+        "processed_tokens_per_s": round((metrics.generated_tokens
+                                         + metrics.prompt_tokens_processed) / seconds, 1),
+        "requests": requests, "seconds": round(seconds, 3), "iterations": iterations,
+        "prompt_tokens": metrics.prompt_tokens_processed,
+        "generated_tokens": metrics.generated_tokens,
+        "time_to_first_token_p50_p95_s": [round(metrics.time_to_first_token.p50_seconds, 3),
+                                          round(metrics.time_to_first_token.p95_seconds, 3)],
+        "inter_token_p50_p95_ms": [round(metrics.inter_token_latency.p50_seconds * 1e3, 2),
+                                   round(metrics.inter_token_latency.p95_seconds * 1e3, 2)],
+        "cache_pages": engine.cache.groups[0].pool.num_pages,
+        "steps_queued_ahead": stats["steps_queued_ahead"],
+        "graphs_recorded": engine.graphs.captures, "layers": config.num_hidden_layers,
+        "impl": "ours"}))
+    return 0
+
+
 def profile_region(options, model, config, fresh, rng) -> int:
     """One eager step (no CUDA graph) inside a profiler range: a decode step of ``--batch``
     requests at context ``--prompt-len``, or a prefill step of ``--prompt-len`` tokens."""
@@ -167,6 +209,9 @@ def main() -> int:
                         help="run one eager step of this kind between cudaProfilerStart/Stop "
                              "(for ncu --profile-from-start off) and print nothing else")
     parser.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    parser.add_argument("--serving", type=int, default=0, metavar="REQUESTS",
+                        help="run a continuous-batching workload of this many requests instead "
+                             "and print its own JSON line")
     parser.add_argument("--log-dir", default=None,
                         help="where the clock samples of the timed region are kept "
                              "(default: a temporary folder)")
@@ -255,6 +300,8 @@ def main() -> int:
 
     if options.profile is not None:
         return profile_region(options, model, config, fresh, rng)
+    if options.serving:
+        return serving_workload(options, model, config, rng)
 
     # ------------------------------------------------------------------ decode, batch B
     sampler_clock = ClockSampler(os.path.join(out_dir, "bench_clocks.csv"))

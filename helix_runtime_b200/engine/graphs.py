@@ -9,7 +9,9 @@ synchronises inside a step.
 
 A graph is keyed by everything that is baked into its launches: the number of tokens, the
 number of wanted rows, the context length attention was launched for (rounded up to a
-bucket, so that one graph serves 256 consecutive steps), and whether sampling is greedy.
+bucket, so that one graph serves hundreds of consecutive steps), and whether sampling is
+greedy.  A key is recorded when it has come up a few times: while requests join one by one,
+batch sizes pass that are never seen again.
 """
 from __future__ import annotations
 
@@ -20,11 +22,18 @@ import torch
 from ..parts.base import StepContext
 
 
-CONTEXT_BUCKET = 256     # decode steps are prepared for a context rounded up to this
+CONTEXT_BUCKET = 256     # decode steps are prepared for a context of this times a power of two
+RECORD_AT_USE = 3        # a key is recorded when it comes up for this many times
 
 
 def bucketed_context(length: int) -> int:
-    return -(-length // CONTEXT_BUCKET) * CONTEXT_BUCKET
+    """The context length a decode step is prepared for: 256, 512, 1024, ...  What is sized by
+    it (the bound of the attention's grid, the key splits of the float32 kernel) costs little
+    when it is too large, and every bucket is a graph to record."""
+    bucket = CONTEXT_BUCKET
+    while bucket < length:
+        bucket *= 2
+    return bucket
 
 
 class DecodeGraphs:
@@ -36,6 +45,7 @@ class DecodeGraphs:
         self._stream = torch.cuda.Stream(device=step_function.device)
         self.replays = 0
         self.captures = 0
+        self._uses: Dict[Tuple, int] = {}
         self.kernels_per_graph: Dict[Tuple[int, int, int, bool], int] = {}
 
     def key_for(self, ctx: StepContext, n_want: int, greedy: bool) -> Tuple[int, int, int, bool]:
@@ -70,7 +80,9 @@ class DecodeGraphs:
             return tokens
 
         tokens = body()                      # eager: gives this step's result, sizes workspaces
-        if len(self._graphs) < self.max_graphs and not advance:
+        self._uses[key] = self._uses.get(key, 0) + 1
+        if (len(self._graphs) < self.max_graphs and not advance
+                and self._uses[key] >= RECORD_AT_USE):
             self._capture(key, body)
         return tokens
 
@@ -93,10 +105,19 @@ class DecodeGraphs:
     def _capture(self, key, body) -> torch.cuda.CUDAGraph:
         from ..ops import library as ops
         graph = torch.cuda.CUDAGraph()
-        torch.cuda.current_stream().synchronize()
+        current = torch.cuda.current_stream()
         before = ops.launch_count()
-        with torch.cuda.graph(graph, stream=self._stream):
-            body()
+        # capture_begin / capture_end directly: the body allocates nothing (the eager run before
+        # it has sized every buffer), so the collector run and the emptying of the allocator's
+        # cache that the context manager brings along, tens of milliseconds, buy nothing here
+        self._stream.wait_stream(current)
+        with torch.cuda.stream(self._stream):
+            graph.capture_begin()
+            try:
+                body()
+            finally:
+                graph.capture_end()
+        current.wait_stream(self._stream)
         self.kernels_per_graph[key] = ops.launch_count() - before
         self._graphs[key] = graph
         self.captures += 1

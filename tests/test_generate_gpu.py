@@ -9,6 +9,7 @@ import sys
 
 import numpy as np
 import pytest
+import torch
 
 from conftest import ROOT, random_tokens
 from helix_runtime_b200 import Engine
@@ -217,8 +218,8 @@ def test_steps_queued_ahead_change_nothing(name, dtype, folders, plain_models):
 def test_graphs_recorded_before_the_scratch_grew_stay_valid(folders, plain_models):
     """A decode graph is recorded while the attention scratch is small; a large mixed step then
     makes the scratch grow (the float32 kernel keeps a part per key split of every row),
-    further graphs are recorded (which lets the allocator hand unused memory back to the
-    driver), and the first graph is replayed again.  The buffer it points at must still be
+    further graphs are recorded, the allocator is told to hand unused memory back to the
+    driver, and the first graph is replayed again.  The buffer it points at must still be
     there."""
     plain = plain_models("B", "float32")
     vocab = tiny_config("B").vocab_size
@@ -233,7 +234,10 @@ def test_graphs_recorded_before_the_scratch_grew_stay_valid(folders, plain_model
     before = workspace.bytes()
     others = [engine.submit(random_tokens(vocab, 200, seed=10 + index), max_new_tokens=4)
               for index in range(4)]
-    engine.run_until_done()                          # mixed step, five-token graphs, alone again
+    while any(not engine.request(other).is_terminal for other in others):
+        engine.run_iteration()                       # mixed step, five-token graphs
+    torch.cuda.empty_cache()
+    engine.run_until_done()                          # alone again: the first graph
     assert workspace._retired, "the scratch did not grow: the test no longer tests anything"
     assert workspace.bytes() > before
     assert engine.graphs.captures >= 2 and engine.graphs.replays > 20
