@@ -106,10 +106,11 @@ class StepFunction:
                 raise StepError(f"request {entry.request!r} is not admitted to the cache")
             if len(entry.tokens) == 0:
                 raise StepError(f"request {entry.request!r} brings no tokens")
-            for token in entry.tokens:
-                if not 0 <= int(token) < vocab:
-                    raise StepError(f"token id {token} of request {entry.request!r} is outside "
-                                    f"the vocabulary of {vocab}")
+            ids = np.asarray(entry.tokens, dtype=np.int64)
+            if ids.ndim != 1 or int(ids.min()) < 0 or int(ids.max()) >= vocab:
+                bad = [int(t) for t in ids.reshape(-1) if not 0 <= int(t) < vocab][:1]
+                raise StepError(f"token id {bad[0] if bad else '?'} of request {entry.request!r} "
+                                f"is outside the vocabulary of {vocab}")
             for place in entry.want:
                 if not 0 <= int(place) < len(entry.tokens):
                     raise StepError(f"wanted place {place} of request {entry.request!r} is "
