@@ -14,8 +14,8 @@
 //  * the CUDA-core kernel takes every dtype, head size, page size and window: per chunk of
 //    32 keys, lane j owns key j for the score and a slice of the head dimension for the
 //    weighted value sum, all in float32;
-//  * the streaming kernel (bfloat16, head sizes 64 and 128, pages of 8, 16 or 32 keys, no
-//    window) is what decoding runs.  The keys of a (page, head) are one contiguous block of
+//  * the streaming kernel (bfloat16, head sizes in steps of 16 up to 128 and of 32 up to
+//    256, pages of 8, 16 or 32 keys, no window) is what decoding runs.  The keys of a (page, head) are one contiguous block of
 //    the cache and so are its values, so a 32-key chunk is fetched with a few bulk copies
 //    (cp.async.bulk counted on an mbarrier) into a ring of shared-memory slots that belongs
 //    to the warp, and both products run on the tensor cores straight out of those slots: the
@@ -390,19 +390,27 @@ __device__ __forceinline__ void cursor_next(const AttentionArgs& a, ChunkCursor&
 template <typename T, int D, int STRIDE>
 __device__ void merge_parts(const AttentionArgs& a, int token, int head, long long row_begin,
                             long long per_warp, int first_warp, int n_parts, int lane) {
-  constexpr int PER_LANE = D / 32;      // consecutive coordinates per lane (2 or 4)
+  // Coordinates per lane: four consecutive ones for a head of 128; otherwise pairs, the
+  // i-th pair of a lane at coordinate 2 lane + 64 i (lanes beyond the head hold zeros).
+  constexpr bool QUADS = D == 128;
+  constexpr int PER_LANE = QUADS ? 4 : 2 * ((D + 63) / 64);
   auto part_of = [&](int index) {
     const long long w = first_warp + index;
     const int slot = row_begin <= w * per_warp ? 0 : 1;
     return a.partial + static_cast<size_t>(w * 2 + slot) * STRIDE;
   };
   auto load_slice = [&](const float* part, float (&o)[PER_LANE]) {
-    if constexpr (PER_LANE == 4) {
+    if constexpr (QUADS) {
       const float4 v = __ldcg(reinterpret_cast<const float4*>(part + 4 * lane));
       o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
     } else {
-      const float2 v = __ldcg(reinterpret_cast<const float2*>(part + 2 * lane));
-      o[0] = v.x; o[1] = v.y;
+#pragma unroll
+      for (int i = 0; i < PER_LANE; i += 2) {
+        const int d = 2 * lane + 32 * i;
+        float2 v = make_float2(0.0f, 0.0f);
+        if (d < D) v = __ldcg(reinterpret_cast<const float2*>(part + d));
+        o[i] = v.x; o[i + 1] = v.y;
+      }
     }
   };
   float total_max = -INFINITY;
@@ -448,11 +456,14 @@ __device__ void merge_parts(const AttentionArgs& a, int token, int head, long lo
   }
   const float inverse = 1.0f / total_sum;
   T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
-           static_cast<size_t>(head) * D + PER_LANE * lane;
+           static_cast<size_t>(head) * D;
 #pragma unroll
-  for (int i = 0; i < PER_LANE; i += 2)
-    *reinterpret_cast<__nv_bfloat162*>(out + i) =
-        __floats2bfloat162_rn(acc[i] * inverse, acc[i + 1] * inverse);
+  for (int i = 0; i < PER_LANE; i += 2) {
+    const int d = QUADS ? 4 * lane + i : 2 * lane + 32 * i;
+    if (d < D)
+      *reinterpret_cast<__nv_bfloat162*>(out + d) =
+          __floats2bfloat162_rn(acc[i] * inverse, acc[i + 1] * inverse);
+  }
 }
 
 // The flat list of chunks is cut into equal runs, one per warp of the grid, so a warp's run
@@ -880,13 +891,29 @@ int launch_stream(const AttentionArgs& a, cudaStream_t stream) {
 }
 
 bool stream_kernel_applies(const AttentionArgs& a, int dtype) {
-  return dtype == HX_BF16 && (a.head_dim == 64 || a.head_dim == 128) && a.window == 0 &&
+  return dtype == HX_BF16 && a.head_dim >= 16 && a.head_dim <= 256 &&
+         a.head_dim % (a.head_dim <= 128 ? 16 : 32) == 0 && a.window == 0 &&
          (a.page_size == 8 || a.page_size == 16 || a.page_size == 32);
 }
 
 int launch_stream_for(const AttentionArgs& a, cudaStream_t stream) {
   // 32-key chunks: the largest page the kernel takes is one block of the cache
-  return a.head_dim == 128 ? launch_stream<128, 32>(a, stream) : launch_stream<64, 32>(a, stream);
+  switch (a.head_dim) {
+    case 16: return launch_stream<16, 32>(a, stream);
+    case 32: return launch_stream<32, 32>(a, stream);
+    case 48: return launch_stream<48, 32>(a, stream);
+    case 64: return launch_stream<64, 32>(a, stream);
+    case 80: return launch_stream<80, 32>(a, stream);
+    case 96: return launch_stream<96, 32>(a, stream);
+    case 112: return launch_stream<112, 32>(a, stream);
+    case 128: return launch_stream<128, 32>(a, stream);
+    case 160: return launch_stream<160, 32>(a, stream);
+    case 192: return launch_stream<192, 32>(a, stream);
+    case 224: return launch_stream<224, 32>(a, stream);
+    case 256: return launch_stream<256, 32>(a, stream);
+  }
+  hx_set_error("hx_paged_attention: no streaming kernel for head_dim %d", a.head_dim);
+  return HX_ERR_UNSUPPORTED;
 }
 
 template <typename T>
@@ -931,7 +958,7 @@ HX_API long long hx_paged_attention_scratch_floats(int tokens, int heads, int he
 }
 
 // The same for a caller that says which case it has: the streaming kernel (bfloat16, head
-// sizes 64 and 128, pages of 8 to 32 keys, no window) needs its two parts per warp only,
+// sizes in steps of 16 up to 128 and of 32 up to 256, pages of 8 to 32 keys, no window) needs its two parts per warp only,
 // whatever the number of tokens and splits.
 HX_API long long hx_paged_attention_scratch_floats_for(int dtype, int tokens, int heads,
                                                        int head_dim, int page_size, int window,

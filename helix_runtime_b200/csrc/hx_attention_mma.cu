@@ -88,8 +88,10 @@ __device__ __forceinline__ uint32_t piece_offset(int key, int c, int page_size,
   return (key / page_size) * page_bytes + ((c * page_size + key % page_size) << 4);
 }
 
+// CTAs per SM the register budget is set for: three up to a head size of 128, one above
+// (the output accumulator of a thread is D / 2 floats).
 template <int D>
-__global__ __launch_bounds__(THREADS, 3) void prefill_attention_kernel(PrefillArgs a) {
+__global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_kernel(PrefillArgs a) {
   constexpr int kHalfBytes = BLOCK_N * D * 2;      // keys (or values) of a 64-key tile
   constexpr int kDSteps = D / 16;                  // k-steps of Q K^T
   constexpr int kOBlocks = D / 8;                  // n-blocks of the output
@@ -387,7 +389,7 @@ int launch(const PrefillArgs& a, int tiles, cudaStream_t stream) {
 
 // 1 when the tensor-core kernel takes this head size and page size (bfloat16 only).
 HX_API int hx_prefill_attention_supports(int head_dim, int page_size) {
-  return (head_dim == 64 || head_dim == 128) &&
+  return head_dim >= 16 && head_dim <= 256 && head_dim % (head_dim <= 128 ? 16 : 32) == 0 &&
          (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
 }
 
@@ -402,8 +404,8 @@ HX_API int hx_prefill_attention(const void* q, int ldq, const void* k_cache, con
                                 int num_pages, float scale, int min_query_len, int* status,
                                 cudaStream_t stream) {
   HX_REQUIRE(hx_prefill_attention_supports(head_dim, page_size),
-             "hx_prefill_attention: head_dim %d with pages of %d is not supported (head sizes 64 "
-             "and 128, pages of 8, 16, 32 or 64)", head_dim, page_size);
+             "hx_prefill_attention: head_dim %d with pages of %d is not supported (head sizes in "
+             "steps of 16 up to 128 and of 32 up to 256, pages of 8, 16, 32 or 64)", head_dim, page_size);
   HX_REQUIRE(requests >= 0 && tile_bound >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
              "hx_prefill_attention: bad sizes");
   HX_REQUIRE(heads <= 65535, "hx_prefill_attention: too many heads");
@@ -420,8 +422,21 @@ HX_API int hx_prefill_attention(const void* q, int ldq, const void* k_cache, con
                 static_cast<const __nv_bfloat16*>(v_cache), request_start, request_context,
                 request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(out),
                 ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status};
-  const int rc = head_dim == 128 ? launch<128>(a, tile_bound, stream)
-                                 : launch<64>(a, tile_bound, stream);
+  int rc = HX_ERR_UNSUPPORTED;
+  switch (head_dim) {
+    case 16: rc = launch<16>(a, tile_bound, stream); break;
+    case 32: rc = launch<32>(a, tile_bound, stream); break;
+    case 48: rc = launch<48>(a, tile_bound, stream); break;
+    case 64: rc = launch<64>(a, tile_bound, stream); break;
+    case 80: rc = launch<80>(a, tile_bound, stream); break;
+    case 96: rc = launch<96>(a, tile_bound, stream); break;
+    case 112: rc = launch<112>(a, tile_bound, stream); break;
+    case 128: rc = launch<128>(a, tile_bound, stream); break;
+    case 160: rc = launch<160>(a, tile_bound, stream); break;
+    case 192: rc = launch<192>(a, tile_bound, stream); break;
+    case 224: rc = launch<224>(a, tile_bound, stream); break;
+    case 256: rc = launch<256>(a, tile_bound, stream); break;
+  }
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_prefill_attention");
   return HX_OK;

@@ -12,6 +12,15 @@ pairs, the rows of q and k are permuted per head to ``[0, D/2, 1, D/2+1, ...]``
 (the reference's converter does the same, tools/convert_hf_llama.py:535-542).
 Steps: fused projection, rotary encoding + cache append, paged attention, output
 projection added into the residual (src/model/cpu_llama.cpp:65-91).
+
+A head whose size is no multiple of 16 (100, say) is held in rows of the next multiple
+(``row_dim``): the projection gets zero rows for the extra coordinates of every head and
+the output projection zero columns, so queries, keys and values carry exact zeros there,
+scores and outputs are unchanged, and the tensor-core attention kernels, which tile the
+head in steps of 16, take the head.  The scale stays ``1/sqrt(head_dim)`` and the rotation
+covers the real coordinates only.  This needs a position encoding that takes a row width
+of its own (``row_dim``); with one that does not, the head keeps its size and the
+CUDA-core attention runs.
 """
 from __future__ import annotations
 
@@ -30,6 +39,7 @@ from .linear import (STREAMING_MAX_TOKENS, Weight, is_weight_stream, project,
 
 
 TENSOR_CORE_MIN_QUERY = 16
+HEAD_STEP = 16      # the tensor-core attention kernels tile a head in steps of this
 
 
 def rotary_row_permutation(heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
@@ -55,27 +65,47 @@ class PagedAttention(Mixer):
         self.scale = float(spec.get("scale") or 1.0 / math.sqrt(float(self.head_dim)))
         window = spec.get("window")
         self.window: Optional[int] = int(window) if window else None
+        self.row_dim = self.head_dim
         self.position = build_part("position", spec["position"], hidden_size)
+        if self.head_dim % HEAD_STEP:
+            wide = -(-self.head_dim // HEAD_STEP) * HEAD_STEP
+            position = spec["position"]
+            padded = build_part("position", PartSpec(position.kind,
+                                                     {**position.params, "row_dim": wide},
+                                                     position.tensors), hidden_size)
+            if getattr(padded, "row_dim", None) == wide:
+                self.position, self.row_dim = padded, wide
         self.checkpoint_pairing = spec.get("checkpoint_pairing", self.position.pairing)
         self.names = dict(spec.tensors)
-        self.q_size = self.heads * self.head_dim
-        self.kv_size = self.kv_heads * self.head_dim
+        # widths of the checkpoint's matrices and of the rows this part computes with
+        self.q_rows = self.heads * self.head_dim
+        self.kv_rows = self.kv_heads * self.head_dim
+        self.q_size = self.heads * self.row_dim
+        self.kv_size = self.kv_heads * self.row_dim
         self.qkv_size = self.q_size + 2 * self.kv_size
         self.w_qkv: Optional[Weight] = None
         self.w_o: Optional[Weight] = None
 
     def kv_need(self) -> Optional[KvNeed]:
-        return KvNeed(self.kv_heads, self.head_dim, self.window)
+        return KvNeed(self.kv_heads, self.row_dim, self.window)
 
     def tensor_requests(self) -> List[TensorRequest]:
         h = self.hidden_size
         return [
-            TensorRequest(self.names["q"], (self.q_size, h)),
-            TensorRequest(self.names["k"], (self.kv_size, h)),
-            TensorRequest(self.names["v"], (self.kv_size, h)),
-            TensorRequest(self.names["o"], (h, self.q_size)),
+            TensorRequest(self.names["q"], (self.q_rows, h)),
+            TensorRequest(self.names["k"], (self.kv_rows, h)),
+            TensorRequest(self.names["v"], (self.kv_rows, h)),
+            TensorRequest(self.names["o"], (h, self.q_rows)),
             *self.position.tensor_requests(),
         ]
+
+    def widen_rows(self, matrix: torch.Tensor, heads: int) -> torch.Tensor:
+        """``[heads * head_dim, in]`` to ``[heads * row_dim, in]``: zero rows behind each head."""
+        if self.row_dim == self.head_dim:
+            return matrix
+        wide = matrix.new_zeros((heads, self.row_dim, matrix.shape[1]))
+        wide[:, :self.head_dim] = matrix.reshape(heads, self.head_dim, matrix.shape[1])
+        return wide.reshape(heads * self.row_dim, matrix.shape[1])
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
         q = tensors[self.names["q"]]
@@ -90,8 +120,11 @@ class PagedAttention(Mixer):
             else:
                 raise ValueError(f"no row permutation from {self.checkpoint_pairing!r} to "
                                  f"{self.position.pairing!r}")
+        q, k, v = (self.widen_rows(q, self.heads), self.widen_rows(k, self.kv_heads),
+                   self.widen_rows(v, self.kv_heads))
+        o = self.widen_rows(tensors[self.names["o"]].t().contiguous(), self.heads).t()
         self.w_qkv = Weight(torch.cat([q, k, v], dim=0).to(device=device, dtype=dtype).contiguous())
-        self.w_o = Weight(tensors[self.names["o"]].to(device=device, dtype=dtype).contiguous())
+        self.w_o = Weight(o.to(device=device, dtype=dtype).contiguous())
         self.position.bind(tensors, dtype, device)
 
     def weight_bytes(self) -> int:
@@ -130,25 +163,25 @@ class PagedAttention(Mixer):
         # to the CUDA-core kernel.  A step may need both.
         tensor_cores = (ctx.dtype == torch.bfloat16 and not window
                         and ctx.max_query_len >= TENSOR_CORE_MIN_QUERY
-                        and ops.prefill_attention_supports(self.head_dim, cache.page_size))
+                        and ops.prefill_attention_supports(self.row_dim, cache.page_size))
         if tensor_cores:
             ops.prefill_attention(qkv, cache.keys, cache.values, ctx.request_start,
                                   ctx.request_context, ctx.request_slot, cache.block_tables,
                                   context, ctx.n_requests, n // 64 + ctx.n_requests, self.heads,
-                                  self.kv_heads, self.head_dim, cache.page_size, cache.num_pages,
+                                  self.kv_heads, self.row_dim, cache.page_size, cache.num_pages,
                                   self.scale, TENSOR_CORE_MIN_QUERY, ctx.status)
         if not tensor_cores or ctx.min_query_len < TENSOR_CORE_MIN_QUERY:
             longest = ctx.max_context_len if not window else min(ctx.max_context_len, window)
             split_keys = self.split_keys_for(n, longest, ctx.attention_split_keys)
             max_splits = max(1, -(-longest // split_keys))
-            floats = ops.attention_scratch_floats(n, self.heads, self.head_dim, max_splits,
+            floats = ops.attention_scratch_floats(n, self.heads, self.row_dim, max_splits,
                                                   ctx.dtype, cache.page_size, window)
             partial = ctx.workspace.at_least("attention.partial", floats, torch.float32)
             arrivals = ctx.workspace.accumulator("attention.arrivals",
                                                  (ctx.capacity * self.heads,), torch.int32)
             ops.paged_attention(qkv, cache.keys, cache.values, ctx.positions, ctx.token_request,
                                 ctx.request_slot, cache.block_tables, context, partial, n,
-                                self.heads, self.kv_heads, self.head_dim, cache.page_size,
+                                self.heads, self.kv_heads, self.row_dim, cache.page_size,
                                 cache.num_pages, window, self.scale, split_keys, max_splits,
                                 ctx.status, request_start=ctx.request_start,
                                 skip_query_len=TENSOR_CORE_MIN_QUERY if tensor_cores else 0,

@@ -1,6 +1,8 @@
 """Rotary position encoding with the cache append fused into the same kernel.
 
 Parameters: ``theta``, ``head_dim``, ``rotary_dim`` (default: all of the head),
+``row_dim`` (default ``head_dim``: the width a head has in the projected rows and in the
+cache; the coordinates from ``head_dim`` on are carried along unrotated),
 ``pairing`` (``adjacent``: pairs ``(2p, 2p+1)`` as the reference rotates,
 src/kernels/cpu/reference.cpp:519-531; ``half_split``: pairs ``(p, p + rotary_dim/2)``),
 ``max_positions``.  The cos/sin table ``[max_positions, rotary_dim/2]`` is built once
@@ -26,6 +28,9 @@ class RotaryEncoding(PositionEncoding):
         self.theta = float(spec["theta"])
         self.head_dim = int(spec["head_dim"])
         self.rotary_dim = int(spec.get("rotary_dim", self.head_dim))
+        self.row_dim = int(spec.get("row_dim", self.head_dim))
+        if self.row_dim < self.head_dim:
+            raise ValueError("row_dim must be at least head_dim")
         self.max_positions = int(spec["max_positions"])
         pairing = spec.get("pairing", "adjacent")
         if pairing not in PAIRINGS:
@@ -57,7 +62,7 @@ class RotaryEncoding(PositionEncoding):
         ops.rope_append(qkv, ctx.positions, ctx.token_request, ctx.request_slot,
                         cache.block_tables, cache.keys if write else None,
                         cache.values if write else None, self.cos, self.sin, ctx.n_tokens, heads,
-                        kv_heads, self.head_dim, self.rotary_dim, PAIRINGS[self.pairing],
+                        kv_heads, self.row_dim, self.rotary_dim, PAIRINGS[self.pairing],
                         cache.page_size, cache.num_pages, ctx.status, accum=accum)
 
 

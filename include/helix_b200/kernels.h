@@ -119,7 +119,8 @@ int hx_paged_attention_no_alloc(const void* q, int ldq, const void* k_cache, con
                                 void* out, int ldo, int tokens, int heads, int kv_heads,
                                 int head_dim, int page_size, int num_pages, int window, float scale,
                                 int split_keys, int max_splits, int* status, cudaStream_t stream);
-/* prompt portions on the tensor cores (bfloat16, head sizes 64 and 128) */
+/* prompt portions on the tensor cores (bfloat16, head sizes in steps of 16 up to 128 and of
+   32 up to 256) */
 int hx_prefill_attention_supports(int head_dim, int page_size);
 int hx_prefill_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,
                          const int* request_start, const int* request_context,

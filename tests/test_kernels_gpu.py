@@ -471,12 +471,13 @@ def test_paged_attention_mixed_batch(dtype, heads, kv_heads, head_dim, page_size
     assert_close(out, expected, "attention", **tol)
 
 
-def test_streaming_attention_row_shared_by_hundreds_of_warps():
+@pytest.mark.parametrize("head_dim", [128, 112, 48, 256])
+def test_streaming_attention_row_shared_by_hundreds_of_warps(head_dim):
     """One decode token over 30,000 keys: each of its rows is cut into a few hundred parts
     (more than one merge batch), and one key far inside takes all the weight."""
     rng = np.random.default_rng(21)
     key_position = 12345
-    out, expected, values, *_ = attention_case(rng, torch.bfloat16, 2, 2, 128, 16, [29999], [1],
+    out, expected, values, *_ = attention_case(rng, torch.bfloat16, 2, 2, head_dim, 16, [29999], [1],
                                                window=None, split_keys=64,
                                                dominant={0: key_position})
     assert_close(out, expected, "attention", atol=2e-2, rtol=8e-3)
@@ -484,7 +485,9 @@ def test_streaming_attention_row_shared_by_hundreds_of_warps():
     assert_close(out, wanted, "dominant key's value", atol=2e-2, rtol=1e-2)
 
 
-@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [(3, 3, 64, 8), (4, 2, 128, 32)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [
+    (3, 3, 64, 8), (4, 2, 128, 32), (2, 2, 16, 8), (3, 1, 48, 16), (2, 2, 80, 32), (4, 2, 96, 8),
+    (2, 1, 112, 16), (2, 2, 160, 16), (1, 1, 192, 32), (2, 1, 224, 8), (1, 1, 256, 32)])
 def test_streaming_attention_many_requests_of_mixed_length(heads, kv_heads, head_dim, page_size):
     """Seventy requests (more than one group of 32 tokens) with contexts from 0 to 700 keys,
     most decoding one token, some bringing two or three: runs of chunks cross rows, tokens
@@ -536,11 +539,13 @@ def test_one_far_key_stands_out(dtype, key_position):
 
 @pytest.mark.parametrize("tensor_memory", [False, True])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [
-    (4, 4, 128, 16), (6, 2, 64, 8), (3, 1, 128, 32), (2, 2, 64, 64), (2, 1, 64, 16)])
+    (4, 4, 128, 16), (6, 2, 64, 8), (3, 1, 128, 32), (2, 2, 64, 64), (2, 1, 64, 16),
+    (3, 3, 16, 8), (2, 1, 32, 64), (5, 1, 48, 16), (2, 2, 80, 32), (3, 1, 96, 16), (2, 2, 112, 16),
+    (2, 1, 160, 16), (1, 1, 192, 8), (2, 2, 224, 32), (2, 1, 256, 32)])
 def test_tensor_core_attention_for_prompt_portions(heads, kv_heads, head_dim, page_size,
                                                    tensor_memory):
     if tensor_memory and not ops.prefill_attention_tc_supports(head_dim, page_size):
-        pytest.skip("the tcgen05 kernel needs pages of at least 16 keys")
+        pytest.skip("the tcgen05 kernel takes heads of 64 and 128 and pages of at least 16 keys")
     rng = np.random.default_rng(12)
     # whole prompts (one longer than two tiles, one a single row short of a tile), continued
     # portions that start inside a page and inside a key tile, and two decode tokens that the
@@ -568,9 +573,11 @@ def test_tensor_core_attention_sees_one_far_key(key_position, tensor_memory):
 
 def test_tensor_core_attention_refuses_what_it_cannot_tile():
     assert ops.prefill_attention_supports(128, 16) and ops.prefill_attention_supports(64, 64)
-    # pages of 4 or 24 keys do not tile its 64-key steps, and a head of 80 is not built: the
-    # mixer then takes the CUDA-core kernel, and a direct call is an error, not a wrong result
-    for head_dim, page_size in ((64, 4), (128, 24), (80, 16)):
+    assert ops.prefill_attention_supports(80, 16) and ops.prefill_attention_supports(256, 8)
+    # pages of 4 or 24 keys do not tile its 64-key steps, and heads of 72 or 144 are not built:
+    # the mixer then takes the CUDA-core kernel, and a direct call is an error, not a wrong
+    # result
+    for head_dim, page_size in ((64, 4), (128, 24), (72, 16), (144, 16), (8, 16), (288, 16)):
         assert not ops.prefill_attention_supports(head_dim, page_size)
     q = torch.zeros((16, 2 * 64), dtype=torch.bfloat16, device=DEVICE)
     cache = torch.zeros((8, 2, 4, 64), dtype=torch.bfloat16, device=DEVICE)

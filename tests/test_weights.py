@@ -157,7 +157,8 @@ def test_random_weights_mode_is_seeded_and_complete(tmp_path):
     assert torch.equal(one.read("model.norm.weight"), torch.ones(120))
     assert one.record("model.norm.weight").dtype == "F32"
     model = load_model(str(tmp_path / "one"), "bfloat16", "cpu")
-    assert model.blocks[0].mixer.w_qkv.shape == (3 * 120, 120)
+    # five heads of 24, each held in a row of 32 (the next multiple of 16)
+    assert model.blocks[0].mixer.w_qkv.shape == (3 * 5 * 32, 120)
     assert model.blocks[0].feed_forward.w_gate_up.shape == (640, 120)
     assert model.final_norm.weight.dtype == torch.float32
 
@@ -167,7 +168,13 @@ def test_rotary_row_permutation_matches_the_plain_conversion(model_root):
     folder = make_folder(model_root, "B", storage_dtype="float32")
     model = load_model(folder, "float32", "cpu")
     plain = plain_llama.PlainModel(folder)
-    fused = model.blocks[1].mixer.w_qkv.matrix.numpy()
-    np.testing.assert_array_equal(fused[:120], plain.weights["layer.1.query"].T)
-    np.testing.assert_array_equal(fused[120:240], plain.weights["layer.1.key"].T)
-    np.testing.assert_array_equal(fused[240:], plain.weights["layer.1.value"].T)
+    # [q | k | v] x five heads, each head's 24 rows followed by 8 rows of zeros
+    fused = model.blocks[1].mixer.w_qkv.matrix.numpy().reshape(3, 5, 32, 120)
+    assert not fused[:, :, 24:].any()
+    for index, name in enumerate(("query", "key", "value")):
+        np.testing.assert_array_equal(fused[index, :, :24].reshape(120, 120),
+                                      plain.weights[f"layer.1.{name}"].T)
+    out = model.blocks[1].mixer.w_o.matrix.numpy().reshape(120, 5, 32)
+    assert not out[:, :, 24:].any()
+    np.testing.assert_array_equal(out[:, :, :24].reshape(120, 120),
+                                  plain.weights["layer.1.attention_output"].T)
