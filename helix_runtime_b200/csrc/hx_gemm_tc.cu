@@ -20,7 +20,9 @@
 // Epilogues: store bf16, store f32 (logits), add into f32 (the residual stream; with
 // split-K through float32 atomics), and SwiGLU, where the CTA multiplies the same
 // token tile with a gate tile and an up tile of the fused [2I, K] matrix into two
-// accumulators and writes silu(gate) * up.
+// accumulators and writes silu(gate) * up.  For prompt portions the fused QKV product can
+// also rotate queries and keys and put keys and values into the cache pages in its epilogue
+// (hx_gemm_tc_rope_append), which saves the separate pass over the projected rows.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out sets a status bit, the
 // CTA skips its remaining work, frees its tensor memory and returns.
@@ -39,7 +41,10 @@ constexpr int BK = 64;         // k elements per stage: 128 bytes, one swizzle s
 constexpr int UMMA_K = 16;     // k elements per tcgen05.mma of kind::f16
 constexpr int THREADS = 192;
 
-enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
+enum Epilogue : int {
+  EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3,
+  EPI_ROPE_APPEND = 4      // persistent kernel only, see RopeArgs
+};
 
 // Where the [128 rows x 64 k] box of the weights that begins at row `row`, k-block `kb`, is.
 // Row-major weights: a box is 128 row segments of 128 bytes, one per row of the matrix.  Tiled
@@ -302,6 +307,26 @@ struct PersistentConfig {
   static constexpr int kTmemColumns = 512;
 };
 
+// What the rotary/append epilogue needs beyond the product: the output row is
+// [q heads | k heads | v heads], each head `head_dim` wide (a multiple of 16, so the 16
+// features a thread handles at a time lie in one head).  Queries are rotated and stored to
+// `out`; keys are rotated and, like the values, written into the token's slot of its page
+// (k_cache == nullptr: the caller owns no cache, keys and values are dropped).  Pairs are
+// adjacent coordinates (2p, 2p + 1); the first `rotary_dim` coordinates of a head rotate.
+struct RopeArgs {
+  const int* positions;
+  const int* token_request;
+  const int* request_table_row;
+  const int* block_tables;
+  int table_stride;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  const float* cos_table;      // [table_positions][rotary_dim / 2]
+  const float* sin_table;
+  int table_positions;
+  int heads, kv_heads, head_dim, rotary_dim, page_size, num_pages;
+};
+
 struct PersistentArgs {
   void* out;
   int ldo;
@@ -314,6 +339,7 @@ struct PersistentArgs {
   int units;                  // token_tiles * feature tiles
   int k_blocks;               // per tile
   int* status;
+  RopeArgs rope;              // EPI_ROPE_APPEND only
 };
 
 struct Unit {
@@ -413,6 +439,79 @@ __device__ __forceinline__ void write_row(void* out, int ldo, int features, uint
           }
         }
       }
+    }
+  }
+}
+
+// The rotary/append epilogue for this thread's token: the same arithmetic as the separate
+// kernel (hx_rope_append) applied to the product rounded to bfloat16, as the plain store
+// would have rounded it: rotation in float32 from the cos/sin table, one more rounding.
+__device__ __forceinline__ void write_row_rope(const PersistentArgs& a, uint32_t lane_address,
+                                               int token, int feature0) {
+  const RopeArgs& r = a.rope;
+  const bool live = token < a.tokens;
+  const int half = r.rotary_dim / 2;
+  const float* cos_row = r.cos_table;
+  const float* sin_row = r.sin_table;
+  int page = -1, slot = 0;
+  if (live) {
+    const int position = r.positions[token];
+    const int table_position = position < r.table_positions ? position : r.table_positions - 1;
+    cos_row += static_cast<size_t>(table_position) * half;
+    sin_row += static_cast<size_t>(table_position) * half;
+    if (r.k_cache != nullptr) {
+      const int table_row = r.request_table_row[r.token_request[token]];
+      page = r.block_tables[static_cast<size_t>(table_row) * r.table_stride + position / r.page_size];
+      slot = position % r.page_size;
+      if (page < 0 || page >= r.num_pages) {
+        atomicOr(a.status, HX_FLAG_BAD_PAGE);
+        page = -1;
+      }
+    }
+  }
+  const int q_features = r.heads * r.head_dim;
+  const int k_end = q_features + r.kv_heads * r.head_dim;
+#pragma unroll 1
+  for (int column = 0; column < 2 * BM; column += 16) {
+    const int feature = feature0 + column;
+    if (feature >= a.features) break;      // uniform over the warp
+    float x[16];
+    tmem_load16(lane_address + column, x);
+    if (!live) continue;
+    const bool is_query = feature < q_features;
+    const bool is_key = !is_query && feature < k_end;
+    const int inside = feature - (is_query ? 0 : (is_key ? q_features : k_end));
+    const int head = inside / r.head_dim;
+    const int d0 = inside - head * r.head_dim;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) x[j] = __bfloat162float(__float2bfloat16_rn(x[j]));
+    if ((is_query || is_key) && d0 < r.rotary_dim) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (d0 + 2 * i + 1 < r.rotary_dim) {
+          const float c = __ldg(cos_row + d0 / 2 + i);
+          const float sn = __ldg(sin_row + d0 / 2 + i);
+          const float u = x[2 * i], v = x[2 * i + 1];
+          x[2 * i] = u * c - v * sn;
+          x[2 * i + 1] = u * sn + v * c;
+        }
+      }
+    }
+    uint4 packed[2];
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(packed);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) pairs[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+    if (is_query) {
+      uint4* row = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) +
+                                            static_cast<size_t>(token) * a.ldo + feature);
+      row[0] = packed[0];
+      row[1] = packed[1];
+    } else if (page >= 0) {
+      __nv_bfloat16* cache = is_key ? r.k_cache : r.v_cache;
+      *reinterpret_cast<uint4*>(cache + hx_cache_offset(page, head, slot, d0, r.kv_heads,
+                                                        r.page_size, r.head_dim, 8)) = packed[0];
+      *reinterpret_cast<uint4*>(cache + hx_cache_offset(page, head, slot, d0 + 8, r.kv_heads,
+                                                        r.page_size, r.head_dim, 8)) = packed[1];
     }
   }
 }
@@ -564,10 +663,15 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
         break;
       }
       tc_fence_after();
-      write_row<EPI>(args.out, args.ldo, args.features,
-                     lane_base + buffer * Config::kBufferColumns,
-                     unit.token_tile * BM + quarter * 32 + lane, args.tokens,
-                     unit.feature_tile * FEATURES);
+      if constexpr (EPI == EPI_ROPE_APPEND) {
+        write_row_rope(args, lane_base + buffer * Config::kBufferColumns,
+                       unit.token_tile * BM + quarter * 32 + lane, unit.feature_tile * FEATURES);
+      } else {
+        write_row<EPI>(args.out, args.ldo, args.features,
+                       lane_base + buffer * Config::kBufferColumns,
+                       unit.token_tile * BM + quarter * 32 + lane, args.tokens,
+                       unit.feature_tile * FEATURES);
+      }
       // every lane's tcgen05.ld has completed (the loads are waited for where they are
       // issued): hand the accumulator back
       if (EPI == EPI_ADD_F32) {
@@ -742,6 +846,7 @@ int launch_persistent_epilogue(int epilogue, const CUtensorMap& map_w, const CUt
     case EPI_STORE_F32: return launch_persistent<EPI_STORE_F32>(map_w, map_x, args, stream);
     case EPI_ADD_F32: return launch_persistent<EPI_ADD_F32>(map_w, map_x, args, stream);
     case EPI_SWIGLU: return launch_persistent<EPI_SWIGLU>(map_w, map_x, args, stream);
+    case EPI_ROPE_APPEND: return launch_persistent<EPI_ROPE_APPEND>(map_w, map_x, args, stream);
     default:
       hx_set_error("hx_gemm_tc: unknown epilogue %d", epilogue);
       return HX_ERR_ARGUMENT;
@@ -788,6 +893,8 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
   HX_REQUIRE(x_capacity_rows >= tokens, "hx_gemm_tc: buffer rows %d < tokens %d", x_capacity_rows,
              tokens);
   HX_REQUIRE(status != nullptr, "hx_gemm_tc: status word missing");
+  HX_REQUIRE(epilogue >= EPI_STORE_BF16 && epilogue <= EPI_SWIGLU,
+             "hx_gemm_tc: unknown epilogue %d", epilogue);
   HX_REQUIRE(k_splits >= 1 && (k_splits == 1 || epilogue == EPI_ADD_F32),
              "hx_gemm_tc: split-K needs the add epilogue");
   HX_REQUIRE(epilogue != EPI_SWIGLU || up_row_offset + features <= weight_rows,
@@ -812,7 +919,7 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
 
   if (persistent) {
     PersistentArgs args{out, ldo, tokens, features, depth, up_row_offset, k_tiles, 0, 0,
-                        total_k_blocks, status};
+                        total_k_blocks, status, RopeArgs{}};
     rc = launch_persistent_epilogue(epilogue, map_w, map_x, args, stream);
     if (rc != HX_OK) return rc;
     HX_CHECK_LAUNCH("hx_gemm_tc");
@@ -834,5 +941,84 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
   }
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_gemm_tc");
+  return HX_OK;
+}
+
+// Fewest tokens hx_gemm_tc_rope_append takes: it exists for the persistent kernel only.
+HX_API int hx_gemm_tc_rope_append_min_tokens() { return 65; }
+
+// The fused QKV product of a prompt portion with the rotary encoding and the cache append as
+// its epilogue: qkv[t] = x[t] @ w.T with w = [q heads | k heads | v heads] x head_dim rows;
+// the queries are rotated and stored to `out` (row stride ldo; the key and value parts of an
+// out row are NOT written), the keys are rotated and, like the values, written to the
+// token's slot of its page in k_cache / v_cache (both nullptr: dropped).  The arguments from
+// `positions` on mean what they mean to hx_rope_append, with adjacent pairs; x, w, ldx, ldw,
+// x_capacity_rows, weight_rows and weight_tiles what they mean to hx_gemm_tc.  Needs more
+// than 64 tokens, bfloat16, head_dim a multiple of 16 and 16-byte aligned out and caches.
+HX_API int hx_gemm_tc_rope_append(const void* x, int ldx, int x_capacity_rows, const void* w,
+                                  int ldw, int weight_rows, void* out, int ldo, int tokens,
+                                  int depth, int weight_tiles, const int* positions,
+                                  const int* token_request, const int* request_table_row,
+                                  const int* block_tables, int table_stride, void* k_cache,
+                                  void* v_cache, const float* cos_table, const float* sin_table,
+                                  int table_positions, int heads, int kv_heads, int head_dim,
+                                  int rotary_dim, int page_size, int num_pages, int* status,
+                                  cudaStream_t stream) {
+  if (weight_tiles) ldw = 8;      // not a stride of anything here
+  HX_REQUIRE(heads > 0 && kv_heads > 0 && head_dim > 0 && head_dim % 16 == 0,
+             "hx_gemm_tc_rope_append: head_dim %d must be a multiple of 16", head_dim);
+  HX_REQUIRE(static_cast<long long>(heads + 2 * kv_heads) * head_dim <= weight_rows,
+             "hx_gemm_tc_rope_append: %d + 2 x %d heads of %d exceed the %d weight rows", heads,
+             kv_heads, head_dim, weight_rows);
+  const int features = (heads + 2 * kv_heads) * head_dim;
+  HX_REQUIRE(tokens >= hx_gemm_tc_rope_append_min_tokens(),
+             "hx_gemm_tc_rope_append: %d tokens; it takes prompt portions of at least %d", tokens,
+             hx_gemm_tc_rope_append_min_tokens());
+  HX_REQUIRE(hx_gemm_tc_supports(tokens, features, depth, ldx, ldw),
+             "hx_gemm_tc_rope_append: shape tokens=%d features=%d depth=%d ldx=%d ldw=%d is not "
+             "supported (depth and strides must be multiples of 8)", tokens, features, depth, ldx,
+             ldw);
+  HX_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
+             "hx_gemm_tc_rope_append: rotary_dim %d must be even and at most head_dim %d",
+             rotary_dim, head_dim);
+  HX_REQUIRE(rotary_dim == 0 || (table_positions > 0 && cos_table && sin_table),
+             "hx_gemm_tc_rope_append: rotary table missing");
+  HX_REQUIRE((k_cache == nullptr) == (v_cache == nullptr),
+             "hx_gemm_tc_rope_append: key and value cache come together");
+  HX_REQUIRE(k_cache == nullptr || (page_size > 0 && num_pages > 0 && table_stride > 0 &&
+                                    token_request && request_table_row && block_tables),
+             "hx_gemm_tc_rope_append: cache arguments missing");
+  HX_REQUIRE(positions != nullptr && status != nullptr,
+             "hx_gemm_tc_rope_append: positions or status word missing");
+  HX_REQUIRE(ldo >= heads * head_dim && ldo % 8 == 0,
+             "hx_gemm_tc_rope_append: output stride %d must hold the queries and be a multiple "
+             "of 8", ldo);
+  HX_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0,
+             "hx_gemm_tc_rope_append: operands must be 16-byte aligned");
+  HX_REQUIRE(x_capacity_rows >= tokens, "hx_gemm_tc_rope_append: buffer rows %d < tokens %d",
+             x_capacity_rows, tokens);
+
+  CUtensorMap map_w, map_x;
+  const int total_k_blocks = (depth + BK - 1) / BK;
+  const int k_tiles = weight_tiles ? total_k_blocks : 0;
+  int rc = weight_tiles
+               ? get_tensor_map(w, static_cast<uint64_t>((weight_rows + BM - 1) / BM) * k_tiles * BM,
+                                BK, BK, BM, &map_w)
+               : get_tensor_map(w, weight_rows, depth, ldw, BM, &map_w);
+  if (rc != HX_OK) return rc;
+  rc = get_tensor_map(x, x_capacity_rows, depth, ldx, BM, &map_x);
+  if (rc != HX_OK) return rc;
+  PersistentArgs args{out, ldo, tokens, features, depth, 0, k_tiles, 0, 0, total_k_blocks, status,
+                      RopeArgs{positions, token_request, request_table_row, block_tables,
+                               table_stride, static_cast<__nv_bfloat16*>(k_cache),
+                               static_cast<__nv_bfloat16*>(v_cache), cos_table, sin_table,
+                               table_positions, heads, kv_heads, head_dim, rotary_dim, page_size,
+                               num_pages}};
+  rc = launch_persistent_epilogue(EPI_ROPE_APPEND, map_w, map_x, args, stream);
+  if (rc != HX_OK) return rc;
+  HX_CHECK_LAUNCH("hx_gemm_tc_rope_append");
   return HX_OK;
 }

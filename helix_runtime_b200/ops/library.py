@@ -56,6 +56,13 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_gemm_tc.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_int,
                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                                    _c_ptr]
+    library.hx_gemm_tc_rope_append.argtypes = [
+        _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+        _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
+    library.hx_gemm_tc_rope_append.restype = _c_int
+    library.hx_gemm_tc_rope_append_min_tokens.argtypes = []
+    library.hx_gemm_tc_rope_append_min_tokens.restype = _c_int
     library.hx_gemm_tc_supports.argtypes = [_c_int] * 5
     library.hx_gemm_tc_token_tile.argtypes = [_c_int]
     library.hx_paged_attention.argtypes = [
@@ -251,6 +258,48 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tokens: int, fe
                             out.data_ptr(), out.stride(0), tokens, features, depth, epilogue,
                             up_row_offset, k_splits, 1 if tiled else 0, status.data_ptr(),
                             _stream()))
+
+
+def gemm_tc_rope_append_min_tokens() -> int:
+    return int(lib().hx_gemm_tc_rope_append_min_tokens())
+
+
+def gemm_tc_rope_append(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, tokens: int,
+                        positions: torch.Tensor, token_request: torch.Tensor,
+                        request_table_row: torch.Tensor, block_tables: Optional[torch.Tensor],
+                        k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                        cos_table: torch.Tensor, sin_table: torch.Tensor, heads: int,
+                        kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,
+                        num_pages: int, status: torch.Tensor,
+                        weight_shape: Optional[Tuple[int, int]] = None) -> None:
+    """The fused QKV product of a prompt portion (more than 64 tokens, bfloat16) with the
+    rotary encoding and the cache append as its epilogue: ``qkv[:tokens, :heads * head_dim]``
+    receives the rotated queries (the key and value columns of ``qkv`` are NOT written), keys
+    (rotated) and values go to their pages.  Adjacent pairs; ``w`` as for :func:`gemm_tc`."""
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    _need(qkv, torch.bfloat16, "qkv")
+    tiled = w.dim() == 4
+    if tiled:
+        if weight_shape is None:
+            raise ValueError("tiled weights need weight_shape=(rows, depth)")
+        rows, depth = weight_shape
+        if tuple(w.shape) != (-(-rows // WEIGHT_TILE_ROWS), -(-depth // WEIGHT_TILE_DEPTH),
+                              WEIGHT_TILE_ROWS, WEIGHT_TILE_DEPTH) or not w.is_contiguous():
+            raise ValueError(f"tiles of shape {tuple(w.shape)} do not hold a {rows} x {depth} matrix")
+        ldw = 0
+    else:
+        rows, depth = w.shape
+        ldw = w.stride(0)
+    write = k_cache is not None
+    _check(lib().hx_gemm_tc_rope_append(
+        x.data_ptr(), x.stride(0), x.shape[0], w.data_ptr(), ldw, rows, qkv.data_ptr(),
+        qkv.stride(0), tokens, depth, 1 if tiled else 0, positions.data_ptr(),
+        token_request.data_ptr(), request_table_row.data_ptr(),
+        _ptr(block_tables) if write else None,
+        block_tables.stride(0) if write else 0, _ptr(k_cache), _ptr(v_cache),
+        cos_table.data_ptr(), sin_table.data_ptr(), cos_table.shape[0], heads, kv_heads, head_dim,
+        rotary_dim, page_size, num_pages, status.data_ptr(), _stream()))
 
 
 def attention_scratch_floats(tokens: int, heads: int, head_dim: int, max_splits: int,

@@ -13,8 +13,8 @@ pairs, the rows of q and k are permuted per head to ``[0, D/2, 1, D/2+1, ...]``
 Steps: fused projection, rotary encoding + cache append, paged attention, output
 projection added into the residual (src/model/cpu_llama.cpp:65-91).
 
-A head whose size is no multiple of 16 (100, say) is held in rows of the next multiple
-(``row_dim``): the projection gets zero rows for the extra coordinates of every head and
+A head whose size is no multiple of 16 (100, say; of 32 above 128) is held in rows of the
+next multiple (``row_dim``): the projection gets zero rows for the extra coordinates of every head and
 the output projection zero columns, so queries, keys and values carry exact zeros there,
 scores and outputs are unchanged, and the tensor-core attention kernels, which tile the
 head in steps of 16, take the head.  The scale stays ``1/sqrt(head_dim)`` and the rotation
@@ -39,7 +39,14 @@ from .linear import (STREAMING_MAX_TOKENS, Weight, is_weight_stream, project,
 
 
 TENSOR_CORE_MIN_QUERY = 16
-HEAD_STEP = 16      # the tensor-core attention kernels tile a head in steps of this
+
+
+def row_width(head_dim: int) -> int:
+    """The head size the tensor-core attention kernels are built for that holds ``head_dim``:
+    steps of 16 up to 128, of 32 up to 256; beyond that the head keeps its size."""
+    step = 16 if head_dim <= 128 else 32
+    wide = -(-head_dim // step) * step
+    return wide if wide <= 256 else head_dim
 
 
 def rotary_row_permutation(heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
@@ -67,8 +74,8 @@ class PagedAttention(Mixer):
         self.window: Optional[int] = int(window) if window else None
         self.row_dim = self.head_dim
         self.position = build_part("position", spec["position"], hidden_size)
-        if self.head_dim % HEAD_STEP:
-            wide = -(-self.head_dim // HEAD_STEP) * HEAD_STEP
+        wide = row_width(self.head_dim)
+        if wide != self.head_dim:
             position = spec["position"]
             padded = build_part("position", PartSpec(position.kind,
                                                      {**position.params, "row_dim": wide},
@@ -153,7 +160,8 @@ class PagedAttention(Mixer):
                                                     (STREAMING_MAX_TOKENS, self.qkv_size))
             project_into_accumulator(x, self.w_qkv, accumulator, n, ctx.status)
             self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads, accum=accumulator)
-        else:
+        elif not self.position.project_and_apply(ctx, cache, x, self.w_qkv, qkv, self.heads,
+                                                 self.kv_heads):
             project(x, self.w_qkv, qkv, n, ops.EPI_STORE, ctx.status)
             self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
 

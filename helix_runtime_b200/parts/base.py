@@ -174,6 +174,14 @@ class PositionEncoding(Part):
         instead of ``qkv`` and the accumulator must be left cleared."""
         raise NotImplementedError
 
+    def project_and_apply(self, ctx: "StepContext", cache: "LayerCache", x: torch.Tensor,
+                          weight, qkv: torch.Tensor, heads: int, kv_heads: int) -> bool:
+        """Optional: the mixer's projection ``qkv[:n] = x[:n] @ weight.T`` and :meth:`apply`
+        as ONE kernel.  Return False (the default) when this encoding has no such kernel for
+        this step; the mixer then projects and calls :meth:`apply`.  After a True only the
+        query columns of ``qkv`` are defined: keys and values live in the pages."""
+        return False
+
 
 class Mixer(Part):
     def kv_need(self) -> Optional[KvNeed]:

@@ -18,6 +18,7 @@ import torch
 from ..config.spec import PartSpec
 from ..ops import library as ops
 from .base import LayerCache, PositionEncoding, StepContext, register_part
+from .linear import Weight, uses_tensor_cores
 
 PAIRINGS = {"adjacent": 0, "half_split": 1}
 
@@ -64,6 +65,29 @@ class RotaryEncoding(PositionEncoding):
                         cache.values if write else None, self.cos, self.sin, ctx.n_tokens, heads,
                         kv_heads, self.row_dim, self.rotary_dim, PAIRINGS[self.pairing],
                         cache.page_size, cache.num_pages, ctx.status, accum=accum)
+
+
+    def project_and_apply(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
+                          weight: Weight, qkv: torch.Tensor, heads: int, kv_heads: int) -> bool:
+        """Prompt portions in bfloat16: rotation and cache append are the epilogue of the
+        tensor-core product, which saves a pass over the projected rows (read 3 heads' worth,
+        write it again) per layer.  Needs adjacent pairs (a thread of the epilogue holds 16
+        consecutive coordinates of one token) and heads in steps of 16."""
+        n = ctx.n_tokens
+        if (self.pairing != "adjacent" or self.row_dim % 16
+                or weight.rows != (heads + 2 * kv_heads) * self.row_dim
+                or n < ops.gemm_tc_rope_append_min_tokens() or not uses_tensor_cores(x, weight, n)
+                or qkv.dtype != torch.bfloat16 or qkv.stride(0) % 8):
+            return False
+        write = cache.owns and cache.keys is not None
+        held = weight.tiles if weight.tiles is not None else weight.matrix
+        ops.gemm_tc_rope_append(x, held, qkv, n, ctx.positions, ctx.token_request,
+                                ctx.request_slot, cache.block_tables if write else None,
+                                cache.keys if write else None, cache.values if write else None,
+                                self.cos, self.sin, heads, kv_heads, self.row_dim, self.rotary_dim,
+                                cache.page_size, cache.num_pages, ctx.status,
+                                weight_shape=weight.shape)
+        return True
 
 
 register_part("position", "rotary", RotaryEncoding)

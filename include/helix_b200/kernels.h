@@ -96,6 +96,17 @@ int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w, int l
                int weight_rows, void* out, int ldo, int tokens, int features, int depth,
                int epilogue, int up_row_offset, int k_splits, int weight_tiles, int* status,
                cudaStream_t stream);
+/* the fused QKV product of a prompt portion (more than 64 tokens) with rotary encoding and
+   cache append as its epilogue: rotated queries to `out`, keys and values to their pages */
+int hx_gemm_tc_rope_append_min_tokens(void);
+int hx_gemm_tc_rope_append(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                           int weight_rows, void* out, int ldo, int tokens, int depth,
+                           int weight_tiles, const int* positions, const int* token_request,
+                           const int* request_table_row, const int* block_tables,
+                           int table_stride, void* k_cache, void* v_cache, const float* cos_table,
+                           const float* sin_table, int table_positions, int heads, int kv_heads,
+                           int head_dim, int rotary_dim, int page_size, int num_pages, int* status,
+                           cudaStream_t stream);
 
 /* ---- attention over the paged cache ----------------------------------------------------- */
 int hx_cache_chunk_elements(int dtype, int head_dim);

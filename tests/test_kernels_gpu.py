@@ -357,6 +357,93 @@ def test_rope_reads_and_clears_a_split_k_accumulator():
         np.testing.assert_array_equal(direct, through_accumulator)
 
 
+@pytest.mark.parametrize("tiled", [False, True])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim,depth,page_size", [
+    (4, 4, 16, 16, 64, 8), (3, 1, 112, 100, 200, 16), (6, 2, 64, 32, 264, 32),
+    (5, 5, 128, 128, 128, 16)])
+@pytest.mark.parametrize("own_cache", [True, False])
+def test_product_with_rotary_append_epilogue(heads, kv_heads, head_dim, rotary_dim, depth,
+                                             page_size, tiled, own_cache):
+    """The fused QKV product of prompt portions against the plain product followed by the
+    rotary/append kernel: rotated queries, and keys and values in their pages, must agree;
+    rows of the output beyond the tokens and every other slot of the cache stay untouched."""
+    rng = np.random.default_rng(31)
+    # three requests in one step: one continues at position 13 (inside a page), one starts at
+    # 0 and spans token tiles, one brings a single token; 301 tokens: the last tile is ragged
+    counts, starts = [150, 150, 1], [13, 0, 77]
+    positions = np.concatenate([np.arange(s, s + c) for s, c in zip(starts, counts)]).astype(np.int32)
+    token_request = np.concatenate([[r] * c for r, c in enumerate(counts)]).astype(np.int32)
+    tokens, max_positions = len(positions), 192
+    slots = np.array([2, 0, 3], dtype=np.int32)
+    per_request = -(-max_positions // page_size)
+    num_pages = 3 * per_request + 2
+    tables = np.full((4, per_request), -1, dtype=np.int32)
+    order = rng.permutation(num_pages)
+    for r in range(3):
+        tables[slots[r]] = order[r * per_request:(r + 1) * per_request]
+    width = (heads + 2 * kv_heads) * head_dim
+    x = dev(rounded(rng.normal(size=(tokens + 5, depth)), torch.bfloat16), torch.bfloat16)
+    w = dev(rounded(rng.normal(size=(width, depth)) / math.sqrt(depth), torch.bfloat16), torch.bfloat16)
+    held = ops.tile_weights(w) if tiled else w
+    half = max(rotary_dim // 2, 1)
+    exponent = -2.0 * np.arange(half) / rotary_dim
+    angle = np.arange(max_positions)[:, None] * np.power(10000.0, exponent)[None, :]
+    cos, sin = dev(np.cos(angle)), dev(np.sin(angle))
+    device_args = (dev(positions, torch.int32), dev(token_request, torch.int32),
+                   dev(slots, torch.int32), dev(tables, torch.int32))
+
+    def caches():
+        k = torch.full((num_pages, kv_heads, page_size, head_dim), float("nan"),
+                       dtype=torch.bfloat16, device=DEVICE)
+        return (k, torch.full_like(k, float("nan"))) if own_cache else (None, None)
+
+    # the two-kernel way
+    qkv = torch.full((tokens + 5, width), float("nan"), dtype=torch.bfloat16, device=DEVICE)
+    k_plain, v_plain = caches()
+    status = status_word()
+    ops.gemm_tc(x, held, qkv, tokens, width, ops.EPI_STORE, status, weight_shape=(width, depth))
+    ops.rope_append(qkv, *device_args, k_plain, v_plain, cos, sin, tokens, heads, kv_heads,
+                    head_dim, rotary_dim, 0, page_size, num_pages, status)
+    # the fused way
+    fused = torch.full((tokens + 5, width), float("nan"), dtype=torch.bfloat16, device=DEVICE)
+    k_fused, v_fused = caches()
+    ops.gemm_tc_rope_append(x, held, fused, tokens, device_args[0], device_args[1],
+                            device_args[2], device_args[3] if own_cache else None, k_fused,
+                            v_fused, cos, sin, heads, kv_heads, head_dim, rotary_dim, page_size,
+                            num_pages, status, weight_shape=(width, depth))
+    assert int(status.item()) == 0
+    q_size = heads * head_dim
+    plain_q, fused_q = host(qkv)[:tokens, :q_size], host(fused)[:tokens, :q_size]
+    assert np.isfinite(fused_q).all()
+    # the same products rounded the same way, then the same rotation: one bfloat16 step at most
+    assert_close(fused_q, plain_q, "rotated queries", atol=1e-6, rtol=2.0 ** -7)
+    assert np.isnan(host(fused)[tokens:]).all() and np.isnan(host(fused)[:, q_size:]).all()
+    if own_cache:
+        for name, one, other in (("keys", k_fused, k_plain), ("values", v_fused, v_plain)):
+            one, other = host(one), host(other)
+            np.testing.assert_array_equal(np.isnan(one), np.isnan(other))
+            filled = ~np.isnan(other)
+            assert filled.sum() == tokens * kv_heads * head_dim
+            assert_close(one[filled], other[filled], name, atol=1e-6, rtol=2.0 ** -7)
+
+
+def test_product_with_rotary_append_epilogue_refuses_short_portions_and_odd_heads():
+    x = torch.zeros((128, 64), dtype=torch.bfloat16, device=DEVICE)
+    w = torch.zeros((3 * 2 * 24, 64), dtype=torch.bfloat16, device=DEVICE)
+    out = torch.zeros((128, 3 * 2 * 24), dtype=torch.bfloat16, device=DEVICE)
+    ints = torch.zeros(128, dtype=torch.int32, device=DEVICE)
+    table = torch.zeros((1, 4), dtype=torch.float32, device=DEVICE)
+    with pytest.raises(ops.KernelError, match="multiple of 16"):
+        ops.gemm_tc_rope_append(x, w, out, 128, ints, ints, ints, None, None, None, table, table,
+                                2, 2, 24, 8, 16, 4, status_word())
+    w = torch.zeros((3 * 2 * 32, 64), dtype=torch.bfloat16, device=DEVICE)
+    out = torch.zeros((128, 3 * 2 * 32), dtype=torch.bfloat16, device=DEVICE)
+    assert ops.gemm_tc_rope_append_min_tokens() == 65
+    with pytest.raises(ops.KernelError, match="at least 65"):
+        ops.gemm_tc_rope_append(x, w, out, 64, ints, ints, ints, None, None, None, table, table,
+                                2, 2, 32, 8, 16, 4, status_word())
+
+
 # ------------------------------------------------------------------- attention
 
 def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, new_tokens,

@@ -98,7 +98,8 @@ def attention_reference(x, w, heads, kv_heads, head_dim, theta, contexts, length
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,head_dim,window,checkpoint_pairing", [
     (6, 6, 16, None, "adjacent"), (6, 2, 16, None, "half_split"), (4, 4, 24, 5, "adjacent"),
-    (3, 1, 64, None, "half_split"), (2, 2, 100, None, "half_split"), (4, 2, 6, None, "adjacent")])
+    (3, 1, 64, None, "half_split"), (2, 2, 100, None, "half_split"), (4, 2, 6, None, "adjacent"),
+    (2, 1, 144, None, "adjacent")])
 def test_attention_part(dtype, heads, kv_heads, head_dim, window, checkpoint_pairing):
     rng = np.random.default_rng(1)
     hidden, theta = 96, 777.0
@@ -115,7 +116,8 @@ def test_attention_part(dtype, heads, kv_heads, head_dim, window, checkpoint_pai
                       "wv": (kv_heads * head_dim, hidden), "wo": (hidden, heads * head_dim)}
     need = part.kv_need()
     # a head that is no multiple of 16 is held in rows of the next multiple (zeros behind it)
-    assert (need.kv_heads, need.head_dim, need.window) == (kv_heads, -(-head_dim // 16) * 16, window)
+    step = 16 if head_dim <= 128 else 32
+    assert (need.kv_heads, need.head_dim, need.window) == (kv_heads, -(-head_dim // step) * step, window)
     weights = {name: as_numpy(held(rng.normal(size=shape) * 0.2, DTYPES[dtype]))
                for name, shape in shapes.items()}
     part.bind({name: torch.as_tensor(value) for name, value in weights.items()}, DTYPES[dtype],
