@@ -300,6 +300,9 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
 
 // ------------------------------------------------------------------ streaming kernel
 
+#ifndef HX_MERGE_LOADS
+#define HX_MERGE_LOADS 8
+#endif
 constexpr int STREAM_WARPS = 2;
 constexpr int STREAM_RING = 2;      // chunks in flight per warp
 constexpr uint32_t STREAM_WAIT_LIMIT = 20u * 1000u * 1000u;
@@ -392,6 +395,7 @@ __device__ void merge_parts(const AttentionArgs& a, int token, int head, long lo
                             long long per_warp, int first_warp, int n_parts, int lane) {
   // Coordinates per lane: four consecutive ones for a head of 128; otherwise pairs, the
   // i-th pair of a lane at coordinate 2 lane + 64 i (lanes beyond the head hold zeros).
+  constexpr int MERGE_LOADS = HX_MERGE_LOADS;      // parts whose loads are in flight together
   constexpr bool QUADS = D == 128;
   constexpr int PER_LANE = QUADS ? 4 : 2 * ((D + 63) / 64);
   auto part_of = [&](int index) {
@@ -438,13 +442,13 @@ __device__ void merge_parts(const AttentionArgs& a, int token, int head, long lo
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) acc[i] *= rescale;
     const float factor = m == -INFINITY ? 0.0f : __expf(m - new_max);
-    for (int first = 0; first < here; first += 4) {
-      float o[4][PER_LANE];
+    for (int first = 0; first < here; first += MERGE_LOADS) {
+      float o[MERGE_LOADS][PER_LANE];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < MERGE_LOADS; ++u)
         if (first + u < here) load_slice(part_of(base + first + u), o[u]);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < MERGE_LOADS; ++u) {
         if (first + u < here) {
           const float f = __shfl_sync(0xffffffffu, factor, first + u);
           total_sum = fmaf(__shfl_sync(0xffffffffu, l, first + u), f, total_sum);
@@ -485,7 +489,10 @@ void paged_attention_stream_kernel(
   constexpr int kMaxPages = KEYS / 8;   // pages of a chunk at the smallest page size
   extern __shared__ __align__(128) uint8_t stream_shared[];
   __shared__ uint64_t full_bar[STREAM_WARPS][RING];
-  hx_pdl_prologue();
+  // The warp first finds its run of chunks from the step's description (positions, requests,
+  // table rows: written before the step's first kernel), and only then waits for the kernel
+  // before it, which wrote the queries and the newest keys and values.
+  hx_pdl_trigger();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const long long n_warps = static_cast<long long>(gridDim.x) * STREAM_WARPS;
@@ -517,7 +524,10 @@ void paged_attention_stream_kernel(
   const long long per_warp = (total + n_warps - 1) / n_warps;
   const long long my_begin = me * per_warp;
   const long long my_end = min(my_begin + per_warp, total);
-  if (my_begin >= my_end) return;
+  if (my_begin >= my_end) {
+    hx_pdl_wait();      // a grid must not be seen complete before its predecessor is
+    return;
+  }
 
   // the row that holds chunk my_begin: among the first 32 tokens straight from the registers
   ChunkCursor at;
@@ -626,6 +636,7 @@ void paged_attention_stream_kernel(
     }
   };
   const long long run = my_end - my_begin;
+  hx_pdl_wait();
   for (int i = 0; i < RING && i < run; ++i) {
     request_chunk(i);
     cursor_next<KEYS>(a, ahead);

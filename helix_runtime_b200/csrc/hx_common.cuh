@@ -72,8 +72,6 @@ __device__ __forceinline__ void hx_pdl_prologue() {
   hx_pdl_trigger();
   hx_pdl_wait();
 }
-// For kernels whose successor would only sit on resources this kernel's later blocks need.
-__device__ __forceinline__ void hx_pdl_prologue_keep_successor_out() { hx_pdl_wait(); }
 
 bool hx_pdl_enabled();
 

@@ -251,6 +251,11 @@ HX_API int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int i
 // cache layer (keys and values alike): [page][kv_head][head_dim / chunk][slot][chunk],
 // see hx_cache_offset.
 constexpr int ROPE_HEADS_PER_BLOCK = 4;
+// Up to this many tokens the kernel that follows (attention) may be scheduled while the
+// rotary kernel still runs.
+#ifndef HX_ROPE_RELEASE_TOKENS
+#define HX_ROPE_RELEASE_TOKENS 16
+#endif
 
 template <typename T>
 __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positions,
@@ -262,12 +267,15 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
                                    const float* __restrict__ sin_table, int table_positions,
                                    int heads, int kv_heads, int head_dim, int rotary_dim,
                                    int pairing, int page_size, int num_pages, int* status,
-                                   float* __restrict__ accum, int ld_accum) {
-    // The attention kernel that follows fills the GPU with one resident grid of warps that
+                                   float* __restrict__ accum, int ld_accum,
+                                   int release_successor) {
+  // The attention kernel that follows fills the GPU with one resident grid of warps that
   // all start on equal runs of work; let in early, they would all leave the wait in the same
   // instant and stay in step, fetching and computing in bursts (measured: twice the time at
-  // batch 64).  So it is launched when this kernel is done.
-  hx_pdl_prologue_keep_successor_out();
+  // batch 64).  So with many tokens it is launched when this kernel is done; with few
+  // (release_successor) it may come in early and find its work while this kernel runs.
+  if (release_successor) hx_pdl_trigger();
+  hx_pdl_wait();
   const int token = blockIdx.x;
   const int position = positions[token];
   T* row = qkv + static_cast<size_t>(token) * ld;
@@ -384,9 +392,11 @@ __global__ void rope_append_pieces_kernel(
     __nv_bfloat16* __restrict__ v_cache, int write_cache, const float* __restrict__ cos_table,
     const float* __restrict__ sin_table, int table_positions, int heads, int kv_heads,
     int head_dim, int rotary_dim, int pairing, int page_size, int num_pages, int* status,
-    float* __restrict__ accum, int ld_accum) {
-  // the attention kernel that follows is launched when this one is done (see above)
-  hx_pdl_prologue_keep_successor_out();
+    float* __restrict__ accum, int ld_accum, int release_successor) {
+  // with many tokens the attention kernel that follows is launched when this one is done
+  // (see above)
+  if (release_successor) hx_pdl_trigger();
+  hx_pdl_wait();
   const int token = blockIdx.x;
   const int pieces_per_head = head_dim / 8;
   const int item = blockIdx.y * blockDim.x + threadIdx.x;
@@ -519,6 +529,7 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
   HX_REQUIRE(accum == nullptr || ld_accum >= (heads + 2 * kv_heads) * head_dim,
              "hx_rope_append: accumulator stride too small");
   if (tokens == 0) return HX_OK;
+  const int release_successor = tokens <= HX_ROPE_RELEASE_TOKENS ? 1 : 0;
   const int threads = head_dim / 2 >= 64 ? 64 : 32;
   const dim3 grid(tokens, (heads + 2 * kv_heads + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
   HX_REQUIRE(grid.y <= 65535, "hx_rope_append: too many heads");
@@ -536,11 +547,11 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
               block_tables, table_stride, static_cast<__nv_bfloat16*>(k_cache),
               static_cast<__nv_bfloat16*>(v_cache), write_cache, cos_table, sin_table,
               table_positions, heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages,
-              status, accum, ld_accum);
+              status, accum, ld_accum, release_successor);
   } else if (dtype == HX_F32) {
-    hx_launch(rope_append_kernel<float>, grid, threads, 0, stream,  static_cast<float*>(qkv), ld, positions, token_request, request_table_row, block_tables, table_stride, static_cast<float*>(k_cache), static_cast<float*>(v_cache), write_cache, cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status, accum, ld_accum);
+    hx_launch(rope_append_kernel<float>, grid, threads, 0, stream,  static_cast<float*>(qkv), ld, positions, token_request, request_table_row, block_tables, table_stride, static_cast<float*>(k_cache), static_cast<float*>(v_cache), write_cache, cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status, accum, ld_accum, release_successor);
   } else if (dtype == HX_BF16) {
-    hx_launch(rope_append_kernel<__nv_bfloat16>, grid, threads, 0, stream,  static_cast<__nv_bfloat16*>(qkv), ld, positions, token_request, request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), write_cache, cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status, accum, ld_accum);
+    hx_launch(rope_append_kernel<__nv_bfloat16>, grid, threads, 0, stream,  static_cast<__nv_bfloat16*>(qkv), ld, positions, token_request, request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), write_cache, cos_table, sin_table, table_positions, heads, kv_heads, head_dim, rotary_dim, pairing, page_size, num_pages, status, accum, ld_accum, release_successor);
   } else {
     HX_REQUIRE(false, "hx_rope_append: unknown dtype %d", dtype);
   }
