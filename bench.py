@@ -195,6 +195,72 @@ def profile_region(options, model, config, fresh, rng) -> int:
     return 0
 
 
+def timeline_region(options, model, config, fresh, rng) -> int:
+    """The kernels of the step as they run in place (``--timeline decode``: four decode steps of
+    ``--batch`` requests through the engine, CUDA graphs and early launches as in serving;
+    ``--timeline prefill``: one step of ``--prompt-len`` tokens), recorded with CUPTI through
+    ``torch.profiler``: launches, mean duration and mean EXCLUSIVE time per kernel (the part of
+    a kernel after every earlier kernel has ended: a kernel that was let in early spends the
+    rest of its duration waiting for its predecessor).  Unlike an ncu capture nothing is
+    serialised or replayed, so the times add up to the step."""
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from helix_runtime_b200 import Engine, EngineConfig
+    from helix_runtime_b200.engine.step import StepEntry
+
+    length, batch = options.prompt_len, options.batch
+    if options.timeline == "prefill":
+        cache, step, _ = fresh(1, length + 8, length)
+        prompt = [int(t) for t in rng.integers(0, config.vocab_size, length)]
+
+        def run():
+            cache.admit(0)
+            step.run([StepEntry(0, prompt, [length - 1])], check_status=False)
+            cache.release(0)
+        steps = 1
+    else:
+        engine = Engine(model, EngineConfig(page_size=PAGE_SIZE, max_running_requests=batch,
+                                            max_tokens_per_iteration=PREFILL_TOKENS,
+                                            num_pages=batch * -(-(length + 64) // PAGE_SIZE) + 8))
+        for _ in range(batch):
+            engine.submit([int(t) for t in rng.integers(0, config.vocab_size, length)],
+                          max_new_tokens=48)
+        while any(engine.request(r).state.value != "decoding" for r in range(batch)):
+            engine.run_iteration()
+        run, steps = engine.run_iteration, 4
+    for _ in range(12 if options.timeline == "decode" else 3):
+        run()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as recorded:
+        for _ in range(steps):
+            run()
+        torch.cuda.synchronize()
+    events = sorted((e for e in recorded.events()
+                     if e.device_type == torch.autograd.DeviceType.CUDA),
+                    key=lambda e: e.time_range.start)
+    table = collections.OrderedDict()
+    latest_end = None
+    for event in events:
+        name = event.name.replace("(anonymous namespace)::", "").replace("void ", "")
+        name = name.split("(")[0][:56]
+        row = table.setdefault(name, [0, 0.0, 0.0])
+        begin, end = event.time_range.start, event.time_range.end
+        row[0] += 1
+        row[1] += end - begin
+        row[2] += max(0.0, end - (begin if latest_end is None else max(begin, latest_end)))
+        latest_end = end if latest_end is None else max(latest_end, end)
+    span = events[-1].time_range.end - events[0].time_range.start
+    print(f"{options.timeline}: {config.num_hidden_layers} layers, batch {batch}, "
+          f"{length} tokens of context or prompt; {steps} step(s) span {span:.1f} us")
+    print(f"{'launches':>8} {'mean us':>9} {'exclusive us':>12} {'sum excl us':>12}  kernel")
+    for name, (count, total, exclusive) in table.items():
+        print(f"{count:8d} {total / count:9.1f} {exclusive / count:12.1f} {exclusive:12.1f}  {name}")
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -208,6 +274,9 @@ def main() -> int:
     parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
                         help="run one eager step of this kind between cudaProfilerStart/Stop "
                              "(for ncu --profile-from-start off) and print nothing else")
+    parser.add_argument("--timeline", choices=("decode", "prefill"), default=None,
+                        help="print the kernels of the step with their times as they run in "
+                             "place (CUPTI through torch.profiler) and nothing else")
     parser.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     parser.add_argument("--serving", type=int, default=0, metavar="REQUESTS",
                         help="run a continuous-batching workload of this many requests instead "
@@ -300,6 +369,8 @@ def main() -> int:
 
     if options.profile is not None:
         return profile_region(options, model, config, fresh, rng)
+    if options.timeline is not None:
+        return timeline_region(options, model, config, fresh, rng)
     if options.serving:
         return serving_workload(options, model, config, rng)
 

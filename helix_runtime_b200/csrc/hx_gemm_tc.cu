@@ -471,6 +471,9 @@ __device__ __forceinline__ void write_row_rope(const PersistentArgs& a, uint32_t
   }
   const int q_features = r.heads * r.head_dim;
   const int k_end = q_features + r.kv_heads * r.head_dim;
+  const bool wide_table = half % 4 == 0 &&
+                          ((reinterpret_cast<uintptr_t>(r.cos_table) |
+                            reinterpret_cast<uintptr_t>(r.sin_table)) & 15) == 0;
 #pragma unroll 1
   for (int column = 0; column < 2 * BM; column += 16) {
     const int feature = feature0 + column;
@@ -486,15 +489,31 @@ __device__ __forceinline__ void write_row_rope(const PersistentArgs& a, uint32_t
 #pragma unroll
     for (int j = 0; j < 16; ++j) x[j] = __bfloat162float(__float2bfloat16_rn(x[j]));
     if ((is_query || is_key) && d0 < r.rotary_dim) {
+      // the eight angles of this piece: four 16-byte loads where the table's rows allow it
+      // (every lane reads another row of the table, so the number of loads is what counts)
+      float c[8], sn[8];
+      if (wide_table && d0 + 16 <= r.rotary_dim) {
+        const float4 c0 = __ldg(reinterpret_cast<const float4*>(cos_row + d0 / 2));
+        const float4 c1 = __ldg(reinterpret_cast<const float4*>(cos_row + d0 / 2 + 4));
+        const float4 s0 = __ldg(reinterpret_cast<const float4*>(sin_row + d0 / 2));
+        const float4 s1 = __ldg(reinterpret_cast<const float4*>(sin_row + d0 / 2 + 4));
+        c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w;
+        c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w;
+        sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const bool rotates = d0 + 2 * i + 1 < r.rotary_dim;
+          c[i] = rotates ? __ldg(cos_row + d0 / 2 + i) : 1.0f;
+          sn[i] = rotates ? __ldg(sin_row + d0 / 2 + i) : 0.0f;
+        }
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        if (d0 + 2 * i + 1 < r.rotary_dim) {
-          const float c = __ldg(cos_row + d0 / 2 + i);
-          const float sn = __ldg(sin_row + d0 / 2 + i);
-          const float u = x[2 * i], v = x[2 * i + 1];
-          x[2 * i] = u * c - v * sn;
-          x[2 * i + 1] = u * sn + v * c;
-        }
+        const float u = x[2 * i], v = x[2 * i + 1];
+        x[2 * i] = u * c[i] - v * sn[i];
+        x[2 * i + 1] = u * sn[i] + v * c[i];
       }
     }
     uint4 packed[2];
