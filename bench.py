@@ -35,6 +35,25 @@ if ROOT not in sys.path:
 SHAPE = dict(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
              num_attention_heads=32, num_key_value_heads=32, head_dim=128,
              max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0)
+# the other two shapes of the reference's benchmark configurations (--shape, serving mode)
+SHAPES = {
+    "llama-2-7b": SHAPE,
+    "openllama-3b": dict(vocab_size=32000, hidden_size=3200, intermediate_size=8640,
+                         num_hidden_layers=26, num_attention_heads=32, num_key_value_heads=32,
+                         head_dim=100, max_position_embeddings=2048, rms_norm_eps=1e-6,
+                         rope_theta=10000.0),
+    "llama-2-13b": dict(vocab_size=32000, hidden_size=5120, intermediate_size=13824,
+                        num_hidden_layers=40, num_attention_heads=40, num_key_value_heads=40,
+                        head_dim=128, max_position_embeddings=4096, rms_norm_eps=1e-5,
+                        rope_theta=10000.0),
+}
+# serving workloads of those configurations: requests, prompt lengths, new tokens, prompt
+# portion, length of the prefix all prompts share (0: none)
+WORKLOADS = {
+    "llama-2-7b": dict(prompt_range=(128, 2048), new_tokens=256, chunk=512, shared_prefix=0),
+    "openllama-3b": dict(prompt_range=(64, 1024), new_tokens=128, chunk=512, shared_prefix=256),
+    "llama-2-13b": dict(prompt_range=(128, 2048), new_tokens=256, chunk=512, shared_prefix=0),
+}
 PROMPT_LEN = 512
 PAGE_SIZE = 16
 PREFILL_TOKENS = 2048
@@ -117,35 +136,60 @@ def reference_arm() -> int:
 
 def serving_workload(options, model, config, rng) -> int:
     """Continuous batching through the Python entry point, not part of the contract line:
-    ``--serving N`` requests with prompts of 128 to 2,048 tokens and 256 new tokens each, prompt
-    portions of 512 tokens interleaved with decoding, the cache pool sized from free memory
-    (the shape of the reference's largest serving benchmark).  Prints one JSON line."""
+    ``--serving N`` requests of the workload that goes with ``--shape`` (Llama-2-7B and 13B
+    shapes: prompts of 128 to 2,048 tokens, 256 new tokens each, prompt portions of 512 tokens
+    interleaved with decoding; OpenLLaMA-3B shape: prompts of 64 to 1,024 tokens that share
+    their first 256, 128 new tokens each, prefix pages shared), the cache pool sized from the
+    memory that is free after the weights.  Prints one JSON line."""
     import torch
 
     from helix_runtime_b200 import Engine, EngineConfig
 
     requests = options.serving
-    prompts = [[int(t) for t in rng.integers(0, config.vocab_size, int(rng.integers(128, 2049)))]
-               for _ in range(requests)]
+    work = WORKLOADS[options.shape]
+    low, high = work["prompt_range"]
+    high = min(high, config.max_position_embeddings - work["new_tokens"])
+    shared = [int(t) for t in rng.integers(0, config.vocab_size, work["shared_prefix"])]
+    prompts = []
+    for _ in range(requests):
+        length = max(int(rng.integers(low, high + 1)), len(shared) + 1)
+        prompts.append(shared + [int(t) for t in rng.integers(0, config.vocab_size,
+                                                              length - len(shared))])
+    submitted = sum(len(prompt) for prompt in prompts)
     engine = Engine(model, EngineConfig(page_size=PAGE_SIZE, max_running_requests=min(requests, 64),
                                         max_tokens_per_iteration=PREFILL_TOKENS,
-                                        max_prefill_chunk=512, cache_memory_fraction=0.5))
+                                        max_prefill_chunk=work["chunk"],
+                                        cache_memory_fraction=options.cache_fraction,
+                                        prefix_cache_entries=8 if shared else 0))
     torch.cuda.synchronize()
     begin = time.perf_counter()
+    iterations = 0
+    if shared:
+        # the first request brings the shared beginning into the cache (its pages are kept
+        # when its prompt is done); the others arrive after that and find them
+        first = engine.submit(prompts[0], max_new_tokens=work["new_tokens"])
+        while engine.request(first).state.value in ("waiting", "prefill"):
+            engine.run_iteration()
+            iterations += 1
+        prompts = prompts[1:]
     for prompt in prompts:
-        engine.submit(prompt, max_new_tokens=256)
-    iterations = engine.run_until_done()
+        engine.submit(prompt, max_new_tokens=work["new_tokens"])
+    iterations += engine.run_until_done()
     torch.cuda.synchronize()
     seconds = time.perf_counter() - begin
     metrics, stats = engine.metrics(), engine.stats()
+    reused = stats["prefix"]["reused_tokens"] if stats["prefix"] else 0      # found in the cache
     print(json.dumps({
-        "metric": "serving: generated tokens/s over the whole run (Llama-2-7B shape, bf16)",
+        "metric": f"serving: generated tokens/s over the whole run ({options.shape} shape, bf16)",
         "value": round(metrics.generated_tokens / seconds, 1), "unit": "tokens/s",
-        "processed_tokens_per_s": round((metrics.generated_tokens
-                                         + metrics.prompt_tokens_processed) / seconds, 1),
+        "processed_tokens_per_s": round((metrics.generated_tokens + metrics.prompt_tokens_processed
+                                         - reused) / seconds, 1),
         "requests": requests, "seconds": round(seconds, 3), "iterations": iterations,
+        "prompt_tokens_submitted": submitted,
+        "prefix": stats["prefix"],
         "prompt_tokens": metrics.prompt_tokens_processed,
         "generated_tokens": metrics.generated_tokens,
+        "shared_prefix": len(shared),
         "time_to_first_token_p50_p95_s": [round(metrics.time_to_first_token.p50_seconds, 3),
                                           round(metrics.time_to_first_token.p95_seconds, 3)],
         "inter_token_p50_p95_ms": [round(metrics.inter_token_latency.p50_seconds * 1e3, 2),
@@ -268,7 +312,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    parser.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"],
+    parser.add_argument("--layers", type=int, default=None,
                         help="run fewer layers of the same sizes (recorded in config)")
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
@@ -281,6 +325,12 @@ def main() -> int:
     parser.add_argument("--serving", type=int, default=0, metavar="REQUESTS",
                         help="run a continuous-batching workload of this many requests instead "
                              "and print its own JSON line")
+    parser.add_argument("--shape", choices=tuple(SHAPES), default="llama-2-7b",
+                        help="layer sizes for --serving, --profile and --timeline (the contract "
+                             "line is always the Llama-2-7B shape)")
+    parser.add_argument("--cache-fraction", type=float, default=0.5,
+                        help="--serving: share of the memory left after the weights that the "
+                             "cache pool takes")
     parser.add_argument("--log-dir", default=None,
                         help="where the clock samples of the timed region are kept "
                              "(default: a temporary folder)")
@@ -292,6 +342,11 @@ def main() -> int:
         return 2
     if options.warmup < 3:
         options.warmup = 3
+    special = bool(options.serving or options.profile or options.timeline)
+    if options.shape != "llama-2-7b" and not special:
+        print("bench.py: the contract line is measured at the Llama-2-7B shape; --shape goes with "
+              "--serving, --profile or --timeline")
+        return 2
 
     import numpy as np
     import torch
@@ -307,7 +362,10 @@ def main() -> int:
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
     ops.lib()
-    shape = dict(SHAPE, num_hidden_layers=options.layers)
+    shape = dict(SHAPES[options.shape])
+    if options.layers is None:
+        options.layers = shape["num_hidden_layers"]
+    shape["num_hidden_layers"] = options.layers
     config = LlamaConfig(**shape)
     model = random_model(config, seed=0, dtype="bfloat16", device=device)
     rng = np.random.default_rng(0)
