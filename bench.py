@@ -490,7 +490,7 @@ def main() -> int:
         decoded += engine.run_iteration().sampled
     torch.cuda.synchronize()
     e2e_seconds = time.perf_counter() - begin
-    h2d = engine.step_function._host.numel() * 4
+    h2d = engine.step_function.upload_bytes
     e2e = {"value": round(decoded / e2e_seconds, 1), "unit": "tokens/s",
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": options.batch * 4 + 4,
            "ms_per_step": round(e2e_seconds / steps * 1e3, 4),

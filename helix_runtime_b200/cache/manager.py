@@ -130,6 +130,10 @@ class CacheManager:
 
     # ------------------------------------------------------------------ lookups
 
+    def owns_pages(self, entry: int) -> bool:
+        """Whether this schedule entry has key/value storage here."""
+        return entry in self._entry_place
+
     def group_of(self, entry: int) -> CacheGroup:
         return self.groups[self._entry_place[entry][0]]
 
@@ -393,12 +397,10 @@ class CacheManager:
     def _give_back(self, group: CacheGroup, pages: List[int]) -> int:
         if not pages:
             return 0
-        before = group.pool.free_pages
         freed = group.pool.release(pages)
         if group.poison and freed:
-            # pages that just became free are the tail of the ring
-            newly_free = list(group.pool._free)[before:]
-            index = torch.tensor(newly_free, dtype=torch.long, device=group.storage.device)
+            index = torch.tensor(group.pool.last_freed(freed), dtype=torch.long,
+                                 device=group.storage.device)
             group.storage[:, :, index] = float("nan")
         return freed
 

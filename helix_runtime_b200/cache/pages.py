@@ -80,6 +80,12 @@ class PagePool:
         self.release_count += freed
         return freed
 
+    def last_freed(self, count: int) -> List[int]:
+        """The ``count`` pages that became free most recently (the tail of the ring)."""
+        if count <= 0:
+            return []
+        return list(self._free)[-count:]
+
     def check(self) -> None:
         """Every page is either free exactly once or held; raises AssertionError otherwise."""
         free = list(self._free)

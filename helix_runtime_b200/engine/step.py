@@ -74,6 +74,11 @@ class StepFunction:
     # --------------------------------------------------------------------- run
 
     @property
+    def upload_bytes(self) -> int:
+        """Bytes of the packed batch description that every step copies to the device."""
+        return self._host.numel() * self._host.element_size()
+
+    @property
     def feed_rows(self) -> torch.Tensor:
         """Device view of the rows named by ``prepare(..., feed_rows=...)``."""
         return self._view("feed_rows", True)

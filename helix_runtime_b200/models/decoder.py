@@ -119,7 +119,7 @@ class DecoderModel:
         entry = self.schedule[index]
         owner = index if entry.cache_from is None else entry.cache_from
         view = LayerCache(entry=owner, owns=entry.cache_from is None)
-        if owner in cache._entry_place:
+        if cache.owns_pages(owner):
             group = cache.group_of(owner)
             view.keys, view.values = cache.layer_storage(owner)
             view.block_tables = group.device_tables
