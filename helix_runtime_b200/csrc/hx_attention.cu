@@ -107,10 +107,12 @@ __device__ __forceinline__ bool find_item(const AttentionArgs& a, long long inde
   if (skipped(a, item.token)) return false;
   int lo, hi;
   key_range(a, item.token, lo, hi);
-  item.n_splits = (hi - lo + a.split_keys - 1) / a.split_keys;
+  // a caller whose split sizes do not cover the context (split_keys * max_splits keys) gets
+  // fewer, longer splits: the last one walks on to the end of the context
+  item.n_splits = min((hi - lo + a.split_keys - 1) / a.split_keys, a.max_splits);
   if (item.split >= item.n_splits) return false;
   item.begin = lo + item.split * a.split_keys;
-  item.end = min(item.begin + a.split_keys, hi);
+  item.end = item.split == item.n_splits - 1 ? hi : item.begin + a.split_keys;
   return true;
 }
 
@@ -1033,13 +1035,16 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
 // whole device wait.  And a caller from plain C, or through a foreign-function interface,
 // has no caching allocator to lean on and would have to size and keep such a buffer itself.
 // For them the scratch lives in the library: one array in device memory, fixed at
-// HX_NO_ALLOC_SCRATCH_WORDS 32-bit words (4.25 MiB), which every GPU that loads the library
+// HX_NO_ALLOC_SCRATCH_WORDS 32-bit words (4.5 MiB), which every GPU that loads the library
 // holds until the process ends.  See hx_no_alloc.h for the contract.
 #include "hx_no_alloc.h"
 
 #include <mutex>
 
 static __device__ __align__(256) unsigned int hx_static_attention_scratch[HX_NO_ALLOC_SCRATCH_WORDS];
+// the streaming kernel's area does not depend on the call: every head size it takes must fit
+static_assert(HX_NO_ALLOC_PARTIAL_WORDS >= 2ll * STREAM_MAX_WARPS * (MAX_HEAD_DIM + 4),
+              "the built-in scratch must hold the streaming kernel's parts at the largest head");
 
 namespace {
 
@@ -1088,7 +1093,10 @@ HX_API int hx_paged_attention_no_alloc(const void* q, int ldq, const void* k_cac
                                        cudaStream_t stream) {
   HX_REQUIRE(tokens >= 0 && heads > 0 && head_dim > 0 && max_splits > 0,
              "hx_paged_attention_no_alloc: bad sizes");
-  const long long floats = hx_paged_attention_scratch_floats(tokens, heads, head_dim, max_splits);
+  // what the kernel that will run needs: two parts per resident warp for the streaming kernel,
+  // a part per key split of every row for the CUDA-core kernel
+  const long long floats = hx_paged_attention_scratch_floats_for(dtype, tokens, heads, head_dim,
+                                                                 page_size, window, max_splits);
   const long long counters = static_cast<long long>(tokens) * heads;
   HX_REQUIRE(floats <= HX_NO_ALLOC_PARTIAL_WORDS,
              "hx_paged_attention_no_alloc: %d tokens x %d heads x %d splits of head size %d need "

@@ -29,6 +29,7 @@ enum HxDeviceFlag : int {
   HX_FLAG_BAD_PAGE = 2,       // block table entry outside the pool
   HX_FLAG_WAIT_TIMEOUT = 4,   // a bounded mbarrier wait gave up
   HX_FLAG_NONFINITE = 8,      // sampling saw a non-finite logit
+  HX_FLAG_BAD_POSITION = 16,  // a token's position lies outside the position table
 };
 
 void hx_set_error(const char* format, ...);

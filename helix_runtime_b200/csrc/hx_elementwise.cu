@@ -284,7 +284,11 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const int* __res
   // would have rounded them, and the accumulator is cleared for its next use.
   float* accum_row = accum != nullptr ? accum + static_cast<size_t>(token) * ld_accum : nullptr;
   const int half = rotary_dim / 2;
-  const int table_position = position < table_positions ? position : table_positions - 1;
+  // a position the table does not hold: flagged, and rotated with the nearest row so that
+  // nothing outside the table is read
+  const int table_position = min(max(position, 0), table_positions - 1);
+  if (table_position != position && rotary_dim > 0 && threadIdx.x == 0 && status != nullptr)
+    atomicOr(status, HX_FLAG_BAD_POSITION);
   const float* cos_row = cos_table + static_cast<size_t>(table_position) * half;
   const float* sin_row = sin_table + static_cast<size_t>(table_position) * half;
 
@@ -469,7 +473,10 @@ __global__ void rope_append_pieces_kernel(
     store(d0, x);
     return;
   }
-  const int table_position = position < table_positions ? position : table_positions - 1;
+  // a position the table does not hold: flagged, and rotated with the nearest row so that
+  // nothing outside the table is read
+  const int table_position = min(max(position, 0), table_positions - 1);
+  if (table_position != position && status != nullptr) atomicOr(status, HX_FLAG_BAD_POSITION);
   const float* cos_row = cos_table + static_cast<size_t>(table_position) * half;
   const float* sin_row = sin_table + static_cast<size_t>(table_position) * half;
   if (pairing == 0) {

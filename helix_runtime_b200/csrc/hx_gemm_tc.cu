@@ -456,7 +456,9 @@ __device__ __forceinline__ void write_row_rope(const PersistentArgs& a, uint32_t
   int page = -1, slot = 0;
   if (live) {
     const int position = r.positions[token];
-    const int table_position = position < r.table_positions ? position : r.table_positions - 1;
+    const int table_position = min(max(position, 0), r.table_positions - 1);
+    if (table_position != position && r.rotary_dim > 0 && feature0 == 0 && a.status != nullptr)
+      atomicOr(a.status, HX_FLAG_BAD_POSITION);
     cos_row += static_cast<size_t>(table_position) * half;
     sin_row += static_cast<size_t>(table_position) * half;
     if (r.k_cache != nullptr) {

@@ -15,12 +15,18 @@
 // output are still the caller's.  It calls no cudaMalloc, no cudaFree and no other routine
 // that allocates.
 //
-// Limits.  The array holds HX_NO_ALLOC_PARTIAL_WORDS floats of partial sums
-// (hx_paged_attention_scratch_floats(): tokens * heads * max_splits * (head_dim + 2), and a
-// fixed amount for the streaming kernel, must fit) and HX_NO_ALLOC_COUNTER_WORDS
-// counters (tokens * heads must fit): 4.25 MiB in all, resident on every GPU that loads the
-// library until the process exits.  A call that needs more is refused with an error message
-// that says how much it needed; nothing is launched then.
+// Limits.  The array holds HX_NO_ALLOC_PARTIAL_WORDS floats of partial sums and
+// HX_NO_ALLOC_COUNTER_WORDS counters (tokens * heads must fit): 4.5 MiB in all, resident on
+// every GPU that loads the library until the process exits.  How many partial sums a call
+// needs depends on the kernel that serves it (hx_paged_attention_scratch_floats_for()):
+//   * bfloat16, no window, pages of 8, 16 or 32 keys, head sizes in steps of 16 up to 128 and
+//     of 32 up to 256 (the streaming kernel): a fixed amount that always fits, whatever the
+//     number of tokens, heads and splits;
+//   * everything else (float32, a window, other page or head sizes; the CUDA-core kernel):
+//     tokens * heads * max_splits * (head_dim + 2) floats when max_splits > 1, which must fit.
+//     At 32 heads of 128 that is tokens * max_splits <= 267: eight tokens cut into 32 splits.
+// A call that needs more is refused with an error message that says how much it needed;
+// nothing is launched then.
 //
 // Set-up.  The first call on a device looks up the array's device address
 // (cudaGetSymbolAddress, with that device current) and remembers it.  Make that first call
@@ -38,7 +44,7 @@
 
 #include <cuda_runtime.h>
 
-#define HX_NO_ALLOC_PARTIAL_WORDS (1 << 20)
+#define HX_NO_ALLOC_PARTIAL_WORDS (17 << 16)
 #define HX_NO_ALLOC_COUNTER_WORDS (1 << 16)
 #define HX_NO_ALLOC_SCRATCH_WORDS (HX_NO_ALLOC_PARTIAL_WORDS + HX_NO_ALLOC_COUNTER_WORDS)
 

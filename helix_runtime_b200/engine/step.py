@@ -231,7 +231,10 @@ class StepFunction:
         names = [name for bit, name in ((ops.FLAG_BAD_TOKEN, "token id outside the vocabulary"),
                                         (ops.FLAG_BAD_PAGE, "block table entry outside the pool"),
                                         (ops.FLAG_WAIT_TIMEOUT, "a bounded kernel wait ran out"),
-                                        (ops.FLAG_NONFINITE, "non-finite logits")) if flags & bit]
+                                        (ops.FLAG_NONFINITE, "non-finite logits"),
+                                        (ops.FLAG_BAD_POSITION,
+                                         "a position outside the position table"))
+                 if flags & bit]
         return "the step's kernels reported: " + "; ".join(names)
 
     def raise_on_status(self) -> None:

@@ -27,6 +27,7 @@ FLAG_BAD_TOKEN = 1
 FLAG_BAD_PAGE = 2
 FLAG_WAIT_TIMEOUT = 4
 FLAG_NONFINITE = 8
+FLAG_BAD_POSITION = 16
 
 _c_int = ctypes.c_int
 _c_ptr = ctypes.c_void_p

@@ -13,7 +13,7 @@
  * (HX_RC_*) and leaves a message for hx_last_error().  Sizes a kernel cannot run are refused
  * on the host, before any launch: never a wrong result.  Kernels that can detect a bad input
  * on the device (a token id outside the vocabulary, a page number outside the pool, a bounded
- * wait that ran out, a non-finite logit) OR a bit into the caller's `status` word
+ * wait that ran out, a non-finite logit, a position beyond the rotary table) OR a bit into the caller's `status` word
  * (HX_STATUS_*), which the host reads after the step.
  *
  * dtype codes: HX_F32 = 0, HX_BF16 = 1.  Matrices are [rows, row stride] row-major; weights
@@ -49,6 +49,7 @@ extern "C" {
 #define HX_STATUS_BAD_PAGE 2
 #define HX_STATUS_WAIT_TIMEOUT 4
 #define HX_STATUS_NONFINITE 8
+#define HX_STATUS_BAD_POSITION 16
 
 /* ---- library ---------------------------------------------------------------------------- */
 int hx_abi_version(void);

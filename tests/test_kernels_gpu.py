@@ -357,6 +357,29 @@ def test_rope_reads_and_clears_a_split_k_accumulator():
         np.testing.assert_array_equal(direct, through_accumulator)
 
 
+@pytest.mark.parametrize("dtype,head_dim", [(torch.float32, 24), (torch.bfloat16, 32)])
+def test_rope_flags_a_position_beyond_its_table(dtype, head_dim):
+    """A caller whose positions run past the cos/sin table gets the bad-position flag (the row
+    is rotated with the table's last row: nothing outside the table is read)."""
+    heads = kv_heads = 2
+    page_size, num_pages, table_positions = 8, 4, 16
+    width = (heads + 2 * kv_heads) * head_dim
+    half = head_dim // 2
+    angle = np.arange(table_positions)[:, None] * np.power(10000.0, -2.0 * np.arange(half) / head_dim)
+    cos, sin = dev(np.cos(angle)), dev(np.sin(angle))
+    tables = dev(np.array([[1, 3, 0, 2]]), torch.int32)
+    zeros = dev(np.zeros(2), torch.int32)
+    for positions, expected in (([14, 15], 0), ([15, 16], ops.FLAG_BAD_POSITION)):
+        qkv = dev(np.random.default_rng(5).normal(size=(2, width)), dtype)
+        k_cache = torch.zeros((num_pages, kv_heads, page_size, head_dim), dtype=dtype, device=DEVICE)
+        status = status_word()
+        ops.rope_append(qkv, dev(positions, torch.int32), zeros, zeros[:1], tables, k_cache,
+                        torch.zeros_like(k_cache), cos, sin, 2, heads, kv_heads, head_dim,
+                        head_dim, 0, page_size, num_pages, status)
+        assert int(status.item()) == expected
+        assert np.isfinite(host(qkv)).all()
+
+
 @pytest.mark.parametrize("tiled", [False, True])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim,depth,page_size", [
     (4, 4, 16, 16, 64, 8), (3, 1, 112, 100, 200, 16), (6, 2, 64, 32, 264, 32),
@@ -448,7 +471,7 @@ def test_product_with_rotary_append_epilogue_refuses_short_portions_and_odd_head
 
 def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, new_tokens,
                    window, split_keys, dominant=None, tensor_core_min=0, lost_page=None,
-                   tensor_memory=None):
+                   tensor_memory=None, max_splits=None):
     """Build a paged cache holding ``contexts[r] + new_tokens[r]`` keys per request in shuffled
     pages and the queries of the new tokens; return kernel output and plain reference.
     ``lost_page=(request, index)`` points that entry of the block table outside the pool: the
@@ -497,7 +520,7 @@ def attention_case(rng, dtype, heads, kv_heads, head_dim, page_size, contexts, n
     q = np.stack(q_rows)
     scale = 1.0 / math.sqrt(head_dim)
     longest = max(totals) if not window else min(max(totals), window)
-    max_splits = max(1, -(-longest // split_keys))
+    max_splits = max_splits or max(1, -(-longest // split_keys))
     partial = None
     if max_splits > 1:
         partial = torch.empty(ops.attention_scratch_floats(tokens, heads, head_dim, max_splits),
@@ -587,6 +610,17 @@ def test_streaming_attention_many_requests_of_mixed_length(heads, kv_heads, head
     out, expected, *_ = attention_case(rng, torch.bfloat16, heads, kv_heads, head_dim, page_size,
                                        contexts, new_tokens, window=None, split_keys=64)
     assert_close(out, expected, "attention", atol=2e-2, rtol=8e-3)
+
+
+@pytest.mark.parametrize("dtype,window", [(torch.float32, None), (torch.bfloat16, 300)])
+def test_attention_with_fewer_splits_than_the_context_needs(dtype, window):
+    """``split_keys * max_splits`` smaller than a row's keys: the last split walks on to the end
+    of the context, so the result is the same and only less parallel."""
+    rng = np.random.default_rng(24)
+    out, expected, *_ = attention_case(rng, dtype, 3, 3, 32, 16, [500, 40, 257], [1, 2, 1],
+                                       window=window, split_keys=64, max_splits=3)
+    tol = dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=8e-3)
+    assert_close(out, expected, "attention", **tol)
 
 
 @pytest.mark.parametrize("dtype,head_dim", [(torch.bfloat16, 128), (torch.bfloat16, 32),
