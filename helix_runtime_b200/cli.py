@@ -1,8 +1,10 @@
 """Command line in the manner of the reference's ``helix_generate`` (examples/generate.cpp).
 
-    helix_generate --model MODEL_DIR [--max-new-tokens N] [--eos TOKEN] TOKEN [TOKEN ...]
+    helix_generate --model MODEL [--max-new-tokens N] [--eos TOKEN] TOKEN [TOKEN ...]
 
-Token ids in, token ids out; there is no tokenizer.  ``--model``, ``--max-new-tokens``
+Token ids in, token ids out; there is no tokenizer.  ``--model`` is a Helix model file
+(``MODEL.helix``, what the reference's command takes, examples/generate.cpp:22-27) or a model
+folder with ``config.json`` and safetensors.  ``--model``, ``--max-new-tokens``
 (default 32) and ``--eos`` have the reference's names and meanings, and the output has its
 three lines: ``generated_token_ids``, ``stop_reason``, ``cached_token_count``.  Added here:
 ``--temperature`` and ``--seed`` (the reference samples greedily only), ``--dtype``,
@@ -22,7 +24,8 @@ def build_parser() -> argparse.ArgumentParser:
         prog="helix_generate",
         description="Generate token ids with the B200 engine (token ids in, token ids out).")
     parser.add_argument("--model", required=True,
-                        help="model folder with config.json and model.safetensors")
+                        help="a Helix model file (MODEL.helix) or a model folder with config.json "
+                             "and model.safetensors")
     parser.add_argument("--max-new-tokens", type=int, default=32)
     parser.add_argument("--eos", type=int, default=None, help="token id that ends generation")
     parser.add_argument("--temperature", type=float, default=0.0,

@@ -140,5 +140,56 @@ def build(verbose: bool = True, force: bool = False) -> str:
     return target
 
 
+# ------------------------------------------------------------------ host library
+#
+# Host-only C++ (the native model file reader): compiled with the C++ compiler alone, so that
+# everything that needs no GPU also needs no CUDA toolkit.
+
+HOST_DIR = os.path.join(CSRC, "host")
+HOST_SOURCES = ("hx_model_file.cpp",)
+HOST_HEADERS = ("hx_model_file.h",)
+HOST_FLAGS = ("-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-fvisibility=default")
+
+
+def _host_hash() -> str:
+    digest = hashlib.sha256()
+    for name in (*HOST_SOURCES, *HOST_HEADERS):
+        with open(os.path.join(HOST_DIR, name), "rb") as source:
+            digest.update(name.encode())
+            digest.update(source.read())
+    digest.update(" ".join(HOST_FLAGS).encode())
+    return digest.hexdigest()[:16]
+
+
+def find_cxx() -> str:
+    for candidate in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"),
+                      shutil.which("clang++")):
+        if candidate and shutil.which(candidate):
+            return shutil.which(candidate)
+    raise RuntimeError("no C++ compiler was found (set CXX); the native model file reader "
+                       "needs one")
+
+
+def build_host(force: bool = False) -> str:
+    """Build the host library if needed and return its path."""
+    build_dir = _writable_build_dir()
+    target = os.path.join(build_dir, f"libhelix_host_{_host_hash()}.so")
+    if os.path.exists(target) and not force:
+        return target
+    partial = target + f".{os.getpid()}.tmp"
+    _run([find_cxx(), *HOST_FLAGS, "-I", HOST_DIR,
+          *(os.path.join(HOST_DIR, name) for name in HOST_SOURCES), "-o", partial])
+    os.replace(partial, target)
+    for name in os.listdir(build_dir):
+        if name.startswith("libhelix_host_") and name.endswith(".so") and \
+                os.path.join(build_dir, name) != target:
+            try:
+                os.remove(os.path.join(build_dir, name))
+            except OSError:
+                pass
+    return target
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv))
+    print(build_host(force="--force" in sys.argv))

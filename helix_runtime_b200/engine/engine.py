@@ -17,12 +17,12 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..cache.prefix import PrefixIndex, PrefixMatch
-from ..config.registry import architecture_for, load_config, read_config_json
+from ..config.registry import architecture_for
 from ..models.decoder import DecoderModel
 from ..sampling.sampler import Sampler, uniform_for
 from ..weights.loader import load_tensors
 from ..weights.random_init import random_tensors, write_model_folder
-from ..weights.safetensors_io import Checkpoint
+from ..weights.source import open_model
 from ..ops import library as ops
 from .scheduler import (FifoScheduler, IterationBatch, Request, RequestState, SchedulerConfig,
                         StopReason, WorkCompletion, WorkKind)
@@ -58,13 +58,16 @@ def require_cuda(device: Union[str, torch.device]) -> torch.device:
 
 def load_model(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16",
                device: Union[str, torch.device] = "cuda:0") -> DecoderModel:
-    """Build the model that ``config.json`` names and bind the folder's weights."""
+    """Build the model that the configuration names and bind the weights.  ``model_dir`` is a
+    folder (``config.json`` and safetensors) or a Helix model file (``MODEL.helix``)."""
     dtype = parse_dtype(dtype)
     device = torch.device(device)
-    architecture, config = load_config(model_dir)
+    document, source = open_model(model_dir)
+    architecture = architecture_for(document)
+    config = architecture.config_from_dict(document)
     model = DecoderModel(architecture.build_spec(config))
     model.config = config
-    tensors = load_tensors(Checkpoint(model_dir), model.tensor_requests(), dtype, device)
+    tensors = load_tensors(source, model.tensor_requests(), dtype, device)
     model.bind(tensors, dtype, device)
     return model
 

@@ -11,7 +11,9 @@ C++ compiler, no GPU):
 4. asks the reference's ``helix_model_inspect`` for the last-position logits of several
    prefixes and for a greedy continuation;
 5. writes ``tests/golden/tiny_<name>.json``: the token ids, the reference's logits
-   (as float32 hex strings, exact), its greedy tokens and a checksum of the weights.
+   (as float32 hex strings, exact), its greedy tokens and a checksum of the weights;
+6. keeps the smaller model as the reference's packer wrote it, ``tests/golden/tiny_A.helix``
+   (half a megabyte): the engine loads that file and must generate the same tokens.
 
 ``tests/test_plain_reference.py`` recomputes the same quantities with
 ``tests/plain_llama.py`` and compares them with the committed files, so the plain
@@ -25,6 +27,7 @@ import argparse
 import hashlib
 import json
 import os
+import shutil
 import subprocess
 import sys
 
@@ -77,6 +80,8 @@ def main() -> None:
         helix_file = os.path.join(scratch, f"tiny_{name}.helix")
         run([sys.executable, converter, "--input", folder, "--output", helix_file,
              "--packer", packer, "--force", "--quiet"])
+        if name == "A":
+            shutil.copyfile(helix_file, os.path.join(ROOT, "tests", "golden", "tiny_A.helix"))
         rng = np.random.default_rng(100 + ord(name))
         tokens = [int(t) for t in rng.integers(0, config.vocab_size, size=max(PREFIX_LENGTHS[name]))]
         record = {"config": config.to_dict(), "weights_sha256": weights_checksum(folder),

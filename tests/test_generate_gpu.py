@@ -342,3 +342,82 @@ def test_command_line(folders, plain_models):
         [sys.executable, os.path.join(ROOT, "bin", "helix_generate"), "--model", folder,
          "--dtype", "float32", "999999"], capture_output=True, text=True, cwd=ROOT)
     assert failed.returncode == 1 and "helix_generate:" in failed.stderr
+
+
+# -------------------------------------------------------------- Helix's native model file
+
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def test_reference_made_model_file_generates_the_references_tokens():
+    """``tests/golden/tiny_A.helix`` was packed by the reference's own tools, and
+    ``tiny_A.json`` holds what the reference's CPU model made of it: its greedy tokens and its
+    last-position logits.  The float32 engine must give the same from the same file."""
+    import json
+    from helix_runtime_b200 import StepEntry, StepFunction, load_model
+    from helix_runtime_b200.cache.manager import CacheManager
+    with open(os.path.join(GOLDEN, "tiny_A.json"), "r", encoding="utf-8") as source:
+        golden = json.load(source)
+    path = os.path.join(GOLDEN, "tiny_A.helix")
+    engine = Engine.from_pretrained(path, dtype="float32", page_size=8, max_running_requests=2)
+    greedy = golden["greedy"]
+    prompt = golden["tokens"][:greedy["prompt_length"]]
+    result = engine.generate([prompt], max_new_tokens=len(greedy["tokens"]))[0]
+    assert result.generated_tokens == greedy["tokens"]
+    assert result.cached_token_count == len(prompt) + len(greedy["tokens"]) - 1
+    # logits, in both precisions (bfloat16 at the tolerance of the other bfloat16 tests)
+    for dtype, atol in (("float32", 2e-5), ("bfloat16", 5e-3)):
+        model = load_model(path, dtype, "cuda:0")
+        kv, state = model.cache_needs()
+        cache = CacheManager(kv, state, 8, 16, 1, model.max_positions, model.dtype, model.device)
+        step = StepFunction(model, cache, max_tokens=64, max_requests=1)
+        for length, values in golden["last_logits_hex"].items():
+            reference = np.asarray([float.fromhex(v) for v in values], dtype=np.float32)
+            cache.admit("r")
+            tokens = golden["tokens"][:int(length)]
+            logits = step.run([StepEntry("r", tokens, [len(tokens) - 1])])
+            np.testing.assert_allclose(logits.cpu().numpy()[0], reference, rtol=1e-4, atol=atol,
+                                       err_msg=f"{dtype}, prefix of {length}")
+            cache.release("r")
+
+
+def test_command_line_and_replay_take_a_model_file(tmp_path):
+    import json
+    with open(os.path.join(GOLDEN, "tiny_A.json"), "r", encoding="utf-8") as source:
+        golden = json.load(source)
+    path = os.path.join(GOLDEN, "tiny_A.helix")
+    greedy = golden["greedy"]
+    prompt = golden["tokens"][:greedy["prompt_length"]]
+    completed = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "helix_generate"), "--model", path,
+         "--dtype", "float32", "--max-new-tokens", str(len(greedy["tokens"])), "--page-size", "8",
+         *map(str, prompt)], capture_output=True, text=True, cwd=ROOT)
+    assert completed.returncode == 0, completed.stderr
+    generated = [int(t) for t in completed.stdout.splitlines()[0].split(":", 1)[1].split()]
+    assert generated == greedy["tokens"]
+    # replay: the last position of the longest golden prefix, fed in two portions
+    length = max(int(key) for key in golden["last_logits_hex"])
+    tokens = golden["tokens"][:length]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:11], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": tokens[11:],
+                                      "want": [length - 12]}], "end": ["a"]}]
+    out_dir = tmp_path / "replay"
+    replay = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", path, "--dtype",
+         "float32", "--out", str(out_dir), "--max-tokens", "64", "--page-size", "8"],
+        input="".join(json.dumps(step) + "\n" for step in steps), capture_output=True, text=True,
+        cwd=ROOT)
+    assert replay.returncode == 0, replay.stderr
+    got = np.fromfile(out_dir / "1.f32", dtype="<f4")
+    reference = np.asarray([float.fromhex(v) for v in golden["last_logits_hex"][str(length)]],
+                           dtype=np.float32)
+    np.testing.assert_allclose(got, reference, rtol=1e-4, atol=2e-5)
+    # a damaged file is refused with the reader's message, exit code 1
+    damaged = tmp_path / "damaged.helix"
+    data = bytearray(open(path, "rb").read())
+    data[4000] ^= 0x01
+    damaged.write_bytes(bytes(data))
+    failed = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "helix_generate"), "--model", str(damaged),
+         "--dtype", "float32", "1", "2"], capture_output=True, text=True, cwd=ROOT)
+    assert failed.returncode == 1 and "checksum mismatch" in failed.stderr
