@@ -1,40 +1,52 @@
 """Typed configuration of the Llama-style MHA decoder, read from ``config.json``.
 
-Keys, defaults and refusals follow the reference's checkpoint converter
-(tools/convert_hf_llama.py:103-196) and its C++ ``LlamaConfig::validate``
-(src/model/llama.cpp:41-78): equal query and key/value heads, full adjacent-pair
-rotary encoding without scaling, SiLU, no biases.
+Which keys are read, their defaults and what is refused follow the reference's checkpoint
+converter (tools/convert_hf_llama.py:103-196) and its ``LlamaConfig::validate``
+(src/model/llama.cpp:41-78): equal query and key/value heads, full adjacent-pair rotary
+encoding without scaling, SiLU, no biases.  The keys are rows of a table
+(:data:`LLAMA_KEYS`); the rules that tie several keys together are in ``validate``.
 """
 from __future__ import annotations
 
 import dataclasses
-import math
 from typing import Any, Dict, Mapping
 
 from .errors import ConfigError
+from .keys import ABSENT, COUNT, FLAG, OBJECT, REAL, TEXT, Key, only_keys, read_keys
 
+_SIZES = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
+          "num_attention_heads", "max_position_embeddings")
 
-def _positive_int(document: Mapping[str, Any], name: str) -> int:
-    value = document.get(name)
-    if isinstance(value, bool) or not isinstance(value, int) or value <= 0:
-        raise ConfigError(f"config field {name!r} must be a positive integer")
-    return value
+LLAMA_KEYS = (
+    Key("model_type", TEXT, requires="llama",
+        refusal="config field 'model_type' must be exactly 'llama'"),
+    *(Key(name, COUNT) for name in _SIZES),
+    # absent or null: as many as there are query heads / hidden_size over heads
+    Key("num_key_value_heads", COUNT, default=None, null_is_default=True),
+    Key("head_dim", COUNT, default=None, null_is_default=True),
+    Key("rms_norm_eps", REAL, default=1.0e-6),
+    Key("rope_theta", REAL, default=10000.0),
+    Key("tie_word_embeddings", FLAG, default=False),
+    # what the kernels do not do: one value each, anything else is refused
+    Key("hidden_act", TEXT, default="silu", requires="silu",
+        refusal="only hidden_act='silu' is supported"),
+    Key("attention_bias", FLAG, default=False, requires=False,
+        refusal="attention projection biases are not supported"),
+    Key("mlp_bias", FLAG, default=False, requires=False,
+        refusal="MLP projection biases are not supported"),
+    Key("partial_rotary_factor", REAL, default=1.0, requires=1.0,
+        refusal="partial rotary dimensions are not supported"),
+    Key("rope_scaling", ABSENT, default=None),
+    Key("rope_parameters", OBJECT, default=None),
+)
 
-
-def _optional_bool(document: Mapping[str, Any], name: str, default: bool) -> bool:
-    value = document.get(name, default)
-    if not isinstance(value, bool):
-        raise ConfigError(f"config field {name!r} must be a boolean")
-    return value
-
-
-def _positive_finite(value: Any, name: str) -> float:
-    if isinstance(value, bool) or not isinstance(value, (int, float)):
-        raise ConfigError(f"config field {name!r} must be a number")
-    result = float(value)
-    if not math.isfinite(result) or result <= 0.0:
-        raise ConfigError(f"config field {name!r} must be positive and finite")
-    return result
+ROPE_PARAMETER_KEYS = (
+    Key("rope_type", TEXT, default="default", requires="default",
+        refusal="only default, unscaled RoPE is supported"),
+    Key("partial_rotary_factor", REAL, default=1.0, requires=1.0,
+        refusal="partial rotary dimensions are not supported"),
+    Key("rope_theta", REAL, default=None),
+)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -58,121 +70,55 @@ class LlamaConfig:
         self.validate()
 
     def validate(self) -> None:
-        for name in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
-                     "num_attention_heads", "max_position_embeddings", "num_key_value_heads",
-                     "head_dim"):
-            value = getattr(self, name)
-            if isinstance(value, bool) or not isinstance(value, int) or value <= 0:
-                raise ConfigError(f"config field {name!r} must be a positive integer")
-        if self.hidden_size % self.num_attention_heads != 0:
+        """Types of the fields (a configuration may be built in code, not only read) and
+        the rules between them."""
+        own = {field.name: getattr(self, field.name) for field in dataclasses.fields(self)}
+        read_keys(own, [key for key in LLAMA_KEYS if key.name in own])
+        heads, hidden = self.num_attention_heads, self.hidden_size
+        if hidden % heads:
             raise ConfigError("hidden_size must be divisible by num_attention_heads")
-        if self.head_dim != self.hidden_size // self.num_attention_heads:
+        if self.head_dim != hidden // heads:
             raise ConfigError("head_dim must equal hidden_size / num_attention_heads")
-        if self.head_dim % 2 != 0:
+        if self.head_dim % 2:
             raise ConfigError("the full rotary head dimension must be even")
-        if self.num_key_value_heads != self.num_attention_heads:
-            raise ConfigError(
-                "num_key_value_heads must equal num_attention_heads; "
-                "GQA/MQA checkpoints are not this architecture")
+        if self.num_key_value_heads != heads:
+            raise ConfigError("num_key_value_heads must equal num_attention_heads; "
+                              "GQA/MQA checkpoints are not this architecture")
         if self.vocab_size > 2 ** 32:
             raise ConfigError("vocab_size exceeds the 32-bit token id range")
-        _positive_finite(self.rms_norm_eps, "rms_norm_eps")
-        _positive_finite(self.rope_theta, "rope_theta")
-        if not isinstance(self.tie_word_embeddings, bool):
-            raise ConfigError("config field 'tie_word_embeddings' must be a boolean")
 
     @classmethod
     def from_dict(cls, document: Mapping[str, Any]) -> "LlamaConfig":
-        if document.get("model_type") != "llama":
-            raise ConfigError("config field 'model_type' must be exactly 'llama'")
-        vocab = _positive_int(document, "vocab_size")
-        hidden = _positive_int(document, "hidden_size")
-        intermediate = _positive_int(document, "intermediate_size")
-        layers = _positive_int(document, "num_hidden_layers")
-        heads = _positive_int(document, "num_attention_heads")
-        max_positions = _positive_int(document, "max_position_embeddings")
-        if hidden % heads != 0:
+        try:
+            values = read_keys(document, LLAMA_KEYS)
+        except ConfigError as problem:
+            if "'rope_scaling'" in str(problem):
+                raise ConfigError("scaled or dynamic RoPE configurations are not "
+                                  "supported") from None
+            raise
+        heads, hidden = values["num_attention_heads"], values["hidden_size"]
+        if hidden % heads:
             raise ConfigError("hidden_size must be divisible by num_attention_heads")
-        derived_head_dim = hidden // heads
-
-        kv_heads = document.get("num_key_value_heads", heads)
-        if kv_heads is None:
-            kv_heads = heads
-        if isinstance(kv_heads, bool) or not isinstance(kv_heads, int):
-            raise ConfigError("config field 'num_key_value_heads' must be an integer")
-        head_dim = document.get("head_dim", derived_head_dim)
-        if head_dim is None:
-            head_dim = derived_head_dim
-        if isinstance(head_dim, bool) or not isinstance(head_dim, int):
-            raise ConfigError("config field 'head_dim' must be an integer")
-
-        if document.get("hidden_act", "silu") != "silu":
-            raise ConfigError("only hidden_act='silu' is supported")
-        if _optional_bool(document, "attention_bias", False):
-            raise ConfigError("attention projection biases are not supported")
-        if _optional_bool(document, "mlp_bias", False):
-            raise ConfigError("MLP projection biases are not supported")
-        if _positive_finite(document.get("partial_rotary_factor", 1.0),
-                            "partial_rotary_factor") != 1.0:
-            raise ConfigError("partial rotary dimensions are not supported")
-        if document.get("rope_scaling") is not None:
-            raise ConfigError("scaled or dynamic RoPE configurations are not supported")
-
-        parameter_theta = None
-        rope_parameters = document.get("rope_parameters")
-        if rope_parameters is not None:
-            if not isinstance(rope_parameters, dict):
-                raise ConfigError("config field 'rope_parameters' must be an object")
-            unknown = set(rope_parameters) - {"rope_type", "rope_theta", "partial_rotary_factor"}
-            if unknown:
-                raise ConfigError("unsupported rope_parameters fields: "
-                                  + ", ".join(sorted(unknown)))
-            if rope_parameters.get("rope_type", "default") != "default":
-                raise ConfigError("only default, unscaled RoPE is supported")
-            if _positive_finite(rope_parameters.get("partial_rotary_factor", 1.0),
-                                "rope_parameters.partial_rotary_factor") != 1.0:
-                raise ConfigError("partial rotary dimensions are not supported")
-            if "rope_theta" in rope_parameters:
-                parameter_theta = _positive_finite(rope_parameters["rope_theta"],
-                                                   "rope_parameters.rope_theta")
-        theta = _positive_finite(document.get("rope_theta", 10000.0), "rope_theta")
-        if parameter_theta is not None and parameter_theta != theta:
-            raise ConfigError("rope_theta and rope_parameters.rope_theta disagree")
-
-        return cls(
-            vocab_size=vocab,
-            hidden_size=hidden,
-            intermediate_size=intermediate,
-            num_hidden_layers=layers,
-            num_attention_heads=heads,
-            max_position_embeddings=max_positions,
-            num_key_value_heads=kv_heads,
-            head_dim=head_dim,
-            rms_norm_eps=_positive_finite(document.get("rms_norm_eps", 1.0e-6), "rms_norm_eps"),
-            rope_theta=theta,
-            tie_word_embeddings=_optional_bool(document, "tie_word_embeddings", False),
-        )
+        if values["rope_parameters"] is not None:
+            only_keys(values["rope_parameters"], ROPE_PARAMETER_KEYS, "rope_parameters")
+            nested = read_keys(values["rope_parameters"], ROPE_PARAMETER_KEYS, "rope_parameters.")
+            if nested["rope_theta"] not in (None, values["rope_theta"]):
+                raise ConfigError("rope_theta and rope_parameters.rope_theta disagree")
+        fields = {field.name for field in dataclasses.fields(cls)}
+        chosen = {name: value for name, value in values.items() if name in fields}
+        if chosen["num_key_value_heads"] is None:
+            chosen["num_key_value_heads"] = heads
+        if chosen["head_dim"] is None:
+            chosen["head_dim"] = hidden // heads
+        return cls(**chosen)
 
     def to_dict(self) -> Dict[str, Any]:
-        return {
-            "architectures": [self.architecture],
-            "model_type": self.model_type,
-            "vocab_size": self.vocab_size,
-            "hidden_size": self.hidden_size,
-            "intermediate_size": self.intermediate_size,
-            "num_hidden_layers": self.num_hidden_layers,
-            "num_attention_heads": self.num_attention_heads,
-            "num_key_value_heads": self.num_key_value_heads,
-            "head_dim": self.head_dim,
-            "max_position_embeddings": self.max_position_embeddings,
-            "hidden_act": "silu",
-            "rms_norm_eps": self.rms_norm_eps,
-            "rope_theta": self.rope_theta,
-            "rope_scaling": None,
-            "attention_bias": False,
-            "mlp_bias": False,
-            "tie_word_embeddings": self.tie_word_embeddings,
-        }
+        document: Dict[str, Any] = {"architectures": [self.architecture],
+                                    "model_type": self.model_type}
+        document.update(dataclasses.asdict(self))
+        document.update(hidden_act="silu", rope_scaling=None, attention_bias=False,
+                        mlp_bias=False)
+        return document
 
     def parameter_count(self) -> int:
         h, i, v = self.hidden_size, self.intermediate_size, self.vocab_size

@@ -9,11 +9,11 @@ gate so a second architecture is one ``register_architecture`` call.
 from __future__ import annotations
 
 import dataclasses
-import json
 import os
 from typing import Any, Callable, Dict, Mapping, Tuple
 
 from .errors import ConfigError
+from .strict_json import parse_object
 from .spec import ModelSpec
 
 
@@ -67,26 +67,15 @@ def architecture_for(document: Mapping[str, Any]) -> Architecture:
         f"known: {', '.join(known_architectures()) or '(none)'}")
 
 
-def _strict_object(pairs):
-    result = {}
-    for key, value in pairs:
-        if key in result:
-            raise ConfigError(f"JSON object contains duplicate key {key!r}")
-        result[key] = value
-    return result
-
-
 def read_config_json(path: str) -> Dict[str, Any]:
-    """Parse ``config.json`` strictly: duplicate keys are an error
-    (tools/convert_hf_llama.py:43-49)."""
+    """``config.json`` as a dictionary; a key given twice, a root that is no object and text
+    that is no JSON are errors (tools/convert_hf_llama.py:43-49)."""
     try:
-        with open(path, "r", encoding="utf-8") as source:
-            document = json.load(source, object_pairs_hook=_strict_object)
-    except (OSError, UnicodeError, json.JSONDecodeError) as error:
-        raise ConfigError(f"could not parse JSON file {path}: {error}") from error
-    if not isinstance(document, dict):
-        raise ConfigError(f"JSON root in {path} must be an object")
-    return document
+        with open(path, "rb") as source:
+            text = source.read()
+    except OSError as problem:
+        raise ConfigError(f"could not parse {path}: {problem}") from problem
+    return parse_object(text, f"could not parse {path}", ConfigError)
 
 
 def load_config(model_dir: str):

@@ -1,6 +1,6 @@
 from .engine import (Engine, EngineConfig, GenerationResult, IterationResult, load_model,
                      parse_dtype, random_model, write_random_model)
-from .metrics import DurationStatistics, SchedulerMetrics, summarize_request_metrics
+from .metrics import DurationStatistics, SchedulerMetrics, observe
 from .scheduler import (FifoScheduler, IterationBatch, Request, RequestState, ScheduledWork,
                         SchedulerConfig, StopReason, WorkCompletion, WorkKind)
 from .step import StepEntry, StepError, StepFunction
@@ -10,6 +10,6 @@ __all__ = [
     "IterationResult", "Request", "RequestState", "ScheduledWork", "SchedulerConfig",
     "SchedulerMetrics",
     "StepEntry", "StepError", "StepFunction", "StopReason", "WorkCompletion", "WorkKind",
-    "load_model", "parse_dtype", "random_model", "summarize_request_metrics",
+    "load_model", "parse_dtype", "random_model", "observe",
     "write_random_model",
 ]

@@ -27,7 +27,7 @@ from ..ops import library as ops
 from .scheduler import (FifoScheduler, IterationBatch, Request, RequestState, SchedulerConfig,
                         StopReason, WorkCompletion, WorkKind)
 from .graphs import DecodeGraphs, bucketed_context
-from .metrics import SchedulerMetrics, summarize_request_metrics
+from .metrics import SchedulerMetrics, observe
 from .step import StepEntry, StepError, StepFunction
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -487,7 +487,7 @@ class Engine:
     def metrics(self, observed_at: Optional[float] = None) -> SchedulerMetrics:
         """Counts, rates and latency distributions over every request this engine has seen
         (include/helix/runtime/cpu_engine.hpp:91); times are ``time.monotonic()`` seconds."""
-        return summarize_request_metrics(self.scheduler.requests.values(),
+        return observe(self.scheduler.requests.values(),
                                          time.monotonic() if observed_at is None else observed_at)
 
     def stats(self) -> Dict[str, object]:

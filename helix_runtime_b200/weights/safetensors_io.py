@@ -1,12 +1,13 @@
-"""A small reader and writer for the safetensors container.
+"""The safetensors container: a reader over a memory map and a writer.
 
-Format: 8-byte little-endian header length, a JSON header mapping each tensor
-name to ``{dtype, shape, data_offsets}``, then the raw little-endian payloads.
-The checks mirror the reference's own parser (tools/convert_hf_llama.py:208-313):
-bounded header, canonical record fields, byte range equal to shape × dtype size,
-payloads that neither overlap nor leave holes, no trailing bytes.  Sharded
-checkpoints (``model.safetensors.index.json``) are resolved inside the folder
-only (tools/convert_hf_llama.py:357-368).
+A file is an 8-byte little-endian header length, a JSON header that maps each tensor name to
+``{dtype, shape, data_offsets}``, and one data buffer.  The reader turns the header into a
+table of :class:`TensorRecord` and then checks the table as a whole: every record's byte
+range must match its shape and dtype, and the ranges, sorted, must tile the data buffer
+exactly (no overlap, no hole, nothing behind the last one).  Tensors are views into one
+read-only memory map of the file, copied out when read.  The reference's converter applies
+the same rules to the same format (tools/convert_hf_llama.py:208-313) and resolves sharded
+checkpoints inside the folder only (tools/convert_hf_llama.py:316-368).
 """
 from __future__ import annotations
 
@@ -14,21 +15,36 @@ import json
 import math
 import os
 import struct
-from typing import Dict, Iterable, List, Mapping, NamedTuple, Optional, Tuple
+from typing import Dict, List, Mapping, NamedTuple, Optional, Tuple
 
 import numpy as np
 import torch
 
-MAX_HEADER_BYTES = 100_000_000
+from ..config.strict_json import parse_object
 
-_DTYPE_BYTES = {"F32": 4, "F16": 2, "BF16": 2, "I32": 4, "I64": 8}
-_NUMPY_DTYPE = {"F32": "<f4", "F16": "<f2", "BF16": "<u2", "I32": "<i4", "I64": "<i8"}
-_TORCH_TO_NAME = {torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16",
-                  torch.int32: "I32", torch.int64: "I64"}
+MAX_HEADER_BYTES = 100_000_000
+INDEX_NAME = "model.safetensors.index.json"
+SINGLE_NAME = "model.safetensors"
 
 
 class SafetensorsError(RuntimeError):
     """The file is not a well-formed safetensors container."""
+
+
+class _Storage(NamedTuple):
+    numpy: str              # how numpy reads the stored bytes
+    torch: torch.dtype
+    bytes: int
+
+
+STORAGE: Dict[str, _Storage] = {
+    "F32": _Storage("<f4", torch.float32, 4),
+    "F16": _Storage("<f2", torch.float16, 2),
+    "BF16": _Storage("<i2", torch.bfloat16, 2),     # read as 16-bit integers, then reinterpreted
+    "I32": _Storage("<i4", torch.int32, 4),
+    "I64": _Storage("<i8", torch.int64, 8),
+}
+_NAME_OF = {storage.torch: name for name, storage in STORAGE.items()}
 
 
 class TensorRecord(NamedTuple):
@@ -39,168 +55,163 @@ class TensorRecord(NamedTuple):
     end: int
 
 
-def _strict_object(pairs):
-    result = {}
-    for key, value in pairs:
-        if key in result:
-            raise SafetensorsError(f"JSON object contains duplicate key {key!r}")
-        result[key] = value
-    return result
+def _is_count(value) -> bool:
+    return isinstance(value, int) and not isinstance(value, bool) and value >= 0
+
+
+def _record_from(where: str, name: str, entry, data_bytes: int) -> TensorRecord:
+    """One header entry as a record, or a SafetensorsError that says what is wrong with it."""
+    def bad(problem: str) -> SafetensorsError:
+        return SafetensorsError(f"{where}: tensor {name!r} {problem}")
+
+    if not isinstance(entry, dict) or sorted(entry) != ["data_offsets", "dtype", "shape"]:
+        raise bad("has noncanonical metadata (exactly dtype, shape, data_offsets)")
+    storage = STORAGE.get(entry["dtype"]) if isinstance(entry["dtype"], str) else None
+    if storage is None:
+        raise bad(f"uses unsupported dtype {entry['dtype']!r}")
+    shape, offsets = entry["shape"], entry["data_offsets"]
+    if not isinstance(shape, list) or not all(_is_count(extent) for extent in shape):
+        raise bad("has an invalid shape")
+    if not isinstance(offsets, list) or len(offsets) != 2 or not all(map(_is_count, offsets)):
+        raise bad("has invalid data offsets")
+    start, end = offsets
+    if not start <= end <= data_bytes:
+        raise bad("exceeds data-buffer bounds")
+    if end - start != math.prod(shape) * storage.bytes:
+        raise bad("has a byte range that does not match its shape and dtype")
+    return TensorRecord(name, entry["dtype"], tuple(shape), start, end)
+
+
+def _check_tiling(where: str, records: List[TensorRecord], data_bytes: int) -> None:
+    """The byte ranges, in file order, must follow one another from 0 to the buffer's end."""
+    ordered = sorted(records, key=lambda record: (record.start, record.end))
+    expected = 0
+    for record in ordered:
+        if record.start < expected:
+            raise SafetensorsError(f"{where}: tensor {record.name!r} overlaps a prior tensor")
+        if record.start > expected:
+            raise SafetensorsError(f"{where}: tensor {record.name!r} leaves a data hole")
+        expected = record.end
+    if expected != data_bytes:
+        raise SafetensorsError(f"{where}: data buffer has trailing unclaimed bytes")
 
 
 class SafetensorsFile:
-    """Header of one file plus lazy, memory-mapped access to its tensors."""
+    """One container file: its record table and a read-only map of its data buffer."""
 
     def __init__(self, path: str) -> None:
         self.path = path
         try:
-            file_size = os.stat(path).st_size
+            size = os.path.getsize(path)
             with open(path, "rb") as source:
-                length_bytes = source.read(8)
-                if len(length_bytes) != 8:
+                prefix = source.read(8)
+                if len(prefix) < 8:
                     raise SafetensorsError(f"{path}: missing header length")
-                (header_length,) = struct.unpack("<Q", length_bytes)
-                if header_length > MAX_HEADER_BYTES:
+                (header_bytes,) = struct.unpack("<Q", prefix)
+                if header_bytes > MAX_HEADER_BYTES:
                     raise SafetensorsError(f"{path}: header exceeds {MAX_HEADER_BYTES} bytes")
-                if header_length > file_size - 8:
+                if 8 + header_bytes > size:
                     raise SafetensorsError(f"{path}: header exceeds file bounds")
-                header_bytes = source.read(header_length)
-        except OSError as error:
-            raise SafetensorsError(f"could not read {path}: {error}") from error
-        try:
-            header = json.loads(header_bytes.decode("utf-8"), object_pairs_hook=_strict_object)
-        except (UnicodeError, json.JSONDecodeError) as error:
-            raise SafetensorsError(f"{path}: invalid JSON header: {error}") from error
-        if not isinstance(header, dict):
-            raise SafetensorsError(f"{path}: header must be an object")
-        header.pop("__metadata__", None)
+                text = source.read(header_bytes)
+        except OSError as problem:
+            raise SafetensorsError(f"could not read {path}: {problem}") from problem
+        header = parse_object(text, f"{path}: header", SafetensorsError)
+        self.data_offset = 8 + header_bytes
+        data_bytes = size - self.data_offset
+        self.records: Dict[str, TensorRecord] = {
+            name: _record_from(path, name, entry, data_bytes)
+            for name, entry in header.items() if name != "__metadata__"}
+        _check_tiling(path, list(self.records.values()), data_bytes)
+        self._map: Optional[np.memmap] = None
 
-        data_bytes = file_size - 8 - header_length
-        self.data_offset = 8 + header_length
-        self.records: Dict[str, TensorRecord] = {}
-        ranges: List[Tuple[int, int, str]] = []
-        for name, record in header.items():
-            if not isinstance(record, dict) or set(record) != {"dtype", "shape", "data_offsets"}:
-                raise SafetensorsError(f"{path}: tensor {name!r} has noncanonical metadata")
-            dtype = record["dtype"]
-            if dtype not in _DTYPE_BYTES:
-                raise SafetensorsError(f"{path}: tensor {name!r} uses unsupported dtype {dtype!r}")
-            shape = record["shape"]
-            if not isinstance(shape, list) or any(
-                    isinstance(d, bool) or not isinstance(d, int) or d < 0 for d in shape):
-                raise SafetensorsError(f"{path}: tensor {name!r} has an invalid shape")
-            offsets = record["data_offsets"]
-            if (not isinstance(offsets, list) or len(offsets) != 2 or any(
-                    isinstance(o, bool) or not isinstance(o, int) for o in offsets)):
-                raise SafetensorsError(f"{path}: tensor {name!r} has invalid data offsets")
-            start, end = offsets
-            if start < 0 or end < start or end > data_bytes:
-                raise SafetensorsError(f"{path}: tensor {name!r} exceeds data-buffer bounds")
-            if end - start != math.prod(shape) * _DTYPE_BYTES[dtype]:
-                raise SafetensorsError(
-                    f"{path}: tensor {name!r} byte range does not match its shape/dtype")
-            self.records[name] = TensorRecord(name, dtype, tuple(shape), start, end)
-            ranges.append((start, end, name))
-        cursor = 0
-        for start, end, name in sorted(ranges):
-            if start != cursor:
-                relation = "overlaps a prior tensor" if start < cursor else "leaves a data hole"
-                raise SafetensorsError(f"{path}: tensor {name!r} {relation}")
-            cursor = end
-        if cursor != data_bytes:
-            raise SafetensorsError(f"{path}: data buffer has trailing unclaimed bytes")
+    def _data(self) -> np.ndarray:
+        if self._map is None:
+            self._map = np.memmap(self.path, dtype=np.uint8, mode="r", offset=self.data_offset) \
+                if os.path.getsize(self.path) > self.data_offset else np.zeros(0, dtype=np.uint8)
+        return self._map
 
     def read(self, name: str) -> torch.Tensor:
-        """Return the tensor in its stored dtype (a fresh CPU tensor)."""
+        """The tensor in its stored dtype: a fresh CPU tensor that owns its memory."""
         record = self.records[name]
-        count = math.prod(record.shape)
-        if count == 0:
-            array = np.zeros(record.shape, dtype=np.dtype(_NUMPY_DTYPE[record.dtype]))
-        else:
-            array = np.fromfile(self.path, dtype=np.dtype(_NUMPY_DTYPE[record.dtype]),
-                                count=count, offset=self.data_offset + record.start)
-            array = array.reshape(record.shape)
-        if record.dtype == "BF16":
-            return torch.from_numpy(array.view(np.int16)).view(torch.bfloat16)
-        return torch.from_numpy(array)
+        storage = STORAGE[record.dtype]
+        raw = np.array(self._data()[record.start:record.end])          # copy out of the map
+        tensor = torch.from_numpy(raw.view(storage.numpy).reshape(record.shape))
+        return tensor.view(storage.torch) if record.dtype == "BF16" else tensor
 
 
 class Checkpoint:
-    """All tensors of a model folder: one ``model.safetensors`` or an index of shards."""
+    """Every tensor of a model folder, whether it is one file or an index over shards."""
 
     def __init__(self, directory: str) -> None:
         self.directory = os.path.realpath(directory)
         if not os.path.isdir(self.directory):
             raise SafetensorsError(f"checkpoint path is not a directory: {directory}")
-        index_path = os.path.join(self.directory, "model.safetensors.index.json")
-        single_path = os.path.join(self.directory, "model.safetensors")
         self._files: Dict[str, SafetensorsFile] = {}
-        self._where: Dict[str, str] = {}
+        self._home: Dict[str, SafetensorsFile] = {}
+        for name, filename in self._placement().items():
+            shard = self._shard(filename)
+            if name not in shard.records:
+                raise SafetensorsError(
+                    f"index maps tensor {name!r} to {filename}, but the shard lacks it")
+            self._home[name] = shard
+
+    def _placement(self) -> Dict[str, Optional[str]]:
+        """``tensor name -> shard file name`` from the index, or from the single file."""
+        index_path = os.path.join(self.directory, INDEX_NAME)
         if os.path.exists(index_path):
-            with open(index_path, "r", encoding="utf-8") as source:
-                index = json.load(source, object_pairs_hook=_strict_object)
-            weight_map = index.get("weight_map") if isinstance(index, dict) else None
-            if not isinstance(weight_map, dict) or any(
-                    not isinstance(k, str) or not isinstance(v, str) or not v
-                    for k, v in weight_map.items()):
+            with open(index_path, "rb") as source:
+                index = parse_object(source.read(), index_path, SafetensorsError)
+            placement = index.get("weight_map")
+            if not isinstance(placement, dict) or not all(
+                    isinstance(filename, str) and filename for filename in placement.values()):
                 raise SafetensorsError("index weight_map must map tensor names to files")
-            for name, filename in weight_map.items():
-                resolved = os.path.realpath(os.path.join(self.directory, filename))
-                if os.path.commonpath([resolved, self.directory]) != self.directory \
-                        or not os.path.isfile(resolved):
-                    raise SafetensorsError(
-                        f"index shard {filename!r} does not resolve inside the checkpoint")
-                if resolved not in self._files:
-                    self._files[resolved] = SafetensorsFile(resolved)
-                if name not in self._files[resolved].records:
-                    raise SafetensorsError(
-                        f"index maps tensor {name!r} to {filename}, but the shard lacks it")
-                self._where[name] = resolved
-        elif os.path.exists(single_path):
-            self._files[single_path] = SafetensorsFile(single_path)
-            for name in self._files[single_path].records:
-                self._where[name] = single_path
-        else:
+            return placement
+        if os.path.exists(os.path.join(self.directory, SINGLE_NAME)):
+            return {name: SINGLE_NAME for name in self._shard(SINGLE_NAME).records}
+        raise SafetensorsError(f"{self.directory} contains neither {SINGLE_NAME} nor {INDEX_NAME}")
+
+    def _shard(self, filename: str) -> SafetensorsFile:
+        """The opened shard; a name that leads out of the folder is refused."""
+        path = os.path.realpath(os.path.join(self.directory, filename))
+        leaves = os.path.relpath(path, self.directory).split(os.sep)[0] == os.pardir
+        if leaves or not os.path.isfile(path):
             raise SafetensorsError(
-                f"{self.directory} contains neither model.safetensors nor "
-                "model.safetensors.index.json")
+                f"index shard {filename!r} does not resolve inside the checkpoint")
+        if path not in self._files:
+            self._files[path] = SafetensorsFile(path)
+        return self._files[path]
 
     def names(self) -> List[str]:
-        return list(self._where)
+        return list(self._home)
 
     def record(self, name: str) -> TensorRecord:
-        return self._files[self._where[name]].records[name]
+        return self._home[name].records[name]
 
     def read(self, name: str) -> torch.Tensor:
-        return self._files[self._where[name]].read(name)
+        return self._home[name].read(name)
 
 
 def write_safetensors(path: str, tensors: Mapping[str, torch.Tensor],
                       metadata: Optional[Mapping[str, str]] = None) -> None:
-    """Write ``tensors`` (CPU, contiguous) in insertion order."""
-    header: Dict[str, object] = {}
-    if metadata:
-        header["__metadata__"] = dict(metadata)
-    cursor = 0
+    """Write ``tensors`` in insertion order, payloads back to back."""
+    payloads: List[bytes] = []
+    header: Dict[str, object] = {"__metadata__": dict(metadata)} if metadata else {}
+    end = 0
     for name, tensor in tensors.items():
-        if tensor.dtype not in _TORCH_TO_NAME:
+        stored = _NAME_OF.get(tensor.dtype)
+        if stored is None:
             raise SafetensorsError(f"tensor {name!r} has unsupported dtype {tensor.dtype}")
-        size = tensor.numel() * tensor.element_size()
-        header[name] = {"dtype": _TORCH_TO_NAME[tensor.dtype], "shape": list(tensor.shape),
-                        "data_offsets": [cursor, cursor + size]}
-        cursor += size
-    header_bytes = json.dumps(header, separators=(",", ":")).encode("utf-8")
-    header_bytes += b" " * ((8 - len(header_bytes) % 8) % 8)
+        data = tensor.detach().contiguous().cpu()
+        if stored == "BF16":
+            data = data.view(torch.int16)
+        payloads.append(data.numpy().astype(STORAGE[stored].numpy, copy=False).tobytes())
+        header[name] = {"dtype": stored, "shape": list(tensor.shape),
+                        "data_offsets": [end, end + len(payloads[-1])]}
+        end += len(payloads[-1])
+    text = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    text += b" " * (-len(text) % 8)                 # the data buffer starts 8-byte aligned
     with open(path, "wb") as output:
-        output.write(struct.pack("<Q", len(header_bytes)))
-        output.write(header_bytes)
-        for tensor in tensors.values():
-            data = tensor.detach().contiguous().cpu()
-            if data.dtype == torch.bfloat16:
-                data = data.view(torch.int16)
-            output.write(data.numpy().tobytes())
-
-
-def iter_names(files: Iterable[SafetensorsFile]) -> Iterable[str]:
-    for file in files:
-        yield from file.records
+        output.write(struct.pack("<Q", len(text)))
+        output.write(text)
+        for payload in payloads:
+            output.write(payload)

@@ -7,22 +7,20 @@ import pytest
 import torch
 
 from helix_runtime_b200.cache import CacheManager, KvNeed
-from helix_runtime_b200.engine import (FifoScheduler, SchedulerConfig, WorkCompletion,
-                                       summarize_request_metrics)
-from helix_runtime_b200.engine.metrics import interpolated_percentile, summarize_durations
+from helix_runtime_b200.engine import (DurationStatistics, FifoScheduler, SchedulerConfig,
+                                       WorkCompletion, observe)
 
 
 def test_percentiles_interpolate_between_sorted_samples():
-    samples = [1.0, 2.0, 4.0, 8.0]
-    assert interpolated_percentile(samples, 0.5) == pytest.approx(3.0)        # position 1.5
-    assert interpolated_percentile(samples, 0.95) == pytest.approx(4.0 + 0.85 * 4.0)
-    assert interpolated_percentile([7.0], 0.95) == 7.0
-    summary = summarize_durations([8.0, 1.0, 4.0, 2.0])
+    summary = DurationStatistics.of([8.0, 1.0, 4.0, 2.0])
     assert (summary.sample_count, summary.minimum_seconds, summary.maximum_seconds) == (4, 1.0, 8.0)
-    assert summary.mean_seconds == pytest.approx(3.75) and summary.p50_seconds == pytest.approx(3.0)
-    assert summarize_durations([]).sample_count == 0
-    with pytest.raises(ValueError):
-        interpolated_percentile([], 0.5)
+    assert summary.mean_seconds == pytest.approx(3.75)
+    assert summary.p50_seconds == pytest.approx(3.0)                    # position 1.5
+    assert summary.p95_seconds == pytest.approx(4.0 + 0.85 * 4.0)       # position 2.85
+    assert DurationStatistics.of([7.0]).p95_seconds == 7.0
+    # events that have not happened are NaN and do not count
+    assert DurationStatistics.of([float("nan"), 2.0]).sample_count == 1
+    assert DurationStatistics.of([]) == DurationStatistics()
 
 
 def drive(scheduler, cache, now, token=7):
@@ -39,14 +37,14 @@ def drive(scheduler, cache, now, token=7):
 def test_metrics_of_a_small_run():
     cache = CacheManager({0: KvNeed(1, 4)}, {}, 4, 16, 2, 64, torch.float32, torch.device("cpu"))
     scheduler = FifoScheduler(SchedulerConfig(8, 2), 4)
-    assert summarize_request_metrics([], 5.0).request_count == 0
+    assert observe([], 5.0).request_count == 0
     first = scheduler.submit([1, 2, 3], max_new_tokens=3, now=10.0)
     second = scheduler.submit([4, 5], max_new_tokens=2, now=11.0)
     third = scheduler.submit([6], max_new_tokens=5, now=12.0)        # waits: two run at a time
     drive(scheduler, cache, 20.0)        # both prompts; first tokens at 20.5
     drive(scheduler, cache, 21.0)        # second tokens at 21.5; the second request finishes
     scheduler.cancel(first, now=22.0)
-    metrics = summarize_request_metrics(scheduler.requests.values(), 30.0)
+    metrics = observe(scheduler.requests.values(), 30.0)
     assert (metrics.request_count, metrics.waiting_count, metrics.finished_count,
             metrics.cancelled_count, metrics.decoding_count) == (3, 1, 1, 1, 0)
     assert metrics.prompt_tokens_processed == 5 and metrics.generated_tokens == 4
@@ -66,10 +64,10 @@ def test_metrics_of_a_small_run():
     assert metrics.inter_token_latency.p95_seconds == pytest.approx(1.0)
     assert scheduler.request(third).first_scheduled_at is None
     with pytest.raises(ValueError, match="precedes"):
-        summarize_request_metrics(scheduler.requests.values(), 21.0)
+        observe(scheduler.requests.values(), 21.0)
     with pytest.raises(ValueError, match="twice"):
-        summarize_request_metrics([scheduler.request(first)] * 2, 30.0)
+        observe([scheduler.request(first)] * 2, 30.0)
     # no window, no rates
     alone = FifoScheduler(SchedulerConfig(8, 2), 4)
     alone.submit([1], max_new_tokens=1, now=3.0)
-    assert not summarize_request_metrics(alone.requests.values(), 3.0).throughput_defined
+    assert not observe(alone.requests.values(), 3.0).throughput_defined

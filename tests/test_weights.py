@@ -178,3 +178,43 @@ def test_rotary_row_permutation_matches_the_plain_conversion(model_root):
     assert not out[:, :, 24:].any()
     np.testing.assert_array_equal(out[:, :, :24].reshape(120, 120),
                                   plain.weights["layer.1.attention_output"].T)
+
+
+def test_sharded_checkpoints_resolve_inside_the_folder_only(tmp_path):
+    """An index maps tensor names to shard files (tools/convert_hf_llama.py:316-368)."""
+    folder = tmp_path / "sharded"
+    folder.mkdir()
+    write_safetensors(str(folder / "one.safetensors"), {"a": torch.arange(4.0)})
+    write_safetensors(str(folder / "two.safetensors"), {"b": torch.ones(2, 2), "c": torch.zeros(3)})
+    index = {"metadata": {}, "weight_map": {"a": "one.safetensors", "b": "two.safetensors",
+                                            "c": "two.safetensors"}}
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    checkpoint = Checkpoint(str(folder))
+    assert sorted(checkpoint.names()) == ["a", "b", "c"]
+    assert torch.equal(checkpoint.read("a"), torch.arange(4.0))
+    assert checkpoint.record("b").shape == (2, 2)
+    # a shard that lacks the tensor the index gives it
+    index["weight_map"]["c"] = "one.safetensors"
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(SafetensorsError, match="lacks it"):
+        Checkpoint(str(folder))
+    # a shard outside the folder, by a relative path or a link
+    write_safetensors(str(tmp_path / "outside.safetensors"), {"c": torch.zeros(3)})
+    index["weight_map"]["c"] = "../outside.safetensors"
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(SafetensorsError, match="does not resolve inside"):
+        Checkpoint(str(folder))
+    os.symlink(str(tmp_path / "outside.safetensors"), str(folder / "link.safetensors"))
+    index["weight_map"]["c"] = "link.safetensors"
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(SafetensorsError, match="does not resolve inside"):
+        Checkpoint(str(folder))
+    # a key given twice in the index
+    (folder / "model.safetensors.index.json").write_text(
+        '{"weight_map": {"a": "one.safetensors"}, "weight_map": {}}')
+    with pytest.raises(SafetensorsError, match="duplicate key 'weight_map'"):
+        Checkpoint(str(folder))
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    with pytest.raises(SafetensorsError, match="contains neither"):
+        Checkpoint(str(empty))
