@@ -1043,3 +1043,43 @@ HX_API int hx_gemm_tc_rope_append(const void* x, int ldx, int x_capacity_rows, c
   HX_CHECK_LAUNCH("hx_gemm_tc_rope_append");
   return HX_OK;
 }
+
+// ------------------------------------------------------------ the bounded wait, by itself
+//
+// What a kernel of this library does when an mbarrier it waits for never completes: the wait
+// gives up after its limit, the thread sets HX_FLAG_WAIT_TIMEOUT in the status word and the
+// kernel returns; the host then fails the step.  This entry point runs exactly that path on a
+// barrier of its own, with a limit of `polls` polls instead of the kernels' forty million, so
+// that the path can be exercised in a fraction of a millisecond: with `arrive` = 0 nobody
+// ever arrives at the barrier and the wait must run out; with `arrive` = 1 the waiting
+// thread's own arrival completes the phase first and the wait must succeed.  `succeeded`
+// (device, one int, may be null) receives 1 when the wait succeeded and 0 when it ran out.
+namespace {
+
+__global__ void bounded_wait_kernel(uint32_t polls, int arrive, int* status, int* succeeded) {
+  __shared__ __align__(8) uint64_t barrier;
+  hx_pdl_prologue();
+  if (threadIdx.x == 0) {
+    mbar_init(&barrier, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (arrive) mbar_arrive(&barrier);
+    const bool ok = mbar_wait(&barrier, 0, polls);
+    if (!ok && status != nullptr) atomicOr(status, HX_FLAG_WAIT_TIMEOUT);
+    if (succeeded != nullptr) *succeeded = ok ? 1 : 0;
+  }
+}
+
+}  // namespace
+
+HX_API int hx_bounded_wait_check(int polls, int arrive, int* status, int* succeeded,
+                                 cudaStream_t stream) {
+  HX_REQUIRE(polls > 0 && polls <= 1000000, "hx_bounded_wait_check: 1 to 1,000,000 polls");
+  HX_REQUIRE(status != nullptr, "hx_bounded_wait_check: status word missing");
+  hx_launch(bounded_wait_kernel, 1, 32, 0, stream, static_cast<uint32_t>(polls), arrive, status,
+            succeeded);
+  HX_CHECK_LAUNCH("hx_bounded_wait_check");
+  return HX_OK;
+}

@@ -27,10 +27,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                : "memory");
 }
 
-// Bounded wait: false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait: false when the limit ran out (``limit`` polls; the kernels use WAIT_LIMIT).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          uint32_t limit = WAIT_LIMIT) {
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < WAIT_LIMIT; ++spin) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

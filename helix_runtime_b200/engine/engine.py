@@ -343,6 +343,14 @@ class Engine:
             feed_rows = [row_of[work.request_id] for work in batch.work]
         for work in batch.work:
             request = self.scheduler.request(work.request_id)
+            # the scheduler counts the tokens a request has fed, the cache the positions it
+            # has pages for; the step takes token values from the one and positions from the
+            # other, so they must agree (src/runtime/cpu_engine.cpp:165, 223)
+            if self.cache.reserved(work.request_id) != work.token_offset:
+                flight.error = (f"request {work.request_id}: the scheduler feeds tokens from "
+                                f"{work.token_offset}, the cache stands at "
+                                f"{self.cache.reserved(work.request_id)}")
+                return flight
             if previous is None:
                 tokens = request.feed_slice(work.token_offset, work.token_count)
             else:

@@ -94,6 +94,8 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_advance_decode.restype = _c_int
     library.hx_feed_tokens.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr]
     library.hx_feed_tokens.restype = _c_int
+    library.hx_bounded_wait_check.argtypes = [_c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]
+    library.hx_bounded_wait_check.restype = _c_int
     for name in ("hx_embed", "hx_rmsnorm", "hx_swiglu", "hx_rope_append", "hx_gemm_simt",
                  "hx_gemm_tc", "hx_gemm_tc_supports", "hx_gemm_tc_token_tile",
                  "hx_paged_attention", "hx_argmax", "hx_sample"):
@@ -423,3 +425,13 @@ def launch_count() -> int:
 def set_dependent_launch(enabled: bool) -> None:
     """Switch programmatic dependent launch of the kernels off (debugging) or on (default)."""
     lib().hx_set_dependent_launch(1 if enabled else 0)
+
+
+def bounded_wait_check(polls: int, arrive: bool, status: torch.Tensor) -> bool:
+    """Run the kernels' bounded mbarrier wait on a barrier of its own with a limit of ``polls``
+    polls.  ``arrive`` False: nobody arrives, the wait runs out, the kernel sets
+    FLAG_WAIT_TIMEOUT in ``status`` and returns.  Returns whether the wait succeeded."""
+    succeeded = torch.full((1,), -1, dtype=torch.int32, device=status.device)
+    _check(lib().hx_bounded_wait_check(int(polls), 1 if arrive else 0, _ptr(status),
+                                       _ptr(succeeded), _stream()))
+    return int(succeeded.item()) == 1

@@ -56,6 +56,10 @@ int hx_abi_version(void);
 const char* hx_last_error(void);          /* message of this thread's last failed call */
 long long hx_launch_count(void);          /* kernels launched by this library so far */
 void hx_set_dependent_launch(int enabled); /* programmatic dependent launch between kernels */
+/* the kernels' bounded mbarrier wait on a barrier of its own, limited to `polls` polls
+   (1..1,000,000): with arrive = 0 it runs out, sets HX_STATUS_WAIT_TIMEOUT in *status and the
+   kernel returns; *succeeded (may be null) receives 1 or 0 */
+int hx_bounded_wait_check(int polls, int arrive, int* status, int* succeeded, cudaStream_t stream);
 
 /* ---- embedding, norm, activation ------------------------------------------------------- */
 /* out[t, :] = table[ids[t], :] as float32 (the residual stream) */

@@ -49,7 +49,7 @@ def read_safetensors(path: str) -> Dict[str, np.ndarray]:
             value = bits.view(F32)
         else:
             raise ValueError(f"unsupported dtype {record['dtype']}")
-        tensors[name] = value.reshape(shape).copy()
+        tensors[name] = value.reshape(shape)      # astype and the shift made fresh arrays
     return tensors
 
 
@@ -84,20 +84,20 @@ def to_helix_layout(config: dict, source: Dict[str, np.ndarray]) -> Dict[str, np
     for layer in range(config["num_hidden_layers"]):
         prefix = f"model.layers.{layer}"
         out[f"layer.{layer}.attention_norm"] = source[f"{prefix}.input_layernorm.weight"]
-        out[f"layer.{layer}.query"] = source[f"{prefix}.self_attn.q_proj.weight"][permutation].T.copy()
-        out[f"layer.{layer}.key"] = source[f"{prefix}.self_attn.k_proj.weight"][permutation].T.copy()
-        out[f"layer.{layer}.value"] = source[f"{prefix}.self_attn.v_proj.weight"].T.copy()
-        out[f"layer.{layer}.attention_output"] = source[f"{prefix}.self_attn.o_proj.weight"].T.copy()
+        out[f"layer.{layer}.query"] = source[f"{prefix}.self_attn.q_proj.weight"][permutation].T
+        out[f"layer.{layer}.key"] = source[f"{prefix}.self_attn.k_proj.weight"][permutation].T
+        out[f"layer.{layer}.value"] = source[f"{prefix}.self_attn.v_proj.weight"].T
+        out[f"layer.{layer}.attention_output"] = source[f"{prefix}.self_attn.o_proj.weight"].T
         out[f"layer.{layer}.ffn_norm"] = source[f"{prefix}.post_attention_layernorm.weight"]
-        out[f"layer.{layer}.gate"] = source[f"{prefix}.mlp.gate_proj.weight"].T.copy()
-        out[f"layer.{layer}.up"] = source[f"{prefix}.mlp.up_proj.weight"].T.copy()
-        out[f"layer.{layer}.down"] = source[f"{prefix}.mlp.down_proj.weight"].T.copy()
+        out[f"layer.{layer}.gate"] = source[f"{prefix}.mlp.gate_proj.weight"].T
+        out[f"layer.{layer}.up"] = source[f"{prefix}.mlp.up_proj.weight"].T
+        out[f"layer.{layer}.down"] = source[f"{prefix}.mlp.down_proj.weight"].T
     out["final_norm"] = source["model.norm.weight"]
     lm_source = "lm_head.weight"
     if lm_source not in source:
         # tied head: the embedding stands in (tools/convert_hf_llama.py:497-510)
         lm_source = "model.embed_tokens.weight"
-    out["lm_head"] = source[lm_source].T.copy()
+    out["lm_head"] = source[lm_source].T
     return out
 
 

@@ -95,6 +95,66 @@ def test_many_requests_chunked_prompts_mixed_with_decoding(dtype, folders, plain
     engine.cache.check()
 
 
+@pytest.mark.parametrize("name,dtype", [("C", "bfloat16"), ("B", "float32")])
+@pytest.mark.parametrize("live", [24, 64])
+def test_decode_steps_with_dozens_of_live_requests(name, dtype, live, folders, plain_models):
+    """24 and 64 requests decode together (the benchmark's largest batch): above 16 tokens a
+    step the streaming attention is launched by another protocol and the weight-streaming
+    products take wider token tiles.  Half as many requests again wait for a slot, so pages
+    and slots are used again; every token of every request is checked."""
+    plain = plain_models(name, dtype)
+    config = tiny_config(name)
+    page = PAGE_SIZE[name]
+    total = live + live // 2
+    rng = np.random.default_rng(live)
+    lengths = [int(n) for n in rng.integers(1, 40, size=total)]
+    lengths[0], lengths[1], lengths[2] = 1, page, page + 1
+    prompts = [random_tokens(config.vocab_size, n, seed=1000 + i) for i, n in enumerate(lengths)]
+    new_tokens = 6
+    pages_each = -(-(max(lengths) + new_tokens) // page)
+    engine = Engine.from_pretrained(folders(name, dtype), dtype=dtype, page_size=page,
+                                    max_running_requests=live, max_tokens_per_iteration=256,
+                                    num_pages=live * pages_each, poison_free_pages=True)
+    results = engine.generate(prompts, max_new_tokens=new_tokens)
+    for prompt, result in zip(prompts, results):
+        assert len(result.generated_tokens) == new_tokens
+        check_greedy(plain, prompt, result.generated_tokens, dtype)
+    stats = engine.stats()
+    assert stats["cache"]["groups"][0]["reuses"] > 0
+    assert stats["scheduler"]["decode_tokens"] >= total * (new_tokens - 1)
+    # steps with more than 16 single-token requests did run
+    assert engine.step_function.tokens_run / max(engine.step_function.steps_run, 1) > 16
+    engine.cache.check()
+    assert not engine.cache.live_requests()
+
+
+def test_a_context_that_crosses_two_graph_buckets(folders, plain_models):
+    """Decode graphs are recorded for contexts rounded up to 256, 512, ...: a request that
+    decodes from position 240 to 530 crosses two of those borders while two shorter requests
+    decode beside it; every token is checked."""
+    plain = plain_models("C", "bfloat16")
+    prompts = [random_tokens(512, n, seed=50 + n) for n in (240, 9, 130)]
+    engine = Engine.from_pretrained(folders("C", "bfloat16"), dtype="bfloat16", page_size=16,
+                                    max_running_requests=3, max_tokens_per_iteration=256)
+    ids = [engine.submit(prompts[0], 272), engine.submit(prompts[1], 272),
+           engine.submit(prompts[2], 272)]
+    engine.run_until_done()
+    assert engine.graphs.captures >= 3 and engine.graphs.replays > 200
+    for request_id, prompt in zip(ids, prompts):
+        generated = engine.request(request_id).generated
+        assert len(generated) == 272
+        # teacher-forced check of every 7th token and of the tokens around the bucket borders
+        full = prompt + generated
+        logits = plain.logits(full[:-1])
+        for index in range(len(generated)):
+            position = len(prompt) + index - 1
+            near_border = any(abs(position + 1 - border) <= 2 for border in (256, 512))
+            if index % 7 and not near_border:
+                continue
+            row = logits[position]
+            assert row[generated[index]] >= row.max() - SLACK["bfloat16"], (request_id, index)
+
+
 def test_stop_reasons_and_cached_token_count(folders, plain_models):
     plain = plain_models("A", "float32")
     engine = Engine.from_pretrained(folders("A", "float32"), dtype="float32", page_size=8,

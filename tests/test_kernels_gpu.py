@@ -692,6 +692,41 @@ def test_tensor_core_attention_sees_one_far_key(key_position, tensor_memory):
     assert_close(out[-1:], wanted, "dominant key's value", atol=2e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("context", [1024, 2048, 4096])
+def test_decode_attention_at_long_contexts(context):
+    """Decode tokens over contexts of thousands of keys (the contexts the benchmark and the
+    configuration allow), one far key scaled to win, in both precisions: the streaming kernel
+    in bfloat16, the CUDA-core kernel with dozens of key splits in float32."""
+    for dtype, heads, head_dim in ((torch.bfloat16, 3, 128), (torch.float32, 2, 64)):
+        rng = np.random.default_rng(context)
+        contexts = [context - 1, context // 2 + 3, 17]
+        far = {0: context // 3 + 1}
+        out, expected, values, *_ = attention_case(rng, dtype, heads, heads, head_dim, 16, contexts,
+                                                   [1, 1, 1], window=None, split_keys=128,
+                                                   dominant=far)
+        tol = dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=8e-3)
+        assert_close(out, expected, f"attention {dtype}", **tol)
+        assert_close(out[:1], values[0][:, far[0]].reshape(1, -1), "far key's value",
+                     atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("tensor_memory", [False, True])
+@pytest.mark.parametrize("context,new", [(0, 1024), (1024, 1024), (3000, 1096)])
+def test_prompt_attention_at_long_contexts(context, new, tensor_memory):
+    """Prompt portions whose last rows see 1,024, 2,048 and 4,096 keys, on the ``mma.sync``
+    kernel and on the tcgen05 kernel; the last query's far key is scaled to win."""
+    rng = np.random.default_rng(context + new)
+    heads, head_dim = 2, 128
+    far = {0: 777 if context else 5}
+    out, expected, values, *_ = attention_case(rng, torch.bfloat16, heads, heads, head_dim, 16,
+                                               [context, 40], [new, 70], window=None,
+                                               split_keys=64, dominant=far, tensor_core_min=16,
+                                               tensor_memory=tensor_memory)
+    assert_close(out, expected, "prompt attention", atol=2e-2, rtol=8e-3)
+    assert_close(out[new - 1:new], values[0][:, far[0]].reshape(1, -1), "far key's value",
+                 atol=2e-2, rtol=1e-2)
+
+
 def test_tensor_core_attention_refuses_what_it_cannot_tile():
     assert ops.prefill_attention_supports(128, 16) and ops.prefill_attention_supports(64, 64)
     assert ops.prefill_attention_supports(80, 16) and ops.prefill_attention_supports(256, 8)

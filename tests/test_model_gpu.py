@@ -7,6 +7,8 @@ NaN, so reading a page that was given back shows at once).
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import pytest
 
@@ -221,3 +223,56 @@ def test_llama_7b_layer_sizes_bfloat16_against_the_float32_path():
     top2 = np.sort(exact, axis=-1)[:, -2:]
     clear = (top2[:, 1] - top2[:, 0]) > 0.1
     assert (np.argmax(exact, axis=-1)[clear] == np.argmax(fast, axis=-1)[clear]).all()
+
+
+@pytest.fixture(scope="module")
+def llama_7b_layer(model_root):
+    """One layer of the benchmark model's sizes as a folder, a sequence, and what the plain
+    implementation makes of it in float32 and with activations rounded to bfloat16."""
+    import plain_llama
+    from helix_runtime_b200 import LlamaConfig, write_random_model
+    from tiny_configs import SCORE_SPREAD
+
+    config = LlamaConfig(vocab_size=32000, hidden_size=4096, intermediate_size=11008,
+                         num_hidden_layers=1, num_attention_heads=32, num_key_value_heads=32,
+                         head_dim=128, max_position_embeddings=512, rms_norm_eps=1e-5,
+                         rope_theta=10000.0)
+    folder = os.path.join(model_root, "llama_7b_layer")
+    gain = (SCORE_SPREAD / (0.02 * 0.02 * 4096)) ** 0.5
+    write_random_model(folder, config, 5, std=0.02, scale_std=0.1, storage_dtype="bfloat16",
+                       gains={"q_proj": gain, "k_proj": gain})
+    tokens = random_tokens(32000, 320, seed=78)
+    plain = plain_llama.PlainModel(folder, precision="float32")
+    exact = plain.logits(tokens)
+    plain.precision = "bfloat16"
+    return folder, tokens, {"float32": exact, "bfloat16": plain.logits(tokens)}
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_llama_7b_layer_sizes_against_the_plain_implementation(dtype, llama_7b_layer):
+    """One layer with the layer sizes of the benchmark model (hidden 4096, 32 heads of 128,
+    intermediate 11008, vocabulary 32000) against the plain implementation, which shares
+    nothing with the engine: split-K over depths of 4096 and 11008, the 32,000-row output head,
+    128-wide heads, tiled weights.  A prompt in two portions, then twenty tokens one by one.
+    The bfloat16 bound is measured, as for the other shapes: 0.8 of what rounding the
+    activations to bfloat16 does to this model's logits in the plain implementation."""
+    from engine_harness import BF16_TOL, F32_TOL, Harness
+
+    folder, tokens, logits = llama_7b_layer
+    expected = logits[dtype]
+    if dtype == "float32":
+        bounds = F32_TOL
+    else:
+        moved = float(np.abs(logits["float32"] - expected).max())
+        assert 1e-3 < moved < 0.5, moved
+        bounds = dict(atol=0.8 * moved, rtol=BF16_TOL["rtol"])
+    harness = Harness(folder, dtype, 16, num_pages=24, max_requests=1, max_tokens=256)
+    out = harness.run([("r", tokens[:180], [0, 100, 179])])
+    assert_close(out, expected[[0, 100, 179]], f"first portion {dtype}", **bounds)
+    out = harness.run([("r", tokens[180:300], [0, 119])])
+    assert_close(out, expected[[180, 299]], f"second portion {dtype}", **bounds)
+    for position in range(300, 320):
+        out = harness.run([("r", [tokens[position]], [0])])
+        assert_close(out, expected[[position]], f"decoded token at {position} {dtype}", **bounds)
+    harness.end("r")
+    harness.cache.check()
