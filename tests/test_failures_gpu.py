@@ -128,11 +128,11 @@ def test_scheduler_and_cache_must_agree_on_where_a_request_stands(folders):
                                     cuda_graphs=False)
     request_id = engine.submit(random_tokens(256, 11, seed=2), 8)
     engine.run_iteration()
-    engine.scheduler.request(request_id).processed += 1          # a fault made by hand
+    engine.scheduler.request(request_id).processed -= 1          # a fault made by hand
     engine.run_iteration()
     request = engine.request(request_id)
     assert request.state is RequestState.FAILED
-    assert "the scheduler feeds tokens from 12, the cache stands at 11" in request.error
+    assert "the scheduler feeds tokens from 10, the cache stands at 11" in request.error
     assert all_pages_free(engine)
 
 

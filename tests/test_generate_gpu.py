@@ -130,8 +130,9 @@ def test_decode_steps_with_dozens_of_live_requests(name, dtype, live, folders, p
 
 def test_a_context_that_crosses_two_graph_buckets(folders, plain_models):
     """Decode graphs are recorded for contexts rounded up to 256, 512, ...: a request that
-    decodes from position 240 to 530 crosses two of those borders while two shorter requests
-    decode beside it; every token is checked."""
+    decodes from position 240 to the model's last position, 511, leaves the first bucket for
+    the second while two shorter requests decode beside it, so two graphs are recorded and
+    replayed; tokens around the border and every seventh token elsewhere are checked."""
     plain = plain_models("C", "bfloat16")
     prompts = [random_tokens(512, n, seed=50 + n) for n in (240, 9, 130)]
     engine = Engine.from_pretrained(folders("C", "bfloat16"), dtype="bfloat16", page_size=16,
@@ -139,7 +140,7 @@ def test_a_context_that_crosses_two_graph_buckets(folders, plain_models):
     ids = [engine.submit(prompts[0], 272), engine.submit(prompts[1], 272),
            engine.submit(prompts[2], 272)]
     engine.run_until_done()
-    assert engine.graphs.captures >= 3 and engine.graphs.replays > 200
+    assert engine.graphs.captures >= 2 and engine.graphs.replays > 200
     for request_id, prompt in zip(ids, prompts):
         generated = engine.request(request_id).generated
         assert len(generated) == 272
@@ -148,7 +149,7 @@ def test_a_context_that_crosses_two_graph_buckets(folders, plain_models):
         logits = plain.logits(full[:-1])
         for index in range(len(generated)):
             position = len(prompt) + index - 1
-            near_border = any(abs(position + 1 - border) <= 2 for border in (256, 512))
+            near_border = abs(position + 1 - 256) <= 3 or position >= 508
             if index % 7 and not near_border:
                 continue
             row = logits[position]

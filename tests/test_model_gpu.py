@@ -261,7 +261,12 @@ def test_llama_7b_layer_sizes_against_the_plain_implementation(dtype, llama_7b_l
     folder, tokens, logits = llama_7b_layer
     expected = logits[dtype]
     if dtype == "float32":
-        bounds = F32_TOL
+        # the tiny models' bound (2e-5 + 1e-4 |x|) is 1e-4 of their logits' spread of 0.2 plus
+        # 1e-4 of the value; the same rule for this model, whose logits spread over 1.3 and
+        # whose float32 sums have 4,096 to 11,008 terms
+        spread = float(expected.std())
+        assert 0.5 < spread < 3.0, spread
+        bounds = dict(atol=F32_TOL["atol"] * spread / 0.2, rtol=F32_TOL["rtol"])
     else:
         moved = float(np.abs(logits["float32"] - expected).max())
         assert 1e-3 < moved < 0.5, moved
