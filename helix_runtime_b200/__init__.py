@@ -9,6 +9,7 @@ model folder (``config.json`` + safetensors) to generated tokens:
 >>> engine.generate([[1, 42, 17]], max_new_tokens=8)[0].generated_tokens
 """
 from . import models  # noqa: F401  (registers the architecture and the parts)
+from .models import register_arrangement
 from .config import (ConfigError, LlamaConfig, ModelSpec, PartSpec, load_config,
                      register_architecture)
 from .engine import (Engine, EngineConfig, GenerationResult, StepEntry, StepError, StepFunction,
@@ -21,6 +22,7 @@ __version__ = "0.1.0"
 __all__ = [
     "ConfigError", "Engine", "EngineConfig", "GenerationResult", "LlamaConfig", "ModelSpec",
     "PartSpec", "StepEntry", "StepError", "StepFunction", "WeightError", "load_config",
-    "load_model", "random_model", "register_architecture", "register_part",
+    "load_model", "random_model", "register_architecture", "register_arrangement",
+    "register_part",
     "write_random_model",
 ]

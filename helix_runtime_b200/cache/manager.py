@@ -178,6 +178,18 @@ class CacheManager:
     def pages_for(self, tokens: int) -> int:
         return -(-tokens // self.page_size)
 
+    def pages_needed_alone(self, rows: int) -> List[int]:
+        """Pages of each group that a request of ``rows`` cache rows must be able to hold at
+        once to run to its end alone, fed in portions as small as the pool demands.  A group
+        that keeps every key needs all its pages; a windowed group gives pages back as its
+        window passes them and never holds more than the window and the page being filled."""
+        needed = []
+        for group in self.groups:
+            window = group.need.window
+            live = rows if window is None else min(rows, window + self.page_size)
+            needed.append(self.pages_for(live))
+        return needed
+
     def pages_to_extend(self, request: Hashable, new_length: int) -> List[int]:
         """Pages each group must add so that positions ``[0, new_length)`` have a place."""
         record = self._requests[request]

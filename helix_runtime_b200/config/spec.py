@@ -35,17 +35,19 @@ class PartSpec:
 
 @dataclasses.dataclass(frozen=True)
 class BlockSpec:
-    """One decoder layer: a mixer and a feed-forward, each behind its own norm.
+    """One decoder layer: a mixer and (usually) a feed-forward, each behind its own norm.
 
-    ``arrangement`` names how the four parts are wired; ``pre_norm`` is
-    ``x += mixer(norm(x)); x += ff(norm(x))`` (src/model/cpu_llama.cpp:62-98).
+    ``arrangement`` names how the parts are wired, a key of the arrangement registry
+    (``models.decoder.register_arrangement``); ``pre_norm`` is
+    ``x += mixer(norm(x)); x += ff(norm(x))`` (src/model/cpu_llama.cpp:62-98).  A block whose
+    arrangement has no feed-forward, or no second norm, leaves those fields ``None``.
     """
 
     arrangement: str
     mixer_norm: PartSpec
     mixer: PartSpec
-    feed_forward_norm: PartSpec
-    feed_forward: PartSpec
+    feed_forward_norm: Optional[PartSpec] = None
+    feed_forward: Optional[PartSpec] = None
 
 
 @dataclasses.dataclass(frozen=True)

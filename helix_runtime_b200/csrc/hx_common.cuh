@@ -35,6 +35,8 @@ enum HxDeviceFlag : int {
 void hx_set_error(const char* format, ...);
 // Every entry point counts the kernels it launches (read with hx_launch_count()).
 void hx_count_launches(int kernels);
+// Streaming multiprocessors of the current device (0 and a message when it cannot be asked).
+int hx_device_sm_count();
 
 #define HX_REQUIRE(cond, ...)            \
   do {                                   \

@@ -37,7 +37,32 @@ void hx_count_launches(int kernels) { g_hx_launches.fetch_add(kernels, std::memo
 // counts once, when it is captured).
 HX_API long long hx_launch_count() { return g_hx_launches.load(std::memory_order_relaxed); }
 
-HX_API int hx_abi_version() { return 6; }
+HX_API int hx_abi_version() { return 7; }
+
+// Streaming multiprocessors of the current device (asked once per device); 0 with a message
+// when the device cannot be asked.  Launch sizes that should fill the GPU come from here.
+int hx_device_sm_count() {
+  static std::atomic<int> counts[64];
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+    cudaGetLastError();
+    hx_set_error("hx_sm_count: no current CUDA device");
+    return 0;
+  }
+  int count = counts[device].load(std::memory_order_relaxed);
+  if (count == 0) {
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        count <= 0) {
+      cudaGetLastError();
+      hx_set_error("hx_sm_count: the device does not report its multiprocessor count");
+      return 0;
+    }
+    counts[device].store(count, std::memory_order_relaxed);
+  }
+  return count;
+}
+
+HX_API int hx_sm_count() { return hx_device_sm_count(); }
 
 // ------------------------------------------------------------------- embedding
 
@@ -224,7 +249,8 @@ HX_API int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int i
   if (tokens == 0) return HX_OK;
   const size_t total = static_cast<size_t>(tokens) * intermediate;
   const int threads = 256;
-  const int blocks = static_cast<int>(total / threads + 1 < 148 * 16 ? total / threads + 1 : 148 * 16);
+  const size_t resident = static_cast<size_t>(hx_device_sm_count() > 0 ? hx_device_sm_count() : 1) * 16;
+  const int blocks = static_cast<int>(total / threads + 1 < resident ? total / threads + 1 : resident);
   if (out_dtype == HX_F32) {
     hx_launch(swiglu_kernel<float>, blocks, threads, 0, stream, gate_up, static_cast<float*>(act), tokens, intermediate, ld_in, zero_input);
   } else if (out_dtype == HX_BF16) {

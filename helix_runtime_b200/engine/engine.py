@@ -250,8 +250,7 @@ class Engine:
             raise ValueError("max_new_tokens must not be negative")
         # the last generated token is never fed back, so it needs no cache row
         rows = min(len(prompt) + max(max_new_tokens - 1, 0), self.model.max_positions)
-        pages = -(-rows // self.config.page_size)
-        for group in self.cache.groups:
+        for group, pages in zip(self.cache.groups, self.cache.pages_needed_alone(rows)):
             if pages > group.pool.num_pages:
                 raise ValueError(f"the request needs {pages} cache pages, the pool has "
                                  f"{group.pool.num_pages}; it could never run")

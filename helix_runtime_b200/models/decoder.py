@@ -6,7 +6,7 @@ schedule entry and returns float32 logits at the wanted rows.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Mapping, Optional, Sequence
+from typing import Callable, Dict, List, Mapping, Optional, Sequence
 
 import torch
 
@@ -16,28 +16,62 @@ from ..parts.base import (FeedForward, LayerCache, Mixer, Norm, StepContext, bui
 from ..weights.loader import TensorRequest
 
 
+# ----------------------------------------------------------------- arrangements
+#
+# An arrangement wires the parts of a block: ``run(block, ctx, cache, residual, normed)`` reads
+# and updates the float32 residual stream ``residual[:n]`` through the block's parts, with
+# ``normed`` as scratch for a norm's output (compute dtype, same rows).  Mixers and
+# feed-forwards ADD their output into the residual they are handed.
+
+Arrangement = Callable[["Block", StepContext, LayerCache, torch.Tensor, torch.Tensor], None]
+_ARRANGEMENTS: Dict[str, Arrangement] = {}
+
+
+def register_arrangement(name: str, run: Arrangement) -> None:
+    """Make ``name`` usable as ``BlockSpec.arrangement``."""
+    _ARRANGEMENTS[name] = run
+
+
+def _pre_norm(block: "Block", ctx: StepContext, cache: LayerCache, residual: torch.Tensor,
+              normed: torch.Tensor) -> None:
+    # x += mixer(norm(x)); x += ff(norm(x))   (src/model/cpu_llama.cpp:62-98)
+    block.mixer_norm.forward(ctx, residual, normed)
+    block.mixer.forward(ctx, cache, normed, residual)
+    if block.feed_forward is not None:
+        block.feed_forward_norm.forward(ctx, residual, normed)
+        block.feed_forward.forward(ctx, normed, residual)
+
+
+register_arrangement("pre_norm", _pre_norm)
+
+
 class Block:
-    """One decoder layer: norm, mixer, norm, feed-forward, wired by ``arrangement``."""
+    """One decoder layer: its parts, and the arrangement that runs them."""
 
     def __init__(self, spec: BlockSpec, hidden_size: int) -> None:
-        if spec.arrangement != "pre_norm":
-            raise ValueError(f"unknown block arrangement {spec.arrangement!r}; known: pre_norm")
+        run = _ARRANGEMENTS.get(spec.arrangement)
+        if run is None:
+            raise ValueError(f"unknown block arrangement {spec.arrangement!r}; known: "
+                             + ", ".join(sorted(_ARRANGEMENTS)))
+        if (spec.feed_forward is None) != (spec.feed_forward_norm is None) \
+                and spec.arrangement == "pre_norm":
+            raise ValueError("a pre_norm block has a feed-forward with its norm, or neither")
         self.arrangement = spec.arrangement
+        self._run = run
         self.mixer_norm: Norm = build_part("norm", spec.mixer_norm, hidden_size)
         self.mixer: Mixer = build_part("mixer", spec.mixer, hidden_size)
-        self.feed_forward_norm: Norm = build_part("norm", spec.feed_forward_norm, hidden_size)
-        self.feed_forward: FeedForward = build_part("feed_forward", spec.feed_forward, hidden_size)
+        self.feed_forward_norm: Optional[Norm] = None if spec.feed_forward_norm is None else \
+            build_part("norm", spec.feed_forward_norm, hidden_size)
+        self.feed_forward: Optional[FeedForward] = None if spec.feed_forward is None else \
+            build_part("feed_forward", spec.feed_forward, hidden_size)
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        return tuple(part for part in (self.mixer_norm, self.mixer, self.feed_forward_norm,
+                                       self.feed_forward) if part is not None)
 
     def forward(self, ctx: StepContext, cache: LayerCache, residual: torch.Tensor,
                 normed: torch.Tensor) -> None:
-        # x += mixer(norm(x)); x += ff(norm(x))   (src/model/cpu_llama.cpp:62-98)
-        self.mixer_norm.forward(ctx, residual, normed)
-        self.mixer.forward(ctx, cache, normed, residual)
-        self.feed_forward_norm.forward(ctx, residual, normed)
-        self.feed_forward.forward(ctx, normed, residual)
+        self._run(self, ctx, cache, residual, normed)
 
 
 class DecoderModel:

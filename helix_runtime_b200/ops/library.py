@@ -45,6 +45,8 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_last_error.restype = ctypes.c_char_p
     library.hx_last_error.argtypes = []
     library.hx_abi_version.restype = _c_int
+    library.hx_sm_count.restype = _c_int
+    library.hx_sm_count.argtypes = []
     library.hx_embed.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
     library.hx_rmsnorm.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_float, _c_ptr]
     library.hx_swiglu.argtypes = [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
@@ -113,6 +115,20 @@ def lib() -> ctypes.CDLL:
                 _declare(library)
                 _library = library
     return _library
+
+
+_sm_counts = {}
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current CUDA device, asked of the device once."""
+    device = torch.cuda.current_device()
+    if device not in _sm_counts:
+        count = int(lib().hx_sm_count())
+        if count <= 0:
+            raise KernelError(lib().hx_last_error().decode("utf-8", "replace"))
+        _sm_counts[device] = count
+    return _sm_counts[device]
 
 
 def library_file() -> str:

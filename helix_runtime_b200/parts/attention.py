@@ -142,7 +142,7 @@ class PagedAttention(Mixer):
         (decoding) gets narrower splits so that about sixteen warps per SM stream the cache,
         a step with many tokens keeps ``limit``.  Splits are multiples of the 32-key chunk,
         so the choice changes the order of float32 sums only."""
-        wanted_warps = 148 * 16
+        wanted_warps = ops.sm_count() * 16
         splits = max(1, wanted_warps // max(1, tokens * self.heads))
         keys = -(-longest // splits)
         keys = max(32, -(-keys // 32) * 32)

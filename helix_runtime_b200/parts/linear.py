@@ -5,8 +5,8 @@ float32) to the CUDA-core kernel; the choice depends on the shape and the dtype 
 on a setting.
 
 Weight streaming.  With few tokens (decoding) a product is a pure stream of its weight
-matrix, and a matrix has too few 128-row tiles to keep all 148 SMs loading: 96 tiles for the
-fused QKV matrix of a 4096-wide model, 32 for the output projection.  Such products are cut
+matrix, and a matrix has too few 128-row tiles to keep every SM loading: 96 tiles for the
+fused QKV matrix of a 4096-wide model, 32 for the output projection, on a GPU of 148 SMs.  Such products are cut
 along the reduction as well (split-K) into a few hundred work units that sum into a float32
 accumulator with atomic adds.  The residual stream is such an accumulator already; for the
 products whose result is stored in bfloat16 (QKV, gate/up) the accumulator is a small
@@ -21,9 +21,8 @@ import torch
 
 from ..ops import library as ops
 
-SM_COUNT = 148
 STREAMING_MAX_TOKENS = 64      # at most this many tokens: the product is a weight stream
-WORK_UNITS = 4 * SM_COUNT      # units a weight stream is cut into (two CTAs share an SM)
+UNITS_PER_SM = 4               # units a weight stream is cut into, per SM (two CTAs share one)
 MIN_K_BLOCKS = 8               # 64-wide reduction blocks per unit, at least
 
 
@@ -89,7 +88,7 @@ def split_k_for(tokens: int, features: int, depth: int) -> int:
         return 1
     tiles = -(-features // 128)
     k_blocks = -(-depth // 64)
-    splits = max(1, round(WORK_UNITS / tiles))
+    splits = max(1, round(UNITS_PER_SM * ops.sm_count() / tiles))
     return max(1, min(splits, k_blocks // MIN_K_BLOCKS))
 
 

@@ -53,6 +53,7 @@ extern "C" {
 
 /* ---- library ---------------------------------------------------------------------------- */
 int hx_abi_version(void);
+int hx_sm_count(void);                     /* multiprocessors of the current device, 0 on error */
 const char* hx_last_error(void);          /* message of this thread's last failed call */
 long long hx_launch_count(void);          /* kernels launched by this library so far */
 void hx_set_dependent_launch(int enabled); /* programmatic dependent launch between kernels */

@@ -52,13 +52,27 @@ class DecayedSum(Mixer):
         self.weight = tensors[self.name].to(device=device, dtype=torch.float32)
 
     def forward(self, ctx, cache, x, residual) -> None:
-        for index in range(ctx.n_requests):
-            slot = ctx.host_request_slots[index]
-            begin, end = ctx.host_request_starts[index], ctx.host_request_starts[index + 1]
-            state = cache.state[slot]
-            for token in range(begin, end):
-                state.mul_(self.decay).add_(x[token].float())
-                residual[token] += self.weight * state
+        """Everything is computed from the step's DEVICE arrays with shapes that depend on
+        the number of tokens and requests only, and nothing is read back to the host, so the
+        same calls can be recorded into a CUDA graph and replayed while positions, slots and
+        tokens change underneath.  s_j = decay^(i+1) * s_before + sum_{k<=i} decay^(i-k) x_k
+        for the i-th token of a request in this step, as one masked matrix product."""
+        n, requests = ctx.n_tokens, ctx.n_requests
+        owner = ctx.token_request[:n].long()                       # request index per token
+        start = ctx.request_start[:requests + 1].long()
+        slot = ctx.request_slot[:requests].long()
+        index = torch.arange(n, device=x.device)
+        local = index - start[owner]                               # place within the request
+        same = owner[:, None] == owner[None, :]
+        earlier = index[None, :] <= index[:, None]
+        power = (index[:, None] - index[None, :]).clamp(min=0).float()
+        weights = torch.where(same & earlier, self.decay ** power, torch.zeros_like(power))
+        before = cache.state.index_select(0, slot)                 # [requests, hidden]
+        carried = (self.decay ** (local + 1).float())[:, None] * before.index_select(0, owner)
+        states = weights @ x[:n].float() + carried
+        residual[:n] += self.weight * states
+        last = start[1:] - 1                                       # last token of each request
+        cache.state.index_copy_(0, slot, states.index_select(0, last))
 
 
 @dataclasses.dataclass(frozen=True)
@@ -187,3 +201,33 @@ def test_toy_architecture_with_state_steps_like_its_plain_form(tmp_path):
     harness.end("a")
     harness.end("b")
     harness.cache.check()
+
+
+@pytest.mark.parametrize("cuda_graphs", [False, True])
+def test_state_of_a_mixer_survives_graph_replay(tmp_path, cuda_graphs):
+    """The toy model through the engine itself: admission, prompt portions, then decode steps
+    that are recorded into CUDA graphs and queued ahead of one another.  The mixer's state is
+    read and written through the device arrays of the step, so the recorded launches serve
+    every later step; the tokens equal the plain form's."""
+    from helix_runtime_b200 import Engine
+    from helix_runtime_b200.weights import Checkpoint
+    folder = str(tmp_path / "toy")
+    write_random_model(folder, ToyConfig(), seed=3, std=0.08, scale_std=0.2,
+                       storage_dtype="float32")
+    checkpoint = Checkpoint(folder)
+    tensors = {name: checkpoint.read(name) for name in checkpoint.names()}
+    engine = Engine.from_pretrained(folder, dtype="float32", page_size=4, max_running_requests=3,
+                                    max_tokens_per_iteration=16, max_prefill_chunk=7,
+                                    cuda_graphs=cuda_graphs)
+    prompts = [random_tokens(VOCAB, n, seed=20 + n) for n in (13, 3, 22, 6)]
+    results = engine.generate(prompts, max_new_tokens=30)
+    if cuda_graphs:
+        assert engine.graphs.captures > 0 and engine.graphs.replays > 20
+        assert engine.steps_queued_ahead > 0
+    for prompt, result in zip(prompts, results):
+        assert len(result.generated_tokens) == 30
+        logits = plain_toy(tensors, prompt + result.generated_tokens[:-1])
+        for index, token in enumerate(result.generated_tokens):
+            row = logits[len(prompt) + index - 1]
+            assert row[token] >= row.max() - 1e-4, f"token {index}"
+    engine.cache.check()
