@@ -3,15 +3,25 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
 
-Prints ONE JSON line.  ``value`` is decoded tokens per second at the default batch of 8
-(512-token prompts, decoding from there), timed on the device with CUDA events around K
-replays of the captured decode step (forward, sampling and feeding the sampled token back,
-all on the device).  ``e2e`` is the same quantity through the Python entry point
-(``Engine.submit`` / ``Engine.run_iteration``): every step copies that step's inputs from
-pinned host memory to the device and reads the sampled tokens back.  ``prefill`` is one
-2,048-token prompt in one step.  ``roofline`` relates the decode step to the HBM bandwidth:
-the bytes it has to read (every weight once, the cache of the live requests) over its time.
-``points`` holds decoding at batch 1 and 64.
+Prints ONE JSON line.  A step is one decode step of the batch.  Every decode number is taken
+on the path generation uses: ``Engine.submit`` and ``Engine.run_iteration`` (the scheduler,
+the step function, CUDA graphs of the decode step, the next step queued on the device before
+this one's tokens are read); there is no second decode driver.
+
+* ``value``: decoded tokens per second at the default batch of 8, timed ON THE DEVICE with
+  CUDA events around K iterations.  The loop of K steps is repeated with fresh requests until
+  at least a second has been timed; ``ms_per_step`` is the median of the repeats, with the
+  fastest and slowest beside it.
+* ``e2e``: the same loop timed by the host's clock around the public calls, with a device
+  synchronisation on both sides: every step copies its inputs from pinned host memory to the
+  device and reads the sampled tokens back.
+* The workload is the reference's: 512-token prompts, 256 generated tokens, so contexts from
+  512 to 767, 640 on average.  K steps cannot cover that range for every K, so each repeat is
+  placed in its middle: its requests bring prompts of ``640 - W - K/2`` tokens, and the timed
+  steps run at contexts around 640 (``config.timed_prompt_len``, ``config.timed_context_mean``).
+* ``prefill``: one 2,048-token prompt in one step.  ``roofline``: the bytes the decode step
+  has to read (every weight once, the cache of the live requests) over its time, against the
+  measured copy bandwidth.  ``points``: decoding at batch 1 and 64, with their fractions.
 
 Weights are random, N(0, 0.02) from a fixed seed, made on the device; prompts are seeded
 uniform token ids.  Every step streams more weight bytes than the L2 cache holds, so no L2
@@ -54,7 +64,9 @@ WORKLOADS = {
     "openllama-3b": dict(prompt_range=(64, 1024), new_tokens=128, chunk=512, shared_prefix=256),
     "llama-2-13b": dict(prompt_range=(128, 2048), new_tokens=256, chunk=512, shared_prefix=0),
 }
-PROMPT_LEN = 512
+PROMPT_LEN = 512             # the workload: prompts of 512 tokens, 256 generated
+GENERATED = 256
+MIN_TIMED_SECONDS = 1.0
 PAGE_SIZE = 16
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -90,7 +102,7 @@ class ClockSampler:
             self.handle = open(self.path, "w")
             self.process = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=self.handle, stderr=subprocess.DEVNULL)
+                 "-lms", "50"], stdout=self.handle, stderr=subprocess.DEVNULL)
         except OSError:
             self.process = None
 
@@ -353,7 +365,6 @@ def main() -> int:
 
     from helix_runtime_b200 import Engine, EngineConfig, LlamaConfig, random_model
     from helix_runtime_b200.cache.manager import CacheManager
-    from helix_runtime_b200.engine.graphs import DecodeGraphs
     from helix_runtime_b200.engine.step import StepEntry, StepFunction
     from helix_runtime_b200.ops import library as ops
     from helix_runtime_b200.sampling import Sampler
@@ -392,38 +403,81 @@ def main() -> int:
         torch.cuda.synchronize()
         return start.elapsed_time(stop)
 
-    def decode_device_loop(batch: int, n_steps: int, n_warmup: int):
-        """Device-timed decoding: returns (tokens/s, ms/step, kernels/step, mean context)."""
-        final = PROMPT_LEN + n_warmup + n_steps + 2
-        cache, step, sampler = fresh(batch, final, max(PREFILL_TOKENS, batch))
-        prompts = [[int(t) for t in rng.integers(0, config.vocab_size, PROMPT_LEN)]
-                   for _ in range(batch)]
-        first = []
-        per_step = max(1, PREFILL_TOKENS // PROMPT_LEN)
-        for begin in range(0, batch, per_step):
-            entries = []
-            for index in range(begin, min(begin + per_step, batch)):
-                cache.admit(index)
-                entries.append(StepEntry(index, prompts[index], [PROMPT_LEN - 1]))
-            logits = step.run(entries)
-            tokens = sampler.launch(logits, True, step.status)
-            first.extend(sampler.to_host(tokens))
-        # the decode step, replayed on the device: pages for every future position are reserved
-        entries = [StepEntry(index, [first[index]], [0]) for index in range(batch)]
-        ctx, want_rows, n_want, _ = step.prepare(entries, context_hint=final)
-        for index in range(batch):
-            cache.extend(index, final)
-        cache.sync_tables()
-        graphs = DecodeGraphs(step, sampler)
-        graphs.run(ctx, want_rows, n_want, True, advance=True)          # eager, sizes workspaces
-        graph = graphs.capture_only(ctx, want_rows, n_want, True, advance=True)
-        kernels = graphs.kernels_per_graph[graphs.key_for(ctx, n_want, True) + (True,)]
-        for _ in range(n_warmup - 1):
-            graph.replay()
-        elapsed = timed(graph.replay, n_steps)
-        step.raise_on_status()
-        mean_context = PROMPT_LEN + n_warmup + (n_steps + 1) / 2.0
-        return batch * n_steps / (elapsed / 1e3), elapsed / n_steps, kernels, mean_context
+    mean_context = PROMPT_LEN + GENERATED // 2
+
+    def decode_through_engine(batch: int, n_steps: int, n_warmup: int, clock: str):
+        """Decoding through the engine's own calls.  Each repeat: ``batch`` fresh requests whose
+        prompts place the timed steps around the workload's mean context, their prompts and
+        ``n_warmup`` decode steps untimed, then ``n_steps`` iterations timed with CUDA events
+        (``clock="device"``) or with the host's clock between two synchronisations
+        (``"host"``).  Repeats go on until a second has been timed.  Returns the per-step
+        milliseconds of every repeat and what the engine says about its graphs."""
+        # prompts are fed a few per iteration while the requests that came first already
+        # decode: those are ahead by up to `feeding` tokens when the timed steps begin
+        feeding = -(-batch * mean_context // PREFILL_TOKENS)
+        prompt_len = max(16, mean_context - n_warmup - n_steps // 2 - feeding // 2)
+        new_tokens = n_warmup + n_steps + feeding + 8
+        rows = prompt_len + new_tokens
+        engine = Engine(model, EngineConfig(
+            page_size=PAGE_SIZE, max_running_requests=batch,
+            max_tokens_per_iteration=PREFILL_TOKENS,
+            num_pages=batch * -(-rows // PAGE_SIZE) + 8))
+        per_step, contexts = [], []
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        while len(per_step) < 3 or sum(per_step) * n_steps < MIN_TIMED_SECONDS * 1e3:
+            ids = [engine.submit([int(t) for t in rng.integers(0, config.vocab_size, prompt_len)],
+                                 max_new_tokens=new_tokens) for _ in range(batch)]
+            while any(engine.request(r).state.value != "decoding" for r in ids):
+                engine.run_iteration()
+            for _ in range(n_warmup):
+                engine.run_iteration()
+            torch.cuda.synchronize()
+            sampled = 0
+            contexts.append(sum(engine.cache.reserved(r) for r in ids) / batch + (n_steps + 1) / 2.0)
+            if clock == "device":
+                start.record()
+                for _ in range(n_steps):
+                    sampled += engine.run_iteration().sampled
+                stop.record()
+                torch.cuda.synchronize()
+                elapsed_ms = start.elapsed_time(stop)
+            else:
+                begin = time.perf_counter()
+                for _ in range(n_steps):
+                    sampled += engine.run_iteration().sampled
+                torch.cuda.synchronize()
+                elapsed_ms = (time.perf_counter() - begin) * 1e3
+            if sampled != batch * n_steps:
+                raise RuntimeError(f"{sampled} tokens decoded in {n_steps} steps of batch {batch}")
+            per_step.append(elapsed_ms / n_steps)
+            for request_id in ids:
+                engine.cancel(request_id)
+            engine.run_until_done()              # the step that was queued ahead
+            if len(per_step) >= 64:
+                break
+        kernels = max(engine.graphs.kernels_per_graph.values(), default=0)
+        facts = {"prompt_len": prompt_len, "kernels_per_step": kernels,
+                 "context_mean": sum(contexts) / len(contexts),
+                 "graph_replays": engine.graphs.replays, "upload_bytes": engine.step_function.upload_bytes,
+                 "steps_queued_ahead": engine.steps_queued_ahead}
+        del engine
+        torch.cuda.empty_cache()
+        return per_step, facts
+
+    weight_bytes = model.weight_bytes_per_step()
+    kv_bytes_per_token = sum(2 * need.kv_heads * need.head_dim * 2
+                             for need in model.cache_needs()[0].values())
+
+    def hbm_fraction(batch: int, ms: float, context: float):
+        """(bytes a decode step of this batch has to read, GB/s achieved, fraction of peak)"""
+        step_bytes = weight_bytes + batch * context * kv_bytes_per_token
+        achieved = step_bytes / (ms / 1e3) / 1e9
+        return step_bytes, achieved, achieved / peaks["hbm_gbs"]
+
+    def median(values):
+        ordered = sorted(values)
+        middle = len(ordered) // 2
+        return ordered[middle] if len(ordered) % 2 else 0.5 * (ordered[middle - 1] + ordered[middle])
 
     if options.profile is not None:
         return profile_region(options, model, config, fresh, rng)
@@ -454,71 +508,63 @@ def main() -> int:
     h, i, layers, t = config.hidden_size, config.intermediate_size, options.layers, PREFILL_TOKENS
     prefill_flops = 2.0 * t * layers * (4 * h * h + 3 * h * i) + 2.0 * h * config.vocab_size \
         + 2.0 * layers * t * (t + 1) * h
+    prefill_rate = prefill_flops / (prefill_ms / 1e3) / 1e12
     prefill = {"value": round(t / (prefill_ms / 1e3), 1), "tokens": t, "ms": round(prefill_ms, 3),
-               "frac": round(prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+               "frac": round(prefill_rate / peaks["bf16_tflops"], 4),
+               "frac_sustained": round(prefill_rate / peaks["bf16_tflops_sustained"], 4),
+               "tflops": round(prefill_rate, 1)}
     del cache, step, sampler
+    torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ decode, batch B
-    value, ms_per_step, kernels_per_step, mean_context = decode_device_loop(
-        options.batch, steps, warmup)
+    repeats_ms, facts = decode_through_engine(options.batch, steps, warmup, "device")
     clocks = sampler_clock.stop()
-    weight_bytes = model.weight_bytes_per_step()
-    kv_bytes_per_token = sum(2 * need.kv_heads * need.head_dim * 2
-                             for need in model.cache_needs()[0].values())
-    step_bytes = weight_bytes + options.batch * mean_context * kv_bytes_per_token
-    achieved_gbs = step_bytes / (ms_per_step / 1e3) / 1e9
+    ms_per_step = median(repeats_ms)
+    value = options.batch / (ms_per_step / 1e3)
+    step_bytes, achieved_gbs, fraction = hbm_fraction(options.batch, ms_per_step, facts["context_mean"])
     roofline = {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peaks["hbm_gbs"],
-                "unit": "GB/s", "frac": round(achieved_gbs / peaks["hbm_gbs"], 4),
-                "peak_source": peaks["source"]}
+                "unit": "GB/s", "frac": round(fraction, 4), "peak_source": peaks["source"]}
 
     # ------------------------------------------------------------------ end to end
-    engine = Engine(model, EngineConfig(page_size=PAGE_SIZE, max_running_requests=options.batch,
-                                        max_tokens_per_iteration=PREFILL_TOKENS,
-                                        num_pages=options.batch * -(-(PROMPT_LEN + warmup + steps + 8)
-                                                                    // PAGE_SIZE) + 8))
-    for _ in range(options.batch):
-        engine.submit([int(t) for t in rng.integers(0, config.vocab_size, PROMPT_LEN)],
-                      max_new_tokens=warmup + steps + 4)
-    while any(engine.request(r).state.value != "decoding" for r in range(options.batch)):
-        engine.run_iteration()
-    for _ in range(warmup):
-        engine.run_iteration()
-    torch.cuda.synchronize()
-    begin = time.perf_counter()
-    decoded = 0
-    for _ in range(steps):
-        decoded += engine.run_iteration().sampled
-    torch.cuda.synchronize()
-    e2e_seconds = time.perf_counter() - begin
-    h2d = engine.step_function.upload_bytes
-    e2e = {"value": round(decoded / e2e_seconds, 1), "unit": "tokens/s",
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": options.batch * 4 + 4,
-           "ms_per_step": round(e2e_seconds / steps * 1e3, 4),
-           "graph_replays": engine.graphs.replays if engine.graphs else 0}
-    del engine
+    host_ms, host_facts = decode_through_engine(options.batch, steps, warmup, "host")
+    e2e_ms = median(host_ms)
+    e2e = {"value": round(options.batch / (e2e_ms / 1e3), 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": host_facts["upload_bytes"],
+           "d2h_bytes_per_step": options.batch * 4 + 4,
+           "ms_per_step": round(e2e_ms, 4), "repeats": len(host_ms),
+           "graph_replays": host_facts["graph_replays"]}
 
     # ------------------------------------------------------------------ batch 1 and 64
     points = {}
     if not options.no_points:
         for batch in (1, 64):
-            tokens_per_s, _, _, _ = decode_device_loop(batch, min(steps, 96), warmup)
-            points[f"decode_b{batch}"] = round(tokens_per_s, 1)
+            point_ms, point_facts = decode_through_engine(batch, steps, warmup, "device")
+            point = median(point_ms)
+            points[f"decode_b{batch}"] = round(batch / (point / 1e3), 1)
+            points[f"decode_b{batch}_ms"] = round(point, 4)
+            points[f"decode_b{batch}_frac"] = round(
+                hbm_fraction(batch, point, point_facts["context_mean"])[2], 4)
+            points[f"decode_b{batch}_context"] = round(point_facts["context_mean"], 1)
 
+    kernels_per_step = facts["kernels_per_step"]
     line = {
         "metric": "decode tokens/s (Llama-2-7B shape, bf16, batch 8)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
-        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(ms_per_step, 4), "ms_per_step_min": round(min(repeats_ms), 4),
+        "ms_per_step_max": round(max(repeats_ms), 4), "repeats": len(repeats_ms),
+        "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random N(0,0.02) weights from seed 0, uniform random token ids",
         "config": {"model": "llama-2-7b-shape", "layers": options.layers,
                    "layers_full": SHAPE["num_hidden_layers"], "hidden": h,
                    "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
                    "head_dim": config.head_dim, "intermediate": i, "vocab": config.vocab_size,
-                   "global_batch": options.batch, "seq_len": PROMPT_LEN, "gen_len": steps,
+                   "global_batch": options.batch, "seq_len": PROMPT_LEN, "gen_len": GENERATED,
+                   "timed_prompt_len": facts["prompt_len"], "timed_context_mean": round(facts["context_mean"], 1),
                    "context": config.max_position_embeddings, "page_size": PAGE_SIZE,
                    "parallelism": "single-gpu",
                    "l2": "each step streams >126MB of weights; no flush needed"},
-        "e2e": e2e, "gpu_launches": int(kernels_per_step * steps),
+        "e2e": e2e, "gpu_launches": int(kernels_per_step * steps * len(repeats_ms)),
         "kernels_per_step": int(kernels_per_step),
         "prefill": prefill, "roofline": roofline, "points": points, "clocks": clocks,
         "step_bytes": int(step_bytes), "impl": "ours",

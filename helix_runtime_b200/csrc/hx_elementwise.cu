@@ -592,28 +592,7 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
   return HX_OK;
 }
 
-// ------------------------------------------------------- decode loop on the device
-
-// After a step that sampled one token per request: feed each sampled token back as the
-// next step's input and move every position on by one, without a round trip to the host.
-__global__ void advance_decode_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
-                                      const int* __restrict__ sampled, int count) {
-  hx_pdl_prologue();
-  const int index = blockIdx.x * blockDim.x + threadIdx.x;
-  if (index < count) {
-    token_ids[index] = sampled[index];
-    positions[index] += 1;
-  }
-}
-
-HX_API int hx_advance_decode(int* token_ids, int* positions, const int* sampled, int count,
-                             cudaStream_t stream) {
-  HX_REQUIRE(count >= 0, "hx_advance_decode: bad count");
-  if (count == 0) return HX_OK;
-  hx_launch(advance_decode_kernel, (count + 127) / 128, 128, 0, stream, token_ids, positions, sampled, count);
-  HX_CHECK_LAUNCH("hx_advance_decode");
-  return HX_OK;
-}
+// ------------------------------------------------- tokens of a step queued ahead
 
 // A step that was prepared before the host knew what the step before it sampled takes its
 // tokens from that step's output on the device: token_ids[i] = sampled[rows[i]].  A row whose

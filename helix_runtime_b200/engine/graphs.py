@@ -54,15 +54,14 @@ class DecodeGraphs:
         return (ctx.n_tokens, n_want, ctx.max_context_len, greedy)
 
     def run(self, ctx: StepContext, want_rows: torch.Tensor, n_want: int, greedy: bool,
-            advance: bool = False, feed_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+            feed_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run the step (forward, then sampling of the wanted rows) and return the device
         tensor of sampled ids.  The first time a key is seen the step runs eagerly and is
         recorded afterwards; from then on it is replayed.  ``feed_rows`` (device, one per
         token): the step's tokens are the ids the previous step sampled in these rows, put in
         place by the first kernel of the graph."""
         from ..ops import library as ops
-        key = self.key_for(ctx, n_want, greedy) + ((advance,) if advance else ()) \
-            + (("fed",) if feed_rows is not None else ())
+        key = self.key_for(ctx, n_want, greedy) + (("fed",) if feed_rows is not None else ())
         graph = self._graphs.get(key)
         if graph is not None:
             graph.replay()
@@ -74,33 +73,13 @@ class DecodeGraphs:
                 ops.feed_tokens(ctx.token_ids, self.sampler.tokens, feed_rows, ctx.n_tokens)
             logits = self.step_function.model.forward(ctx, self.step_function.cache, want_rows,
                                                       n_want)
-            tokens = self.sampler.launch(logits, greedy, ctx.status)
-            if advance:
-                ops.advance_decode(ctx.token_ids, ctx.positions, tokens, ctx.n_tokens)
-            return tokens
+            return self.sampler.launch(logits, greedy, ctx.status)
 
         tokens = body()                      # eager: gives this step's result, sizes workspaces
         self._uses[key] = self._uses.get(key, 0) + 1
-        if (len(self._graphs) < self.max_graphs and not advance
-                and self._uses[key] >= RECORD_AT_USE):
+        if len(self._graphs) < self.max_graphs and self._uses[key] >= RECORD_AT_USE:
             self._capture(key, body)
         return tokens
-
-    def capture_only(self, ctx: StepContext, want_rows: torch.Tensor, n_want: int, greedy: bool,
-                     advance: bool) -> torch.cuda.CUDAGraph:
-        """Record the step without using its result (the caller has run it eagerly before, so
-        that every workspace buffer exists)."""
-        from ..ops import library as ops
-
-        def body() -> None:
-            logits = self.step_function.model.forward(ctx, self.step_function.cache, want_rows,
-                                                      n_want)
-            tokens = self.sampler.launch(logits, greedy, ctx.status)
-            if advance:
-                ops.advance_decode(ctx.token_ids, ctx.positions, tokens, ctx.n_tokens)
-
-        key = self.key_for(ctx, n_want, greedy) + (advance,)
-        return self._capture(key, body)
 
     def _capture(self, key, body) -> torch.cuda.CUDAGraph:
         from ..ops import library as ops

@@ -92,8 +92,6 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_set_dependent_launch.restype = None
     library.hx_launch_count.restype = ctypes.c_longlong
     library.hx_launch_count.argtypes = []
-    library.hx_advance_decode.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]
-    library.hx_advance_decode.restype = _c_int
     library.hx_feed_tokens.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr]
     library.hx_feed_tokens.restype = _c_int
     library.hx_bounded_wait_check.argtypes = [_c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]
@@ -413,13 +411,6 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     rows, vocab = logits.shape
     _check(lib().hx_sample(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
                            uniform.data_ptr(), tokens_out.data_ptr(), _ptr(status), _stream()))
-
-
-def advance_decode(token_ids: torch.Tensor, positions: torch.Tensor, sampled: torch.Tensor,
-                   count: int) -> None:
-    """token_ids[:count] = sampled[:count]; positions[:count] += 1 (the device-side decode loop)."""
-    _check(lib().hx_advance_decode(token_ids.data_ptr(), positions.data_ptr(), sampled.data_ptr(),
-                                   count, _stream()))
 
 
 def feed_tokens(token_ids: torch.Tensor, sampled: torch.Tensor, rows: torch.Tensor,

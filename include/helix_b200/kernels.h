@@ -82,8 +82,6 @@ int hx_rope_append(void* qkv, int dtype, int ld, const int* positions, const int
                    const float* sin_table, int table_positions, int tokens, int heads, int kv_heads,
                    int head_dim, int rotary_dim, int pairing, int page_size, int num_pages,
                    int* status, float* accum, int ld_accum, cudaStream_t stream);
-int hx_advance_decode(int* token_ids, int* positions, const int* sampled, int count,
-                      cudaStream_t stream);
 /* token_ids[i] = max(sampled[rows[i]], 0): a step takes its tokens from the output of the
  * step before it without a round trip to the host */
 int hx_feed_tokens(int* token_ids, const int* sampled, const int* rows, int count,
