@@ -190,6 +190,53 @@ def build_host(force: bool = False) -> str:
     return target
 
 
+# ------------------------------------------------------- the engine for C and C++ callers
+#
+# include/helix_b200/engine.h over an embedded interpreter: compiled against the headers and
+# the shared library of the Python that runs this build, under a fixed name so that a C++
+# program can link it (-lhelix_b200_engine).
+
+ENGINE_API_SOURCE = os.path.join(HOST_DIR, "hx_engine_api.cpp")
+ENGINE_API_HEADER = os.path.join(os.path.dirname(os.path.dirname(CSRC)), "include", "helix_b200",
+                                 "engine.h")
+
+
+def build_engine_api(force: bool = False) -> str:
+    """Build ``libhelix_b200_engine.so`` if its sources changed and return its path."""
+    import sysconfig
+    build_dir = _writable_build_dir()
+    target = os.path.join(build_dir, "libhelix_b200_engine.so")
+    stamp = target + ".sources"
+    digest = hashlib.sha256()
+    for path in (ENGINE_API_SOURCE, ENGINE_API_HEADER):
+        with open(path, "rb") as source:
+            digest.update(source.read())
+    digest.update(sys.version.encode())
+    wanted = digest.hexdigest()
+    if os.path.exists(target) and not force:
+        try:
+            with open(stamp, "r") as source:
+                if source.read().strip() == wanted:
+                    return target
+        except OSError:
+            pass
+    include = sysconfig.get_config_var("INCLUDEPY")
+    library_dir = sysconfig.get_config_var("LIBDIR")
+    version = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+    if not include or not os.path.exists(os.path.join(include, "Python.h")):
+        raise RuntimeError("the C and C++ interface of the engine needs Python's development "
+                           f"headers (Python.h not found in {include})")
+    partial = target + f".{os.getpid()}.tmp"
+    _run([find_cxx(), "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", f"-I{include}",
+          ENGINE_API_SOURCE, "-o", partial, f"-L{library_dir}", f"-lpython{version}", "-ldl",
+          f"-Wl,-rpath,{library_dir}"])
+    os.replace(partial, target)
+    with open(stamp, "w") as output:
+        output.write(wanted)
+    return target
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv))
     print(build_host(force="--force" in sys.argv))
+    print(build_engine_api(force="--force" in sys.argv))

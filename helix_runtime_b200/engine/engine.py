@@ -267,6 +267,11 @@ class Engine:
     def request(self, request_id: int) -> Request:
         return self.scheduler.request(request_id)
 
+    def cached_at_finish(self, request_id: int) -> int:
+        """Tokens a request that has ended had in the cache when it ended (0: still running,
+        or never admitted)."""
+        return self._cached_at_finish.get(request_id, 0)
+
     def _finish_cache(self, request_id: int) -> None:
         self._cached_at_finish[request_id] = self.cache.length(request_id)
         self.cache.release(request_id)
@@ -487,7 +492,7 @@ class Engine:
             results.append(GenerationResult(
                 generated_tokens=list(request.generated),
                 stop_reason=request.stop_reason.value if request.stop_reason else "",
-                cached_token_count=self._cached_at_finish.get(request_id, 0),
+                cached_token_count=self.cached_at_finish(request_id),
                 request_id=request_id))
         return results
 
