@@ -638,9 +638,21 @@ void paged_attention_stream_kernel(
     }
   };
   const long long run = my_end - my_begin;
+  // The kernel before this one writes the keys and values of THIS step's tokens and nothing
+  // else of the cache.  A request brings at most a.tokens tokens, so of the keys a token
+  // sees only the last a.tokens can be new: a chunk that ends before them holds what
+  // earlier steps left, and its copies may start before the wait, while the predecessor
+  // still runs.  (Let in early, a warp then finds its first chunks in shared memory when the
+  // queries arrive.)
+  int requested = 0;
+  for (; requested < RING && requested < run; ++requested) {
+    if ((ahead.chunk + 1) * KEYS > ahead.keys - a.tokens) break;
+    request_chunk(requested);
+    cursor_next<KEYS>(a, ahead);
+  }
   hx_pdl_wait();
-  for (int i = 0; i < RING && i < run; ++i) {
-    request_chunk(i);
+  for (; requested < RING && requested < run; ++requested) {
+    request_chunk(requested);
     cursor_next<KEYS>(a, ahead);
   }
 
