@@ -327,6 +327,10 @@ struct RopeArgs {
   int heads, kv_heads, head_dim, rotary_dim, page_size, num_pages;
 };
 
+#ifndef HX_GEMM_STREAM_K
+#define HX_GEMM_STREAM_K 1      // 0: every unit of the persistent kernel is a whole tile
+#endif
+
 struct PersistentArgs {
   void* out;
   int ldo;
@@ -340,19 +344,47 @@ struct PersistentArgs {
   int k_blocks;               // per tile
   int* status;
   RopeArgs rope;              // EPI_ROPE_APPEND only
+  int whole_rounds;           // >= 0: the tiles behind this many whole rounds are shared out by
+                              // k-blocks (add epilogue only); -1: every unit is a whole tile
 };
 
+// What a CTA works on at a time: a tile, or (`partial`) a run of k-blocks of a tile that
+// other CTAs hold the rest of.
 struct Unit {
   int token_tile, feature_tile, kb_begin, kb_end;
+  bool partial;
 };
 
+// The grid walks the tiles round by round.  The last round seldom fills the grid: 256 tiles
+// on 148 CTAs are 1.73 rounds that cost 2.  Where the epilogue ADDS into a float32 output the
+// order of the sum is free, so the tiles of that last round are laid end to end as one list
+// of k-blocks and every CTA takes an equal run of it (one or two pieces of tiles), which it
+// adds to the output with atomic adds; whole tiles keep the plain read-add-store.
 __device__ __forceinline__ bool unit_at(const PersistentArgs& a, int iteration, Unit& u) {
-  const int index = blockIdx.x + iteration * gridDim.x;
-  if (index >= a.units) return false;
+  const int grid = static_cast<int>(gridDim.x);
+  int index;
+  if (a.whole_rounds < 0 || iteration < a.whole_rounds) {
+    index = static_cast<int>(blockIdx.x) + iteration * grid;
+    if (index >= a.units) return false;
+    u.kb_begin = 0;
+    u.kb_end = a.k_blocks;
+    u.partial = false;
+  } else {
+    const int first = a.whole_rounds * grid;
+    const long long blocks = static_cast<long long>(a.units - first) * a.k_blocks;
+    const long long begin = blocks * blockIdx.x / grid;
+    const long long end = blocks * (blockIdx.x + 1) / grid;
+    const long long tile = begin / a.k_blocks + (iteration - a.whole_rounds);
+    const long long from = max(begin, tile * a.k_blocks);
+    const long long to = min(end, (tile + 1) * a.k_blocks);
+    if (from >= to) return false;
+    index = first + static_cast<int>(tile);
+    u.kb_begin = static_cast<int>(from - tile * a.k_blocks);
+    u.kb_end = static_cast<int>(to - tile * a.k_blocks);
+    u.partial = u.kb_begin != 0 || u.kb_end != a.k_blocks;
+  }
   u.token_tile = index % a.token_tiles;
   u.feature_tile = index / a.token_tiles;
-  u.kb_begin = 0;
-  u.kb_end = a.k_blocks;
   return true;
 }
 
@@ -537,6 +569,33 @@ __device__ __forceinline__ void write_row_rope(const PersistentArgs& a, uint32_t
   }
 }
 
+// The piece of a tile that a partial unit computed: added to the float32 output with atomic
+// adds (four values at a time where the row allows).
+__device__ __forceinline__ void add_row_atomically(float* out, int ldo, int features,
+                                                   uint32_t lane_address, int token, int tokens,
+                                                   int feature0) {
+  const bool wide = (ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+#pragma unroll 1
+  for (int column = 0; column < 2 * BM; column += 16) {
+    if (feature0 + column >= features) break;      // uniform over the warp
+    float acc[16];
+    tmem_load16(lane_address + column, acc);
+    if (token >= tokens) continue;
+    float* row = out + static_cast<size_t>(token) * ldo + feature0 + column;
+    if (wide && feature0 + column + 16 <= features) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(row + 4 * j),
+                     "f"(acc[4 * j]), "f"(acc[4 * j + 1]), "f"(acc[4 * j + 2]),
+                     "f"(acc[4 * j + 3]) : "memory");
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (feature0 + column + j < features) atomicAdd(row + j, acc[j]);
+    }
+  }
+}
+
 template <int EPI>
 __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -640,8 +699,9 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t step = static_cast<uint64_t>(k * UMMA_K * 2 >> 4);
+            // a whole tile of the add epilogue starts from the old output in the accumulator
             const uint32_t accumulate =
-                (EPI == EPI_ADD_F32 || kb > unit.kb_begin || k > 0) ? 1u : 0u;
+                ((EPI == EPI_ADD_F32 && !unit.partial) || kb > unit.kb_begin || k > 0) ? 1u : 0u;
             umma_bf16(accumulator, desc_a + step, desc_b + step, idesc, accumulate);
           }
           umma_commit(&empty_bar[s]);
@@ -660,10 +720,11 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
     auto prepare = [&](int iteration) {
       if (EPI != EPI_ADD_F32 || !unit_at(args, iteration, unit)) return;
       const int buffer = iteration & 1;
-      load_row_into_accumulator(static_cast<const float*>(args.out), args.ldo, args.features,
-                                lane_base + buffer * Config::kBufferColumns,
-                                unit.token_tile * BM + quarter * 32 + lane, args.tokens,
-                                unit.feature_tile * FEATURES);
+      if (!unit.partial)      // a piece starts from zero and is added to the output afterwards
+        load_row_into_accumulator(static_cast<const float*>(args.out), args.ldo, args.features,
+                                  lane_base + buffer * Config::kBufferColumns,
+                                  unit.token_tile * BM + quarter * 32 + lane, args.tokens,
+                                  unit.feature_tile * FEATURES);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
@@ -687,6 +748,11 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
       if constexpr (EPI == EPI_ROPE_APPEND) {
         write_row_rope(args, lane_base + buffer * Config::kBufferColumns,
                        unit.token_tile * BM + quarter * 32 + lane, unit.feature_tile * FEATURES);
+      } else if (EPI == EPI_ADD_F32 && unit.partial) {
+        add_row_atomically(static_cast<float*>(args.out), args.ldo, args.features,
+                           lane_base + buffer * Config::kBufferColumns,
+                           unit.token_tile * BM + quarter * 32 + lane, args.tokens,
+                           unit.feature_tile * FEATURES);
       } else {
         write_row<EPI>(args.out, args.ldo, args.features,
                        lane_base + buffer * Config::kBufferColumns,
@@ -854,7 +920,21 @@ int launch_persistent(const CUtensorMap& map_w, const CUtensorMap& map_x, Persis
   const long long tiles = static_cast<long long>(args.token_tiles) * feature_tiles;
   HX_REQUIRE(tiles < (1ll << 30), "hx_gemm_tc: too many tiles");
   args.units = static_cast<int>(tiles);
-  const int ctas = args.units < sms ? args.units : sms;
+  // The add epilogue shares the last, partly filled round out by k-blocks (see unit_at) when
+  // that pays.  Every piece costs an epilogue of atomic adds (128 KB of them, all CTAs at the
+  // same time), which measured about as much as 30 k-blocks of products: with 2,048 tokens
+  // (108 tiles left for 148 SMs) sharing out gains nothing, with 512 tokens (64 tiles, less
+  // than half the grid) the output and down projections take 20 % and 23 % less time.
+  args.whole_rounds = -1;
+  int ctas = args.units < sms ? args.units : sms;
+  if (EPI == EPI_ADD_F32 && HX_GEMM_STREAM_K) {
+    const int rest = args.units % sms;
+    const long long run = static_cast<long long>(rest) * args.k_blocks / sms;
+    if (rest > 0 && rest * 2 <= sms && run >= 8 && args.k_blocks - run >= 32) {
+      args.whole_rounds = args.units / sms;
+      ctas = sms;
+    }
+  }
   hx_launch(gemm_tc_persistent_kernel<EPI>, ctas, THREADS, Config::kSmemBytes, stream, map_w,
             map_x, args);
   return HX_OK;

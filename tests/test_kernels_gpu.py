@@ -164,6 +164,10 @@ TC_SHAPES = [
     # more tiles than SMs: CTAs of the persistent kernel take three tiles and more, so both
     # accumulators in tensor memory are used again
     (1100, 9000, 136),
+    # the add epilogue shares a short last round out by k-blocks: 45 tiles of 64 k-blocks for
+    # the whole grid (every tile in pieces, ragged edges in tokens and features), and 188 tiles
+    # on 148 SMs (one round of whole tiles, then 40 tiles in pieces)
+    (600, 2250, 4096), (512, 12032, 4096),
 ]
 
 
