@@ -16,7 +16,17 @@ holds is one contiguous block.
 
 Pages are reserved before a step (:meth:`CacheManager.extend`) and a request's
 length is published after it (:meth:`CacheManager.commit`), which is the reference's
-transaction boundary (src/runtime/cpu_engine.cpp:191, 207, 235).  Next to the pages
+transaction boundary (src/runtime/cpu_engine.cpp:191, 207, 235).
+
+Deferred reclamation.  A request may end while a step that still reads or writes its pages
+is queued on the device (cancelled in flight; retired by the step before the one queued
+ahead).  ``release(request, after=step)`` then PARKS its pages and its slot behind that
+step's sequence number; they return to the ring, in the order they were parked, when the
+engine reports that step complete (:meth:`CacheManager.settle`), and only then can they
+reach another request.  The reference built the same rule into an allocator of its own (a
+free is held until a completion is ready, src/memory/deferred_allocator.cpp:43-70, an event
+on the releasing stream, src/memory/stream_ordered_allocator.cpp:15-31) and never wired it to
+its cache; here the unit is the page and the completion is the step.  Next to the pages
 every request owns one *state slot*: a row in each per-layer state tensor that a
 mixer asked for (fixed size, zeroed at admission), and a row in the block tables.
 """
@@ -127,6 +137,10 @@ class CacheManager:
         self._requests: Dict[Hashable, RequestCache] = {}
         # page lists held without a request (published prefixes): per anchor, per group
         self._anchors: Dict[Hashable, Tuple[int, List[List[int]]]] = {}
+        # what was given up while a step still used it: (step, slot or None, pages per group),
+        # oldest first
+        self._parked: Deque[Tuple[int, Optional[int], List[List[int]]]] = deque()
+        self.settled_step = -1
 
     # ------------------------------------------------------------------ lookups
 
@@ -285,37 +299,68 @@ class CacheManager:
                 group.dirty = True
                 record.first_live[index] = dead_pages
 
-    def rollback(self, request: Hashable, keep_length: Optional[int] = None) -> None:
+    def rollback(self, request: Hashable, keep_length: Optional[int] = None,
+                 after: Optional[int] = None) -> None:
         """Give back pages reserved beyond the published length (a step that failed), or
         beyond ``keep_length`` when an earlier step that reserved up to there is still in
-        flight."""
+        flight.  ``after``: a step on the device that may still write them (see
+        :meth:`release`)."""
         record = self._requests[request]
         target = record.length if keep_length is None else keep_length
         if not record.length <= target <= record.reserved:
             raise ValueError(f"cannot roll back to {target}: published {record.length}, "
                              f"reserved {record.reserved}")
         keep = self.pages_for(target)
+        parked: List[List[int]] = []
         for index, group in enumerate(self.groups):
             table = record.tables[index]
+            extra: List[int] = []
             if len(table) > keep:
                 extra = [page for page in table[keep:] if page >= 0]
-                self._give_back(group, extra)
                 group.host_tables[record.slot, keep:len(table)] = -1
                 del table[keep:]
                 group.dirty = True
+            parked.append(extra)
+        if after is not None and after > self.settled_step and any(parked):
+            self._parked.append((after, None, parked))
+        else:
+            for group, pages in zip(self.groups, parked):
+                self._give_back(group, pages)
         record.reserved = target
 
-    def release(self, request: Hashable) -> int:
-        """The request is over: give back its pages (in table order) and its slot."""
+    def release(self, request: Hashable, after: Optional[int] = None) -> int:
+        """The request is over: give back its pages (in table order) and its slot.  ``after``:
+        the sequence number of a step on the device that may still touch them; pages and slot
+        are then parked until :meth:`settle` hears that step is complete.  Returns the pages
+        that became free now."""
         record = self._requests.pop(request)
-        freed = 0
-        for index, group in enumerate(self.groups):
-            pages = [page for page in record.tables[index] if page >= 0]
-            freed += self._give_back(group, pages)
+        held = [[page for page in record.tables[index] if page >= 0]
+                for index in range(len(self.groups))]
+        for group in self.groups:
             group.host_tables[record.slot, :] = -1
             group.dirty = True
+        if after is not None and after > self.settled_step:
+            self._parked.append((after, record.slot, held))
+            return 0
         self._free_slots.append(record.slot)
+        return sum(self._give_back(group, pages) for group, pages in zip(self.groups, held))
+
+    def settle(self, step: int) -> int:
+        """Every step up to ``step`` has completed on the device: what was parked behind them
+        goes back, oldest first.  Returns the pages that became free."""
+        self.settled_step = max(self.settled_step, step)
+        freed = 0
+        while self._parked and self._parked[0][0] <= self.settled_step:
+            _, slot, held = self._parked.popleft()
+            if slot is not None:
+                self._free_slots.append(slot)
+            freed += sum(self._give_back(group, pages) for group, pages in zip(self.groups, held))
         return freed
+
+    @property
+    def parked_pages(self) -> int:
+        """Pages (summed over groups) that wait for a step to complete."""
+        return sum(len(pages) for _, _, held in self._parked for pages in held)
 
     def fork(self, source: Hashable, request: Hashable, tokens: int) -> int:
         """Admit ``request`` sharing the first ``tokens`` positions of ``source``.
@@ -428,7 +473,8 @@ class CacheManager:
 
     def check(self) -> None:
         """No page lost, held twice by mistake, or freed twice; no slot lost."""
-        slots = [record.slot for record in self._requests.values()]
+        slots = [record.slot for record in self._requests.values()] + \
+            [slot for _, slot, _ in self._parked if slot is not None]
         assert len(slots) == len(set(slots)), "a state slot is held twice"
         assert sorted(slots + list(self._free_slots)) == list(range(self.max_requests)), \
             "a state slot is lost"
@@ -449,6 +495,9 @@ class CacheManager:
                 assert len(held[index]) == len(set(held[index])), "an anchor holds a page twice"
                 for page in held[index]:
                     holders[page] += 1
+            for _, _, held in self._parked:
+                for page in held[index]:
+                    holders[page] += 1
             for page in range(group.pool.num_pages):
                 assert holders[page] == group.pool.refcount(page), \
                     f"group {index} page {page}: {holders[page]} holders, " \
@@ -460,6 +509,7 @@ class CacheManager:
             "free_slots": len(self._free_slots),
             "anchors": len(self._anchors),
             "anchor_pages": self.anchor_pages(),
+            "parked_pages": self.parked_pages,
             "groups": [{
                 "window": group.need.window,
                 "layers": len(group.entries),

@@ -149,6 +149,8 @@ class _Flight:
     new_lengths: List[int] = dataclasses.field(default_factory=list)
     decode_only: bool = False
     error: Optional[str] = None
+    sequence: int = 0                                 # steps are numbered as they are queued
+    done: object = None                               # event behind the step's last kernel
 
     def __post_init__(self) -> None:
         self.result = IterationResult()
@@ -209,6 +211,7 @@ class Engine:
                                       config.prefix_cache_pages)
         self._matches: Dict[int, PrefixMatch] = {}      # lookups of the iteration being planned
         self._flight: Optional[_Flight] = None          # the step queued ahead, if any
+        self._steps_queued = 0                          # sequence number of the next step
         self.steps_queued_ahead = 0
 
     # ------------------------------------------------------------ construction
@@ -273,8 +276,11 @@ class Engine:
         return self._cached_at_finish.get(request_id, 0)
 
     def _finish_cache(self, request_id: int) -> None:
+        """The request has ended: its pages and slot go back, at once or, while a step that was
+        queued ahead may still touch them, when that step has completed."""
         self._cached_at_finish[request_id] = self.cache.length(request_id)
-        self.cache.release(request_id)
+        in_flight = self._flight
+        self.cache.release(request_id, after=None if in_flight is None else in_flight.sequence)
 
     # ------------------------------------------------------------- prefix index
 
@@ -331,7 +337,9 @@ class Engine:
     def _launch(self, batch: IterationBatch, previous: Optional["_Flight"]) -> "_Flight":
         """Queue the batch's step on the device.  ``previous``: the step in flight whose
         sampled tokens this one reads on the device (same requests, one token each)."""
-        flight = _Flight(batch=batch, slot=0 if previous is None else 1 - previous.slot)
+        flight = _Flight(batch=batch, slot=0 if previous is None else 1 - previous.slot,
+                         sequence=self._steps_queued)
+        self._steps_queued += 1
         result = flight.result
         result.preempted = list(batch.preempted)
         result.kv_limited = batch.kv_limited
@@ -393,6 +401,8 @@ class Engine:
                 else:
                     self.model.forward(flight.ctx, self.cache, want_rows, 0)
                 self.sampler.fetch(flight.slot, tokens, step.status)
+                flight.done = torch.cuda.Event()
+                flight.done.record()
             except Exception:
                 # what a step still in flight reserved stays; this step's pages go back
                 step.fail(entries, [length - len(entry.tokens) for entry, length
@@ -414,7 +424,7 @@ class Engine:
             if flags & ~ops.FLAG_NONFINITE:
                 # anything but per-row non-finite logits condemns the whole step, and with it a
                 # step that was queued behind it and has read what this one left
-                step.fail(entries)
+                step.fail(entries, after=None if self._flight is None else self._flight.sequence)
                 flight.error = StepFunction.describe_status(flags)
                 if self._flight is not None:
                     self._flight.error = flight.error
@@ -449,6 +459,12 @@ class Engine:
         else:
             completions = [WorkCompletion(work.request_id, False, error=flight.error)
                            for work in batch.work]
+        # the step is complete on the device (its results have been read; the event behind
+        # its last kernel is waited for, which costs nothing by now): what ended while it was
+        # queued may be handed out again
+        if flight.done is not None:
+            flight.done.synchronize()
+        self.cache.settle(flight.sequence)
         retired = self.scheduler.complete_iteration(batch.id, completions,
                                                     self.model.max_positions,
                                                     now=time.monotonic())

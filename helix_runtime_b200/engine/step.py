@@ -216,15 +216,17 @@ class StepFunction:
         self.tokens_run += ctx.n_tokens
 
     def fail(self, entries: Sequence[StepEntry],
-             keep_lengths: Optional[Sequence[int]] = None) -> None:
+             keep_lengths: Optional[Sequence[int]] = None, after: Optional[int] = None) -> None:
         """The step failed: give back what was reserved for it; no length moves.
         ``keep_lengths``: what an earlier step that is still in flight has reserved for each
-        entry, which stays."""
+        entry, which stays.  ``after``: a later step, already queued on the device, that may
+        still write the pages given back (they are parked until it completes)."""
         self.workspace.clear_accumulators()
         for index, entry in enumerate(entries):
             if self.cache.has(entry.request):
                 self.cache.rollback(entry.request,
-                                    None if keep_lengths is None else keep_lengths[index])
+                                    None if keep_lengths is None else keep_lengths[index],
+                                    after=after)
 
     @staticmethod
     def describe_status(flags: int) -> str:

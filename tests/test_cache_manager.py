@@ -229,3 +229,80 @@ def test_random_orders_of_requests_never_lose_a_page(seed):
     assert cache.free_slots == 3
     if counter > 6:
         assert any(group.pool.reuse_count > 0 for group in cache.groups)
+
+
+def test_what_ends_while_a_step_is_queued_is_parked_until_that_step_completes():
+    """Pages and the slot of a request that ends while step 7 is on the device stay out of the
+    ring until ``settle(7)``; then they return in the order they were parked, so page reuse
+    stays a function of the trace.  The reference tests its deferred allocator the same way,
+    with completions that the test controls (tests/deferred_allocator_test.cpp:51-160)."""
+    cache = CacheManager({0: KvNeed(1, 4)}, {}, 4, 8, 2, 64, torch.float32, torch.device("cpu"))
+    cache.admit("a")
+    cache.extend("a", 10)
+    cache.commit("a", 10)                         # pages 0, 1, 2
+    cache.admit("b")
+    cache.extend("b", 5)
+    cache.commit("b", 5)                          # pages 3, 4
+    assert cache.free_pages() == [3] and cache.free_slots == 0
+    assert cache.release("a", after=7) == 0       # nothing free yet
+    assert cache.free_pages() == [3] and cache.free_slots == 0 and cache.parked_pages == 3
+    assert not cache.has("a")
+    cache.check()
+    with pytest.raises(OutOfPages):               # the slot is parked too
+        cache.admit("c")
+    assert cache.settle(6) == 0                   # an earlier step completing changes nothing
+    cache.extend("b", 9)
+    cache.rollback("b", after=7)                  # a failed step's page, also behind step 7
+    assert cache.parked_pages == 4 and cache.free_pages() == [2]
+    cache.check()
+    assert cache.settle(7) == 4
+    assert cache.free_pages() == [6] and cache.free_slots == 1 and cache.parked_pages == 0
+    cache.admit("c")
+    cache.extend("c", 24)
+    # the ring: never-used pages 6, 7 first, then a's pages in their order, then b's rolled back
+    assert cache._requests["c"].tables[0] == [6, 7, 0, 1, 2, 5]
+    # a step that has completed already parks nothing
+    assert cache.release("b", after=7) == 2
+    cache.release("c")
+    cache.check()
+    assert cache.free_pages() == [8] and cache.free_slots == 2
+
+
+def test_random_orders_with_parking_lose_nothing():
+    rng = np.random.default_rng(11)
+    cache = CacheManager({0: KvNeed(2, 8), 1: KvNeed(2, 8, window=12)}, {}, 4, 24, 4, 96,
+                         torch.float32, torch.device("cpu"))
+    live, step, settled = {}, 0, -1
+    for _ in range(600):
+        action = rng.integers(0, 5)
+        name = f"r{rng.integers(0, 8)}"
+        if action == 0 and name not in live and cache.free_slots:
+            cache.admit(name)
+            live[name] = 0
+        elif action == 1 and name in live:
+            grow = int(rng.integers(1, 9))
+            target = min(live[name] + grow, 96)
+            try:
+                cache.extend(name, target)
+            except OutOfPages:
+                continue
+            if rng.integers(0, 4) == 0:
+                cache.rollback(name, after=step if rng.integers(0, 2) else None)
+            else:
+                cache.commit(name, target)
+                live[name] = target
+        elif action == 2 and name in live:
+            cache.release(name, after=step if rng.integers(0, 2) else None)
+            del live[name]
+        elif action == 3:
+            step += 1
+        elif action == 4 and settled < step:
+            settled = int(rng.integers(settled + 1, step + 1))
+            cache.settle(settled)
+        cache.check()
+    cache.settle(step)
+    for name in list(live):
+        cache.release(name)
+    cache.check()
+    assert cache.parked_pages == 0 and cache.free_slots == 4
+    assert cache.free_pages() == [24, 24]

@@ -149,3 +149,39 @@ def test_a_bounded_wait_that_runs_out_sets_the_flag_and_the_kernel_returns():
     assert ops.bounded_wait_check(5, True, status) is True and int(status.item()) == 0
     with pytest.raises(ops.KernelError, match="polls"):
         ops.bounded_wait_check(10 ** 9, False, status)
+
+
+def test_pages_of_a_request_cancelled_in_flight_wait_for_the_step_that_uses_them(folders,
+                                                                                  plain_models):
+    """A request cancelled while a decode step with its row is queued on the device: its pages
+    and slot are parked, reach nobody until that step has completed, and the request beside
+    it generates what the plain implementation generates."""
+    plain = plain_models("C", "bfloat16")
+    engine = Engine.from_pretrained(folders("C", "bfloat16"), dtype="bfloat16",
+                                    page_size=PAGE_SIZE["C"], max_running_requests=2,
+                                    num_pages=12)
+    prompts = [random_tokens(512, n, seed=70 + n) for n in (33, 21)]
+    ids = [engine.submit(prompt, 24) for prompt in prompts]
+    while engine._flight is None:
+        engine.run_iteration()
+    free_before = engine.cache.free_pages()
+    assert engine.cancel(ids[0])
+    cache = engine.stats()["cache"]
+    assert cache["parked_pages"] >= 3 and engine.cache.free_pages() == free_before
+    assert not engine.cache.has(ids[0]) and engine.cache.free_slots == 0
+    engine.cache.check()
+    engine.run_iteration()                        # completes the step that was queued
+    assert engine.stats()["cache"]["parked_pages"] == 0
+    assert engine.cache.free_pages()[0] >= free_before[0] + 3
+    late = engine.submit(random_tokens(512, 40, seed=5), 6)     # takes the parked slot and pages
+    engine.run_until_done()
+    assert engine.request(ids[0]).state is RequestState.CANCELLED
+    for request_id, prompt in ((ids[1], prompts[1]), (late, random_tokens(512, 40, seed=5))):
+        generated = engine.request(request_id).generated
+        tokens = list(prompt)
+        for token in generated:
+            row = plain.logits(tokens)[-1]
+            assert row[token] >= row.max() - 6e-3
+            tokens.append(token)
+    assert len(engine.request(ids[1]).generated) == 24
+    assert all_pages_free(engine)
