@@ -127,6 +127,9 @@ class EngineConfig:
     cuda_graphs: bool = True                  # replay decode-only steps as CUDA graphs
     lookahead: bool = True                    # queue the next decode step before this one's
                                               # tokens have been read (needs cuda_graphs)
+    ordered_sums: bool = False                # decode products sum in a fixed order (no split-K
+                                              # atomics): logits repeat bit for bit from run to
+                                              # run, at the price of slower weight streams
 
 
 @dataclasses.dataclass
@@ -194,7 +197,7 @@ class Engine:
                                   device, poison=config.poison_free_pages)
         self.step_function = StepFunction(model, self.cache, config.max_tokens_per_iteration,
                                           config.max_running_requests,
-                                          config.attention_split_keys)
+                                          config.attention_split_keys, config.ordered_sums)
         self.scheduler = FifoScheduler(
             SchedulerConfig(config.max_tokens_per_iteration, config.max_running_requests,
                             config.max_prefill_chunk), config.page_size)

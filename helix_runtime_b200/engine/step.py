@@ -37,7 +37,8 @@ class StepError(RuntimeError):
 
 class StepFunction:
     def __init__(self, model: DecoderModel, cache: CacheManager, max_tokens: int,
-                 max_requests: int, attention_split_keys: int = 256) -> None:
+                 max_requests: int, attention_split_keys: int = 256,
+                 ordered_sums: bool = False) -> None:
         if model.device is None:
             raise StepError("the model has no weights bound")
         self.model = model
@@ -47,6 +48,7 @@ class StepFunction:
         self.max_tokens = int(max_tokens)
         self.max_requests = int(max_requests)
         self.attention_split_keys = int(attention_split_keys)
+        self.ordered_sums = bool(ordered_sums)
         self.workspace = Workspace(self.device)
         cap, req = self.max_tokens, self.max_requests
         # one packed int32 block: a single host-to-device copy per step
@@ -184,7 +186,7 @@ class StepFunction:
             request_context=self._view("request_context", True),
             status=self.status, max_query_len=max_query, min_query_len=min_query,
             max_context_len=max(max_context, context_hint),
-            attention_split_keys=self.attention_split_keys,
+            attention_split_keys=self.attention_split_keys, ordered_sums=self.ordered_sums,
             host_request_slots=[int(v) for v in request_slot[:len(entries)]],
             host_request_starts=[int(v) for v in request_start[:len(entries) + 1]],
             host_request_contexts=[int(v) for v in request_context[:len(entries)]],

@@ -158,7 +158,8 @@ class PagedAttention(Mixer):
             # rounds as the product's store would have, and clears
             accumulator = ctx.workspace.accumulator("attention.qkv",
                                                     (STREAMING_MAX_TOKENS, self.qkv_size))
-            project_into_accumulator(x, self.w_qkv, accumulator, n, ctx.status)
+            project_into_accumulator(x, self.w_qkv, accumulator, n, ctx.status,
+                                     ctx.ordered_sums)
             self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads, accum=accumulator)
         elif not self.position.project_and_apply(ctx, cache, x, self.w_qkv, qkv, self.heads,
                                                  self.kv_heads):
@@ -194,7 +195,7 @@ class PagedAttention(Mixer):
                                 ctx.status, request_start=ctx.request_start,
                                 skip_query_len=TENSOR_CORE_MIN_QUERY if tensor_cores else 0,
                                 arrivals=arrivals)
-        project(context, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status)
+        project(context, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
 
 
 register_part("mixer", "paged_attention", PagedAttention)

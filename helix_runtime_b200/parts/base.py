@@ -130,6 +130,7 @@ class StepContext:
     min_query_len: int                  # fewest tokens any request brings to this step
     max_context_len: int                # longest (cached + new) length in the batch
     attention_split_keys: int = 256
+    ordered_sums: bool = False          # products must sum in a fixed order (no split-K atomics)
     # host-side copies for parts that are not kernels (tests' toy parts)
     host_request_slots: Optional[List[int]] = None
     host_request_starts: Optional[List[int]] = None

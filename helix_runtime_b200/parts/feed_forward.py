@@ -48,8 +48,8 @@ class GatedMlp(FeedForward):
         n = ctx.n_tokens
         act = ctx.workspace.get("mlp.act", (ctx.capacity, self.intermediate), ctx.dtype)
         project_swiglu(x, self.w_gate_up, self.intermediate, act, ctx.workspace, ctx.capacity, n,
-                       ctx.status)
-        project(act, self.w_down, residual, n, ops.EPI_ADD_F32, ctx.status)
+                       ctx.status, ctx.ordered_sums)
+        project(act, self.w_down, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
 
 
 register_part("feed_forward", "gated_mlp", GatedMlp)

@@ -92,9 +92,10 @@ def units_per_sm(tokens: int) -> float:
     return UNITS_FEW_TOKENS if tokens <= 16 else UNITS_MANY_TOKENS
 
 
-def split_k_for(tokens: int, features: int, depth: int) -> int:
-    """Ways to cut the reduction of a weight-streaming product (1: not at all)."""
-    if tokens > STREAMING_MAX_TOKENS:
+def split_k_for(tokens: int, features: int, depth: int, ordered: bool = False) -> int:
+    """Ways to cut the reduction of a weight-streaming product (1: not at all).  ``ordered``:
+    the caller wants sums in a fixed order, which atomic adds of several splits cannot give."""
+    if tokens > STREAMING_MAX_TOKENS or ordered:
         return 1
     tiles = -(-features // 128)
     k_blocks = -(-depth // 64)
@@ -103,28 +104,30 @@ def split_k_for(tokens: int, features: int, depth: int) -> int:
 
 
 def project(x: torch.Tensor, w: Weight, out: torch.Tensor, tokens: int, epilogue: int,
-            status: torch.Tensor) -> None:
+            status: torch.Tensor, ordered: bool = False) -> None:
     """``out[:tokens] (op)= x[:tokens] @ w.T``; epilogue is one of ops.EPI_STORE,
-    ops.EPI_STORE_F32, ops.EPI_ADD_F32."""
+    ops.EPI_STORE_F32, ops.EPI_ADD_F32.  ``ordered``: no split-K (see ``split_k_for``)."""
     if tokens == 0:
         return
     if uses_tensor_cores(x, w, tokens):
-        splits = split_k_for(tokens, w.rows, w.depth) if epilogue == ops.EPI_ADD_F32 else 1
+        splits = split_k_for(tokens, w.rows, w.depth, ordered) \
+            if epilogue == ops.EPI_ADD_F32 else 1
         _gemm_tc(x, w, out, tokens, w.rows, epilogue, status, k_splits=splits)
     else:
         _gemm_simt(x, w, out, tokens, epilogue)
 
 
 def project_into_accumulator(x: torch.Tensor, w: Weight, accumulator: torch.Tensor,
-                             tokens: int, status: torch.Tensor) -> None:
+                             tokens: int, status: torch.Tensor, ordered: bool = False) -> None:
     """``accumulator[:tokens] += x[:tokens] @ w.T`` as a split-K weight stream (float32; the
     accumulator is clear on entry and its reader clears it again)."""
-    splits = split_k_for(tokens, w.rows, w.depth)
+    splits = split_k_for(tokens, w.rows, w.depth, ordered)
     _gemm_tc(x, w, accumulator, tokens, w.rows, ops.EPI_ADD_F32, status, k_splits=splits)
 
 
 def project_swiglu(x: torch.Tensor, w_gate_up: Weight, intermediate: int, act: torch.Tensor,
-                   workspace, capacity: int, tokens: int, status: torch.Tensor) -> None:
+                   workspace, capacity: int, tokens: int, status: torch.Tensor,
+                   ordered: bool = False) -> None:
     """``act[:tokens] = silu(x @ gate.T) * (x @ up.T)`` with ``w_gate_up = [gate; up]``.
 
     Three routes, one rounding each (float32 gate and up, float32 activation, one store):
@@ -135,7 +138,7 @@ def project_swiglu(x: torch.Tensor, w_gate_up: Weight, intermediate: int, act: t
         return
     if is_weight_stream(x, w_gate_up, tokens):
         accumulator = workspace.accumulator("mlp.gate_up", (STREAMING_MAX_TOKENS, 2 * intermediate))
-        project_into_accumulator(x, w_gate_up, accumulator, tokens, status)
+        project_into_accumulator(x, w_gate_up, accumulator, tokens, status, ordered)
         ops.swiglu(accumulator[:tokens], act[:tokens], zero_input=True)
     elif uses_tensor_cores(x, w_gate_up, tokens):
         _gemm_tc(x, w_gate_up, act, tokens, intermediate, ops.EPI_SWIGLU, status,

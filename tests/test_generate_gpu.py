@@ -250,9 +250,11 @@ def test_steps_queued_ahead_change_nothing(name, dtype, folders, plain_models):
                for length in (5, 33, 12, limit - 6, 20, 3)]
     budgets = [24, 40, 7, 30, 18, 33]
     temperatures = [0.0, 0.7, 0.0, 0.0, 0.9, 0.0]
+    # token for token between two runs: the bfloat16 engine is asked for sums in a fixed order
+    # (split-K atomics would leave a greedy pick between near-equal logits to chance)
     options = dict(dtype=dtype, page_size=page, max_running_requests=3,
                    max_tokens_per_iteration=64, num_pages=-(-limit // page) + 8,
-                   poison_free_pages=True)
+                   poison_free_pages=True, ordered_sums=dtype == "bfloat16")
     free = Engine.from_pretrained(folders(name, dtype), lookahead=False, **options)
     free_run = run_requests(free, prompts, budgets, None, temperatures)
     eos = free_run[0][0][9]                     # the first request meets it at its tenth token
@@ -274,6 +276,38 @@ def test_steps_queued_ahead_change_nothing(name, dtype, folders, plain_models):
     assert cancelled[1][1] == "cancelled"
     for index in (0, 2):                         # those that ran beside it are untouched
         assert cancelled[index] == outcomes[True][index]
+
+
+def test_ordered_sums_repeat_bit_for_bit(folders, plain_models):
+    """With ``ordered_sums`` the decode products are not cut along the reduction, so nothing is
+    summed by atomic adds: the same steps give the same logits to the last bit on a second
+    run, and they are the plain implementation's within the usual tolerance."""
+    from engine_harness import assert_close, tolerance
+    from helix_runtime_b200 import StepEntry, StepFunction, load_model
+    from helix_runtime_b200.cache.manager import CacheManager
+    plain = plain_models("C", "bfloat16")
+    a = random_tokens(512, 90, seed=1)
+    b = random_tokens(512, 37, seed=2)
+    runs = []
+    for _ in range(2):
+        model = load_model(folders("C", "bfloat16"), "bfloat16", "cuda:0")
+        kv, state = model.cache_needs()
+        cache = CacheManager(kv, state, 16, 16, 2, model.max_positions, model.dtype, model.device)
+        step = StepFunction(model, cache, max_tokens=128, max_requests=2, ordered_sums=True)
+        cache.admit("a")
+        cache.admit("b")
+        rows = [step.run([StepEntry("a", a[:70], [69]), StepEntry("b", b[:20], [19])])
+                .cpu().numpy().copy()]
+        for index in range(17):
+            rows.append(step.run([StepEntry("a", [a[70 + index]], [0]),
+                                  StepEntry("b", [b[20 + index]], [0])]).cpu().numpy().copy())
+        runs.append(np.concatenate(rows))
+    assert np.array_equal(runs[0], runs[1])
+    expected_a, expected_b = plain.logits(a[:87]), plain.logits(b[:37])
+    want = [expected_a[69], expected_b[19]]
+    for index in range(17):
+        want += [expected_a[70 + index], expected_b[20 + index]]
+    assert_close(runs[0], np.stack(want), "ordered sums", **tolerance("bfloat16", "C"))
 
 
 def test_graphs_recorded_before_the_scratch_grew_stay_valid(folders, plain_models):
