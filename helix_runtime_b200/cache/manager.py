@@ -110,10 +110,18 @@ class RequestCache:
 class CacheManager:
     def __init__(self, kv_needs: Mapping[int, KvNeed], state_needs: Mapping[int, StateNeed],
                  page_size: int, num_pages: int, max_requests: int, max_positions: int,
-                 dtype: torch.dtype, device: torch.device, poison: bool = False) -> None:
+                 dtype: torch.dtype, device: torch.device, poison: bool = False,
+                 window_slack_pages: int = 0) -> None:
         if page_size <= 0 or max_requests <= 0 or max_positions <= 0:
             raise ValueError("page_size, max_requests and max_positions must be positive")
+        if window_slack_pages < 0:
+            raise ValueError("window_slack_pages must not be negative")
         self.page_size = int(page_size)
+        # Pages a windowed group keeps behind its window before it gives them back.  A prefix
+        # is kept for later requests at the last page boundary of a prompt, up to a page
+        # short of where its request stands by then: with one page of slack the keys that the
+        # window of that boundary reaches back to are still there.
+        self.window_slack_pages = int(window_slack_pages)
         self.max_requests = int(max_requests)
         self.max_positions = int(max_positions)
         self.max_pages_per_request = -(-self.max_positions // self.page_size)
@@ -200,9 +208,18 @@ class CacheManager:
         needed = []
         for group in self.groups:
             window = group.need.window
-            live = rows if window is None else min(rows, window + self.page_size)
+            live = rows if window is None else \
+                min(rows, window + (1 + self.window_slack_pages) * self.page_size)
             needed.append(self.pages_for(live))
         return needed
+
+    def first_page_seen(self, group: CacheGroup, length: int) -> int:
+        """Index of the first page that the query at position ``length`` still reads in
+        ``group``: 0 without a window."""
+        window = group.need.window
+        if window is None:
+            return 0
+        return max(0, length - window + 1) // self.page_size
 
     def pages_to_extend(self, request: Hashable, new_length: int) -> List[int]:
         """Pages each group must add so that positions ``[0, new_length)`` have a place."""
@@ -287,7 +304,7 @@ class CacheManager:
             if window is None:
                 continue
             # the next query sits at position new_length and reads keys >= new_length-window+1
-            dead_pages = max(0, new_length - window + 1) // self.page_size
+            dead_pages = max(0, self.first_page_seen(group, new_length) - self.window_slack_pages)
             table = record.tables[index]
             first = record.first_live[index]
             if dead_pages > first:
@@ -362,32 +379,50 @@ class CacheManager:
         """Pages (summed over groups) that wait for a step to complete."""
         return sum(len(pages) for _, _, held in self._parked for pages in held)
 
-    def fork(self, source: Hashable, request: Hashable, tokens: int) -> int:
-        """Admit ``request`` sharing the first ``tokens`` positions of ``source``.
+    def _shared_pages(self, parent: RequestCache, tokens: int) -> List[List[int]]:
+        """The pages of ``parent`` that a request standing at ``tokens`` reads, per group, by
+        page index (-1 where a window has passed: nobody reads there again).  Raises when a
+        page that is still read has been given back already."""
+        count = tokens // self.page_size
+        shared = []
+        for index, group in enumerate(self.groups):
+            first = self.first_page_seen(group, tokens)
+            if parent.first_live[index] > first:
+                raise ValueError(
+                    f"group {group.index}: the source has given back pages that a request at "
+                    f"{tokens} tokens still reads (window {group.need.window})")
+            shared.append([-1] * first + list(parent.tables[index][first:count]))
+        return shared
 
-        Only whole pages are shared, so nothing is ever copied on write
-        (src/kv_cache/paged.cpp:535-620).  Groups with a window cannot share."""
-        if tokens <= 0 or tokens % self.page_size != 0:
-            raise ValueError("a shared prefix must be a positive multiple of the page size")
-        parent = self._requests[source]
-        if tokens > parent.length:
-            raise ValueError("cannot share more than the source has published")
-        if any(group.need.window is not None for group in self.groups):
-            raise ValueError("groups with a window do not share prefixes")
-        if self.states:
-            raise ValueError("requests with per-request state do not share prefixes")
+    def _admit_with(self, request: Hashable, tokens: int, shared: List[List[int]]) -> int:
         slot = self.admit(request)
         record = self._requests[request]
         count = tokens // self.page_size
         for index, group in enumerate(self.groups):
-            pages = parent.tables[index][:count]
-            group.pool.share(pages)
+            pages = shared[index][:count]
+            group.pool.share([page for page in pages if page >= 0])
             record.tables[index] = list(pages)
+            record.first_live[index] = next((i for i, page in enumerate(pages) if page >= 0), count)
             group.host_tables[slot, :count] = pages
             group.dirty = True
         record.length = tokens
         record.reserved = tokens
         return slot
+
+    def fork(self, source: Hashable, request: Hashable, tokens: int) -> int:
+        """Admit ``request`` sharing the first ``tokens`` positions of ``source``.
+
+        Only whole pages are shared, so nothing is ever copied on write
+        (src/kv_cache/paged.cpp:535-620).  A group with a window shares the pages its window
+        still reaches from ``tokens``; they must not have been given back yet."""
+        if tokens <= 0 or tokens % self.page_size != 0:
+            raise ValueError("a shared prefix must be a positive multiple of the page size")
+        parent = self._requests[source]
+        if tokens > parent.length:
+            raise ValueError("cannot share more than the source has published")
+        if self.states:
+            raise ValueError("requests with per-request state do not share prefixes")
+        return self._admit_with(request, tokens, self._shared_pages(parent, tokens))
 
     # ------------------------------------------------------------------ anchors
     #
@@ -397,30 +432,35 @@ class CacheManager:
 
     @property
     def can_share(self) -> bool:
-        """Whole-page sharing needs every key of the prefix to stay in its page: no group
-        with a window, no per-request state."""
-        return not self.states and all(group.need.window is None for group in self.groups)
+        """Whole-page sharing needs the prefix to be in pages and nowhere else: no
+        per-request state (its value at the end of the prefix would have to be kept too)."""
+        return not self.states
+
+    @property
+    def shares_whole_prefixes_only(self) -> bool:
+        """With a windowed group an anchor holds the pages its window reaches from the END of
+        the prefix, so a request can adopt all of the prefix or none of it; without windows
+        any number of its leading pages."""
+        return any(group.need.window is not None for group in self.groups)
 
     def hold(self, anchor: Hashable, source: Hashable, tokens: int) -> int:
         """Keep the first ``tokens`` positions (whole pages) of ``source`` under ``anchor``;
-        returns the pages it now holds per group."""
+        returns the page references it now holds, summed over groups.  Raises ValueError
+        when a windowed group of the source has already given back pages it would need."""
         if anchor in self._anchors:
             raise KeyError(f"anchor {anchor!r} exists")
         if tokens <= 0 or tokens % self.page_size != 0:
             raise ValueError("a shared prefix must be a positive multiple of the page size")
         if not self.can_share:
-            raise ValueError("this cache cannot share prefixes (windows or per-request state)")
+            raise ValueError("this cache cannot share prefixes (per-request state)")
         parent = self._requests[source]
         if tokens > parent.length:
             raise ValueError("cannot share more than the source has published")
-        count = tokens // self.page_size
-        held = []
-        for index, group in enumerate(self.groups):
-            pages = list(parent.tables[index][:count])
-            group.pool.share(pages)
-            held.append(pages)
+        held = self._shared_pages(parent, tokens)
+        for group, pages in zip(self.groups, held):
+            group.pool.share([page for page in pages if page >= 0])
         self._anchors[anchor] = (tokens, held)
-        return count
+        return sum(1 for pages in held for page in pages if page >= 0)
 
     def adopt(self, request: Hashable, anchor: Hashable, tokens: Optional[int] = None) -> int:
         """Admit ``request`` with the first ``tokens`` positions (default: all) of ``anchor``
@@ -429,27 +469,20 @@ class CacheManager:
         tokens = held_tokens if tokens is None else tokens
         if tokens <= 0 or tokens % self.page_size != 0 or tokens > held_tokens:
             raise ValueError("a request adopts a positive number of whole pages of the anchor")
-        slot = self.admit(request)
-        record = self._requests[request]
-        count = tokens // self.page_size
-        for index, group in enumerate(self.groups):
-            pages = held[index][:count]
-            group.pool.share(pages)
-            record.tables[index] = list(pages)
-            group.host_tables[slot, :count] = pages
-            group.dirty = True
-        record.length = tokens
-        record.reserved = tokens
-        return slot
+        if tokens != held_tokens and self.shares_whole_prefixes_only:
+            raise ValueError("with a windowed group a request adopts all of an anchor or none")
+        return self._admit_with(request, tokens, held)
 
     def drop(self, anchor: Hashable) -> int:
         """Forget the anchor; returns the pages that became free."""
         _, held = self._anchors.pop(anchor)
-        return sum(self._give_back(group, pages) for group, pages in zip(self.groups, held))
+        return sum(self._give_back(group, [page for page in pages if page >= 0])
+                   for group, pages in zip(self.groups, held))
 
     def anchor_pages(self) -> int:
         """Pages (per group, summed) that anchors hold references to."""
-        return sum(len(pages) for _, held in self._anchors.values() for pages in held)
+        return sum(1 for _, held in self._anchors.values() for pages in held
+                   for page in pages if page >= 0)
 
     def _give_back(self, group: CacheGroup, pages: List[int]) -> int:
         if not pages:
@@ -492,8 +525,9 @@ class CacheManager:
                 assert list(row[:len(table)]) == table, "host block table out of date"
                 assert (row[len(table):] == -1).all(), "stale block table entries"
             for _, held in self._anchors.values():
-                assert len(held[index]) == len(set(held[index])), "an anchor holds a page twice"
-                for page in held[index]:
+                kept = [page for page in held[index] if page >= 0]
+                assert len(kept) == len(set(kept)), "an anchor holds a page twice"
+                for page in kept:
                     holders[page] += 1
             for _, _, held in self._parked:
                 for page in held[index]:

@@ -8,6 +8,10 @@ manager that keeps those pages alive.  It follows the reference's ``PagedPrefixC
 * keys are a namespace plus the exact token ids; an incremental FNV-1a digest per aligned
   length finds candidates (every aligned length of a published prefix is a key, so a later
   prompt may share only the first pages of it), a full comparison of the tokens confirms a hit;
+  when the cache has a group with a window, an anchor holds only the pages that window reaches
+  from the END of the prefix, so only the prefix's full length is a key: a later prompt that
+  goes on from it (the next turn of a conversation) shares it, one that departs earlier
+  does not;
 * a request reuses at most ``floor((P - 1) / page) * page`` tokens of a prompt of ``P``
   tokens: keys and values are cached, logits are not, so at least one prompt token must run;
 * a prefix is published when the request's LAST prompt portion has succeeded, and only its
@@ -56,6 +60,7 @@ class PrefixEntry:
     namespace: str
     tokens: Tuple[int, ...]
     pages: int
+    keys: Tuple[Tuple[str, int, int], ...] = ()
     hits: int = 0
 
 
@@ -71,7 +76,7 @@ class PrefixIndex:
         if maximum_entries <= 0:
             raise ValueError("maximum_entries must be positive")
         if not cache.can_share:
-            raise ValueError("this cache cannot share prefixes (windows or per-request state)")
+            raise ValueError("this cache cannot share prefixes (per-request state)")
         self.cache = cache
         self.page_size = cache.page_size
         self.maximum_entries = int(maximum_entries)
@@ -85,7 +90,7 @@ class PrefixIndex:
         self._by_key: Dict[Tuple[str, int, int], List[Hashable]] = {}
         self._next_anchor = 0
         self.stats = {"lookups": 0, "hits": 0, "reused_tokens": 0, "published": 0,
-                      "evicted": 0, "evicted_under_pressure": 0}
+                      "not_kept": 0, "evicted": 0, "evicted_under_pressure": 0}
 
     def __len__(self) -> int:
         return len(self._entries)
@@ -143,13 +148,21 @@ class PrefixIndex:
                                  self.page_references + pages > self.maximum_page_references):
             self._evict_coldest()
         anchor = ("prefix", self._next_anchor)
+        try:
+            self.cache.hold(anchor, request, length)
+        except ValueError:
+            # a windowed group has given back pages the prefix's end still reads
+            self.stats["not_kept"] += 1
+            return None
         self._next_anchor += 1
-        self.cache.hold(anchor, request, length)
-        self._entries[anchor] = PrefixEntry(anchor, namespace, tokens, pages)
         # every aligned length of the prefix is a key: a later prompt may share only the
-        # first pages of it
-        for part, digest in digests:
-            self._by_key.setdefault((namespace, part, digest), []).append(anchor)
+        # first pages of it; with a windowed group only all of it can be shared
+        if self.cache.shares_whole_prefixes_only:
+            digests = digests[-1:]
+        keys = tuple((namespace, part, digest) for part, digest in digests)
+        self._entries[anchor] = PrefixEntry(anchor, namespace, tokens, pages, keys)
+        for key in keys:
+            self._by_key.setdefault(key, []).append(anchor)
         self.stats["published"] += 1
         return anchor
 
@@ -157,8 +170,7 @@ class PrefixIndex:
 
     def _evict_coldest(self) -> int:
         anchor, entry = self._entries.popitem(last=False)
-        for part, digest in aligned_digests(entry.tokens, self.page_size, len(entry.tokens)):
-            key = (entry.namespace, part, digest)
+        for key in entry.keys:
             self._by_key[key].remove(anchor)
             if not self._by_key[key]:
                 del self._by_key[key]

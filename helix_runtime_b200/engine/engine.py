@@ -194,7 +194,8 @@ class Engine:
                 raise ValueError("cache_memory_fraction leaves no room for a single page")
         self.cache = CacheManager(kv_needs, state_needs, config.page_size, num_pages,
                                   config.max_running_requests, model.max_positions, model.dtype,
-                                  device, poison=config.poison_free_pages)
+                                  device, poison=config.poison_free_pages,
+                                  window_slack_pages=1 if config.prefix_cache_entries > 0 else 0)
         self.step_function = StepFunction(model, self.cache, config.max_tokens_per_iteration,
                                           config.max_running_requests,
                                           config.attention_split_keys, config.ordered_sums)
@@ -202,14 +203,16 @@ class Engine:
             SchedulerConfig(config.max_tokens_per_iteration, config.max_running_requests,
                             config.max_prefill_chunk), config.page_size)
         self.sampler = Sampler(device, config.max_running_requests)
-        self.graphs = DecodeGraphs(self.step_function, self.sampler) if config.cuda_graphs else None
+        # a model with a part that cannot be recorded runs every step eagerly
+        self.graphs = DecodeGraphs(self.step_function, self.sampler) \
+            if config.cuda_graphs and model.graph_safe else None
         self._cached_at_finish: Dict[int, int] = {}
         self._release_later: List[int] = []
         self.prefix: Optional[PrefixIndex] = None
         if config.prefix_cache_entries > 0:
             if not self.cache.can_share:
-                raise ValueError("prefix sharing needs a cache without windows and without "
-                                 "per-request state")
+                raise ValueError("prefix sharing needs a model without per-request state: the "
+                                 "state at the end of a prefix is not kept")
             self.prefix = PrefixIndex(self.cache, config.prefix_cache_entries,
                                       config.prefix_cache_pages)
         self._matches: Dict[int, PrefixMatch] = {}      # lookups of the iteration being planned

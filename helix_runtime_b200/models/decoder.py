@@ -98,6 +98,11 @@ class DecoderModel:
         yield self.final_norm
         yield self.lm_head
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether every part may be recorded into a CUDA graph (see ``Part.graph_safe``)."""
+        return all(part.graph_safe for part in self.all_parts())
+
     def tensor_requests(self) -> List[TensorRequest]:
         requests: List[TensorRequest] = []
         seen = set()

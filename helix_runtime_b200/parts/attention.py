@@ -134,6 +134,10 @@ class PagedAttention(Mixer):
         self.w_o = Weight(o.to(device=device, dtype=dtype).contiguous())
         self.position.bind(tensors, dtype, device)
 
+    @property
+    def graph_safe(self) -> bool:
+        return self.position.graph_safe
+
     def weight_bytes(self) -> int:
         return self.w_qkv.nbytes() + self.w_o.nbytes()
 

@@ -138,6 +138,11 @@ class StepContext:
 
 
 class Part:
+    # Decode steps are recorded into CUDA graphs and replayed.  A part whose forward reads
+    # device values on the host (``.item()``, ``nonzero()``, a loop over requests) cannot be
+    # recorded: it says so here, and the engine then runs every step of its model eagerly.
+    graph_safe: bool = True
+
     def __init__(self, spec: PartSpec, hidden_size: int) -> None:
         self.spec = spec
         self.hidden_size = hidden_size

@@ -16,11 +16,12 @@ CPU = torch.device("cpu")
 PAGE = 4
 
 
-def manager(num_pages=32, max_requests=4, window=None, states=None):
+def manager(num_pages=32, max_requests=4, window=None, states=None, slack=0):
     needs = {0: KvNeed(2, 8), 1: KvNeed(2, 8)}
     if window is not None:
         needs[2] = KvNeed(2, 8, window=window)
-    return CacheManager(needs, states or {}, PAGE, num_pages, max_requests, 256, torch.float32, CPU)
+    return CacheManager(needs, states or {}, PAGE, num_pages, max_requests, 256, torch.float32, CPU,
+                        window_slack_pages=slack)
 
 
 def run_prompt(cache, request, tokens, adopt=None):
@@ -133,11 +134,114 @@ def test_equal_digests_do_not_confuse_different_prefixes(monkeypatch):
     assert index.lookup("ns", list(range(90, 99))) is None
 
 
-def test_caches_with_windows_or_state_do_not_share():
-    with pytest.raises(ValueError, match="cannot share"):
-        PrefixIndex(manager(window=6), maximum_entries=4)
+def test_caches_with_state_do_not_share():
     with pytest.raises(ValueError, match="cannot share"):
         PrefixIndex(manager(states={5: StateNeed((3,), torch.float32)}), maximum_entries=4)
+
+
+def test_with_a_window_a_prefix_is_shared_whole_or_not_at_all():
+    """A windowed group keeps, for a kept prefix, only the pages its window reaches from the
+    prefix's end.  A later prompt that goes on from the whole prefix adopts them (the full
+    group shares every page, the windowed one the last few); one that departs earlier finds
+    nothing; and the pages come back when request and entry have both gone."""
+    cache = manager(window=6, slack=1)
+    index = PrefixIndex(cache, maximum_entries=4)
+    full, windowed = cache.groups
+    prompt = list(range(100, 122))                       # 22 tokens: 5 whole pages kept
+    cache.admit("a")
+    for length in (7, 15, 22):                           # portions: the window passes pages
+        cache.extend("a", length)
+        cache.commit("a", length)
+    assert index.publish("ns", "a", prompt) is not None and index.stats["not_kept"] == 0
+    # the request at 20 tokens reads keys 15..19: pages 3 and 4 of the windowed group
+    assert cache.anchor_pages() == 5 + 2
+    pages_of_a = list(full.host_tables[cache.slot("a")][:5])
+    cache.release("a")
+    cache.check()
+    assert full.pool.pages_in_use == 5 and windowed.pool.pages_in_use == 2
+
+    follow_up = prompt[:20] + [7, 8, 9]
+    match = index.lookup("ns", follow_up)
+    assert match is not None and match.tokens == 20
+    assert index.lookup("ns", prompt[:13] + [1, 2, 3]) is None      # shares three pages only
+    assert index.lookup("ns", prompt[:20]) is None                  # one token must still run
+    run_prompt(cache, "b", follow_up, adopt=match)
+    cache.check()
+    table = list(windowed.host_tables[cache.slot("b")][:6])
+    assert table[:3] == [-1, -1, -1] and all(page >= 0 for page in table[3:6])
+    assert list(full.host_tables[cache.slot("b")][:5]) == pages_of_a
+    with pytest.raises(ValueError, match="all of an anchor or none"):
+        cache.adopt("c", match.anchor, 8)
+    # decoding on: the window passes the shared pages, the entry keeps them alive
+    for length in range(24, 40):
+        cache.extend("b", length)
+        cache.commit("b", length)
+        cache.check()
+    assert windowed.pool.pages_in_use <= 2 + 4
+    cache.release("b")
+    index.clear()
+    cache.check()
+    assert all(group.pool.pages_in_use == 0 for group in cache.groups)
+
+
+def test_a_prefix_whose_window_pages_are_gone_is_not_kept():
+    """Without the page of slack a windowed group may have given back a page that the end of
+    the aligned prefix still reads; then nothing is kept and nothing is lost."""
+    cache = manager(window=6, slack=0)
+    index = PrefixIndex(cache, maximum_entries=4)
+    prompt = list(range(50, 73))                         # 23 tokens; aligned prefix 20
+    run_prompt(cache, "a", prompt)                       # at 23 the window starts at key 18
+    assert index.publish("ns", "a", prompt) is None      # the prefix's end reads key 15
+    assert index.stats["not_kept"] == 1 and len(index) == 0 and cache.anchor_pages() == 0
+    cache.release("a")
+    cache.check()
+    assert all(group.pool.pages_in_use == 0 for group in cache.groups)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_traffic_with_a_window_never_loses_a_page(seed):
+    rng = np.random.default_rng(seed)
+    cache = manager(num_pages=48, max_requests=4, window=int(rng.integers(3, 14)), slack=1)
+    index = PrefixIndex(cache, maximum_entries=4, maximum_page_references=24)
+    stem = list(rng.integers(0, 50, size=40))
+    live, kept = {}, 0
+    for step in range(300):
+        action = rng.integers(0, 4)
+        if action <= 1 and len(live) < 4:
+            # prompts that go on from an aligned cut of the stem: what an earlier one left
+            # behind is a whole prefix of a later, longer one
+            cut = int(rng.integers(1, 10)) * PAGE
+            prompt = stem[:cut] + list(rng.integers(50, 60, size=int(rng.integers(1, 6))))
+            name = f"r{step}"
+            match = index.lookup("ns", prompt)
+            if min(group.pool.free_pages for group in cache.groups) < -(-len(prompt) // PAGE):
+                continue
+            if match is None:
+                cache.admit(name)
+            else:
+                cache.adopt(name, match.anchor, match.tokens)
+                assert tuple(prompt[:match.tokens]) == index._entries[match.anchor].tokens
+                kept += 1
+            at = cache.length(name)
+            while at < len(prompt):                      # portions of changing size
+                at = min(len(prompt), at + int(rng.integers(1, 9)))
+                cache.extend(name, at)
+                cache.commit(name, at)
+            live[name] = prompt
+            index.publish("ns", name, prompt)
+        elif action == 2 and live:
+            name = list(live)[int(rng.integers(0, len(live)))]
+            cache.release(name)
+            del live[name]
+        elif action == 3:
+            index.evict_for_pressure()
+        cache.check()
+    assert kept > 0 and index.stats["not_kept"] == 0
+    for name in live:
+        cache.release(name)
+    index.clear()
+    cache.check()
+    assert all(group.pool.pages_in_use == 0 for group in cache.groups)
 
 
 def test_random_traffic_never_loses_or_double_frees_a_page():

@@ -67,7 +67,11 @@ class LearnedQueryKeyBias(PositionEncoding):
 
 
 class RoutedMlp(FeedForward):
-    """Router logits in float32, softmax, the best expert only, weighted by its probability."""
+    """Router logits in float32, softmax, the best expert only, weighted by its probability.
+    It asks the device which rows chose an expert (``nonzero``), so it cannot be recorded
+    into a CUDA graph and says so; the engine then runs this model's steps eagerly."""
+
+    graph_safe = False
 
     def __init__(self, spec: PartSpec, hidden_size: int) -> None:
         super().__init__(spec, hidden_size)
@@ -238,3 +242,46 @@ def test_routing_a_learned_position_encoding_and_a_window_step_like_their_plain_
     harness.end("b")
     harness.cache.check()
     del router
+
+
+def test_the_next_turn_of_a_conversation_adopts_its_prefix_across_a_windowed_group(tmp_path):
+    """Prefix sharing with two cache groups, one of them windowed: the second prompt goes on
+    from the first prompt and its answer, finds the first prompt's aligned prefix in the index
+    and adopts it (every page of the full group, the window's last pages of the windowed one;
+    free pages are poisoned, so a key read from a page the window gave back would show).
+    Same tokens as an engine without the index, and as the plain form."""
+    from helix_runtime_b200 import Engine
+    folder = str(tmp_path / "toy_routed")
+    write_random_model(folder, ToyRoutedConfig(), seed=5, std=0.15, scale_std=0.3,
+                       storage_dtype="float32")
+    checkpoint = Checkpoint(folder)
+    tensors = {name: checkpoint.read(name) for name in checkpoint.names()}
+
+    def conversation(engine):
+        first = random_tokens(VOCAB, 18, seed=21)
+        one = engine.generate([first], max_new_tokens=5)[0]
+        second = first + one.generated_tokens + random_tokens(VOCAB, 6, seed=22)
+        two = engine.generate([second], max_new_tokens=5)[0]
+        return second, one, two
+
+    options = dict(dtype="float32", page_size=4, num_pages=30, max_running_requests=2,
+                   max_tokens_per_iteration=64, poison_free_pages=True)
+    sharing = Engine.from_pretrained(folder, prefix_cache_entries=4, **options)
+    alone = Engine.from_pretrained(folder, **options)
+    assert not sharing.model.graph_safe and sharing.graphs is None      # the routed part's word
+    second, one, two = conversation(sharing)
+    _, one_alone, two_alone = conversation(alone)
+    assert one.generated_tokens == one_alone.generated_tokens
+    assert two.generated_tokens == two_alone.generated_tokens
+    logits = plain_toy(tensors, second + two.generated_tokens[:-1])
+    for index, token in enumerate(two.generated_tokens):
+        row = logits[len(second) + index - 1]
+        assert row[token] >= row.max() - 1e-4, f"token {index}"
+    stats = sharing.stats()["prefix"]
+    assert stats["hits"] == 1 and stats["reused_tokens"] == 16 and stats["not_kept"] == 0
+    assert sharing.request(two.request_id).reused_tokens == 16
+    assert alone.request(two_alone.request_id).reused_tokens == 0
+    sharing.cache.check()
+    sharing.prefix.clear()
+    sharing.cache.check()
+    assert all(group.pool.pages_in_use == 0 for group in sharing.cache.groups)
