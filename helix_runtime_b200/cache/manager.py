@@ -105,6 +105,18 @@ class RequestCache:
     reserved: int = 0                                # tokens the tables have pages for
     tables: List[List[int]] = dataclasses.field(default_factory=list)   # per group, -1 = gone
     first_live: List[int] = dataclasses.field(default_factory=list)     # per group
+    # per-request state as it stood after `kept_state_length` tokens: copies, one per entry
+    kept_state_length: int = -1
+    kept_state: Optional[Dict[int, torch.Tensor]] = None
+
+
+@dataclasses.dataclass
+class Anchor:
+    """Pages (per group, by page index; -1 where a window had passed) and, for models with
+    per-request state, the state at the end of a prefix of ``tokens`` tokens."""
+    tokens: int
+    pages: List[List[int]]
+    state: Optional[Dict[int, torch.Tensor]] = None
 
 
 class CacheManager:
@@ -144,7 +156,7 @@ class CacheManager:
         self._free_slots: Deque[int] = deque(range(self.max_requests))
         self._requests: Dict[Hashable, RequestCache] = {}
         # page lists held without a request (published prefixes): per anchor, per group
-        self._anchors: Dict[Hashable, Tuple[int, List[List[int]]]] = {}
+        self._anchors: Dict[Hashable, Anchor] = {}
         # what was given up while a step still used it: (step, slot or None, pages per group),
         # oldest first
         self._parked: Deque[Tuple[int, Optional[int], List[List[int]]]] = deque()
@@ -394,9 +406,23 @@ class CacheManager:
             shared.append([-1] * first + list(parent.tables[index][first:count]))
         return shared
 
-    def _admit_with(self, request: Hashable, tokens: int, shared: List[List[int]]) -> int:
+    def _state_at(self, parent: RequestCache, tokens: int) -> Optional[Dict[int, torch.Tensor]]:
+        """The kept state of ``parent`` if it is the state after exactly ``tokens`` tokens."""
+        if not self.states:
+            return None
+        if parent.kept_state is None or parent.kept_state_length != tokens:
+            raise ValueError(f"no state was kept after {tokens} tokens "
+                             f"(kept after {parent.kept_state_length})")
+        return parent.kept_state
+
+    def _admit_with(self, request: Hashable, tokens: int, shared: List[List[int]],
+                    state: Optional[Dict[int, torch.Tensor]] = None) -> int:
         slot = self.admit(request)
         record = self._requests[request]
+        if state is not None:
+            for entry, tensor in self.states.items():
+                tensor[slot].copy_(state[entry])
+            record.kept_state_length, record.kept_state = tokens, state
         count = tokens // self.page_size
         for index, group in enumerate(self.groups):
             pages = shared[index][:count]
@@ -414,15 +440,15 @@ class CacheManager:
 
         Only whole pages are shared, so nothing is ever copied on write
         (src/kv_cache/paged.cpp:535-620).  A group with a window shares the pages its window
-        still reaches from ``tokens``; they must not have been given back yet."""
+        still reaches from ``tokens``; they must not have been given back yet.  With
+        per-request state the source must have kept its state after exactly ``tokens``."""
         if tokens <= 0 or tokens % self.page_size != 0:
             raise ValueError("a shared prefix must be a positive multiple of the page size")
         parent = self._requests[source]
         if tokens > parent.length:
             raise ValueError("cannot share more than the source has published")
-        if self.states:
-            raise ValueError("requests with per-request state do not share prefixes")
-        return self._admit_with(request, tokens, self._shared_pages(parent, tokens))
+        return self._admit_with(request, tokens, self._shared_pages(parent, tokens),
+                                self._state_at(parent, tokens))
 
     # ------------------------------------------------------------------ anchors
     #
@@ -431,57 +457,69 @@ class CacheManager:
     # state slot and no block-table row: it is only a holder of pages.
 
     @property
-    def can_share(self) -> bool:
-        """Whole-page sharing needs the prefix to be in pages and nowhere else: no
-        per-request state (its value at the end of the prefix would have to be kept too)."""
-        return not self.states
-
-    @property
     def shares_whole_prefixes_only(self) -> bool:
         """With a windowed group an anchor holds the pages its window reaches from the END of
-        the prefix, so a request can adopt all of the prefix or none of it; without windows
-        any number of its leading pages."""
-        return any(group.need.window is not None for group in self.groups)
+        the prefix, and with per-request state the state at its end, so a request can adopt
+        all of the prefix or none of it; otherwise any number of its leading pages."""
+        return bool(self.states) or any(group.need.window is not None for group in self.groups)
+
+    # Per-request state is not in pages: what a later request needs of a prefix is the state
+    # as it stood at the prefix's end.  The engine copies it there (in stream order behind the
+    # step that reaches that length, before the next step changes it) and hands the copy to
+    # the request's record once the step has succeeded.
+
+    def snapshot_state(self, request: Hashable) -> Dict[int, torch.Tensor]:
+        """Copies of the request's state rows, queued on the current stream."""
+        slot = self._requests[request].slot
+        return {entry: tensor[slot].clone() for entry, tensor in self.states.items()}
+
+    def keep_state(self, request: Hashable, tokens: int, snapshot: Dict[int, torch.Tensor]) -> None:
+        """``snapshot`` is the request's state after ``tokens`` tokens."""
+        record = self._requests[request]
+        if sorted(snapshot) != sorted(self.states):
+            raise ValueError("a state snapshot has one tensor per state entry")
+        record.kept_state_length, record.kept_state = int(tokens), snapshot
 
     def hold(self, anchor: Hashable, source: Hashable, tokens: int) -> int:
         """Keep the first ``tokens`` positions (whole pages) of ``source`` under ``anchor``;
         returns the page references it now holds, summed over groups.  Raises ValueError
-        when a windowed group of the source has already given back pages it would need."""
+        when a windowed group of the source has already given back pages it would need, or
+        when the model has per-request state and none was kept after ``tokens``."""
         if anchor in self._anchors:
             raise KeyError(f"anchor {anchor!r} exists")
         if tokens <= 0 or tokens % self.page_size != 0:
             raise ValueError("a shared prefix must be a positive multiple of the page size")
-        if not self.can_share:
-            raise ValueError("this cache cannot share prefixes (per-request state)")
         parent = self._requests[source]
         if tokens > parent.length:
             raise ValueError("cannot share more than the source has published")
         held = self._shared_pages(parent, tokens)
+        state = self._state_at(parent, tokens)
         for group, pages in zip(self.groups, held):
             group.pool.share([page for page in pages if page >= 0])
-        self._anchors[anchor] = (tokens, held)
+        self._anchors[anchor] = Anchor(tokens, held, state)
         return sum(1 for pages in held for page in pages if page >= 0)
 
     def adopt(self, request: Hashable, anchor: Hashable, tokens: Optional[int] = None) -> int:
         """Admit ``request`` with the first ``tokens`` positions (default: all) of ``anchor``
         already in its cache; returns its slot."""
-        held_tokens, held = self._anchors[anchor]
-        tokens = held_tokens if tokens is None else tokens
-        if tokens <= 0 or tokens % self.page_size != 0 or tokens > held_tokens:
+        kept = self._anchors[anchor]
+        tokens = kept.tokens if tokens is None else tokens
+        if tokens <= 0 or tokens % self.page_size != 0 or tokens > kept.tokens:
             raise ValueError("a request adopts a positive number of whole pages of the anchor")
-        if tokens != held_tokens and self.shares_whole_prefixes_only:
-            raise ValueError("with a windowed group a request adopts all of an anchor or none")
-        return self._admit_with(request, tokens, held)
+        if tokens != kept.tokens and self.shares_whole_prefixes_only:
+            raise ValueError("with a windowed group or per-request state a request adopts all "
+                             "of an anchor or none")
+        return self._admit_with(request, tokens, kept.pages, kept.state)
 
     def drop(self, anchor: Hashable) -> int:
         """Forget the anchor; returns the pages that became free."""
-        _, held = self._anchors.pop(anchor)
+        kept = self._anchors.pop(anchor)
         return sum(self._give_back(group, [page for page in pages if page >= 0])
-                   for group, pages in zip(self.groups, held))
+                   for group, pages in zip(self.groups, kept.pages))
 
     def anchor_pages(self) -> int:
         """Pages (per group, summed) that anchors hold references to."""
-        return sum(1 for _, held in self._anchors.values() for pages in held
+        return sum(1 for kept in self._anchors.values() for pages in kept.pages
                    for page in pages if page >= 0)
 
     def _give_back(self, group: CacheGroup, pages: List[int]) -> int:
@@ -524,8 +562,8 @@ class CacheManager:
                 row = group.host_tables[record.slot]
                 assert list(row[:len(table)]) == table, "host block table out of date"
                 assert (row[len(table):] == -1).all(), "stale block table entries"
-            for _, held in self._anchors.values():
-                kept = [page for page in held[index] if page >= 0]
+            for anchor in self._anchors.values():
+                kept = [page for page in anchor.pages[index] if page >= 0]
                 assert len(kept) == len(set(kept)), "an anchor holds a page twice"
                 for page in kept:
                     holders[page] += 1

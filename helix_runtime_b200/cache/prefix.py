@@ -9,9 +9,9 @@ manager that keeps those pages alive.  It follows the reference's ``PagedPrefixC
   length finds candidates (every aligned length of a published prefix is a key, so a later
   prompt may share only the first pages of it), a full comparison of the tokens confirms a hit;
   when the cache has a group with a window, an anchor holds only the pages that window reaches
-  from the END of the prefix, so only the prefix's full length is a key: a later prompt that
-  goes on from it (the next turn of a conversation) shares it, one that departs earlier
-  does not;
+  from the END of the prefix, and when the model keeps per-request state, the state at its
+  end, so only the prefix's full length is a key: a later prompt that goes on from it (the
+  next turn of a conversation) shares it, one that departs earlier does not;
 * a request reuses at most ``floor((P - 1) / page) * page`` tokens of a prompt of ``P``
   tokens: keys and values are cached, logits are not, so at least one prompt token must run;
 * a prefix is published when the request's LAST prompt portion has succeeded, and only its
@@ -75,8 +75,6 @@ class PrefixIndex:
                  maximum_page_references: Optional[int] = None) -> None:
         if maximum_entries <= 0:
             raise ValueError("maximum_entries must be positive")
-        if not cache.can_share:
-            raise ValueError("this cache cannot share prefixes (per-request state)")
         self.cache = cache
         self.page_size = cache.page_size
         self.maximum_entries = int(maximum_entries)
@@ -151,7 +149,8 @@ class PrefixIndex:
         try:
             self.cache.hold(anchor, request, length)
         except ValueError:
-            # a windowed group has given back pages the prefix's end still reads
+            # a windowed group has given back pages the prefix's end still reads, or no
+            # state was kept at the prefix's end
             self.stats["not_kept"] += 1
             return None
         self._next_anchor += 1

@@ -11,7 +11,7 @@ from __future__ import annotations
 import dataclasses
 import os
 import time
-from typing import Dict, List, Optional, Sequence, Union
+from typing import Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 
@@ -154,6 +154,9 @@ class _Flight:
     error: Optional[str] = None
     sequence: int = 0                                 # steps are numbered as they are queued
     done: object = None                               # event behind the step's last kernel
+    # request -> (tokens, copies of its per-request state as this step leaves it)
+    kept_states: Dict[int, Tuple[int, Dict[int, torch.Tensor]]] = \
+        dataclasses.field(default_factory=dict)
 
     def __post_init__(self) -> None:
         self.result = IterationResult()
@@ -201,7 +204,11 @@ class Engine:
                                           config.attention_split_keys, config.ordered_sums)
         self.scheduler = FifoScheduler(
             SchedulerConfig(config.max_tokens_per_iteration, config.max_running_requests,
-                            config.max_prefill_chunk), config.page_size)
+                            config.max_prefill_chunk,
+                            # per-request state is kept for later requests as it stands at
+                            # the prompt's last page boundary: a portion must end there
+                            cut_prompt_at_last_page=bool(state_needs)
+                            and config.prefix_cache_entries > 0), config.page_size)
         self.sampler = Sampler(device, config.max_running_requests)
         # a model with a part that cannot be recorded runs every step eagerly
         self.graphs = DecodeGraphs(self.step_function, self.sampler) \
@@ -210,9 +217,6 @@ class Engine:
         self._release_later: List[int] = []
         self.prefix: Optional[PrefixIndex] = None
         if config.prefix_cache_entries > 0:
-            if not self.cache.can_share:
-                raise ValueError("prefix sharing needs a model without per-request state: the "
-                                 "state at the end of a prefix is not kept")
             self.prefix = PrefixIndex(self.cache, config.prefix_cache_entries,
                                       config.prefix_cache_pages)
         self._matches: Dict[int, PrefixMatch] = {}      # lookups of the iteration being planned
@@ -407,6 +411,7 @@ class Engine:
                 else:
                     self.model.forward(flight.ctx, self.cache, want_rows, 0)
                 self.sampler.fetch(flight.slot, tokens, step.status)
+                self._copy_states_at_prefix_ends(flight)
                 flight.done = torch.cuda.Event()
                 flight.done.record()
             except Exception:
@@ -417,6 +422,22 @@ class Engine:
         except StepError as error:
             flight.error = str(error)
         return flight
+
+    def _copy_states_at_prefix_ends(self, flight: "_Flight") -> None:
+        """A model with per-request state and the prefix index on: a prompt portion that ends
+        at the prompt's last page boundary (the scheduler cuts one there) leaves the state
+        that a later request must start from when it adopts that prefix.  It is copied here,
+        on the stream, right behind the step and before the next one changes it."""
+        if self.prefix is None or not self.cache.states:
+            return
+        page = self.config.page_size
+        for work in flight.batch.work:
+            request = self.scheduler.request(work.request_id)
+            boundary = len(request.prompt) // page * page
+            if (work.kind is WorkKind.PREFILL and request.namespace is not None and boundary > 0
+                    and work.token_offset + work.token_count == boundary):
+                flight.kept_states[work.request_id] = (
+                    boundary, self.cache.snapshot_state(work.request_id))
 
     def _complete(self, flight: "_Flight") -> IterationResult:
         """Wait for the step's results and apply them."""
@@ -436,6 +457,9 @@ class Engine:
                     self._flight.error = flight.error
         if flight.error is None:
             step.finish(entries, flight.new_lengths, flight.ctx)
+            for request_id, (tokens, snapshot) in flight.kept_states.items():
+                if self.cache.has(request_id):
+                    self.cache.keep_state(request_id, tokens, snapshot)
             if self.prefix is not None:
                 # a request whose LAST prompt portion has just succeeded leaves its longest
                 # aligned prefix to later requests (src/runtime/cpu_engine.cpp:136-160)

@@ -158,6 +158,10 @@ class SchedulerConfig:
     max_tokens_per_iteration: int
     max_running_requests: int
     max_prefill_chunk: Optional[int] = None
+    # A prompt portion never runs across the prompt's last page boundary, so that some step
+    # ends exactly there: what a model keeps per request beside its pages can then be copied
+    # as it stands at the end of the prompt's longest page-aligned prefix.
+    cut_prompt_at_last_page: bool = False
 
     def __post_init__(self) -> None:
         if self.max_tokens_per_iteration <= 0 or self.max_running_requests <= 0:
@@ -341,6 +345,10 @@ class FifoScheduler:
             assert desired > 0, "an active request always has something to feed"
             if prefill and self.config.max_prefill_chunk is not None:
                 desired = min(desired, self.config.max_prefill_chunk)
+            if prefill and self.config.cut_prompt_at_last_page:
+                boundary = len(request.prompt) // self.page_size * self.page_size
+                if start < boundary < start + desired:
+                    desired = boundary - start
             budgeted = min(desired, remaining_tokens)
             if waiting:
                 granted = ledger.max_extend_new(budgeted, available)

@@ -134,9 +134,45 @@ def test_equal_digests_do_not_confuse_different_prefixes(monkeypatch):
     assert index.lookup("ns", list(range(90, 99))) is None
 
 
-def test_caches_with_state_do_not_share():
-    with pytest.raises(ValueError, match="cannot share"):
-        PrefixIndex(manager(states={5: StateNeed((3,), torch.float32)}), maximum_entries=4)
+def test_with_per_request_state_a_prefix_is_shared_with_the_state_at_its_end():
+    """What a model keeps per request beside its pages belongs to a kept prefix as it stood
+    at the prefix's end: the request's record is given a copy at that length, the anchor
+    takes it over, and a request that adopts the whole prefix starts from it.  Without a
+    copy at exactly that length nothing is kept."""
+    cache = manager(states={5: StateNeed((3,), torch.float32)})
+    index = PrefixIndex(cache, maximum_entries=4)
+    prompt = list(range(30, 41))                         # 11 tokens: the prefix is 8
+    cache.admit("a")
+    cache.extend("a", 8)
+    cache.commit("a", 8)
+    cache.state(5)[cache.slot("a")] = torch.tensor([1.0, 2.0, 3.0])      # the state after 8
+    cache.keep_state("a", 8, cache.snapshot_state("a"))
+    cache.extend("a", 11)
+    cache.commit("a", 11)
+    cache.state(5)[cache.slot("a")] = torch.tensor([9.0, 9.0, 9.0])      # it has moved on
+    assert index.publish("ns", "a", prompt) is not None
+    cache.release("a")
+
+    match = index.lookup("ns", prompt[:8] + [1, 2])
+    assert match is not None and match.tokens == 8
+    assert index.lookup("ns", prompt[:4] + [1, 2]) is None               # whole or not at all
+    cache.adopt("b", match.anchor, match.tokens)
+    assert cache.state(5)[cache.slot("b")].tolist() == [1.0, 2.0, 3.0]
+    assert cache.length("b") == 8
+    # b goes on and publishes its own, longer prompt: it needs a copy at ITS boundary
+    longer = prompt[:8] + list(range(60, 70))            # 18 tokens: the prefix is 16
+    cache.extend("b", 18)
+    cache.commit("b", 18)
+    assert index.publish("ns", "b", longer) is None and index.stats["not_kept"] == 1
+    cache.release("b")
+    cache.check()
+    # a fresh request: the slot is cleared, nothing of b's state is left in it
+    cache.admit("c")
+    assert cache.state(5)[cache.slot("c")].tolist() == [0.0, 0.0, 0.0]
+    cache.release("c")
+    index.clear()
+    cache.check()
+    assert all(group.pool.pages_in_use == 0 for group in cache.groups)
 
 
 def test_with_a_window_a_prefix_is_shared_whole_or_not_at_all():

@@ -109,6 +109,33 @@ def test_prefill_chunk_knob_mixes_portions_with_decode_tokens():
     assert summary(batch) == [(a, WorkKind.DECODE, 5, 1, True), (b, WorkKind.PREFILL, 8, 2, True)]
 
 
+def test_a_portion_may_be_made_to_end_at_the_prompts_last_page_boundary():
+    """For models that keep state beside their pages: some step ends exactly where the
+    prompt's longest page-aligned prefix ends (pages of 4: 8 of 11 tokens), whatever the
+    budget and the chunk size would have cut; a prompt that ends on a boundary, or that is
+    shorter than a page, is not cut."""
+    rig = Rig(max_tokens=64, max_running=3, num_pages=32)
+    rig.scheduler = FifoScheduler(SchedulerConfig(64, 3, None, cut_prompt_at_last_page=True), 4)
+    a = rig.scheduler.submit([1] * 11, 2)
+    b = rig.scheduler.submit([2] * 8, 2)
+    c = rig.scheduler.submit([3] * 3, 2)
+    batch, _ = rig.step()
+    assert summary(batch) == [(a, WorkKind.PREFILL, 0, 8, False), (b, WorkKind.PREFILL, 0, 8, True),
+                              (c, WorkKind.PREFILL, 0, 3, True)]
+    batch, _ = rig.step()
+    assert summary(batch)[0] == (a, WorkKind.PREFILL, 8, 3, True)
+    rig.drain()
+    # with a chunk of 5 the boundary at 8 is met by cutting the second chunk short
+    rig = Rig(max_tokens=64, max_running=3, num_pages=32)
+    rig.scheduler = FifoScheduler(SchedulerConfig(64, 3, 5, cut_prompt_at_last_page=True), 4)
+    a = rig.scheduler.submit([1] * 11, 2)
+    cuts = []
+    while rig.scheduler.request(a).state is not RequestState.DECODING:
+        batch, _ = rig.step()
+        cuts.append(summary(batch)[0][2:4])
+    assert cuts == [(0, 5), (5, 3), (8, 3)]
+
+
 def test_eos_ends_a_request_and_the_token_is_emitted():
     rig = Rig(token=lambda request: 9 if len(request.generated) == 2 else 7)
     rid = rig.scheduler.submit([1, 2], max_new_tokens=10, eos_token=9)

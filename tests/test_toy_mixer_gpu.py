@@ -231,3 +231,51 @@ def test_state_of_a_mixer_survives_graph_replay(tmp_path, cuda_graphs):
             row = logits[len(prompt) + index - 1]
             assert row[token] >= row.max() - 1e-4, f"token {index}"
     engine.cache.check()
+
+
+@pytest.mark.parametrize("cuda_graphs", [False, True])
+def test_the_next_turn_of_a_conversation_starts_from_the_kept_state(tmp_path, cuda_graphs):
+    """Prefix sharing for a model with per-request state.  The scheduler ends a prompt portion
+    at the prompt's last page boundary, the engine copies the mixers' state as that step
+    leaves it, and the prefix index keeps the copy with the pages; the next turn (the first
+    prompt, its answer and more) adopts pages AND state and computes only what is new.  Its
+    tokens equal the plain form's, which knows nothing of any of this."""
+    from helix_runtime_b200 import Engine
+    from helix_runtime_b200.weights import Checkpoint
+    folder = str(tmp_path / "toy")
+    write_random_model(folder, ToyConfig(), seed=3, std=0.08, scale_std=0.2,
+                       storage_dtype="float32")
+    checkpoint = Checkpoint(folder)
+    tensors = {name: checkpoint.read(name) for name in checkpoint.names()}
+    engine = Engine.from_pretrained(folder, dtype="float32", page_size=4, max_running_requests=3,
+                                    max_tokens_per_iteration=16, max_prefill_chunk=7,
+                                    cuda_graphs=cuda_graphs, prefix_cache_entries=4,
+                                    poison_free_pages=True)
+
+    def check(prompt, result):
+        logits = plain_toy(tensors, prompt + result.generated_tokens[:-1])
+        for index, token in enumerate(result.generated_tokens):
+            row = logits[len(prompt) + index - 1]
+            assert row[token] >= row.max() - 1e-4, f"token {index}"
+
+    first = random_tokens(VOCAB, 14, seed=31)            # its prefix: 12 tokens
+    one = engine.generate([first], max_new_tokens=6)[0]
+    check(first, one)
+    second = first + one.generated_tokens + random_tokens(VOCAB, 5, seed=32)      # 25 tokens
+    other = random_tokens(VOCAB, 9, seed=33)             # runs beside it, shares nothing
+    two, beside = engine.generate([second, other], max_new_tokens=8)
+    check(second, two)
+    check(other, beside)
+    assert engine.request(two.request_id).reused_tokens == 12
+    assert engine.request(beside.request_id).reused_tokens == 0
+    stats = engine.stats()["prefix"]
+    assert stats["hits"] == 1 and stats["not_kept"] == 0 and stats["published"] == 3
+    # the third turn goes on from the second: 24 of its tokens are there already
+    third = second + two.generated_tokens + random_tokens(VOCAB, 3, seed=34)
+    three = engine.generate([third], max_new_tokens=5)[0]
+    check(third, three)
+    assert engine.request(three.request_id).reused_tokens == 24
+    engine.cache.check()
+    engine.prefix.clear()
+    engine.cache.check()
+    assert all(group.pool.pages_in_use == 0 for group in engine.cache.groups)
