@@ -123,7 +123,8 @@ class CacheManager:
     def __init__(self, kv_needs: Mapping[int, KvNeed], state_needs: Mapping[int, StateNeed],
                  page_size: int, num_pages: int, max_requests: int, max_positions: int,
                  dtype: torch.dtype, device: torch.device, poison: bool = False,
-                 window_slack_pages: int = 0) -> None:
+                 window_slack_pages: int = 0,
+                 window_pages: Optional[Mapping[int, int]] = None) -> None:
         if page_size <= 0 or max_requests <= 0 or max_positions <= 0:
             raise ValueError("page_size, max_requests and max_positions must be positive")
         if window_slack_pages < 0:
@@ -144,8 +145,19 @@ class CacheManager:
         by_need: Dict[KvNeed, List[int]] = {}
         for entry in sorted(kv_needs):
             by_need.setdefault(kv_needs[entry], []).append(entry)
+        # ``num_pages`` is every group's pool unless ``window_pages`` gives the groups of a
+        # window (by its length) a pool of their own size: a request never holds more of such
+        # a group than its window, the page being filled and the portion it is fed.
+        window_pages = dict(window_pages or {})
+        unknown = set(window_pages) - {need.window for need in by_need}
+        if unknown:
+            raise ValueError(f"window_pages names windows no layer has: {sorted(unknown)}")
         for need, entries in by_need.items():
-            group = CacheGroup(len(self.groups), need, entries, num_pages, self.page_size,
+            pages = window_pages.get(need.window, num_pages) if need.window is not None \
+                else num_pages
+            if pages <= 0:
+                raise ValueError("a pool needs at least one page")
+            group = CacheGroup(len(self.groups), need, entries, pages, self.page_size,
                                self.max_requests, self.max_pages_per_request, dtype, device, poison)
             for layer, entry in enumerate(entries):
                 self._entry_place[entry] = (group.index, layer)

@@ -78,7 +78,11 @@ class PrefixIndex:
         self.cache = cache
         self.page_size = cache.page_size
         self.maximum_entries = int(maximum_entries)
-        smallest_pool = min(group.pool.num_pages for group in cache.groups)
+        # an entry's pages are counted as its prefix's length in pages, which is what it holds
+        # of every group that keeps all keys (a windowed group holds a few pages per entry)
+        pools = [group.pool.num_pages for group in cache.groups if group.need.window is None] \
+            or [group.pool.num_pages for group in cache.groups]
+        smallest_pool = min(pools)
         self.maximum_page_references = int(maximum_page_references
                                            if maximum_page_references is not None
                                            else smallest_pool // 2)

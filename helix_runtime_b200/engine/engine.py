@@ -112,6 +112,8 @@ def write_random_model(directory: str, config, seed: int, std: float = 0.02,
 class EngineConfig:
     page_size: int = 16
     num_pages: Optional[int] = None           # default: enough for max_running * max positions
+    window_pages: Optional[Dict[int, int]] = None   # window length -> pages of the groups with
+                                              # that window (default: num_pages, like the rest)
     cache_memory_fraction: Optional[float] = None   # instead of num_pages: this share of the
                                               # device memory that is free once the weights are
                                               # loaded goes to the cache pool
@@ -189,16 +191,24 @@ class Engine:
             if not 0.0 < config.cache_memory_fraction <= 1.0:
                 raise ValueError("cache_memory_fraction must be in (0, 1]")
             element = torch.empty((), dtype=model.dtype).element_size()
-            page_bytes = sum(2 * need.kv_heads * need.head_dim * element * config.page_size
-                             for need in kv_needs.values())
+            fixed = dict(config.window_pages or {})      # pools whose size is given
+            page_bytes = fixed_bytes = 0
+            for need in kv_needs.values():
+                layer_page = 2 * need.kv_heads * need.head_dim * element * config.page_size
+                if need.window is not None and need.window in fixed:
+                    fixed_bytes += layer_page * fixed[need.window]
+                else:
+                    page_bytes += layer_page
             free_bytes, _ = torch.cuda.mem_get_info(device)
-            num_pages = int(free_bytes * config.cache_memory_fraction) // max(page_bytes, 1)
+            num_pages = (int(free_bytes * config.cache_memory_fraction) - fixed_bytes) \
+                // max(page_bytes, 1)
             if num_pages < 1:
                 raise ValueError("cache_memory_fraction leaves no room for a single page")
         self.cache = CacheManager(kv_needs, state_needs, config.page_size, num_pages,
                                   config.max_running_requests, model.max_positions, model.dtype,
                                   device, poison=config.poison_free_pages,
-                                  window_slack_pages=1 if config.prefix_cache_entries > 0 else 0)
+                                  window_slack_pages=1 if config.prefix_cache_entries > 0 else 0,
+                                  window_pages=config.window_pages)
         self.step_function = StepFunction(model, self.cache, config.max_tokens_per_iteration,
                                           config.max_running_requests,
                                           config.attention_split_keys, config.ordered_sums)

@@ -182,6 +182,34 @@ def test_poisoned_pages_are_nan_when_free():
     assert torch.isnan(cache.groups[0].storage[:, :, page]).all()
 
 
+def test_groups_with_a_window_may_have_a_pool_of_their_own_size():
+    """Two full-attention layers with 12 pages and two windowed layers with 4: a request of 40
+    positions holds ten pages of the one and never more than three of the other."""
+    needs = {0: KvNeed(2, 8), 1: KvNeed(2, 8), 2: KvNeed(2, 8, window=6), 3: KvNeed(2, 8, window=6)}
+    cache = CacheManager(needs, {}, 4, 12, 2, 64, torch.float32, torch.device("cpu"),
+                         window_pages={6: 4})
+    full, windowed = cache.groups
+    assert (full.pool.num_pages, windowed.pool.num_pages) == (12, 4)
+    assert full.storage.shape[2] == 12 and windowed.storage.shape[2] == 4
+    assert cache.free_pages() == [12, 4]
+    cache.admit("a")
+    # the small pool limits the portion: 16 tokens of pages at most at once
+    assert cache.max_extend("a", 40) == 16
+    length = 0
+    while length < 40:
+        length += cache.max_extend("a", min(5, 40 - length))
+        cache.extend("a", length)
+        cache.commit("a", length)
+        cache.check()
+        assert windowed.pool.pages_in_use <= 3
+    assert full.pool.pages_in_use == 10
+    cache.release("a")
+    cache.check()
+    with pytest.raises(ValueError, match="no layer has"):
+        CacheManager(needs, {}, 4, 12, 2, 64, torch.float32, torch.device("cpu"),
+                     window_pages={7: 4})
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_orders_of_requests_never_lose_a_page(seed):
     rng = np.random.default_rng(seed)

@@ -266,7 +266,11 @@ def test_the_next_turn_of_a_conversation_adopts_its_prefix_across_a_windowed_gro
 
     options = dict(dtype="float32", page_size=4, num_pages=30, max_running_requests=2,
                    max_tokens_per_iteration=64, poison_free_pages=True)
-    sharing = Engine.from_pretrained(folder, prefix_cache_entries=4, **options)
+    # the windowed layers get a pool of their own size: a window of 6 and pages of 4 are four
+    # pages a request with a page of slack, times two requests, and two for the kept prefixes
+    sharing = Engine.from_pretrained(folder, prefix_cache_entries=4, window_pages={WINDOW: 12},
+                                     **options)
+    assert sorted(group.pool.num_pages for group in sharing.cache.groups) == [12, 30]
     alone = Engine.from_pretrained(folder, **options)
     assert not sharing.model.graph_safe and sharing.graphs is None      # the routed part's word
     second, one, two = conversation(sharing)
