@@ -254,7 +254,9 @@ def profile_region(options, model, config, fresh, rng) -> int:
 def timeline_region(options, model, config, fresh, rng) -> int:
     """The kernels of the step as they run in place (``--timeline decode``: four decode steps of
     ``--batch`` requests through the engine, CUDA graphs and early launches as in serving;
-    ``--timeline prefill``: one step of ``--prompt-len`` tokens), recorded with CUPTI through
+    ``--timeline prefill``: one step of ``--prompt-len`` tokens; ``--timeline mixed``: one step
+    of four 512-token prompt portions at contexts 0 to 1,536 beside ``--batch`` decode tokens
+    at a context of ``--prompt-len``), recorded with CUPTI through
     ``torch.profiler``: launches, mean duration and mean EXCLUSIVE time per kernel (the part of
     a kernel after every earlier kernel has ended: a kernel that was let in early spends the
     rest of its duration waiting for its predecessor).  Unlike an ncu capture nothing is
@@ -276,6 +278,30 @@ def timeline_region(options, model, config, fresh, rng) -> int:
             cache.admit(0)
             step.run([StepEntry(0, prompt, [length - 1])], check_status=False)
             cache.release(0)
+        steps = 1
+    elif options.timeline == "mixed":
+        # a serving step: four prompt portions of 512 tokens that go on from 0, 512, 1,024 and
+        # 1,536 cached tokens, beside --batch decode tokens at a context of --prompt-len
+        contexts = (0, 512, 1024, 1536)
+        cache, step, _ = fresh(batch + len(contexts), max(length, contexts[-1] + 512) + 8,
+                               PREFILL_TOKENS + batch)
+        draw = lambda count: [int(t) for t in rng.integers(0, config.vocab_size, count)]
+        for request in range(batch + len(contexts)):
+            cache.admit(request)
+        for request in range(batch):                       # bring the decode requests to length
+            step.run([StepEntry(request, draw(length), [])], check_status=False)
+        for index, context in enumerate(contexts):
+            if context:
+                step.run([StepEntry(batch + index, draw(context), [])], check_status=False)
+
+        def run():
+            # running requests first, then the prompts: the order the scheduler gives a step
+            entries = [StepEntry(request, draw(1), [0]) for request in range(batch)]
+            entries += [StepEntry(batch + index, draw(512), [511]) for index in range(len(contexts))]
+            ctx, want_rows, n_want, _ = step.prepare(entries)
+            model.forward(ctx, cache, want_rows, n_want)
+            torch.cuda.synchronize()
+            step.fail(entries)      # nothing is published: the next run repeats the same step
         steps = 1
     else:
         engine = Engine(model, EngineConfig(page_size=PAGE_SIZE, max_running_requests=batch,
@@ -330,7 +356,7 @@ def main() -> int:
     parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
                         help="run one eager step of this kind between cudaProfilerStart/Stop "
                              "(for ncu --profile-from-start off) and print nothing else")
-    parser.add_argument("--timeline", choices=("decode", "prefill"), default=None,
+    parser.add_argument("--timeline", choices=("decode", "prefill", "mixed"), default=None,
                         help="print the kernels of the step with their times as they run in "
                              "place (CUPTI through torch.profiler) and nothing else")
     parser.add_argument("--prompt-len", type=int, default=PROMPT_LEN)

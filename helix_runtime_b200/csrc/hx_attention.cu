@@ -504,23 +504,25 @@ void paged_attention_stream_kernel(
   // count and, at the same time, the row of the block table its pages are in.
   int first_keys = 0, first_table_row = 0, first_inclusive = 0;      // of the first 32 tokens
   long long total = 0;
-  for (int base = 0; base < a.tokens; base += 32) {
-    const int token = base + lane;
-    const int keys = row_keys(a, token);
-    int table_row = 0;
-    if (base == 0 && token < a.tokens) table_row = a.request_table_row[a.token_request[token]];
-    int inclusive = (keys + KEYS - 1) / KEYS;
+  {
+    first_keys = row_keys(a, lane);
+    if (lane < a.tokens) first_table_row = a.request_table_row[a.token_request[lane]];
+    first_inclusive = (first_keys + KEYS - 1) / KEYS;
+    // the rest of the tokens (a step that mixes prompt portions with decode tokens brings
+    // thousands): every lane adds up its own, with the loads of several rounds in flight
+    int mine = first_inclusive;
+#pragma unroll 4
+    for (int token = 32 + lane; token < a.tokens; token += 32)
+      mine += (row_keys(a, token) + KEYS - 1) / KEYS;
 #pragma unroll
     for (int offset = 1; offset < 32; offset <<= 1) {
-      const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
-      if (lane >= offset) inclusive += other;
+      const int other = __shfl_up_sync(0xffffffffu, first_inclusive, offset);
+      if (lane >= offset) first_inclusive += other;
     }
-    if (base == 0) {
-      first_keys = keys;
-      first_table_row = table_row;
-      first_inclusive = inclusive;
-    }
-    total += __shfl_sync(0xffffffffu, inclusive, 31);
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+      mine += __shfl_xor_sync(0xffffffffu, mine, offset);
+    total = mine;
   }
   total *= a.heads;
   const long long per_warp = (total + n_warps - 1) / n_warps;
@@ -536,6 +538,7 @@ void paged_attention_stream_kernel(
   {
     long long before = 0;      // chunks of one head of all earlier tokens
     int found = -1;
+#pragma unroll 1
     for (int base = 0; base < a.tokens && found < 0; base += 32) {
       int keys = first_keys, inclusive = first_inclusive, table_row = first_table_row;
       if (base > 0) {
@@ -644,16 +647,19 @@ void paged_attention_stream_kernel(
   // earlier steps left, and its copies may start before the wait, while the predecessor
   // still runs.  (Let in early, a warp then finds its first chunks in shared memory when the
   // queries arrive.)
+  // (A cursor never steps past the end of the run: behind the last row of a step that mixes
+  // decode tokens with prompt portions lie thousands of tokens that are not this kernel's,
+  // and walking over them costs a chain of loads each.)
   int requested = 0;
   for (; requested < RING && requested < run; ++requested) {
     if ((ahead.chunk + 1) * KEYS > ahead.keys - a.tokens) break;
     request_chunk(requested);
-    cursor_next<KEYS>(a, ahead);
+    if (requested + 1 < run) cursor_next<KEYS>(a, ahead);
   }
   hx_pdl_wait();
   for (; requested < RING && requested < run; ++requested) {
     request_chunk(requested);
-    cursor_next<KEYS>(a, ahead);
+    if (requested + 1 < run) cursor_next<KEYS>(a, ahead);
   }
 
   // Both products put the cache on the 16-row side of the tensor-core tile, where none of it
@@ -824,7 +830,7 @@ void paged_attention_stream_kernel(
       // the slot is free: order this warp's reads before the copy engine's writes
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       request_chunk(slot);
-      cursor_next<KEYS>(a, ahead);
+      if (i + RING + 1 < run) cursor_next<KEYS>(a, ahead);
     }
 
     if (at.chunk == at.n - 1 || i == run - 1) {
@@ -873,7 +879,7 @@ void paged_attention_stream_kernel(
         }
       }
     }
-    cursor_next<KEYS>(a, at);
+    if (i + 1 < run) cursor_next<KEYS>(a, at);
   }
   if (lane == 0 && any_unreadable && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
 }

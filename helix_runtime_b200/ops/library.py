@@ -147,7 +147,16 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise KernelError(f"unsupported compute dtype {dtype}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle.  Every launch asks for it, and a step has hundreds of
+    launches: the direct accessor costs a fraction of a microsecond where building a
+    ``torch.cuda.Stream`` object costs fourteen (measured: 3.6 ms of a 2,048-token step's
+    10 ms of host time)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
