@@ -107,21 +107,9 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
   const int kv_head = head / (a.heads / a.kv_heads);
 
   // which request and which 64-row tile of it is this CTA?
-  int request = -1, tile_in_request = 0;
-  {
-    int remaining = blockIdx.x;
-    for (int r = 0; r < a.requests; ++r) {
-      const int length = a.request_start[r + 1] - a.request_start[r];
-      if (length < a.min_query_len) continue;
-      const int tiles = (length + BLOCK_M - 1) / BLOCK_M;
-      if (remaining < tiles) {
-        request = r;
-        tile_in_request = remaining;
-        break;
-      }
-      remaining -= tiles;
-    }
-  }
+  int tile_in_request = 0, tiles_of_request = 0;
+  const int request = hx_find_query_tile(a.request_start, a.requests, a.min_query_len, BLOCK_M,
+                                         blockIdx.x, tile_in_request, tiles_of_request);
   if (request < 0) return;
   const int q_begin = a.request_start[request];
   const int q_len = a.request_start[request + 1] - q_begin;

@@ -126,24 +126,14 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   constexpr int kDSteps = D / 16;      // k-steps of Q K^T
   hx_pdl_trigger();
 
-  // which request and which 128-row tile of it is this CTA?
-  int request = -1, tile_in_request = 0;
-  {
-    int remaining = blockIdx.y;
-    for (int r = 0; r < a.requests; ++r) {
-      const int length = a.request_start[r + 1] - a.request_start[r];
-      if (length < a.min_query_len) continue;
-      const int tiles = (length + LANES * BLOCK_M - 1) / (LANES * BLOCK_M);
-      if (remaining < tiles) {
-        request = r;
-        // the last rows of a request see the most keys: their CTAs are started first (the grid
-        // is walked heads first, then tiles), so the short ones fill the gaps at the end
-        tile_in_request = tiles - 1 - remaining;
-        break;
-      }
-      remaining -= tiles;
-    }
-  }
+  // which request and which 256-row tile of it is this CTA?  The last rows of a request see
+  // the most keys: their CTAs are started first (the grid is walked heads first, then tiles),
+  // so the short ones fill the gaps at the end.
+  int tile_in_request = 0, tiles_of_request = 0;
+  const int request = hx_find_query_tile(a.request_start, a.requests, a.min_query_len,
+                                         LANES * BLOCK_M, blockIdx.y, tile_in_request,
+                                         tiles_of_request);
+  tile_in_request = tiles_of_request - 1 - tile_in_request;
   if (request < 0) return;      // before any barrier or allocation: the whole CTA leaves
 
   extern __shared__ uint8_t smem_raw[];

@@ -169,6 +169,43 @@ __host__ __device__ __forceinline__ size_t hx_cache_offset(int page, int kv_head
   return ((page_head * (head_dim / chunk) + dim / chunk) * page_size + slot) * chunk + dim % chunk;
 }
 
+// The requests that bring at least `min_len` tokens to a step are cut into tiles of `rows`
+// tokens, and the tiles are numbered in the order of the requests.  Which request holds tile
+// number `tile`, which of its tiles is it, and how many has it?  Every lane of a (whole,
+// converged) warp calls this and gets the same answer; -1: there is no such tile.  Thirty-two
+// requests are looked at per round: a step may bring a few prompt portions behind dozens of
+// decode tokens, and every CTA of a prompt kernel asks this before anything else.
+__device__ __forceinline__ int hx_find_query_tile(const int* request_start, int requests,
+                                                  int min_len, int rows, int tile,
+                                                  int& tile_in_request, int& tiles_of_request) {
+  const int lane = threadIdx.x & 31;
+  int before = 0;
+  for (int base = 0; base < requests; base += 32) {
+    const int r = base + lane;
+    int tiles = 0;
+    if (r < requests) {
+      const int length = request_start[r + 1] - request_start[r];
+      if (length >= min_len) tiles = (length + rows - 1) / rows;
+    }
+    int inclusive = tiles;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+      if (lane >= offset) inclusive += other;
+    }
+    const unsigned beyond = __ballot_sync(0xffffffffu, before + inclusive > tile);
+    if (beyond != 0u) {
+      const int source = __ffs(beyond) - 1;
+      tiles_of_request = __shfl_sync(0xffffffffu, tiles, source);
+      tile_in_request =
+          tile - (before + __shfl_sync(0xffffffffu, inclusive, source) - tiles_of_request);
+      return base + source;
+    }
+    before += __shfl_sync(0xffffffffu, inclusive, 31);
+  }
+  return -1;
+}
+
 // silu(x) = x * sigmoid(x) with the branch-stable sigmoid of the reference
 // (src/kernels/cuda/transformer.cu:68-83).
 __device__ __forceinline__ float hx_silu(float x) {

@@ -190,6 +190,7 @@ class StepFunction:
             host_request_slots=[int(v) for v in request_slot[:len(entries)]],
             host_request_starts=[int(v) for v in request_start[:len(entries) + 1]],
             host_request_contexts=[int(v) for v in request_context[:len(entries)]],
+            host_query_lengths=[len(entry.tokens) for entry in entries],
         )
         return ctx, self._view("want_rows", True), n_want, new_lengths
 

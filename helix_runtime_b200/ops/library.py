@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -368,6 +368,10 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         float(scale), split_keys, max_splits, _ptr(status), _stream()))
 
 
+PREFILL_TILE_ROWS = 64        # query rows of a CTA of the ``mma.sync`` prompt kernel
+PREFILL_TILE_ROWS_TC = 256    # and of the tcgen05 prompt kernel
+
+
 def prefill_attention_supports(head_dim: int, page_size: int) -> bool:
     return bool(lib().hx_prefill_attention_supports(head_dim, page_size))
 
@@ -382,10 +386,14 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       out: torch.Tensor, requests: int, tile_bound: int, heads: int,
                       kv_heads: int, head_dim: int, page_size: int, num_pages: int, scale: float,
                       min_query_len: int, status: torch.Tensor,
-                      tensor_memory: Optional[bool] = None) -> None:
+                      tensor_memory: Optional[bool] = None,
+                      query_lengths: Optional[Sequence[int]] = None) -> None:
     """Tensor-core attention (bfloat16) of every request that brings at least
     ``min_query_len`` tokens; ``tile_bound`` bounds the number of query tiles of 64 tokens
-    (the tensor-memory kernel, whose tiles hold 256 tokens, needs no more).
+    (the tensor-memory kernel, whose tiles hold 256 tokens, needs no more).  A CTA that finds
+    no tile leaves at once, but it holds an SM's shared memory while it looks, so a caller
+    that knows the requests' token counts on the host passes them (``query_lengths``) and the
+    grid is exactly the tiles there are.
     ``tensor_memory``: take the tcgen05 kernel (scores, probabilities and output in tensor
     memory; pages of at least 16 keys) or the ``mma.sync`` kernel; default: tcgen05 where it
     applies."""
@@ -395,6 +403,12 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     if tensor_memory is None:
         tensor_memory = prefill_attention_tc_supports(head_dim, page_size)
     entry = lib().hx_prefill_attention_tc if tensor_memory else lib().hx_prefill_attention
+    if query_lengths is not None:
+        rows = PREFILL_TILE_ROWS_TC if tensor_memory else PREFILL_TILE_ROWS
+        tile_bound = sum(-(-length // rows) for length in query_lengths
+                         if length >= min_query_len)
+        if tile_bound == 0:
+            return
     _check(entry(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), request_start.data_ptr(),
         request_context.data_ptr(), request_table_row.data_ptr(), block_tables.data_ptr(),

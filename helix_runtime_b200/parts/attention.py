@@ -182,7 +182,8 @@ class PagedAttention(Mixer):
                                   ctx.request_context, ctx.request_slot, cache.block_tables,
                                   context, ctx.n_requests, n // 64 + ctx.n_requests, self.heads,
                                   self.kv_heads, self.row_dim, cache.page_size, cache.num_pages,
-                                  self.scale, TENSOR_CORE_MIN_QUERY, ctx.status)
+                                  self.scale, TENSOR_CORE_MIN_QUERY, ctx.status,
+                                  query_lengths=ctx.host_query_lengths)
         if not tensor_cores or ctx.min_query_len < TENSOR_CORE_MIN_QUERY:
             longest = ctx.max_context_len if not window else min(ctx.max_context_len, window)
             split_keys = self.split_keys_for(n, longest, ctx.attention_split_keys)

@@ -135,6 +135,7 @@ class StepContext:
     host_request_slots: Optional[List[int]] = None
     host_request_starts: Optional[List[int]] = None
     host_request_contexts: Optional[List[int]] = None
+    host_query_lengths: Optional[List[int]] = None      # tokens each request brings
 
 
 class Part:

@@ -683,6 +683,24 @@ def test_tensor_core_attention_for_prompt_portions(heads, kv_heads, head_dim, pa
     assert_close(out, expected, "tensor-core attention", atol=2e-2, rtol=8e-3)
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [(4, 4, 128, 16), (6, 2, 64, 8)])
+def test_decode_tokens_between_long_prompt_portions(heads, kv_heads, head_dim, page_size):
+    """A serving step: decode tokens and short prompt tails before, between and after prompt
+    portions of hundreds of tokens (1,400 tokens in all, 45 rounds of the decode kernel's
+    search for its own); the last decode token's far key is scaled to win."""
+    rng = np.random.default_rng(17)
+    contexts = [130, 0, 999, 512, 40, 77, 64, 301]
+    new_tokens = [1, 600, 1, 512, 3, 1, 280, 1]
+    far = {7: 123}
+    out, expected, values, *_ = attention_case(rng, torch.bfloat16, heads, kv_heads, head_dim,
+                                               page_size, contexts, new_tokens, window=None,
+                                               split_keys=64, tensor_core_min=16, dominant=far)
+    assert_close(out, expected, "attention", atol=2e-2, rtol=8e-3)
+    if heads == kv_heads:       # (the key is aimed at one query head of each key head)
+        assert_close(out[-1:], values[7][:, far[7]].reshape(1, -1), "far key's value",
+                     atol=2e-2, rtol=1e-2)
+
+
 @pytest.mark.parametrize("tensor_memory", [False, True])
 @pytest.mark.parametrize("key_position", [0, 63, 64, 200, 299])
 def test_tensor_core_attention_sees_one_far_key(key_position, tensor_memory):
