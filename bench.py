@@ -255,7 +255,7 @@ def timeline_region(options, model, config, fresh, rng) -> int:
     """The kernels of the step as they run in place (``--timeline decode``: four decode steps of
     ``--batch`` requests through the engine, CUDA graphs and early launches as in serving;
     ``--timeline prefill``: one step of ``--prompt-len`` tokens; ``--timeline mixed``: one step
-    of four 512-token prompt portions at contexts 0 to 1,536 beside ``--batch`` decode tokens
+    of four 512-token prompt portions at contexts 1,536 to 0 beside ``--batch`` decode tokens
     at a context of ``--prompt-len``), recorded with CUPTI through
     ``torch.profiler``: launches, mean duration and mean EXCLUSIVE time per kernel (the part of
     a kernel after every earlier kernel has ended: a kernel that was let in early spends the
@@ -280,10 +280,11 @@ def timeline_region(options, model, config, fresh, rng) -> int:
             cache.release(0)
         steps = 1
     elif options.timeline == "mixed":
-        # a serving step: four prompt portions of 512 tokens that go on from 0, 512, 1,024 and
-        # 1,536 cached tokens, beside --batch decode tokens at a context of --prompt-len
-        contexts = (0, 512, 1024, 1536)
-        cache, step, _ = fresh(batch + len(contexts), max(length, contexts[-1] + 512) + 8,
+        # a serving step: four prompt portions of 512 tokens that go on from 1,536, 1,024, 512
+        # and 0 cached tokens (the request admitted first is furthest along), beside --batch
+        # decode tokens at a context of --prompt-len
+        contexts = (1536, 1024, 512, 0)
+        cache, step, _ = fresh(batch + len(contexts), max(length, max(contexts) + 512) + 8,
                                PREFILL_TOKENS + batch)
         draw = lambda count: [int(t) for t in rng.integers(0, config.vocab_size, count)]
         for request in range(batch + len(contexts)):
