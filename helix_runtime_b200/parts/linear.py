@@ -21,7 +21,11 @@ import torch
 
 from ..ops import library as ops
 
-STREAMING_MAX_TOKENS = 64      # at most this many tokens: the product is a weight stream
+# At most this many tokens: the product is a weight stream.  (Measured on whole steps of the
+# Llama-2-7B sizes: a prompt portion of 65, 96 and 128 tokens takes 4.5, 4.8 and 5.1 ms this
+# way against 5.4, 5.6 and 5.8 ms through the tiles of the prompt kernel, of which so few
+# tokens make fewer than there are SMs; from 192 tokens on the prompt kernel wins.)
+STREAMING_MAX_TOKENS = 128
 UNITS_FEW_TOKENS = 4.0         # units a weight stream is cut into, per SM (two CTAs share one),
 UNITS_MANY_TOKENS = 1.5        # with at most 16 tokens, and with more
 MIN_K_BLOCKS = 8               # 64-wide reduction blocks per unit, at least
