@@ -509,9 +509,23 @@ __global__ void rope_append_pieces_kernel(
     // pairs (2p, 2p + 1): this piece holds pairs d0 / 2 .. d0 / 2 + 3
     float x[8];
     load(d0, x);
-    const float4 c = *reinterpret_cast<const float4*>(cos_row + d0 / 2);
-    const float4 sn = *reinterpret_cast<const float4*>(sin_row + d0 / 2);
-    const float cs[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+    float cs[4], ss[4];
+    if (rotary_dim % 8 == 0) {
+      // the table's rows are whole 16-byte runs of four angles
+      const float4 c = *reinterpret_cast<const float4*>(cos_row + d0 / 2);
+      const float4 sn = *reinterpret_cast<const float4*>(sin_row + d0 / 2);
+      cs[0] = c.x; cs[1] = c.y; cs[2] = c.z; cs[3] = c.w;
+      ss[0] = sn.x; ss[1] = sn.y; ss[2] = sn.z; ss[3] = sn.w;
+    } else {
+      // a rotary part that ends inside a piece (100 of 112 coordinates): the pairs behind
+      // its end turn by nothing
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool turns = d0 + 2 * i < rotary_dim;
+        cs[i] = turns ? cos_row[d0 / 2 + i] : 1.0f;
+        ss[i] = turns ? sin_row[d0 / 2 + i] : 0.0f;
+      }
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float a = x[2 * i], b = x[2 * i + 1];
@@ -569,7 +583,7 @@ HX_API int hx_rope_append(void* qkv, int dtype, int ld, const int* positions,
   const int half = rotary_dim / 2;
   const bool whole_pieces =
       dtype == HX_BF16 && head_dim % 8 == 0 && ld % 8 == 0 && (accum == nullptr || ld_accum % 4 == 0) &&
-      (pairing == 0 ? rotary_dim % 8 == 0 : half % 8 == 0);
+      (pairing == 0 || half % 8 == 0);
   if (whole_pieces) {
     const int items = (heads + 2 * kv_heads) * (head_dim / 8);
     const int block = items >= 256 ? 256 : ((items + 31) / 32) * 32;

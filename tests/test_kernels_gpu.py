@@ -265,7 +265,9 @@ def rope_reference(x, positions, theta, rotary_dim, pairing):
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim,pairing", [
     (4, 4, 16, 16, "adjacent"), (6, 2, 24, 24, "half_split"), (3, 1, 32, 16, "adjacent"),
     (5, 5, 100, 100, "adjacent"), (2, 2, 48, 32, "half_split"),
-    (12, 12, 128, 128, "adjacent"), (48, 8, 64, 64, "adjacent"), (20, 10, 96, 64, "adjacent")])
+    (12, 12, 128, 128, "adjacent"), (48, 8, 64, 64, "adjacent"), (20, 10, 96, 64, "adjacent"),
+    # a rotary part that ends inside a 16-byte piece of the head (100 of 112, 20 of 40)
+    (3, 1, 112, 100, "adjacent"), (2, 2, 40, 20, "adjacent")])
 @pytest.mark.parametrize("long_portions", [False, True])
 def test_rope_and_cache_append(dtype, heads, kv_heads, head_dim, rotary_dim, pairing, long_portions):
     rng = np.random.default_rng(6)
