@@ -343,6 +343,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         uint4 low[8], high[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
+          if (piece0 + i >= D / 8) continue;      // (a head of 112: fourteen pieces)
           asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                        : "=r"(low[i].x), "=r"(low[i].y), "=r"(low[i].z), "=r"(low[i].w)
                        : "r"(source + source_low + (piece0 + i) * piece_stride));
@@ -352,6 +353,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
+          if (piece0 + i >= D / 8) continue;
           asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(
                            target + (piece0 + i) * (BLOCK_N * 16)),
                        "r"(low[i].x), "r"(low[i].y), "r"(low[i].z), "r"(low[i].w) : "memory");
@@ -527,17 +529,18 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         tc_fence_after();
 #pragma unroll
         for (int d0 = 0; d0 < D; d0 += 32) {
+          const bool both = d0 + 16 < D;      // (compile time: D is a multiple of 16)
           uint32_t r0[16], r1[16];
           tmem_load16_issue(output_base + d0, r0);
-          tmem_load16_issue(output_base + d0 + 16, r1);
+          if (both) tmem_load16_issue(output_base + d0 + 16, r1);
           tmem_load_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             r0[i] = __float_as_uint(__uint_as_float(r0[i]) * correction);
-            r1[i] = __float_as_uint(__uint_as_float(r1[i]) * correction);
+            if (both) r1[i] = __float_as_uint(__uint_as_float(r1[i]) * correction);
           }
           tmem_store16_raw(output_base + d0, r0);
-          tmem_store16_raw(output_base + d0 + 16, r1);
+          if (both) tmem_store16_raw(output_base + d0 + 16, r1);
         }
       }
       float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -607,13 +610,14 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
                              static_cast<size_t>(head) * D;
 #pragma unroll
         for (int d0 = 0; d0 < D; d0 += 32) {
+          const bool both = d0 + 16 < D;
           uint32_t r[2][16];
           tmem_load16_issue(output_base + d0, r[0]);
-          tmem_load16_issue(output_base + d0 + 16, r[1]);
+          if (both) tmem_load16_issue(output_base + d0 + 16, r[1]);
           tmem_load_wait();
           if (row < my_rows) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int h = 0; h < (both ? 2 : 1); ++h)
 #pragma unroll
               for (int d = 0; d < 16; d += 8) {
                 uint4 packed;
@@ -663,7 +667,7 @@ int launch(const TcPrefillArgs& a, int tiles, cudaStream_t stream) {
 // 1 when the tcgen05 kernel takes this head size and page size: a page is the N operand of a
 // product, so it has at least 16 keys.
 HX_API int hx_prefill_attention_tc_supports(int head_dim, int page_size) {
-  return (head_dim == 64 || head_dim == 128) &&
+  return head_dim >= 64 && head_dim <= 128 && head_dim % 16 == 0 &&
          (page_size == 16 || page_size == 32 || page_size == 64);
 }
 
@@ -678,7 +682,7 @@ HX_API int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache,
                                    int min_query_len, int* status, cudaStream_t stream) {
   HX_REQUIRE(hx_prefill_attention_tc_supports(head_dim, page_size),
              "hx_prefill_attention_tc: head_dim %d with pages of %d is not supported (head sizes "
-             "64 and 128, pages of 16, 32 or 64)", head_dim, page_size);
+             "64 to 128 in steps of 16, pages of 16, 32 or 64)", head_dim, page_size);
   HX_REQUIRE(requests >= 0 && tile_bound >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
              "hx_prefill_attention_tc: bad sizes");
   HX_REQUIRE(tile_bound <= 65535, "hx_prefill_attention_tc: too many query tiles");
@@ -695,8 +699,14 @@ HX_API int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache,
                   static_cast<const __nv_bfloat16*>(v_cache), request_start, request_context,
                   request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(out),
                   ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status};
-  const int rc = head_dim == 128 ? launch<128>(a, tile_bound, stream)
-                                 : launch<64>(a, tile_bound, stream);
+  int rc;
+  switch (head_dim) {
+    case 64: rc = launch<64>(a, tile_bound, stream); break;
+    case 80: rc = launch<80>(a, tile_bound, stream); break;
+    case 96: rc = launch<96>(a, tile_bound, stream); break;
+    case 112: rc = launch<112>(a, tile_bound, stream); break;
+    default: rc = launch<128>(a, tile_bound, stream); break;
+  }
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_prefill_attention_tc");
   return HX_OK;

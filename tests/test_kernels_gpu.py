@@ -672,7 +672,7 @@ def test_one_far_key_stands_out(dtype, key_position):
 def test_tensor_core_attention_for_prompt_portions(heads, kv_heads, head_dim, page_size,
                                                    tensor_memory):
     if tensor_memory and not ops.prefill_attention_tc_supports(head_dim, page_size):
-        pytest.skip("the tcgen05 kernel takes heads of 64 and 128 and pages of at least 16 keys")
+        pytest.skip("the tcgen05 kernel takes heads of 64 to 128 in steps of 16 and pages of at least 16 keys")
     rng = np.random.default_rng(12)
     # whole prompts (one longer than two tiles, one a single row short of a tile), continued
     # portions that start inside a page and inside a key tile, and two decode tokens that the
