@@ -128,11 +128,10 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 }
 
 // The same for widths that are a multiple of four and fit in registers: each thread keeps up
-// to four float4 of the row, so the row is read once; the weight (which no earlier kernel
-// writes) is fetched before the dependency wait.
-constexpr int RMS_VECTORS = 4;
-
-template <typename TOut>
+// to RMS_VECTORS float4 of the row (four: widths to 4,096; eight: to 8,192), so the row is
+// read once; the weight (which no earlier kernel writes) is fetched before the dependency
+// wait.
+template <typename TOut, int RMS_VECTORS>
 __global__ __launch_bounds__(256) void rmsnorm_vector_kernel(
     const float* __restrict__ x, const float* __restrict__ weight, TOut* __restrict__ y,
     const int* __restrict__ rows, int hidden, float eps) {
@@ -192,15 +191,26 @@ HX_API int hx_rmsnorm(const float* x, const float* weight, void* y, int out_dtyp
   HX_REQUIRE(n_rows >= 0 && hidden > 0, "hx_rmsnorm: bad sizes");
   HX_REQUIRE(eps > 0.0f, "hx_rmsnorm: eps must be positive");
   if (n_rows == 0) return HX_OK;
-  if (hidden % 4 == 0 && hidden <= 4 * 256 * RMS_VECTORS &&
+  if (hidden % 4 == 0 && hidden <= 4 * 256 * 8 &&
       ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) |
         reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+    const bool four = hidden <= 4 * 256 * 4;
     if (out_dtype == HX_F32) {
-      hx_launch(rmsnorm_vector_kernel<float>, n_rows, 256, 0, stream, x, weight,
-                static_cast<float*>(y), rows, hidden, eps);
+      float* out = static_cast<float*>(y);
+      if (four)
+        hx_launch(rmsnorm_vector_kernel<float, 4>, n_rows, 256, 0, stream, x, weight, out, rows,
+                  hidden, eps);
+      else
+        hx_launch(rmsnorm_vector_kernel<float, 8>, n_rows, 256, 0, stream, x, weight, out, rows,
+                  hidden, eps);
     } else if (out_dtype == HX_BF16) {
-      hx_launch(rmsnorm_vector_kernel<__nv_bfloat16>, n_rows, 256, 0, stream, x, weight,
-                static_cast<__nv_bfloat16*>(y), rows, hidden, eps);
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(y);
+      if (four)
+        hx_launch(rmsnorm_vector_kernel<__nv_bfloat16, 4>, n_rows, 256, 0, stream, x, weight, out,
+                  rows, hidden, eps);
+      else
+        hx_launch(rmsnorm_vector_kernel<__nv_bfloat16, 8>, n_rows, 256, 0, stream, x, weight, out,
+                  rows, hidden, eps);
     } else {
       HX_REQUIRE(false, "hx_rmsnorm: unknown dtype %d", out_dtype);
     }

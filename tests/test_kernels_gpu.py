@@ -87,7 +87,8 @@ def test_embedding_gathers_rows_and_flags_bad_ids(dtype):
 # --------------------------------------------------------------------- RMSNorm
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden,eps", [(200, 1e-5), (4104, 1e-6), (24, 1e-3)])
+@pytest.mark.parametrize("hidden,eps", [(200, 1e-5), (4104, 1e-6), (24, 1e-3), (4096, 1e-5),
+                                        (5120, 1e-5), (8192, 1e-6), (8200, 1e-5), (1022, 1e-5)])
 def test_rmsnorm(dtype, hidden, eps):
     rng = np.random.default_rng(1)
     x = (rng.normal(size=(7, hidden)) * 3.0).astype(np.float32)
