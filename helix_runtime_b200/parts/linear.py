@@ -26,8 +26,7 @@ from ..ops import library as ops
 # way against 5.4, 5.6 and 5.8 ms through the tiles of the prompt kernel, of which so few
 # tokens make fewer than there are SMs; from 192 tokens on the prompt kernel wins.)
 STREAMING_MAX_TOKENS = 128
-UNITS_FEW_TOKENS = 4.0         # units a weight stream is cut into, per SM (two CTAs share one),
-UNITS_MANY_TOKENS = 1.5        # with at most 16 tokens, and with more
+WAVE_FILL = 0.8                # share of the CTA slots of one wave that a weight stream takes
 MIN_K_BLOCKS = 8               # 64-wide reduction blocks per unit, at least
 
 
@@ -87,23 +86,28 @@ def is_weight_stream(x: torch.Tensor, w: Weight, tokens: int) -> bool:
     return tokens <= STREAMING_MAX_TOKENS and uses_tensor_cores(x, w, tokens)
 
 
-def units_per_sm(tokens: int) -> float:
-    """Work units per SM that a weight-streaming product is cut into.  Every unit ends with
-    atomic adds of tokens x 128 float32 sums: with 64 tokens, 600 units are 19 MB of them per
-    product, and fewer, longer units win (measured on the whole step, Llama-2-7B sizes:
-    batch 64 6.81 -> 6.61 ms, batch 32 4.75 -> 4.64 ms at 1.5 units per SM instead of 4; at
-    batch 8 and 1, where a unit adds 16 tokens' worth at most, 4 is best and 2 costs 5 %)."""
-    return UNITS_FEW_TOKENS if tokens <= 16 else UNITS_MANY_TOKENS
-
-
 def split_k_for(tokens: int, features: int, depth: int, ordered: bool = False) -> int:
     """Ways to cut the reduction of a weight-streaming product (1: not at all).  ``ordered``:
-    the caller wants sums in a fixed order, which atomic adds of several splits cannot give."""
+    the caller wants sums in a fixed order, which atomic adds of several splits cannot give.
+
+    A product of few tokens has too few 128-row tiles to keep every SM loading, so its tiles
+    are cut along the reduction until the CTAs fill ONE wave to about four fifths (two CTAs
+    share an SM up to 64 tokens, one has it alone above): every CTA then starts at once, each
+    ends with one round of atomic adds, and the slots left over take the CTAs of the NEXT
+    kernel, which is let in early and fetches its first weights meanwhile.  Measured on whole
+    decode steps of the Llama-2-7B sizes against cutting into four units per SM (two waves):
+    batch 1, 4, 8: 4 % less time (2.87 -> 2.75, 3.10 -> 2.98, 3.29 -> 3.16 ms), batch 16:
+    2 % less.  A wave filled to the brim (the fused QKV matrix cut three ways: 288 CTAs on 296
+    slots) costs 3 % at batch 8 and 13 % at batch 16, and a wave and a bit is as bad."""
     if tokens > STREAMING_MAX_TOKENS or ordered:
         return 1
     tiles = -(-features // 128)
     k_blocks = -(-depth // 64)
-    splits = max(1, round(units_per_sm(tokens) * ops.sm_count() / tiles))
+    sms = ops.sm_count()
+    if tokens <= 64:
+        splits = int(WAVE_FILL * 2 * sms) // tiles
+    else:
+        splits = sms // tiles
     return max(1, min(splits, k_blocks // MIN_K_BLOCKS))
 
 
