@@ -305,14 +305,26 @@ def timeline_region(options, model, config, fresh, rng) -> int:
             step.fail(entries)      # nothing is published: the next run repeats the same step
         steps = 1
     else:
-        engine = Engine(model, EngineConfig(page_size=PAGE_SIZE, max_running_requests=batch,
-                                            max_tokens_per_iteration=PREFILL_TOKENS,
-                                            num_pages=batch * -(-(length + 64) // PAGE_SIZE) + 8))
+        # the first requests decode while the prompts of the last are still being fed: every
+        # request gets tokens enough to be decoding still when the recorded steps are over
+        feeding = -(-batch * length // PREFILL_TOKENS) + batch
+        budget = min(feeding + 48, config.max_position_embeddings - length)
+        if budget < feeding + 17:
+            raise SystemExit(f"bench.py: {batch} prompts of {length} tokens leave no room to "
+                             f"decode within {config.max_position_embeddings} positions")
+        engine = Engine(model, EngineConfig(
+            page_size=PAGE_SIZE, max_running_requests=batch,
+            max_tokens_per_iteration=PREFILL_TOKENS,
+            num_pages=batch * -(-(length + budget) // PAGE_SIZE) + 8))
         for _ in range(batch):
             engine.submit([int(t) for t in rng.integers(0, config.vocab_size, length)],
-                          max_new_tokens=48)
-        while any(engine.request(r).state.value != "decoding" for r in range(batch)):
+                          max_new_tokens=budget)
+        for _ in range(4 * feeding + 16):
+            if all(engine.request(r).state.value == "decoding" for r in range(batch)):
+                break
             engine.run_iteration()
+        else:
+            raise SystemExit("bench.py: the requests did not all reach decoding")
         run, steps = engine.run_iteration, 4
     for _ in range(12 if options.timeline == "decode" else 3):
         run()
