@@ -22,7 +22,7 @@ import torch
 from ..ops import library as ops
 
 # At most this many tokens: the product is a weight stream.  (Measured on whole steps of the
-# Llama-2-7B sizes: a prompt portion of 65, 96 and 128 tokens takes 4.5, 4.8 and 5.1 ms this
+# Llama-2-7B sizes: a prompt portion of 65, 96 and 128 tokens takes 4.1, 4.4 and 4.6 ms this
 # way against 5.4, 5.6 and 5.8 ms through the tiles of the prompt kernel, of which so few
 # tokens make fewer than there are SMs; from 192 tokens on the prompt kernel wins.)
 STREAMING_MAX_TOKENS = 128
@@ -92,7 +92,7 @@ def split_k_for(tokens: int, features: int, depth: int, ordered: bool = False) -
 
     A product of few tokens has too few 128-row tiles to keep every SM loading, so its tiles
     are cut along the reduction until the CTAs fill ONE wave to about four fifths (two CTAs
-    share an SM up to 64 tokens, one has it alone above): every CTA then starts at once, each
+    share an SM): every CTA then starts at once, each
     ends with one round of atomic adds, and the slots left over take the CTAs of the NEXT
     kernel, which is let in early and fetches its first weights meanwhile.  Measured on whole
     decode steps of the Llama-2-7B sizes against cutting into four units per SM (two waves):
@@ -103,11 +103,7 @@ def split_k_for(tokens: int, features: int, depth: int, ordered: bool = False) -
         return 1
     tiles = -(-features // 128)
     k_blocks = -(-depth // 64)
-    sms = ops.sm_count()
-    if tokens <= 64:
-        splits = int(WAVE_FILL * 2 * sms) // tiles
-    else:
-        splits = sms // tiles
+    splits = int(WAVE_FILL * 2 * ops.sm_count()) // tiles
     return max(1, min(splits, k_blocks // MIN_K_BLOCKS))
 
 
