@@ -22,7 +22,7 @@ import torch
 from ..ops import library as ops
 
 # At most this many tokens: the product is a weight stream.  (Measured on whole steps of the
-# Llama-2-7B sizes: a prompt portion of 65, 96 and 128 tokens takes 4.1, 4.4 and 4.6 ms this
+# Llama-2-7B sizes: a prompt portion of 65, 96 and 128 tokens takes 3.9, 4.0 and 4.2 ms this
 # way against 5.4, 5.6 and 5.8 ms through the tiles of the prompt kernel, of which so few
 # tokens make fewer than there are SMs; from 192 tokens on the prompt kernel wins.)
 STREAMING_MAX_TOKENS = 128
