@@ -96,11 +96,12 @@ def test_many_requests_chunked_prompts_mixed_with_decoding(dtype, folders, plain
 
 
 @pytest.mark.parametrize("name,dtype", [("C", "bfloat16"), ("B", "float32")])
-@pytest.mark.parametrize("live", [24, 64])
+@pytest.mark.parametrize("live", [24, 64, 100])
 def test_decode_steps_with_dozens_of_live_requests(name, dtype, live, folders, plain_models):
-    """24 and 64 requests decode together (the benchmark's largest batch): above 16 tokens a
-    step the streaming attention is launched by another protocol and the weight-streaming
-    products take wider token tiles.  Half as many requests again wait for a slot, so pages
+    """24, 64 and 100 requests decode together (64 is the benchmark's largest batch): above 16
+    tokens a step the streaming attention is launched by another protocol and the
+    weight-streaming products take wider token tiles, up to 128 tokens, the widest, with 100.
+    Half as many requests again wait for a slot, so pages
     and slots are used again; every token of every request is checked."""
     plain = plain_models(name, dtype)
     config = tiny_config(name)
