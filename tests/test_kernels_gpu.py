@@ -705,6 +705,20 @@ def test_decode_tokens_between_long_prompt_portions(heads, kv_heads, head_dim, p
 
 
 @pytest.mark.parametrize("tensor_memory", [False, True])
+def test_prompt_portions_behind_dozens_of_decode_requests(tensor_memory):
+    """Forty decode requests come first in the step, as running requests do, and three prompt
+    portions behind them: a CTA of the prompt kernels finds its tile among requests 40 to 42,
+    beyond the first 32 it looks at."""
+    rng = np.random.default_rng(19)
+    contexts = [int(c) for c in rng.integers(1, 200, size=40)] + [0, 130, 64]
+    new_tokens = [1] * 40 + [300, 100, 70]
+    out, expected, *_ = attention_case(rng, torch.bfloat16, 2, 2, 128, 16, contexts, new_tokens,
+                                       window=None, split_keys=64, tensor_core_min=64,
+                                       tensor_memory=tensor_memory)
+    assert_close(out, expected, "attention", atol=2e-2, rtol=8e-3)
+
+
+@pytest.mark.parametrize("tensor_memory", [False, True])
 @pytest.mark.parametrize("key_position", [0, 63, 64, 200, 299])
 def test_tensor_core_attention_sees_one_far_key(key_position, tensor_memory):
     rng = np.random.default_rng(13)
