@@ -82,6 +82,24 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     return;
   }
   const T* row = table + static_cast<size_t>(id) * hidden;
+  if constexpr (sizeof(T) == 2) {
+    // rows of whole 16-byte pieces: eight values a load, all of a thread's loads in flight
+    // together (one value at a time the row is a chain of sixteen cold loads)
+    if (hidden % 8 == 0 && ((reinterpret_cast<uintptr_t>(table) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+      const uint4* pieces = reinterpret_cast<const uint4*>(row);
+      float4* wide = reinterpret_cast<float4*>(row_out);
+#pragma unroll 4
+      for (int p = threadIdx.x; p < hidden / 8; p += blockDim.x) {
+        const uint4 packed = pieces[p];
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&packed);
+        const float2 a = __bfloat1622float2(pairs[0]), b = __bfloat1622float2(pairs[1]);
+        const float2 c = __bfloat1622float2(pairs[2]), d = __bfloat1622float2(pairs[3]);
+        wide[2 * p] = make_float4(a.x, a.y, b.x, b.y);
+        wide[2 * p + 1] = make_float4(c.x, c.y, d.x, d.y);
+      }
+      return;
+    }
+  }
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_out[c] = hx_to_float<T>(row[c]);
 }
 

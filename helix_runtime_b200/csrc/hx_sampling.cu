@@ -26,14 +26,28 @@ __global__ __launch_bounds__(THREADS) void argmax_kernel(const float* __restrict
   float value = -INFINITY;
   int index = 0x7fffffff;
   bool nonfinite = false;
-  for (int c = threadIdx.x; c < vocab; c += THREADS) {
-    const float v = row[c];
+  auto take = [&](float v, int c) {
     nonfinite |= !isfinite(v);
     if (v > value) {  // strict: within a thread ids ascend, so the lowest id stays
       value = v;
       index = c;
     }
+  };
+  int done = 0;
+  if (ld % 4 == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+    // four logits a load, several loads in flight: the row is 128 KB that nobody has read yet
+    const float4* wide = reinterpret_cast<const float4*>(row);
+#pragma unroll 4
+    for (int q = threadIdx.x; q < vocab / 4; q += THREADS) {
+      const float4 v = wide[q];
+      take(v.x, 4 * q);
+      take(v.y, 4 * q + 1);
+      take(v.z, 4 * q + 2);
+      take(v.w, 4 * q + 3);
+    }
+    done = vocab / 4 * 4;
   }
+  for (int c = done + threadIdx.x; c < vocab; c += THREADS) take(row[c], c);
   if (nonfinite) bad = 1;
   best_value[threadIdx.x] = value;
   best_index[threadIdx.x] = index;
