@@ -454,13 +454,19 @@ __global__ void rope_append_pieces_kernel(
   // with many tokens the attention kernel that follows is launched when this one is done
   // (see above)
   if (release_successor) hx_pdl_trigger();
-  hx_pdl_wait();
+  // Where the piece goes and by what it turns are the step's own description and the table
+  // of angles, which no kernel of the step writes: all of that is looked up BEFORE the wait
+  // for the product, while the product still runs.  What is left after the wait is one load
+  // of the sums, the rotation and one store.
   const int token = blockIdx.x;
   const int pieces_per_head = head_dim / 8;
   const int item = blockIdx.y * blockDim.x + threadIdx.x;
   const int head = item / pieces_per_head;
   const int piece = item - head * pieces_per_head;
-  if (head >= heads + 2 * kv_heads) return;
+  if (head >= heads + 2 * kv_heads) {
+    hx_pdl_wait();      // a grid must not be seen complete before its predecessor is
+    return;
+  }
 
   const int position = positions[token];
   int page = -1, slot = 0;
@@ -521,6 +527,7 @@ __global__ void rope_append_pieces_kernel(
   if (!rotates) {
     // values, and coordinates behind the rotary part: moved as they are (a query piece that
     // came from the row is already where it belongs)
+    hx_pdl_wait();
     if (accum == nullptr && head < heads) return;
     float x[8];
     load(d0, x);
@@ -535,8 +542,6 @@ __global__ void rope_append_pieces_kernel(
   const float* sin_row = sin_table + static_cast<size_t>(table_position) * half;
   if (pairing == 0) {
     // pairs (2p, 2p + 1): this piece holds pairs d0 / 2 .. d0 / 2 + 3
-    float x[8];
-    load(d0, x);
     float cs[4], ss[4];
     if (rotary_dim % 8 == 0) {
       // the table's rows are whole 16-byte runs of four angles
@@ -554,6 +559,9 @@ __global__ void rope_append_pieces_kernel(
         ss[i] = turns ? sin_row[d0 / 2 + i] : 0.0f;
       }
     }
+    hx_pdl_wait();
+    float x[8];
+    load(d0, x);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float a = x[2 * i], b = x[2 * i + 1];
@@ -563,16 +571,20 @@ __global__ void rope_append_pieces_kernel(
     store(d0, x);
   } else {
     // pairs (p, p + half): the thread of the first-half piece rotates both pieces
-    if (d0 >= half) return;
-    float x[8], y[8];
-    load(d0, x);
-    load(d0 + half, y);
+    if (d0 >= half) {
+      hx_pdl_wait();
+      return;
+    }
     const float4 c0 = *reinterpret_cast<const float4*>(cos_row + d0);
     const float4 c1 = *reinterpret_cast<const float4*>(cos_row + d0 + 4);
     const float4 s0 = *reinterpret_cast<const float4*>(sin_row + d0);
     const float4 s1 = *reinterpret_cast<const float4*>(sin_row + d0 + 4);
     const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
     const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    hx_pdl_wait();
+    float x[8], y[8];
+    load(d0, x);
+    load(d0 + half, y);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float a = x[i], b = y[i];
